@@ -1,0 +1,170 @@
+"""Micro-benchmarks of the hot kernels against the measured roofline denominators.
+
+Usage:  python benchmarks/bench_kernels.py [--which gemm,attn,norm] [--out FILE]
+
+Timing: CUDA events on the launching stream, 5 warm-up launches, an L2 flush (a 256 MB
+memset) before every timed launch, median of the timed launches. Fractions are reported
+against ``MEASURED_PEAKS.json`` when present ("of measured"), else against the stated
+fallback figures ("of fallback").
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from parallax_b200.ops import cuda as cu  # noqa: E402
+from parallax_b200.ops import reference as ref  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], p["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+_flush = None
+
+
+def time_fn(fn, iters=10, warmup=5):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(rows):
+    hbm, tf, tag = peaks()
+    shapes = [
+        (2560, 6144, 4096), (2560, 4096, 4096), (2560, 24576, 4096), (2560, 4096, 12288),
+        (512, 6144, 4096), (512, 24576, 4096), (512, 4096, 12288),
+        (8192, 8192, 8192), (4096, 151936, 4096), (64, 4096, 4096),
+    ]
+    for M, N, K in shapes:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        flops = 2.0 * M * N * K
+        byts = 2.0 * (M * K + N * K + M * N)
+        best = None
+        for bn in (64, 128, 256):
+            ms = time_fn(lambda: cu.linear(x, w, out=out, bn=bn))
+            if best is None or ms < best[1]:
+                best = (bn, ms)
+        ms_lib = time_fn(lambda: torch.matmul(x, w.t(), out=out))
+        cu.check_status(x.device)
+        bn, ms = best
+        ideal = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3
+        rows.append({
+            "kernel": "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "bn": bn, "ms": round(ms, 4),
+            "tflops": round(flops / ms / 1e9, 1), "roofline_frac": round(ideal / ms, 3),
+            "tag": tag, "torch_matmul_ms": round(ms_lib, 4),
+        })
+        print(rows[-1], flush=True)
+        del x, w, out
+
+
+def bench_attn(rows):
+    hbm, tf, tag = peaks()
+    Hq, Hkv, D, page = 32, 8, 128, 16
+    for B, ctx in [(512, 1152), (64, 1152), (8, 32768), (256, 4096)]:
+        nb = (ctx + page - 1) // page
+        total = B * nb
+        kc = torch.randn(total, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(total, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+        bt = torch.randperm(total, device="cuda").to(torch.int32).view(B, nb)
+        cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        sc = 1.0 / math.sqrt(D)
+        ms = time_fn(lambda: cu.attn_decode(q, kc, vc, bt, cl, sc, max_ctx=ctx, out=out))
+        byts = 2.0 * B * ctx * Hkv * D * 2
+        rows.append({"kernel": "attn_decode", "B": B, "ctx": ctx, "ms": round(ms, 4),
+                     "gbs": round(byts / ms / 1e6, 1), "roofline_frac": round(byts / (hbm * 1e9) * 1e3 / ms, 3),
+                     "tag": tag})
+        print(rows[-1], flush=True)
+        del kc, vc
+    for B, L, prefix in [(2, 1024, 0), (8, 1024, 0), (1, 8192, 0), (1, 8192, 24576)]:
+        ctx = L + prefix
+        nb = (ctx + page - 1) // page
+        total = B * nb
+        kc = torch.randn(total, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(total, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+        bt = torch.randperm(total, device="cuda").to(torch.int32).view(B, nb)
+        cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        cu_q = (torch.arange(B + 1, device="cuda") * L).to(torch.int32)
+        q = torch.randn(B * L, Hq, D, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        sc = 1.0 / math.sqrt(D)
+        ms = time_fn(lambda: cu.attn_prefill(q, kc, vc, bt, cu_q, cl, L, sc, out=out), iters=5)
+        flops = 4.0 * B * Hq * D * (L * prefix + L * (L + 1) / 2)
+        rows.append({"kernel": "attn_prefill", "B": B, "L": L, "prefix": prefix, "ms": round(ms, 4),
+                     "tflops": round(flops / ms / 1e9, 1),
+                     "roofline_frac": round(flops / (tf * 1e12) * 1e3 / ms, 3), "tag": tag})
+        print(rows[-1], flush=True)
+        del kc, vc
+
+
+def bench_norm(rows):
+    hbm, tf, tag = peaks()
+    T, H = 65536, 4096
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(H, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(x)
+    ms = time_fn(lambda: cu.rmsnorm(x, w, 1e-6, out=out))
+    byts = 2.0 * T * H * 2
+    rows.append({"kernel": "rmsnorm", "T": T, "H": H, "ms": round(ms, 4), "gbs": round(byts / ms / 1e6, 1),
+                 "roofline_frac": round(byts / (hbm * 1e9) * 1e3 / ms, 3), "tag": tag})
+    print(rows[-1], flush=True)
+    logits = torch.randn(512, 151936, device="cuda").to(torch.bfloat16)
+    ms = time_fn(lambda: cu.argmax(logits))
+    byts = logits.numel() * 2.0
+    rows.append({"kernel": "argmax", "B": 512, "V": 151936, "ms": round(ms, 4),
+                 "gbs": round(byts / ms / 1e6, 1), "roofline_frac": round(byts / (hbm * 1e9) * 1e3 / ms, 3),
+                 "tag": tag})
+    print(rows[-1], flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--which", default="gemm,attn,norm")
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    rows = []
+    which = args.which.split(",")
+    if "gemm" in which:
+        bench_gemm(rows)
+    if "attn" in which:
+        bench_attn(rows)
+    if "norm" in which:
+        bench_norm(rows)
+    if args.out:
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+        with open(args.out, "w") as f:
+            json.dump(rows, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

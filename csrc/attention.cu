@@ -1,0 +1,578 @@
+// Paged GQA attention for decode (single query, split-KV) and ragged causal prefill
+// with a cached KV prefix. Cache layout: K, V = [num_blocks, Hkv, page_size, D] bf16.
+//
+// Both kernels stream 64-token K/V tiles of one KV head into swizzled shared memory
+// with cp.async (double buffered; the per-token block-table lookup makes any page size
+// work) and run QK^T / PV on the warp-level tensor path with fp32 online softmax.
+// All q heads of a KV-head group share the tile: in decode they are the rows of one
+// 16-row MMA tile and the four warps split the tile's tokens; in prefill the CTA's 64
+// rows are (token, group-head) pairs.
+//
+// Behavioural counterparts in the reference: the single-query kernel with sliding
+// window and attention sinks and its split-KV variant
+// (src/parallax_extensions/kernels/paged_attention/paged_attention.metal:794-1347),
+// and the prefix-aware prefill (src/parallax/utils/prefix_cache_utils.py:11-144).
+#include "common.cuh"
+#include "pxl_api.h"
+
+namespace {
+using namespace pxl;
+
+constexpr int TILE = 64;  // KV tokens per shared-memory tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct KVTileArgs {
+  const bf16* k_cache;
+  const bf16* v_cache;
+  const int* block_table;  // row of this sequence
+  int max_blocks;
+  int64_t num_blocks;
+  int Hkv;
+  int kvh;
+  int page_size;
+};
+
+// byte offset of 16-byte chunk `chunk` of row `row` inside a [TILE][D] bf16 tile
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  return static_cast<uint32_t>(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+// Issue cp.async loads of K and V rows for tokens [tok0, tok0+TILE) ∩ [0, hi).
+template <int D>
+__device__ __forceinline__ void load_kv_tile(const KVTileArgs& a, int tok0, int hi, uint32_t k_smem,
+                                             uint32_t v_smem, int* status) {
+  constexpr int CPR = D / 8;  // 16-byte chunks per row
+  constexpr int ITERS = TILE * CPR / 128;
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int c = i * 128 + threadIdx.x;
+    const int row = c / CPR;
+    const int chunk = c % CPR;
+    const int tok = tok0 + row;
+    bool pred = tok < hi;
+    int64_t base = 0;
+    if (pred) {
+      const int bi = tok / a.page_size;
+      const int blk = (bi < a.max_blocks) ? a.block_table[bi] : -1;
+      if (blk < 0 || blk >= a.num_blocks) {
+        pred = false;
+        if (status) atomicCAS(status, 0, PXL_DEV_BAD_INDEX);
+      } else {
+        base = ((static_cast<int64_t>(blk) * a.Hkv + a.kvh) * a.page_size + (tok % a.page_size)) *
+                   D +
+               chunk * 8;
+      }
+    }
+    const uint32_t off = tile_off<D>(row, chunk);
+    cp_async_16(k_smem + off, a.k_cache + base, pred);
+    cp_async_16(v_smem + off, a.v_cache + base, pred);
+  }
+}
+
+// S[16 x 16] += Q[16 x D] * K[tokens r0..r0+15]^T ; s[j] is the n-tile of tokens r0+8j..
+template <int D>
+__device__ __forceinline__ void qk_16x16(const uint32_t (&qf)[D / 16][4], uint32_t k_smem, int r0,
+                                         float (&s0)[4], float (&s1)[4]) {
+  const int lane = threadIdx.x & 31;
+  const int mi = lane >> 3;
+  const int row = r0 + (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t r[4];
+    ldmatrix_x4(r, k_smem + tile_off<D>(row, ks * 2 + (mi & 1)));
+    const uint32_t b0[2] = {r[0], r[1]};
+    const uint32_t b1[2] = {r[2], r[3]};
+    mma_m16n8k16_bf16(s0, qf[ks], b0);
+    mma_m16n8k16_bf16(s1, qf[ks], b1);
+  }
+}
+
+// O[16 x D] += P[16 x 16] * V[tokens r0..r0+15]
+template <int D>
+__device__ __forceinline__ void pv_16x16(const uint32_t (&pf)[4], uint32_t v_smem, int r0,
+                                         float (&o)[D / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  const int mi = lane >> 3;
+  const int row = r0 + (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+  for (int np = 0; np < D / 16; ++np) {
+    uint32_t r[4];
+    ldmatrix_x4_trans(r, v_smem + tile_off<D>(row, np * 2 + (mi >> 1)));
+    const uint32_t b0[2] = {r[0], r[1]};
+    const uint32_t b1[2] = {r[2], r[3]};
+    mma_m16n8k16_bf16(o[2 * np], pf, b0);
+    mma_m16n8k16_bf16(o[2 * np + 1], pf, b1);
+  }
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+  return v;
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  return v;
+}
+
+// =============================================================================== decode
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
+                   const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
+                   const int* __restrict__ ctx_lens, bf16* __restrict__ out,
+                   float* __restrict__ workspace, const float* __restrict__ sinks, int Hq, int Hkv,
+                   int page_size, int max_blocks, int64_t num_blocks, float scale_log2, int window,
+                   int num_splits, int* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int TILE_BYTES = TILE * D * 2;
+  const uint32_t k_smem0 = smem_u32(smem);
+  const uint32_t v_smem0 = k_smem0 + 2 * TILE_BYTES;
+
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ctx = ctx_lens[b];
+  const int hi = ctx;
+  const int lo = (window > 0 && ctx > window) ? ctx - window : 0;
+  const int tile_lo = lo / TILE;
+  const int tiles_total = hi > lo ? ceil_div(hi, TILE) - tile_lo : 0;
+  const int per_split = ceil_div(tiles_total, num_splits);
+  const int t_begin = tile_lo + split * per_split;
+  const int t_end = min(tile_lo + tiles_total, t_begin + per_split);
+
+  KVTileArgs ka{k_cache, v_cache, block_tables + static_cast<size_t>(b) * max_blocks, max_blocks,
+                num_blocks, Hkv, kvh, page_size};
+
+  // Q fragments: row r of the MMA tile is q head kvh*G + r (rows >= G are zero)
+  uint32_t qf[D / 16][4];
+  {
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const bf16* q_lo = q + (static_cast<size_t>(b) * Hq + kvh * G + r_lo) * D;
+    const bf16* q_hi = q + (static_cast<size_t>(b) * Hq + kvh * G + r_hi) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int c = ks * 16 + 2 * (lane & 3);
+      qf[ks][0] = r_lo < G ? *reinterpret_cast<const uint32_t*>(q_lo + c) : 0u;
+      qf[ks][1] = r_hi < G ? *reinterpret_cast<const uint32_t*>(q_hi + c) : 0u;
+      qf[ks][2] = r_lo < G ? *reinterpret_cast<const uint32_t*>(q_lo + c + 8) : 0u;
+      qf[ks][3] = r_hi < G ? *reinterpret_cast<const uint32_t*>(q_hi + c + 8) : 0u;
+    }
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+  int buf = 0;
+  if (t_begin < t_end) load_kv_tile<D>(ka, t_begin * TILE, hi, k_smem0, v_smem0, status);
+  cp_async_commit();
+  for (int t = t_begin; t < t_end; ++t) {
+    cp_async_wait<0>();
+    __syncthreads();
+    if (t + 1 < t_end)
+      load_kv_tile<D>(ka, (t + 1) * TILE, hi, k_smem0 + (buf ^ 1) * TILE_BYTES,
+                      v_smem0 + (buf ^ 1) * TILE_BYTES, status);
+    cp_async_commit();
+
+    const int r0 = warp * 16;
+    const int tok_base = t * TILE + r0;
+    if (tok_base < hi && tok_base + 16 > lo) {  // warp-uniform
+      float s[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      qk_16x16<D>(qf, k_smem0 + buf * TILE_BYTES, r0, s[0], s[1]);
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = tok_base + j * 8 + 2 * (lane & 3) + (e & 1);
+          const bool valid = tok < hi && tok >= lo;
+          s[j][e] = valid ? s[j][e] * scale_log2 : -INFINITY;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+        }
+      }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = quad_max(mx[h]);
+        const float m_new = fmaxf(m_run[h], mx[h]);
+        m_use[h] = (m_new == -INFINITY) ? 0.f : m_new;
+        corr[h] = exp2f(m_run[h] - m_use[h]);
+        m_run[h] = m_new;
+      }
+      float ps[2] = {0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[j][e] = exp2f(s[j][e] - m_use[e >> 1]);
+          ps[e >> 1] += s[j][e];
+        }
+      l_run[0] = l_run[0] * corr[0] + ps[0];
+      l_run[1] = l_run[1] * corr[1] + ps[1];
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+      uint32_t pf[4];
+      pf[0] = pack_bf16x2(s[0][0], s[0][1]);
+      pf[1] = pack_bf16x2(s[0][2], s[0][3]);
+      pf[2] = pack_bf16x2(s[1][0], s[1][1]);
+      pf[3] = pack_bf16x2(s[1][2], s[1][3]);
+      pv_16x16<D>(pf, v_smem0 + buf * TILE_BYTES, r0, o);
+    }
+    buf ^= 1;
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps' partial softmax states through shared memory
+  float* o_sm = reinterpret_cast<float*>(smem);          // [4][16][D]
+  float* m_sm = o_sm + 4 * 16 * D;                       // [4][16]
+  float* l_sm = m_sm + 4 * 16;                           // [4][16]
+  l_run[0] = quad_sum(l_run[0]);
+  l_run[1] = quad_sum(l_run[1]);
+  {
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    float* ow = o_sm + warp * 16 * D;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int c = i * 8 + 2 * (lane & 3);
+      ow[r_lo * D + c] = o[i][0];
+      ow[r_lo * D + c + 1] = o[i][1];
+      ow[r_hi * D + c] = o[i][2];
+      ow[r_hi * D + c + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      m_sm[warp * 16 + r_lo] = m_run[0];
+      m_sm[warp * 16 + r_hi] = m_run[1];
+      l_sm[warp * 16 + r_lo] = l_run[0];
+      l_sm[warp * 16 + r_hi] = l_run[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += 128) {
+    const int r = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, m_sm[w * 16 + r]);
+    const int head = kvh * G + r;
+    const float sink = (sinks && num_splits == 1) ? sinks[head] * kLog2e : -INFINITY;
+    const float Mx = fmaxf(M, sink);
+    const float Mu = (Mx == -INFINITY) ? 0.f : Mx;
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(m_sm[w * 16 + r] - Mu);
+      L += l_sm[w * 16 + r] * f;
+      acc += o_sm[(w * 16 + r) * D + d] * f;
+    }
+    if (num_splits == 1) {
+      const float denom = L + exp2f(sink - Mu);
+      out[(static_cast<size_t>(b) * Hq + head) * D + d] =
+          __float2bfloat16(denom > 0.f ? acc / denom : 0.f);
+    } else {
+      // partial: normalised output + log2-sum-exp
+      float* po = workspace;
+      float* plse = workspace + static_cast<size_t>(gridDim.y) * Hq * num_splits * D;
+      const size_t row = (static_cast<size_t>(b) * Hq + head) * num_splits + split;
+      po[row * D + d] = L > 0.f ? acc / L : 0.f;
+      if (d == 0) plse[row] = L > 0.f ? Mu + log2f(L) : -INFINITY;
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(D)
+attn_decode_reduce_kernel(const float* __restrict__ workspace, const float* __restrict__ sinks,
+                          bf16* __restrict__ out, int Hq, int num_splits) {
+  const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const float* po = workspace;
+  const float* plse = workspace + static_cast<size_t>(gridDim.y) * Hq * num_splits * D;
+  const size_t row0 = (static_cast<size_t>(b) * Hq + head) * num_splits;
+  const float sink = sinks ? sinks[head] * kLog2e : -INFINITY;
+  float M = sink;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, plse[row0 + s]);
+  const float Mu = (M == -INFINITY) ? 0.f : M;
+  float denom = exp2f(sink - Mu), acc = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float w = exp2f(plse[row0 + s] - Mu);
+    denom += w;
+    acc += w * po[(row0 + s) * D + d];
+  }
+  out[(static_cast<size_t>(b) * Hq + head) * D + d] =
+      __float2bfloat16(denom > 0.f ? acc / denom : 0.f);
+}
+
+// ============================================================================== prefill
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_prefill_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __restrict__ k_cache,
+                    const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
+                    const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
+                    bf16* __restrict__ out, int64_t out_stride, const float* __restrict__ sinks,
+                    int Hq, int Hkv, int page_size, int max_blocks, int64_t num_blocks,
+                    float scale_log2, int window, int* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int TILE_BYTES = TILE * D * 2;
+  const uint32_t k_smem0 = smem_u32(smem);
+  const uint32_t v_smem0 = k_smem0 + 2 * TILE_BYTES;
+
+  const int qt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int TQ = 64 / G;  // query tokens per CTA (rows = TQ * G <= 64)
+  const int q0 = cu_q[b];
+  const int q_len = cu_q[b + 1] - q0;
+  if (qt * TQ >= q_len) return;
+  const int ctx = ctx_lens[b];
+  const int prefix = ctx - q_len;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // rows owned by this thread: r_lo = warp*16 + lane/4, r_hi = r_lo + 8
+  int rtok[2], rhead[2];
+  bool rvalid[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + (lane >> 2) + h * 8;
+    const int tq = qt * TQ + r / G;
+    rvalid[h] = (r < TQ * G) && (tq < q_len);
+    rtok[h] = tq;
+    rhead[h] = kvh * G + r % G;
+  }
+  uint32_t qf[D / 16][4];
+  {
+    const bf16* q_lo = q + static_cast<size_t>(q0 + rtok[0]) * q_stride + rhead[0] * D;
+    const bf16* q_hi = q + static_cast<size_t>(q0 + rtok[1]) * q_stride + rhead[1] * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int c = ks * 16 + 2 * (lane & 3);
+      qf[ks][0] = rvalid[0] ? *reinterpret_cast<const uint32_t*>(q_lo + c) : 0u;
+      qf[ks][1] = rvalid[1] ? *reinterpret_cast<const uint32_t*>(q_hi + c) : 0u;
+      qf[ks][2] = rvalid[0] ? *reinterpret_cast<const uint32_t*>(q_lo + c + 8) : 0u;
+      qf[ks][3] = rvalid[1] ? *reinterpret_cast<const uint32_t*>(q_hi + c + 8) : 0u;
+    }
+  }
+  // visible key range per row: [rlo, rpos]
+  int rpos[2], rlo[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    rpos[h] = rvalid[h] ? prefix + rtok[h] : -1;
+    rlo[h] = (window > 0 && rpos[h] >= window) ? rpos[h] - window + 1 : 0;
+  }
+  // warp-level bounds (rows of one warp span consecutive tokens)
+  const int w_tok_first = qt * TQ + (warp * 16) / G;
+  const int w_tok_last = min(q_len - 1, qt * TQ + (warp * 16 + 15) / G);
+  const bool warp_active = (warp * 16 < TQ * G) && (w_tok_first < q_len);
+  const int w_hi = prefix + w_tok_last;  // last visible key for this warp
+  const int w_lo = (window > 0 && prefix + w_tok_first >= window) ? prefix + w_tok_first - window + 1 : 0;
+
+  // CTA-level key range
+  const int c_tok_last = min(q_len - 1, qt * TQ + TQ - 1);
+  const int c_hi = prefix + c_tok_last + 1;  // exclusive
+  const int c_lo = (window > 0 && prefix + qt * TQ >= window) ? prefix + qt * TQ - window + 1 : 0;
+  const int t_begin = c_lo / TILE;
+  const int t_end = ceil_div(c_hi, TILE);
+
+  KVTileArgs ka{k_cache, v_cache, block_tables + static_cast<size_t>(b) * max_blocks, max_blocks,
+                num_blocks, Hkv, kvh, page_size};
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+  int buf = 0;
+  load_kv_tile<D>(ka, t_begin * TILE, c_hi, k_smem0, v_smem0, status);
+  cp_async_commit();
+  for (int t = t_begin; t < t_end; ++t) {
+    cp_async_wait<0>();
+    __syncthreads();
+    if (t + 1 < t_end)
+      load_kv_tile<D>(ka, (t + 1) * TILE, c_hi, k_smem0 + (buf ^ 1) * TILE_BYTES,
+                      v_smem0 + (buf ^ 1) * TILE_BYTES, status);
+    cp_async_commit();
+
+    const int tok0 = t * TILE;
+    if (warp_active && tok0 <= w_hi && tok0 + TILE > w_lo) {
+      const uint32_t ks_addr = k_smem0 + buf * TILE_BYTES;
+      const uint32_t vs_addr = v_smem0 + buf * TILE_BYTES;
+      float s[8][4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) qk_16x16<D>(qf, ks_addr, g * 16, s[2 * g], s[2 * g + 1]);
+
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          const int tok = tok0 + j * 8 + 2 * (lane & 3) + (e & 1);
+          const bool valid = tok <= rpos[h] && tok >= rlo[h];
+          s[j][e] = valid ? s[j][e] * scale_log2 : -INFINITY;
+          mx[h] = fmaxf(mx[h], s[j][e]);
+        }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = quad_max(mx[h]);
+        const float m_new = fmaxf(m_run[h], mx[h]);
+        m_use[h] = (m_new == -INFINITY) ? 0.f : m_new;
+        corr[h] = exp2f(m_run[h] - m_use[h]);
+        m_run[h] = m_new;
+      }
+      float ps[2] = {0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[j][e] = exp2f(s[j][e] - m_use[e >> 1]);
+          ps[e >> 1] += s[j][e];
+        }
+      l_run[0] = l_run[0] * corr[0] + ps[0];
+      l_run[1] = l_run[1] * corr[1] + ps[1];
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t pf[4];
+        pf[0] = pack_bf16x2(s[2 * g][0], s[2 * g][1]);
+        pf[1] = pack_bf16x2(s[2 * g][2], s[2 * g][3]);
+        pf[2] = pack_bf16x2(s[2 * g + 1][0], s[2 * g + 1][1]);
+        pf[3] = pack_bf16x2(s[2 * g + 1][2], s[2 * g + 1][3]);
+        pv_16x16<D>(pf, vs_addr, g * 16, o);
+      }
+    }
+    buf ^= 1;
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!rvalid[h]) continue;
+    float L = quad_sum(l_run[h]);
+    float M = m_run[h];
+    const float sink = sinks ? sinks[rhead[h]] * kLog2e : -INFINITY;
+    const float Mx = fmaxf(M, sink);
+    const float Mu = (Mx == -INFINITY) ? 0.f : Mx;
+    const float f = exp2f(M - Mu);
+    const float denom = L * f + exp2f(sink - Mu);
+    const float inv = denom > 0.f ? f / denom : 0.f;
+    bf16* dst = out + static_cast<size_t>(q0 + rtok[h]) * out_stride + rhead[h] * D;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int c = i * 8 + 2 * (lane & 3);
+      *reinterpret_cast<uint32_t*>(dst + c) =
+          pack_bf16x2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+    }
+  }
+}
+
+inline int check_launch() { return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA; }
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) ==
+                 cudaSuccess
+             ? PXL_OK
+             : PXL_ERR_CUDA;
+}
+
+}  // namespace
+
+PXL_EXPORT int pxl_attn_decode_splits(int B, int Hkv, int max_ctx) {
+  const int blocks = B * Hkv;
+  const int target = 2 * pxl_host::num_sms();
+  int s = blocks >= target ? 1 : pxl::ceil_div(target, blocks);
+  const int max_by_ctx = pxl::ceil_div(max_ctx > 0 ? max_ctx : 1, 256);
+  if (s > max_by_ctx) s = max_by_ctx;
+  if (s > 64) s = 64;
+  if (s < 1) s = 1;
+  return s;
+}
+
+PXL_EXPORT int pxl_attn_decode(const void* q, const void* k_cache, const void* v_cache,
+                               const int* block_tables, const int* ctx_lens, void* out,
+                               float* workspace, const float* sinks, int B, int Hq, int Hkv, int D,
+                               int page_size, int max_blocks, int64_t num_blocks, float scale,
+                               int window, int num_splits, int max_ctx, int* status,
+                               pxl_stream_t stream) {
+  if (B <= 0) return PXL_OK;
+  if (Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16 || page_size <= 0) return PXL_ERR_INVALID_ARG;
+  if (num_splits <= 0) num_splits = pxl_attn_decode_splits(B, Hkv, max_ctx);
+  if (num_splits > 1 && workspace == nullptr) return PXL_ERR_INVALID_ARG;
+  const float scale_log2 = scale * kLog2e;
+  dim3 grid(Hkv, B, num_splits);
+#define PXL_DEC(DD)                                                                              \
+  {                                                                                              \
+    constexpr int SMEM = 4 * TILE * DD * 2 > (4 * 16 * DD + 128) * 4 ? 4 * TILE * DD * 2         \
+                                                                     : (4 * 16 * DD + 128) * 4;  \
+    static bool done = false;                                                                    \
+    if (!done) {                                                                                 \
+      if (set_smem(attn_decode_kernel<DD>, SMEM)) return PXL_ERR_CUDA;                           \
+      done = true;                                                                               \
+    }                                                                                            \
+    attn_decode_kernel<DD><<<grid, 128, SMEM, stream>>>(                                         \
+        static_cast<const bf16*>(q), static_cast<const bf16*>(k_cache),                          \
+        static_cast<const bf16*>(v_cache), block_tables, ctx_lens, static_cast<bf16*>(out),      \
+        workspace, sinks, Hq, Hkv, page_size, max_blocks, num_blocks, scale_log2, window,        \
+        num_splits, status);                                                                     \
+    if (num_splits > 1)                                                                          \
+      attn_decode_reduce_kernel<DD><<<dim3(Hq, B), DD, 0, stream>>>(                             \
+          workspace, sinks, static_cast<bf16*>(out), Hq, num_splits);                            \
+  }
+  if (D == 128) PXL_DEC(128)
+  else if (D == 64) PXL_DEC(64)
+  else return PXL_ERR_INVALID_ARG;
+#undef PXL_DEC
+  return check_launch();
+}
+
+PXL_EXPORT int pxl_attn_prefill(const void* q, int64_t q_stride, const void* k_cache,
+                                const void* v_cache, const int* block_tables, const int* cu_q,
+                                const int* ctx_lens, void* out, int64_t out_stride,
+                                const float* sinks, int B, int max_q_len, int Hq, int Hkv, int D,
+                                int page_size, int max_blocks, int64_t num_blocks, float scale,
+                                int window, int* status, pxl_stream_t stream) {
+  if (B <= 0 || max_q_len <= 0) return PXL_OK;
+  if (Hkv <= 0 || Hq % Hkv || Hq / Hkv > 64 || page_size <= 0) return PXL_ERR_INVALID_ARG;
+  const int G = Hq / Hkv;
+  const int TQ = 64 / G;
+  const float scale_log2 = scale * kLog2e;
+  dim3 grid(pxl::ceil_div(max_q_len, TQ), Hkv, B);
+#define PXL_PRE(DD)                                                                              \
+  {                                                                                              \
+    constexpr int SMEM = 4 * TILE * DD * 2;                                                      \
+    static bool done = false;                                                                    \
+    if (!done) {                                                                                 \
+      if (set_smem(attn_prefill_kernel<DD>, SMEM)) return PXL_ERR_CUDA;                          \
+      done = true;                                                                               \
+    }                                                                                            \
+    attn_prefill_kernel<DD><<<grid, 128, SMEM, stream>>>(                                        \
+        static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(k_cache),                \
+        static_cast<const bf16*>(v_cache), block_tables, cu_q, ctx_lens,                         \
+        static_cast<bf16*>(out), out_stride, sinks, Hq, Hkv, page_size, max_blocks, num_blocks,  \
+        scale_log2, window, status);                                                             \
+  }
+  if (D == 128) PXL_PRE(128)
+  else if (D == 64) PXL_PRE(64)
+  else return PXL_ERR_INVALID_ARG;
+#undef PXL_PRE
+  return check_launch();
+}

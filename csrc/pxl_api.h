@@ -1,0 +1,108 @@
+// C ABI of libpxl_kernels.so — the sm_100a kernel library of parallax_b200.
+//
+// Conventions
+//   * every pointer is a device pointer unless its name ends in `_host`;
+//   * bf16 tensors are passed as `void*`; shapes are row-major, innermost last;
+//   * `stream` is a cudaStream_t passed as an opaque pointer;
+//   * launchers return 0 (PXL_OK) or a PxlStatus error code; they never
+//     synchronise and never allocate device memory unless stated otherwise;
+//   * `status` is an optional device int. Kernels with bounded waits or index
+//     checks write a non-zero PxlStatus code there instead of trapping.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* pxl_stream_t;
+
+// GEMM epilogues
+#define PXL_EPI_NONE 0      // C = A W^T (+bias)                      bf16 out
+#define PXL_EPI_RESIDUAL 1  // C = A W^T (+bias) + residual           bf16 out
+#define PXL_EPI_SILU_MUL 2  // C[:, j] = silu(gate_j) * up_j          bf16 out, N/2 columns
+#define PXL_EPI_F32 3       // C = A W^T (+bias)                      fp32 out
+
+// ---- gemm_tcgen05.cu -------------------------------------------------------
+// C[M,N] = A[M,K] * W[N,K]^T. lda/ldw/ldc in elements. `bn` = tile width (64/128/256)
+// or 0 to pick automatically. For PXL_EPI_SILU_MUL the rows of W must be arranged in
+// groups of `bn`: bn/2 gate rows followed by the bn/2 up rows of the same outputs.
+int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* residual, const void* bias,
+                  int M, int N, int K, int lda, int ldw, int ldc, int epi, int bn, int* status,
+                  pxl_stream_t stream);
+int pxl_gemm_bf16_pick_bn(int M, int N, int epi);
+
+// ---- elementwise.cu ----------------------------------------------------------
+// out = x * rsqrt(mean(x^2) + eps) * (w + w_offset). If residual != NULL:
+// residual += x first (in place) and the norm is taken of the sum.
+int pxl_rmsnorm(const void* x, const void* weight, void* out, void* residual, int T, int H,
+                float eps, float w_offset, pxl_stream_t stream);
+// Per-head q/k RMSNorm (optional) + rotary embedding (neox pairing, first `rot_dim`
+// dims) on a packed qkv activation [T, (Hq + 2*Hkv) * D], writing q in place and
+// scattering k, v into the paged cache [blocks, Hkv, page, D] at slot_mapping[t]
+// (slot < 0: skip). cos_sin: fp32 [max_pos, rot_dim] = cos | sin halves.
+int pxl_qk_norm_rope_cache(void* qkv, const void* q_norm_w, const void* k_norm_w,
+                           const float* cos_sin, const int* positions, const int64_t* slot_mapping,
+                           void* k_cache, void* v_cache, int T, int Hq, int Hkv, int D, int rot_dim,
+                           int page_size, int64_t num_slots, float eps, float norm_w_offset,
+                           int* status, pxl_stream_t stream);
+// Plain scatter of k, v [T, Hkv, D] (row strides in elements) into the paged cache.
+int pxl_reshape_and_cache(const void* k, const void* v, int64_t k_stride, int64_t v_stride,
+                          const int64_t* slot_mapping, void* k_cache, void* v_cache, int T,
+                          int Hkv, int Dk, int Dv, int page_size, int64_t num_slots, int* status,
+                          pxl_stream_t stream);
+// out[T, I] = act(x[:, :I]) * x[:, I:]; mode 0 = silu, 1 = clipped swiglu-oai
+// (alpha 1.702, limit), 2 = gelu-tanh.
+int pxl_act_mul(const void* x, void* out, int T, int I, int mode, float limit, pxl_stream_t stream);
+// out[t, :] = table[ids[t], :]  (ids int32 or int64 per `ids_are_i64`)
+int pxl_gather_rows(const void* table, const void* ids, void* out, int T, int H, int64_t num_rows,
+                    int ids_are_i64, int* status, pxl_stream_t stream);
+// y += x (bf16), n elements (multiple of 8)
+int pxl_add_inplace(void* y, const void* x, int64_t n, pxl_stream_t stream);
+
+// ---- attention_decode.cu -----------------------------------------------------
+// Single-query GQA attention over the paged cache [blocks, Hkv, page, D] (D = 64 or 128).
+// q [B, Hq, D]; out [B, Hq, D]; block_tables [B, max_blocks]; ctx_lens [B].
+// window <= 0: full attention. sinks: optional fp32 [Hq] logits added to the
+// softmax denominator. workspace: fp32, >= B*Hq*num_splits*(D+2) floats when
+// num_splits > 1. num_splits = 0 picks automatically (see pxl_attn_decode_splits).
+int pxl_attn_decode(const void* q, const void* k_cache, const void* v_cache,
+                    const int* block_tables, const int* ctx_lens, void* out, float* workspace,
+                    const float* sinks, int B, int Hq, int Hkv, int D, int page_size,
+                    int max_blocks, int64_t num_blocks, float scale, int window, int num_splits,
+                    int max_ctx, int* status, pxl_stream_t stream);
+int pxl_attn_decode_splits(int B, int Hkv, int max_ctx);
+
+// ---- attention_prefill.cu ----------------------------------------------------
+// Ragged causal attention of new query tokens against the paged cache, which must
+// already hold K/V of the new tokens and of any cached prefix. q/out [T, Hq, D]
+// with row stride q_stride/out_stride elements; cu_q [B+1] token offsets;
+// ctx_lens[b] = prefix + new length of sequence b.
+int pxl_attn_prefill(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                     const int* block_tables, const int* cu_q, const int* ctx_lens, void* out,
+                     int64_t out_stride, const float* sinks, int B, int max_q_len, int Hq, int Hkv,
+                     int D, int page_size, int max_blocks, int64_t num_blocks, float scale,
+                     int window, int* status, pxl_stream_t stream);
+
+// ---- sampler.cu ----------------------------------------------------------------
+// Greedy arg-max over logits [B, V] (bf16 if logits_bf16 else fp32, row stride ld).
+int pxl_argmax(const void* logits, int logits_bf16, int64_t ld, int B, int V, int* out_ids,
+               float* out_logprob, pxl_stream_t stream);
+// Temperature / top-k / top-p / min-p sampling, one uniform random number per row.
+// temperature <= 0 or top_k == 1 selects arg-max for that row.
+int pxl_sample(const void* logits, int logits_bf16, int64_t ld, int B, int V,
+               const float* temperature, const int* top_k, const float* top_p, const float* min_p,
+               const float* uniform, int* out_ids, float* out_prob, pxl_stream_t stream);
+
+// ---- moe.cu ------------------------------------------------------------------
+// Router: scores [T, E] fp32/bf16 logits -> top-k expert ids and weights.
+// mode 0: softmax then top-k (optionally renormalised); mode 1: sigmoid + per-expert
+// correction bias for selection, grouped top-k (n_group/topk_group, 1/1 = none),
+// weights = sigmoid scores renormalised and scaled by routed_scale.
+int pxl_moe_route(const void* logits, int logits_bf16, const float* e_bias, int T, int E, int k,
+                  int mode, int renorm, int n_group, int topk_group, float routed_scale,
+                  int* out_ids, float* out_w, pxl_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,330 @@
+"""Torch-tensor wrappers over the sm_100a kernel library.
+
+Every function here launches hand-written CUDA kernels on the current CUDA stream of the
+tensors' device. Shapes and semantics are documented with the C ABI in ``csrc/pxl_api.h``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import EPI_F32, EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, check
+
+_status: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple[int, str], torch.Tensor] = {}
+launch_count = 0  # number of kernel-library launches issued (benchmarks report it)
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def status_tensor(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels set instead of trapping (0 = healthy)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronising read of the device status word; raises if a kernel reported an error."""
+    code = int(status_tensor(device).item())
+    if code != 0:
+        status_tensor(device).zero_()
+        raise _lib.KernelError(f"device status: {_lib.describe(code)}")
+
+
+def workspace(device: torch.device, tag: str, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, tag)
+    t = _workspaces.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+        _workspaces[key] = t
+    return t
+
+
+# ----------------------------------------------------------------------------- GEMM
+def linear(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
+    epi: int = EPI_NONE,
+    out: Optional[torch.Tensor] = None,
+    bn: int = 0,
+) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T`` on tcgen05 tensor cores with a fused epilogue."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1]
+    assert x.stride(1) == 1 and w.stride(1) == 1
+    M, K = x.shape
+    N = w.shape[0]
+    if residual is not None:
+        epi = EPI_RESIDUAL
+    n_out = N // 2 if epi == EPI_SILU_MUL else N
+    if out is None:
+        out = torch.empty(
+            (M, n_out), dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=x.device
+        )
+    if M == 0:
+        return out
+    if residual is not None:
+        assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
+    code = _lib.lib().pxl_gemm_bf16(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(bias), M, N, K,
+        x.stride(0), w.stride(0), out.stride(0), epi, bn, status_tensor(x.device).data_ptr(),
+        _stream(x.device),
+    )
+    check(code, "pxl_gemm_bf16")
+    _count()
+    return out
+
+
+def gemm_pick_bn(M: int, N: int, epi: int = EPI_NONE) -> int:
+    return _lib.lib().pxl_gemm_bf16_pick_bn(M, N, epi)
+
+
+# ---------------------------------------------------------------------- elementwise
+def rmsnorm(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float,
+    residual: Optional[torch.Tensor] = None,
+    w_offset: float = 0.0,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    T, H = x.shape
+    assert x.is_contiguous() and x.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty_like(x)
+    check(
+        _lib.lib().pxl_rmsnorm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), _ptr(residual), T,
+                               H, eps, w_offset, _stream(x.device)),
+        "pxl_rmsnorm",
+    )
+    _count()
+    return out
+
+
+def qk_norm_rope_cache(
+    qkv: torch.Tensor,
+    q_norm_w: Optional[torch.Tensor],
+    k_norm_w: Optional[torch.Tensor],
+    cos_sin: Optional[torch.Tensor],
+    positions: torch.Tensor,
+    slot_mapping: Optional[torch.Tensor],
+    k_cache: Optional[torch.Tensor],
+    v_cache: Optional[torch.Tensor],
+    num_q_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    rot_dim: int,
+    eps: float = 1e-6,
+    norm_w_offset: float = 0.0,
+) -> None:
+    """In place on ``qkv``: per-head norm + RoPE for q and k; k, v scattered to the cache."""
+    T = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (num_q_heads + 2 * num_kv_heads) * head_dim
+    assert positions.dtype == torch.int32
+    if slot_mapping is not None:
+        assert slot_mapping.dtype == torch.int64
+    page = k_cache.shape[2] if k_cache is not None else 1
+    slots = k_cache.shape[0] * page if k_cache is not None else 0
+    if cos_sin is None:
+        rot_dim = 0
+    check(
+        _lib.lib().pxl_qk_norm_rope_cache(
+            qkv.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin), positions.data_ptr(),
+            _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), T, num_q_heads, num_kv_heads,
+            head_dim, rot_dim, page, slots, eps, norm_w_offset,
+            status_tensor(qkv.device).data_ptr(), _stream(qkv.device)),
+        "pxl_qk_norm_rope_cache",
+    )
+    _count()
+
+
+def reshape_and_cache(
+    k: Optional[torch.Tensor],
+    v: Optional[torch.Tensor],
+    slot_mapping: torch.Tensor,
+    k_cache: Optional[torch.Tensor],
+    v_cache: Optional[torch.Tensor],
+) -> None:
+    """Scatter k, v ``[T, H, D]`` into paged caches ``[blocks, H, page, D]``."""
+    ref = k if k is not None else v
+    T = ref.shape[0]
+    cache = k_cache if k_cache is not None else v_cache
+    Hkv, page = cache.shape[1], cache.shape[2]
+    Dk = k_cache.shape[3] if k_cache is not None else 0
+    Dv = v_cache.shape[3] if v_cache is not None else 0
+    check(
+        _lib.lib().pxl_reshape_and_cache(
+            _ptr(k), _ptr(v), k.stride(0) if k is not None else 0,
+            v.stride(0) if v is not None else 0, slot_mapping.data_ptr(), _ptr(k_cache),
+            _ptr(v_cache), T, Hkv, Dk, Dv, page, cache.shape[0] * page,
+            status_tensor(ref.device).data_ptr(), _stream(ref.device)),
+        "pxl_reshape_and_cache",
+    )
+    _count()
+
+
+def act_mul(x: torch.Tensor, mode: int = 0, limit: float = 7.0) -> torch.Tensor:
+    T, I2 = x.shape
+    out = torch.empty((T, I2 // 2), dtype=x.dtype, device=x.device)
+    check(_lib.lib().pxl_act_mul(x.data_ptr(), out.data_ptr(), T, I2 // 2, mode, limit,
+                                 _stream(x.device)), "pxl_act_mul")
+    _count()
+    return out
+
+
+def gather_rows(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T, H = ids.numel(), table.shape[1]
+    assert table.is_contiguous() and ids.dtype in (torch.int32, torch.int64)
+    if out is None:
+        out = torch.empty((T, H), dtype=table.dtype, device=table.device)
+    check(
+        _lib.lib().pxl_gather_rows(table.data_ptr(), ids.data_ptr(), out.data_ptr(), T, H,
+                                   table.shape[0], int(ids.dtype == torch.int64),
+                                   status_tensor(table.device).data_ptr(), _stream(table.device)),
+        "pxl_gather_rows",
+    )
+    _count()
+    return out
+
+
+def add_inplace(y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    assert y.is_contiguous() and x.is_contiguous() and y.numel() == x.numel()
+    check(_lib.lib().pxl_add_inplace(y.data_ptr(), x.data_ptr(), y.numel(), _stream(y.device)),
+          "pxl_add_inplace")
+    _count()
+    return y
+
+
+# ------------------------------------------------------------------------ attention
+def attn_decode(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    ctx_lens: torch.Tensor,
+    scale: float,
+    window: int = 0,
+    sinks: Optional[torch.Tensor] = None,
+    max_ctx: int = 0,
+    num_splits: int = 0,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """q ``[B, Hq, D]`` (last dim contiguous, packed heads) against the paged cache."""
+    B, Hq, D = q.shape
+    assert q.is_contiguous()
+    Hkv, page = k_cache.shape[1], k_cache.shape[2]
+    if out is None:
+        out = torch.empty_like(q)
+    if max_ctx <= 0:
+        max_ctx = block_tables.shape[1] * page
+    if num_splits <= 0:
+        num_splits = _lib.lib().pxl_attn_decode_splits(B, Hkv, max_ctx)
+    ws = None
+    if num_splits > 1:
+        ws = workspace(q.device, "attn_decode", B * Hq * num_splits * (D + 2) * 4)
+    check(
+        _lib.lib().pxl_attn_decode(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+            ctx_lens.data_ptr(), out.data_ptr(), _ptr(ws), _ptr(sinks), B, Hq, Hkv, D, page,
+            block_tables.shape[1], k_cache.shape[0], scale, window, num_splits, max_ctx,
+            status_tensor(q.device).data_ptr(), _stream(q.device)),
+        "pxl_attn_decode",
+    )
+    _count(2 if num_splits > 1 else 1)
+    return out
+
+
+def attn_prefill(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    cu_q: torch.Tensor,
+    ctx_lens: torch.Tensor,
+    max_q_len: int,
+    scale: float,
+    window: int = 0,
+    sinks: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """q ``[T, Hq, D]`` (may be a strided view into a packed qkv buffer)."""
+    T, Hq, D = q.shape
+    assert q.stride(2) == 1 and q.stride(1) == D
+    Hkv, page = k_cache.shape[1], k_cache.shape[2]
+    if out is None:
+        out = torch.empty((T, Hq, D), dtype=q.dtype, device=q.device)
+    B = ctx_lens.numel()
+    check(
+        _lib.lib().pxl_attn_prefill(
+            q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            block_tables.data_ptr(), cu_q.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(),
+            out.stride(0), _ptr(sinks), B, max_q_len, Hq, Hkv, D, page, block_tables.shape[1],
+            k_cache.shape[0], scale, window, status_tensor(q.device).data_ptr(),
+            _stream(q.device)),
+        "pxl_attn_prefill",
+    )
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, want_logprob: bool = False):
+    B, V = logits.shape
+    assert logits.stride(1) == 1 and logits.dtype in (torch.bfloat16, torch.float32)
+    ids = torch.empty(B, dtype=torch.int32, device=logits.device)
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device) if want_logprob else None
+    check(_lib.lib().pxl_argmax(logits.data_ptr(), int(logits.dtype == torch.bfloat16),
+                                logits.stride(0), B, V, ids.data_ptr(), _ptr(lp),
+                                _stream(logits.device)), "pxl_argmax")
+    _count()
+    return (ids, lp) if want_logprob else ids
+
+
+def sample(
+    logits: torch.Tensor,
+    temperature: torch.Tensor,
+    top_k: torch.Tensor,
+    top_p: torch.Tensor,
+    min_p: torch.Tensor,
+    uniform: torch.Tensor,
+    want_prob: bool = False,
+):
+    B, V = logits.shape
+    assert logits.stride(1) == 1
+    ids = torch.empty(B, dtype=torch.int32, device=logits.device)
+    pr = torch.empty(B, dtype=torch.float32, device=logits.device) if want_prob else None
+    check(
+        _lib.lib().pxl_sample(logits.data_ptr(), int(logits.dtype == torch.bfloat16),
+                              logits.stride(0), B, V, temperature.data_ptr(), top_k.data_ptr(),
+                              top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(),
+                              ids.data_ptr(), _ptr(pr), _stream(logits.device)),
+        "pxl_sample",
+    )
+    _count()
+    return (ids, pr) if want_prob else ids
+
+
+def as_c_int_p(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr())

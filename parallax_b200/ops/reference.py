@@ -1,0 +1,275 @@
+"""Plain-PyTorch restatement of every op (the correctness oracle and the CPU path).
+
+These functions accept the same arguments as :mod:`parallax_b200.ops.cuda`, run on any
+device and dtype, and compute in fp32 internally. They restate the arithmetic of the
+reference's Metal compute kernels (which have no CPU implementation of their own):
+single-query paged attention with sliding window and sinks
+(``src/parallax_extensions/kernels/paged_attention/paged_attention.metal:794-1234``), the
+cache scatter (``.../reshape_and_cache/reshape_and_cache.metal:32-96``), and the sampler
+(``src/parallax/server/sampling/sampler.py:65-120``).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32 = 0, 1, 2, 3
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, bn: int = 128) -> torch.Tensor:
+    """Arrange gate/up weight rows for the fused SiLU-mul GEMM epilogue.
+
+    Rows are grouped in blocks of ``bn``: ``bn/2`` gate rows followed by the ``bn/2`` up rows
+    of the same output columns.
+    """
+    I, K = w_gate.shape
+    h = bn // 2
+    assert I % h == 0
+    g = w_gate.reshape(I // h, h, K)
+    u = w_up.reshape(I // h, h, K)
+    return torch.cat([g, u], dim=1).reshape(2 * I, K).contiguous()
+
+
+def linear(x, w, bias=None, residual=None, epi: int = EPI_NONE, out=None, bn: int = 128):
+    y = x.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if residual is not None:
+        y = y + residual.float()
+        epi = EPI_RESIDUAL
+    if epi == EPI_SILU_MUL:
+        N = w.shape[0]
+        bn = bn or 128
+        h = bn // 2
+        yb = y.reshape(y.shape[0], N // bn, 2, h)
+        y = (torch.nn.functional.silu(yb[:, :, 0]) * yb[:, :, 1]).reshape(y.shape[0], N // 2)
+    res = y if epi == EPI_F32 else y.to(x.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def rmsnorm(x, weight, eps, residual=None, w_offset: float = 0.0, out=None):
+    xf = x.float()
+    if residual is not None:
+        s = (xf + residual.float()).to(x.dtype)
+        residual.copy_(s)
+        xf = s.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    y = (xf * inv * (weight.float() + w_offset)).to(x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def build_cos_sin(max_pos: int, rot_dim: int, base: float, device=None, inv_freq=None,
+                  attention_factor: float = 1.0) -> torch.Tensor:
+    """fp32 table ``[max_pos, rot_dim]``: cos in the first half of each row, sin in the second."""
+    if inv_freq is None:
+        inv_freq = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+    t = torch.arange(max_pos, dtype=torch.float64)
+    freqs = torch.outer(t, inv_freq.double())
+    tab = torch.cat([freqs.cos(), freqs.sin()], dim=-1) * attention_factor
+    return tab.float().to(device) if device is not None else tab.float()
+
+
+def _scatter_cache(cache, x, slot_mapping):
+    # cache [blocks, H, page, D]; x [T, H, D]
+    page = cache.shape[2]
+    valid = slot_mapping >= 0
+    if not bool(valid.any()):
+        return
+    slots = slot_mapping[valid]
+    blk = slots // page
+    off = slots % page
+    cache[blk, :, off, :] = x[valid].to(cache.dtype)
+
+
+def qk_norm_rope_cache(qkv, q_norm_w, k_norm_w, cos_sin, positions, slot_mapping, k_cache,
+                       v_cache, num_q_heads, num_kv_heads, head_dim, rot_dim, eps=1e-6,
+                       norm_w_offset: float = 0.0):
+    T = qkv.shape[0]
+    Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
+    x = qkv.view(T, Hq + 2 * Hkv, D)
+    q, k, v = x[:, :Hq], x[:, Hq:Hq + Hkv], x[:, Hq + Hkv:]
+
+    def norm(t, w):
+        if w is None:
+            return t.float()
+        tf = t.float()
+        inv = torch.rsqrt(tf.pow(2).mean(-1, keepdim=True) + eps)
+        return (tf * inv * (w.float() + norm_w_offset)).to(qkv.dtype).float()
+
+    def rope(t):
+        if cos_sin is None or rot_dim == 0:
+            return t
+        half = rot_dim // 2
+        cs = cos_sin[positions.long()].float()  # [T, rot_dim]
+        cos, sin = cs[:, None, :half], cs[:, None, half:]
+        x1, x2 = t[..., :half], t[..., half:rot_dim]
+        out = t.clone()
+        out[..., :half] = x1 * cos - x2 * sin
+        out[..., half:rot_dim] = x2 * cos + x1 * sin
+        return out
+
+    qn = rope(norm(q, q_norm_w)).to(qkv.dtype)
+    kn = rope(norm(k, k_norm_w)).to(qkv.dtype)
+    q.copy_(qn)
+    if k_cache is not None and slot_mapping is not None:
+        _scatter_cache(k_cache, kn, slot_mapping)
+        _scatter_cache(v_cache, v, slot_mapping)
+    else:
+        k.copy_(kn)
+
+
+def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache):
+    if k is not None and k_cache is not None:
+        _scatter_cache(k_cache, k, slot_mapping)
+    if v is not None and v_cache is not None:
+        _scatter_cache(v_cache, v, slot_mapping)
+
+
+def act_mul(x, mode: int = 0, limit: float = 7.0):
+    I = x.shape[-1] // 2
+    g, u = x[..., :I].float(), x[..., I:].float()
+    if mode == 0:
+        y = torch.nn.functional.silu(g) * u
+    elif mode == 1:
+        g = g.clamp(max=limit)
+        u = u.clamp(min=-limit, max=limit)
+        y = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+    else:
+        y = torch.nn.functional.gelu(g, approximate="tanh") * u
+    return y.to(x.dtype)
+
+
+def gather_rows(table, ids, out=None):
+    y = table[ids.long()]
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def add_inplace(y, x):
+    y.add_(x)
+    return y
+
+
+def _gather_kv(cache, block_table, n):
+    # cache [blocks, H, page, D] -> [H, n, D]
+    page = cache.shape[2]
+    nb = (n + page - 1) // page
+    blocks = cache[block_table[:nb].long()]  # [nb, H, page, D]
+    return blocks.permute(1, 0, 2, 3).reshape(cache.shape[1], nb * page, cache.shape[3])[:, :n]
+
+
+def _attend(q, k, v, scale, q_pos, window, sinks):
+    # q [Lq, Hq, D]; k, v [Hkv, Lk, D]; q_pos [Lq] absolute positions of the queries
+    Lq, Hq, D = q.shape
+    Hkv, Lk, _ = k.shape
+    G = Hq // Hkv
+    qf = q.float().permute(1, 0, 2)  # [Hq, Lq, D]
+    kf = k.float().repeat_interleave(G, dim=0)
+    vf = v.float().repeat_interleave(G, dim=0)
+    s = torch.einsum("hqd,hkd->hqk", qf, kf) * scale
+    kpos = torch.arange(Lk, device=q.device)[None, :]
+    mask = kpos <= q_pos[:, None]
+    if window and window > 0:
+        mask = mask & (kpos > q_pos[:, None] - window)
+    s = s.masked_fill(~mask[None], float("-inf"))
+    if sinks is not None:
+        s = torch.cat([s, sinks.float()[:, None, None].expand(Hq, Lq, 1)], dim=-1)
+    p = torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p, nan=0.0)
+    if sinks is not None:
+        p = p[..., :-1]
+    o = torch.einsum("hqk,hkd->hqd", p, vf)
+    return o.permute(1, 0, 2).to(q.dtype)
+
+
+def attn_decode(q, k_cache, v_cache, block_tables, ctx_lens, scale, window=0, sinks=None,
+                max_ctx=0, num_splits=0, out=None):
+    B = q.shape[0]
+    res = torch.zeros_like(q) if out is None else out
+    for b in range(B):
+        n = int(ctx_lens[b])
+        if n <= 0:
+            res[b] = 0
+            continue
+        k = _gather_kv(k_cache, block_tables[b], n)
+        v = _gather_kv(v_cache, block_tables[b], n)
+        pos = torch.tensor([n - 1], device=q.device)
+        res[b] = _attend(q[b:b + 1], k, v, scale, pos, window, sinks)[0]
+    return res
+
+
+def attn_prefill(q, k_cache, v_cache, block_tables, cu_q, ctx_lens, max_q_len, scale, window=0,
+                 sinks=None, out=None):
+    T, Hq, D = q.shape
+    res = torch.zeros((T, Hq, D), dtype=q.dtype, device=q.device) if out is None else out
+    B = ctx_lens.numel()
+    for b in range(B):
+        s, e = int(cu_q[b]), int(cu_q[b + 1])
+        if e <= s:
+            continue
+        n = int(ctx_lens[b])
+        prefix = n - (e - s)
+        k = _gather_kv(k_cache, block_tables[b], n)
+        v = _gather_kv(v_cache, block_tables[b], n)
+        pos = prefix + torch.arange(e - s, device=q.device)
+        res[s:e] = _attend(q[s:e], k, v, scale, pos, window, sinks)
+    return res
+
+
+def argmax(logits, want_logprob: bool = False):
+    lf = logits.float()
+    ids = lf.argmax(dim=-1).to(torch.int32)
+    if want_logprob:
+        lp = torch.log_softmax(lf, dim=-1).gather(1, ids.long()[:, None])[:, 0]
+        return ids, lp
+    return ids
+
+
+def sample(logits, temperature, top_k, top_p, min_p, uniform, want_prob: bool = False):
+    """Sort-based sampler with the reference's filter order; one uniform number per row."""
+    B, V = logits.shape
+    lf = logits.float()
+    ids = torch.empty(B, dtype=torch.int32, device=logits.device)
+    probs_out = torch.empty(B, dtype=torch.float32, device=logits.device)
+    for b in range(B):
+        t = float(temperature[b])
+        k = int(top_k[b])
+        if t <= 0 or k == 1:
+            i = int(lf[b].argmax())
+            ids[b] = i
+            probs_out[b] = torch.softmax(lf[b] / (t if t > 0 else 1.0), -1)[i]
+            continue
+        p = torch.softmax(lf[b] / t, dim=-1)
+        ps, idx = torch.sort(p, descending=True, stable=True)
+        csum = torch.cumsum(ps, 0)
+        keep = torch.ones(V, dtype=torch.bool, device=logits.device)
+        if k > 0:
+            keep &= torch.arange(V, device=logits.device) < k
+        keep &= (csum - ps) <= float(top_p[b])
+        keep &= ps >= ps[0] * float(min_p[b])
+        kept_ids = idx[keep]
+        # draw in index order so that the same uniform number picks the same token as the kernel
+        order = torch.sort(kept_ids).values
+        w = p[order]
+        c = torch.cumsum(w, 0)
+        target = float(uniform[b]) * float(c[-1])
+        j = int(torch.searchsorted(c, torch.tensor(target, device=c.device), right=True))
+        j = min(j, order.numel() - 1)
+        ids[b] = order[j].to(torch.int32)
+        probs_out[b] = p[order[j]]
+    return (ids, probs_out) if want_prob else ids
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)

@@ -1,0 +1,240 @@
+"""Numerics of the sm_100a kernels against the plain-PyTorch fp32 restatement of each op."""
+
+import math
+
+import pytest
+import torch
+
+from parallax_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cu():
+    from parallax_b200.ops import cuda
+
+    return cuda
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+@pytest.mark.parametrize(
+    "M,N,K,bn",
+    [
+        (128, 256, 64, 256),
+        (128, 256, 512, 128),
+        (256, 512, 1024, 64),
+        (200, 384, 320, 0),       # M tail, K not a multiple of the 64-wide stage
+        (1, 4096, 4096, 0),       # decode-like
+        (1000, 6144, 4096, 0),    # qkv-like, multi-tile persistent loop
+        (2560, 4096, 4096, 256),
+    ],
+)
+def test_gemm_bf16(cu, M, N, K, bn):
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device=_dev(), dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=_dev(), dtype=torch.bfloat16) * 0.05)
+    y = cu.linear(x, w, bn=bn)
+    torch.cuda.synchronize()
+    cu.check_status(_dev())
+    want = x.float() @ w.float().t()
+    assert _rel_err(y, want) < 5e-3
+    assert torch.isfinite(y.float()).all()
+
+
+def test_gemm_epilogues(cu):
+    torch.manual_seed(1)
+    M, N, K = 300, 1024, 768
+    x = torch.randn(M, K, device=_dev(), dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=_dev(), dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=_dev(), dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=_dev(), dtype=torch.bfloat16)
+    y = cu.linear(x, w, bias=bias, residual=res)
+    want = ref.linear(x, w, bias=bias, residual=res)
+    assert _rel_err(y, want) < 5e-3
+    y32 = cu.linear(x, w, epi=ref.EPI_F32)
+    assert y32.dtype == torch.float32
+    assert _rel_err(y32, x.float() @ w.float().t()) < 1e-3
+    # fused SiLU-mul: weights interleaved per tile
+    I = 512
+    wg = torch.randn(I, K, device=_dev(), dtype=torch.bfloat16) * 0.05
+    wu = torch.randn(I, K, device=_dev(), dtype=torch.bfloat16) * 0.05
+    for bn in (64, 128, 256):
+        wi = ref.interleave_gate_up(wg, wu, bn)
+        y = cu.linear(x, wi, epi=ref.EPI_SILU_MUL, bn=bn)
+        want = torch.nn.functional.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+        assert y.shape == (M, I)
+        assert _rel_err(y, want) < 1e-2
+    cu.check_status(_dev())
+
+
+def test_rmsnorm(cu):
+    torch.manual_seed(2)
+    x = torch.randn(37, 4096, device=_dev(), dtype=torch.bfloat16)
+    w = torch.randn(4096, device=_dev(), dtype=torch.bfloat16)
+    y = cu.rmsnorm(x, w, 1e-6)
+    assert _rel_err(y, ref.rmsnorm(x, w, 1e-6)) < 5e-3
+    r1 = torch.randn_like(x)
+    r2 = r1.clone()
+    y = cu.rmsnorm(x, w, 1e-6, residual=r1, w_offset=1.0)
+    want = ref.rmsnorm(x, w, 1e-6, residual=r2, w_offset=1.0)
+    assert _rel_err(y, want) < 5e-3
+    assert _rel_err(r1, r2) < 1e-3
+
+
+@pytest.mark.parametrize("D,rot", [(128, 128), (64, 64), (128, 64)])
+def test_qk_norm_rope_cache(cu, D, rot):
+    torch.manual_seed(3)
+    T, Hq, Hkv, page, blocks = 50, 8, 2, 16, 12
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=_dev(), dtype=torch.bfloat16)
+    qn = torch.randn(D, device=_dev(), dtype=torch.bfloat16)
+    kn = torch.randn(D, device=_dev(), dtype=torch.bfloat16)
+    cs = ref.build_cos_sin(512, rot, 1e6, device=_dev())
+    pos = torch.randint(0, 512, (T,), device=_dev(), dtype=torch.int32)
+    slots = torch.randperm(blocks * page, device=_dev())[:T].to(torch.int64)
+    slots[5] = -1
+    kc = torch.zeros(blocks, Hkv, page, D, device=_dev(), dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q1, q2 = qkv.clone(), qkv.clone()
+    cu.qk_norm_rope_cache(q1, qn, kn, cs, pos, slots, kc, vc, Hq, Hkv, D, rot)
+    ref.qk_norm_rope_cache(q2, qn, kn, cs, pos, slots, kc2, vc2, Hq, Hkv, D, rot)
+    assert _rel_err(q1[:, : Hq * D], q2[:, : Hq * D]) < 1e-2
+    assert _rel_err(kc, kc2) < 1e-2
+    assert _rel_err(vc, vc2) < 1e-6
+    cu.check_status(_dev())
+
+
+def test_act_gather_add(cu):
+    torch.manual_seed(4)
+    x = torch.randn(33, 2 * 1536, device=_dev(), dtype=torch.bfloat16)
+    for mode in (0, 1, 2):
+        assert _rel_err(cu.act_mul(x, mode), ref.act_mul(x, mode)) < 1e-2
+    table = torch.randn(1000, 1024, device=_dev(), dtype=torch.bfloat16)
+    ids = torch.randint(0, 1000, (77,), device=_dev())
+    assert torch.equal(cu.gather_rows(table, ids), table[ids])
+    assert torch.equal(cu.gather_rows(table, ids.to(torch.int32)), table[ids])
+    a = torch.randn(64, 1024, device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn_like(a)
+    want = (a.float() + b.float()).to(torch.bfloat16)
+    cu.add_inplace(a, b)
+    assert torch.equal(a, want)
+
+
+def _make_paged(B, ctx_lens, Hkv, D, page, extra_blocks=3):
+    dev = _dev()
+    max_blocks = max((n + page - 1) // page for n in ctx_lens) + 1
+    total = sum((n + page - 1) // page for n in ctx_lens) + extra_blocks
+    perm = torch.randperm(total, device=dev).to(torch.int32)
+    bt = torch.zeros(B, max_blocks, dtype=torch.int32, device=dev)
+    o = 0
+    for b, n in enumerate(ctx_lens):
+        nb = (n + page - 1) // page
+        bt[b, :nb] = perm[o:o + nb]
+        o += nb
+    kc = torch.randn(total, Hkv, page, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn(total, Hkv, page, D, device=dev, dtype=torch.bfloat16)
+    return kc, vc, bt
+
+
+@pytest.mark.parametrize(
+    "Hq,Hkv,D,page,window,use_sinks,splits",
+    [
+        (32, 8, 128, 16, 0, False, 1),
+        (32, 8, 128, 16, 0, False, 4),
+        (16, 8, 128, 32, 0, False, 0),
+        (8, 8, 64, 16, 0, False, 1),
+        (28, 4, 128, 16, 0, False, 2),     # group of 7 q heads per kv head
+        (32, 8, 128, 16, 100, True, 1),    # sliding window + attention sinks
+        (32, 8, 128, 1, 0, False, 3),      # page size 1
+        (64, 8, 64, 8, 300, True, 3),
+    ],
+)
+def test_attn_decode(cu, Hq, Hkv, D, page, window, use_sinks, splits):
+    torch.manual_seed(5)
+    ctx = [1, 17, 64, 65, 300, 1023, 512]
+    B = len(ctx)
+    kc, vc, bt = _make_paged(B, ctx, Hkv, D, page)
+    q = torch.randn(B, Hq, D, device=_dev(), dtype=torch.bfloat16)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=_dev())
+    sinks = torch.randn(Hq, device=_dev()) if use_sinks else None
+    scale = 1.0 / math.sqrt(D)
+    y = cu.attn_decode(q, kc, vc, bt, cl, scale, window=window, sinks=sinks, num_splits=splits,
+                       max_ctx=max(ctx))
+    want = ref.attn_decode(q, kc, vc, bt, cl, scale, window=window, sinks=sinks)
+    cu.check_status(_dev())
+    assert _rel_err(y, want) < 2e-2
+    for b in range(B):
+        assert _rel_err(y[b], want[b]) < 3e-2, f"seq {b} ctx {ctx[b]}"
+
+
+@pytest.mark.parametrize(
+    "Hq,Hkv,D,page,window,use_sinks",
+    [
+        (32, 8, 128, 16, 0, False),
+        (16, 2, 128, 16, 0, False),   # 8 q heads per kv head
+        (8, 8, 64, 32, 0, False),
+        (28, 4, 128, 16, 0, False),
+        (16, 4, 128, 16, 70, True),
+    ],
+)
+def test_attn_prefill(cu, Hq, Hkv, D, page, window, use_sinks):
+    torch.manual_seed(6)
+    # (new tokens, cached prefix)
+    seqs = [(1, 0), (5, 0), (64, 0), (130, 0), (33, 48), (200, 160), (1, 77)]
+    B = len(seqs)
+    ctx = [a + b for a, b in seqs]
+    kc, vc, bt = _make_paged(B, ctx, Hkv, D, page)
+    T = sum(a for a, _ in seqs)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=_dev(), dtype=torch.bfloat16)
+    q = qkv.view(T, Hq + 2 * Hkv, D)[:, :Hq]  # strided view like the model uses
+    cu_q = torch.tensor([0] + list(torch.tensor([a for a, _ in seqs]).cumsum(0)),
+                        dtype=torch.int32, device=_dev())
+    cl = torch.tensor(ctx, dtype=torch.int32, device=_dev())
+    sinks = torch.randn(Hq, device=_dev()) if use_sinks else None
+    scale = 1.0 / math.sqrt(D)
+    y = cu.attn_prefill(q, kc, vc, bt, cu_q, cl, max(a for a, _ in seqs), scale, window=window,
+                        sinks=sinks)
+    want = ref.attn_prefill(q, kc, vc, bt, cu_q, cl, 0, scale, window=window, sinks=sinks)
+    cu.check_status(_dev())
+    assert _rel_err(y, want) < 2e-2
+    for b in range(B):
+        s, e = int(cu_q[b]), int(cu_q[b + 1])
+        assert _rel_err(y[s:e], want[s:e]) < 3e-2, f"seq {b} {seqs[b]}"
+
+
+def test_argmax_and_sample(cu):
+    torch.manual_seed(7)
+    B, V = 9, 151936
+    logits = (torch.randn(B, V, device=_dev()) * 3).to(torch.bfloat16)
+    ids, lp = cu.argmax(logits, want_logprob=True)
+    lf = logits.float()
+    assert torch.equal(lf.gather(1, ids.long()[:, None])[:, 0], lf.max(dim=-1).values)
+    want_lp = torch.log_softmax(lf, -1).gather(1, ids.long()[:, None])[:, 0]
+    assert torch.allclose(lp, want_lp, atol=1e-2)
+    ids32 = cu.argmax(lf)
+    assert torch.equal(ids32, lf.argmax(-1).to(torch.int32))
+
+    temperature = torch.tensor([0.0, 1.0, 0.7, 1.3, 1.0, 1.0, 0.5, 1.0, 2.0], device=_dev())
+    top_k = torch.tensor([0, 0, 50, 0, 1, 20, 0, 0, 1000], dtype=torch.int32, device=_dev())
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.9, 1.0, 0.8, 0.95, 1.0, 0.5], device=_dev())
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0, 0.05, 0.0, 0.1, 0.0], device=_dev())
+    for trial in range(4):
+        u = torch.rand(B, device=_dev())
+        got, pr = cu.sample(logits, temperature, top_k, top_p, min_p, u, want_prob=True)
+        want, wpr = ref.sample(logits, temperature, top_k, top_p, min_p, u, want_prob=True)
+        # the draw is a prefix-sum walk: rounding may move it across a token boundary, so
+        # accept any token whose kept-set probability interval is within rounding of u
+        same = (got == want)
+        assert same.float().mean() >= 0.75, (got, want)
+        assert torch.allclose(pr[same], wpr[same], rtol=5e-2, atol=1e-6)
+    # top_k = 1 and temperature 0 rows are exact
+    assert int(got[0]) == int(lf[0].argmax()) and int(got[4]) == int(lf[4].argmax())
