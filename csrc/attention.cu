@@ -120,7 +120,7 @@ __device__ __forceinline__ float quad_sum(float v) {
 // =============================================================================== decode
 template <int D>
 __global__ void __launch_bounds__(128)
-attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
+attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __restrict__ k_cache,
                    const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
                    const int* __restrict__ ctx_lens, bf16* __restrict__ out,
                    float* __restrict__ workspace, const float* __restrict__ sinks, int Hq, int Hkv,
@@ -150,8 +150,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
   uint32_t qf[D / 16][4];
   {
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
-    const bf16* q_lo = q + (static_cast<size_t>(b) * Hq + kvh * G + r_lo) * D;
-    const bf16* q_hi = q + (static_cast<size_t>(b) * Hq + kvh * G + r_hi) * D;
+    const bf16* q_lo = q + static_cast<size_t>(b) * q_stride + (kvh * G + r_lo) * D;
+    const bf16* q_hi = q + static_cast<size_t>(b) * q_stride + (kvh * G + r_hi) * D;
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       const int c = ks * 16 + 2 * (lane & 3);
@@ -507,7 +507,8 @@ PXL_EXPORT int pxl_attn_decode_splits(int B, int Hkv, int max_ctx) {
   return s;
 }
 
-PXL_EXPORT int pxl_attn_decode(const void* q, const void* k_cache, const void* v_cache,
+PXL_EXPORT int pxl_attn_decode(const void* q, int64_t q_stride, const void* k_cache,
+                               const void* v_cache,
                                const int* block_tables, const int* ctx_lens, void* out,
                                float* workspace, const float* sinks, int B, int Hq, int Hkv, int D,
                                int page_size, int max_blocks, int64_t num_blocks, float scale,
@@ -529,7 +530,7 @@ PXL_EXPORT int pxl_attn_decode(const void* q, const void* k_cache, const void* v
       done = true;                                                                               \
     }                                                                                            \
     attn_decode_kernel<DD><<<grid, 128, SMEM, stream>>>(                                         \
-        static_cast<const bf16*>(q), static_cast<const bf16*>(k_cache),                          \
+        static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(k_cache),                \
         static_cast<const bf16*>(v_cache), block_tables, ctx_lens, static_cast<bf16*>(out),      \
         workspace, sinks, Hq, Hkv, page_size, max_blocks, num_blocks, scale_log2, window,        \
         num_splits, status);                                                                     \

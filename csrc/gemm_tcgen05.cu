@@ -179,28 +179,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row = m_blk * BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       if constexpr (EPI == PXL_EPI_SILU_MUL) {
-        // columns [0,BN/2) of the tile hold gate, [BN/2,BN) hold up for the same outputs
-        constexpr int HN = BN / 2;
-        const int out_col0 = n_blk * HN;
+        // W rows come in groups of 128: 64 gate rows then the 64 up rows of the same outputs
         const int n_out = N / 2;
 #pragma unroll 1
-        for (int c0 = 0; c0 < HN; c0 += 32) {
+        for (int c = 0; c < BN / 2; c += 32) {
+          const int grp = c / 64, cin = c % 64;
+          const int out_col = n_blk * (BN / 2) + c;
           uint32_t g[32], u[32];
-          tmem_ld_32x32b_x32(t_row + c0, g);
-          tmem_ld_32x32b_x32(t_row + HN + c0, u);
+          tmem_ld_32x32b_x32(t_row + grp * 128 + cin, g);
+          tmem_ld_32x32b_x32(t_row + grp * 128 + 64 + cin, u);
           tmem_ld_wait();
           if (row < M) {
-            bf16* dst = ep.C + static_cast<size_t>(row) * ep.ldc + out_col0 + c0;
+            bf16* dst = ep.C + static_cast<size_t>(row) * ep.ldc + out_col;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-              if (out_col0 + c0 + v * 8 < n_out) {
+              if (out_col + v * 8 < n_out) {
                 bf16x8 o;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   float g0 = __uint_as_float(g[v * 8 + 2 * j]);
                   float g1 = __uint_as_float(g[v * 8 + 2 * j + 1]);
-                  float u0 = __uint_as_float(u[v * 8 + 2 * j]);
-                  float u1 = __uint_as_float(u[v * 8 + 2 * j + 1]);
+                  const float u0 = __uint_as_float(u[v * 8 + 2 * j]);
+                  const float u1 = __uint_as_float(u[v * 8 + 2 * j + 1]);
                   g0 = g0 / (1.f + __expf(-g0));
                   g1 = g1 / (1.f + __expf(-g1));
                   o.u[j] = pack_bf16x2(g0 * u0, g1 * u1);
@@ -324,10 +324,10 @@ PXL_EXPORT int pxl_gemm_bf16_pick_bn(int M, int N, int epi) {
   const int cands[3] = {256, 128, 64};
   for (int i = 0; i < 3; ++i) {
     const int bn = cands[i];
-    if (epi == PXL_EPI_SILU_MUL && (N % bn) != 0) continue;
+    if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) continue;
     if (num_m * pxl::ceil_div(N, bn) >= sms) return bn;
   }
-  return 64;
+  return epi == PXL_EPI_SILU_MUL ? 128 : 64;
 }
 
 PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* residual,
@@ -340,7 +340,7 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
     return PXL_ERR_INVALID_ARG;
   if (epi == PXL_EPI_RESIDUAL && residual == nullptr) return PXL_ERR_INVALID_ARG;
   if (bn == 0) bn = pxl_gemm_bf16_pick_bn(M, N, epi);
-  if (epi == PXL_EPI_SILU_MUL && (N % bn) != 0) return PXL_ERR_INVALID_ARG;
+  if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;
 
   CUtensorMap ta, tb;
   if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, lda, BM, BK))

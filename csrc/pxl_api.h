@@ -26,7 +26,7 @@ typedef struct CUstream_st* pxl_stream_t;
 // ---- gemm_tcgen05.cu -------------------------------------------------------
 // C[M,N] = A[M,K] * W[N,K]^T. lda/ldw/ldc in elements. `bn` = tile width (64/128/256)
 // or 0 to pick automatically. For PXL_EPI_SILU_MUL the rows of W must be arranged in
-// groups of `bn`: bn/2 gate rows followed by the bn/2 up rows of the same outputs.
+// groups of 128: 64 gate rows followed by the 64 up rows of the same outputs (bn >= 128).
 int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* residual, const void* bias,
                   int M, int N, int K, int lda, int ldw, int ldc, int epi, int bn, int* status,
                   pxl_stream_t stream);
@@ -62,11 +62,11 @@ int pxl_add_inplace(void* y, const void* x, int64_t n, pxl_stream_t stream);
 
 // ---- attention_decode.cu -----------------------------------------------------
 // Single-query GQA attention over the paged cache [blocks, Hkv, page, D] (D = 64 or 128).
-// q [B, Hq, D]; out [B, Hq, D]; block_tables [B, max_blocks]; ctx_lens [B].
+// q [B, Hq, D] with row stride q_stride elements; out [B, Hq, D]; block_tables [B, max_blocks]; ctx_lens [B].
 // window <= 0: full attention. sinks: optional fp32 [Hq] logits added to the
 // softmax denominator. workspace: fp32, >= B*Hq*num_splits*(D+2) floats when
 // num_splits > 1. num_splits = 0 picks automatically (see pxl_attn_decode_splits).
-int pxl_attn_decode(const void* q, const void* k_cache, const void* v_cache,
+int pxl_attn_decode(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
                     const int* block_tables, const int* ctx_lens, void* out, float* workspace,
                     const float* sinks, int B, int Hq, int Hkv, int D, int page_size,
                     int max_blocks, int64_t num_blocks, float scale, int window, int num_splits,

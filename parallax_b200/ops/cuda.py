@@ -231,12 +231,12 @@ def attn_decode(
     num_splits: int = 0,
     out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """q ``[B, Hq, D]`` (last dim contiguous, packed heads) against the paged cache."""
+    """q ``[B, Hq, D]`` (may be a strided view into a packed qkv buffer) vs the paged cache."""
     B, Hq, D = q.shape
-    assert q.is_contiguous()
+    assert q.stride(2) == 1 and q.stride(1) == D
     Hkv, page = k_cache.shape[1], k_cache.shape[2]
     if out is None:
-        out = torch.empty_like(q)
+        out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
     if max_ctx <= 0:
         max_ctx = block_tables.shape[1] * page
     if num_splits <= 0:
@@ -246,8 +246,9 @@ def attn_decode(
         ws = workspace(q.device, "attn_decode", B * Hq * num_splits * (D + 2) * 4)
     check(
         _lib.lib().pxl_attn_decode(
-            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
-            ctx_lens.data_ptr(), out.data_ptr(), _ptr(ws), _ptr(sinks), B, Hq, Hkv, D, page,
+            q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            block_tables.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(), _ptr(ws), _ptr(sinks),
+            B, Hq, Hkv, D, page,
             block_tables.shape[1], k_cache.shape[0], scale, window, num_splits, max_ctx,
             status_tensor(q.device).data_ptr(), _stream(q.device)),
         "pxl_attn_decode",

@@ -19,14 +19,14 @@ import torch
 EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32 = 0, 1, 2, 3
 
 
-def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, bn: int = 128) -> torch.Tensor:
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     """Arrange gate/up weight rows for the fused SiLU-mul GEMM epilogue.
 
-    Rows are grouped in blocks of ``bn``: ``bn/2`` gate rows followed by the ``bn/2`` up rows
-    of the same output columns.
+    Rows are grouped in blocks of 128: 64 gate rows followed by the 64 up rows of the same
+    output columns.
     """
     I, K = w_gate.shape
-    h = bn // 2
+    h = 64
     assert I % h == 0
     g = w_gate.reshape(I // h, h, K)
     u = w_up.reshape(I // h, h, K)
@@ -42,9 +42,8 @@ def linear(x, w, bias=None, residual=None, epi: int = EPI_NONE, out=None, bn: in
         epi = EPI_RESIDUAL
     if epi == EPI_SILU_MUL:
         N = w.shape[0]
-        bn = bn or 128
-        h = bn // 2
-        yb = y.reshape(y.shape[0], N // bn, 2, h)
+        h = 64
+        yb = y.reshape(y.shape[0], N // 128, 2, h)
         y = (torch.nn.functional.silu(yb[:, :, 0]) * yb[:, :, 1]).reshape(y.shape[0], N // 2)
     res = y if epi == EPI_F32 else y.to(x.dtype)
     if out is not None:
