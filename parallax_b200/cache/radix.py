@@ -1,0 +1,209 @@
+"""Block-granular radix prefix cache.
+
+One tree node represents one FULL KV block (``block_size`` tokens) and is keyed by the
+block's token tuple under its parent. Matching walks whole blocks only; requests pin the
+nodes they use through lock reference counts; unpinned leaves are evicted in LRU order and
+report the freed block (and, for hybrid linear-attention models, the state slot snapshot)
+through callbacks. Behavioural counterpart:
+``src/parallax/server/block_radix_cache.py:74-310``.
+"""
+
+from __future__ import annotations
+
+import heapq
+import itertools
+import time
+from typing import Callable, Optional
+
+
+class BlockNode:
+    __slots__ = ("key", "block_id", "parent", "children", "lock_ref", "last_access", "linear_slot",
+                 "alive")
+
+    def __init__(self, key: Optional[tuple], block_id: int, parent: Optional["BlockNode"]):
+        self.key = key
+        self.block_id = block_id
+        self.parent = parent
+        self.children: dict[tuple, BlockNode] = {}
+        self.lock_ref = 0
+        self.last_access = 0.0
+        self.linear_slot: Optional[int] = None
+        self.alive = True
+
+
+class BlockRadixCache:
+    def __init__(
+        self,
+        block_size: int,
+        on_evict_block: Optional[Callable[[int], None]] = None,
+        on_evict_linear_slot: Optional[Callable[[int], None]] = None,
+        require_linear_slot: bool = False,
+    ):
+        self.block_size = block_size
+        self.on_evict_block = on_evict_block
+        self.on_evict_linear_slot = on_evict_linear_slot
+        self.require_linear_slot = require_linear_slot
+        self.root = BlockNode(None, -1, None)
+        self.root.lock_ref = 1
+        self.request_to_nodes: dict[str, list[BlockNode]] = {}
+        self.num_nodes = 0
+        self._clock = itertools.count()
+        self.hits = 0
+        self.queries = 0
+
+    # ------------------------------------------------------------------ lookup
+    def _tick(self) -> float:
+        return time.monotonic() + next(self._clock) * 1e-9
+
+    def get_path(self, token_ids) -> list[BlockNode]:
+        """Nodes along the longest fully matching block path (no side effects)."""
+        bs = self.block_size
+        node, path = self.root, []
+        for i in range(0, len(token_ids) - bs + 1, bs):
+            child = node.children.get(tuple(token_ids[i:i + bs]))
+            if child is None:
+                break
+            path.append(child)
+            node = child
+        return path
+
+    def match_prefix(self, token_ids) -> tuple[list[int], int]:
+        """Longest cached prefix in whole blocks: (block ids, matched token count).
+
+        With ``require_linear_slot`` the match is cut back to the deepest node that carries
+        a linear-state snapshot, because a hybrid model can only resume from such a node.
+        """
+        self.queries += 1
+        path = self.get_path(token_ids)
+        if self.require_linear_slot:
+            while path and path[-1].linear_slot is None:
+                path.pop()
+        now = self._tick()
+        for n in path:
+            n.last_access = now
+        if path:
+            self.hits += 1
+        return [n.block_id for n in path], len(path) * self.block_size
+
+    def get_node_for_token_ids(self, token_ids) -> Optional[BlockNode]:
+        path = self.get_path(token_ids)
+        if len(path) * self.block_size == len(token_ids) and path:
+            return path[-1]
+        return None
+
+    # ------------------------------------------------------------------ insert
+    def insert_block(self, prefix_nodes: list[BlockNode], block_tokens, block_id: int,
+                     linear_slot: Optional[int] = None) -> tuple[BlockNode, bool]:
+        """Insert one full block under the path ``prefix_nodes``.
+
+        Returns (node, inserted). If the block is already cached the existing node is
+        returned with ``inserted=False`` and the caller keeps ownership of ``block_id``.
+        """
+        assert len(block_tokens) == self.block_size
+        parent = prefix_nodes[-1] if prefix_nodes else self.root
+        key = tuple(block_tokens)
+        node = parent.children.get(key)
+        if node is not None:
+            node.last_access = self._tick()
+            if linear_slot is not None and node.linear_slot is None:
+                node.linear_slot = linear_slot
+                return node, False
+            return node, False
+        node = BlockNode(key, block_id, parent)
+        node.last_access = self._tick()
+        node.linear_slot = linear_slot
+        parent.children[key] = node
+        self.num_nodes += 1
+        return node, True
+
+    # ------------------------------------------------------------------ pinning
+    def increase_lock_ref(self, nodes: list[BlockNode]) -> None:
+        for n in nodes:
+            n.lock_ref += 1
+
+    def decrease_lock_ref(self, nodes: list[BlockNode]) -> None:
+        for n in nodes:
+            if n.lock_ref > 0:
+                n.lock_ref -= 1
+
+    def register_request(self, request_id: str, nodes: list[BlockNode]) -> None:
+        self.increase_lock_ref(nodes)
+        self.request_to_nodes.setdefault(request_id, []).extend(nodes)
+
+    def release_request(self, request_id: str) -> None:
+        nodes = self.request_to_nodes.pop(request_id, None)
+        if nodes:
+            now = self._tick()
+            for n in nodes:
+                n.last_access = now
+            self.decrease_lock_ref(nodes)
+
+    # ------------------------------------------------------------------ eviction
+    def _evictable_leaves(self) -> list[BlockNode]:
+        out, stack = [], [self.root]
+        while stack:
+            n = stack.pop()
+            if n.children:
+                stack.extend(n.children.values())
+            elif n is not self.root and n.lock_ref == 0:
+                out.append(n)
+        return out
+
+    def evict_lru_blocks(self, num_blocks: int) -> int:
+        """Evict up to ``num_blocks`` unpinned leaf blocks, least recently used first."""
+        heap = [(n.last_access, id(n), n) for n in self._evictable_leaves()]
+        heapq.heapify(heap)
+        evicted = 0
+        while heap and evicted < num_blocks:
+            _, _, n = heapq.heappop(heap)
+            if not n.alive or n.children or n.lock_ref > 0:
+                continue
+            parent = n.parent
+            self._delete_leaf(n)
+            evicted += 1
+            if parent is not self.root and not parent.children and parent.lock_ref == 0:
+                heapq.heappush(heap, (parent.last_access, id(parent), parent))
+        return evicted
+
+    def _delete_leaf(self, node: BlockNode) -> None:
+        node.alive = False
+        del node.parent.children[node.key]
+        self.num_nodes -= 1
+        if self.on_evict_block is not None:
+            self.on_evict_block(node.block_id)
+        if node.linear_slot is not None and self.on_evict_linear_slot is not None:
+            self.on_evict_linear_slot(node.linear_slot)
+
+    def evictable_size(self) -> int:
+        """Blocks that eviction could free. Requests pin whole root-to-node paths, so an
+        unpinned node never has a pinned descendant and counting unpinned nodes is exact."""
+        n_free, stack = 0, list(self.root.children.values())
+        while stack:
+            n = stack.pop()
+            stack.extend(n.children.values())
+            if n.lock_ref == 0:
+                n_free += 1
+        return n_free
+
+    def get_stats(self) -> dict:
+        return {
+            "nodes": self.num_nodes,
+            "queries": self.queries,
+            "hits": self.hits,
+            "hit_rate": self.hits / self.queries if self.queries else 0.0,
+            "locked_requests": len(self.request_to_nodes),
+        }
+
+    def reset(self) -> None:
+        stack = list(self.root.children.values())
+        self.root.children.clear()
+        while stack:
+            n = stack.pop()
+            stack.extend(n.children.values())
+            n.alive = False
+            if self.on_evict_block is not None:
+                self.on_evict_block(n.block_id)
+            if n.linear_slot is not None and self.on_evict_linear_slot is not None:
+                self.on_evict_linear_slot(n.linear_slot)
+        self.num_nodes = 0
+        self.request_to_nodes.clear()

@@ -1,0 +1,344 @@
+"""In-process serving engine: scheduler + KV planner + pipeline stages + sampler.
+
+``Engine`` is the object a user (or the HTTP frontend, or ``bench.py``) drives:
+
+    eng = Engine(named_config("qwen3-8b"), device="cuda:0")
+    eng.add_request(Request(input_ids=[...], sampling_params=SamplingParams(max_new_tokens=64)))
+    while eng.has_work():
+        for req, token in eng.step():
+            ...
+
+One ``step()`` is one continuous-batching iteration: admit, form a mixed prefill+decode
+batch, plan KV slots, one packed host-to-device copy of the step's index tensors, forward
+through every stage, sample on the last stage, one device-to-host copy of the sampled ids,
+commit. It is the counterpart of one iteration of the reference's executor run loop
+(``src/parallax/server/executor/base_executor.py:634-769``), with the stage hand-off being
+a device tensor instead of a serialised network packet.
+
+Stages passed as ``stage_layers=[(0,14),(14,28)]`` run in this process one after another
+(used for correctness checks of sharded execution); multi-GPU pipelines use one process
+per GPU, see :mod:`parallax_b200.parallel.pipeline`.
+"""
+
+from __future__ import annotations
+
+import logging
+import time
+from typing import Callable, Iterable, Optional
+
+import numpy as np
+import torch
+
+from parallax_b200 import ops
+from parallax_b200.cache.manager import CacheManager
+from parallax_b200.engine.batch import BatchBuilder, ForwardBatch
+from parallax_b200.engine.request import Request, RequestStatus, SamplingParams
+from parallax_b200.engine.scheduler import BatchScheduler, ScheduledSeq
+from parallax_b200.engine.worker import StageWorker
+from parallax_b200.models.config import ModelConfig
+
+logger = logging.getLogger(__name__)
+
+
+class StepPlan:
+    """Host-side description of one step, kept until its tokens come back."""
+
+    __slots__ = ("seqs", "fb", "logit_owner", "t_start", "greedy", "sampling")
+
+    def __init__(self):
+        self.seqs: list[ScheduledSeq] = []
+        self.fb: Optional[ForwardBatch] = None
+        self.logit_owner: list[ScheduledSeq] = []
+        self.t_start = 0.0
+        self.greedy = True
+        self.sampling = None
+
+
+class Planner:
+    """Scheduler + logical KV cache: turns ready requests into packed step inputs."""
+
+    def __init__(self, cfg: ModelConfig, num_blocks: int, page_size: int, max_batch_size: int,
+                 max_num_tokens_per_batch: int, micro_batch_ratio: int = 1,
+                 chunked_prefill_size: Optional[int] = 1024, enable_prefix_cache: bool = True,
+                 max_total_length: int = 32768, request_timeout_s: Optional[float] = 600,
+                 eos_token_id=None, shared_state=None):
+        self.cfg = cfg
+        self.page_size = page_size
+        max_blocks_per_seq = (max_total_length + page_size - 1) // page_size + 1
+        self.cache = CacheManager(num_blocks, page_size, max_requests=max(max_batch_size * 2, 16),
+                                  max_blocks_per_seq=max_blocks_per_seq,
+                                  enable_prefix_cache=enable_prefix_cache)
+        self.scheduler = BatchScheduler(
+            max_batch_size=max_batch_size, max_num_tokens_per_batch=max_num_tokens_per_batch,
+            micro_batch_ratio=micro_batch_ratio, cache_manager=self.cache,
+            chunked_prefill_size=chunked_prefill_size, request_timeout_s=request_timeout_s,
+            eos_token_id=eos_token_id, max_total_length=max_total_length, shared_state=shared_state)
+        self.max_total_length = max_total_length
+
+    def plan_arrays(self, seqs: list[ScheduledSeq]):
+        """Numpy inputs of a step. Returns None if nothing can run (e.g. all aborted by OOM)."""
+        cache, bs = self.cache, self.page_size
+        prefill = [s for s in seqs if s.is_prefill]
+        decode = []
+        for s in seqs:
+            if s.is_prefill:
+                continue
+            if not cache.append_slot(s.req.request_id):
+                # out of KV memory while decoding: abort the request (reference behaviour,
+                # src/parallax/server/executor/mlx_executor.py:766-784)
+                s.req.abort = True
+                s.req.update_status(RequestStatus.FINISHED_ABORT)
+                continue
+            decode.append(s)
+        ordered = prefill + decode
+        if not ordered:
+            return None
+        T = sum(s.num_tokens for s in ordered)
+        ids = np.empty(T, dtype=np.int32)
+        pos = np.empty(T, dtype=np.int32)
+        rows_of_tok = np.empty(T, dtype=np.int32)
+        logit_rows, owners = [], []
+        o = 0
+        p_q, p_ctx, p_rows = [], [], []
+        for s in prefill:
+            n, st = s.num_tokens, s.start
+            ids[o:o + n] = s.req.input_ids[st:st + n]
+            pos[o:o + n] = np.arange(st, st + n, dtype=np.int32)
+            row = cache.get_row(s.req.request_id)
+            rows_of_tok[o:o + n] = row
+            p_q.append(n)
+            p_ctx.append(st + n)
+            p_rows.append(row)
+            if s.produces_token:
+                logit_rows.append(o + n - 1)
+                owners.append(s)
+            o += n
+        d_rows = np.empty(len(decode), dtype=np.int32)
+        d_ctx = np.empty(len(decode), dtype=np.int32)
+        for i, s in enumerate(decode):
+            r = s.req
+            ids[o] = r.output_ids[-1]
+            pos[o] = r.total_length - 1
+            row = cache.get_row(r.request_id)
+            rows_of_tok[o] = row
+            d_rows[i] = row
+            d_ctx[i] = r.total_length
+            logit_rows.append(o)
+            owners.append(s)
+            o += 1
+        slots = cache.tables[rows_of_tok, pos // bs].astype(np.int64) * bs + (pos % bs)
+        maxb_p = (max(p_ctx) + bs - 1) // bs if prefill else 0
+        maxb_d = (int(d_ctx.max()) + bs - 1) // bs if len(decode) else 0
+        p_tables = cache.tables[np.asarray(p_rows, dtype=np.int64), :maxb_p] if prefill else None
+        d_tables = cache.tables[d_rows, :maxb_d] if len(decode) else None
+        return dict(ordered=ordered, ids=ids, pos=pos, slots=slots, p_q=p_q, p_ctx=p_ctx,
+                    p_tables=p_tables, d_ctx=d_ctx, d_tables=d_tables,
+                    logit_rows=np.asarray(logit_rows, dtype=np.int32), owners=owners)
+
+
+class Engine:
+    def __init__(
+        self,
+        cfg: ModelConfig,
+        device="cuda:0",
+        dtype=None,
+        stage_layers: Optional[list[tuple[int, int]]] = None,
+        page_size: int = 16,
+        num_blocks: Optional[int] = None,
+        kv_fraction: float = 0.85,
+        max_batch_size: int = 8,
+        max_num_tokens_per_batch: int = 16384,
+        micro_batch_ratio: int = 1,
+        chunked_prefill_size: Optional[int] = 1024,
+        enable_prefix_cache: bool = True,
+        max_total_length: int = 32768,
+        request_timeout_s: Optional[float] = 600,
+        eos_token_id=None,
+        seed: int = 0,
+        weights: Optional[dict] = None,
+        max_kv_tokens: Optional[int] = None,
+        shared_state=None,
+        wire_hook: Optional[Callable] = None,
+    ):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.page_size = page_size
+        stage_layers = stage_layers or [(0, cfg.num_hidden_layers)]
+        max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
+        self.stages: list[StageWorker] = []
+        for (s, e) in stage_layers:
+            w = None
+            if weights is not None:
+                from parallax_b200.loader.filter import filter_weights_for_range
+
+                w = filter_weights_for_range(weights, s, e, cfg.num_hidden_layers, cfg.tie_word_embeddings)
+            self.stages.append(StageWorker(cfg, s, e, self.device, dtype, page_size, num_blocks=num_blocks,
+                                           kv_fraction=kv_fraction / len(stage_layers), seed=seed, weights=w,
+                                           max_kv_tokens=max_kv_tokens, max_positions=max_positions))
+        nb = min(st.num_blocks for st in self.stages)
+        self.planner = Planner(cfg, nb, page_size, max_batch_size, max_num_tokens_per_batch,
+                               micro_batch_ratio, chunked_prefill_size, enable_prefix_cache,
+                               max_total_length, request_timeout_s, eos_token_id, shared_state)
+        self.scheduler = self.planner.scheduler
+        self.cache = self.planner.cache
+        max_blocks = self.cache.max_blocks_per_seq
+        self.builder = BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size,
+                                    max_batch_size, max_blocks)
+        self.wire_hook = wire_hook  # optional transform applied to hidden states between stages
+        self._gen = torch.Generator(device=self.device)
+        self._gen.manual_seed(seed + 12345)
+        self.last_step_stats: dict = {}
+        self.total_steps = 0
+        self.keep_logits = False
+        self.last_logits: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, req: Request) -> None:
+        req.sampling_params.verify()
+        req.max_total_length = min(req.max_total_length, self.planner.max_total_length)
+        self.scheduler.enque_request(req)
+
+    def abort_request(self, rid: str) -> None:
+        try:
+            self.scheduler.cancel_request(rid)
+        except ValueError:
+            pass
+
+    def has_work(self) -> bool:
+        return self.scheduler.num_queued_requests > 0 or self.scheduler.num_running_requests > 0
+
+    # ------------------------------------------------------------------ sampling
+    def _sample(self, logits: torch.Tensor, owners: list[ScheduledSeq]):
+        sps = [s.req.sampling_params for s in owners]
+        want_prob = any(s.req.return_probs for s in owners)
+        if all(sp.is_greedy for sp in sps):
+            if want_prob:
+                ids, lp = ops.argmax(logits, want_logprob=True)
+                return ids, lp.exp()
+            return ops.argmax(logits), None
+        dev = logits.device
+        temperature = torch.tensor([0.0 if sp.is_greedy else sp.temperature for sp in sps],
+                                   dtype=torch.float32, device=dev)
+        top_k = torch.tensor([sp.top_k if sp.top_k > 0 else 0 for sp in sps], dtype=torch.int32, device=dev)
+        top_p = torch.tensor([sp.top_p for sp in sps], dtype=torch.float32, device=dev)
+        min_p = torch.tensor([sp.min_p for sp in sps], dtype=torch.float32, device=dev)
+        u = torch.rand(len(sps), generator=self._gen, device=dev, dtype=torch.float32)
+        if want_prob:
+            return ops.sample(logits, temperature, top_k, top_p, min_p, u, want_prob=True)
+        return ops.sample(logits, temperature, top_k, top_p, min_p, u), None
+
+    # ------------------------------------------------------------------ one step
+    def _release(self, req: Request) -> None:
+        self.cache.free_request(req.request_id)
+
+    @torch.inference_mode()
+    def step(self, events=None) -> list[tuple[Request, Optional[int]]]:
+        """Run one engine iteration. Returns ``(request, new_token or None)`` for every
+        request that produced a token or finished in this step.
+
+        ``events``: optional ``(start, end)`` CUDA events recorded on the compute stream right
+        before the step's host-to-device copy and right after sampling (device-time probes)."""
+        out: list[tuple[Request, Optional[int]]] = []
+        sched = self.scheduler
+        for req in sched.get_timed_out_requests():
+            req.update_status(RequestStatus.FINISHED_ABORT)
+            sched.evict_request(req.request_id)
+            self._release(req)
+            out.append((req, None))
+        seqs = sched.form_batch()
+        for req in sched.pop_rejected():
+            out.append((req, None))
+        # requests aborted by the client while waiting for their turn
+        live = []
+        for s in seqs:
+            if s.req.abort:
+                s.req.update_status(RequestStatus.FINISHED_ABORT)
+                sched.evict_request(s.req.request_id)
+                self._release(s.req)
+                out.append((s.req, None))
+            else:
+                live.append(s)
+        if not live:
+            return out
+        arrays = self.planner.plan_arrays(live)
+        for s in live:
+            if s.req.is_finished:  # aborted by KV exhaustion during planning
+                sched.evict_request(s.req.request_id)
+                self._release(s.req)
+                out.append((s.req, None))
+        if arrays is None:
+            return out
+        t0 = time.perf_counter()
+        if events is not None:
+            events[0].record()
+        fb = self.builder.build(arrays["ids"], arrays["pos"], arrays["slots"], arrays["p_q"],
+                                arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"], arrays["d_tables"],
+                                arrays["logit_rows"])
+        owners = arrays["owners"]
+        h = None
+        for i, st in enumerate(self.stages):
+            h = st.run(fb, h)
+            if self.wire_hook is not None and i + 1 < len(self.stages):
+                h = self.wire_hook(h)
+        token_list, prob_list = [], None
+        if self.keep_logits:
+            self.last_logits = h
+        ids = probs = None
+        if owners:
+            ids, probs = self._sample(h, owners)
+        if events is not None:
+            events[1].record()
+        if owners:
+            token_list = ids.tolist()  # device-to-host copy of the step's result (synchronises)
+            if probs is not None:
+                prob_list = probs.tolist()
+        elif self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+        self.total_steps += 1
+        self.last_step_stats = {
+            "tokens": fb.num_tokens, "prefill_tokens": fb.num_prefill_tokens, "decode": fb.num_decode,
+            "h2d_bytes": fb.h2d_bytes, "d2h_bytes": 4 * len(token_list) * (2 if prob_list else 1),
+            "new_tokens": len(token_list), "wall_s": time.perf_counter() - t0,
+        }
+        # ---- commit
+        owner_idx = {id(s): i for i, s in enumerate(owners)}
+        for s in arrays["ordered"]:
+            req = s.req
+            if s.is_prefill:
+                req.num_computed_tokens = s.start + s.num_tokens
+                self.cache.insert_full_blocks_to_cache(req.request_id, req.num_computed_tokens)
+            tok = None
+            i = owner_idx.get(id(s))
+            if i is not None:
+                tok = int(token_list[i])
+                req.commit_new_token(tok, prob_list[i] if prob_list else None)
+                self.cache.update_request_tokens(req.request_id, [tok])
+            if sched.check_and_update_request_status(req):
+                self._release(req)
+                out.append((req, tok))
+            else:
+                sched.enque_request(req)
+                if tok is not None:
+                    out.append((req, tok))
+        return out
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: Iterable[list[int]], sampling_params: Optional[SamplingParams] = None,
+                 max_steps: int = 1 << 30) -> list[list[int]]:
+        """Blocking helper: run the prompts to completion and return the generated ids."""
+        reqs = []
+        for p in prompts:
+            sp = sampling_params or SamplingParams()
+            r = Request(input_ids=list(p), sampling_params=SamplingParams.from_dict(sp.to_dict()),
+                        max_total_length=self.planner.max_total_length)
+            reqs.append(r)
+            self.add_request(r)
+        steps = 0
+        while self.has_work() and steps < max_steps:
+            self.step()
+            steps += 1
+        if self.device.type == "cuda":
+            from parallax_b200.ops import cuda as _cuda
+
+            _cuda.check_status(self.device)
+        return [r.output_ids for r in reqs]

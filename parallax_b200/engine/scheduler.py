@@ -1,0 +1,250 @@
+"""Per-node continuous-batching scheduler.
+
+Two phases per step, like the reference's local scheduler
+(``src/parallax/server/scheduler.py:251-392``): (1) admit waiting requests into the running
+set while ``max_batch_size`` and the KV pool allow (allocation includes the prefix-cache
+match); (2) form the next micro-batch from *ready* running requests — prefills first in
+admission order, each costing ``min(remaining prompt, chunked_prefill_size)`` tokens, then
+ready decodes — bounded by ``micro_batch_size = max_batch_size // micro_batch_ratio``
+sequences and ``max_num_tokens_per_batch`` tokens. A request that is in flight in the
+pipeline is not ready again until its token came back, which is what keeps several
+micro-batches in flight across stages.
+
+Unlike the reference, several requests may be mid-way through a chunked prefill at once and
+prefill chunks share a forward pass with decodes.
+"""
+
+from __future__ import annotations
+
+import logging
+import time
+from collections import OrderedDict, deque
+from dataclasses import dataclass
+from typing import Iterable, Optional
+
+from parallax_b200.engine.request import Request, RequestStatus
+
+logger = logging.getLogger(__name__)
+
+
+def _normalize_token_ids(x) -> set[int]:
+    if x is None:
+        return set()
+    if isinstance(x, int):
+        return {x}
+    return {int(t) for t in x}
+
+
+@dataclass
+class ScheduledSeq:
+    req: Request
+    num_tokens: int        # tokens run in this step
+    start: int             # sequence position of the first token run in this step
+    is_prefill: bool
+    produces_token: bool   # last prompt chunk or decode step => a token is sampled
+
+
+class BatchScheduler:
+    def __init__(
+        self,
+        max_batch_size: int = 8,
+        max_num_tokens_per_batch: int = 16384,
+        micro_batch_ratio: int = 1,
+        cache_manager=None,
+        chunked_prefill_size: Optional[int] = 1024,
+        request_timeout_s: Optional[float] = 600,
+        eos_token_id=None,
+        max_total_length: int = 32768,
+        is_first_peer: bool = True,
+        prefill_priority: int = 0,
+        shared_state=None,
+    ):
+        self.max_batch_size = max_batch_size
+        self.max_num_tokens_per_batch = max_num_tokens_per_batch
+        self.micro_batch_size = max(1, max_batch_size // max(1, micro_batch_ratio))
+        self.cache_manager = cache_manager
+        self.chunked_prefill_size = chunked_prefill_size
+        self.request_timeout_s = request_timeout_s
+        self.eos_token_ids = _normalize_token_ids(eos_token_id)
+        self.max_total_length = max_total_length
+        self.is_first_peer = is_first_peer
+        self.prefill_priority = prefill_priority
+        self.shared_state = shared_state
+        self._wait_queue: deque[Request] = deque()
+        self._running: "OrderedDict[str, Request]" = OrderedDict()
+        self._last_reported = -1
+        self._rejected: list[Request] = []
+
+    # ------------------------------------------------------------------ queues
+    @property
+    def num_queued_requests(self) -> int:
+        return len(self._wait_queue)
+
+    @property
+    def num_running_requests(self) -> int:
+        return len(self._running)
+
+    def running_requests(self) -> Iterable[Request]:
+        return self._running.values()
+
+    def get_running_request(self, rid: str) -> Optional[Request]:
+        return self._running.get(rid)
+
+    def enque_request(self, req: Request) -> None:
+        """New requests go to the wait queue; a running request coming back from the
+        pipeline becomes ready for its next step (and moves to the end of the ready order)."""
+        if req.is_finished:
+            return
+        running = self._running.get(req.request_id)
+        if running is not None:
+            running.ready_for_next_step = True
+            running.last_updated_time = time.time()
+            self._running.move_to_end(req.request_id)
+            return
+        req.last_updated_time = time.time()
+        self._wait_queue.append(req)
+
+    def evict_request(self, rid: str) -> Optional[Request]:
+        return self._running.pop(rid, None)
+
+    def cancel_request(self, rid: str) -> None:
+        req = self._running.get(rid)
+        if req is not None:
+            req.abort = True
+            return
+        for r in list(self._wait_queue):
+            if r.request_id == rid:
+                self._wait_queue.remove(r)
+                r.update_status(RequestStatus.CANCELLED)
+                return
+        raise ValueError(f"Attempted to cancel non-existent request {rid}.")
+
+    # ------------------------------------------------------------------ phase 1
+    def admit_requests(self) -> None:
+        while self._wait_queue and len(self._running) < self.max_batch_size:
+            req = self._wait_queue.popleft()
+            rid = req.request_id
+            if rid in self._running:
+                continue
+            if req.total_length > self.max_total_length:
+                req.update_status(RequestStatus.FINISHED_ABORT)
+                req.abort = True
+                self._rejected.append(req)
+                continue
+            if self.cache_manager is not None and not self.cache_manager.has_request(rid):
+                ok, matched = self.cache_manager.allocate_request(rid, req.total_length, token_ids=req.input_ids)
+                if not ok:
+                    # out of KV memory: keep FIFO order and stop admitting
+                    self._wait_queue.appendleft(req)
+                    break
+                req.num_cached_tokens = matched
+                req.num_computed_tokens = max(req.num_computed_tokens, matched)
+            self._running[rid] = req
+            req.ready_for_next_step = True
+            req.last_updated_time = time.time()
+        self._report_metrics()
+
+    def pop_rejected(self) -> list[Request]:
+        out, self._rejected = self._rejected, []
+        return out
+
+    def _report_metrics(self) -> None:
+        if self.shared_state is None:
+            return
+        cur = len(self._running)
+        if cur != self._last_reported:
+            try:
+                self.shared_state.update_metrics(current_requests=cur)
+            except Exception:  # metrics must never break serving
+                pass
+            self._last_reported = cur
+
+    # ------------------------------------------------------------------ timeouts
+    def get_timed_out_requests(self) -> list[Request]:
+        if not self.request_timeout_s:
+            return []
+        now = time.time()
+        out = []
+        for req in self._running.values():
+            if req.last_updated_time is not None and now - req.last_updated_time > self.request_timeout_s:
+                req.abort = True
+                out.append(req)
+        return out
+
+    # ------------------------------------------------------------------ phase 2
+    def form_batch(self) -> list[ScheduledSeq]:
+        self.admit_requests()
+        if not self._running:
+            return []
+        budget = self.max_num_tokens_per_batch
+        batch: list[ScheduledSeq] = []
+        prefills, decodes = [], []
+        for req in self._running.values():
+            if not req.ready_for_next_step or req.is_finished:
+                continue
+            (prefills if req.is_prefill else decodes).append(req)
+        used = 0
+        chunk = self.chunked_prefill_size
+        for req in prefills:
+            if len(batch) >= self.micro_batch_size:
+                break
+            remaining = req.remaining_prefill
+            if remaining <= 0:
+                # whole prompt is cached: recompute the last token to obtain logits
+                req.num_computed_tokens = req.prompt_len - 1
+                remaining = 1
+            cost = remaining if not chunk else min(remaining, chunk)
+            room = budget - used
+            if room <= 0:
+                break
+            if cost > room:
+                if not chunk:
+                    continue
+                cost = room
+            last = cost == remaining
+            if not last:
+                req.is_chunked = True
+            batch.append(ScheduledSeq(req, cost, req.num_computed_tokens, True, last))
+            used += cost
+        for req in decodes:
+            if len(batch) >= self.micro_batch_size or used + 1 > budget:
+                break
+            batch.append(ScheduledSeq(req, 1, req.total_length - 1, False, True))
+            used += 1
+        now = time.time()
+        for s in batch:
+            s.req.ready_for_next_step = False
+            s.req.last_updated_time = now
+        return batch
+
+    # ------------------------------------------------------------------ finish rules
+    def check_and_update_request_status(self, req: Request) -> bool:
+        """EOS / stop ids (honouring ``min_new_tokens``) / max_new / max_total / abort."""
+        if req.is_finished:
+            self.evict_request(req.request_id)
+            return True
+        if req.abort:
+            req.update_status(RequestStatus.FINISHED_ABORT)
+            self.evict_request(req.request_id)
+            return True
+        if not self.is_first_peer:
+            return False
+        sp = req.sampling_params
+        last = req.output_ids[-1] if req.output_ids else None
+        can_stop = req.output_length > sp.min_new_tokens
+        finished = False
+        if can_stop and not sp.ignore_eos and last is not None and last in self.eos_token_ids:
+            req.update_status(RequestStatus.FINISHED_EOS)
+            finished = True
+        elif can_stop and last is not None and sp.stop_token_ids and last in sp.stop_token_ids:
+            req.update_status(RequestStatus.FINISHED_EOS)
+            finished = True
+        elif req.output_length >= req.max_new_tokens:
+            req.update_status(RequestStatus.FINISHED_MAX_LENGTH)
+            finished = True
+        elif req.total_length >= req.max_total_length:
+            req.update_status(RequestStatus.FINISHED_MAX_LENGTH)
+            finished = True
+        if finished:
+            self.evict_request(req.request_id)
+        return finished

@@ -1,0 +1,230 @@
+"""Pipeline-stage model for GQA decoder-only transformers (Llama, Qwen2, Qwen3, Qwen3-MoE,
+GLM4-MoE, MiniMax-M2, GPT-OSS, Step-3.5 families).
+
+A stage owns decoder layers ``[start_layer, end_layer)``; the first stage also owns the
+embedding table, the last stage the final norm, lm_head and sampling inputs — the same
+split the reference uses for its shards (``src/parallax/server/model.py:52-73``) and
+contract per block (``src/parallax/models/qwen3.py:56-203``).
+
+Weights are stored in the fused layouts the kernels want:
+  * ``w_qkv``  [(Hq+2Hkv)*D, H]       (q | k | v rows)
+  * ``w_gu``   [2I, H]                gate/up rows interleaved in groups of 64 (see
+                                      :func:`parallax_b200.ops.interleave_gate_up`)
+The same code runs on CPU (fp32, reference ops) and on B200 (bf16, sm_100a kernels).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from parallax_b200 import ops
+from parallax_b200.engine.batch import ForwardBatch
+from parallax_b200.models.config import ModelConfig
+from parallax_b200.models.rope import build_rope_table
+
+
+class LayerWeights:
+    __slots__ = (
+        "ln1", "ln2", "w_qkv", "b_qkv", "q_norm", "k_norm", "w_o", "b_o", "w_gu", "w_down", "sinks",
+        "moe", "window", "layer_idx",
+    )
+
+    def __init__(self):
+        for s in self.__slots__:
+            setattr(self, s, None)
+        self.window = 0
+
+
+class DecoderStage:
+    def __init__(self, cfg: ModelConfig, start_layer: int, end_layer: int, device, dtype=None,
+                 max_positions: Optional[int] = None):
+        self.cfg = cfg
+        self.start_layer = start_layer
+        self.end_layer = end_layer
+        self.device = torch.device(device)
+        self.dtype = dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        self.is_first = start_layer == 0
+        self.is_last = end_layer == cfg.num_hidden_layers
+        self.layers: list[LayerWeights] = [LayerWeights() for _ in range(start_layer, end_layer)]
+        self.embed: Optional[torch.Tensor] = None
+        self.norm_w: Optional[torch.Tensor] = None
+        self.lm_head: Optional[torch.Tensor] = None
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.max_positions = max_positions or cfg.max_position_embeddings
+        self.cos_sin = build_rope_table(cfg, self.max_positions, self.device)
+        self.kv_caches: list = []  # per local layer: (k_cache, v_cache)
+        self.norm_offset = 0.0
+
+    # ------------------------------------------------------------------ weights
+    def num_local_layers(self) -> int:
+        return self.end_layer - self.start_layer
+
+    def init_random(self, seed: int = 0, std: float = 0.02) -> None:
+        """Random N(0, std) weights of the configured architecture (benchmarks, tests)."""
+        cfg, dev, dt = self.cfg, self.device, self.dtype
+        g = torch.Generator(device=dev)
+
+        def rnd(*shape, layer_seed):
+            g.manual_seed(seed * 1000003 + layer_seed)
+            return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * std).to(dt)
+
+        H, D = cfg.hidden_size, cfg.head_dim
+        Hq, Hkv, I = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
+        if self.is_first or (self.is_last and cfg.tie_word_embeddings):
+            self.embed = rnd(cfg.vocab_size, H, layer_seed=900001)
+        if self.is_last:
+            self.norm_w = torch.ones(H, device=dev, dtype=dt)
+            self.lm_head = self.embed if cfg.tie_word_embeddings else rnd(cfg.vocab_size, H, layer_seed=900002)
+        for li, lw in enumerate(self.layers):
+            gi = self.start_layer + li
+            s = gi * 16
+            lw.layer_idx = gi
+            lw.window = cfg.layer_window(gi)
+            lw.ln1 = torch.ones(H, device=dev, dtype=dt)
+            lw.ln2 = torch.ones(H, device=dev, dtype=dt)
+            wq = rnd(Hq * D, H, layer_seed=s + 1)
+            wk = rnd(Hkv * D, H, layer_seed=s + 2)
+            wv = rnd(Hkv * D, H, layer_seed=s + 3)
+            lw.w_qkv = torch.cat([wq, wk, wv], dim=0).contiguous()
+            if cfg.attention_bias:
+                lw.b_qkv = rnd((Hq + 2 * Hkv) * D, layer_seed=s + 4)
+            if cfg.qk_norm:
+                lw.q_norm = torch.ones(D, device=dev, dtype=dt)
+                lw.k_norm = torch.ones(D, device=dev, dtype=dt)
+            lw.w_o = rnd(H, Hq * D, layer_seed=s + 5)
+            if cfg.attention_sinks:
+                lw.sinks = rnd(Hq, layer_seed=s + 9).float()
+            if cfg.layer_is_moe(gi):
+                from parallax_b200.models.moe import MoEWeights
+
+                lw.moe = MoEWeights.random(cfg, dev, dt, lambda *sh, k: rnd(*sh, layer_seed=s + 10 + k))
+            else:
+                wg = rnd(I, H, layer_seed=s + 6)
+                wu = rnd(I, H, layer_seed=s + 7)
+                lw.w_gu = ops.interleave_gate_up(wg, wu)
+                lw.w_down = rnd(H, I, layer_seed=s + 8)
+
+    def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Install HF-named tensors (already filtered to this stage's layer range)."""
+        cfg, dev, dt = self.cfg, self.device, self.dtype
+
+        def get(name, required=True):
+            t = tensors.get(name)
+            if t is None:
+                if required:
+                    raise KeyError(f"missing weight {name}")
+                return None
+            return t.to(device=dev, dtype=dt)
+
+        if self.is_first or (self.is_last and cfg.tie_word_embeddings):
+            self.embed = get("model.embed_tokens.weight").contiguous()
+        if self.is_last:
+            self.norm_w = get("model.norm.weight")
+            lm = get("lm_head.weight", required=False)
+            self.lm_head = lm.contiguous() if lm is not None else self.embed
+        for li, lw in enumerate(self.layers):
+            gi = self.start_layer + li
+            p = f"model.layers.{gi}."
+            lw.layer_idx = gi
+            lw.window = cfg.layer_window(gi)
+            lw.ln1 = get(p + "input_layernorm.weight")
+            lw.ln2 = get(p + "post_attention_layernorm.weight")
+            lw.w_qkv = torch.cat([get(p + "self_attn.q_proj.weight"), get(p + "self_attn.k_proj.weight"),
+                                  get(p + "self_attn.v_proj.weight")], dim=0).contiguous()
+            bq = get(p + "self_attn.q_proj.bias", required=False)
+            if bq is not None:
+                lw.b_qkv = torch.cat([bq, get(p + "self_attn.k_proj.bias"),
+                                      get(p + "self_attn.v_proj.bias")]).contiguous()
+            lw.q_norm = get(p + "self_attn.q_norm.weight", required=False)
+            lw.k_norm = get(p + "self_attn.k_norm.weight", required=False)
+            lw.w_o = get(p + "self_attn.o_proj.weight").contiguous()
+            lw.b_o = get(p + "self_attn.o_proj.bias", required=False)
+            sk = tensors.get(p + "self_attn.sinks")
+            if sk is not None:
+                lw.sinks = sk.to(device=dev, dtype=torch.float32)
+            if cfg.layer_is_moe(gi):
+                from parallax_b200.models.moe import MoEWeights
+
+                lw.moe = MoEWeights.from_hf(cfg, tensors, p + "mlp.", dev, dt)
+            else:
+                lw.w_gu = ops.interleave_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"))
+                lw.w_down = get(p + "mlp.down_proj.weight").contiguous()
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        def add(t):
+            nonlocal total
+            if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        for t in (self.embed, self.norm_w, self.lm_head):
+            add(t)
+        for lw in self.layers:
+            for s in LayerWeights.__slots__:
+                v = getattr(lw, s)
+                if isinstance(v, torch.Tensor):
+                    add(v)
+                elif v is not None and hasattr(v, "tensors"):
+                    for t in v.tensors():
+                        add(t)
+        return total
+
+    # ------------------------------------------------------------------ forward
+    def attach_kv(self, kv_caches: list) -> None:
+        assert len(kv_caches) == len(self.layers)
+        self.kv_caches = kv_caches
+
+    def embed_tokens(self, fb: ForwardBatch) -> torch.Tensor:
+        return ops.gather_rows(self.embed, fb.input_ids)
+
+    def _attention(self, lw: LayerWeights, li: int, xn: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        cfg = self.cfg
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        T = xn.shape[0]
+        qkv = ops.linear(xn, lw.w_qkv, bias=lw.b_qkv)
+        kc, vc = self.kv_caches[li]
+        ops.qk_norm_rope_cache(qkv, lw.q_norm, lw.k_norm, self.cos_sin, fb.positions, fb.slot_mapping,
+                               kc, vc, Hq, Hkv, D, cfg.rot_dim, cfg.rms_norm_eps, self.norm_offset)
+        q = qkv.view(T, Hq + 2 * Hkv, D)[:, :Hq]
+        attn = torch.empty((T, Hq, D), dtype=qkv.dtype, device=qkv.device)
+        Tp = fb.num_prefill_tokens
+        if Tp:
+            ops.attn_prefill(q[:Tp], kc, vc, fb.p_block_tables, fb.p_cu_q, fb.p_ctx_lens, fb.p_max_q,
+                             self.scale, window=lw.window, sinks=lw.sinks, out=attn[:Tp])
+        if fb.num_decode:
+            ops.attn_decode(q[Tp:], kc, vc, fb.d_block_tables, fb.d_ctx_lens, self.scale,
+                            window=lw.window, sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:])
+        return attn.view(T, Hq * D)
+
+    def _mlp(self, lw: LayerWeights, xn: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        if lw.moe is not None:
+            return lw.moe.forward(xn, h)
+        act = ops.linear(xn, lw.w_gu, epi=ops.EPI_SILU_MUL)
+        return ops.linear(act, lw.w_down, residual=h)
+
+    def forward_layers(self, h: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        eps = self.cfg.rms_norm_eps
+        for li, lw in enumerate(self.layers):
+            xn = ops.rmsnorm(h, lw.ln1, eps, w_offset=self.norm_offset)
+            a = self._attention(lw, li, xn, fb)
+            h = ops.linear(a, lw.w_o, bias=lw.b_o, residual=h)
+            xn = ops.rmsnorm(h, lw.ln2, eps, w_offset=self.norm_offset)
+            h = self._mlp(lw, xn, h)
+        return h
+
+    def logits(self, h: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        rows = ops.gather_rows(h, fb.logit_rows) if fb.num_logits != h.shape[0] else h
+        hn = ops.rmsnorm(rows, self.norm_w, self.cfg.rms_norm_eps, w_offset=self.norm_offset)
+        return ops.linear(hn, self.lm_head)
+
+    def forward(self, fb: ForwardBatch, hidden: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """First stage: ``hidden`` is ignored and tokens are embedded. Returns hidden states
+        ``[T, H]`` (non-last stage) or logits ``[num_logits, V]`` (last stage)."""
+        h = self.embed_tokens(fb) if self.is_first else hidden
+        h = self.forward_layers(h, fb)
+        if self.is_last:
+            return self.logits(h, fb)
+        return h

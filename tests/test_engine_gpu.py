@@ -1,0 +1,106 @@
+"""The engine on B200 (bf16, sm_100a kernels) against the same engine on CPU (fp32, reference ops)."""
+
+import pytest
+import torch
+
+from parallax_b200.engine.engine import Engine
+from parallax_b200.engine.request import Request, SamplingParams
+from parallax_b200.models.config import config_from_hf
+
+pytestmark = pytest.mark.gpu
+
+
+def _cfg():
+    return config_from_hf(dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=512,
+                               num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                               intermediate_size=1024, vocab_size=2048, tie_word_embeddings=False, rope_theta=1e4))
+
+
+def _prompts(n, length, vocab, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def _first_step_logits(device, dtype, prompts, weights=None, **kw):
+    eng = Engine(_cfg(), device=device, dtype=dtype, num_blocks=128, page_size=16, max_batch_size=8,
+                 weights=weights, **kw)
+    eng.keep_logits = True
+    for p in prompts:
+        eng.add_request(Request(input_ids=p, sampling_params=SamplingParams(max_new_tokens=4, temperature=0.0,
+                                                                            ignore_eos=True)))
+    eng.step()
+    first = eng.last_logits.float().cpu()
+    eng.step()  # one decode step
+    second = eng.last_logits.float().cpu()
+    return eng, first, second
+
+
+def _export_weights(eng):
+    """HF-named fp32 weights of a random-init stage (undo the fused layouts)."""
+    m = eng.stages[0].model
+    cfg = m.cfg
+    Hq, Hkv, D, I = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
+    w = {"model.embed_tokens.weight": m.embed, "model.norm.weight": m.norm_w, "lm_head.weight": m.lm_head}
+    for lw in m.layers:
+        p = f"model.layers.{lw.layer_idx}."
+        q, k, v = lw.w_qkv.split([Hq * D, Hkv * D, Hkv * D], dim=0)
+        gu = lw.w_gu.view(I // 64, 2, 64, -1)
+        w.update({p + "input_layernorm.weight": lw.ln1, p + "post_attention_layernorm.weight": lw.ln2,
+                  p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k,
+                  p + "self_attn.v_proj.weight": v, p + "self_attn.o_proj.weight": lw.w_o,
+                  p + "self_attn.q_norm.weight": lw.q_norm, p + "self_attn.k_norm.weight": lw.k_norm,
+                  p + "mlp.gate_proj.weight": gu[:, 0].reshape(I, -1), p + "mlp.up_proj.weight": gu[:, 1].reshape(I, -1),
+                  p + "mlp.down_proj.weight": lw.w_down})
+    return {k: v.detach().float().cpu() for k, v in w.items()}
+
+
+def test_gpu_engine_matches_cpu_engine():
+    prompts = _prompts(5, 70, 2048) + _prompts(2, 5, 2048, seed=1)
+    gpu, g1, g2 = _first_step_logits("cuda:0", torch.bfloat16, prompts)
+    weights = _export_weights(gpu)
+    # the CPU engine runs the bf16-rounded weights in fp32
+    _cpu, c1, c2 = _first_step_logits("cpu", torch.float32, prompts, weights=weights)
+    from parallax_b200.ops import cuda as cu
+    cu.check_status(torch.device("cuda:0"))
+    for g, c in ((g1, c1), (g2, c2)):
+        assert g.shape == c.shape
+        rel = (g - c).norm() / c.norm()
+        assert rel < 3e-2, rel
+        agree = (g.argmax(-1) == c.argmax(-1)).float().mean()
+        assert agree >= 0.7
+
+
+def test_gpu_sharded_chunked_prefix_consistency():
+    prompts = _prompts(6, 150, 2048, seed=2)
+    sp = SamplingParams(max_new_tokens=12, temperature=0.0, ignore_eos=True)
+    base = Engine(_cfg(), device="cuda:0", num_blocks=256, max_batch_size=8, chunked_prefill_size=None,
+                  enable_prefix_cache=False).generate(prompts, sp)
+    shard = Engine(_cfg(), device="cuda:0", num_blocks=256, max_batch_size=8, chunked_prefill_size=None,
+                   enable_prefix_cache=False, stage_layers=[(0, 2), (2, 4)]).generate(prompts, sp)
+    assert base == shard
+    eng = Engine(_cfg(), device="cuda:0", num_blocks=256, max_batch_size=8, chunked_prefill_size=64)
+    a = eng.generate(prompts, sp)
+    b = eng.generate(prompts, sp)  # served from the prefix cache
+    assert eng.cache.prefix_cache.hits >= 6
+    # chunking and cached prefixes change the reduction order slightly; most sequences agree
+    same = sum(x == y for x, y in zip(a, b))
+    assert same >= 4
+    match_base = sum(x[:4] == y[:4] for x, y in zip(a, base))
+    assert match_base >= 4
+
+
+def test_gpu_sampling_requests_finish():
+    eng = Engine(_cfg(), device="cuda:0", num_blocks=128, max_batch_size=8)
+    reqs = [Request(input_ids=p, sampling_params=SamplingParams(max_new_tokens=10, temperature=0.8, top_k=40,
+                                                                top_p=0.9, ignore_eos=True), return_probs=True)
+            for p in _prompts(4, 20, 2048, seed=5)]
+    for r in reqs:
+        eng.add_request(r)
+    n = 0
+    while eng.has_work() and n < 100:
+        eng.step()
+        n += 1
+    assert all(len(r.output_ids) == 10 for r in reqs)
+    assert all(0 <= t < 2048 for r in reqs for t in r.output_ids)
+    assert all(0.0 < p <= 1.0 for r in reqs for p in r.output_probs)
+    assert eng.cache.num_free_blocks() + eng.cache.prefix_cache.num_nodes == eng.cache.num_blocks
