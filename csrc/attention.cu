@@ -14,6 +14,7 @@
 // and the prefix-aware prefill (src/parallax/utils/prefix_cache_utils.py:11-144).
 #include "common.cuh"
 #include "pxl_api.h"
+#include "pxl_noalloc.h"
 
 namespace {
 using namespace pxl;
@@ -576,4 +577,54 @@ PXL_EXPORT int pxl_attn_prefill(const void* q, int64_t q_stride, const void* k_c
   else return PXL_ERR_INVALID_ARG;
 #undef PXL_PRE
   return check_launch();
+}
+
+// ----------------------------------------------------------------------------------------
+// Allocation-free decode attention (see pxl_noalloc.h). The scratch for the split-KV partial
+// results is this file-scope device array. In host code `g_decode_static_scratch` is only a
+// stand-in for the symbol, not a device address, so the launcher asks the runtime for the
+// real address once per device and hands that pointer to the kernels.
+static __device__ __align__(256) float g_decode_static_scratch[PXL_DECODE_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device, or nullptr on error.
+float* static_scratch_ptr() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_decode_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();  // leave no sticky error behind for the caller
+      return nullptr;
+    }
+    g_static_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  return g_static_scratch_addr[dev];
+}
+}  // namespace
+
+PXL_EXPORT int pxl_attn_decode_static_scratch(const void* q, int64_t q_stride, const void* k_cache,
+                                              const void* v_cache, const int* block_tables,
+                                              const int* ctx_lens, void* out, const float* sinks,
+                                              int B, int Hq, int Hkv, int D, int page_size,
+                                              int max_blocks, int64_t num_blocks, float scale,
+                                              int window, int num_splits, int* status,
+                                              pxl_stream_t stream) {
+  if (B <= 0) return PXL_OK;
+  if (num_splits < 1 || Hq <= 0 || D <= 0) return PXL_ERR_INVALID_ARG;
+  float* scratch = nullptr;
+  if (num_splits > 1) {
+    const int64_t need = static_cast<int64_t>(B) * Hq * num_splits * (D + 2);
+    if (need > static_cast<int64_t>(PXL_DECODE_STATIC_SCRATCH_FLOATS)) return PXL_ERR_TOO_LARGE;
+    scratch = static_scratch_ptr();
+    if (scratch == nullptr) return PXL_ERR_CUDA;
+  }
+  // Every (sequence, head, split) partial that the reduction reads is written by the main
+  // kernel of this same call, so the array needs no clearing between calls.
+  return pxl_attn_decode(q, q_stride, k_cache, v_cache, block_tables, ctx_lens, out, scratch, sinks,
+                         B, Hq, Hkv, D, page_size, max_blocks, num_blocks, scale, window, num_splits,
+                         0, status, stream);
 }
