@@ -130,6 +130,10 @@ def create_app(scheduler_manage: SchedulerManage, request_handler: Optional[Requ
             return err
         return h.node_leave(await req.json())
 
+    @app.post("/node/addresses")
+    async def node_addresses():
+        return dict(sm.call_urls)
+
     @app.post("/v1/chat/completions")
     async def chat(req: HttpRequest):
         try:

@@ -210,6 +210,28 @@ class CacheManager:
         st.ctx_len += 1
         return True
 
+    def extend_request(self, rid: str, new_len: int) -> bool:
+        """Grow a request's reservation to ``new_len`` tokens (later prefill chunks on peers that
+        learn the prompt piecewise). False = out of KV memory; nothing is changed then."""
+        st = self.reqs.get(rid)
+        if st is None:
+            raise ValueError(f"request {rid} not found")
+        need = self.blocks_needed(new_len)
+        if need > self.max_blocks_per_seq:
+            return False
+        extra = need - st.num_blocks
+        if extra > 0:
+            free = self.allocator.get_num_free_blocks()
+            if free < extra:
+                self._evict(extra - free)
+            got = self.allocator.allocate_np(extra)
+            if got is None:
+                return False
+            self.tables[st.row, st.num_blocks:need] = got
+            st.num_blocks = need
+        st.ctx_len = max(st.ctx_len, new_len)
+        return True
+
     def slot_of(self, rid: str, pos: int) -> int:
         st = self.reqs[rid]
         return int(self.tables[st.row, pos // self.block_size]) * self.block_size + pos % self.block_size

@@ -1,0 +1,289 @@
+"""Executor of ONE pipeline peer that talks to its neighbours through stage packets.
+
+This is the cross-node path (``parallax join``): a peer owns layers ``[start, end)``; the
+first peer owns the request state and the batch scheduler, later peers are driven by the
+packets they receive, the last peer samples and sends only the token id back to the first
+peer - the protocol of the reference's executor
+(``src/parallax/server/executor/base_executor.py:566-769,845-863``,
+``src/parallax/server/request.py:268-393``). Packets are :class:`IntermediateRequest`s and
+are serialised by :mod:`parallax_b200.p2p.message_util` when they leave the process.
+
+Every peer keeps its own paged KV cache and prefix cache; the prompt token ids travel with
+prefill packets so that each peer can publish and match prefixes itself. The first peer
+decides how many cached tokens are skipped (``chunk_start``); a later peer that cannot serve
+that prefix from its own cache answers with an abort for the request.
+
+Chunked prefill: the first peer re-queues a request for its next chunk as soon as its own
+layers are done with the current one, so chunks stream through the stages back to back; the
+last peer drops the logits of non-final chunks.
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Optional
+
+import torch
+
+from parallax_b200 import ops
+from parallax_b200.engine.batch import BatchBuilder
+from parallax_b200.engine.engine import Planner
+from parallax_b200.engine.request import IntermediateRequest, Request, RequestStatus, SamplingParams
+from parallax_b200.engine.scheduler import ScheduledSeq
+from parallax_b200.engine.worker import StageWorker
+from parallax_b200.models.config import ModelConfig
+
+logger = logging.getLogger(__name__)
+
+
+class PeerExecutor:
+    def __init__(self, cfg: ModelConfig, start_layer: int, end_layer: int, device="cpu", dtype=None,
+                 node_id: str = "node", page_size: int = 16, num_blocks: Optional[int] = None,
+                 kv_fraction: float = 0.8, max_batch_size: int = 8, max_num_tokens_per_batch: int = 16384,
+                 micro_batch_ratio: int = 1, chunked_prefill_size: Optional[int] = 1024,
+                 enable_prefix_cache: bool = True, max_total_length: int = 32768,
+                 request_timeout_s: Optional[float] = 600, eos_token_id=None, seed: int = 0,
+                 weights: Optional[dict] = None, shared_state=None):
+        self.cfg, self.node_id = cfg, node_id
+        self.device = torch.device(device)
+        max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
+        self.worker = StageWorker(cfg, start_layer, end_layer, self.device, dtype, page_size, num_blocks=num_blocks,
+                                  kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions)
+        self.is_first, self.is_last = self.worker.is_first, self.worker.is_last
+        self.planner = Planner(cfg, self.worker.num_blocks, page_size, max_batch_size, max_num_tokens_per_batch,
+                               micro_batch_ratio, chunked_prefill_size, enable_prefix_cache, max_total_length,
+                               request_timeout_s, eos_token_id, shared_state)
+        self.scheduler, self.cache = self.planner.scheduler, self.planner.cache
+        self.builder = BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size, max_batch_size,
+                                    self.cache.max_blocks_per_seq)
+        self.mirror: dict[str, Request] = {}   # later peers: per-request shadow state
+        self._gen = torch.Generator(device=self.device)
+        self._gen.manual_seed(seed + 777)
+
+    # ------------------------------------------------------------------ shared forward
+    def _run(self, seqs: list[ScheduledSeq], hidden: Optional[torch.Tensor]):
+        arrays = self.planner.plan_arrays(seqs)
+        if arrays is None:
+            return None, None
+        fb = self.builder.build(arrays["ids"] if self.is_first else None, arrays["pos"], arrays["slots"],
+                                arrays["p_q"], arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"],
+                                arrays["d_tables"], arrays["logit_rows"])
+        with torch.inference_mode():
+            if self.is_last:
+                h = self.worker.model.embed_tokens(fb) if self.is_first else hidden
+                h = self.worker.model.forward_layers(h, fb)
+                out = (h, self.worker.model.logits(h, fb) if arrays["owners"] else None)
+            else:
+                out = (self.worker.run(fb, hidden), None)
+        return arrays, out
+
+    def _sample(self, logits: torch.Tensor, owners: list[ScheduledSeq]):
+        sps = [s.req.sampling_params for s in owners]
+        if all(sp.is_greedy for sp in sps):
+            ids, lp = ops.argmax(logits, want_logprob=True)
+            return ids.tolist(), lp.exp().tolist()
+        dev = logits.device
+        t = torch.tensor([0.0 if sp.is_greedy else sp.temperature for sp in sps], dtype=torch.float32, device=dev)
+        k = torch.tensor([sp.top_k if sp.top_k > 0 else 0 for sp in sps], dtype=torch.int32, device=dev)
+        p = torch.tensor([sp.top_p for sp in sps], dtype=torch.float32, device=dev)
+        mp = torch.tensor([sp.min_p for sp in sps], dtype=torch.float32, device=dev)
+        u = torch.rand(len(sps), generator=self._gen, device=dev, dtype=torch.float32)
+        ids, pr = ops.sample(logits, t, k, p, mp, u, want_prob=True)
+        return ids.tolist(), pr.tolist()
+
+    def _hidden_packets(self, arrays, h: torch.Tensor) -> list[IntermediateRequest]:
+        """One packet per sequence carrying its slice of the stage output."""
+        out, o = [], 0
+        for s in arrays["ordered"]:
+            n = s.num_tokens
+            pk = IntermediateRequest.from_request(s.req, hidden_states=h[o:o + n], chunk_start=s.start,
+                                                  num_tokens=n) if s.is_prefill else \
+                IntermediateRequest.from_request(s.req, hidden_states=h[o:o + 1])
+            if s.is_prefill:
+                pk.is_last_chunk = s.produces_token
+                pk.is_chunked = s.req.is_chunked
+            out.append(pk)
+            o += n
+        return out
+
+    # ------------------------------------------------------------------ first peer
+    def add_request(self, req: Request) -> None:
+        assert self.is_first, "requests enter the pipeline at the first peer"
+        req.sampling_params.verify()
+        req.max_total_length = min(req.max_total_length, self.planner.max_total_length)
+        self.scheduler.enque_request(req)
+
+    def has_work(self) -> bool:
+        return self.scheduler.num_queued_requests > 0 or self.scheduler.num_running_requests > 0
+
+    def step_first(self):
+        """Form and run one batch on the first peer.
+
+        Returns ``(packets_for_next_peer, events, releases)``: ``events`` are
+        ``(request, token or None)`` for requests that progressed or finished locally (single-peer
+        pipelines sample here); ``releases`` are request ids every other peer must free."""
+        assert self.is_first
+        events, releases = [], []
+        for req in self.scheduler.get_timed_out_requests():
+            req.update_status(RequestStatus.FINISHED_ABORT)
+            self._finish_first(req, events, releases)
+        seqs = [s for s in self.scheduler.form_batch()]
+        for req in self.scheduler.pop_rejected():
+            events.append((req, None))
+        live = []
+        for s in seqs:
+            if s.req.abort:
+                s.req.update_status(RequestStatus.FINISHED_ABORT)
+                self._finish_first(s.req, events, releases)
+            else:
+                live.append(s)
+        if not live:
+            return [], events, releases
+        arrays, out = self._run(live, None)
+        for s in live:
+            if s.req.is_finished:
+                self._finish_first(s.req, events, releases)
+        if arrays is None:
+            return [], events, releases
+        h, logits = out
+        for s in arrays["ordered"]:
+            if s.is_prefill:
+                s.req.num_computed_tokens = s.start + s.num_tokens
+                self.cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens)
+        if self.is_last:
+            toks, probs = self._sample(logits, arrays["owners"]) if arrays["owners"] else ([], [])
+            idx = {id(s): i for i, s in enumerate(arrays["owners"])}
+            for s in arrays["ordered"]:
+                i = idx.get(id(s))
+                self._commit(s.req, None if i is None else toks[i], None if i is None else probs[i], events, releases)
+            return [], events, releases
+        packets = self._hidden_packets(arrays, h)
+        for s in arrays["ordered"]:
+            if s.is_prefill and not s.produces_token:
+                self.scheduler.enque_request(s.req)   # next chunk may start right away
+        return packets, events, releases
+
+    def _finish_first(self, req: Request, events, releases) -> None:
+        self.scheduler.evict_request(req.request_id)
+        self.cache.free_request(req.request_id)
+        events.append((req, None))
+        releases.append(req.request_id)
+
+    def _commit(self, req: Request, tok, prob, events, releases) -> None:
+        if tok is not None:
+            req.commit_new_token(int(tok), prob if req.return_probs else None)
+            self.cache.update_request_tokens(req.request_id, [int(tok)])
+        if self.scheduler.check_and_update_request_status(req):
+            self.cache.free_request(req.request_id)
+            releases.append(req.request_id)
+            events.append((req, tok))
+        else:
+            self.scheduler.enque_request(req)
+            if tok is not None:
+                events.append((req, tok))
+
+    def receive_tokens(self, packets: list[IntermediateRequest]):
+        """First peer: tokens (or aborts) coming back from the last peer."""
+        assert self.is_first
+        events, releases = [], []
+        for pk in packets:
+            req = self.scheduler.get_running_request(pk.request_id)
+            if req is None:
+                continue
+            if pk.abort or pk.status in (RequestStatus.FINISHED_ABORT, RequestStatus.ERROR):
+                req.abort = True
+                self._commit(req, None, None, events, releases)
+                continue
+            self._commit(req, pk.next_token_id, pk.token_prob, events, releases)
+        return events, releases
+
+    # ------------------------------------------------------------------ later peers
+    def release(self, request_ids) -> None:
+        for rid in request_ids:
+            self.mirror.pop(rid, None)
+            self.cache.free_request(rid)
+
+    def _admit_packet(self, pk: IntermediateRequest) -> Optional[ScheduledSeq]:
+        rid = pk.request_id
+        m = self.mirror.get(rid)
+        if pk.is_prefill:
+            end = pk.current_position
+            ids = list(pk.input_ids or [])
+            if m is None:
+                m = Request(request_id=rid, input_ids=ids, sampling_params=pk.sampling_params,
+                            routing_table=pk.routing_table, return_probs=pk.return_probs,
+                            max_total_length=self.planner.max_total_length)
+                ok, matched = self.cache.allocate_request(rid, end, token_ids=ids)
+                if not ok or matched < pk.chunk_start:
+                    if ok:
+                        self.cache.free_request(rid)
+                    return None
+                self.mirror[rid] = m
+            else:
+                m.input_ids, m.prompt_len = ids, len(ids)
+                known = self.cache.reqs[rid].tokens
+                if known is not None:
+                    self.cache.update_request_tokens(rid, ids[len(known):])
+                if not self.cache.extend_request(rid, end):
+                    return None
+            m.is_chunked = pk.is_chunked
+            return ScheduledSeq(m, end - pk.chunk_start, pk.chunk_start, True, pk.is_last_chunk)
+        if m is None:
+            return None
+        m.status = RequestStatus.DECODING
+        n_out = pk.current_position - m.prompt_len
+        m.output_ids = [0] * max(n_out - 1, 0) + [int(pk.next_token_id or 0)]
+        return ScheduledSeq(m, 1, pk.current_position - 1, False, True)
+
+    def process_packets(self, packets: list[IntermediateRequest]) -> list[IntermediateRequest]:
+        """Run this peer's layers on a batch of incoming packets.
+
+        Returns hidden-state packets for the next peer, or (on the last peer) token packets for
+        the first peer. Requests this peer cannot serve come back as abort packets."""
+        assert not self.is_first
+        out: list[IntermediateRequest] = []
+        seqs, hidden = [], []
+        for pk in packets:
+            if pk.abort or pk.is_finished:
+                self.release([pk.request_id])
+                continue
+            s = self._admit_packet(pk)
+            if s is None:
+                bad = IntermediateRequest(pk.request_id, pk.current_position, RequestStatus.FINISHED_ABORT,
+                                          routing_table=pk.routing_table)
+                bad.abort = True
+                out.append(bad)
+                self.release([pk.request_id])
+                continue
+            seqs.append((s, pk))
+        if not seqs:
+            return out
+        # plan order is prefill first, then decode: order the hidden states the same way
+        seqs.sort(key=lambda sp: 0 if sp[0].is_prefill else 1)
+        for s, pk in seqs:
+            hidden.append(pk.hidden_states.to(device=self.device, dtype=self.worker.dtype))
+        arrays, res = self._run([s for s, _ in seqs], torch.cat(hidden, dim=0))
+        for s, pk in seqs:
+            if s.req.is_finished:   # KV exhausted while appending a decode slot
+                bad = IntermediateRequest(pk.request_id, pk.current_position, RequestStatus.FINISHED_ABORT,
+                                          routing_table=pk.routing_table)
+                bad.abort = True
+                out.append(bad)
+                self.release([pk.request_id])
+        if arrays is None:
+            return out
+        h, logits = res
+        for s in arrays["ordered"]:
+            if s.is_prefill:
+                self.cache.insert_full_blocks_to_cache(s.req.request_id, s.start + s.num_tokens)
+        if not self.is_last:
+            return out + self._hidden_packets(arrays, h)
+        if arrays["owners"]:
+            toks, probs = self._sample(logits, arrays["owners"])
+            for s, t, p in zip(arrays["owners"], toks, probs):
+                r = s.req
+                out.append(IntermediateRequest(r.request_id, r.total_length + 1, RequestStatus.DECODING,
+                                               next_token_id=int(t), routing_table=r.routing_table,
+                                               sampling_params=r.sampling_params, token_prob=float(p),
+                                               return_probs=r.return_probs))
+        return out

@@ -153,6 +153,53 @@ class DecoderStage:
                 lw.w_gu = ops.interleave_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"))
                 lw.w_down = get(p + "mlp.down_proj.weight").contiguous()
 
+    @torch.no_grad()
+    def update_weights(self, tensors: dict[str, torch.Tensor]) -> int:
+        """Patch weights in place from HF-named tensors (online refit). Tensors of layers that
+        this stage does not own are ignored. Returns the number of tensors applied."""
+        cfg = self.cfg
+        Hq, Hkv, D, I = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
+        by_layer = {lw.layer_idx: lw for lw in self.layers}
+        n = 0
+
+        def cp(dst, src):
+            dst.copy_(src.to(device=dst.device, dtype=dst.dtype))
+
+        for key, t in tensors.items():
+            if key == "model.embed_tokens.weight" and self.embed is not None:
+                cp(self.embed, t); n += 1
+            elif key == "model.norm.weight" and self.norm_w is not None:
+                cp(self.norm_w, t); n += 1
+            elif key == "lm_head.weight" and self.lm_head is not None:
+                cp(self.lm_head, t); n += 1
+            elif key.startswith("model.layers."):
+                parts = key.split(".")
+                lw = by_layer.get(int(parts[2]))
+                if lw is None:
+                    continue
+                name = ".".join(parts[3:])
+                qkv_off = {"self_attn.q_proj": (0, Hq * D), "self_attn.k_proj": (Hq * D, Hkv * D),
+                           "self_attn.v_proj": ((Hq + Hkv) * D, Hkv * D)}
+                base, _, kind = name.rpartition(".")
+                if base in qkv_off:
+                    o, ln = qkv_off[base]
+                    tgt = lw.w_qkv if kind == "weight" else lw.b_qkv
+                    if tgt is not None:
+                        cp(tgt[o:o + ln], t); n += 1
+                elif name == "self_attn.o_proj.weight":
+                    cp(lw.w_o, t); n += 1
+                elif name in ("mlp.gate_proj.weight", "mlp.up_proj.weight") and lw.w_gu is not None:
+                    view = lw.w_gu.view(I // 64, 2, 64, -1)
+                    cp(view[:, 0 if "gate" in name else 1], t.reshape(I // 64, 64, -1)); n += 1
+                elif name == "mlp.down_proj.weight" and lw.w_down is not None:
+                    cp(lw.w_down, t); n += 1
+                else:
+                    simple = {"input_layernorm.weight": "ln1", "post_attention_layernorm.weight": "ln2",
+                              "self_attn.q_norm.weight": "q_norm", "self_attn.k_norm.weight": "k_norm"}.get(name)
+                    if simple and getattr(lw, simple) is not None:
+                        cp(getattr(lw, simple), t); n += 1
+        return n
+
     def weight_bytes(self) -> int:
         seen, total = set(), 0
         def add(t):

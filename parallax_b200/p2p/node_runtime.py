@@ -1,0 +1,271 @@
+"""Runtime of a cluster worker node: peer executor + packet endpoints + (first peer) frontend.
+
+One ``NodeRuntime`` serves one layer allocation. It owns a :class:`PeerExecutor`, a run thread
+and an HTTP app with
+
+* ``POST /pp_forward``  - ForwardRequest message from the previous peer (hidden states) or, on
+                          the first peer, from the last peer (sampled tokens);
+* ``POST /pp_abort``    - request ids to release;
+* the OpenAI endpoints when this node hosts layer 0.
+
+The run thread is the counterpart of the reference's executor loop for non-standalone nodes
+(``src/parallax/server/executor/base_executor.py:634-769``) and of its P2P sender
+(``src/parallax/p2p/server.py:628-749``).
+"""
+
+from __future__ import annotations
+
+import logging
+import queue
+import threading
+import time
+from typing import Optional
+
+from fastapi import FastAPI
+from fastapi import Request as HttpRequest
+
+from parallax_b200.engine.request import Request, RequestStatus
+from parallax_b200.engine.service import TokenEvent
+
+logger = logging.getLogger(__name__)
+
+
+class PeerLoop:
+    """Drives a PeerExecutor; exposes the EngineLoop interface (submit / abort) on the first peer."""
+
+    def __init__(self, peer, transport, shared_state=None, idle_sleep_s: float = 0.002):
+        self.peer, self.transport, self.state = peer, transport, shared_state
+        self.idle_sleep_s = idle_sleep_s
+        self._inbox: "queue.Queue[tuple[str, object]]" = queue.Queue()
+        self._streams: dict[str, "queue.Queue[TokenEvent]"] = {}
+        self._lock = threading.Lock()
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+        self.steps = 0
+
+    # ---- frontend side
+    def submit(self, req: Request):
+        q: "queue.Queue[TokenEvent]" = queue.Queue()
+        with self._lock:
+            self._streams[req.request_id] = q
+        if not req.routing_table:
+            req.routing_table = [self.peer.node_id]
+        self._inbox.put(("add", req))
+        return q
+
+    def abort(self, request_id: str) -> None:
+        self._inbox.put(("abort", request_id))
+
+    @property
+    def num_inflight(self) -> int:
+        with self._lock:
+            return len(self._streams)
+
+    # ---- network side
+    def on_packets(self, packets) -> None:
+        self._inbox.put(("packets", packets))
+
+    def on_abort(self, request_ids) -> None:
+        self._inbox.put(("release", list(request_ids)))
+
+    def start(self) -> None:
+        self._thread = threading.Thread(target=self._run, name="PeerLoop", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(5.0)
+
+    # ---- loop
+    def _emit(self, req: Request, tok) -> None:
+        ev = TokenEvent(req.request_id, tok, req.is_finished, req.status,
+                        prob=req.output_probs[-1] if (tok is not None and req.output_probs) else None)
+        with self._lock:
+            q = self._streams.get(req.request_id)
+            if ev.finished:
+                self._streams.pop(req.request_id, None)
+        if q is not None:
+            q.put(ev)
+
+    def _broadcast_release(self, releases, tables: dict) -> None:
+        for rid in releases:
+            table = tables.pop(rid, None)
+            if table and len(table) > 1:
+                self.transport.send_abort([rid], table, self.peer.node_id)
+
+    def _run(self) -> None:
+        peer = self.peer
+        tables: dict[str, list[str]] = {}
+        n_layers = peer.worker.end_layer - peer.worker.start_layer
+        while not self._stop.is_set():
+            busy = False
+            while True:
+                try:
+                    kind, payload = self._inbox.get_nowait()
+                except queue.Empty:
+                    break
+                busy = True
+                try:
+                    if kind == "add":
+                        req: Request = payload  # type: ignore[assignment]
+                        tables[req.request_id] = list(req.routing_table)
+                        try:
+                            peer.add_request(req)
+                        except Exception as exc:
+                            req.update_status(RequestStatus.ERROR)
+                            self._emit(req, None)
+                            logger.warning("rejected request %s: %s", req.request_id, exc)
+                    elif kind == "abort":
+                        try:
+                            peer.scheduler.cancel_request(str(payload))
+                        except ValueError:
+                            pass
+                    elif kind == "release":
+                        peer.release(payload)
+                    elif kind == "packets":
+                        if peer.is_first:
+                            events, releases = peer.receive_tokens(payload)
+                            for req, tok in events:
+                                self._emit(req, tok)
+                            self._broadcast_release(releases, tables)
+                        else:
+                            t0 = time.perf_counter()
+                            out = peer.process_packets(payload)
+                            self.steps += 1
+                            if out:
+                                self.transport.send_forward(out, peer.node_id)
+                            if self.state is not None:
+                                self.state.update_metrics(current_requests=len(peer.mirror),
+                                                          layer_latency_ms_sample=(time.perf_counter() - t0) * 1e3 / n_layers)
+                except Exception as exc:
+                    logger.exception("peer loop error: %s", exc)
+            if peer.is_first and peer.has_work():
+                busy = True
+                t0 = time.perf_counter()
+                try:
+                    packets, events, releases = peer.step_first()
+                except Exception as exc:
+                    logger.exception("first-peer step failed: %s", exc)
+                    for req in list(peer.scheduler.running_requests()):
+                        req.update_status(RequestStatus.ERROR)
+                        peer.scheduler.evict_request(req.request_id)
+                        peer.cache.free_request(req.request_id)
+                        self._emit(req, None)
+                    continue
+                self.steps += 1
+                for req, tok in events:
+                    self._emit(req, tok)
+                self._broadcast_release(releases, tables)
+                if packets:
+                    self.transport.send_forward(packets, peer.node_id)
+                if self.state is not None and (packets or events):
+                    self.state.update_metrics(current_requests=peer.scheduler.num_running_requests,
+                                              layer_latency_ms_sample=(time.perf_counter() - t0) * 1e3 / n_layers)
+            if not busy:
+                time.sleep(self.idle_sleep_s)
+
+
+def create_peer_app(loop: PeerLoop, tokenizer=None, model_name: str = "", max_model_len: int = 32768):
+    from parallax_b200.p2p.message_util import proto_to_abort_request, proto_to_request
+
+    if loop.peer.is_first and tokenizer is not None:
+        from parallax_b200.frontend.openai_api import create_app
+
+        app = create_app(loop, tokenizer, model_name, max_model_len)
+    else:
+        app = FastAPI(title="parallax_b200 peer")
+
+        @app.get("/health")
+        async def health():
+            return {"status": "ok", "steps": loop.steps}
+
+    @app.post("/pp_forward")
+    async def pp_forward(req: HttpRequest):
+        loop.on_packets(proto_to_request(await req.body()))
+        return {"ok": True}
+
+    @app.post("/pp_abort")
+    async def pp_abort(req: HttpRequest):
+        loop.on_abort(proto_to_abort_request(await req.body()))
+        return {"ok": True}
+
+    return app
+
+
+class NodeRuntime:
+    def __init__(self, args, agent, state, model_name: str, start_layer: int, end_layer: int):
+        import torch
+
+        from parallax_b200.engine.peer import PeerExecutor
+        from parallax_b200.frontend.tokenizer import TokenizerWrapper
+        from parallax_b200.launch import resolve_model, serve_http
+        from parallax_b200.p2p.server import PeerTransport
+
+        self.args, self.agent, self.state = args, agent, state
+        args.model_path = args.model_path or model_name
+        args.start_layer, args.end_layer = start_layer, end_layer
+        cfg, loader, name, path = resolve_model(args)
+        device = "cuda:0" if torch.cuda.is_available() else "cpu"
+        weights = loader.load_weights("cpu", None) if loader is not None else None
+        self.peer = PeerExecutor(cfg, start_layer, end_layer, device=device, node_id=agent.node_id,
+                                 page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
+                                 max_batch_size=args.max_batch_size,
+                                 max_num_tokens_per_batch=args.max_num_tokens_per_batch,
+                                 micro_batch_ratio=args.micro_batch_ratio,
+                                 chunked_prefill_size=args.chunked_prefill_size,
+                                 enable_prefix_cache=args.enable_prefix_cache,
+                                 max_total_length=args.max_sequence_length,
+                                 request_timeout_s=args.request_timeout_s, weights=weights, shared_state=state,
+                                 num_blocks=None if device != "cpu" else 1024)
+        self.peer_urls: dict[str, str] = {}
+
+        def resolve(node_id: str):
+            if node_id not in self.peer_urls:
+                try:
+                    self.peer_urls.update(agent.scheduler.node_addresses())
+                except Exception as e:
+                    logger.warning("could not fetch peer addresses: %s", e)
+            return self.peer_urls.get(node_id)
+
+        self.loop = PeerLoop(self.peer, PeerTransport(resolve, notify_url=args.notify_url), state)
+        tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size) if self.peer.is_first else None
+        self.app = create_peer_app(self.loop, tok, name, args.max_sequence_length)
+
+        @self.app.post("/peers")
+        async def set_peers(req: HttpRequest):
+            self.peer_urls.update(await req.json())
+            return {"ok": True}
+
+        self.loop.start()
+        self.server, self.thread = serve_http(self.app, args.host, args.port, args.log_level)
+
+    def apply_refit(self, refit: dict) -> int:
+        """Apply a weight-refit request whose blocks are readable files (``paths``: cid -> file)."""
+        from parallax_b200.utils.weight_refit import (concat_weight_partition, filter_weight_cid_list,
+                                                      parse_safetensors_from_memory, verify_block)
+
+        cfg = self.peer.cfg
+        need = filter_weight_cid_list(self.peer.worker.start_layer, self.peer.worker.end_layer,
+                                      cfg.num_hidden_layers, refit.get("index_map") or {})
+        paths = refit.get("paths") or {}
+        tensors = {}
+        for cid in need:
+            p = paths.get(cid)
+            if p is None:
+                logger.warning("refit block %s has no source; skipped", cid)
+                continue
+            blob = open(p, "rb").read()
+            if not verify_block(blob, cid):
+                raise ValueError(f"refit block {cid} failed its content-id check")
+            tensors.update(parse_safetensors_from_memory(blob))
+        return self.peer.worker.model.update_weights(concat_weight_partition(tensors))
+
+    def serve_until_allocation_changes(self, poll_s: float = 0.5) -> None:
+        while not self.state.get_layer_allocation_changed() and self.thread.is_alive():
+            time.sleep(poll_s)
+
+    def shutdown(self) -> None:
+        self.server.should_exit = True
+        self.loop.stop()
+        self.thread.join(5.0)

@@ -1,0 +1,102 @@
+"""Three pipeline peers chained in one process with the wire emulated: every hop goes through
+request_to_proto / proto_to_request, as the reference's executor test does
+(tests/test_executor.py:67-285). The result must equal the single-engine run."""
+
+import torch
+
+from parallax_b200.engine.engine import Engine
+from parallax_b200.engine.peer import PeerExecutor
+from parallax_b200.engine.request import Request, SamplingParams
+from parallax_b200.models.config import named_config
+from parallax_b200.p2p.message_util import proto_to_request, request_to_proto
+
+
+def _wire(packets):
+    return proto_to_request(request_to_proto(packets)) if packets else []
+
+
+def _prompts(n, length, vocab, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def _run_pipeline(cfg, spans, prompts, max_new, **kw):
+    peers = [PeerExecutor(cfg, s, e, device="cpu", node_id=f"n{i}", num_blocks=128, max_batch_size=8, **kw)
+             for i, (s, e) in enumerate(spans)]
+    table = [p.node_id for p in peers]
+    reqs = [Request(input_ids=p, routing_table=table,
+                    sampling_params=SamplingParams(max_new_tokens=max_new, temperature=0.0, ignore_eos=True))
+            for p in prompts]
+    for r in reqs:
+        peers[0].add_request(r)
+    steps = 0
+    while peers[0].has_work() and steps < 500:
+        steps += 1
+        packets, _events, releases = peers[0].step_first()
+        for peer in peers[1:]:
+            peer.release(releases)
+        back = []
+        for peer in peers[1:]:
+            packets = peer.process_packets(_wire(packets))
+            back = packets
+        if len(peers) > 1:
+            _events, releases = peers[0].receive_tokens(_wire([p for p in back if p.hidden_states is None]))
+            for peer in peers[1:]:
+                peer.release(releases)
+    return [r.output_ids for r in reqs], peers
+
+
+def test_three_peers_match_single_engine():
+    cfg = named_config("tiny")
+    prompts = _prompts(3, 41, cfg.vocab_size, seed=4)
+    want = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=8).generate(
+        prompts, SamplingParams(max_new_tokens=9, temperature=0.0, ignore_eos=True))
+    got, peers = _run_pipeline(cfg, [(0, 1), (1, 3), (3, 4)], prompts, 9)
+    assert got == want
+    # every peer released every request
+    for p in peers:
+        assert not p.cache.reqs and not p.mirror
+
+
+def test_chunked_prefill_streams_through_peers_and_prefix_cache_is_per_peer():
+    cfg = named_config("tiny")
+    prompts = _prompts(2, 100, cfg.vocab_size, seed=5)
+    want = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=8, chunked_prefill_size=None,
+                  enable_prefix_cache=False).generate(prompts, SamplingParams(max_new_tokens=5, temperature=0.0,
+                                                                              ignore_eos=True))
+    got, peers = _run_pipeline(cfg, [(0, 2), (2, 4)], prompts, 5, chunked_prefill_size=32)
+    assert got == want
+    assert all(p.cache.prefix_cache.num_nodes >= 2 * (100 // 16) for p in peers)
+
+
+def test_single_peer_pipeline_samples_locally():
+    cfg = named_config("tiny")
+    prompts = _prompts(2, 20, cfg.vocab_size, seed=6)
+    want = Engine(cfg, device="cpu", num_blocks=64, max_batch_size=8).generate(
+        prompts, SamplingParams(max_new_tokens=4, temperature=0.0, ignore_eos=True))
+    got, _ = _run_pipeline(cfg, [(0, 4)], prompts, 4)
+    assert got == want
+
+
+def test_peer_without_the_prefix_aborts_the_request():
+    cfg = named_config("tiny")
+    first = PeerExecutor(cfg, 0, 2, device="cpu", node_id="a", num_blocks=64)
+    last = PeerExecutor(cfg, 2, 4, device="cpu", node_id="b", num_blocks=64)
+    prompt = _prompts(1, 48, cfg.vocab_size, seed=7)[0]
+    # warm only the first peer's prefix cache
+    warm = Request(input_ids=prompt, routing_table=["a", "b"],
+                   sampling_params=SamplingParams(max_new_tokens=1, temperature=0.0, ignore_eos=True))
+    first.add_request(warm)
+    pk, _, _ = first.step_first()
+    first.receive_tokens(_wire(last.process_packets(_wire(pk))))
+    last.release([warm.request_id])
+    last.cache.prefix_cache.reset()
+    again = Request(input_ids=prompt, routing_table=["a", "b"],
+                    sampling_params=SamplingParams(max_new_tokens=2, temperature=0.0, ignore_eos=True))
+    first.add_request(again)
+    pk, _, _ = first.step_first()
+    assert pk[0].chunk_start > 0                                   # first peer skipped cached tokens
+    back = last.process_packets(_wire(pk))
+    assert back and back[0].abort
+    events, releases = first.receive_tokens(_wire(back))
+    assert again.is_finished and releases == [again.request_id]
