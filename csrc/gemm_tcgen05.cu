@@ -43,11 +43,46 @@ struct GemmEpilogueArgs {
   int ldc;
 };
 
+// Grouped (per-expert) mode: the m-tiles are listed on the device, one entry per 128-row
+// tile of an expert's segment of the permuted activation matrix. num_mt == nullptr selects
+// the plain dense mode.
+struct GemmGroupArgs {
+  const int* mt_expert;    // expert id of m-tile i
+  const int* mt_row0;      // first row of m-tile i in A / C
+  const int* mt_row_end;   // end (exclusive) of the expert's segment: rows beyond are not stored
+  const int* num_mt;       // number of m-tiles (device scalar)
+  int w_rows_per_expert;   // rows of W per expert (N of one expert's matrix)
+};
+
+struct TileCoord {
+  int a_row, b_row, row_end, n_blk;
+};
+
+template <int BN>
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int M,
+                                                const GemmGroupArgs& g) {
+  TileCoord c;
+  if (g.num_mt != nullptr) {
+    const int mt = tile / num_n;
+    c.n_blk = tile % num_n;
+    c.a_row = g.mt_row0[mt];
+    c.row_end = g.mt_row_end[mt];
+    c.b_row = g.mt_expert[mt] * g.w_rows_per_expert + c.n_blk * BN;
+  } else {
+    const int m_blk = tile % num_m;
+    c.n_blk = tile / num_m;
+    c.a_row = m_blk * BM;
+    c.row_end = M;
+    c.b_row = c.n_blk * BN;
+  }
+  return c;
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                         const __grid_constant__ CUtensorMap tmap_b, GemmEpilogueArgs ep, int M,
-                         int N, int K, int* status) {
+                         const __grid_constant__ CUtensorMap tmap_b, GemmEpilogueArgs ep,
+                         GemmGroupArgs grp, int M, int N, int K, int* status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -68,7 +103,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int num_m = ceil_div(M, BM);
+  const int num_m = grp.num_mt != nullptr ? *grp.num_mt : ceil_div(M, BM);
   const int num_n = ceil_div(N, BN);
   const int num_tiles = num_m * num_n;
   const int num_kb = ceil_div(K, BK);
@@ -104,17 +139,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m_blk = tile % num_m;
-        const int n_blk = tile / num_m;
+        const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, status,
                                  PXL_DEV_TIMEOUT_EMPTY);
           if (!ok) break;
           const uint32_t fb = full0 + 8 * stage;
           mbar_arrive_expect_tx(fb, A_STAGE_BYTES + Cfg::B_STAGE_BYTES);
-          tma_load_2d(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, kb * BK, m_blk * BM);
+          tma_load_2d(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, kb * BK, tc.a_row);
           tma_load_2d(smem_u32(smem_b + stage * Cfg::B_STAGE_BYTES), &tmap_b, fb, kb * BK,
-                      n_blk * BN);
+                      tc.b_row);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -169,14 +203,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const int m_blk = tile % num_m;
-      const int n_blk = tile / num_m;
+      const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp);
+      const int n_blk = tc.n_blk;
+      const int M_end = tc.row_end;
       ok = mbar_wait_bounded(tfull0 + 8 * acc, acc_phase, abort_flag, status,
                              PXL_DEV_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = m_blk * BM + q * 32 + lane;
+      const int row = tc.a_row + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       if constexpr (EPI == PXL_EPI_SILU_MUL) {
         // W rows come in groups of 128: 64 gate rows then the 64 up rows of the same outputs
@@ -189,7 +224,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tmem_ld_32x32b_x32(t_row + grp * 128 + cin, g);
           tmem_ld_32x32b_x32(t_row + grp * 128 + 64 + cin, u);
           tmem_ld_wait();
-          if (row < M) {
+          if (row < M_end) {
             bf16* dst = ep.C + static_cast<size_t>(row) * ep.ldc + out_col;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -217,7 +252,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_row + c0, r);
           tmem_ld_wait();
-          if (row < M) {
+          if (row < M_end) {
             const size_t off = static_cast<size_t>(row) * ep.ldc + col0 + c0;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -280,8 +315,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 template <int BN, int EPI>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogueArgs& ep, int M,
-                int N, int K, int* status, cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogueArgs& ep,
+                const GemmGroupArgs& grp, int max_tiles, int M, int N, int K, int* status,
+                cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI>;
   static bool configured[64] = {false};
@@ -293,24 +329,26 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue
       return PXL_ERR_CUDA;
     configured[dev] = true;
   }
-  const int tiles = pxl::ceil_div(M, BM) * pxl::ceil_div(N, BN);
+  const int tiles = max_tiles > 0 ? max_tiles : pxl::ceil_div(M, BM) * pxl::ceil_div(N, BN);
   const int grid = tiles < pxl_host::num_sms() ? tiles : pxl_host::num_sms();
-  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, ep, M, N, K, status);
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, ep, grp, M, N, K, status);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
 }
 
 template <int BN>
 int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogueArgs& ep,
-                 int M, int N, int K, int* status, cudaStream_t stream) {
+                 const GemmGroupArgs& grp, int max_tiles, int M, int N, int K, int* status,
+                 cudaStream_t stream) {
+#define PXL_GEMM_CASE(E) \
+  case E: return launch_gemm<BN, E>(ta, tb, ep, grp, max_tiles, M, N, K, status, stream)
   switch (epi) {
-    case PXL_EPI_NONE: return launch_gemm<BN, PXL_EPI_NONE>(ta, tb, ep, M, N, K, status, stream);
-    case PXL_EPI_RESIDUAL:
-      return launch_gemm<BN, PXL_EPI_RESIDUAL>(ta, tb, ep, M, N, K, status, stream);
-    case PXL_EPI_SILU_MUL:
-      return launch_gemm<BN, PXL_EPI_SILU_MUL>(ta, tb, ep, M, N, K, status, stream);
-    case PXL_EPI_F32: return launch_gemm<BN, PXL_EPI_F32>(ta, tb, ep, M, N, K, status, stream);
+    PXL_GEMM_CASE(PXL_EPI_NONE);
+    PXL_GEMM_CASE(PXL_EPI_RESIDUAL);
+    PXL_GEMM_CASE(PXL_EPI_SILU_MUL);
+    PXL_GEMM_CASE(PXL_EPI_F32);
     default: return PXL_ERR_INVALID_ARG;
   }
+#undef PXL_GEMM_CASE
 }
 
 }  // namespace
@@ -353,10 +391,48 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
   ep.residual = static_cast<const pxl::bf16*>(residual);
   ep.bias = static_cast<const pxl::bf16*>(bias);
   ep.ldc = ldc;
+  GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
   switch (bn) {
-    case 256: return dispatch_epi<256>(epi, ta, tb, ep, M, N, K, status, stream);
-    case 128: return dispatch_epi<128>(epi, ta, tb, ep, M, N, K, status, stream);
-    case 64: return dispatch_epi<64>(epi, ta, tb, ep, M, N, K, status, stream);
+    case 256: return dispatch_epi<256>(epi, ta, tb, ep, grp, 0, M, N, K, status, stream);
+    case 128: return dispatch_epi<128>(epi, ta, tb, ep, grp, 0, M, N, K, status, stream);
+    case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, 0, M, N, K, status, stream);
+    default: return PXL_ERR_INVALID_ARG;
+  }
+}
+
+// Grouped GEMM over experts: for every m-tile i listed on the device,
+//   C[rows of tile i, :] = A[rows of tile i, :] * W[expert_i]^T
+// A: [P, K] activations permuted so that each expert's tokens are contiguous; W: [E*N, K]
+// (expert matrices stacked); C: [P, N] (N/2 columns with PXL_EPI_SILU_MUL).
+// max_m_tiles bounds the device-side count and sizes the grid.
+PXL_EXPORT int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int P, int E, int N,
+                                     int K, int lda, int ldw, int ldc, const int* mt_expert,
+                                     const int* mt_row0, const int* mt_row_end, const int* num_mt,
+                                     int max_m_tiles, int epi, int bn, int* status,
+                                     cudaStream_t stream) {
+  if (P <= 0 || E <= 0 || N <= 0 || K <= 0 || max_m_tiles <= 0) return PXL_ERR_INVALID_ARG;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || (ldc % 8) || (N % 8)) return PXL_ERR_INVALID_ARG;
+  if (epi == PXL_EPI_RESIDUAL) return PXL_ERR_INVALID_ARG;
+  if (bn == 0) bn = (N % 256 == 0 && N >= 1024) ? 256 : 128;
+  if (N % bn) return PXL_ERR_INVALID_ARG;  // a tile must not straddle two experts' rows of W
+  CUtensorMap ta, tb;
+  if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, P, K, lda, BM, BK))
+    return PXL_ERR_TENSORMAP;
+  if (!pxl_host::make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W,
+                              static_cast<uint64_t>(E) * N, K, ldw, bn, BK))
+    return PXL_ERR_TENSORMAP;
+  GemmEpilogueArgs ep;
+  ep.C = static_cast<pxl::bf16*>(C);
+  ep.C_f32 = static_cast<float*>(C);
+  ep.residual = nullptr;
+  ep.bias = nullptr;
+  ep.ldc = ldc;
+  GemmGroupArgs grp{mt_expert, mt_row0, mt_row_end, num_mt, N};
+  const int max_tiles = max_m_tiles * pxl::ceil_div(N, bn);
+  switch (bn) {
+    case 256: return dispatch_epi<256>(epi, ta, tb, ep, grp, max_tiles, P, N, K, status, stream);
+    case 128: return dispatch_epi<128>(epi, ta, tb, ep, grp, max_tiles, P, N, K, status, stream);
+    case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, max_tiles, P, N, K, status, stream);
     default: return PXL_ERR_INVALID_ARG;
   }
 }

@@ -103,6 +103,19 @@ int pxl_moe_route(const void* logits, int logits_bf16, const float* e_bias, int 
                   int mode, int renorm, int n_group, int topk_group, float routed_scale,
                   int* out_ids, float* out_w, pxl_stream_t stream);
 
+int pxl_moe_align(const int* ids, int T, int k, int E, int e_lo, int e_hi, int* counts,
+                  int* offsets, int* cursor, int* mt_expert, int* mt_row0, int* mt_row_end,
+                  int* num_mt, int max_mt, int* pos_of, int* src_tok, pxl_stream_t stream);
+int pxl_moe_gather(const void* x, const int* src_tok, const int* n_rows, void* x_perm,
+                   int max_rows, int H, pxl_stream_t stream);
+int pxl_moe_combine(const void* y_perm, const int* pos_of, const float* w, const void* base,
+                    void* out, int T, int k, int H, pxl_stream_t stream);
+// Grouped GEMM over experts (see gemm_tcgen05.cu).
+int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int P, int E, int N, int K,
+                          int lda, int ldw, int ldc, const int* mt_expert, const int* mt_row0,
+                          const int* mt_row_end, const int* num_mt, int max_m_tiles, int epi,
+                          int bn, int* status, pxl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,107 @@
+"""Mixture-of-experts FFN block (router + stacked SwiGLU experts + optional shared experts).
+
+Covers the routing variants of the supported families: softmax top-k with renormalisation
+(Qwen3-MoE, GLM4-MoE, MiniMax-M2, GPT-OSS style) and sigmoid + correction bias with
+group-limited selection and a routed scaling factor (DeepSeek-V3 / Kimi-K2, MiniMax-M3).
+The reference reaches these through mlx-lm switch layers (``src/parallax/models/qwen3_moe.py``)
+or its own ``minimax_m3.py:155-277``; here routing, permutation, the grouped tcgen05 GEMMs and
+the weighted combine are the kernels of ``csrc/moe.cu`` / ``csrc/gemm_tcgen05.cu``.
+
+Expert weights are stacked: ``w1 [E*2I, H]`` (gate/up rows interleaved in groups of 64 per
+expert) and ``w2 [E*H, I]``. With expert parallelism a rank holds experts ``[e_lo, e_hi)``.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from parallax_b200 import ops
+from parallax_b200.models.config import ModelConfig
+
+
+class MoEWeights:
+    def __init__(self, cfg: ModelConfig):
+        self.cfg = cfg
+        self.router: Optional[torch.Tensor] = None      # [E, H]
+        self.e_bias: Optional[torch.Tensor] = None      # [E] fp32 (noaux_tc correction bias)
+        self.w1: Optional[torch.Tensor] = None          # [E*2I, H]
+        self.w2: Optional[torch.Tensor] = None          # [E*H, I]
+        self.shared_gu: Optional[torch.Tensor] = None   # [2*Is, H] interleaved
+        self.shared_down: Optional[torch.Tensor] = None  # [H, Is]
+        self.shared_gate: Optional[torch.Tensor] = None  # [1, H] sigmoid gate on the shared expert (Qwen2-MoE style)
+        self.num_experts = cfg.num_experts
+        self.top_k = cfg.num_experts_per_tok
+        self.mode = 1 if cfg.scoring_func == "sigmoid" else 0
+
+    def tensors(self):
+        return [t for t in (self.router, self.e_bias, self.w1, self.w2, self.shared_gu, self.shared_down,
+                            self.shared_gate) if t is not None]
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def random(cls, cfg: ModelConfig, device, dtype, rnd: Callable) -> "MoEWeights":
+        m = cls(cfg)
+        E, H, I = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
+        m.router = rnd(E, H, k=0)
+        if cfg.moe_router_bias:
+            m.e_bias = torch.zeros(E, device=device, dtype=torch.float32)
+        g = rnd(E * I, H, k=1).view(E, I, H)
+        u = rnd(E * I, H, k=2).view(E, I, H)
+        m.w1 = torch.stack([ops.interleave_gate_up(g[e], u[e]) for e in range(E)]).view(E * 2 * I, H).contiguous()
+        m.w2 = rnd(E * H, I, k=3)
+        Is = cfg.shared_expert_intermediate_size or (cfg.n_shared_experts * I)
+        if Is:
+            m.shared_gu = ops.interleave_gate_up(rnd(Is, H, k=4), rnd(Is, H, k=5))
+            m.shared_down = rnd(H, Is, k=6)
+        return m
+
+    @classmethod
+    def from_hf(cls, cfg: ModelConfig, tensors: dict, prefix: str, device, dtype) -> "MoEWeights":
+        m = cls(cfg)
+        E = cfg.num_experts
+
+        def get(name, required=True, dt=dtype):
+            t = tensors.get(prefix + name)
+            if t is None:
+                if required:
+                    raise KeyError(f"missing weight {prefix + name}")
+                return None
+            return t.to(device=device, dtype=dt)
+
+        m.router = get("gate.weight").contiguous()
+        m.e_bias = get("gate.e_score_correction_bias", required=False, dt=torch.float32)
+        w1, w2 = [], []
+        for e in range(E):
+            w1.append(ops.interleave_gate_up(get(f"experts.{e}.gate_proj.weight"), get(f"experts.{e}.up_proj.weight")))
+            w2.append(get(f"experts.{e}.down_proj.weight"))
+        m.w1 = torch.cat(w1, dim=0).contiguous()
+        m.w2 = torch.cat(w2, dim=0).contiguous()
+        for shared in ("shared_experts", "shared_expert"):
+            g = get(f"{shared}.gate_proj.weight", required=False)
+            if g is not None:
+                m.shared_gu = ops.interleave_gate_up(g, get(f"{shared}.up_proj.weight"))
+                m.shared_down = get(f"{shared}.down_proj.weight").contiguous()
+        m.shared_gate = get("shared_expert_gate.weight", required=False)
+        return m
+
+    # ------------------------------------------------------------------ forward
+    def route(self, xn: torch.Tensor):
+        cfg = self.cfg
+        logits = ops.linear(xn, self.router, epi=ops.EPI_F32)
+        return ops.moe_route(logits, self.e_bias, self.top_k, self.mode, cfg.norm_topk_prob, cfg.n_group,
+                             cfg.topk_group, cfg.routed_scaling_factor)
+
+    def forward(self, xn: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        """Returns ``h + MoE(xn)`` (the residual add is fused into the combine / shared-expert GEMM)."""
+        ids, w = self.route(xn)
+        base = h
+        if self.shared_gu is not None:
+            act = ops.linear(xn, self.shared_gu, epi=ops.EPI_SILU_MUL)
+            if self.shared_gate is None:
+                base = ops.linear(act, self.shared_down, residual=h)
+            else:
+                gate = torch.sigmoid(xn.float() @ self.shared_gate.float().t()).to(h.dtype)  # [T, 1]: too thin for a tile
+                base = h + gate * ops.linear(act, self.shared_down)
+        return ops.moe_ffn(xn, ids, w, self.w1, self.w2, self.num_experts, base=base)

@@ -59,6 +59,12 @@ _SIGS = {
     "pxl_attn_decode_splits": [c_int, c_int, c_int],
     "pxl_attn_prefill": [_P, c_int64, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int,
                          c_int, c_int, c_int, c_int, c_int64, c_float, c_int, _P, _P],
+    "pxl_moe_route": [_P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P],
+    "pxl_moe_align": [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, _P],
+    "pxl_moe_gather": [_P, _P, _P, _P, c_int, c_int, _P],
+    "pxl_moe_combine": [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P],
+    "pxl_gemm_bf16_grouped": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
+                              c_int, c_int, c_int, _P, _P],
     "pxl_argmax": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P],
     "pxl_sample": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
 }

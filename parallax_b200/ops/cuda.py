@@ -327,5 +327,105 @@ def sample(
     return (ids, pr) if want_prob else ids
 
 
+# ------------------------------------------------------------------------------ MoE
+def moe_route(logits: torch.Tensor, e_bias: Optional[torch.Tensor], k: int, mode: int = 0, renorm: bool = True,
+              n_group: int = 1, topk_group: int = 1, routed_scale: float = 1.0):
+    """Router logits ``[T, E]`` -> (expert ids int32 ``[T, k]``, weights fp32 ``[T, k]``)."""
+    T, E = logits.shape
+    assert logits.is_contiguous()
+    ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    check(_lib.lib().pxl_moe_route(logits.data_ptr(), int(logits.dtype == torch.bfloat16), _ptr(e_bias), T, E, k,
+                                   mode, int(renorm), n_group, topk_group, routed_scale, ids.data_ptr(),
+                                   w.data_ptr(), _stream(logits.device)), "pxl_moe_route")
+    _count()
+    return ids, w
+
+
+class MoEPlan:
+    """Device-side expert-sorted layout of one batch (no host synchronisation)."""
+
+    __slots__ = ("offsets", "mt_expert", "mt_row0", "mt_row_end", "num_mt", "pos_of", "src_tok", "max_mt",
+                 "max_rows", "n_local")
+
+
+def moe_align(ids: torch.Tensor, num_experts: int, e_lo: int = 0, e_hi: Optional[int] = None) -> MoEPlan:
+    T, k = ids.shape
+    e_hi = num_experts if e_hi is None else e_hi
+    n_local = e_hi - e_lo
+    dev = ids.device
+    max_rows = T * k
+    max_mt = (max_rows + 127) // 128 + n_local
+    ints = torch.zeros(n_local * 2 + (n_local + 1) + 3 * max_mt + 1 + 2 * max_rows, dtype=torch.int32, device=dev)
+    o = 0
+
+    def take(n):
+        nonlocal o
+        v = ints[o:o + n]
+        o += n
+        return v
+
+    counts, cursor, offsets = take(n_local), take(n_local), take(n_local + 1)
+    p = MoEPlan()
+    p.mt_expert, p.mt_row0, p.mt_row_end, p.num_mt = take(max_mt), take(max_mt), take(max_mt), take(1)
+    p.pos_of, p.src_tok = take(max_rows), take(max_rows)
+    p.offsets, p.max_mt, p.max_rows, p.n_local = offsets, max_mt, max_rows, n_local
+    check(_lib.lib().pxl_moe_align(ids.data_ptr(), T, k, num_experts, e_lo, e_hi, counts.data_ptr(),
+                                   offsets.data_ptr(), cursor.data_ptr(), p.mt_expert.data_ptr(),
+                                   p.mt_row0.data_ptr(), p.mt_row_end.data_ptr(), p.num_mt.data_ptr(), max_mt,
+                                   p.pos_of.data_ptr(), p.src_tok.data_ptr(), _stream(dev)), "pxl_moe_align")
+    _count(4)
+    return p
+
+
+def moe_gather(x: torch.Tensor, plan: MoEPlan) -> torch.Tensor:
+    H = x.shape[1]
+    # one padding tile so that the last m-tile's TMA box stays inside the allocation
+    xp = torch.empty((plan.max_rows + 128, H), dtype=x.dtype, device=x.device)
+    check(_lib.lib().pxl_moe_gather(x.data_ptr(), plan.src_tok.data_ptr(), plan.offsets[plan.n_local:].data_ptr(),
+                                    xp.data_ptr(), plan.max_rows, H, _stream(x.device)), "pxl_moe_gather")
+    _count()
+    return xp
+
+
+def grouped_linear(a: torch.Tensor, w: torch.Tensor, plan: MoEPlan, num_local_experts: int,
+                   epi: int = EPI_NONE, bn: int = 0) -> torch.Tensor:
+    """``a [P, K]`` (expert-sorted rows) times stacked expert weights ``w [E*N, K]``."""
+    P, K = a.shape
+    N = w.shape[0] // num_local_experts
+    n_out = N // 2 if epi == EPI_SILU_MUL else N
+    out = torch.empty((P, n_out), dtype=a.dtype, device=a.device)
+    check(_lib.lib().pxl_gemm_bf16_grouped(a.data_ptr(), w.data_ptr(), out.data_ptr(), P, num_local_experts, N, K,
+                                           a.stride(0), w.stride(0), out.stride(0), plan.mt_expert.data_ptr(),
+                                           plan.mt_row0.data_ptr(), plan.mt_row_end.data_ptr(),
+                                           plan.num_mt.data_ptr(), plan.max_mt, epi, bn,
+                                           status_tensor(a.device).data_ptr(), _stream(a.device)),
+          "pxl_gemm_bf16_grouped")
+    _count()
+    return out
+
+
+def moe_combine(y_perm: torch.Tensor, plan: MoEPlan, weights: torch.Tensor, base: Optional[torch.Tensor],
+                T: int) -> torch.Tensor:
+    k, H = weights.shape[1], y_perm.shape[1]
+    out = torch.empty((T, H), dtype=y_perm.dtype, device=y_perm.device)
+    check(_lib.lib().pxl_moe_combine(y_perm.data_ptr(), plan.pos_of.data_ptr(), weights.data_ptr(), _ptr(base),
+                                     out.data_ptr(), T, k, H, _stream(y_perm.device)), "pxl_moe_combine")
+    _count()
+    return out
+
+
+def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
+            num_experts: int, base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``base + sum_j weights[:, j] * FFN_{ids[:, j]}(x)`` with SwiGLU experts.
+
+    w1: ``[E * 2I, H]`` gate/up rows interleaved per expert; w2: ``[E * H, I]``."""
+    plan = moe_align(ids, num_experts)
+    xp = moe_gather(x, plan)
+    act = grouped_linear(xp, w1, plan, num_experts, epi=EPI_SILU_MUL)
+    y = grouped_linear(act, w2, plan, num_experts)
+    return moe_combine(y, plan, weights, base, x.shape[0])
+
+
 def as_c_int_p(t: torch.Tensor) -> ctypes.c_void_p:
     return ctypes.c_void_p(t.data_ptr())

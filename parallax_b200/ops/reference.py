@@ -270,5 +270,47 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, want_prob: bool = 
     return (ids, probs_out) if want_prob else ids
 
 
+def moe_route(logits, e_bias, k, mode=0, renorm=True, n_group=1, topk_group=1, routed_scale=1.0):
+    """Top-k expert selection (see csrc/moe.cu for the two modes)."""
+    lf = logits.float()
+    T, E = lf.shape
+    if mode == 0:
+        s = torch.softmax(lf, dim=-1)
+        sel = s
+    else:
+        s = torch.sigmoid(lf)
+        sel = s + (e_bias.float() if e_bias is not None else 0.0)
+        if n_group > 1 and topk_group < n_group:
+            g = sel.view(T, n_group, E // n_group)
+            gscore = g.topk(2, dim=-1).values.sum(-1)
+            keep = torch.zeros_like(gscore, dtype=torch.bool)
+            keep.scatter_(1, gscore.topk(topk_group, dim=-1).indices, True)
+            sel = g.masked_fill(~keep[:, :, None], float("-inf")).reshape(T, E)
+    ids = sel.topk(k, dim=-1).indices
+    w = s.gather(1, ids)
+    if renorm:
+        w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+    return ids.to(torch.int32), (w * routed_scale).float()
+
+
+def moe_ffn(x, ids, weights, w1, w2, num_experts, base=None):
+    """Dense restatement: loop over experts. w1 ``[E*2I, H]`` (interleaved), w2 ``[E*H, I]``."""
+    T, H = x.shape
+    two_i = w1.shape[0] // num_experts
+    w1e = w1.view(num_experts, two_i, H)
+    w2e = w2.view(num_experts, H, two_i // 2)
+    out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    for e in range(num_experts):
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        a = linear(x[tok], w1e[e], epi=EPI_SILU_MUL)
+        y = linear(a, w2e[e])
+        out.index_add_(0, tok, y.float() * weights[tok, slot][:, None])
+    if base is not None:
+        out = out + base.float()
+    return out.to(x.dtype)
+
+
 def default_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(head_dim)

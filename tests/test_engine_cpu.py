@@ -95,3 +95,41 @@ def test_cpu_plumbing_qwen3_0p6b_two_shards():
     assert len(logits[0]) == len(logits[1])
     for a, b in zip(logits[0], logits[1]):
         assert torch.allclose(a, b, atol=1e-4, rtol=1e-4)
+
+
+def test_moe_engine_matches_huggingface_qwen3_moe():
+    transformers = pytest.importorskip("transformers")
+    hf_cfg = transformers.Qwen3MoeConfig(
+        hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+        intermediate_size=256, moe_intermediate_size=64, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True,
+        vocab_size=512, rope_theta=10000.0, tie_word_embeddings=False, max_position_embeddings=512,
+        decoder_sparse_step=1, mlp_only_layers=[])
+    torch.manual_seed(0)
+    hf = transformers.Qwen3MoeForCausalLM(hf_cfg).eval().float()
+    cfg = config_from_hf(hf_cfg.to_dict() | {"architectures": ["Qwen3MoeForCausalLM"]})
+    assert cfg.is_moe and cfg.layer_is_moe(0)
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    # newer HF releases store experts fused: split them back into per-expert tensors
+    for li in range(2):
+        p = f"model.layers.{li}.mlp.experts."
+        if p + "gate_up_proj" in sd:
+            gu, dn = sd.pop(p + "gate_up_proj"), sd.pop(p + "down_proj")
+            for e in range(8):
+                g_u = gu[e] if gu[e].shape[0] == 128 else gu[e].t()
+                sd[f"{p}{e}.gate_proj.weight"], sd[f"{p}{e}.up_proj.weight"] = g_u[:64], g_u[64:]
+                sd[f"{p}{e}.down_proj.weight"] = dn[e] if dn[e].shape == (128, 64) else dn[e].t()
+    eng = Engine(cfg, device="cpu", num_blocks=64, page_size=16, max_batch_size=4, weights=sd)
+    eng.keep_logits = True
+    prompt = _prompts(1, 23, 512, seed=9)[0]
+    req = Request(input_ids=prompt, sampling_params=SamplingParams(max_new_tokens=4, temperature=0.0, ignore_eos=True))
+    eng.add_request(req)
+    eng.step()
+    with torch.no_grad():
+        want = hf(torch.tensor([prompt])).logits[0, -1]
+    assert torch.allclose(eng.last_logits[0], want, atol=3e-4, rtol=1e-3)
+
+
+def test_tiny_moe_sharded_equals_unsharded():
+    cfg = named_config("tiny-moe")
+    prompts = _prompts(3, 30, cfg.vocab_size, seed=11)
+    assert _run(cfg, prompts, max_new=5) == _run(cfg, prompts, max_new=5, stage_layers=[(0, 2), (2, 4)])
