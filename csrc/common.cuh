@@ -285,6 +285,57 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int a_fmt, int b
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// --- cross-GPU signalling (flags live in peer-mapped symmetric memory) --------------------
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Makes data written through the generic proxy visible to subsequent async-proxy (TMA) reads.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+constexpr uint64_t kPeerWaitLimitNs = 1500000000ull;  // 1.5 s
+
+// Bounded wait until a flag written by another CTA / another GPU reaches `epoch`. On expiry
+// the error is recorded, the CTA-wide abort flag (if any) is raised and false is returned.
+template <bool SYS>
+__device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t epoch,
+                                                  volatile int* abort_flag, int* status) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    const uint32_t v = SYS ? ld_acquire_sys_u32(flag) : ld_acquire_gpu_u32(flag);
+    if (static_cast<int32_t>(v - epoch) >= 0) return true;
+    if ((++spins & 0xffu) == 0) {
+      if (abort_flag && *abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kPeerWaitLimitNs) {
+        if (abort_flag) *abort_flag = 1;
+        if (status) atomicCAS(status, 0, PXL_DEV_TIMEOUT_PEER);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
 // --- legacy tensor path used by the attention kernels ------------------------
 __device__ __forceinline__ void mma_m16n8k16_bf16(float (&d)[4], const uint32_t (&a)[4],
                                                   const uint32_t (&b)[2]) {

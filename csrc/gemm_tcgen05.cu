@@ -54,13 +54,34 @@ struct GemmGroupArgs {
   int w_rows_per_expert;   // rows of W per expert (N of one expert's matrix)
 };
 
+// Fused collectives (tensor parallelism inside a pipeline stage). All pointers in the arrays
+// are peer-mapped symmetric-memory addresses, index = rank.
+//  * reduce-scatter epilogue (EPI == PXL_EPI_RS): the tile of partial sums is stored straight
+//    into the staging slot [this rank] of the rank that owns the tile's rows, then a flag is
+//    published; after its own tiles every CTA reduces owned tiles whose tp partials arrived.
+//  * all-gather prologue (ag_ncopy > 0): the last ag_ncopy CTAs pull the other ranks' row
+//    shards of A into this GPU's copy of the full matrix and publish one flag per 128-row
+//    tile; the TMA producer waits for a tile's flag before loading it.
+struct GemmCommArgs {
+  bf16* stage[8];            // RS: [tp][rows_per_rank][ldc] staging buffer of rank i
+  uint32_t* flags[8];        // RS: [tp][tiles_per_shard] arrival flags of rank i
+  const bf16* ag_src[8];     // AG: rank i's copy of the full A matrix [tp*rows_per_rank][lda]
+  uint32_t* ag_ready[8];     // AG: [tp] "shard of rank j is complete" flags of rank i
+  uint32_t* ag_tile_flags;   // AG: local [num_m_tiles] flags, set when a tile has landed
+  bf16* ag_dst;              // AG: this rank's copy of the full A matrix (written by copy CTAs)
+  bf16* out;                 // RS: local result [rows_per_rank][ldo]
+  const bf16* residual;      // RS: optional local residual shard [rows_per_rank][ldo]
+  int rank, tp, rows_per_rank, ldo, lda, ag_ncopy, first_shard;
+  uint32_t epoch;
+};
+
 struct TileCoord {
   int a_row, b_row, row_end, n_blk;
 };
 
 template <int BN>
 __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int M,
-                                                const GemmGroupArgs& g) {
+                                                const GemmGroupArgs& g, const GemmCommArgs& comm) {
   TileCoord c;
   if (g.num_mt != nullptr) {
     const int mt = tile / num_n;
@@ -69,8 +90,20 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
     c.row_end = g.mt_row_end[mt];
     c.b_row = g.mt_expert[mt] * g.w_rows_per_expert + c.n_blk * BN;
   } else {
-    const int m_blk = tile % num_m;
-    c.n_blk = tile / num_m;
+    int m_blk;
+    if (comm.tp > 1) {
+      // fused-collective order: one row shard after the other, starting at comm.first_shard,
+      // so that every rank computes (and ships / needs) a different shard at any moment
+      const int mps = comm.rows_per_rank / BM;
+      const int per_shard = mps * num_n;
+      const int within = tile % per_shard;
+      const int shard = (comm.first_shard + tile / per_shard) % comm.tp;
+      m_blk = shard * mps + within % mps;
+      c.n_blk = within / mps;
+    } else {
+      m_blk = tile % num_m;
+      c.n_blk = tile / num_m;
+    }
     c.a_row = m_blk * BM;
     c.row_end = M;
     c.b_row = c.n_blk * BN;
@@ -82,7 +115,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, GemmEpilogueArgs ep,
-                         GemmGroupArgs grp, int M, int N, int K, int* status) {
+                         GemmGroupArgs grp, const __grid_constant__ GemmCommArgs comm, int M, int N,
+                         int K, int* status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -102,6 +136,43 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+
+  const int gemm_ctas = gridDim.x - comm.ag_ncopy;
+  if (comm.ag_ncopy > 0 && static_cast<int>(blockIdx.x) >= gemm_ctas) {
+    // ---------------------------------------------------------- all-gather copy CTA
+    // Pull the shards of the other ranks (next rank first) into the local full matrix.
+    __shared__ int s_ok;
+    const int c = blockIdx.x - gemm_ctas;
+    if (c == 0 && threadIdx.x < comm.tp) {
+      // this rank's shard is complete (the launch is ordered after its producer): tell everyone
+      __threadfence_system();
+      st_release_sys_u32(comm.ag_ready[threadIdx.x] + comm.rank, comm.epoch);
+    }
+    const int tiles_per_shard = comm.rows_per_rank / BM;
+    const int vec_per_row = K / 8;
+    for (int step = 1; step < comm.tp; ++step) {
+      const int src = (comm.rank + step) % comm.tp;
+      if (threadIdx.x == 0)
+        s_ok = flag_wait_bounded<true>(comm.ag_ready[comm.rank] + src, comm.epoch, nullptr, status) ? 1 : 0;
+      __syncthreads();
+      if (!s_ok) return;
+      for (int t = c; t < tiles_per_shard; t += comm.ag_ncopy) {
+        const int row0 = src * comm.rows_per_rank + t * BM;
+        const bf16* sp = comm.ag_src[src] + static_cast<size_t>(row0) * comm.lda;
+        bf16* dp = comm.ag_dst + static_cast<size_t>(row0) * comm.lda;
+        for (int i = threadIdx.x; i < BM * vec_per_row; i += blockDim.x) {
+          const int r = i / vec_per_row, v = i % vec_per_row;
+          st_bf16x8(dp + static_cast<size_t>(r) * comm.lda + v * 8,
+                    ld_bf16x8(sp + static_cast<size_t>(r) * comm.lda + v * 8));
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) st_release_gpu_u32(comm.ag_tile_flags + row0 / BM, comm.epoch);
+      }
+      __syncthreads();
+    }
+    return;
+  }
 
   const int num_m = grp.num_mt != nullptr ? *grp.num_mt : ceil_div(M, BM);
   const int num_n = ceil_div(N, BN);
@@ -138,8 +209,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp);
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gemm_ctas) {
+        const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
+        if (comm.ag_ncopy > 0 && tc.a_row / comm.rows_per_rank != comm.rank) {
+          // rows of another rank: wait until the copy CTAs have landed this tile locally
+          ok = flag_wait_bounded<false>(comm.ag_tile_flags + tc.a_row / BM, comm.epoch, abort_flag,
+                                        status);
+          if (!ok) break;
+          fence_proxy_async_all();
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, status,
                                  PXL_DEV_TIMEOUT_EMPTY);
@@ -165,7 +243,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gemm_ctas) {
         ok = mbar_wait_bounded(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status,
                                PXL_DEV_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
@@ -202,8 +280,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp);
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gemm_ctas) {
+      const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
       const int n_blk = tc.n_blk;
       const int M_end = tc.row_end;
       ok = mbar_wait_bounded(tfull0 + 8 * acc, acc_phase, abort_flag, status,
@@ -253,7 +331,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tmem_ld_32x32b_x32(t_row + c0, r);
           tmem_ld_wait();
           if (row < M_end) {
-            const size_t off = static_cast<size_t>(row) * ep.ldc + col0 + c0;
+            size_t off = static_cast<size_t>(row) * ep.ldc + col0 + c0;
+            bf16* c_base = ep.C;
+            if constexpr (EPI == PXL_EPI_RS) {
+              const int owner = row / comm.rows_per_rank;
+              const int lrow = row - owner * comm.rows_per_rank;
+              c_base = comm.stage[owner];
+              off = (static_cast<size_t>(comm.rank) * comm.rows_per_rank + lrow) * ep.ldc + col0 + c0;
+            }
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               const int col = col0 + c0 + v * 8;
@@ -287,7 +372,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   bf16x8 o;
 #pragma unroll
                   for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
-                  st_bf16x8(ep.C + off + v * 8, o);
+                  st_bf16x8(c_base + off + v * 8, o);
                 }
               }
             }
@@ -297,8 +382,69 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      if constexpr (EPI == PXL_EPI_RS) {
+        // all 128 epilogue threads have stored their rows of the tile: publish it to the owner
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        if (threadIdx.x == 64) {
+          const int owner = tc.a_row / comm.rows_per_rank;
+          const int t_in_shard = ((tc.a_row - owner * comm.rows_per_rank) / BM) * num_n + n_blk;
+          st_release_sys_u32(comm.flags[owner] + comm.rank * (comm.rows_per_rank / BM) * num_n + t_in_shard,
+                             comm.epoch);
+        }
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  if constexpr (EPI == PXL_EPI_RS) {
+    if (warp >= 2) {
+      // ---------------------------------------------- reduce the tiles this rank owns
+      const int q = warp & 3;
+      const int tiles_per_shard = (comm.rows_per_rank / BM) * num_n;
+      const bf16* my_stage = comm.stage[comm.rank];
+      const uint32_t* my_flags = comm.flags[comm.rank];
+      bool ok = !*abort_flag;
+      for (int ot = blockIdx.x; ok && ot < tiles_per_shard; ot += gemm_ctas) {
+        for (int src = 0; src < comm.tp && ok; ++src)
+          ok = flag_wait_bounded<true>(my_flags + src * tiles_per_shard + ot, comm.epoch, abort_flag, status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int lrow = (ot / num_n) * BM + q * 32 + lane;
+        const int col0 = (ot % num_n) * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 8) {
+          const int col = col0 + c0;
+          if (col >= N) break;
+          float f[8];
+          if (comm.residual) {
+            const bf16x8 r8 = ld_bf16x8(comm.residual + static_cast<size_t>(lrow) * comm.ldo + col);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t2 = unpack_bf16x2(r8.u[j]);
+              f[2 * j] = t2.x;
+              f[2 * j + 1] = t2.y;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = 0.f;
+          }
+          for (int src = 0; src < comm.tp; ++src) {
+            const bf16x8 p8 = ld_bf16x8(my_stage + (static_cast<size_t>(src) * comm.rows_per_rank + lrow) * ep.ldc + col);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t2 = unpack_bf16x2(p8.u[j]);
+              f[2 * j] += t2.x;
+              f[2 * j + 1] += t2.y;
+            }
+          }
+          bf16x8 o;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+          st_bf16x8(comm.out + static_cast<size_t>(lrow) * comm.ldo + col, o);
+        }
+      }
     }
   }
 
@@ -316,8 +462,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 template <int BN, int EPI>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogueArgs& ep,
-                const GemmGroupArgs& grp, int max_tiles, int M, int N, int K, int* status,
-                cudaStream_t stream) {
+                const GemmGroupArgs& grp, const GemmCommArgs& comm, int max_tiles, int M, int N,
+                int K, int* status, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI>;
   static bool configured[64] = {false};
@@ -330,22 +476,28 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue
     configured[dev] = true;
   }
   const int tiles = max_tiles > 0 ? max_tiles : pxl::ceil_div(M, BM) * pxl::ceil_div(N, BN);
-  const int grid = tiles < pxl_host::num_sms() ? tiles : pxl_host::num_sms();
-  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, ep, grp, M, N, K, status);
+  int grid = tiles < pxl_host::num_sms() ? tiles : pxl_host::num_sms();
+  if (comm.ag_ncopy > 0) {
+    // copy CTAs ride along: keep the whole grid co-resident (one CTA per SM)
+    grid = grid + comm.ag_ncopy <= pxl_host::num_sms() ? grid + comm.ag_ncopy : pxl_host::num_sms();
+    if (grid <= comm.ag_ncopy) return PXL_ERR_INVALID_ARG;
+  }
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, ep, grp, comm, M, N, K, status);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
 }
 
 template <int BN>
 int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogueArgs& ep,
-                 const GemmGroupArgs& grp, int max_tiles, int M, int N, int K, int* status,
-                 cudaStream_t stream) {
+                 const GemmGroupArgs& grp, const GemmCommArgs& comm, int max_tiles, int M, int N,
+                 int K, int* status, cudaStream_t stream) {
 #define PXL_GEMM_CASE(E) \
-  case E: return launch_gemm<BN, E>(ta, tb, ep, grp, max_tiles, M, N, K, status, stream)
+  case E: return launch_gemm<BN, E>(ta, tb, ep, grp, comm, max_tiles, M, N, K, status, stream)
   switch (epi) {
     PXL_GEMM_CASE(PXL_EPI_NONE);
     PXL_GEMM_CASE(PXL_EPI_RESIDUAL);
     PXL_GEMM_CASE(PXL_EPI_SILU_MUL);
     PXL_GEMM_CASE(PXL_EPI_F32);
+    PXL_GEMM_CASE(PXL_EPI_RS);
     default: return PXL_ERR_INVALID_ARG;
   }
 #undef PXL_GEMM_CASE
@@ -393,9 +545,9 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
   ep.ldc = ldc;
   GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
   switch (bn) {
-    case 256: return dispatch_epi<256>(epi, ta, tb, ep, grp, 0, M, N, K, status, stream);
-    case 128: return dispatch_epi<128>(epi, ta, tb, ep, grp, 0, M, N, K, status, stream);
-    case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, 0, M, N, K, status, stream);
+    case 256: return dispatch_epi<256>(epi, ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
+    case 128: return dispatch_epi<128>(epi, ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
+    case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
     default: return PXL_ERR_INVALID_ARG;
   }
 }
@@ -430,9 +582,113 @@ PXL_EXPORT int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int 
   GemmGroupArgs grp{mt_expert, mt_row0, mt_row_end, num_mt, N};
   const int max_tiles = max_m_tiles * pxl::ceil_div(N, bn);
   switch (bn) {
-    case 256: return dispatch_epi<256>(epi, ta, tb, ep, grp, max_tiles, P, N, K, status, stream);
-    case 128: return dispatch_epi<128>(epi, ta, tb, ep, grp, max_tiles, P, N, K, status, stream);
-    case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, max_tiles, P, N, K, status, stream);
+    case 256: return dispatch_epi<256>(epi, ta, tb, ep, grp, GemmCommArgs{}, max_tiles, P, N, K, status, stream);
+    case 128: return dispatch_epi<128>(epi, ta, tb, ep, grp, GemmCommArgs{}, max_tiles, P, N, K, status, stream);
+    case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, GemmCommArgs{}, max_tiles, P, N, K, status, stream);
+    default: return PXL_ERR_INVALID_ARG;
+  }
+}
+
+namespace {
+int check_comm_common(int tp, int rank, int rows_per_rank, int K, int N) {
+  if (tp < 2 || tp > 8 || rank < 0 || rank >= tp) return PXL_ERR_INVALID_ARG;
+  if (rows_per_rank <= 0 || rows_per_rank % BM) return PXL_ERR_INVALID_ARG;
+  if ((K % 8) || (N % 8)) return PXL_ERR_INVALID_ARG;
+  return PXL_OK;
+}
+}  // namespace
+
+// Fused GEMM -> reduce-scatter over tensor-parallel ranks.
+//   A [tp*rows_per_rank, K] (this rank's K-slice of the activations), W [N, K];
+//   out[rows_per_rank, N] = sum over ranks of (A_r W_r^T)[rows owned by this rank] (+ residual).
+// stage_ptrs[i] / flag_ptrs[i]: rank i's staging buffer [tp][rows_per_rank][N] bf16 and flag
+// array [tp][tiles] uint32 in peer-mapped symmetric memory (flags zero-initialised once;
+// `epoch` must grow by one on every call that uses the same buffers).
+PXL_EXPORT int pxl_gemm_bf16_rs(const void* A, const void* W, void* out, const void* residual,
+                                void* const* stage_ptrs, void* const* flag_ptrs, int rank, int tp,
+                                int rows_per_rank, int N, int K, int lda, int ldw, int ldo,
+                                uint32_t epoch, int bn, int* status, cudaStream_t stream) {
+  int rc = check_comm_common(tp, rank, rows_per_rank, K, N);
+  if (rc) return rc;
+  if ((lda % 8) || (ldw % 8) || (ldo % 8)) return PXL_ERR_INVALID_ARG;
+  const int M = tp * rows_per_rank;
+  if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  if (N % bn) return PXL_ERR_INVALID_ARG;
+  CUtensorMap ta, tb;
+  if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, lda, BM, BK))
+    return PXL_ERR_TENSORMAP;
+  if (!pxl_host::make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, ldw, bn, BK))
+    return PXL_ERR_TENSORMAP;
+  GemmEpilogueArgs ep{};
+  ep.ldc = N;
+  GemmCommArgs comm{};
+  for (int i = 0; i < tp; ++i) {
+    comm.stage[i] = static_cast<pxl::bf16*>(stage_ptrs[i]);
+    comm.flags[i] = static_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  comm.out = static_cast<pxl::bf16*>(out);
+  comm.residual = static_cast<const pxl::bf16*>(residual);
+  comm.rank = rank;
+  comm.tp = tp;
+  comm.rows_per_rank = rows_per_rank;
+  comm.ldo = ldo;
+  comm.first_shard = (rank + 1) % tp;  // own rows last: the partials of the peers arrive meanwhile
+  comm.epoch = epoch;
+  GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
+  switch (bn) {
+    case 256: return dispatch_epi<256>(PXL_EPI_RS, ta, tb, ep, grp, comm, 0, M, N, K, status, stream);
+    case 128: return dispatch_epi<128>(PXL_EPI_RS, ta, tb, ep, grp, comm, 0, M, N, K, status, stream);
+    default: return PXL_ERR_INVALID_ARG;
+  }
+}
+
+// Fused all-gather -> GEMM. Every rank holds the full-size matrix X [tp*rows_per_rank, K] in
+// symmetric memory but only its own row shard is valid on entry; copy CTAs pull the other
+// shards over NVLink while the tensor cores already work on the local shard.
+//   C[tp*rows_per_rank, N] = X_full W^T  with the usual epilogues (bias / SiLU-mul).
+// x_ptrs[i]: rank i's X; ready_ptrs[i]: rank i's [tp] shard-ready flags (symmetric memory);
+// tile_flags: local [tp*rows_per_rank/128] flags. Flags zero-initialised once; epoch grows.
+PXL_EXPORT int pxl_gemm_bf16_ag(void* const* x_ptrs, void* const* ready_ptrs, void* tile_flags,
+                                const void* W, void* C, const void* bias, int rank, int tp,
+                                int rows_per_rank, int N, int K, int lda, int ldw, int ldc, int epi,
+                                uint32_t epoch, int ncopy, int bn, int* status, cudaStream_t stream) {
+  int rc = check_comm_common(tp, rank, rows_per_rank, K, N);
+  if (rc) return rc;
+  if (epi != PXL_EPI_NONE && epi != PXL_EPI_SILU_MUL && epi != PXL_EPI_F32) return PXL_ERR_INVALID_ARG;
+  if ((lda % 8) || (ldw % 8) || (ldc % 8)) return PXL_ERR_INVALID_ARG;
+  const int M = tp * rows_per_rank;
+  if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;
+  if (ncopy <= 0) ncopy = 16;
+  CUtensorMap ta, tb;
+  if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x_ptrs[rank], M, K, lda, BM, BK))
+    return PXL_ERR_TENSORMAP;
+  if (!pxl_host::make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, ldw, bn, BK))
+    return PXL_ERR_TENSORMAP;
+  GemmEpilogueArgs ep{};
+  ep.C = static_cast<pxl::bf16*>(C);
+  ep.C_f32 = static_cast<float*>(C);
+  ep.bias = static_cast<const pxl::bf16*>(bias);
+  ep.ldc = ldc;
+  GemmCommArgs comm{};
+  for (int i = 0; i < tp; ++i) {
+    comm.ag_src[i] = static_cast<const pxl::bf16*>(x_ptrs[i]);
+    comm.ag_ready[i] = static_cast<uint32_t*>(ready_ptrs[i]);
+  }
+  comm.ag_dst = static_cast<pxl::bf16*>(x_ptrs[rank]);
+  comm.ag_tile_flags = static_cast<uint32_t*>(tile_flags);
+  comm.rank = rank;
+  comm.tp = tp;
+  comm.rows_per_rank = rows_per_rank;
+  comm.lda = lda;
+  comm.ag_ncopy = ncopy;
+  comm.first_shard = rank;  // local rows first
+  comm.epoch = epoch;
+  GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
+  switch (bn) {
+    case 256: return dispatch_epi<256>(epi, ta, tb, ep, grp, comm, 0, M, N, K, status, stream);
+    case 128: return dispatch_epi<128>(epi, ta, tb, ep, grp, comm, 0, M, N, K, status, stream);
+    case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, comm, 0, M, N, K, status, stream);
     default: return PXL_ERR_INVALID_ARG;
   }
 }

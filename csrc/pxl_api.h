@@ -22,6 +22,7 @@ typedef struct CUstream_st* pxl_stream_t;
 #define PXL_EPI_RESIDUAL 1  // C = A W^T (+bias) + residual           bf16 out
 #define PXL_EPI_SILU_MUL 2  // C[:, j] = silu(gate_j) * up_j          bf16 out, N/2 columns
 #define PXL_EPI_F32 3       // C = A W^T (+bias)                      fp32 out
+#define PXL_EPI_RS 4        // partial sums scattered to the owning rank + reduce (pxl_gemm_bf16_rs)
 
 // ---- gemm_tcgen05.cu -------------------------------------------------------
 // C[M,N] = A[M,K] * W[N,K]^T. lda/ldw/ldc in elements. `bn` = tile width (64/128/256)
@@ -115,6 +116,16 @@ int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int P, int E, i
                           int lda, int ldw, int ldc, const int* mt_expert, const int* mt_row0,
                           const int* mt_row_end, const int* num_mt, int max_m_tiles, int epi,
                           int bn, int* status, pxl_stream_t stream);
+
+// Fused tensor-parallel collectives (see gemm_tcgen05.cu for the buffer contracts).
+int pxl_gemm_bf16_rs(const void* A, const void* W, void* out, const void* residual,
+                     void* const* stage_ptrs, void* const* flag_ptrs, int rank, int tp,
+                     int rows_per_rank, int N, int K, int lda, int ldw, int ldo, uint32_t epoch,
+                     int bn, int* status, pxl_stream_t stream);
+int pxl_gemm_bf16_ag(void* const* x_ptrs, void* const* ready_ptrs, void* tile_flags, const void* W,
+                     void* C, const void* bias, int rank, int tp, int rows_per_rank, int N, int K,
+                     int lda, int ldw, int ldc, int epi, uint32_t epoch, int ncopy, int bn,
+                     int* status, pxl_stream_t stream);
 
 #ifdef __cplusplus
 }
