@@ -160,10 +160,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int row0 = src * comm.rows_per_rank + t * BM;
         const bf16* sp = comm.ag_src[src] + static_cast<size_t>(row0) * comm.lda;
         bf16* dp = comm.ag_dst + static_cast<size_t>(row0) * comm.lda;
-        for (int i = threadIdx.x; i < BM * vec_per_row; i += blockDim.x) {
-          const int r = i / vec_per_row, v = i % vec_per_row;
-          st_bf16x8(dp + static_cast<size_t>(r) * comm.lda + v * 8,
-                    ld_bf16x8(sp + static_cast<size_t>(r) * comm.lda + v * 8));
+        // 8 independent 16-byte peer loads in flight per thread hide the NVLink round trip
+        const int total = BM * vec_per_row;
+        for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * 8) {
+          bf16x8 buf[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i < total) {
+              const int r = i / vec_per_row, v = i % vec_per_row;
+              buf[u] = ld_bf16x8(sp + static_cast<size_t>(r) * comm.lda + v * 8);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i < total) {
+              const int r = i / vec_per_row, v = i % vec_per_row;
+              st_bf16x8(dp + static_cast<size_t>(r) * comm.lda + v * 8, buf[u]);
+            }
+          }
         }
         __threadfence();
         __syncthreads();
@@ -411,38 +427,44 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           ok = flag_wait_bounded<true>(my_flags + src * tiles_per_shard + ot, comm.epoch, abort_flag, status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const int lrow = (ot / num_n) * BM + q * 32 + lane;
+        // one warp per row at a time: 32 lanes x 16 bytes cover 256 columns, fully coalesced
         const int col0 = (ot % num_n) * BN;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 8) {
-          const int col = col0 + c0;
-          if (col >= N) break;
-          float f[8];
-          if (comm.residual) {
-            const bf16x8 r8 = ld_bf16x8(comm.residual + static_cast<size_t>(lrow) * comm.ldo + col);
+        constexpr int CHUNKS = BN / 256 > 0 ? BN / 256 : 1;
+        constexpr int LANES_USED = BN >= 256 ? 32 : BN / 8;
+#pragma unroll 2
+        for (int rr = 0; rr < 32; ++rr) {
+          const int lrow = (ot / num_n) * BM + q * 32 + rr;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 t2 = unpack_bf16x2(r8.u[j]);
-              f[2 * j] = t2.x;
-              f[2 * j + 1] = t2.y;
+          for (int ch = 0; ch < CHUNKS; ++ch) {
+            const int col = col0 + ch * 256 + lane * 8;
+            if (lane >= LANES_USED || col >= N) continue;
+            float f[8];
+            if (comm.residual) {
+              const bf16x8 r8 = ld_bf16x8(comm.residual + static_cast<size_t>(lrow) * comm.ldo + col);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 t2 = unpack_bf16x2(r8.u[j]);
+                f[2 * j] = t2.x;
+                f[2 * j + 1] = t2.y;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = 0.f;
             }
-          } else {
+            for (int src = 0; src < comm.tp; ++src) {
+              const bf16x8 p8 = ld_bf16x8(my_stage + (static_cast<size_t>(src) * comm.rows_per_rank + lrow) * ep.ldc + col);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = 0.f;
-          }
-          for (int src = 0; src < comm.tp; ++src) {
-            const bf16x8 p8 = ld_bf16x8(my_stage + (static_cast<size_t>(src) * comm.rows_per_rank + lrow) * ep.ldc + col);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 t2 = unpack_bf16x2(p8.u[j]);
-              f[2 * j] += t2.x;
-              f[2 * j + 1] += t2.y;
+              for (int j = 0; j < 4; ++j) {
+                const float2 t2 = unpack_bf16x2(p8.u[j]);
+                f[2 * j] += t2.x;
+                f[2 * j + 1] += t2.y;
+              }
             }
-          }
-          bf16x8 o;
+            bf16x8 o;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
-          st_bf16x8(comm.out + static_cast<size_t>(lrow) * comm.ldo + col, o);
+            for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+            st_bf16x8(comm.out + static_cast<size_t>(lrow) * comm.ldo + col, o);
+          }
         }
       }
     }
@@ -659,7 +681,7 @@ PXL_EXPORT int pxl_gemm_bf16_ag(void* const* x_ptrs, void* const* ready_ptrs, vo
   const int M = tp * rows_per_rank;
   if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
   if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;
-  if (ncopy <= 0) ncopy = 16;
+  if (ncopy <= 0) ncopy = 24;
   CUtensorMap ta, tb;
   if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x_ptrs[rank], M, K, lda, BM, BK))
     return PXL_ERR_TENSORMAP;

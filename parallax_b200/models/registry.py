@@ -49,14 +49,14 @@ def family_of(arch: str) -> str:
 
 
 def build_stage(cfg: ModelConfig, start_layer: int, end_layer: int, device, dtype, max_positions=None,
-                tp_rank: int = 0, tp_size: int = 1, tp_group=None):
+                tp_rank: int = 0, tp_size: int = 1, tp_group=None, comm=None):
     fam = family_of(cfg.architecture)
     if fam == "decoder":
         if tp_size > 1:
             from parallax_b200.models.decoder_tp import TPDecoderStage
 
             return TPDecoderStage(cfg, start_layer, end_layer, device, dtype, max_positions=max_positions,
-                                  tp_rank=tp_rank, tp_size=tp_size, tp_group=tp_group)
+                                  tp_rank=tp_rank, tp_size=tp_size, tp_group=tp_group, comm=comm)
         from parallax_b200.models.decoder import DecoderStage
 
         return DecoderStage(cfg, start_layer, end_layer, device, dtype, max_positions=max_positions)

@@ -1,0 +1,345 @@
+"""Multi-GPU engine inside one box: pipeline stages x tensor-parallel ranks, one process per GPU.
+
+Rank layout: ``rank = pp_rank * tp + tp_rank``. Rank 0 owns the scheduler and the logical KV
+plan; every step it broadcasts the packed step inputs (a few hundred KB of indices) to all
+ranks over a CPU control group, so that every rank can enqueue its kernels without waiting on
+a device-to-host copy. Activations move stage to stage with NCCL point-to-point on NVLink -
+each tensor-parallel rank sends its own row shard to its counterpart in the next stage - and
+only the sampled token ids travel back to rank 0, on a separate communicator so that the
+return path never queues behind the forward path. Several micro-batches are kept in flight
+(``pp`` by default) to fill the pipeline: rank 0 issues plan k+1 before it reads the tokens of
+plan k.
+
+This replaces the reference's stage transport (hidden states -> safetensors bytes -> protobuf
+-> ZMQ -> libp2p RPC -> ZMQ, with a GPU<->CPU copy on every hop;
+``src/parallax/p2p/message_util.py:202-219``, ``src/parallax/p2p/server.py:628-711``) for the
+case where all stages live on one NVSwitch domain.
+"""
+
+from __future__ import annotations
+
+import logging
+import time
+from collections import deque
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from parallax_b200 import ops
+from parallax_b200.engine.batch import BatchBuilder
+from parallax_b200.engine.engine import Planner
+from parallax_b200.engine.request import Request, RequestStatus
+from parallax_b200.engine.worker import StageWorker
+from parallax_b200.models.config import ModelConfig
+from parallax_b200.parallel.tp_comm import CollectiveTPComm, FusedTPComm
+
+logger = logging.getLogger(__name__)
+
+
+def split_layers(num_layers: int, pp: int) -> list[tuple[int, int]]:
+    """Even contiguous split (what water-filling yields for identical GPUs); earlier stages get
+    the remainder layers because the last stage also runs the lm_head."""
+    base, rem = divmod(num_layers, pp)
+    out, s = [], 0
+    for i in range(pp):
+        n = base + (1 if i < rem else 0)
+        out.append((s, s + n))
+        s += n
+    return out
+
+
+@dataclass
+class Topology:
+    world: int
+    rank: int
+    pp: int
+    tp: int
+
+    @property
+    def pp_rank(self) -> int:
+        return self.rank // self.tp
+
+    @property
+    def tp_rank(self) -> int:
+        return self.rank % self.tp
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.pp_rank == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.pp_rank == self.pp - 1
+
+    @property
+    def last_stage_root(self) -> int:
+        return (self.pp - 1) * self.tp
+
+
+class DistEngine:
+    def __init__(self, cfg: ModelConfig, pp: int, tp: int, device, dtype=None, page_size: int = 16,
+                 num_blocks: Optional[int] = None, kv_fraction: float = 0.85, max_batch_size: int = 8,
+                 max_num_tokens_per_batch: int = 16384, micro_batch_ratio: Optional[int] = None,
+                 chunked_prefill_size: Optional[int] = 1024, enable_prefix_cache: bool = True,
+                 max_total_length: int = 32768, request_timeout_s: Optional[float] = 600, eos_token_id=None,
+                 seed: int = 0, weights: Optional[dict] = None, fused: Optional[bool] = None,
+                 max_in_flight: Optional[int] = None, weights_prefiltered: bool = False):
+        assert dist.is_initialized(), "init the default process group first (nccl on GPUs, gloo on CPU)"
+        self.cfg = cfg
+        self.device = torch.device(device)
+        world, rank = dist.get_world_size(), dist.get_rank()
+        assert world == pp * tp, f"world size {world} != pp*tp = {pp * tp}"
+        self.topo = Topology(world, rank, pp, tp)
+        on_gpu = self.device.type == "cuda"
+        # groups (every rank creates every group, in the same order)
+        self.ctrl = dist.new_group(list(range(world)), backend="gloo")
+        self.ret = dist.new_group(list(range(world)), backend="nccl" if on_gpu else "gloo")
+        self.tp_group = None
+        for s in range(pp):
+            g = dist.new_group(list(range(s * tp, (s + 1) * tp)), backend="nccl" if on_gpu else "gloo")
+            if s == self.topo.pp_rank:
+                self.tp_group = g
+        start, end = split_layers(cfg.num_hidden_layers, pp)[self.topo.pp_rank]
+        comm = None
+        if tp > 1:
+            use_fused = on_gpu if fused is None else fused
+            if use_fused:
+                comm = FusedTPComm(self.tp_group, tp, self.topo.tp_rank, self.device, max_num_tokens_per_batch,
+                                   cfg.hidden_size, max_n=cfg.hidden_size,
+                                   max_k=max(cfg.hidden_size, cfg.intermediate_size // tp, cfg.q_size // tp))
+            else:
+                comm = CollectiveTPComm(self.tp_group, tp, self.topo.tp_rank, align=128 if on_gpu else 1)
+        if weights is not None and not weights_prefiltered:
+            from parallax_b200.loader.filter import filter_weights_for_range
+
+            weights = filter_weights_for_range(weights, start, end, cfg.num_hidden_layers, cfg.tie_word_embeddings)
+        max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
+        self.worker = StageWorker(cfg, start, end, self.device, dtype, page_size, num_blocks=num_blocks,
+                                  kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
+                                  tp_rank=self.topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm)
+        # every rank must agree on the number of KV blocks
+        nb = torch.tensor([self.worker.num_blocks], dtype=torch.int64)
+        dist.all_reduce(nb, op=dist.ReduceOp.MIN, group=self.ctrl)
+        self.num_blocks = int(nb)
+        self.max_in_flight = max_in_flight or pp
+        ratio = micro_batch_ratio or pp
+        self.planner = None
+        if rank == 0:
+            self.planner = Planner(cfg, self.num_blocks, page_size, max_batch_size, max_num_tokens_per_batch, ratio,
+                                   chunked_prefill_size, enable_prefix_cache, max_total_length, request_timeout_s,
+                                   eos_token_id)
+        max_blocks = (max_total_length + page_size - 1) // page_size + 1
+        self.builders = [BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size, max_batch_size,
+                                      max_blocks) for _ in range(self.max_in_flight + 1)]
+        self._bi = 0
+        self.in_flight: deque = deque()
+        self._pending_sends: deque = deque()
+        self._side_events: list = []
+        self._rng = np.random.default_rng(seed + 12345)
+        self.steps = 0
+        self.keep_logits = False
+        self.last_logits = None
+
+    # ------------------------------------------------------------------ rank-0 API
+    @property
+    def scheduler(self):
+        return self.planner.scheduler
+
+    @property
+    def cache(self):
+        return self.planner.cache
+
+    def add_request(self, req: Request) -> None:
+        req.sampling_params.verify()
+        req.max_total_length = min(req.max_total_length, self.planner.max_total_length)
+        self.scheduler.enque_request(req)
+
+    def abort_request(self, rid: str) -> None:
+        try:
+            self.scheduler.cancel_request(rid)
+        except ValueError:
+            pass
+
+    @property
+    def stages(self):
+        """Layer span served by the whole group (what :class:`EngineLoop` reports latency over)."""
+        class _Span:
+            start_layer, end_layer = 0, self.cfg.num_hidden_layers
+        return [_Span]
+
+    def has_work(self) -> bool:
+        return bool(self.in_flight) or self.scheduler.num_queued_requests > 0 or self.scheduler.num_running_requests > 0
+
+    # ------------------------------------------------------------------ plan broadcast
+    def _bcast(self, plan: Optional[dict]) -> dict:
+        box = [plan]
+        dist.broadcast_object_list(box, src=0, group=self.ctrl)
+        return box[0]
+
+    def _execute(self, plan: dict):
+        """Run this rank's part of one planned micro-batch. Returns the sampled-token tensor on
+        rank 0 (after the return hop) or None."""
+        topo, w = self.topo, self.worker
+        b = self.builders[self._bi]
+        self._bi = (self._bi + 1) % len(self.builders)
+        fb = b.build(plan["ids"] if topo.is_first_stage else None, plan["pos"], plan["slots"], plan["p_q"],
+                     plan["p_ctx"], plan["p_tables"], plan["d_ctx"], plan["d_tables"], plan["logit_rows"])
+        T, H = fb.num_tokens, self.cfg.hidden_size
+        hidden = None
+        if not topo.is_first_stage:
+            rows = w.model.comm.rows_per_rank(T) if topo.tp > 1 else T
+            hidden = torch.empty((rows, H), dtype=w.dtype, device=self.device)
+            dist.recv(hidden, src=topo.rank - topo.tp)
+        with torch.inference_mode():
+            out = w.run(fb, hidden)
+        tokens = None
+        if self.keep_logits and topo.is_last_stage:
+            self.last_logits = out
+        if not topo.is_last_stage:
+            self._pending_sends.append((dist.isend(out.contiguous(), dst=topo.rank + topo.tp), out))
+        elif plan["n_logits"] > 0:
+            if plan["greedy"]:
+                tokens = ops.argmax(out)
+            else:
+                dev = out.device
+                sp = plan["sampling"]
+                tokens = ops.sample(out, torch.tensor(sp["t"], dtype=torch.float32, device=dev),
+                                    torch.tensor(sp["k"], dtype=torch.int32, device=dev),
+                                    torch.tensor(sp["p"], dtype=torch.float32, device=dev),
+                                    torch.tensor(sp["mp"], dtype=torch.float32, device=dev),
+                                    torch.tensor(sp["u"], dtype=torch.float32, device=dev))
+            if topo.rank == topo.last_stage_root and topo.last_stage_root != 0:
+                self._pending_sends.append((dist.isend(tokens, dst=0, group=self.ret), tokens))
+        while len(self._pending_sends) > 2 * self.max_in_flight:
+            self._pending_sends.popleft()[0].wait()
+        if topo.rank != 0 or plan["n_logits"] == 0:
+            return None
+        if topo.last_stage_root != 0:
+            return ("recv", torch.empty(plan["n_logits"], dtype=torch.int32, device=self.device))
+        return ("have", tokens)
+
+    # ------------------------------------------------------------------ follower loop
+    def serve_forever(self) -> None:
+        """Ranks other than 0: execute broadcast plans until rank 0 says stop."""
+        assert self.topo.rank != 0
+        while True:
+            plan = self._bcast(None)
+            if plan.get("cmd") == "stop":
+                break
+            self._execute(plan)
+            self.steps += 1
+        for work, _ in self._pending_sends:
+            work.wait()
+
+    def shutdown(self) -> None:
+        if self.topo.rank == 0:
+            self._bcast({"cmd": "stop"})
+
+    # ------------------------------------------------------------------ rank-0 step
+    def _drop(self, req: Request) -> None:
+        self.scheduler.evict_request(req.request_id)
+        self.cache.free_request(req.request_id)
+        self._side_events.append((req, None))
+
+    def _issue(self) -> bool:
+        sched = self.scheduler
+        seqs = sched.form_batch()
+        for req in sched.pop_rejected():
+            self._side_events.append((req, None))
+        live = []
+        for s in seqs:
+            if s.req.abort:
+                s.req.update_status(RequestStatus.FINISHED_ABORT)
+                self._drop(s.req)
+            else:
+                live.append(s)
+        if not live:
+            return False
+        arrays = self.planner.plan_arrays(live)
+        for s in live:
+            if s.req.is_finished:      # aborted by KV exhaustion during planning
+                self._drop(s.req)
+        if arrays is None:
+            return False
+        owners = arrays["owners"]
+        sps = [s.req.sampling_params for s in owners]
+        greedy = all(sp.is_greedy for sp in sps)
+        plan = {k: arrays[k] for k in ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables",
+                                       "logit_rows")}
+        plan.update(cmd="step", n_logits=len(owners), greedy=greedy)
+        if not greedy:
+            plan["sampling"] = {"t": [0.0 if sp.is_greedy else sp.temperature for sp in sps],
+                                "k": [sp.top_k if sp.top_k > 0 else 0 for sp in sps], "p": [sp.top_p for sp in sps],
+                                "mp": [sp.min_p for sp in sps], "u": self._rng.random(len(sps)).tolist()}
+        self._bcast(plan)
+        res = self._execute(plan)
+        # prefill bookkeeping that does not depend on the sampled token: the next chunk of a long
+        # prompt may enter the pipeline right behind this one
+        for s in arrays["ordered"]:
+            if s.is_prefill:
+                s.req.num_computed_tokens = s.start + s.num_tokens
+                self.cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens)
+                if not s.produces_token:
+                    sched.enque_request(s.req)
+        self.in_flight.append((arrays, res))
+        return True
+
+    def _collect(self) -> list:
+        arrays, res = self.in_flight.popleft()
+        out = []
+        owners = arrays["owners"]
+        token_list = []
+        if owners:
+            kind, t = res
+            if kind == "recv":
+                dist.recv(t, src=self.topo.last_stage_root, group=self.ret)
+            token_list = t.tolist()
+        sched = self.scheduler
+        for s, tok in zip(owners, token_list):
+            req = s.req
+            req.commit_new_token(int(tok))
+            self.cache.update_request_tokens(req.request_id, [int(tok)])
+            if sched.check_and_update_request_status(req):
+                self.cache.free_request(req.request_id)
+            else:
+                sched.enque_request(req)
+            out.append((req, int(tok)))
+        return out
+
+    def step(self) -> list:
+        """Rank 0: issue micro-batches while the pipeline has room, then collect the oldest."""
+        assert self.topo.rank == 0
+        out = []
+        for req in self.scheduler.get_timed_out_requests():
+            req.update_status(RequestStatus.FINISHED_ABORT)
+            self.scheduler.evict_request(req.request_id)
+            self.cache.free_request(req.request_id)
+            out.append((req, None))
+        issued = False
+        while len(self.in_flight) < self.max_in_flight:
+            if not self._issue():
+                break
+            issued = True
+        if self.in_flight and (len(self.in_flight) >= self.max_in_flight or not issued):
+            out += self._collect()
+        if self._side_events:
+            out += self._side_events
+            self._side_events = []
+        self.steps += 1
+        return out
+
+    def generate(self, prompts, sampling_params, max_steps: int = 1 << 30) -> list[list[int]]:
+        from parallax_b200.engine.request import SamplingParams
+
+        reqs = [Request(input_ids=list(p), sampling_params=SamplingParams.from_dict(sampling_params.to_dict()),
+                        max_total_length=self.planner.max_total_length) for p in prompts]
+        for r in reqs:
+            self.add_request(r)
+        n = 0
+        while self.has_work() and n < max_steps:
+            self.step()
+            n += 1
+        return [r.output_ids for r in reqs]

@@ -70,7 +70,7 @@ def gemm_ag_begin(ws: TPWorkspace, rows_per_rank: int, k: int):
 
 
 def gemm_ag(ws: TPWorkspace, token, w: torch.Tensor, bias: Optional[torch.Tensor] = None, epi: int = EPI_NONE,
-            ncopy: int = 16, bn: int = 0) -> torch.Tensor:
+            ncopy: int = 0, bn: int = 0) -> torch.Tensor:
     s, epoch, Rp, K = token
     N = w.shape[0]
     M = ws.tp * Rp

@@ -1,0 +1,35 @@
+"""One rank of a CPU (gloo) DistEngine group, started by tests/test_dist_engine_cpu.py."""
+
+import json
+import os
+import sys
+
+import torch
+
+from parallax_b200.engine.request import SamplingParams
+from parallax_b200.parallel import launcher
+
+
+def main() -> None:
+    spec = json.loads(sys.argv[1])
+    out_path = sys.argv[2]
+    torch.manual_seed(0)
+    torch.set_num_threads(2)
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    launcher.init_process_group(rank, world, int(os.environ["MASTER_PORT"]), "cpu")
+    eng = launcher.build_dist_engine(spec)
+    if rank == 0:
+        prompts = spec["prompts"]
+        outs = eng.generate(prompts, SamplingParams(max_new_tokens=spec["max_new"], temperature=0.0, ignore_eos=True))
+        eng.shutdown()
+        with open(out_path, "w") as f:
+            json.dump({"outputs": outs, "steps": eng.steps}, f)
+    else:
+        eng.serve_forever()
+    import torch.distributed as dist
+
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,65 @@
+"""DistEngine (pipeline x tensor parallel) on CPU ranks over gloo: the sharded, pipelined
+engine must generate exactly what the single-process engine generates."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from parallax_b200.engine.engine import Engine
+from parallax_b200.engine.request import SamplingParams
+from parallax_b200.models.config import named_config
+from parallax_b200.parallel.dist_engine import split_layers
+from parallax_b200.parallel.launcher import free_port
+from parallax_b200.parallel.tp_comm import padded_rows_per_rank
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HELPER = os.path.join(os.path.dirname(__file__), "helpers", "dist_engine_rank.py")
+PROMPTS = [[5, 9, 77, 3, 250, 12, 8], [100, 101, 102], list(range(20, 75)), [7] * 19, [1, 2, 3, 4, 5, 6, 7, 8, 9]]
+
+
+def _run_group(pp, tp, tmp_path, max_new=6, chunk=16):
+    spec = dict(model_name="tiny", pp=pp, tp=tp, device_type="cpu", num_blocks=256, page_size=16, max_batch_size=4,
+                max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256, prompts=PROMPTS,
+                max_new=max_new, seed=0)
+    world, port = pp * tp, free_port()
+    out = tmp_path / f"out_{pp}_{tp}.json"
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   OMP_NUM_THREADS="2", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        procs.append(subprocess.Popen([sys.executable, HELPER, json.dumps(spec), str(out)], env=env))
+    codes = []
+    for p in procs:
+        try:
+            codes.append(p.wait(timeout=240))
+        except subprocess.TimeoutExpired:
+            p.kill()
+            codes.append(-9)
+    assert codes == [0] * world, codes
+    return json.loads(out.read_text())
+
+
+def _single(max_new=6, chunk=16):
+    torch.manual_seed(0)
+    eng = Engine(named_config("tiny"), device="cpu", num_blocks=256, page_size=16, max_batch_size=4,
+                 max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256, seed=0)
+    return eng.generate(PROMPTS, SamplingParams(max_new_tokens=max_new, temperature=0.0, ignore_eos=True))
+
+
+def test_split_layers_and_padding():
+    assert split_layers(28, 4) == [(0, 7), (7, 14), (14, 21), (21, 28)]
+    assert split_layers(10, 3) == [(0, 4), (4, 7), (7, 10)]
+    assert padded_rows_per_rank(1, 2, 128) == 128
+    assert padded_rows_per_rank(300, 2, 128) == 256
+    assert padded_rows_per_rank(7, 2, 1) == 4
+
+
+@pytest.mark.parametrize("pp,tp", [(1, 2), (2, 1), (2, 2)])
+def test_dist_engine_matches_single_process(pp, tp, tmp_path):
+    want = _single()
+    got = _run_group(pp, tp, tmp_path)
+    assert got["outputs"] == want
