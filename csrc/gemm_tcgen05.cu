@@ -26,6 +26,8 @@ constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int kAgChunkRows = 8;                     // rows per all-gather copy chunk
+constexpr int kAgChunksPerTile = BM / kAgChunkRows;  // flags per 128-row tile
 
 template <int BN>
 struct GemmCfg {
@@ -34,6 +36,15 @@ struct GemmCfg {
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
 };
+
+// Reduce-scatter epilogue staging: one 128-byte line (64 bf16) per accumulator row, padded to
+// 144 bytes so that the 16-byte vector stores of a quarter-warp fall into distinct banks.
+constexpr int kRsLinePitch = 144;
+constexpr int kRsStageBytes = BM * kRsLinePitch;
+template <int BN, int EPI>
+constexpr int gemm_smem_bytes() {
+  return GemmCfg<BN>::SMEM_BYTES + (EPI == PXL_EPI_RS ? kRsStageBytes : 0);
+}
 
 struct GemmEpilogueArgs {
   bf16* C;
@@ -128,6 +139,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // reduce-scatter epilogue staging lines (allocated only for that epilogue)
+  uint8_t* rs_stage = smem_b + STAGES * Cfg::B_STAGE_BYTES + 256;
 
   const uint32_t full0 = smem_u32(bars);
   const uint32_t empty0 = smem_u32(bars + STAGES);
@@ -140,52 +153,92 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int gemm_ctas = gridDim.x - comm.ag_ncopy;
   if (comm.ag_ncopy > 0 && static_cast<int>(blockIdx.x) >= gemm_ctas) {
     // ---------------------------------------------------------- all-gather copy CTA
-    // Pull the shards of the other ranks (next rank first) into the local full matrix.
-    __shared__ int s_ok;
+    // One warp per copy CTA drives the TMA engine: chunks of kAgChunkRows rows are pulled from
+    // the peer's shard into this CTA's shared memory with untiled bulk copies (a whole chunk
+    // in flight per buffer, up to three buffers) and written to the local full matrix with
+    // bulk stores. Chunks of a shard are dealt round-robin to the copy CTAs so that all of
+    // them work on the first tiles first; one flag per chunk tells the producer what landed.
+    __shared__ uint64_t cbar[3];
+    __shared__ int c_abort;
+    if (warp != 0) return;
     const int c = blockIdx.x - gemm_ctas;
-    if (c == 0 && threadIdx.x < comm.tp) {
+    if (lane == 0) {
+      c_abort = 0;
+      for (int i = 0; i < 3; ++i) mbar_init(smem_u32(&cbar[i]), 1);
+      mbar_fence_init();
+      fence_proxy_async_smem();
+    }
+    __syncwarp();
+    if (c == 0 && lane < comm.tp) {
       // this rank's shard is complete (the launch is ordered after its producer): tell everyone
       __threadfence_system();
-      st_release_sys_u32(comm.ag_ready[threadIdx.x] + comm.rank, comm.epoch);
+      st_release_sys_u32(comm.ag_ready[lane] + comm.rank, comm.epoch);
     }
-    const int tiles_per_shard = comm.rows_per_rank / BM;
-    const int vec_per_row = K / 8;
-    for (int step = 1; step < comm.tp; ++step) {
+    const uint32_t row_bytes = static_cast<uint32_t>(K) * 2u;
+    const uint32_t chunk_bytes = kAgChunkRows * row_bytes;
+    int nbuf = static_cast<int>((192u * 1024u) / chunk_bytes);
+    nbuf = nbuf > 3 ? 3 : nbuf;  // the host rejects K for which not even one chunk fits
+    const int chunks_per_shard = comm.rows_per_rank / kAgChunkRows;
+    const uint32_t smem0 = smem_u32(smem);
+    int n_issue = 0, n_done = 0;  // sequence numbers: buffer = n % nbuf, parity = (n / nbuf) & 1
+    bool ok = true;
+    for (int step = 1; ok && step < comm.tp; ++step) {
       const int src = (comm.rank + step) % comm.tp;
-      if (threadIdx.x == 0)
-        s_ok = flag_wait_bounded<true>(comm.ag_ready[comm.rank] + src, comm.epoch, nullptr, status) ? 1 : 0;
-      __syncthreads();
-      if (!s_ok) return;
-      for (int t = c; t < tiles_per_shard; t += comm.ag_ncopy) {
-        const int row0 = src * comm.rows_per_rank + t * BM;
-        const bf16* sp = comm.ag_src[src] + static_cast<size_t>(row0) * comm.lda;
-        bf16* dp = comm.ag_dst + static_cast<size_t>(row0) * comm.lda;
-        // 8 independent 16-byte peer loads in flight per thread hide the NVLink round trip
-        const int total = BM * vec_per_row;
-        for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * 8) {
-          bf16x8 buf[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * blockDim.x;
-            if (i < total) {
-              const int r = i / vec_per_row, v = i % vec_per_row;
-              buf[u] = ld_bf16x8(sp + static_cast<size_t>(r) * comm.lda + v * 8);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * blockDim.x;
-            if (i < total) {
-              const int r = i / vec_per_row, v = i % vec_per_row;
-              st_bf16x8(dp + static_cast<size_t>(r) * comm.lda + v * 8, buf[u]);
-            }
-          }
-        }
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) st_release_gpu_u32(comm.ag_tile_flags + row0 / BM, comm.epoch);
+      int okf = 1;
+      if (lane == 0)
+        okf = flag_wait_bounded<true>(comm.ag_ready[comm.rank] + src, comm.epoch, nullptr, status) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
+      if (!ok) break;
+      const bf16* sbase = comm.ag_src[src] + static_cast<size_t>(src) * comm.rows_per_rank * comm.lda;
+      bf16* dbase = comm.ag_dst + static_cast<size_t>(src) * comm.rows_per_rank * comm.lda;
+      auto issue_load = [&](int chunk) {
+        const int buf = n_issue % nbuf;
+        const uint32_t bar = smem_u32(&cbar[buf]);
+        if (lane == 0) mbar_arrive_expect_tx(bar, chunk_bytes);
+        __syncwarp();
+        if (lane < kAgChunkRows)
+          bulk_load_g2s(smem0 + buf * chunk_bytes + lane * row_bytes,
+                        sbase + static_cast<size_t>(chunk * kAgChunkRows + lane) * comm.lda, row_bytes, bar);
+        ++n_issue;
+      };
+      int next = c, cur = c;
+      while (n_issue - n_done < nbuf && next < chunks_per_shard) {
+        issue_load(next);
+        next += comm.ag_ncopy;
       }
-      __syncthreads();
+      while (cur < chunks_per_shard) {
+        const int buf = n_done % nbuf;
+        if (lane == 0)
+          okf = mbar_wait_bounded(smem_u32(&cbar[buf]), (n_done / nbuf) & 1, &c_abort, status,
+                                  PXL_DEV_TIMEOUT_FULL) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
+        if (!ok) break;
+        if (lane < kAgChunkRows) {
+          bulk_store_s2g(dbase + static_cast<size_t>(cur * kAgChunkRows + lane) * comm.lda,
+                         smem0 + buf * chunk_bytes + lane * row_bytes, row_bytes);
+          bulk_commit();
+          bulk_wait_read_all();
+        }
+        __syncwarp();
+        ++n_done;
+        if (next < chunks_per_shard) {  // refill the buffer that was just drained
+          issue_load(next);
+          next += comm.ag_ncopy;
+        }
+        if (lane < kAgChunkRows) bulk_wait_all();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          const int row0 = src * comm.rows_per_rank + cur * kAgChunkRows;
+          st_release_gpu_u32(comm.ag_tile_flags + (row0 / BM) * kAgChunksPerTile + (row0 % BM) / kAgChunkRows,
+                             comm.epoch);
+        }
+        cur += comm.ag_ncopy;
+      }
+    }
+    if (!ok) {
+      // loads that are still in flight must land before this CTA's shared memory is released
+      for (int i = 0; i < 64; ++i) __nanosleep(20000);
     }
     return;
   }
@@ -229,8 +282,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
         if (comm.ag_ncopy > 0 && tc.a_row / comm.rows_per_rank != comm.rank) {
           // rows of another rank: wait until the copy CTAs have landed this tile locally
-          ok = flag_wait_bounded<false>(comm.ag_tile_flags + tc.a_row / BM, comm.epoch, abort_flag,
-                                        status);
+          const uint32_t* tf = comm.ag_tile_flags + (tc.a_row / BM) * kAgChunksPerTile;
+          for (int ch = 0; ok && ch < kAgChunksPerTile; ++ch)
+            ok = flag_wait_bounded<false>(tf + ch, comm.epoch, abort_flag, status);
           if (!ok) break;
           fence_proxy_async_all();
         }
@@ -339,6 +393,42 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
         }
+      } else if constexpr (EPI == PXL_EPI_RS) {
+        // Partial sums go to the staging slot [this rank] of the rank that owns the rows. Each
+        // lane packs 64 columns of its row into its private 128-byte line of shared memory and
+        // ships the line with one bulk store: NVLink sees 128-byte writes instead of 16-byte ones.
+        const int col0 = n_blk * BN;
+        const int owner = row / comm.rows_per_rank;
+        const int lrow = row - owner * comm.rows_per_rank;
+        bf16* dst_row = comm.stage[owner] +
+                        (static_cast<size_t>(comm.rank) * comm.rows_per_rank + lrow) * ep.ldc + col0;
+        const uint32_t line = smem_u32(rs_stage) + (q * 32 + lane) * kRsLinePitch;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(t_row + c0, r0);
+          tmem_ld_32x32b_x32(t_row + c0 + 32, r1);
+          bulk_wait_read_all();  // the previous bulk store has read this lane's line
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(line + v * 16),
+                         "r"(pack_bf16x2(__uint_as_float(r0[v * 8 + 0]), __uint_as_float(r0[v * 8 + 1]))),
+                         "r"(pack_bf16x2(__uint_as_float(r0[v * 8 + 2]), __uint_as_float(r0[v * 8 + 3]))),
+                         "r"(pack_bf16x2(__uint_as_float(r0[v * 8 + 4]), __uint_as_float(r0[v * 8 + 5]))),
+                         "r"(pack_bf16x2(__uint_as_float(r0[v * 8 + 6]), __uint_as_float(r0[v * 8 + 7])))
+                         : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(line + 64 + v * 16),
+                         "r"(pack_bf16x2(__uint_as_float(r1[v * 8 + 0]), __uint_as_float(r1[v * 8 + 1]))),
+                         "r"(pack_bf16x2(__uint_as_float(r1[v * 8 + 2]), __uint_as_float(r1[v * 8 + 3]))),
+                         "r"(pack_bf16x2(__uint_as_float(r1[v * 8 + 4]), __uint_as_float(r1[v * 8 + 5]))),
+                         "r"(pack_bf16x2(__uint_as_float(r1[v * 8 + 6]), __uint_as_float(r1[v * 8 + 7])))
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          if (row < M_end && col0 + c0 < N) bulk_store_s2g(dst_row + c0, line, 128);
+          bulk_commit();
+        }
       } else {
         const int col0 = n_blk * BN;
 #pragma unroll 1
@@ -349,12 +439,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (row < M_end) {
             size_t off = static_cast<size_t>(row) * ep.ldc + col0 + c0;
             bf16* c_base = ep.C;
-            if constexpr (EPI == PXL_EPI_RS) {
-              const int owner = row / comm.rows_per_rank;
-              const int lrow = row - owner * comm.rows_per_rank;
-              c_base = comm.stage[owner];
-              off = (static_cast<size_t>(comm.rank) * comm.rows_per_rank + lrow) * ep.ldc + col0 + c0;
-            }
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               const int col = col0 + c0 + v * 8;
@@ -400,6 +484,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
       if constexpr (EPI == PXL_EPI_RS) {
         // all 128 epilogue threads have stored their rows of the tile: publish it to the owner
+        bulk_wait_all();
         __threadfence_system();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
@@ -416,54 +501,67 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if constexpr (EPI == PXL_EPI_RS) {
     if (warp >= 2) {
-      // ---------------------------------------------- reduce the tiles this rank owns
+      // ---------------------------------------------- reduce the rows this rank owns
+      // Work item = one 32-row quarter of an owned tile, dealt round-robin over all CTAs; each of
+      // the four warps sums 8 rows, every row's loads (residual + tp partials) issued up front.
       const int q = warp & 3;
       const int tiles_per_shard = (comm.rows_per_rank / BM) * num_n;
       const bf16* my_stage = comm.stage[comm.rank];
       const uint32_t* my_flags = comm.flags[comm.rank];
+      constexpr int LPR = BN / 8;        // lanes per row (16 bytes each)
+      constexpr int RPP = 32 / LPR;      // rows per pass of the warp
+      constexpr int PASSES = 8 / RPP;
       bool ok = !*abort_flag;
-      for (int ot = blockIdx.x; ok && ot < tiles_per_shard; ot += gemm_ctas) {
-        for (int src = 0; src < comm.tp && ok; ++src)
-          ok = flag_wait_bounded<true>(my_flags + src * tiles_per_shard + ot, comm.epoch, abort_flag, status);
-        ok = __all_sync(0xffffffffu, ok);
+      for (int item = blockIdx.x; ok && item < tiles_per_shard * 4; item += gemm_ctas) {
+        const int ot = item >> 2, quarter = item & 3;
+        int okf = 1;
+        if (lane == 0) {
+          for (int src = 0; src < comm.tp && okf; ++src)
+            okf = flag_wait_bounded<true>(my_flags + src * tiles_per_shard + ot, comm.epoch, abort_flag, status) ? 1 : 0;
+        }
+        ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
         if (!ok) break;
-        // one warp per row at a time: 32 lanes x 16 bytes cover 256 columns, fully coalesced
-        const int col0 = (ot % num_n) * BN;
-        constexpr int CHUNKS = BN / 256 > 0 ? BN / 256 : 1;
-        constexpr int LANES_USED = BN >= 256 ? 32 : BN / 8;
-#pragma unroll 2
-        for (int rr = 0; rr < 32; ++rr) {
-          const int lrow = (ot / num_n) * BM + q * 32 + rr;
+        const int col = (ot % num_n) * BN + (lane % LPR) * 8;
+        const int row_base = (ot / num_n) * BM + quarter * 32 + q * 8 + lane / LPR;
+        if (col < N) {
+          float f[PASSES][8];
 #pragma unroll
-          for (int ch = 0; ch < CHUNKS; ++ch) {
-            const int col = col0 + ch * 256 + lane * 8;
-            if (lane >= LANES_USED || col >= N) continue;
-            float f[8];
+          for (int p = 0; p < PASSES; ++p) {
             if (comm.residual) {
-              const bf16x8 r8 = ld_bf16x8(comm.residual + static_cast<size_t>(lrow) * comm.ldo + col);
+              const bf16x8 r8 = ld_bf16x8(comm.residual + static_cast<size_t>(row_base + p * RPP) * comm.ldo + col);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const float2 t2 = unpack_bf16x2(r8.u[j]);
-                f[2 * j] = t2.x;
-                f[2 * j + 1] = t2.y;
+                f[p][2 * j] = t2.x;
+                f[p][2 * j + 1] = t2.y;
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = 0.f;
+              for (int j = 0; j < 8; ++j) f[p][j] = 0.f;
             }
-            for (int src = 0; src < comm.tp; ++src) {
-              const bf16x8 p8 = ld_bf16x8(my_stage + (static_cast<size_t>(src) * comm.rows_per_rank + lrow) * ep.ldc + col);
+          }
+#pragma unroll 1
+          for (int src = 0; src < comm.tp; ++src) {
+            bf16x8 part[PASSES];
+#pragma unroll
+            for (int p = 0; p < PASSES; ++p)
+              part[p] = ld_bf16x8(my_stage + (static_cast<size_t>(src) * comm.rows_per_rank + row_base + p * RPP) * ep.ldc + col);
+#pragma unroll
+            for (int p = 0; p < PASSES; ++p) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const float2 t2 = unpack_bf16x2(p8.u[j]);
-                f[2 * j] += t2.x;
-                f[2 * j + 1] += t2.y;
+                const float2 t2 = unpack_bf16x2(part[p].u[j]);
+                f[p][2 * j] += t2.x;
+                f[p][2 * j + 1] += t2.y;
               }
             }
+          }
+#pragma unroll
+          for (int p = 0; p < PASSES; ++p) {
             bf16x8 o;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
-            st_bf16x8(comm.out + static_cast<size_t>(lrow) * comm.ldo + col, o);
+            for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[p][2 * j], f[p][2 * j + 1]);
+            st_bf16x8(comm.out + static_cast<size_t>(row_base + p * RPP) * comm.ldo + col, o);
           }
         }
       }
@@ -492,7 +590,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) !=
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem_bytes<BN, EPI>()) !=
         cudaSuccess)
       return PXL_ERR_CUDA;
     configured[dev] = true;
@@ -504,7 +602,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue
     grid = grid + comm.ag_ncopy <= pxl_host::num_sms() ? grid + comm.ag_ncopy : pxl_host::num_sms();
     if (grid <= comm.ag_ncopy) return PXL_ERR_INVALID_ARG;
   }
-  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, ep, grp, comm, M, N, K, status);
+  kern<<<grid, kGemmThreads, gemm_smem_bytes<BN, EPI>(), stream>>>(ta, tb, ep, grp, comm, M, N, K, status);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
 }
 
@@ -634,7 +732,8 @@ PXL_EXPORT int pxl_gemm_bf16_rs(const void* A, const void* W, void* out, const v
   if (rc) return rc;
   if ((lda % 8) || (ldw % 8) || (ldo % 8)) return PXL_ERR_INVALID_ARG;
   const int M = tp * rows_per_rank;
-  if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  // wide tiles only when they still give every SM a tile
+  if (bn == 0) bn = (N % 256 == 0 && (M / BM) * (N / 256) >= pxl_host::num_sms()) ? 256 : 128;
   if (N % bn) return PXL_ERR_INVALID_ARG;
   CUtensorMap ta, tb;
   if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, lda, BM, BK))
@@ -669,7 +768,8 @@ PXL_EXPORT int pxl_gemm_bf16_rs(const void* A, const void* W, void* out, const v
 // shards over NVLink while the tensor cores already work on the local shard.
 //   C[tp*rows_per_rank, N] = X_full W^T  with the usual epilogues (bias / SiLU-mul).
 // x_ptrs[i]: rank i's X; ready_ptrs[i]: rank i's [tp] shard-ready flags (symmetric memory);
-// tile_flags: local [tp*rows_per_rank/128] flags. Flags zero-initialised once; epoch grows.
+// tile_flags: local [tp*rows_per_rank/128][16] flags (one per 8-row chunk). Flags zero-initialised
+// once; epoch grows.
 PXL_EXPORT int pxl_gemm_bf16_ag(void* const* x_ptrs, void* const* ready_ptrs, void* tile_flags,
                                 const void* W, void* C, const void* bias, int rank, int tp,
                                 int rows_per_rank, int N, int K, int lda, int ldw, int ldc, int epi,
@@ -679,9 +779,13 @@ PXL_EXPORT int pxl_gemm_bf16_ag(void* const* x_ptrs, void* const* ready_ptrs, vo
   if (epi != PXL_EPI_NONE && epi != PXL_EPI_SILU_MUL && epi != PXL_EPI_F32) return PXL_ERR_INVALID_ARG;
   if ((lda % 8) || (ldw % 8) || (ldc % 8)) return PXL_ERR_INVALID_ARG;
   const int M = tp * rows_per_rank;
-  if (bn == 0) bn = (N % 256 == 0) ? 256 : 128;
+  if (ncopy <= 0) ncopy = 32;
+  if (ncopy >= pxl_host::num_sms()) return PXL_ERR_INVALID_ARG;
+  // a chunk of kAgChunkRows rows must fit into the copy CTA's shared memory
+  if (static_cast<long long>(kAgChunkRows) * K * 2 > 192 * 1024 || (lda % 8)) return PXL_ERR_INVALID_ARG;
+  if (bn == 0)
+    bn = (N % 256 == 0 && (M / BM) * (N / 256) >= pxl_host::num_sms() - ncopy) ? 256 : 128;
   if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;
-  if (ncopy <= 0) ncopy = 24;
   CUtensorMap ta, tb;
   if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x_ptrs[rank], M, K, lda, BM, BK))
     return PXL_ERR_TENSORMAP;

@@ -98,7 +98,7 @@ class DistEngine:
         self.ctrl = dist.new_group(list(range(world)), backend="gloo")
         self.ret = dist.new_group(list(range(world)), backend="nccl" if on_gpu else "gloo")
         self.tp_group = None
-        for s in range(pp):
+        for s in range(pp if tp > 1 else 0):
             g = dist.new_group(list(range(s * tp, (s + 1) * tp)), backend="nccl" if on_gpu else "gloo")
             if s == self.topo.pp_rank:
                 self.tp_group = g
@@ -125,6 +125,7 @@ class DistEngine:
         dist.all_reduce(nb, op=dist.ReduceOp.MIN, group=self.ctrl)
         self.num_blocks = int(nb)
         self.max_in_flight = max_in_flight or pp
+        self._warm_links()
         ratio = micro_batch_ratio or pp
         self.planner = None
         if rank == 0:
@@ -142,6 +143,25 @@ class DistEngine:
         self.steps = 0
         self.keep_logits = False
         self.last_logits = None
+
+    def _warm_links(self) -> None:
+        """Open every point-to-point connection once, in an order that all ranks share, so that
+        connection set-up (which blocks the host until the peer arrives) never meets the
+        serving loop, where the ranks post their transfers at different times."""
+        topo = self.topo
+        x = torch.zeros(8, dtype=self.worker.dtype, device=self.device)
+        if not topo.is_first_stage:
+            dist.recv(x, src=topo.rank - topo.tp)
+        if not topo.is_last_stage:
+            dist.send(x, dst=topo.rank + topo.tp)
+        if topo.last_stage_root != 0:
+            t = torch.zeros(8, dtype=torch.int32, device=self.device)
+            if topo.rank == topo.last_stage_root:
+                dist.send(t, dst=0, group=self.ret)
+            elif topo.rank == 0:
+                dist.recv(t, src=topo.last_stage_root, group=self.ret)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
 
     # ------------------------------------------------------------------ rank-0 API
     @property
@@ -218,7 +238,9 @@ class DistEngine:
         if topo.rank != 0 or plan["n_logits"] == 0:
             return None
         if topo.last_stage_root != 0:
-            return ("recv", torch.empty(plan["n_logits"], dtype=torch.int32, device=self.device))
+            # post the receive now, in the same order in which the last stage posts its sends
+            t = torch.empty(plan["n_logits"], dtype=torch.int32, device=self.device)
+            return ("recv", (t, dist.irecv(t, src=topo.last_stage_root, group=self.ret)))
         return ("have", tokens)
 
     # ------------------------------------------------------------------ follower loop
@@ -295,7 +317,8 @@ class DistEngine:
         if owners:
             kind, t = res
             if kind == "recv":
-                dist.recv(t, src=self.topo.last_stage_root, group=self.ret)
+                t, work = t
+                work.wait()
             token_list = t.tolist()
         sched = self.scheduler
         for s, tok in zip(owners, token_list):

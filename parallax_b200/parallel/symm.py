@@ -74,8 +74,8 @@ class TPWorkspace:
         self.num_sets = num_sets
         self._use = 0
         self._epoch = [0] * num_sets
-        # local (non-symmetric) tile flags of the all-gather
-        self.tile_flags = torch.zeros((num_sets, rows_all // 128 + 8), dtype=torch.int32, device=device)
+        # local (non-symmetric) flags of the all-gather: 16 chunk flags per 128-row tile
+        self.tile_flags = torch.zeros((num_sets, (rows_all // 128 + 8) * 16), dtype=torch.int32, device=device)
 
     def next_set(self) -> tuple[int, int]:
         """(set index, epoch) for the next fused op."""

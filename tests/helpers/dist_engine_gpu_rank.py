@@ -22,6 +22,9 @@ from parallax_b200.parallel.dist_engine import DistEngine
 
 
 def main() -> None:
+    import faulthandler
+
+    faulthandler.dump_traceback_later(120, exit=True)   # a stuck rank shows where and ends itself
     mode, out_path = sys.argv[1], sys.argv[2]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     launcher.init_process_group(rank, world, int(os.environ["MASTER_PORT"]), "cuda")
