@@ -17,8 +17,11 @@ Two numbers come out of the same K timed steps:
   * ``e2e``    — output tokens / wall time through the public API (`Engine.step()`), including
     the per-step host-to-device copy of the packed index tensors from pinned memory and the
     device-to-host read of the sampled token ids.
-With N GPUs the 512 requests are split over N engine replicas (one per rank, strong scaling);
-times are the max over ranks, tokens the sum.
+With N GPUs the model runs as an N-stage pipeline (the layout BASELINE.json names: PP8 at
+N=8; ``--parallelism pp2tp4`` selects two stages of four tensor-parallel ranks, ``dp`` N engine
+replicas). Rank 0 schedules; ``N`` micro-batches of ``512/N`` requests are in flight; a step is
+one rotation (every running request advances one token). The same 512 requests are served at
+every N (strong scaling); times are the max over ranks.
 
     python bench.py --gpus 1 --steps 64 --warmup 8
     python -m torch.distributed.run --nproc-per-node 8 ... bench.py --gpus 8 --steps 64 --warmup 8
@@ -125,6 +128,100 @@ def make_workload(rank: int, vocab: int):
     return new_prompt
 
 
+def result_line(args, world, parallelism, tokens, dev_s, wall_s, launches, h2d, d2h, clocks, invalid, extra=None):
+    out = {
+        "metric": METRIC, "value": round(tokens / dev_s, 1), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_s / args.steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic uniform-random token ids, random-init N(0,0.02) weights",
+        "config": {"model": "Qwen3-8B", "global_batch": args.concurrency, "seq_len": IN_LEN + OUT_LEN,
+                   "input_len": IN_LEN, "output_len": OUT_LEN,
+                   "shared_prefix": "50% of requests share one of 8 x 512 tokens", "parallelism": parallelism,
+                   "step": "one continuous-batching iteration over all running requests",
+                   "l2": "inputs larger than L2 (16 GB weights + >80 GB KV read per step)",
+                   "timing": "CUDA events, max over ranks"},
+        "e2e": {"value": round(tokens / wall_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d / args.steps),
+                "d2h_bytes_per_step": int(d2h / args.steps), "ms_per_step": round(wall_s / args.steps * 1e3, 3)},
+        "gpu_launches": int(launches), "clocks": clocks, "tokens": int(tokens),
+    }
+    if extra:
+        out.update(extra)
+    if invalid:
+        out["invalid"] = "debug run with a truncated model"
+    return out
+
+
+def run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid) -> None:
+    """N GPUs as pipeline stages (optionally x tensor-parallel ranks) behind one scheduler."""
+    import re
+
+    import torch
+    import torch.distributed as dist
+
+    from parallax_b200.engine.request import Request, SamplingParams
+    from parallax_b200.ops import cuda as cu
+    from parallax_b200.parallel.dist_engine import DistEngine
+
+    m = re.fullmatch(r"pp(\d+)tp(\d+)", par)
+    pp, tp = (int(m.group(1)), int(m.group(2))) if m else ((1, world) if par == "tp" else (world, 1))
+    assert pp * tp == world, f"{par} does not fit {world} GPUs"
+    conc = args.concurrency
+    eng = DistEngine(cfg, pp, tp, device, torch.bfloat16, page_size=16, kv_fraction=0.85, max_batch_size=conc,
+                     max_num_tokens_per_batch=8192 + conc, micro_batch_ratio=pp, chunked_prefill_size=4096,
+                     enable_prefix_cache=True, max_total_length=IN_LEN + OUT_LEN + 64, request_timeout_s=None, seed=0)
+    if rank != 0:
+        eng.serve_forever()
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+    new_prompt = make_workload(0, cfg.vocab_size)
+    greedy = dict(temperature=0.0, ignore_eos=True)
+
+    def admit(n_out: int, length: int = IN_LEN):
+        r = Request(input_ids=new_prompt(length), sampling_params=SamplingParams(max_new_tokens=n_out, **greedy),
+                    max_total_length=IN_LEN + OUT_LEN + 64)
+        eng.add_request(r)
+        return r
+
+    initial = [admit(OUT_LEN - (i * OUT_LEN) // conc, IN_LEN + (i * OUT_LEN) // conc) for i in range(conc)]
+
+    def rotation() -> int:
+        """pp engine iterations: every running request advances by one token."""
+        toks = 0
+        for _ in range(pp):
+            for req, tok in eng.step():
+                if tok is not None:
+                    toks += 1
+                if req.is_finished:
+                    admit(OUT_LEN)
+        return toks
+
+    while any(r.is_prefill for r in initial):
+        rotation()
+    for _ in range(max(args.warmup, 0)):
+        rotation()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    eng.mark()
+    tokens = 0
+    for _ in range(args.steps):
+        tokens += rotation()
+    torch.cuda.synchronize()
+    eng.mark()
+    res = eng.elapsed()
+    clocks = sampler.stop()
+    cu.check_status(device)
+    eng.shutdown()
+    label = f"pp{pp}" + (f"tp{tp}" if tp > 1 else "")
+    print(json.dumps(result_line(args, world, label, tokens, res["device_ms"] / 1e3, res["wall_s"], res["launches"],
+                                 res["h2d_bytes"], 4 * tokens, clocks, invalid,
+                                 {"prefix_cache": eng.cache.prefix_cache.get_stats() if eng.cache.prefix_cache else None})),
+          flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -134,6 +231,7 @@ def main() -> None:
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--concurrency", type=int, default=CONCURRENCY)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the run invalid)")
+    ap.add_argument("--parallelism", default="auto", help="auto (single GPU, or ppN on N GPUs) | dp | pp | pp<P>tp<T>")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -163,6 +261,12 @@ def main() -> None:
     if args.layers:
         cfg.num_hidden_layers = args.layers
         invalid = True
+    par = args.parallelism
+    if par == "auto":
+        par = "pp" if world > 1 else "dp"
+    if par != "dp" and world > 1:
+        run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid)
+        return
     conc = args.concurrency // world
     eng = Engine(cfg, device=device, page_size=16, kv_fraction=0.88, max_batch_size=conc,
                  max_num_tokens_per_batch=8192 + conc, chunked_prefill_size=4096, enable_prefix_cache=True,
@@ -237,24 +341,10 @@ def main() -> None:
         dev_s, wall_s = float(mx[0]), float(mx[1])
         tokens, launches, h2d, d2h = float(sm[2]), float(sm[3]), float(sm[4]), float(sm[5])
     if rank == 0:
-        value = tokens / dev_s
-        out = {
-            "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_s / args.steps * 1e3, 3),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic uniform-random token ids, random-init N(0,0.02) weights",
-            "config": {"model": "Qwen3-8B", "global_batch": args.concurrency, "seq_len": IN_LEN + OUT_LEN,
-                       "input_len": IN_LEN, "output_len": OUT_LEN, "shared_prefix": "50% of requests share one of 8 x 512 tokens",
-                       "parallelism": f"dp{world}" if world > 1 else "single", "step": "one continuous-batching iteration",
-                       "l2": "inputs larger than L2 (16 GB weights + >80 GB KV read per step)",
-                       "timing": "CUDA events per step, max over ranks"},
-            "e2e": {"value": round(tokens / wall_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d / args.steps / world),
-                    "d2h_bytes_per_step": int(d2h / args.steps / world), "ms_per_step": round(wall_s / args.steps * 1e3, 3)},
-            "gpu_launches": int(launches), "clocks": clocks, "tokens": int(tokens),
-            "prefix_cache": eng.cache.prefix_cache.get_stats() if eng.cache.prefix_cache else None,
-        }
-        if invalid:
-            out["invalid"] = "debug run with a truncated model"
+        out = result_line(args, world, f"dp{world}" if world > 1 else "single", tokens, dev_s, wall_s, launches, h2d,
+                          d2h, clocks, invalid,
+                          {"prefix_cache": eng.cache.prefix_cache.get_stats() if eng.cache.prefix_cache else None})
+        out["config"]["timing"] = "CUDA events per step, max over ranks"
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()

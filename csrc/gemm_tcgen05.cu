@@ -779,7 +779,12 @@ PXL_EXPORT int pxl_gemm_bf16_ag(void* const* x_ptrs, void* const* ready_ptrs, vo
   if (epi != PXL_EPI_NONE && epi != PXL_EPI_SILU_MUL && epi != PXL_EPI_F32) return PXL_ERR_INVALID_ARG;
   if ((lda % 8) || (ldw % 8) || (ldc % 8)) return PXL_ERR_INVALID_ARG;
   const int M = tp * rows_per_rank;
-  if (ncopy <= 0) ncopy = 32;
+  if (ncopy <= 0) {
+    // copy CTAs take SMs from the GEMM: many when the GEMM is short (latency matters), few
+    // when it runs for several waves anyway and the copy hides behind the local shard's tiles
+    const int tiles = (M / BM) * pxl::ceil_div(N, 256);
+    ncopy = tiles >= 2 * pxl_host::num_sms() ? 8 : (tiles >= pxl_host::num_sms() ? 16 : 32);
+  }
   if (ncopy >= pxl_host::num_sms()) return PXL_ERR_INVALID_ARG;
   // a chunk of kAgChunkRows rows must fit into the copy CTA's shared memory
   if (static_cast<long long>(kAgChunkRows) * K * 2 > 192 * 1024 || (lda % 8)) return PXL_ERR_INVALID_ARG;

@@ -39,6 +39,12 @@ from parallax_b200.parallel.tp_comm import CollectiveTPComm, FusedTPComm
 logger = logging.getLogger(__name__)
 
 
+def cu_launch_count() -> int:
+    from parallax_b200.ops import cuda as cu
+
+    return cu.launch_count
+
+
 def split_layers(num_layers: int, pp: int) -> list[tuple[int, int]]:
     """Even contiguous split (what water-filling yields for identical GPUs); earlier stages get
     the remainder layers because the last stage also runs the lm_head."""
@@ -143,6 +149,8 @@ class DistEngine:
         self.steps = 0
         self.keep_logits = False
         self.last_logits = None
+        self.marks: list = []
+        self.h2d_bytes = 0
 
     def _warm_links(self) -> None:
         """Open every point-to-point connection once, in an order that all ranks share, so that
@@ -207,6 +215,7 @@ class DistEngine:
         self._bi = (self._bi + 1) % len(self.builders)
         fb = b.build(plan["ids"] if topo.is_first_stage else None, plan["pos"], plan["slots"], plan["p_q"],
                      plan["p_ctx"], plan["p_tables"], plan["d_ctx"], plan["d_tables"], plan["logit_rows"])
+        self.h2d_bytes += fb.h2d_bytes
         T, H = fb.num_tokens, self.cfg.hidden_size
         hidden = None
         if not topo.is_first_stage:
@@ -243,6 +252,36 @@ class DistEngine:
             return ("recv", (t, dist.irecv(t, src=topo.last_stage_root, group=self.ret)))
         return ("have", tokens)
 
+    # ------------------------------------------------------------------ device-time probes
+    def _on_mark(self) -> None:
+        ev = None
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+        self.marks.append((ev, time.perf_counter(), cu_launch_count(), self.h2d_bytes))
+
+    def _on_elapsed(self) -> dict:
+        """Device time between the last two marks (max over ranks) and the kernels launched /
+        bytes copied to the device between them (sum over ranks)."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        (e0, t0, l0, h0), (e1, t1, l1, h1) = self.marks[-2], self.marks[-1]
+        ms = e0.elapsed_time(e1) if e0 is not None else (t1 - t0) * 1e3
+        mx = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=self.ctrl)
+        sm = torch.tensor([float(l1 - l0), float(h1 - h0)], dtype=torch.float64)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM, group=self.ctrl)
+        return {"device_ms": float(mx[0]), "launches": int(sm[0]), "h2d_bytes": int(sm[1]), "wall_s": t1 - t0}
+
+    def mark(self) -> None:
+        """Rank 0: every rank records a CUDA event at this point of its stream."""
+        self._bcast({"cmd": "mark"})
+        self._on_mark()
+
+    def elapsed(self) -> dict:
+        self._bcast({"cmd": "elapsed"})
+        return self._on_elapsed()
+
     # ------------------------------------------------------------------ follower loop
     def serve_forever(self) -> None:
         """Ranks other than 0: execute broadcast plans until rank 0 says stop."""
@@ -251,6 +290,12 @@ class DistEngine:
             plan = self._bcast(None)
             if plan.get("cmd") == "stop":
                 break
+            if plan.get("cmd") == "mark":
+                self._on_mark()
+                continue
+            if plan.get("cmd") == "elapsed":
+                self._on_elapsed()
+                continue
             self._execute(plan)
             self.steps += 1
         for work, _ in self._pending_sends:

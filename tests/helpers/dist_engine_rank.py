@@ -20,10 +20,13 @@ def main() -> None:
     eng = launcher.build_dist_engine(spec)
     if rank == 0:
         prompts = spec["prompts"]
+        eng.mark()
         outs = eng.generate(prompts, SamplingParams(max_new_tokens=spec["max_new"], temperature=0.0, ignore_eos=True))
+        eng.mark()
+        probe = eng.elapsed()
         eng.shutdown()
         with open(out_path, "w") as f:
-            json.dump({"outputs": outs, "steps": eng.steps}, f)
+            json.dump({"outputs": outs, "steps": eng.steps, "probe": probe}, f)
     else:
         eng.serve_forever()
     import torch.distributed as dist

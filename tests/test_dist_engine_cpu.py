@@ -63,3 +63,4 @@ def test_dist_engine_matches_single_process(pp, tp, tmp_path):
     want = _single()
     got = _run_group(pp, tp, tmp_path)
     assert got["outputs"] == want
+    assert got["probe"]["device_ms"] > 0 and got["probe"]["h2d_bytes"] > 0
