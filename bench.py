@@ -19,7 +19,7 @@ Two numbers come out of the same K timed steps:
     device-to-host read of the sampled token ids.
 With N GPUs the model runs as an N-stage pipeline (the layout BASELINE.json names: PP8 at
 N=8; ``--parallelism pp2tp4`` selects two stages of four tensor-parallel ranks, ``dp`` N engine
-replicas). Rank 0 schedules; ``N`` micro-batches of ``512/N`` requests are in flight; a step is
+replicas). Rank 0 schedules; ``N+1`` or ``N+2`` micro-batches are in flight; a step is
 one rotation (every running request advances one token). The same 512 requests are served at
 every N (strong scaling); times are the max over ranks.
 
@@ -166,8 +166,12 @@ def run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid) -> No
     pp, tp = (int(m.group(1)), int(m.group(2))) if m else ((1, world) if par == "tp" else (world, 1))
     assert pp * tp == world, f"{par} does not fit {world} GPUs"
     conc = args.concurrency
+    # a couple of micro-batches more than stages, so that a stage always has one queued while the
+    # scheduler on rank 0 commits the tokens of another and plans its next turn
+    n_mb = 1 if pp == 1 else pp + (1 if pp <= 2 else 2)
     eng = DistEngine(cfg, pp, tp, device, torch.bfloat16, page_size=16, kv_fraction=0.85, max_batch_size=conc,
-                     max_num_tokens_per_batch=8192 + conc, micro_batch_ratio=pp, chunked_prefill_size=4096,
+                     max_num_tokens_per_batch=8192 + conc, micro_batch_ratio=n_mb, max_in_flight=n_mb,
+                     chunked_prefill_size=4096,
                      enable_prefix_cache=True, max_total_length=IN_LEN + OUT_LEN + 64, request_timeout_s=None, seed=0)
     if rank != 0:
         eng.serve_forever()
@@ -186,9 +190,9 @@ def run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid) -> No
     initial = [admit(OUT_LEN - (i * OUT_LEN) // conc, IN_LEN + (i * OUT_LEN) // conc) for i in range(conc)]
 
     def rotation() -> int:
-        """pp engine iterations: every running request advances by one token."""
+        """One engine iteration per micro-batch: every running request advances by one token."""
         toks = 0
-        for _ in range(pp):
+        for _ in range(n_mb):
             for req, tok in eng.step():
                 if tok is not None:
                     toks += 1
