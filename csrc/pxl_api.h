@@ -127,6 +127,40 @@ int pxl_gemm_bf16_ag(void* const* x_ptrs, void* const* ready_ptrs, void* tile_fl
                      int lda, int ldw, int ldc, int epi, uint32_t epoch, int ncopy, int bn,
                      int* status, pxl_stream_t stream);
 
+// ---- mla.cu: multi-head latent attention on the compressed cache [blocks, page, 512 + 64] ----
+// RMSNorm(latent) + interleaved RoPE(k_pe) of ckv [T, 576] (row stride ld) written to the cache.
+int pxl_mla_kv_prep(const void* ckv, int64_t ld, const void* norm_w, const float* cos_sin,
+                    const int* positions, const int64_t* slots, void* cache, int T, int latent,
+                    int rope, int64_t num_slots, float eps, int* status, pxl_stream_t stream);
+// q [T, H, nope + 64] -> q_nope_hm [H, Tpad, nope] (head-major, input of the absorb GEMM) and
+// q_pe [T, H, 64] with interleaved RoPE applied.
+int pxl_mla_q_prep(const void* q, int64_t ld, const float* cos_sin, const int* positions,
+                   void* q_nope_hm, void* q_pe, int T, int Tpad, int H, int nope, int rope,
+                   pxl_stream_t stream);
+// Absorbed attention for tokens [tok_begin, tok_begin + n_tok): q_lat [H, Tpad, 512], q_pe
+// [T, H, 64] -> out [H, Tpad, 512]. Query token t sits at positions[t] of sequence
+// cu_q-lookup(t) (cu_q NULL: sequence t - tok_begin) and attends keys 0..positions[t], or, when
+// topk != NULL and topk[t][0] >= 0, the listed positions only (topk rows indexed by t).
+int pxl_mla_attn(const void* q_lat, const void* q_pe, const void* cache, const int* block_tables,
+                 const int* cu_q, const int* positions, const int* topk, void* out, int tok_begin,
+                 int n_tok, int Tpad, int H, int B, int max_blocks, int page, int latent, int rope,
+                 int topk_k, int topk_stride, float scale, pxl_stream_t stream);
+
+// ---- dsa.cu: lightning indexer -------------------------------------------------------------
+// scores[t, j] = sum_h relu(q[t,h,:] . k_j) * w[t,h] for j <= positions[t], -inf beyond;
+// ld_scores >= ceil(max_ctx / 64) * 64.
+int pxl_dsa_index_scores(const void* q, const float* w, const void* index_cache,
+                         const int* block_tables, const int* cu_q, const int* positions,
+                         float* scores, int64_t ld_scores, int T, int B, int Hi, int Di,
+                         int max_blocks, int page, int max_ctx, pxl_stream_t stream);
+// Positions of the k largest scores among [0, positions[t]] per row (unordered); rows with at
+// most k candidates are filled with -1 ("attend densely").
+int pxl_topk_select(const float* scores, int64_t ld, const int* positions, int T, int k, int* out,
+                    int64_t ld_out, pxl_stream_t stream);
+// cache[slots[t], :] = src[t, :] (slot < 0: skip)
+int pxl_store_rows(const void* src, int64_t ld, const int64_t* slots, void* cache, int T, int D,
+                   int64_t num_slots, int* status, pxl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -28,6 +28,7 @@ class ForwardBatch:
     p_ctx_lens: Optional[torch.Tensor] = None     # int32 [Bp]
     p_block_tables: Optional[torch.Tensor] = None  # int32 [Bp, MB]
     p_max_q: int = 0
+    p_max_ctx: int = 0
     # decode part
     d_ctx_lens: Optional[torch.Tensor] = None     # int32 [Bd]
     d_block_tables: Optional[torch.Tensor] = None  # int32 [Bd, MB]
@@ -120,6 +121,7 @@ class BatchBuilder:
             fb.p_ctx_lens = view("p_ctx")
             fb.p_block_tables = view("p_bt").view(Bp, -1)
             fb.p_max_q = int(max(p_q_lens))
+            fb.p_max_ctx = int(max(p_ctx_lens))
         if Bd:
             fb.d_ctx_lens = view("d_ctx")
             fb.d_block_tables = view("d_bt").view(Bd, -1)

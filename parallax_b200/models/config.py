@@ -283,6 +283,22 @@ def named_config(name: str) -> ModelConfig:
         if v32:
             d.update(index_n_heads=64, index_head_dim=128, index_topk=2048)
         return config_from_hf(d)
+    if n in {"tiny-mla", "tiny-dsa", "small-mla", "small-dsa"}:
+        small = n.startswith("small")   # "small": the widths the sm_100a MLA kernels are built for
+        d = dict(architectures=["DeepseekV32ForCausalLM" if n.endswith("dsa") else "DeepseekV3ForCausalLM"],
+                 model_type="deepseek_v32" if n.endswith("dsa") else "deepseek_v3",
+                 hidden_size=512 if small else 128, num_hidden_layers=3, num_attention_heads=8 if small else 4,
+                 num_key_value_heads=8 if small else 4, q_lora_rank=256 if small else 48,
+                 kv_lora_rank=512 if small else 32, qk_nope_head_dim=128 if small else 32,
+                 qk_rope_head_dim=64 if small else 16, v_head_dim=128 if small else 32,
+                 intermediate_size=1024 if small else 256, moe_intermediate_size=256 if small else 64,
+                 n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, first_k_dense_replace=1,
+                 scoring_func="sigmoid", topk_method="noaux_tc", n_group=2, topk_group=1, routed_scaling_factor=2.5,
+                 norm_topk_prob=True, vocab_size=1024, rope_theta=10000.0, max_position_embeddings=4096)
+        if n.endswith("dsa"):
+            d.update(index_n_heads=8 if small else 4, index_head_dim=128 if small else 32,
+                     index_topk=64 if small else 16)
+        return config_from_hf(d)
     if n == "tiny":
         return config_from_hf(dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=256,
                                    num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,

@@ -65,6 +65,13 @@ _SIGS = {
     "pxl_moe_combine": [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P],
     "pxl_gemm_bf16_grouped": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                               c_int, c_int, c_int, _P, _P],
+    "pxl_mla_kv_prep": [_P, c_int64, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_float, _P, _P],
+    "pxl_mla_q_prep": [_P, c_int64, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "pxl_mla_attn": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_int, c_float, _P],
+    "pxl_dsa_index_scores": [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "pxl_topk_select": [_P, c_int64, _P, c_int, c_int, _P, c_int64, _P],
+    "pxl_store_rows": [_P, c_int64, _P, _P, c_int, c_int, c_int64, _P, _P],
     "pxl_argmax": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P],
     "pxl_sample": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
 }

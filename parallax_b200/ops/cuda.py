@@ -429,3 +429,119 @@ def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w1: torch
 
 def as_c_int_p(t: torch.Tensor) -> ctypes.c_void_p:
     return ctypes.c_void_p(t.data_ptr())
+
+
+# ---------------------------------------------------------------------------- MLA / DSA
+class _HeadPlan:
+    """Static tile lists that run the grouped GEMM with attention heads in the role of experts:
+    rows [h * Tpad, (h + 1) * Tpad) of a head-major matrix use weight block h."""
+
+    __slots__ = ("mt_expert", "mt_row0", "mt_row_end", "num_mt", "max_mt")
+
+
+_head_plans: dict = {}
+
+
+def _head_plan(H: int, Tpad: int, device) -> _HeadPlan:
+    key = (H, Tpad, device.index)
+    p = _head_plans.get(key)
+    if p is None:
+        tiles = Tpad // 128
+        h = torch.arange(H, dtype=torch.int32).repeat_interleave(tiles)
+        i = torch.arange(tiles, dtype=torch.int32).repeat(H)
+        p = _HeadPlan()
+        p.mt_expert = h.to(device)
+        p.mt_row0 = (h * Tpad + i * 128).to(device)
+        p.mt_row_end = ((h + 1) * Tpad).to(device)
+        p.num_mt = torch.tensor([H * tiles], dtype=torch.int32, device=device)
+        p.max_mt = H * tiles
+        _head_plans[key] = p
+    return p
+
+
+def _pad128(n: int) -> int:
+    return max(128, (n + 127) // 128 * 128)
+
+
+def mla_kv_prep(ckv, norm_w, cos_sin, positions, slot_mapping, cache, eps, latent: int):
+    T = ckv.shape[0]
+    rope = ckv.shape[1] - latent
+    num_slots = cache.shape[0] * cache.shape[-2]
+    check(_lib.lib().pxl_mla_kv_prep(ckv.data_ptr(), ckv.stride(0), norm_w.data_ptr(), cos_sin.data_ptr(),
+                                     positions.data_ptr(), slot_mapping.data_ptr(), cache.data_ptr(), T, latent, rope,
+                                     num_slots, eps, status_tensor(ckv.device).data_ptr(), _stream(ckv.device)),
+          "pxl_mla_kv_prep")
+    _count()
+
+
+def mla_q_absorb(q, w_uk_s, cos_sin, positions, H: int, nope: int, latent: int):
+    T = q.shape[0]
+    rope = q.shape[1] // H - nope
+    Tpad = _pad128(T)
+    dev = q.device
+    q_nope_hm = torch.zeros((H, Tpad, nope), dtype=q.dtype, device=dev) if Tpad != T else \
+        torch.empty((H, Tpad, nope), dtype=q.dtype, device=dev)
+    q_pe = torch.empty((T, H, rope), dtype=q.dtype, device=dev)
+    check(_lib.lib().pxl_mla_q_prep(q.data_ptr(), q.stride(0), cos_sin.data_ptr(), positions.data_ptr(),
+                                    q_nope_hm.data_ptr(), q_pe.data_ptr(), T, Tpad, H, nope, rope, _stream(dev)),
+          "pxl_mla_q_prep")
+    _count()
+    plan = _head_plan(H, Tpad, dev)
+    q_lat = grouped_linear(q_nope_hm.view(H * Tpad, nope), w_uk_s, plan, H)
+    return q_lat.view(H, Tpad, latent), q_pe
+
+
+def mla_attn(q_lat_hm, q_pe, cache, block_tables, cu_q, positions, scale, tok_begin: int, n_tok: int, topk=None,
+             out=None):
+    H, Tpad, L = q_lat_hm.shape
+    if out is None:
+        out = torch.zeros_like(q_lat_hm)
+    if n_tok <= 0:
+        return out
+    B = block_tables.shape[0]
+    check(_lib.lib().pxl_mla_attn(q_lat_hm.data_ptr(), q_pe.data_ptr(), cache.data_ptr(), block_tables.data_ptr(),
+                                  _ptr(cu_q), positions.data_ptr(), _ptr(topk), out.data_ptr(), tok_begin, n_tok, Tpad,
+                                  H, B, block_tables.shape[1], cache.shape[-2], L, q_pe.shape[-1],
+                                  0 if topk is None else topk.shape[1], 0 if topk is None else topk.stride(0),
+                                  float(scale), _stream(out.device)), "pxl_mla_attn")
+    _count()
+    return out
+
+
+def mla_unabsorb(o_lat_hm, w_uv_s, T: int):
+    H, Tpad, L = o_lat_hm.shape
+    plan = _head_plan(H, Tpad, o_lat_hm.device)
+    o = grouped_linear(o_lat_hm.view(H * Tpad, L), w_uv_s, plan, H)       # [H*Tpad, V]
+    V = o.shape[1]
+    return o.view(H, Tpad, V)[:, :T].transpose(0, 1).reshape(T, H * V)
+
+
+def store_rows(src, slot_mapping, cache):
+    T, D = src.shape
+    num_slots = cache.numel() // D
+    check(_lib.lib().pxl_store_rows(src.data_ptr(), src.stride(0), slot_mapping.data_ptr(), cache.data_ptr(), T, D,
+                                    num_slots, status_tensor(src.device).data_ptr(), _stream(src.device)),
+          "pxl_store_rows")
+    _count()
+
+
+def dsa_index_scores(q_idx, w, index_cache, block_tables, cu_q, positions, max_ctx: int):
+    T, Hi, Di = q_idx.shape
+    ld = (max_ctx + 63) // 64 * 64
+    scores = torch.empty((T, ld), dtype=torch.float32, device=q_idx.device)
+    check(_lib.lib().pxl_dsa_index_scores(q_idx.data_ptr(), w.data_ptr(), index_cache.data_ptr(),
+                                          block_tables.data_ptr(), _ptr(cu_q), positions.data_ptr(),
+                                          scores.data_ptr(), ld, T, block_tables.shape[0], Hi, Di,
+                                          block_tables.shape[1], index_cache.shape[-2], max_ctx,
+                                          _stream(q_idx.device)), "pxl_dsa_index_scores")
+    _count()
+    return scores
+
+
+def topk_select(scores, positions, k: int):
+    T = scores.shape[0]
+    out = torch.empty((T, k), dtype=torch.int32, device=scores.device)
+    check(_lib.lib().pxl_topk_select(scores.data_ptr(), scores.stride(0), positions.data_ptr(), T, k, out.data_ptr(), k,
+                                     _stream(scores.device)), "pxl_topk_select")
+    _count()
+    return out

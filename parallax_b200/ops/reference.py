@@ -314,3 +314,108 @@ def moe_ffn(x, ids, weights, w1, w2, num_experts, base=None):
 
 def default_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(head_dim)
+
+
+# ---------------------------------------------------------------------------- MLA / DSA
+def _rope_interleaved(x, cos_sin, positions):
+    """Rotate pairs (2i, 2i+1) of the last dim by the angle of ``positions`` (fp32)."""
+    R = x.shape[-1]
+    cs = cos_sin[positions.long()].float()                  # [T, R]
+    cos, sin = cs[:, : R // 2], cs[:, R // 2:]
+    while cos.dim() < x.dim():
+        cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+    x0, x1 = x[..., 0::2].float(), x[..., 1::2].float()
+    out = torch.stack([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
+    return out.flatten(-2)
+
+
+def mla_kv_prep(ckv, norm_w, cos_sin, positions, slot_mapping, cache, eps, latent: int):
+    """cache[slot] = [rmsnorm(ckv[:, :latent]) * w | rope_interleaved(ckv[:, latent:])]."""
+    lat = ckv[:, :latent].float()
+    lat = lat * torch.rsqrt(lat.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+    pe = _rope_interleaved(ckv[:, latent:], cos_sin, positions)
+    rows = torch.cat([lat, pe], dim=-1).to(cache.dtype)
+    flat = cache.view(-1, cache.shape[-1])
+    ok = slot_mapping >= 0
+    flat[slot_mapping[ok].long()] = rows[ok]
+
+
+def mla_q_absorb(q, w_uk_s, cos_sin, positions, H: int, nope: int, latent: int):
+    """q [T, H*(nope+R)] -> (q_lat_hm [H, Tpad, latent], q_pe [T, H, R]); w_uk_s [H*latent, nope]."""
+    T = q.shape[0]
+    q = q.view(T, H, -1)
+    q_nope, q_pe = q[..., :nope], q[..., nope:]
+    q_pe = _rope_interleaved(q_pe, cos_sin, positions).to(q.dtype)
+    w = w_uk_s.view(H, latent, nope).float()
+    q_lat = torch.einsum("thd,hcd->htc", q_nope.float(), w).to(q.dtype)
+    return q_lat.contiguous(), q_pe.contiguous()
+
+
+def mla_attn(q_lat_hm, q_pe, cache, block_tables, cu_q, positions, scale, tok_begin: int, n_tok: int, topk=None,
+             out=None):
+    """Absorbed latent attention for tokens [tok_begin, tok_begin + n_tok) -> o_lat_hm [H, Tpad, latent].
+    ``positions`` / ``topk`` / ``q_pe`` rows are indexed by the batch-wide token index."""
+    H, Tpad, L = q_lat_hm.shape
+    page = cache.shape[-2]
+    flat = cache.view(-1, cache.shape[-1]).float()
+    if out is None:
+        out = torch.zeros_like(q_lat_hm)
+    cu = None if cu_q is None else cu_q.tolist()
+    for t in range(tok_begin, tok_begin + n_tok):
+        seq = t - tok_begin if cu is None else max(i for i in range(len(cu) - 1) if cu[i] <= t)
+        pos = int(positions[t])
+        if topk is not None and int(topk[t, 0]) >= 0:
+            keys = topk[t]
+            keys = keys[(keys >= 0) & (keys <= pos)].long()
+        else:
+            keys = torch.arange(pos + 1)
+        bt = block_tables[seq].long()
+        rows = flat[bt[keys // page] * page + keys % page]            # [n, L+R]
+        ql = torch.cat([q_lat_hm[:, t].float(), q_pe[t].float()], dim=-1)   # [H, L+R]
+        p = torch.softmax(ql @ rows.t() * scale, dim=-1)
+        out[:, t] = (p @ rows[:, :L]).to(out.dtype)
+    return out
+
+
+def mla_unabsorb(o_lat_hm, w_uv_s, T: int):
+    """o_lat_hm [H, Tpad, latent], w_uv_s [H*V, latent] -> [T, H*V]."""
+    H, _Tpad, L = o_lat_hm.shape
+    w = w_uv_s.view(H, -1, L).float()
+    o = torch.einsum("htc,hvc->thv", o_lat_hm[:, :T].float(), w)
+    return o.reshape(T, -1).to(o_lat_hm.dtype)
+
+
+def store_rows(src, slot_mapping, cache):
+    flat = cache.view(-1, cache.shape[-1])
+    ok = slot_mapping >= 0
+    flat[slot_mapping[ok].long()] = src[ok].to(cache.dtype)
+
+
+def dsa_index_scores(q_idx, w, index_cache, block_tables, cu_q, positions, max_ctx: int):
+    """scores[t, j] = sum_h relu(q[t,h] . k_j) * w[t,h] for j <= positions[t], -inf beyond."""
+    T = q_idx.shape[0]
+    page = index_cache.shape[-2]
+    flat = index_cache.view(-1, index_cache.shape[-1]).float()
+    ld = (max_ctx + 63) // 64 * 64
+    out = torch.full((T, ld), float("-inf"), dtype=torch.float32)
+    cu = None if cu_q is None else cu_q.tolist()
+    for t in range(T):
+        seq = t if cu is None else max(i for i in range(len(cu) - 1) if cu[i] <= t)
+        pos = int(positions[t])
+        keys = torch.arange(pos + 1)
+        bt = block_tables[seq].long()
+        k = flat[bt[keys // page] * page + keys % page]               # [n, Di]
+        s = torch.relu(q_idx[t].float() @ k.t())                        # [Hi, n]
+        out[t, : pos + 1] = (s * w[t].float()[:, None]).sum(0)
+    return out
+
+
+def topk_select(scores, positions, k: int):
+    """Positions of the k largest scores among [0, positions[t]]; rows with <= k candidates are -1."""
+    T = scores.shape[0]
+    out = torch.full((T, k), -1, dtype=torch.int32)
+    for t in range(T):
+        n = int(positions[t]) + 1
+        if n > k:
+            out[t] = torch.topk(scores[t, :n], k).indices.to(torch.int32)
+    return out

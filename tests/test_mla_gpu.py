@@ -1,0 +1,164 @@
+"""sm_100a MLA / DSA kernels against the fp32 PyTorch restatement of the same ops."""
+
+import pytest
+import torch
+
+from parallax_b200.models.config import named_config
+from parallax_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float().cpu() - b.float().cpu()).norm() / (b.float().cpu().norm() + 1e-12))
+
+
+def _setup(seed=0, H=16, page=16, n_blocks=96):
+    torch.manual_seed(seed)
+    L, R, nope, V = 512, 64, 128, 128
+    cache = torch.zeros(n_blocks, 1, page, L + R)
+    cos_sin = ref.build_cos_sin(4096, R, 10000.0)
+    return L, R, nope, V, cache, cos_sin
+
+
+def test_mla_pipeline_prefill_decode_sparse():
+    from parallax_b200.ops import cuda as cu
+
+    dev = torch.device("cuda", 0)
+    H, page = 16, 16
+    L, R, nope, V, cache, cos_sin = _setup(H=H, page=page)
+    # two prefill sequences (one continuing after a cached prefix) + three decode sequences
+    p_q, p_ctx = [70, 33], [70, 133]
+    d_ctx = [200, 17, 1]
+    Tp, Bd = sum(p_q), len(d_ctx)
+    T = Tp + Bd
+    positions = torch.cat([torch.arange(0, 70), torch.arange(100, 133), torch.tensor([c - 1 for c in d_ctx])]).int()
+    # block tables: distinct blocks per sequence
+    nb = [(c + page - 1) // page for c in p_ctx + d_ctx]
+    ids = torch.randperm(cache.shape[0])[: sum(nb)].int()
+    tables, o = [], 0
+    for n in nb:
+        tables.append(ids[o:o + n]); o += n
+    maxb = max(nb)
+    bt = torch.zeros(len(nb), maxb, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, : len(t)] = t
+    p_bt, d_bt = bt[:2].contiguous(), bt[2:].contiguous()
+    cu_q = torch.tensor([0, 70, 103], dtype=torch.int32)
+    # pre-existing cache content for every sequence (prefix / earlier tokens)
+    cache.normal_(0, 0.5)
+    seq_of_tok = [0] * 70 + [1] * 33 + [2, 3, 4]
+    slots = torch.tensor([int(bt[s, int(p) // page]) * page + int(p) % page for s, p in zip(seq_of_tok, positions)],
+                         dtype=torch.int64)
+    ckv = torch.randn(T, L + R + 40) * 0.5           # extra columns: the strided view must be honoured
+    norm_w = torch.rand(L) + 0.5
+    q = torch.randn(T, H * (nope + R)) * 0.3
+    w_uk_s = torch.randn(H * L, nope) * 0.05
+    w_uv_s = torch.randn(H * V, L) * 0.05
+    topk_k = 48
+    topk = torch.full((T, topk_k), -1, dtype=torch.int32)
+    for t in range(T):
+        pos = int(positions[t])
+        if pos + 1 > topk_k and t % 2 == 0:       # sparse rows mixed with dense rows
+            sel = torch.randperm(pos + 1)[:topk_k]
+            sel[:3] = torch.tensor([-1, pos + 5, pos])[:3]   # a hole, a future position (masked), the diagonal
+            topk[t] = sel.int()
+            topk[t, 0] = int(torch.randint(0, pos + 1, ()))
+    scale = (nope + R) ** -0.5
+
+    def run(mod, to):
+        c = to(cache.clone().to(torch.bfloat16))
+        mod.mla_kv_prep(to(ckv.to(torch.bfloat16))[:, : L + R], to(norm_w.to(torch.bfloat16)), to(cos_sin), to(positions),
+                        to(slots), c, 1e-6, L)
+        q_lat, q_pe = mod.mla_q_absorb(to(q.to(torch.bfloat16)), to(w_uk_s.to(torch.bfloat16)), to(cos_sin), to(positions),
+                                       H, nope, L)
+        o_lat = mod.mla_attn(q_lat, q_pe, c, to(p_bt), to(cu_q), to(positions), scale, 0, Tp, topk=to(topk))
+        o_lat = mod.mla_attn(q_lat, q_pe, c, to(d_bt), None, to(positions), scale, Tp, Bd, topk=to(topk), out=o_lat)
+        out = mod.mla_unabsorb(o_lat, to(w_uv_s.to(torch.bfloat16)), T)
+        return c, q_lat[:, :T], q_pe, o_lat[:, :T], out
+
+    want = run(ref, lambda x: x)
+    got = run(cu, lambda x: x.to(dev))
+    torch.cuda.synchronize()
+    cu.check_status(dev)
+    names = ["cache", "q_lat", "q_pe", "o_lat", "out"]
+    for n, g, w in zip(names, got, want):
+        assert _rel(g, w) < 2e-2, (n, _rel(g, w))
+
+
+def test_dsa_scores_topk_store():
+    from parallax_b200.ops import cuda as cu
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(2)
+    T, Hi, Di, page = 5, 64, 128, 16
+    cache = (torch.randn(64, 1, page, Di) * 0.5).to(torch.bfloat16)
+    bt = torch.randperm(64)[:60].int().view(5, 12)
+    pos = torch.tensor([150, 3, 64, 191, 100], dtype=torch.int32)
+    q = (torch.randn(T, Hi, Di) * 0.3).to(torch.bfloat16)
+    w = torch.rand(T, Hi)
+    want = ref.dsa_index_scores(q, w, cache, bt, None, pos, 192)
+    got = cu.dsa_index_scores(q.to(dev), w.to(dev), cache.to(dev), bt.to(dev), None, pos.to(dev), 192).cpu()
+    fin = torch.isfinite(want)
+    assert torch.equal(torch.isfinite(got), fin)
+    assert _rel(got[fin], want[fin]) < 1e-2
+    k = 32
+    sel = cu.topk_select(got.to(dev), pos.to(dev), k).cpu()
+    for t in range(T):
+        n = int(pos[t]) + 1
+        if n <= k:
+            assert (sel[t] == -1).all()
+        else:
+            kth = torch.topk(got[t, :n], k).values[-1]
+            vals = got[t, sel[t].long()]
+            assert len(set(sel[t].tolist())) == k and (sel[t] >= 0).all() and (sel[t] < n).all()
+            assert (vals >= kth).all()
+    # ragged (prefill) addressing through cu_q: three tokens of sequence 1, two of sequence 3
+    cu_q = torch.tensor([0, 0, 3, 3, 5], dtype=torch.int32)
+    pos2 = torch.tensor([10, 11, 12, 77, 78], dtype=torch.int32)
+    want2 = ref.dsa_index_scores(q, w, cache, bt[:4], cu_q, pos2, 80)
+    got2 = cu.dsa_index_scores(q.to(dev), w.to(dev), cache.to(dev), bt[:4].contiguous().to(dev), cu_q.to(dev), pos2.to(dev), 80).cpu()
+    fin2 = torch.isfinite(want2)
+    assert torch.equal(torch.isfinite(got2), fin2) and _rel(got2[fin2], want2[fin2]) < 1e-2
+    # key store
+    src = torch.randn(T, Di).to(torch.bfloat16)
+    slots = torch.tensor([5, -1, 17, 1000, 3], dtype=torch.int64)
+    c_ref, c_dev = cache.clone(), cache.clone().to(dev)
+    ref.store_rows(src, slots, c_ref)
+    cu.store_rows(src.to(dev), slots.to(dev), c_dev)
+    assert torch.equal(c_dev.cpu(), c_ref)
+    cu.check_status(dev)
+
+
+@pytest.mark.parametrize("name", ["small-mla", "small-dsa"])
+def test_deepseek_engine_gpu_matches_cpu(name):
+    from parallax_b200.engine.engine import Engine
+    from parallax_b200.engine.request import Request, SamplingParams
+    from parallax_b200.ops import cuda as cu
+
+    cfg = named_config(name)
+    kw = dict(num_blocks=128, page_size=16, max_batch_size=4, max_num_tokens_per_batch=512, chunked_prefill_size=96,
+              max_total_length=512, seed=0)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (150, 20, 97)]
+
+    def first_logits(device, dtype):
+        eng = Engine(cfg, device=device, dtype=dtype, **kw)
+        eng.keep_logits = True
+        for p in prompts:
+            eng.add_request(Request(input_ids=p, sampling_params=SamplingParams(max_new_tokens=3, temperature=0.0,
+                                                                               ignore_eos=True), max_total_length=512))
+        outs = []
+        while eng.has_work():
+            eng.step()
+            if eng.last_logits is not None:
+                outs.append(eng.last_logits.float().cpu().clone())
+                eng.last_logits = None
+        return outs
+
+    want = first_logits("cpu", torch.float32)
+    got = first_logits("cuda:0", torch.bfloat16)
+    cu.check_status(torch.device("cuda", 0))
+    assert len(want) == len(got)
+    for a, b in zip(got[:3], want[:3]):
+        assert a.shape == b.shape and _rel(a, b) < 6e-2, _rel(a, b)
