@@ -161,6 +161,19 @@ int pxl_topk_select(const float* scores, int64_t ld, const int* positions, int T
 int pxl_store_rows(const void* src, int64_t ld, const int64_t* slots, void* cache, int T, int D,
                    int64_t num_slots, int* status, pxl_stream_t stream);
 
+// ---- gemm_fp8.cu: block-scaled e4m3 GEMM (1x128 activation groups, weight scales per 64 rows x 128 cols)
+// C[M,N] bf16 = sum over 128-wide K blocks of a_s[m,kb] * w_s[n/64,kb] * (A_kb W_kb^T). K % 128 == 0,
+// N % 128 == 0. epi: PXL_EPI_NONE / PXL_EPI_RESIDUAL / PXL_EPI_SILU_MUL (W rows interleaved as for bf16).
+int pxl_gemm_fp8_block(const void* A, const float* a_s, const void* W, const float* w_s, void* C,
+                       const void* residual, int M, int N, int K, int lda, int ldw, int ldc, int epi,
+                       int* status, pxl_stream_t stream);
+int pxl_gemm_fp8_block_grouped(const void* A, const float* a_s, const void* W, const float* w_s, void* C,
+                               int P, int E, int N, int K, int lda, int ldw, int ldc, const int* mt_expert,
+                               const int* mt_row0, const int* mt_row_end, const int* num_mt, int max_m_tiles,
+                               int epi, int* status, pxl_stream_t stream);
+// x [T,K] bf16 (row stride ld) -> q [T,K] e4m3 + scales [T, K/128]: x ~= q * scale per group
+int pxl_quant_fp8_rows(const void* x, int64_t ld, void* q, float* scales, int T, int K, pxl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -72,6 +72,10 @@ _SIGS = {
     "pxl_dsa_index_scores": [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "pxl_topk_select": [_P, c_int64, _P, c_int, c_int, _P, c_int64, _P],
     "pxl_store_rows": [_P, c_int64, _P, _P, c_int, c_int, c_int64, _P, _P],
+    "pxl_gemm_fp8_block": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "pxl_gemm_fp8_block_grouped": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
+                                   c_int, c_int, _P, _P],
+    "pxl_quant_fp8_rows": [_P, c_int64, _P, _P, c_int, c_int, _P],
     "pxl_argmax": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P],
     "pxl_sample": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
 }

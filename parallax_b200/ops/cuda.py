@@ -545,3 +545,50 @@ def topk_select(scores, positions, k: int):
                                      _stream(scores.device)), "pxl_topk_select")
     _count()
     return out
+
+
+# ---------------------------------------------------------------------------- block-scaled fp8
+def quant_fp8_rows(x: torch.Tensor):
+    """bf16 ``[T, K]`` -> (e4m3 ``[T, K]``, fp32 scales ``[T, K/128]``)."""
+    T, K = x.shape
+    q = torch.empty((T, K), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((T, K // 128), dtype=torch.float32, device=x.device)
+    check(_lib.lib().pxl_quant_fp8_rows(x.data_ptr(), x.stride(0), q.data_ptr(), s.data_ptr(), T, K, _stream(x.device)),
+          "pxl_quant_fp8_rows")
+    _count()
+    return q, s
+
+
+def linear_fp8(x: torch.Tensor, wq: torch.Tensor, w_s64: torch.Tensor, residual: Optional[torch.Tensor] = None,
+               epi: int = EPI_NONE) -> torch.Tensor:
+    """``x [T, K]`` bf16 times block-scaled e4m3 weights ``wq [N, K]`` (scales ``[N/64, K/128]``)."""
+    T, K = x.shape
+    N = wq.shape[0]
+    if residual is not None:
+        epi = _lib.EPI_RESIDUAL
+    xq, xs = quant_fp8_rows(x)
+    n_out = N // 2 if epi == EPI_SILU_MUL else N
+    out = torch.empty((T, n_out), dtype=torch.bfloat16, device=x.device)
+    check(_lib.lib().pxl_gemm_fp8_block(xq.data_ptr(), xs.data_ptr(), wq.data_ptr(), w_s64.data_ptr(), out.data_ptr(),
+                                        _ptr(residual), T, N, K, xq.stride(0), wq.stride(0), out.stride(0), epi,
+                                        status_tensor(x.device).data_ptr(), _stream(x.device)), "pxl_gemm_fp8_block")
+    _count()
+    return out
+
+
+def grouped_linear_fp8(a: torch.Tensor, wq: torch.Tensor, w_s64: torch.Tensor, plan, num_local_experts: int,
+                       epi: int = EPI_NONE) -> torch.Tensor:
+    """Expert-sorted rows ``a [P, K]`` bf16 times stacked e4m3 expert weights ``wq [E*N, K]``."""
+    P, K = a.shape
+    N = wq.shape[0] // num_local_experts
+    aq, a_s = quant_fp8_rows(a)
+    n_out = N // 2 if epi == EPI_SILU_MUL else N
+    out = torch.empty((P, n_out), dtype=torch.bfloat16, device=a.device)
+    check(_lib.lib().pxl_gemm_fp8_block_grouped(aq.data_ptr(), a_s.data_ptr(), wq.data_ptr(), w_s64.data_ptr(),
+                                                out.data_ptr(), P, num_local_experts, N, K, aq.stride(0), wq.stride(0),
+                                                out.stride(0), plan.mt_expert.data_ptr(), plan.mt_row0.data_ptr(),
+                                                plan.mt_row_end.data_ptr(), plan.num_mt.data_ptr(), plan.max_mt, epi,
+                                                status_tensor(a.device).data_ptr(), _stream(a.device)),
+          "pxl_gemm_fp8_block_grouped")
+    _count()
+    return out

@@ -419,3 +419,30 @@ def topk_select(scores, positions, k: int):
         if n > k:
             out[t] = torch.topk(scores[t, :n], k).indices.to(torch.int32)
     return out
+
+
+# ---------------------------------------------------------------------------- block-scaled fp8
+def quant_fp8_rows(x):
+    from parallax_b200.loader.quant import quantize_fp8_rows
+
+    return quantize_fp8_rows(x, 128)
+
+
+def _dequant_w64(wq, w_s64):
+    N, K = wq.shape
+    s = w_s64.float().repeat_interleave(64, dim=0)[:N].repeat_interleave(128, dim=1)[:, :K]
+    return wq.float() * s
+
+
+def linear_fp8(x, wq, w_s64, residual=None, epi: int = EPI_NONE):
+    """Same contraction as the fp8 kernel: activations are rounded to e4m3 per 1x128 group."""
+    xq, xs = quant_fp8_rows(x)
+    xd = xq.float() * xs.repeat_interleave(128, dim=1)[:, : x.shape[1]]
+    y = xd @ _dequant_w64(wq, w_s64).t()
+    if epi == EPI_SILU_MUL:
+        N = wq.shape[0]
+        yg = y.view(-1, N // 128, 2, 64)
+        y = (torch.nn.functional.silu(yg[:, :, 0]) * yg[:, :, 1]).reshape(-1, N // 2)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
