@@ -130,6 +130,8 @@ class DeepseekStage(DecoderStage):
             else:
                 lw.w_gu = ops.interleave_gate_up(rnd(I, Hd, layer_seed=s + 6), rnd(I, Hd, layer_seed=s + 7))
                 lw.w_down = rnd(Hd, I, layer_seed=s + 8)
+        if cfg.quant_method == "fp8":
+            self.quantize_fp8()
 
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
         cfg, dev, dt = self.cfg, self.device, self.dtype
@@ -179,6 +181,33 @@ class DeepseekStage(DecoderStage):
             else:
                 lw.w_gu = ops.interleave_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"))
                 lw.w_down = get(p + "mlp.down_proj.weight").contiguous()
+        if cfg.quant_method == "fp8":
+            self.quantize_fp8()
+
+    def quantize_fp8(self) -> None:
+        """Keep the large projections (q_b, o, dense FFN, experts) as block-scaled e4m3; the narrow
+        down-projections into the latents, norms, router and embeddings stay bf16."""
+        from parallax_b200.loader.quant import quantize_fp8_block
+
+        for lw in self.layers:
+            for name in ("w_q_b", "w_o", "w_gu", "w_down"):
+                w = getattr(lw, name)
+                if isinstance(w, torch.Tensor) and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+                    setattr(lw, name, quantize_fp8_block(w, (64, 128)))
+            if lw.moe is not None and lw.moe.fp8 is None:
+                lw.moe.quantize_fp8()
+        self.fp8 = True
+
+    @staticmethod
+    def _lin(x, w, residual=None, epi=ops.EPI_NONE):
+        if isinstance(w, tuple):
+            return ops.linear_fp8(x, w[0], w[1], residual=residual, epi=epi)
+        return ops.linear(x, w, residual=residual, epi=epi)
+
+    def _mlp(self, lw, xn, h):
+        if lw.moe is not None:
+            return lw.moe.forward(xn, h)
+        return self._lin(self._lin(xn, lw.w_gu, epi=ops.EPI_SILU_MUL), lw.w_down, residual=h)
 
     def update_weights(self, tensors) -> int:
         raise NotImplementedError("online weight refit is implemented for the GQA decoder families")
@@ -197,6 +226,9 @@ class DeepseekStage(DecoderStage):
                 v = getattr(lw, s)
                 if isinstance(v, torch.Tensor):
                     add(v)
+                elif isinstance(v, tuple):
+                    for t in v:
+                        add(t)
                 elif v is not None and hasattr(v, "tensors"):
                     for t in v.tensors():
                         add(t)
@@ -241,7 +273,7 @@ class DeepseekStage(DecoderStage):
             qr = ops.rmsnorm(ops.linear(xn, lw.w_q_a), lw.q_a_norm, eps)
         else:
             qr = xn
-        q = ops.linear(qr, lw.w_q_b)
+        q = self._lin(qr, lw.w_q_b)
         kv = ops.linear(xn, lw.w_kv_a)
         cache = self.kv_caches[li].k
         ops.mla_kv_prep(kv[:, :lw.n_kv_a], lw.kv_a_norm, self.cos_sin, fb.positions, fb.slot_mapping, cache, eps, self.L)
@@ -265,7 +297,7 @@ class DeepseekStage(DecoderStage):
         for li, lw in enumerate(self.layers):
             xn = ops.rmsnorm(h, lw.ln1, eps)
             a, topk = self._attention(lw, li, xn, fb, topk)
-            h = ops.linear(a.contiguous(), lw.w_o, residual=h)
+            h = self._lin(a.contiguous(), lw.w_o, residual=h)
             xn = ops.rmsnorm(h, lw.ln2, eps)
             h = self._mlp(lw, xn, h)
         return h

@@ -31,13 +31,28 @@ class MoEWeights:
         self.shared_gu: Optional[torch.Tensor] = None   # [2*Is, H] interleaved
         self.shared_down: Optional[torch.Tensor] = None  # [H, Is]
         self.shared_gate: Optional[torch.Tensor] = None  # [1, H] sigmoid gate on the shared expert (Qwen2-MoE style)
+        self.fp8: Optional[dict] = None                 # block-scaled e4m3 copies: name -> (q, scales per 64 rows)
         self.num_experts = cfg.num_experts
         self.top_k = cfg.num_experts_per_tok
         self.mode = 1 if cfg.scoring_func == "sigmoid" else 0
 
     def tensors(self):
-        return [t for t in (self.router, self.e_bias, self.w1, self.w2, self.shared_gu, self.shared_down,
-                            self.shared_gate) if t is not None]
+        ts = [t for t in (self.router, self.e_bias, self.w1, self.w2, self.shared_gu, self.shared_down,
+                          self.shared_gate) if t is not None]
+        for q, s in (self.fp8 or {}).values():
+            ts += [q, s]
+        return ts
+
+    def quantize_fp8(self) -> None:
+        """Replace the expert (and shared-expert) matrices by e4m3 + scales per 64 x 128 block."""
+        from parallax_b200.loader.quant import quantize_fp8_block
+
+        self.fp8 = {}
+        for name in ("w1", "w2", "shared_gu", "shared_down"):
+            w = getattr(self, name)
+            if w is not None:
+                self.fp8[name] = quantize_fp8_block(w, (64, 128))
+                setattr(self, name, None)
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -97,6 +112,12 @@ class MoEWeights:
         """Returns ``h + MoE(xn)`` (the residual add is fused into the combine / shared-expert GEMM)."""
         ids, w = self.route(xn)
         base = h
+        if self.fp8 is not None:
+            f = self.fp8
+            if "shared_gu" in f:
+                act = ops.linear_fp8(xn, *f["shared_gu"], epi=ops.EPI_SILU_MUL)
+                base = ops.linear_fp8(act, *f["shared_down"], residual=h)
+            return ops.moe_ffn_fp8(xn, ids, w, *f["w1"], *f["w2"], self.num_experts, base=base)
         if self.shared_gu is not None:
             act = ops.linear(xn, self.shared_gu, epi=ops.EPI_SILU_MUL)
             if self.shared_gate is None:

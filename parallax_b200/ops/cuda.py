@@ -592,3 +592,12 @@ def grouped_linear_fp8(a: torch.Tensor, wq: torch.Tensor, w_s64: torch.Tensor, p
           "pxl_gemm_fp8_block_grouped")
     _count()
     return out
+
+
+def moe_ffn_fp8(x, ids, weights, w1q, w1s, w2q, w2s, num_experts: int, base=None):
+    """:func:`moe_ffn` with block-scaled e4m3 expert weights (activations quantised per 1x128 group)."""
+    plan = moe_align(ids, num_experts)
+    xp = moe_gather(x, plan)
+    act = grouped_linear_fp8(xp, w1q, w1s, plan, num_experts, epi=EPI_SILU_MUL)
+    y = grouped_linear_fp8(act, w2q, w2s, plan, num_experts)
+    return moe_combine(y, plan, weights, base, x.shape[0])

@@ -446,3 +446,17 @@ def linear_fp8(x, wq, w_s64, residual=None, epi: int = EPI_NONE):
     if residual is not None:
         y = y + residual.float()
     return y.to(x.dtype)
+
+
+def moe_ffn_fp8(x, ids, weights, w1q, w1s, w2q, w2s, num_experts: int, base=None):
+    T, H = x.shape
+    n1, n2 = w1q.shape[0] // num_experts, w2q.shape[0] // num_experts
+    out = torch.zeros(T, n2, dtype=torch.float32) if base is None else base.float().clone()
+    for e in range(num_experts):
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        a = linear_fp8(x[tok], w1q[e * n1:(e + 1) * n1], w1s[e * n1 // 64:(e + 1) * n1 // 64], epi=EPI_SILU_MUL)
+        y = linear_fp8(a, w2q[e * n2:(e + 1) * n2], w2s[e * n2 // 64:(e + 1) * n2 // 64])
+        out.index_add_(0, tok, y.float() * weights[tok, slot].float()[:, None])
+    return out.to(x.dtype)

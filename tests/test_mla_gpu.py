@@ -130,13 +130,15 @@ def test_dsa_scores_topk_store():
     cu.check_status(dev)
 
 
-@pytest.mark.parametrize("name", ["small-mla", "small-dsa"])
+@pytest.mark.parametrize("name", ["small-mla", "small-dsa", "small-dsa/fp8"])
 def test_deepseek_engine_gpu_matches_cpu(name):
     from parallax_b200.engine.engine import Engine
     from parallax_b200.engine.request import Request, SamplingParams
     from parallax_b200.ops import cuda as cu
 
-    cfg = named_config(name)
+    cfg = named_config(name.split("/")[0])
+    if name.endswith("/fp8"):
+        cfg.quant_method = "fp8"      # large projections and experts as block-scaled e4m3
     kw = dict(num_blocks=128, page_size=16, max_batch_size=4, max_num_tokens_per_batch=512, chunked_prefill_size=96,
               max_total_length=512, seed=0)
     g = torch.Generator().manual_seed(5)
@@ -145,19 +147,25 @@ def test_deepseek_engine_gpu_matches_cpu(name):
     def clone_weights(src, dst):
         """Give the fp32 CPU stage the bf16-rounded weights of the GPU stage."""
         def conv(t):
-            return t.detach().cpu().float() if t.is_floating_point() else t.detach().cpu()
+            if isinstance(t, tuple):
+                return tuple(conv(x) for x in t)
+            if t.dtype in (torch.bfloat16, torch.float16):
+                return t.detach().cpu().float()
+            return t.detach().cpu()
         for name in ("embed", "norm_w", "lm_head"):
             if getattr(src, name) is not None:
                 setattr(dst, name, conv(getattr(src, name)))
         for ls, ld in zip(src.layers, dst.layers):
             for slot in type(ls).__slots__:
                 v = getattr(ls, slot)
-                if isinstance(v, torch.Tensor):
+                if isinstance(v, (torch.Tensor, tuple)):
                     setattr(ld, slot, conv(v))
                 elif slot == "moe" and v is not None:
                     for k2, t in vars(v).items():
                         if isinstance(t, torch.Tensor):
                             setattr(ld.moe, k2, conv(t))
+                        elif k2 == "fp8" and t is not None:
+                            ld.moe.fp8 = {k3: conv(p) for k3, p in t.items()}
 
     gpu_stage = []
 
