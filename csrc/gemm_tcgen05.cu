@@ -43,7 +43,7 @@ constexpr int kRsLinePitch = 144;
 constexpr int kRsStageBytes = BM * kRsLinePitch;
 template <int BN, int EPI>
 constexpr int gemm_smem_bytes() {
-  return GemmCfg<BN>::SMEM_BYTES + (EPI == PXL_EPI_RS ? kRsStageBytes : 0);
+  return GemmCfg<BN>::SMEM_BYTES + ((EPI == PXL_EPI_RS || EPI == PXL_EPI_SCATTER) ? kRsStageBytes : 0);
 }
 
 struct GemmEpilogueArgs {
@@ -52,6 +52,8 @@ struct GemmEpilogueArgs {
   const bf16* bias;      // optional, length N (pre-activation columns)
   float* C_f32;          // EPI_F32 output
   int ldc;
+  bf16* const* row_ptrs; // EPI_SCATTER: destination of every output row (null = drop), N elements each
+  uint32_t* done_counter;  // EPI_SCATTER: local counter for the "last CTA publishes the flags" step
 };
 
 // Grouped (per-expert) mode: the m-tiles are listed on the device, one entry per 128-row
@@ -393,15 +395,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
         }
-      } else if constexpr (EPI == PXL_EPI_RS) {
-        // Partial sums go to the staging slot [this rank] of the rank that owns the rows. Each
-        // lane packs 64 columns of its row into its private 128-byte line of shared memory and
+      } else if constexpr (EPI == PXL_EPI_RS || EPI == PXL_EPI_SCATTER) {
+        // RS: partial sums go to the staging slot [this rank] of the rank that owns the rows.
+        // SCATTER: every row has its own destination (a row of a peer's combine buffer).
+        // Each lane packs 64 columns of its row into its private 128-byte line of shared memory and
         // ships the line with one bulk store: NVLink sees 128-byte writes instead of 16-byte ones.
         const int col0 = n_blk * BN;
-        const int owner = row / comm.rows_per_rank;
-        const int lrow = row - owner * comm.rows_per_rank;
-        bf16* dst_row = comm.stage[owner] +
-                        (static_cast<size_t>(comm.rank) * comm.rows_per_rank + lrow) * ep.ldc + col0;
+        bf16* dst_row;
+        if constexpr (EPI == PXL_EPI_RS) {
+          const int owner = row / comm.rows_per_rank;
+          const int lrow = row - owner * comm.rows_per_rank;
+          dst_row = comm.stage[owner] +
+                    (static_cast<size_t>(comm.rank) * comm.rows_per_rank + lrow) * ep.ldc + col0;
+        } else {
+          dst_row = row < M_end ? ep.row_ptrs[row] : nullptr;
+          if (dst_row != nullptr) dst_row += col0;
+        }
         const uint32_t line = smem_u32(rs_stage) + (q * 32 + lane) * kRsLinePitch;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 64) {
@@ -426,7 +435,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          : "memory");
           }
           fence_proxy_async_smem();
-          if (row < M_end && col0 + c0 < N) bulk_store_s2g(dst_row + c0, line, 128);
+          if (row < M_end && col0 + c0 < N && dst_row != nullptr) bulk_store_s2g(dst_row + c0, line, 128);
           bulk_commit();
         }
       } else {
@@ -496,6 +505,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+    if constexpr (EPI == PXL_EPI_SCATTER) {
+      // every row of this CTA is on its way: the CTA that finishes last tells all peers
+      bulk_wait_all();
+      __threadfence_system();
+      named_bar_sync(1, 128);
+      if (threadIdx.x == 64) {
+        const uint32_t old = atomicAdd(ep.done_counter, 1u);
+        if (old == gridDim.x - 1) {
+          *ep.done_counter = 0;
+          __threadfence_system();
+          for (int r = 0; r < comm.tp; ++r) st_release_sys_u32(comm.flags[r] + comm.rank, comm.epoch);
+        }
+      }
     }
   }
 
@@ -618,6 +641,7 @@ int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const Ge
     PXL_GEMM_CASE(PXL_EPI_SILU_MUL);
     PXL_GEMM_CASE(PXL_EPI_F32);
     PXL_GEMM_CASE(PXL_EPI_RS);
+    PXL_GEMM_CASE(PXL_EPI_SCATTER);
     default: return PXL_ERR_INVALID_ARG;
   }
 #undef PXL_GEMM_CASE
@@ -657,7 +681,7 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
     return PXL_ERR_TENSORMAP;
   if (!pxl_host::make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, ldw, bn, BK))
     return PXL_ERR_TENSORMAP;
-  GemmEpilogueArgs ep;
+  GemmEpilogueArgs ep{};
   ep.C = static_cast<pxl::bf16*>(C);
   ep.C_f32 = static_cast<float*>(C);
   ep.residual = static_cast<const pxl::bf16*>(residual);
@@ -693,7 +717,7 @@ PXL_EXPORT int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int 
   if (!pxl_host::make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W,
                               static_cast<uint64_t>(E) * N, K, ldw, bn, BK))
     return PXL_ERR_TENSORMAP;
-  GemmEpilogueArgs ep;
+  GemmEpilogueArgs ep{};
   ep.C = static_cast<pxl::bf16*>(C);
   ep.C_f32 = static_cast<float*>(C);
   ep.residual = nullptr;
@@ -707,6 +731,39 @@ PXL_EXPORT int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int 
     case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, GemmCommArgs{}, max_tiles, P, N, K, status, stream);
     default: return PXL_ERR_INVALID_ARG;
   }
+}
+
+
+// Grouped GEMM whose output rows leave through per-row pointers (expert-parallel combine fused
+// into the down projection): row i of the expert-sorted result is stored to row_ptrs[i] (N bf16,
+// 16-byte aligned, may be peer memory; null = drop). When the whole grid is done, flag_ptrs[r][rank]
+// of every rank r is set to `epoch` (release, system scope).
+PXL_EXPORT int pxl_gemm_bf16_grouped_scatter(const void* A, const void* W, void* const* row_ptrs, int P, int E,
+                                             int N, int K, int lda, int ldw, const int* mt_expert,
+                                             const int* mt_row0, const int* mt_row_end, const int* num_mt,
+                                             int max_m_tiles, void* const* flag_ptrs, uint32_t* done_counter,
+                                             int rank, int ep_size, uint32_t epoch, int* status,
+                                             cudaStream_t stream) {
+  if (P <= 0 || E <= 0 || N <= 0 || K <= 0 || max_m_tiles <= 0) return PXL_ERR_INVALID_ARG;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || (N % 128)) return PXL_ERR_INVALID_ARG;
+  if (ep_size < 1 || ep_size > 8 || rank < 0 || rank >= ep_size) return PXL_ERR_INVALID_ARG;
+  const int bn = 128;
+  CUtensorMap ta, tb;
+  if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, P, K, lda, BM, BK))
+    return PXL_ERR_TENSORMAP;
+  if (!pxl_host::make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, static_cast<uint64_t>(E) * N, K, ldw, bn, BK))
+    return PXL_ERR_TENSORMAP;
+  GemmEpilogueArgs ep{};
+  ep.ldc = N;
+  ep.row_ptrs = reinterpret_cast<pxl::bf16* const*>(row_ptrs);
+  ep.done_counter = done_counter;
+  GemmCommArgs comm{};
+  for (int i = 0; i < ep_size; ++i) comm.flags[i] = static_cast<uint32_t*>(flag_ptrs[i]);
+  comm.rank = rank;
+  comm.tp = ep_size;
+  comm.epoch = epoch;
+  GemmGroupArgs grp{mt_expert, mt_row0, mt_row_end, num_mt, N};
+  return dispatch_epi<128>(PXL_EPI_SCATTER, ta, tb, ep, grp, comm, max_m_tiles * (N / bn), P, N, K, status, stream);
 }
 
 namespace {

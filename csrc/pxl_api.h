@@ -23,6 +23,7 @@ typedef struct CUstream_st* pxl_stream_t;
 #define PXL_EPI_SILU_MUL 2  // C[:, j] = silu(gate_j) * up_j          bf16 out, N/2 columns
 #define PXL_EPI_F32 3       // C = A W^T (+bias)                      fp32 out
 #define PXL_EPI_RS 4        // partial sums scattered to the owning rank + reduce (pxl_gemm_bf16_rs)
+#define PXL_EPI_SCATTER 5   // every output row stored through its own pointer, possibly on a peer GPU
 
 // ---- gemm_tcgen05.cu -------------------------------------------------------
 // C[M,N] = A[M,K] * W[N,K]^T. lda/ldw/ldc in elements. `bn` = tile width (64/128/256)
@@ -173,6 +174,24 @@ int pxl_gemm_fp8_block_grouped(const void* A, const float* a_s, const void* W, c
                                int epi, int* status, pxl_stream_t stream);
 // x [T,K] bf16 (row stride ld) -> q [T,K] e4m3 + scales [T, K/128]: x ~= q * scale per group
 int pxl_quant_fp8_rows(const void* x, int64_t ld, void* q, float* scales, int T, int K, pxl_stream_t stream);
+
+// ---- moe_ep.cu + the scatter epilogue of gemm_tcgen05.cu: expert parallelism over peer memory ----
+int pxl_ep_dispatch(const void* x, int64_t ldx, const int* ids, int n_rows, int k, int H,
+                    int experts_per_rank, int cap, int rank, int ep, void* const* recv_x_ptrs,
+                    void* const* recv_meta_ptrs, void* const* recv_cnt_ptrs, void* const* flag_ptrs,
+                    int* cursor, uint32_t* done_counter, uint32_t epoch, int* status, pxl_stream_t stream);
+int pxl_ep_recv_ids(const int* recv_meta, const int* recv_cnt, const void* disp_flag, int ep, int cap,
+                    uint32_t epoch, int* ids_out, int* status, pxl_stream_t stream);
+int pxl_ep_row_ptrs(const int* src_slot, const int* n_rows, const int* recv_meta, int cap, int H, int ep,
+                    void* const* comb_ptrs, void** row_ptrs, int max_rows, pxl_stream_t stream);
+int pxl_gemm_bf16_grouped_scatter(const void* A, const void* W, void* const* row_ptrs, int P, int E, int N,
+                                  int K, int lda, int ldw, const int* mt_expert, const int* mt_row0,
+                                  const int* mt_row_end, const int* num_mt, int max_m_tiles,
+                                  void* const* flag_ptrs, uint32_t* done_counter, int rank, int ep_size,
+                                  uint32_t epoch, int* status, pxl_stream_t stream);
+int pxl_ep_combine(const void* comb, const float* w, const void* base, int64_t ld_base, void* out,
+                   int64_t ld_out, const void* ret_flag, int ep, uint32_t epoch, int n_rows, int k, int H,
+                   int* status, pxl_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,175 @@
+"""Expert-parallel MoE layer over NVLink peer memory (the kernels of ``csrc/moe_ep.cu`` plus the
+scatter epilogue of the grouped tcgen05 GEMM).
+
+Each rank of the group owns ``E / ep`` consecutive experts and a slice of the batch's token
+rows. ``ep_moe_ffn`` routes nothing itself: it takes the rows, their expert ids and weights,
+pushes every (row, slot) pair to the rank that owns the expert, runs the two grouped GEMMs
+there and returns the expert outputs to the rank the row came from - the return trip is the
+epilogue of the down projection, which stores each output row through a pointer into the source
+rank's combine buffer. ``ep_moe_ffn_nccl`` is the library baseline (all-to-all of padded
+buffers) that the benchmark compares against; it is not used for serving.
+
+The reference runs with expert parallelism switched off
+(``src/parallax/sglang/model_runner.py:394-395``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_int64, c_uint32, c_void_p as P
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from parallax_b200.ops import _lib, cuda as cu
+from parallax_b200.ops._lib import EPI_SILU_MUL, check
+from parallax_b200.parallel.symm import SymmBuffer
+
+_bound = {}
+
+
+def _fn(name, argtypes):
+    if name not in _bound:
+        _bound[name] = _lib.bind(name, argtypes)
+    return _bound[name]
+
+
+def _dispatch_fn():
+    return _fn("pxl_ep_dispatch", [P, c_int64, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P,
+                                   c_uint32, P, P])
+
+
+def _recv_ids_fn():
+    return _fn("pxl_ep_recv_ids", [P, P, P, c_int, c_int, c_uint32, P, P, P])
+
+
+def _row_ptrs_fn():
+    return _fn("pxl_ep_row_ptrs", [P, P, P, c_int, c_int, c_int, P, P, c_int, P])
+
+
+def _scatter_fn():
+    return _fn("pxl_gemm_bf16_grouped_scatter", [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P, P, c_int,
+                                                 P, P, c_int, c_int, c_uint32, P, P])
+
+
+def _combine_fn():
+    return _fn("pxl_ep_combine", [P, P, P, c_int64, P, c_int64, P, c_int, c_uint32, c_int, c_int, c_int, P, P])
+
+
+class EPWorkspace:
+    """Symmetric receive / combine buffers of one expert-parallel group."""
+
+    def __init__(self, group, device: torch.device, ep: int, rank: int, max_rows_per_rank: int, top_k: int,
+                 hidden: int):
+        self.group, self.device, self.ep, self.rank = group, device, ep, rank
+        self.max_rows, self.k, self.H = max_rows_per_rank, top_k, hidden
+        self.cap = max_rows_per_rank * top_k          # worst case: every pair of one source lands on one rank
+        n_recv = ep * self.cap
+        self.off_recv_x = 0
+        self.off_comb = self.off_recv_x + n_recv * hidden * 2
+        self.off_meta = self.off_comb + self.cap * hidden * 2
+        self.off_cnt = self.off_meta + n_recv * 8
+        self.off_dflag = self.off_cnt + 64
+        self.off_rflag = self.off_dflag + 64
+        total = self.off_rflag + 64
+        self.buf = SymmBuffer(total, group, device)
+        self.recv_x = self.buf.view(self.off_recv_x, (n_recv, hidden), torch.bfloat16)
+        self.comb = self.buf.view(self.off_comb, (self.cap, hidden), torch.bfloat16)
+        self.recv_meta = self.buf.view(self.off_meta, (n_recv, 2), torch.int32)
+        self.recv_cnt = self.buf.view(self.off_cnt, (16,), torch.int32)
+        self.disp_flag = self.buf.view(self.off_dflag, (16,), torch.int32)
+        self.ret_flag = self.buf.view(self.off_rflag, (16,), torch.int32)
+        # local scratch
+        self.cursor = torch.zeros(16, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(4, dtype=torch.int32, device=device)
+        self.ids_local = torch.empty(n_recv, dtype=torch.int32, device=device)
+        self.row_ptrs = torch.zeros(n_recv + 256, dtype=torch.int64, device=device)
+        self.epoch = 0
+        self._p = {name: self.buf.ptr_array(off) for name, off in
+                   (("recv_x", self.off_recv_x), ("comb", self.off_comb), ("meta", self.off_meta),
+                    ("cnt", self.off_cnt), ("dflag", self.off_dflag), ("rflag", self.off_rflag))}
+
+
+def ep_moe_ffn(ws: EPWorkspace, x: torch.Tensor, n_valid: int, ids: torch.Tensor, weights: torch.Tensor,
+               w1: torch.Tensor, w2: torch.Tensor, experts_per_rank: int, base: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[:n_valid] = base + sum_j weights[:, j] * FFN_{ids[:, j]}(x)`` for this rank's rows.
+
+    x ``[rows, H]``, ids/weights ``[rows, k]`` (global expert ids); w1 ``[E_local * 2I, H]``
+    (gate/up interleaved), w2 ``[E_local * H, I]`` hold this rank's experts only."""
+    dev = x.device
+    H, k = ws.H, ws.k
+    assert x.shape[1] == H and ids.shape[1] == k and n_valid <= ws.max_rows
+    ws.epoch += 1
+    epoch = ws.epoch
+    st = cu.status_tensor(dev).data_ptr()
+    stream = cu._stream(dev)
+    check(_dispatch_fn()(x.data_ptr(), x.stride(0), ids.data_ptr(), n_valid, k, H, experts_per_rank, ws.cap, ws.rank,
+                         ws.ep, ws._p["recv_x"], ws._p["meta"], ws._p["cnt"], ws._p["dflag"], ws.cursor.data_ptr(),
+                         ws.counters[0:].data_ptr(), epoch, st, stream), "pxl_ep_dispatch")
+    check(_recv_ids_fn()(ws.recv_meta.data_ptr(), ws.recv_cnt.data_ptr(), ws.disp_flag.data_ptr(), ws.ep, ws.cap,
+                         epoch, ws.ids_local.data_ptr(), st, stream), "pxl_ep_recv_ids")
+    cu._count(2)
+    plan = cu.moe_align(ws.ids_local.view(-1, 1), experts_per_rank)
+    xp = cu.moe_gather(ws.recv_x, plan)
+    act = cu.grouped_linear(xp, w1, plan, experts_per_rank, epi=EPI_SILU_MUL)
+    n_rows_dev = plan.offsets[plan.n_local:]
+    check(_row_ptrs_fn()(plan.src_tok.data_ptr(), n_rows_dev.data_ptr(), ws.recv_meta.data_ptr(), ws.cap, H, ws.ep,
+                         ws._p["comb"], ws.row_ptrs.data_ptr(), plan.max_rows, stream), "pxl_ep_row_ptrs")
+    N = w2.shape[0] // experts_per_rank
+    check(_scatter_fn()(act.data_ptr(), w2.data_ptr(), ws.row_ptrs.data_ptr(), act.shape[0], experts_per_rank, N,
+                        act.shape[1], act.stride(0), w2.stride(0), plan.mt_expert.data_ptr(), plan.mt_row0.data_ptr(),
+                        plan.mt_row_end.data_ptr(), plan.num_mt.data_ptr(), plan.max_mt, ws._p["rflag"],
+                        ws.counters[1:].data_ptr(), ws.rank, ws.ep, epoch, st, stream),
+          "pxl_gemm_bf16_grouped_scatter")
+    if out is None:
+        out = torch.empty_like(x)
+    check(_combine_fn()(ws.comb.data_ptr(), weights.data_ptr(), None if base is None else base.data_ptr(),
+                        0 if base is None else base.stride(0), out.data_ptr(), out.stride(0), ws.ret_flag.data_ptr(),
+                        ws.ep, epoch, n_valid, k, H, st, stream), "pxl_ep_combine")
+    cu._count(3)
+    return out
+
+
+def ep_moe_ffn_nccl(group, x: torch.Tensor, n_valid: int, ids: torch.Tensor, weights: torch.Tensor, w1, w2,
+                    experts_per_rank: int, base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Library baseline with the same sharding: all-gather rows and routing, every rank applies
+    its own experts to all rows (others masked out), reduce-scatter of the partial sums."""
+    ep = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    rows, H = x.shape
+    k = ids.shape[1]
+    xa = torch.empty((ep * rows, H), dtype=x.dtype, device=x.device)
+    ia = torch.empty((ep * rows, k), dtype=ids.dtype, device=x.device)
+    wa = torch.empty((ep * rows, k), dtype=weights.dtype, device=x.device)
+    valid = torch.zeros(rows, dtype=torch.int32, device=x.device)
+    valid[:n_valid] = 1
+    va = torch.empty(ep * rows, dtype=torch.int32, device=x.device)
+    dist.all_gather_into_tensor(xa, x.contiguous(), group=group)
+    dist.all_gather_into_tensor(ia, ids.contiguous(), group=group)
+    dist.all_gather_into_tensor(wa, weights.contiguous(), group=group)
+    dist.all_gather_into_tensor(va, valid, group=group)
+    lo = rank * experts_per_rank
+    local = (ia >= lo) & (ia < lo + experts_per_rank) & (va[:, None] > 0)
+    ids_l = torch.where(local, ia - lo, torch.full_like(ia, -1))
+    from parallax_b200 import ops
+
+    if x.is_cuda:
+        plan = cu.moe_align(ids_l.contiguous(), experts_per_rank)
+        xp = cu.moe_gather(xa, plan)
+        act = cu.grouped_linear(xp, w1, plan, experts_per_rank, epi=EPI_SILU_MUL)
+        y = cu.grouped_linear(act, w2, plan, experts_per_rank)
+        part = cu.moe_combine(y, plan, wa.float().contiguous(), None, ep * rows).float()
+    else:
+        wl = torch.where(local, wa.float(), torch.zeros_like(wa, dtype=torch.float32))
+        part = ops.reference.moe_ffn(xa, ids_l.clamp_min(0), wl, w1, w2, experts_per_rank).float()
+    if x.is_cuda:
+        outp = torch.empty((rows, H), dtype=torch.float32, device=x.device)
+        dist.reduce_scatter_tensor(outp, part.contiguous(), group=group)
+    else:
+        dist.all_reduce(part, group=group)
+        outp = part[rank * rows:(rank + 1) * rows]
+    if base is not None:
+        outp = outp + base.float()
+    return outp.to(x.dtype)

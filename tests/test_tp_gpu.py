@@ -50,3 +50,14 @@ def test_dist_engine_pipeline_two_stages(tmp_path):
     """pp=2 over NCCL send/recv with two micro-batches in flight: same tokens as one GPU."""
     r = _run_dist("pp", tmp_path, 29521)
     assert r["token_agreement"] > 0.95, r
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_moe_two_ranks():
+    """Dispatch / grouped GEMMs / combine-in-epilogue over peer memory against fp32 math."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29523", os.path.join(ROOT, "benchmarks", "bench_fused_ep.py"), "--check-only"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert '"kernel": "ep_moe_ffn"' in res.stdout
