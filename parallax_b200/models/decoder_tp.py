@@ -33,7 +33,7 @@ class TPDecoderStage(DecoderStage):
         self.comm = comm
         if cfg.num_attention_heads % tp_size or cfg.num_key_value_heads % tp_size:
             raise ValueError("attention heads must divide by the tensor-parallel size")
-        if cfg.intermediate_size % (64 * tp_size):
+        if not cfg.is_moe and cfg.intermediate_size % (64 * tp_size):
             raise ValueError("intermediate size must divide by 64 * tp")
         self.hq_l = cfg.num_attention_heads // tp_size
         self.hkv_l = cfg.num_key_value_heads // tp_size
@@ -56,7 +56,7 @@ class TPDecoderStage(DecoderStage):
         hq, hkv, il = self.hq_l, self.hkv_l, I // tp
         for lw in self.layers:
             if lw.moe is not None:
-                raise NotImplementedError("MoE layers use expert parallelism, not tensor parallelism")
+                lw.moe.shard_experts(r, tp)     # expert parallelism over the same group
             q, k, v = lw.w_qkv.split([Hq * D, Hkv * D, Hkv * D], dim=0)
             lw.w_qkv = torch.cat([q[r * hq * D:(r + 1) * hq * D], k[r * hkv * D:(r + 1) * hkv * D],
                                   v[r * hkv * D:(r + 1) * hkv * D]], dim=0).contiguous()
@@ -65,10 +65,11 @@ class TPDecoderStage(DecoderStage):
                 lw.b_qkv = torch.cat([bq[r * hq * D:(r + 1) * hq * D], bk[r * hkv * D:(r + 1) * hkv * D],
                                       bv[r * hkv * D:(r + 1) * hkv * D]]).contiguous()
             lw.w_o = lw.w_o[:, r * hq * D:(r + 1) * hq * D].contiguous()
-            # gate/up are interleaved in groups of 64 outputs: a contiguous slice of groups is a slice of I
-            g = lw.w_gu.view(I // 64, 128, -1)
-            lw.w_gu = g[r * il // 64:(r + 1) * il // 64].reshape(2 * il, -1).contiguous()
-            lw.w_down = lw.w_down[:, r * il:(r + 1) * il].contiguous()
+            if lw.moe is None:
+                # gate/up are interleaved in groups of 64 outputs: a contiguous slice of groups is a slice of I
+                g = lw.w_gu.view(I // 64, 128, -1)
+                lw.w_gu = g[r * il // 64:(r + 1) * il // 64].reshape(2 * il, -1).contiguous()
+                lw.w_down = lw.w_down[:, r * il:(r + 1) * il].contiguous()
             if lw.sinks is not None:
                 lw.sinks = lw.sinks[r * hq:(r + 1) * hq].contiguous()
         if self.lm_head is not None:
@@ -116,6 +117,16 @@ class TPDecoderStage(DecoderStage):
                 ops.attn_decode(q[Tp:], kc, vc, fb.d_block_tables, fb.d_ctx_lens, self.scale, window=lw.window,
                                 sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:T])
             h_shard = comm.linear_rs(attn.view(T_pad, hq * D), lw.w_o, residual=h_shard)
+            if lw.moe is not None:
+                # attention is tensor parallel, the experts are expert parallel: every rank routes its
+                # own token rows and the dispatch / combine kernels move them to the experts' owners
+                Rp = h_shard.shape[0]
+                n_valid = min(max(T - self.tp_rank * Rp, 0), Rp)
+                xn = ops.rmsnorm(h_shard, lw.ln2, eps, w_offset=self.norm_offset)
+                ids, w = lw.moe.route(xn)
+                base = lw.moe.shared_base(xn, h_shard)
+                h_shard = comm.moe_ffn(xn, n_valid, ids, w, lw.moe.w1, lw.moe.w2, lw.moe.experts_per_rank, base=base)
+                continue
             act = comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, epi=ops.EPI_SILU_MUL, w_offset=self.norm_offset)
             h_shard = comm.linear_rs(act, lw.w_down, residual=h_shard)
         return h_shard

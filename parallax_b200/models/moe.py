@@ -43,6 +43,29 @@ class MoEWeights:
             ts += [q, s]
         return ts
 
+    def shard_experts(self, rank: int, ep: int) -> int:
+        """Keep only this rank's ``E / ep`` consecutive experts (router and shared expert stay
+        replicated). Returns the number of local experts."""
+        E = self.num_experts
+        if E % ep:
+            raise ValueError("the number of experts must divide by the expert-parallel size")
+        epr = E // ep
+        n1, n2 = self.w1.shape[0] // E, self.w2.shape[0] // E
+        self.w1 = self.w1[rank * epr * n1:(rank + 1) * epr * n1].contiguous()
+        self.w2 = self.w2[rank * epr * n2:(rank + 1) * epr * n2].contiguous()
+        self.experts_per_rank = epr
+        return epr
+
+    def shared_base(self, xn: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        """``h`` plus the shared expert's output (``h`` itself when the model has none)."""
+        if self.shared_gu is None:
+            return h
+        act = ops.linear(xn, self.shared_gu, epi=ops.EPI_SILU_MUL)
+        if self.shared_gate is None:
+            return ops.linear(act, self.shared_down, residual=h)
+        gate = torch.sigmoid(xn.float() @ self.shared_gate.float().t()).to(h.dtype)
+        return h + gate * ops.linear(act, self.shared_down)
+
     def quantize_fp8(self) -> None:
         """Replace the expert (and shared-expert) matrices by e4m3 + scales per 64 x 128 block."""
         from parallax_b200.loader.quant import quantize_fp8_block

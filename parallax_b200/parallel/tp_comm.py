@@ -60,6 +60,12 @@ class CollectiveTPComm:
             out = out + residual.float()
         return out.to(a.dtype)
 
+    def moe_ffn(self, xn, n_valid: int, ids, weights, w1, w2, experts_per_rank: int, base=None):
+        """Expert-parallel FFN on this rank's rows (experts sharded over the group)."""
+        from parallax_b200.parallel.ep import ep_moe_ffn_nccl
+
+        return ep_moe_ffn_nccl(self.group, xn, n_valid, ids, weights, w1, w2, experts_per_rank, base=base)
+
     def all_gather_rows(self, x_shard):
         full = torch.empty((x_shard.shape[0] * self.tp, x_shard.shape[1]), dtype=x_shard.dtype, device=x_shard.device)
         dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
@@ -79,6 +85,7 @@ class FusedTPComm(CollectiveTPComm):
         super().__init__(group, tp, rank, align=128)
         from parallax_b200.parallel.symm import TPWorkspace
 
+        self._ep_ws = None
         self.ws = TPWorkspace(group, torch.device(device), tp, rank,
                               max_rows_per_rank=padded_rows_per_rank(max_tokens, tp), max_k=max(hidden, max_k),
                               max_n=max(hidden, max_n))
@@ -94,3 +101,13 @@ class FusedTPComm(CollectiveTPComm):
         from parallax_b200.parallel import fused
 
         return fused.gemm_rs(self.ws, a, w, residual=residual)
+
+    def moe_ffn(self, xn, n_valid: int, ids, weights, w1, w2, experts_per_rank: int, base=None):
+        from parallax_b200.parallel.ep import EPWorkspace, ep_moe_ffn
+
+        if self._ep_ws is None:
+            self._ep_ws = EPWorkspace(self.group, self.ws.device, self.tp, self.rank, self.ws.max_rows,
+                                      ids.shape[1], xn.shape[1])
+        out = torch.zeros_like(xn) if n_valid < xn.shape[0] else torch.empty_like(xn)
+        return ep_moe_ffn(self._ep_ws, xn, n_valid, ids.contiguous(), weights.contiguous(), w1, w2, experts_per_rank,
+                          base=base, out=out)

@@ -2,6 +2,8 @@
 
 mode "tp": pp=1, tp=2 with the fused kernels; rank 0 compares the logits of one mixed step and
 the generated tokens with a single-GPU engine built on its own GPU.
+mode "ep": like "tp" on a two-layer Qwen3-30B-A3B-shaped MoE model: attention tensor-parallel,
+experts expert-parallel through the dispatch / combine kernels.
 mode "pp": pp=2, tp=1; the generated tokens must equal the single-GPU engine's exactly (same
 kernels in the same order, only the hand-off differs).
 """
@@ -30,7 +32,10 @@ def main() -> None:
     launcher.init_process_group(rank, world, int(os.environ["MASTER_PORT"]), "cuda")
     dev = torch.device("cuda", rank)
     cfg = named_config("qwen3-0.6b")
-    pp, tp = (1, 2) if mode == "tp" else (2, 1)
+    if mode == "ep":        # Qwen3-30B-A3B layer shapes (128 experts, top-8), two layers
+        cfg = named_config("qwen3-30b-a3b")
+        cfg.num_hidden_layers = 2
+    pp, tp = (2, 1) if mode == "pp" else (1, 2)
     kw = dict(page_size=16, num_blocks=512, max_batch_size=8, max_num_tokens_per_batch=2048, chunked_prefill_size=512,
               max_total_length=2048, seed=0)
     eng = DistEngine(cfg, pp, tp, dev, torch.bfloat16, **kw)

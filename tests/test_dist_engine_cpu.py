@@ -21,8 +21,8 @@ HELPER = os.path.join(os.path.dirname(__file__), "helpers", "dist_engine_rank.py
 PROMPTS = [[5, 9, 77, 3, 250, 12, 8], [100, 101, 102], list(range(20, 75)), [7] * 19, [1, 2, 3, 4, 5, 6, 7, 8, 9]]
 
 
-def _run_group(pp, tp, tmp_path, max_new=6, chunk=16):
-    spec = dict(model_name="tiny", pp=pp, tp=tp, device_type="cpu", num_blocks=256, page_size=16, max_batch_size=4,
+def _run_group(pp, tp, tmp_path, max_new=6, chunk=16, model="tiny"):
+    spec = dict(model_name=model, pp=pp, tp=tp, device_type="cpu", num_blocks=256, page_size=16, max_batch_size=4,
                 max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256, prompts=PROMPTS,
                 max_new=max_new, seed=0)
     world, port = pp * tp, free_port()
@@ -43,9 +43,9 @@ def _run_group(pp, tp, tmp_path, max_new=6, chunk=16):
     return json.loads(out.read_text())
 
 
-def _single(max_new=6, chunk=16):
+def _single(max_new=6, chunk=16, model="tiny"):
     torch.manual_seed(0)
-    eng = Engine(named_config("tiny"), device="cpu", num_blocks=256, page_size=16, max_batch_size=4,
+    eng = Engine(named_config(model), device="cpu", num_blocks=256, page_size=16, max_batch_size=4,
                  max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256, seed=0)
     return eng.generate(PROMPTS, SamplingParams(max_new_tokens=max_new, temperature=0.0, ignore_eos=True))
 
@@ -64,3 +64,10 @@ def test_dist_engine_matches_single_process(pp, tp, tmp_path):
     got = _run_group(pp, tp, tmp_path)
     assert got["outputs"] == want
     assert got["probe"]["device_ms"] > 0 and got["probe"]["h2d_bytes"] > 0
+
+
+def test_dist_engine_moe_expert_parallel(tmp_path):
+    """Attention tensor-parallel, experts expert-parallel over the same two ranks."""
+    want = _single(model="tiny-moe")
+    got = _run_group(1, 2, tmp_path, model="tiny-moe")
+    assert got["outputs"] == want

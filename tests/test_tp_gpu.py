@@ -61,3 +61,11 @@ def test_expert_parallel_moe_two_ranks():
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert '"kernel": "ep_moe_ffn"' in res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_dist_engine_expert_parallel_fused(tmp_path):
+    """Attention tp=2 + experts ep=2 (peer-memory dispatch/combine) against one GPU."""
+    r = _run_dist("ep", tmp_path, 29525)
+    assert r["logit_rel_err"] < 3e-2, r
+    assert r["token_agreement"] > 0.7, r
