@@ -193,6 +193,24 @@ int pxl_ep_combine(const void* comb, const float* w, const void* base, int64_t l
                    int64_t ld_out, const void* ret_flag, int ep, uint32_t epoch, int n_rows, int k, int H,
                    int* status, pxl_stream_t stream);
 
+// ---- linear_attn.cu: gated delta-net layers (per-request state slots) ---------------------------
+// y = silu(causal_conv(x)) per channel with the last K-1 inputs carried in conv_state [slots, C, K-1];
+// sequence b covers tokens [seq_cu[b], seq_cu[b+1]) and uses slot seq_slots[b]; a sequence whose
+// first token has position 0 starts from zeros.
+int pxl_causal_conv1d_silu(const void* x, int64_t ldx, const void* w, const void* bias, void* conv_state,
+                           const int* seq_cu, const int* seq_slots, const int* positions, void* out,
+                           int64_t ldo, int B, int C, int K, pxl_stream_t stream);
+// Gated delta rule over qkv [T, 2*Hk*Dk + Hv*Dv] (q | k | v), gates a, b [T, Hv] (shared row stride),
+// output gate z [T, Hv*Dv]; rec_state [slots, Hv, Dv, Dk] fp32; out [T, Hv*Dv] after the gated RMSNorm.
+int pxl_gated_delta_rule(const void* qkv, int64_t ld_qkv, const void* a, const void* b, int64_t ld_ab,
+                         const float* A_log, const float* dt_bias, const void* z, int64_t ld_z,
+                         const void* norm_w, float* rec_state, const int* seq_cu, const int* seq_slots,
+                         const int* positions, void* out, int64_t ld_out, int B, int Hk, int Hv, int Dk,
+                         int Dv, float eps, pxl_stream_t stream);
+// out = x * sigmoid(gate), rows of N elements with their own strides
+int pxl_sigmoid_gate_mul(const void* x, int64_t ldx, const void* gate, int64_t ldg, void* out, int64_t ldo,
+                         int T, int N, pxl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

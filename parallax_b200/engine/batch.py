@@ -36,6 +36,9 @@ class ForwardBatch:
     # rows whose logits are needed (last token of finished prefills + every decode row)
     logit_rows: Optional[torch.Tensor] = None     # int32 [n_logits]
     num_logits: int = 0
+    # every sequence of the step (prefill sequences, then one per decode row)
+    seq_cu: Optional[torch.Tensor] = None         # int32 [B+1] token ranges
+    seq_slots: Optional[torch.Tensor] = None      # int32 [B] request rows (state slots of linear-attention layers)
     h2d_bytes: int = 0
     # model-specific extras (e.g. linear-attention state slots)
     extras: dict = field(default_factory=dict)
@@ -52,7 +55,7 @@ class BatchBuilder:
         # int32 words: ids T, positions T, slots 2T (as int64), cu_q S+1, p_ctx S, d_ctx S,
         # logit_rows S, block tables 2*S*MB (prefill and decode parts never overlap, but keep
         # room for both so that offsets are static)
-        words = 4 * max_tokens + 4 * max_seqs + 8 + max_seqs * max_blocks_per_seq + 64
+        words = 4 * max_tokens + 6 * max_seqs + 16 + max_seqs * max_blocks_per_seq + 64
         self.capacity = words
         pin = device.type == "cuda"
         self.host = torch.empty(words, dtype=torch.int32, pin_memory=pin)
@@ -70,6 +73,7 @@ class BatchBuilder:
         d_ctx_lens: np.ndarray,
         d_tables: Optional[np.ndarray],
         logit_rows: np.ndarray,
+        seq_rows: Optional[np.ndarray] = None,
     ) -> ForwardBatch:
         T = int(positions.shape[0])
         Bp, Bd = len(p_q_lens), int(d_ctx_lens.shape[0])
@@ -103,6 +107,12 @@ class BatchBuilder:
             spans["d_ctx"] = put(d_ctx_lens.astype(np.int32, copy=False))
             spans["d_bt"] = put(d_tables.astype(np.int32, copy=False))
         spans["rows"] = put(logit_rows.astype(np.int32, copy=False))
+        if seq_rows is not None:
+            lens = np.concatenate([np.asarray(p_q_lens, dtype=np.int32), np.ones(Bd, dtype=np.int32)])
+            scu = np.zeros(Bp + Bd + 1, dtype=np.int32)
+            np.cumsum(lens, out=scu[1:])
+            spans["seq_cu"] = put(scu)
+            spans["seq_slots"] = put(seq_rows.astype(np.int32, copy=False))
         total = off
         self.dev[:total].copy_(self.host[:total], non_blocking=True)
 
@@ -127,5 +137,8 @@ class BatchBuilder:
             fb.d_block_tables = view("d_bt").view(Bd, -1)
             fb.d_max_ctx = int(d_ctx_lens.max())
         fb.logit_rows = view("rows")
+        if seq_rows is not None:
+            fb.seq_cu = view("seq_cu")
+            fb.seq_slots = view("seq_slots")
         fb.num_logits = int(logit_rows.shape[0])
         return fb

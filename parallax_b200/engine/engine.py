@@ -131,9 +131,10 @@ class Planner:
         maxb_d = (int(d_ctx.max()) + bs - 1) // bs if len(decode) else 0
         p_tables = cache.tables[np.asarray(p_rows, dtype=np.int64), :maxb_p] if prefill else None
         d_tables = cache.tables[d_rows, :maxb_d] if len(decode) else None
+        seq_rows = np.concatenate([np.asarray(p_rows, dtype=np.int32), d_rows])
         return dict(ordered=ordered, ids=ids, pos=pos, slots=slots, p_q=p_q, p_ctx=p_ctx,
                     p_tables=p_tables, d_ctx=d_ctx, d_tables=d_tables,
-                    logit_rows=np.asarray(logit_rows, dtype=np.int32), owners=owners)
+                    logit_rows=np.asarray(logit_rows, dtype=np.int32), owners=owners, seq_rows=seq_rows)
 
 
 class Engine:
@@ -166,6 +167,10 @@ class Engine:
         stage_layers = stage_layers or [(0, cfg.num_hidden_layers)]
         max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
         self.stages: list[StageWorker] = []
+        max_requests = max(max_batch_size * 2, 16)
+        if cfg.has_linear_layers:
+            # a recurrent state cannot be rebuilt from cached KV pages of a shared prefix
+            enable_prefix_cache = False
         for (s, e) in stage_layers:
             w = None
             if weights is not None:
@@ -174,7 +179,8 @@ class Engine:
                 w = filter_weights_for_range(weights, s, e, cfg.num_hidden_layers, cfg.tie_word_embeddings)
             self.stages.append(StageWorker(cfg, s, e, self.device, dtype, page_size, num_blocks=num_blocks,
                                            kv_fraction=kv_fraction / len(stage_layers), seed=seed, weights=w,
-                                           max_kv_tokens=max_kv_tokens, max_positions=max_positions))
+                                           max_kv_tokens=max_kv_tokens, max_positions=max_positions,
+                                           num_linear_slots=max_requests if cfg.has_linear_layers else 0))
         nb = min(st.num_blocks for st in self.stages)
         self.planner = Planner(cfg, nb, page_size, max_batch_size, max_num_tokens_per_batch,
                                micro_batch_ratio, chunked_prefill_size, enable_prefix_cache,
@@ -273,7 +279,7 @@ class Engine:
             events[0].record()
         fb = self.builder.build(arrays["ids"], arrays["pos"], arrays["slots"], arrays["p_q"],
                                 arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"], arrays["d_tables"],
-                                arrays["logit_rows"])
+                                arrays["logit_rows"], arrays["seq_rows"])
         owners = arrays["owners"]
         h = None
         for i, st in enumerate(self.stages):

@@ -129,6 +129,10 @@ class ModelConfig:
             return MSA_ATTENTION
         return ATTENTION
 
+    @property
+    def has_linear_layers(self) -> bool:
+        return any(self.layer_kind(i) == LINEAR for i in range(self.num_hidden_layers))
+
     def layer_window(self, layer_idx: int) -> int:
         if not self.sliding_window:
             return 0
@@ -299,6 +303,16 @@ def named_config(name: str) -> ModelConfig:
             d.update(index_n_heads=8 if small else 4, index_head_dim=128 if small else 32,
                      index_topk=64 if small else 16)
         return config_from_hf(d)
+    if n in {"tiny-hybrid", "small-hybrid"}:
+        small = n.startswith("small")   # "small": the head sizes the sm_100a kernels are built for
+        hd = 128 if small else 32
+        return config_from_hf(dict(architectures=["Qwen3NextForCausalLM"], model_type="qwen3_next",
+                                   hidden_size=512 if small else 128, num_hidden_layers=4, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=hd, intermediate_size=1024 if small else 256,
+                                   vocab_size=1024, rope_theta=1e4, partial_rotary_factor=0.25,
+                                   full_attention_interval=2, linear_num_key_heads=2, linear_num_value_heads=4,
+                                   linear_key_head_dim=hd, linear_value_head_dim=hd, linear_conv_kernel_dim=4,
+                                   num_experts=0, max_position_embeddings=4096))
     if n == "tiny":
         return config_from_hf(dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=256,
                                    num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,

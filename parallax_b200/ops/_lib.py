@@ -76,6 +76,10 @@ _SIGS = {
     "pxl_gemm_fp8_block_grouped": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                                    c_int, c_int, _P, _P],
     "pxl_quant_fp8_rows": [_P, c_int64, _P, _P, c_int, c_int, _P],
+    "pxl_causal_conv1d_silu": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, _P],
+    "pxl_gated_delta_rule": [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, _P, _P, _P, _P, _P, _P, c_int64,
+                             c_int, c_int, c_int, c_int, c_int, c_float, _P],
+    "pxl_sigmoid_gate_mul": [_P, c_int64, _P, c_int64, _P, c_int64, c_int, c_int, _P],
     "pxl_argmax": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P],
     "pxl_sample": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
 }

@@ -601,3 +601,40 @@ def moe_ffn_fp8(x, ids, weights, w1q, w1s, w2q, w2s, num_experts: int, base=None
     act = grouped_linear_fp8(xp, w1q, w1s, plan, num_experts, epi=EPI_SILU_MUL)
     y = grouped_linear_fp8(act, w2q, w2s, plan, num_experts)
     return moe_combine(y, plan, weights, base, x.shape[0])
+
+
+# ---------------------------------------------------------------------------- gated delta net
+def causal_conv1d_silu(x, w, bias, conv_state, seq_cu, seq_slots, positions):
+    T, C = x.shape
+    out = torch.empty((T, C), dtype=x.dtype, device=x.device)
+    B = seq_slots.shape[0]
+    check(_lib.lib().pxl_causal_conv1d_silu(x.data_ptr(), x.stride(0), w.data_ptr(), _ptr(bias), conv_state.data_ptr(),
+                                            seq_cu.data_ptr(), seq_slots.data_ptr(), positions.data_ptr(),
+                                            out.data_ptr(), out.stride(0), B, C, w.shape[1], _stream(x.device)),
+          "pxl_causal_conv1d_silu")
+    _count()
+    return out
+
+
+def gated_delta_rule(qkv, a, b, A_log, dt_bias, z, norm_w, rec_state, seq_cu, seq_slots, positions, Hk: int, Hv: int,
+                     Dk: int, Dv: int, eps: float):
+    T = qkv.shape[0]
+    out = torch.empty((T, Hv * Dv), dtype=qkv.dtype, device=qkv.device)
+    assert a.stride(0) == b.stride(0)
+    check(_lib.lib().pxl_gated_delta_rule(qkv.data_ptr(), qkv.stride(0), a.data_ptr(), b.data_ptr(), a.stride(0),
+                                          A_log.data_ptr(), dt_bias.data_ptr(), z.data_ptr(), z.stride(0),
+                                          norm_w.data_ptr(), rec_state.data_ptr(), seq_cu.data_ptr(),
+                                          seq_slots.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
+                                          seq_slots.shape[0], Hk, Hv, Dk, Dv, eps, _stream(qkv.device)),
+          "pxl_gated_delta_rule")
+    _count()
+    return out
+
+
+def sigmoid_gate_mul(x, gate):
+    T, N = x.shape
+    out = torch.empty((T, N), dtype=x.dtype, device=x.device)
+    check(_lib.lib().pxl_sigmoid_gate_mul(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), out.data_ptr(),
+                                          out.stride(0), T, N, _stream(x.device)), "pxl_sigmoid_gate_mul")
+    _count()
+    return out

@@ -460,3 +460,66 @@ def moe_ffn_fp8(x, ids, weights, w1q, w1s, w2q, w2s, num_experts: int, base=None
         y = linear_fp8(a, w2q[e * n2:(e + 1) * n2], w2s[e * n2 // 64:(e + 1) * n2 // 64])
         out.index_add_(0, tok, y.float() * weights[tok, slot].float()[:, None])
     return out.to(x.dtype)
+
+
+# ---------------------------------------------------------------------------- gated delta net
+def causal_conv1d_silu(x, w, bias, conv_state, seq_cu, seq_slots, positions):
+    """Per-channel causal convolution + SiLU with the last K-1 inputs carried per request slot."""
+    T, C = x.shape
+    K = w.shape[1]
+    out = torch.empty((T, C), dtype=x.dtype)
+    cu = seq_cu.tolist()
+    wf = w.float()
+    for b in range(len(cu) - 1):
+        t0, t1 = cu[b], cu[b + 1]
+        if t1 <= t0:
+            continue
+        slot = int(seq_slots[b])
+        hist = torch.zeros(K - 1, C) if int(positions[t0]) == 0 else conv_state[slot].float().t()
+        u = torch.cat([hist, x[t0:t1].float()], dim=0)                 # [K-1+n, C]
+        win = u.unfold(0, K, 1)                                        # [n, C, K]
+        y = (win * wf[None]).sum(-1)
+        if bias is not None:
+            y = y + bias.float()
+        out[t0:t1] = torch.nn.functional.silu(y).to(x.dtype)
+        conv_state[slot] = u[-(K - 1):].t().to(conv_state.dtype)
+    return out
+
+
+def gated_delta_rule(qkv, a, b, A_log, dt_bias, z, norm_w, rec_state, seq_cu, seq_slots, positions, Hk: int, Hv: int,
+                     Dk: int, Dv: int, eps: float):
+    """Sequential gated delta rule with a per-request state ``[Hv, Dv, Dk]`` and gated RMSNorm."""
+    T = qkv.shape[0]
+    out = torch.empty((T, Hv * Dv), dtype=qkv.dtype)
+    cu = seq_cu.tolist()
+    rep = Hv // Hk
+    for s in range(len(cu) - 1):
+        t0, t1 = cu[s], cu[s + 1]
+        if t1 <= t0:
+            continue
+        slot = int(seq_slots[s])
+        S = torch.zeros(Hv, Dv, Dk) if int(positions[t0]) == 0 else rec_state[slot].float().clone()
+        for t in range(t0, t1):
+            row = qkv[t].float()
+            q = row[:Hk * Dk].view(Hk, Dk)
+            k = row[Hk * Dk:2 * Hk * Dk].view(Hk, Dk)
+            v = row[2 * Hk * Dk:].view(Hv, Dv)
+            q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) / Dk ** 0.5
+            k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+            q, k = q.repeat_interleave(rep, 0), k.repeat_interleave(rep, 0)        # [Hv, Dk]
+            g = -torch.exp(A_log.float()) * torch.nn.functional.softplus(a[t].float() + dt_bias.float())
+            beta = torch.sigmoid(b[t].float())
+            S = S * torch.exp(g)[:, None, None]
+            mem = torch.einsum("hvk,hk->hv", S, k)
+            d = (v - mem) * beta[:, None]
+            S = S + d[:, :, None] * k[:, None, :]
+            o = torch.einsum("hvk,hk->hv", S, q)
+            zz = z[t].float().view(Hv, Dv)
+            y = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float() * torch.nn.functional.silu(zz)
+            out[t] = y.reshape(-1).to(out.dtype)
+        rec_state[slot] = S.to(rec_state.dtype)
+    return out
+
+
+def sigmoid_gate_mul(x, gate):
+    return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)

@@ -125,7 +125,10 @@ class DistEngine:
         max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
         self.worker = StageWorker(cfg, start, end, self.device, dtype, page_size, num_blocks=num_blocks,
                                   kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
-                                  tp_rank=self.topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm)
+                                  tp_rank=self.topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm,
+                                  num_linear_slots=max(max_batch_size * 2, 16) if cfg.has_linear_layers else 0)
+        if cfg.has_linear_layers:
+            enable_prefix_cache = False
         # every rank must agree on the number of KV blocks
         nb = torch.tensor([self.worker.num_blocks], dtype=torch.int64)
         dist.all_reduce(nb, op=dist.ReduceOp.MIN, group=self.ctrl)
@@ -214,7 +217,8 @@ class DistEngine:
         b = self.builders[self._bi]
         self._bi = (self._bi + 1) % len(self.builders)
         fb = b.build(plan["ids"] if topo.is_first_stage else None, plan["pos"], plan["slots"], plan["p_q"],
-                     plan["p_ctx"], plan["p_tables"], plan["d_ctx"], plan["d_tables"], plan["logit_rows"])
+                     plan["p_ctx"], plan["p_tables"], plan["d_ctx"], plan["d_tables"], plan["logit_rows"],
+                     plan.get("seq_rows"))
         self.h2d_bytes += fb.h2d_bytes
         T, H = fb.num_tokens, self.cfg.hidden_size
         hidden = None
@@ -335,7 +339,7 @@ class DistEngine:
         sps = [s.req.sampling_params for s in owners]
         greedy = all(sp.is_greedy for sp in sps)
         plan = {k: arrays[k] for k in ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables",
-                                       "logit_rows")}
+                                       "logit_rows", "seq_rows")}
         plan.update(cmd="step", n_logits=len(owners), greedy=greedy)
         if not greedy:
             plan["sampling"] = {"t": [0.0 if sp.is_greedy else sp.temperature for sp in sps],
