@@ -211,6 +211,19 @@ int pxl_gated_delta_rule(const void* qkv, int64_t ld_qkv, const void* a, const v
 int pxl_sigmoid_gate_mul(const void* x, int64_t ldx, const void* gate, int64_t ldg, void* out, int64_t ldo,
                          int T, int N, pxl_stream_t stream);
 
+// ---- msa.cu: block-sparse attention indexer --------------------------------------------------
+// scores[t, j] = max over index heads and visible tokens of 128-token block j of scale * iq . ik
+int pxl_msa_block_scores(const void* iq, const void* index_cache, const int* block_tables, const int* cu_q,
+                         const int* positions, float* scores, int64_t ld, int T, int B, int Hi, int Di,
+                         int max_blocks, int page, int sparse_block, int max_ctx, float scale,
+                         pxl_stream_t stream);
+// top-k blocks per query (first init_blocks and the last local_blocks always kept) expanded into a
+// virtual block table v_tables [T, topk * sparse_block / page] and visible-token count v_ctx [T]
+int pxl_msa_select(const float* scores, int64_t ld, const int* positions, const int* block_tables,
+                   const int* cu_q, int T, int B, int max_blocks, int page, int sparse_block, int topk,
+                   int init_blocks, int local_blocks, int* v_tables, int64_t ld_vt, int* v_ctx,
+                   pxl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -126,6 +126,9 @@ class ModelConfig:
         if self.is_mla:
             return DSA_ATTENTION if self.index_topk > 0 else MLA_ATTENTION
         if self.raw.get("index_topk_blocks"):
+            freq = (self.raw.get("sparse_attention_config") or {}).get("sparse_attention_freq")
+            if isinstance(freq, list) and not (layer_idx < len(freq) and freq[layer_idx]):
+                return ATTENTION
             return MSA_ATTENTION
         return ATTENTION
 
@@ -191,7 +194,8 @@ def config_from_hf(cfg: dict) -> ModelConfig:
         rms_norm_eps=cfg.get("rms_norm_eps", 1e-6),
         rope_theta=float(rope_theta or 10000.0),
         rope_scaling=rope_scaling if isinstance(rope_scaling, dict) else None,
-        partial_rotary_factor=float(cfg.get("partial_rotary_factor", 1.0)),
+        partial_rotary_factor=float(cfg.get("partial_rotary_factor")
+                                    or (cfg["rotary_dim"] / head_dim if cfg.get("rotary_dim") else 1.0)),
         max_position_embeddings=cfg.get("max_position_embeddings", 32768),
         tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
         attention_bias=bool(cfg.get("attention_bias", cfg.get("qkv_bias", mt == "qwen2"))),
@@ -313,6 +317,20 @@ def named_config(name: str) -> ModelConfig:
                                    full_attention_interval=2, linear_num_key_heads=2, linear_num_value_heads=4,
                                    linear_key_head_dim=hd, linear_value_head_dim=hd, linear_conv_kernel_dim=4,
                                    num_experts=0, max_position_embeddings=4096))
+    if n in {"tiny-msa", "small-msa"}:
+        small = n.startswith("small")
+        hd = 128 if small else 32
+        sparse = dict(use_sparse_attention=True, sparse_attention_freq=[0, 1, 1], sparse_block_size=32 if not small else 128,
+                      sparse_topk_blocks=2 if not small else 3, sparse_init_block=1, sparse_local_block=1,
+                      sparse_index_dim=hd, sparse_num_index_heads=2)
+        return config_from_hf(dict(architectures=["MiniMaxM3SparseForCausalLM"], model_type="minimax_m3",
+                                   hidden_size=512 if small else 128, num_hidden_layers=3, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=hd, intermediate_size=1024 if small else 256,
+                                   vocab_size=1024, rope_theta=1e4, rotary_dim=hd // 2, use_qk_norm=True,
+                                   use_gemma_norm=True, sparse_attention_config=sparse,
+                                   index_head_dim=hd, index_block_size=sparse["sparse_block_size"],
+                                   index_topk_blocks=sparse["sparse_topk_blocks"], index_local_blocks=1,
+                                   max_position_embeddings=4096))
     if n == "tiny":
         return config_from_hf(dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=256,
                                    num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,

@@ -80,6 +80,9 @@ _SIGS = {
     "pxl_gated_delta_rule": [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, _P, _P, _P, _P, _P, _P, c_int64,
                              c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "pxl_sigmoid_gate_mul": [_P, c_int64, _P, c_int64, _P, c_int64, c_int, c_int, _P],
+    "pxl_msa_block_scores": [_P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_float, _P],
+    "pxl_msa_select": [_P, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P],
     "pxl_argmax": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P],
     "pxl_sample": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
 }

@@ -638,3 +638,30 @@ def sigmoid_gate_mul(x, gate):
                                           out.stride(0), T, N, _stream(x.device)), "pxl_sigmoid_gate_mul")
     _count()
     return out
+
+
+# ---------------------------------------------------------------------------- block-sparse indexer (MSA)
+def msa_block_scores(iq, index_cache, block_tables, cu_q, positions, max_ctx: int, sparse_block: int, scale: float):
+    T, Hi, Di = iq.shape
+    nb = (max_ctx + sparse_block - 1) // sparse_block
+    scores = torch.empty((T, nb), dtype=torch.float32, device=iq.device)
+    check(_lib.lib().pxl_msa_block_scores(iq.data_ptr(), index_cache.data_ptr(), block_tables.data_ptr(), _ptr(cu_q),
+                                          positions.data_ptr(), scores.data_ptr(), nb, T, block_tables.shape[0], Hi, Di,
+                                          block_tables.shape[1], index_cache.shape[-2], sparse_block, max_ctx,
+                                          float(scale), _stream(iq.device)), "pxl_msa_block_scores")
+    _count()
+    return scores
+
+
+def msa_select(scores, positions, block_tables, cu_q, page: int, sparse_block: int, topk: int, init_blocks: int,
+               local_blocks: int):
+    T = scores.shape[0]
+    ppb = sparse_block // page
+    v_tables = torch.zeros((T, topk * ppb), dtype=torch.int32, device=scores.device)
+    v_ctx = torch.empty(T, dtype=torch.int32, device=scores.device)
+    check(_lib.lib().pxl_msa_select(scores.data_ptr(), scores.stride(0), positions.data_ptr(), block_tables.data_ptr(),
+                                    _ptr(cu_q), T, block_tables.shape[0], block_tables.shape[1], page, sparse_block, topk,
+                                    init_blocks, local_blocks, v_tables.data_ptr(), v_tables.stride(0),
+                                    v_ctx.data_ptr(), _stream(scores.device)), "pxl_msa_select")
+    _count()
+    return v_tables, v_ctx

@@ -523,3 +523,52 @@ def gated_delta_rule(qkv, a, b, A_log, dt_bias, z, norm_w, rec_state, seq_cu, se
 
 def sigmoid_gate_mul(x, gate):
     return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------- block-sparse indexer (MSA)
+def msa_block_scores(iq, index_cache, block_tables, cu_q, positions, max_ctx: int, sparse_block: int, scale: float):
+    """scores[t, j] = max over index heads and visible tokens of block j of scale * iq . ik."""
+    T = iq.shape[0]
+    page = index_cache.shape[-2]
+    flat = index_cache.view(-1, index_cache.shape[-1]).float()
+    nb = (max_ctx + sparse_block - 1) // sparse_block
+    out = torch.full((T, nb), float("-inf"), dtype=torch.float32)
+    cu = None if cu_q is None else cu_q.tolist()
+    for t in range(T):
+        seq = t if cu is None else max(i for i in range(len(cu) - 1) if cu[i] <= t)
+        pos = int(positions[t])
+        keys = torch.arange(pos + 1)
+        bt = block_tables[seq].long()
+        k = flat[bt[keys // page] * page + keys % page]
+        s = (iq[t].float() @ k.t() * scale).max(0).values                 # [pos+1]
+        for j in range(pos // sparse_block + 1):
+            out[t, j] = s[j * sparse_block:(j + 1) * sparse_block].max()
+    return out
+
+
+def msa_select(scores, positions, block_tables, cu_q, page: int, sparse_block: int, topk: int, init_blocks: int,
+               local_blocks: int):
+    """Top-k causal blocks per query (forced init/local blocks) -> virtual block table + visible tokens."""
+    T = scores.shape[0]
+    ppb = sparse_block // page
+    v_tables = torch.zeros((T, topk * ppb), dtype=torch.int32)
+    v_ctx = torch.empty(T, dtype=torch.int32)
+    cu = None if cu_q is None else cu_q.tolist()
+    for t in range(T):
+        seq = t if cu is None else max(i for i in range(len(cu) - 1) if cu[i] <= t)
+        pos = int(positions[t])
+        cur = pos // sparse_block
+        s = scores[t, :cur + 1].clone()
+        s[torch.isnan(s)] = float("-inf")
+        s[:init_blocks] = 1e30
+        s[max(cur - local_blocks + 1, 0):] = 1e29
+        k = min(topk, cur + 1)
+        # arg-max rounds with ties to the lower index (stable sort by descending score)
+        order = torch.sort(s, descending=True, stable=True).indices[:k]
+        blocks = torch.sort(order).values
+        pages = (blocks[:, None] * ppb + torch.arange(ppb)[None]).reshape(-1)
+        bt = block_tables[seq].long()
+        v_tables[t, : k * ppb] = torch.where(pages < bt.shape[0], bt[pages.clamp_max(bt.shape[0] - 1)],
+                                             torch.zeros_like(pages)).int()
+        v_ctx[t] = (k - 1) * sparse_block + pos - cur * sparse_block + 1
+    return v_tables, v_ctx
