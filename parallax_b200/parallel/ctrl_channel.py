@@ -1,0 +1,94 @@
+"""Single-box control channel: rank 0 publishes step plans, every other rank reads them.
+
+A ring of fixed-size slots in POSIX shared memory; each slot carries a sequence number that the
+writer stores last, readers poll it. Per-reader cursors in the same segment give the writer flow
+control (a slot is reused only after every reader has consumed it). One plan is a pickled dict of
+small numpy arrays (tens of KB), so publishing costs one memcpy instead of a collective per step.
+
+This is the in-box replacement of the reference's python-object broadcast to its tensor-parallel
+ranks over ``multiprocessing.Pipe`` (``src/parallax/server/executor/sglang_executor.py:560-571``).
+"""
+
+from __future__ import annotations
+
+import pickle
+import time
+from multiprocessing import shared_memory
+
+import numpy as np
+
+_HDR = 64            # bytes: [0:8] reserved, then 8 bytes per reader cursor (up to 7 readers)
+_SLOT_HDR = 16       # seq (int64), nbytes (int64)
+
+
+class CtrlChannel:
+    def __init__(self, name: str, create: bool, n_readers: int, reader_index: int = -1, slots: int = 32,
+                 slot_bytes: int = 1 << 20):
+        self.slots, self.slot_bytes, self.n_readers, self.reader_index = slots, slot_bytes, n_readers, reader_index
+        size = _HDR + slots * (slot_bytes + _SLOT_HDR)
+        if create:
+            self.shm = shared_memory.SharedMemory(name=name, create=True, size=size)
+            self.shm.buf[:_HDR] = bytes(_HDR)
+            for i in range(slots):
+                o = _HDR + i * (slot_bytes + _SLOT_HDR)
+                self.shm.buf[o:o + _SLOT_HDR] = bytes(_SLOT_HDR)
+        else:
+            self.shm = shared_memory.SharedMemory(name=name, create=False)
+            try:        # the creating process owns the segment; readers must not unlink it at exit
+                from multiprocessing import resource_tracker
+
+                resource_tracker.unregister(self.shm._name, "shared_memory")
+            except Exception:
+                pass
+        self.owner = create
+        self.cursors = np.ndarray((7,), dtype=np.int64, buffer=self.shm.buf, offset=8)
+        self.seq = 0      # writer: messages published; reader: messages consumed
+
+    def _slot(self, seq: int):
+        o = _HDR + (seq % self.slots) * (self.slot_bytes + _SLOT_HDR)
+        hdr = np.ndarray((2,), dtype=np.int64, buffer=self.shm.buf, offset=o)
+        return hdr, o + _SLOT_HDR
+
+    # ------------------------------------------------------------------ writer (rank 0)
+    def publish(self, obj, timeout_s: float = 600.0) -> None:
+        data = pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL)
+        if len(data) > self.slot_bytes:
+            raise ValueError(f"control message of {len(data)} bytes exceeds the slot size {self.slot_bytes}")
+        nxt = self.seq + 1
+        t0 = time.monotonic()
+        while self.n_readers and nxt - int(self.cursors[: self.n_readers].min()) > self.slots:
+            if time.monotonic() - t0 > timeout_s:
+                raise TimeoutError("a reader of the control channel stopped consuming")
+            time.sleep(0.0002)
+        hdr, off = self._slot(nxt)
+        self.shm.buf[off:off + len(data)] = data
+        hdr[1] = len(data)
+        hdr[0] = nxt          # published last: readers poll this word
+        self.seq = nxt
+
+    # ------------------------------------------------------------------ readers
+    def receive(self, timeout_s: float = 600.0):
+        nxt = self.seq + 1
+        hdr, off = self._slot(nxt)
+        t0 = time.monotonic()
+        spins = 0
+        while int(hdr[0]) != nxt:
+            spins += 1
+            if spins > 2000:             # stay hot for a moment, then yield the core
+                time.sleep(0.0001)
+                if time.monotonic() - t0 > timeout_s:
+                    raise TimeoutError("no control message from rank 0")
+        n = int(hdr[1])
+        obj = pickle.loads(bytes(self.shm.buf[off:off + n]))
+        self.seq = nxt
+        self.cursors[self.reader_index] = nxt
+        return obj
+
+    def close(self) -> None:
+        self.cursors = None
+        try:
+            self.shm.close()
+            if self.owner:
+                self.shm.unlink()
+        except (FileNotFoundError, BufferError):
+            pass

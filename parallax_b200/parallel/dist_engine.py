@@ -19,6 +19,7 @@ case where all stages live on one NVSwitch domain.
 from __future__ import annotations
 
 import logging
+import os
 import time
 from collections import deque
 from dataclasses import dataclass
@@ -108,6 +109,16 @@ class DistEngine:
             g = dist.new_group(list(range(s * tp, (s + 1) * tp)), backend="nccl" if on_gpu else "gloo")
             if s == self.topo.pp_rank:
                 self.tp_group = g
+        # step plans travel through shared memory (all ranks live on one box); the name is agreed once
+        from parallax_b200.parallel.ctrl_channel import CtrlChannel
+
+        box = [None]
+        if rank == 0:
+            box[0] = f"pxl_ctrl_{os.getpid()}_{int(time.time() * 1e3) % 100000000}"
+            self.chan = CtrlChannel(box[0], create=True, n_readers=world - 1)
+        dist.broadcast_object_list(box, src=0, group=self.ctrl)      # also orders attach after create
+        if rank != 0:
+            self.chan = CtrlChannel(box[0], create=False, n_readers=world - 1, reader_index=rank - 1)
         start, end = split_layers(cfg.num_hidden_layers, pp)[self.topo.pp_rank]
         comm = None
         if tp > 1:
@@ -134,6 +145,7 @@ class DistEngine:
         dist.all_reduce(nb, op=dist.ReduceOp.MIN, group=self.ctrl)
         self.num_blocks = int(nb)
         self.max_in_flight = max_in_flight or pp
+        self._ret_stream = torch.cuda.Stream(self.device) if on_gpu else None
         self._warm_links()
         ratio = micro_batch_ratio or pp
         self.planner = None
@@ -206,9 +218,10 @@ class DistEngine:
 
     # ------------------------------------------------------------------ plan broadcast
     def _bcast(self, plan: Optional[dict]) -> dict:
-        box = [plan]
-        dist.broadcast_object_list(box, src=0, group=self.ctrl)
-        return box[0]
+        if self.topo.rank == 0:
+            self.chan.publish(plan)
+            return plan
+        return self.chan.receive()
 
     def _execute(self, plan: dict):
         """Run this rank's part of one planned micro-batch. Returns the sampled-token tensor on
@@ -252,8 +265,20 @@ class DistEngine:
             return None
         if topo.last_stage_root != 0:
             # post the receive now, in the same order in which the last stage posts its sends
-            t = torch.empty(plan["n_logits"], dtype=torch.int32, device=self.device)
-            return ("recv", (t, dist.irecv(t, src=topo.last_stage_root, group=self.ret)))
+            if self.device.type != "cuda":
+                t = torch.empty(plan["n_logits"], dtype=torch.int32, device=self.device)
+                return ("recv", (t, dist.irecv(t, src=topo.last_stage_root, group=self.ret), None, None))
+            # on a side stream: reading the tokens later must not wait for the compute of the
+            # micro-batches that were queued behind this one
+            host = torch.empty(plan["n_logits"], dtype=torch.int32, pin_memory=True)
+            ev = torch.cuda.Event()
+            with torch.cuda.stream(self._ret_stream):
+                t = torch.empty(plan["n_logits"], dtype=torch.int32, device=self.device)   # from the side stream's pool
+                work = dist.irecv(t, src=topo.last_stage_root, group=self.ret)
+                work.wait()
+                host.copy_(t, non_blocking=True)
+                ev.record()
+            return ("recv", (t, None, host, ev))
         return ("have", tokens)
 
     # ------------------------------------------------------------------ device-time probes
@@ -304,10 +329,14 @@ class DistEngine:
             self.steps += 1
         for work, _ in self._pending_sends:
             work.wait()
+        dist.barrier(group=self.ctrl)
+        self.chan.close()
 
     def shutdown(self) -> None:
         if self.topo.rank == 0:
             self._bcast({"cmd": "stop"})
+            dist.barrier(group=self.ctrl)       # every reader has seen the stop message
+            self.chan.close()
 
     # ------------------------------------------------------------------ rank-0 step
     def _drop(self, req: Request) -> None:
@@ -366,8 +395,12 @@ class DistEngine:
         if owners:
             kind, t = res
             if kind == "recv":
-                t, work = t
-                work.wait()
+                t, work, host, ev = t
+                if ev is not None:
+                    ev.synchronize()
+                    t = host
+                else:
+                    work.wait()
             token_list = t.tolist()
         sched = self.scheduler
         for s, tok in zip(owners, token_list):
