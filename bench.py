@@ -209,6 +209,8 @@ def run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid) -> No
     sampler.start()
     eng.mark()
     tokens = 0
+    for k in eng.host_s:
+        eng.host_s[k] = 0.0
     for _ in range(args.steps):
         tokens += rotation()
     torch.cuda.synchronize()
@@ -220,7 +222,9 @@ def run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid) -> No
     label = f"pp{pp}" + (f"tp{tp}" if tp > 1 else "")
     print(json.dumps(result_line(args, world, label, tokens, res["device_ms"] / 1e3, res["wall_s"], res["launches"],
                                  res["h2d_bytes"], 4 * tokens, clocks, invalid,
-                                 {"prefix_cache": eng.cache.prefix_cache.get_stats() if eng.cache.prefix_cache else None})),
+                                 {"prefix_cache": eng.cache.prefix_cache.get_stats() if eng.cache.prefix_cache else None,
+                                  "rank0_host_ms_per_step": {k: round(v / args.steps * 1e3, 2) for k, v in eng.host_s.items()},
+                                  "micro_batches": n_mb})),
           flush=True)
     dist.barrier()
     dist.destroy_process_group()

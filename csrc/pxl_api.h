@@ -224,6 +224,15 @@ int pxl_msa_select(const float* scores, int64_t ld, const int* positions, const 
                    int init_blocks, int local_blocks, int* v_tables, int64_t ld_vt, int* v_ctx,
                    pxl_stream_t stream);
 
+// ---- stage_exec.cu: all layers of a dense GQA stage for one step behind one call --------------
+// The descriptor structs are defined in stage_exec.cu (mirrored by parallax_b200/engine/native_stage.py).
+struct PxlStageDesc;
+struct PxlStepDesc;
+struct PxlStageWorkspace;
+int pxl_stage_forward_dense(const struct PxlStageDesc* stage, const struct PxlStepDesc* step,
+                            const struct PxlStageWorkspace* ws, const void* h_in, void** h_out, int* launches,
+                            int* status, pxl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

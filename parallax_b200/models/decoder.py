@@ -57,6 +57,7 @@ class DecoderStage:
         self.cos_sin = build_rope_table(cfg, self.max_positions, self.device)
         self.kv_caches: list = []  # per local layer: (k_cache, v_cache)
         self.norm_offset = 0.0
+        self._native = None     # native stage executor (built on first use) or False if not applicable
 
     # ------------------------------------------------------------------ weights
     def num_local_layers(self) -> int:
@@ -253,6 +254,16 @@ class DecoderStage:
         return ops.linear(act, lw.w_down, residual=h)
 
     def forward_layers(self, h: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        if self._native is None and type(self).forward_layers is DecoderStage.forward_layers \
+                and type(self)._attention is DecoderStage._attention:
+            from parallax_b200.engine.native_stage import NativeDenseStage
+
+            # dense GQA stage on a GPU: all layers of a step run behind one call into the library
+            self._native = NativeDenseStage(self) if NativeDenseStage.supported(self) else False
+        if self._native:
+            out = self._native.forward(h.contiguous(), fb)
+            # the result lives in the executor's workspace: hand out a copy when it leaves the stage
+            return out if self.is_last else out.clone()
         eps = self.cfg.rms_norm_eps
         for li, lw in enumerate(self.layers):
             xn = ops.rmsnorm(h, lw.ln1, eps, w_offset=self.norm_offset)

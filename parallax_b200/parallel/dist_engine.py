@@ -166,6 +166,7 @@ class DistEngine:
         self.last_logits = None
         self.marks: list = []
         self.h2d_bytes = 0
+        self.host_s = {"plan": 0.0, "publish": 0.0, "launch": 0.0, "wait": 0.0, "commit": 0.0}
 
     def _warm_links(self) -> None:
         """Open every point-to-point connection once, in an order that all ranks share, so that
@@ -345,6 +346,7 @@ class DistEngine:
         self._side_events.append((req, None))
 
     def _issue(self) -> bool:
+        t0 = time.perf_counter()
         sched = self.scheduler
         seqs = sched.form_batch()
         for req in sched.pop_rejected():
@@ -374,8 +376,15 @@ class DistEngine:
             plan["sampling"] = {"t": [0.0 if sp.is_greedy else sp.temperature for sp in sps],
                                 "k": [sp.top_k if sp.top_k > 0 else 0 for sp in sps], "p": [sp.top_p for sp in sps],
                                 "mp": [sp.min_p for sp in sps], "u": self._rng.random(len(sps)).tolist()}
+        t1 = time.perf_counter()
         self._bcast(plan)
+        t2 = time.perf_counter()
         res = self._execute(plan)
+        t3 = time.perf_counter()
+        hs = self.host_s
+        hs["plan"] += t1 - t0
+        hs["publish"] += t2 - t1
+        hs["launch"] += t3 - t2
         # prefill bookkeeping that does not depend on the sampled token: the next chunk of a long
         # prompt may enter the pipeline right behind this one
         for s in arrays["ordered"]:
@@ -394,6 +403,7 @@ class DistEngine:
         token_list = []
         if owners:
             kind, t = res
+            tw = time.perf_counter()
             if kind == "recv":
                 t, work, host, ev = t
                 if ev is not None:
@@ -402,7 +412,9 @@ class DistEngine:
                 else:
                     work.wait()
             token_list = t.tolist()
+            self.host_s["wait"] += time.perf_counter() - tw
         sched = self.scheduler
+        tc = time.perf_counter()
         for s, tok in zip(owners, token_list):
             req = s.req
             req.commit_new_token(int(tok))
@@ -412,6 +424,7 @@ class DistEngine:
             else:
                 sched.enque_request(req)
             out.append((req, int(tok)))
+        self.host_s["commit"] += time.perf_counter() - tc
         return out
 
     def step(self) -> list:

@@ -104,3 +104,23 @@ def test_gpu_sampling_requests_finish():
     assert all(0 <= t < 2048 for r in reqs for t in r.output_ids)
     assert all(0.0 < p <= 1.0 for r in reqs for p in r.output_probs)
     assert eng.cache.num_free_blocks() + eng.cache.prefix_cache.num_nodes == eng.cache.num_blocks
+
+
+def test_native_stage_executor_equals_python_layer_loop():
+    """One call into the library per stage must launch exactly the kernels of the Python loop."""
+    prompts = _prompts(4, 90, 2048, seed=7) + _prompts(2, 7, 2048, seed=8)
+    native, n1, n2 = _first_step_logits("cuda:0", torch.bfloat16, prompts)
+    assert native.stages[0].model._native, "the dense GQA stage should use the native executor"
+    weights = _export_weights(native)
+    eng = Engine(_cfg(), device="cuda:0", dtype=torch.bfloat16, num_blocks=128, page_size=16, max_batch_size=8,
+                 weights=weights)
+    eng.stages[0].model._native = False          # force the per-layer Python loop
+    eng.keep_logits = True
+    for p in prompts:
+        eng.add_request(Request(input_ids=p, sampling_params=SamplingParams(max_new_tokens=4, temperature=0.0,
+                                                                            ignore_eos=True)))
+    eng.step()
+    p1 = eng.last_logits.float().cpu()
+    eng.step()
+    p2 = eng.last_logits.float().cpu()
+    assert torch.equal(n1, p1) and torch.equal(n2, p2)
