@@ -38,6 +38,11 @@ template <int D>
 __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
   return static_cast<uint32_t>(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
 }
+// Same for a tile that TMA wrote with the 128-byte swizzle: two halves of [TILE][64] elements
+// (128-byte rows); inside a half the 16-byte chunk c of row r sits at position c ^ (r % 8).
+__device__ __forceinline__ uint32_t tile_off_sw128(int row, int chunk) {
+  return static_cast<uint32_t>((chunk >> 3) * (64 * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
 
 // Issue cp.async loads of K and V rows for tokens [tok0, tok0+TILE) ∩ [0, hi).
 template <int D>
@@ -72,7 +77,7 @@ __device__ __forceinline__ void load_kv_tile(const KVTileArgs& a, int tok0, int 
 }
 
 // S[16 x 16] += Q[16 x D] * K[tokens r0..r0+15]^T ; s[j] is the n-tile of tokens r0+8j..
-template <int D>
+template <int D, bool SW128 = false>
 __device__ __forceinline__ void qk_16x16(const uint32_t (&qf)[D / 16][4], uint32_t k_smem, int r0,
                                          float (&s0)[4], float (&s1)[4]) {
   const int lane = threadIdx.x & 31;
@@ -81,7 +86,7 @@ __device__ __forceinline__ void qk_16x16(const uint32_t (&qf)[D / 16][4], uint32
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
     uint32_t r[4];
-    ldmatrix_x4(r, k_smem + tile_off<D>(row, ks * 2 + (mi & 1)));
+    ldmatrix_x4(r, k_smem + (SW128 ? tile_off_sw128(row, ks * 2 + (mi & 1)) : tile_off<D>(row, ks * 2 + (mi & 1))));
     const uint32_t b0[2] = {r[0], r[1]};
     const uint32_t b1[2] = {r[2], r[3]};
     mma_m16n8k16_bf16(s0, qf[ks], b0);
@@ -90,7 +95,7 @@ __device__ __forceinline__ void qk_16x16(const uint32_t (&qf)[D / 16][4], uint32
 }
 
 // O[16 x D] += P[16 x 16] * V[tokens r0..r0+15]
-template <int D>
+template <int D, bool SW128 = false>
 __device__ __forceinline__ void pv_16x16(const uint32_t (&pf)[4], uint32_t v_smem, int r0,
                                          float (&o)[D / 8][4]) {
   const int lane = threadIdx.x & 31;
@@ -99,7 +104,7 @@ __device__ __forceinline__ void pv_16x16(const uint32_t (&pf)[4], uint32_t v_sme
 #pragma unroll
   for (int np = 0; np < D / 16; ++np) {
     uint32_t r[4];
-    ldmatrix_x4_trans(r, v_smem + tile_off<D>(row, np * 2 + (mi >> 1)));
+    ldmatrix_x4_trans(r, v_smem + (SW128 ? tile_off_sw128(row, np * 2 + (mi >> 1)) : tile_off<D>(row, np * 2 + (mi >> 1))));
     const uint32_t b0[2] = {r[0], r[1]};
     const uint32_t b1[2] = {r[2], r[3]};
     mma_m16n8k16_bf16(o[2 * np], pf, b0);
@@ -283,6 +288,226 @@ attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __r
           __float2bfloat16(denom > 0.f ? acc / denom : 0.f);
     } else {
       // partial: normalised output + log2-sum-exp
+      float* po = workspace;
+      float* plse = workspace + static_cast<size_t>(gridDim.y) * Hq * num_splits * D;
+      const size_t row = (static_cast<size_t>(b) * Hq + head) * num_splits + split;
+      po[row * D + d] = L > 0.f ? acc / L : 0.f;
+      if (d == 0) plse[row] = L > 0.f ? Mu + log2f(L) : -INFINITY;
+    }
+  }
+}
+
+// ---- decode, TMA-fed variant (D = 128; page_size 16, 32 or 64) ------------------------------------
+// A (block, kv head) page of the cache is one contiguous [page, 128] matrix, so a KV tile of 64
+// tokens is 64 / page box loads per operand half: one thread issues them through the TMA engine
+// (128-byte swizzle, completion on an mbarrier) two tiles ahead of the four consumer warps. This
+// removes the per-thread address arithmetic and the 2048 cp.async instructions per tile of the
+// kernel above, which was issue-bound at half of the DRAM bandwidth.
+constexpr int kDecStages = 3;
+
+__global__ void __launch_bounds__(128, 2)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                       const bf16* __restrict__ q, int64_t q_stride, const int* __restrict__ block_tables,
+                       const int* __restrict__ ctx_lens, bf16* __restrict__ out, float* __restrict__ workspace,
+                       const float* __restrict__ sinks, int Hq, int Hkv, int page_size, int max_blocks,
+                       int64_t num_blocks, float scale_log2, int window, int num_splits, int* status) {
+  constexpr int D = 128;
+  constexpr int TILE_BYTES = TILE * D * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t stage0 = smem_u32(smem);  // stage s: K tile at s * 2 * TILE_BYTES, V tile behind it
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecStages * 2 * TILE_BYTES);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kDecStages);
+  const uint32_t full0 = smem_u32(bars);
+
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ctx = ctx_lens[b];
+  const int hi = ctx;
+  const int lo = (window > 0 && ctx > window) ? ctx - window : 0;
+  const int tile_lo = lo / TILE;
+  const int tiles_total = hi > lo ? ceil_div(hi, TILE) - tile_lo : 0;
+  const int per_split = ceil_div(tiles_total, num_splits);
+  const int t_begin = tile_lo + split * per_split;
+  const int t_end = min(tile_lo + tiles_total, t_begin + per_split);
+  const int n_tiles = t_end > t_begin ? t_end - t_begin : 0;
+  const int* bt = block_tables + static_cast<size_t>(b) * max_blocks;
+  const int ppt = TILE / page_size;  // pages per tile
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kDecStages; ++s) mbar_init(full0 + 8 * s, 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  __syncthreads();
+
+  auto issue = [&](int t, int stage) {
+    const uint32_t bar = full0 + 8 * stage;
+    const uint32_t k_dst = stage0 + stage * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
+    mbar_arrive_expect_tx(bar, 2 * TILE_BYTES);
+    for (int p = 0; p < ppt; ++p) {
+      int bi = t * ppt + p;
+      if (bi * page_size >= hi) bi = (hi - 1) / page_size;  // beyond the context: re-read the last page (masked)
+      int blk = bi < max_blocks ? bt[bi] : -1;
+      if (blk < 0 || blk >= num_blocks) {
+        if (status) atomicCAS(status, 0, PXL_DEV_BAD_INDEX);
+        blk = 0;
+      }
+      const int row0 = (blk * Hkv + kvh) * page_size;
+      const uint32_t off = p * page_size * 128;
+      tma_load_2d(k_dst + off, &tm_k, bar, 0, row0);
+      tma_load_2d(k_dst + TILE * 128 + off, &tm_k, bar, 64, row0);
+      tma_load_2d(v_dst + off, &tm_v, bar, 0, row0);
+      tma_load_2d(v_dst + TILE * 128 + off, &tm_v, bar, 64, row0);
+    }
+  };
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kDecStages - 1 && i < n_tiles; ++i) issue(t_begin + i, i);
+  }
+
+  uint32_t qf[D / 16][4];
+  {
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const bf16* q_lo = q + static_cast<size_t>(b) * q_stride + (kvh * G + r_lo) * D;
+    const bf16* q_hi = q + static_cast<size_t>(b) * q_stride + (kvh * G + r_hi) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int c = ks * 16 + 2 * (lane & 3);
+      qf[ks][0] = r_lo < G ? *reinterpret_cast<const uint32_t*>(q_lo + c) : 0u;
+      qf[ks][1] = r_hi < G ? *reinterpret_cast<const uint32_t*>(q_hi + c) : 0u;
+      qf[ks][2] = r_lo < G ? *reinterpret_cast<const uint32_t*>(q_lo + c + 8) : 0u;
+      qf[ks][3] = r_hi < G ? *reinterpret_cast<const uint32_t*>(q_hi + c + 8) : 0u;
+    }
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+  int failed = 0;
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it % kDecStages;
+    // everyone is done with tile it-1, whose buffer is the one refilled below
+    if (__syncthreads_or(failed)) {
+      failed = 1;
+      break;
+    }
+    if (threadIdx.x == 0 && it + kDecStages - 1 < n_tiles)
+      issue(t_begin + it + kDecStages - 1, (it + kDecStages - 1) % kDecStages);
+    if (!mbar_wait_bounded(full0 + 8 * stage, (it / kDecStages) & 1, abort_flag, status, PXL_DEV_TIMEOUT_FULL)) {
+      failed = 1;
+      continue;  // reported to the whole CTA at the next barrier
+    }
+    const int t = t_begin + it;
+    const uint32_t k_smem = stage0 + stage * 2 * TILE_BYTES, v_smem = k_smem + TILE_BYTES;
+    const int r0 = warp * 16;
+    const int tok_base = t * TILE + r0;
+    if (tok_base < hi && tok_base + 16 > lo) {  // warp-uniform
+      float s[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      qk_16x16<D, true>(qf, k_smem, r0, s[0], s[1]);
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = tok_base + j * 8 + 2 * (lane & 3) + (e & 1);
+          const bool valid = tok < hi && tok >= lo;
+          s[j][e] = valid ? s[j][e] * scale_log2 : -INFINITY;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+        }
+      }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = quad_max(mx[h]);
+        const float m_new = fmaxf(m_run[h], mx[h]);
+        m_use[h] = (m_new == -INFINITY) ? 0.f : m_new;
+        corr[h] = exp2f(m_run[h] - m_use[h]);
+        m_run[h] = m_new;
+      }
+      float ps[2] = {0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[j][e] = exp2f(s[j][e] - m_use[e >> 1]);
+          ps[e >> 1] += s[j][e];
+        }
+      l_run[0] = l_run[0] * corr[0] + ps[0];
+      l_run[1] = l_run[1] * corr[1] + ps[1];
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+      uint32_t pf[4];
+      pf[0] = pack_bf16x2(s[0][0], s[0][1]);
+      pf[1] = pack_bf16x2(s[0][2], s[0][3]);
+      pf[2] = pack_bf16x2(s[1][0], s[1][1]);
+      pf[3] = pack_bf16x2(s[1][2], s[1][3]);
+      pv_16x16<D, true>(pf, v_smem, r0, o);
+    }
+  }
+  if (__syncthreads_or(failed)) {
+    // loads that are still in flight must land before the CTA's shared memory is released
+    __nanosleep(200000);
+    return;
+  }
+
+  // ---- merge the four warps' partial softmax states through shared memory
+  float* o_sm = reinterpret_cast<float*>(smem);          // [4][16][D]
+  float* m_sm = o_sm + 4 * 16 * D;                       // [4][16]
+  float* l_sm = m_sm + 4 * 16;                           // [4][16]
+  l_run[0] = quad_sum(l_run[0]);
+  l_run[1] = quad_sum(l_run[1]);
+  {
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    float* ow = o_sm + warp * 16 * D;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int c = i * 8 + 2 * (lane & 3);
+      ow[r_lo * D + c] = o[i][0];
+      ow[r_lo * D + c + 1] = o[i][1];
+      ow[r_hi * D + c] = o[i][2];
+      ow[r_hi * D + c + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      m_sm[warp * 16 + r_lo] = m_run[0];
+      m_sm[warp * 16 + r_hi] = m_run[1];
+      l_sm[warp * 16 + r_lo] = l_run[0];
+      l_sm[warp * 16 + r_hi] = l_run[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += 128) {
+    const int r = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, m_sm[w * 16 + r]);
+    const int head = kvh * G + r;
+    const float sink = (sinks && num_splits == 1) ? sinks[head] * kLog2e : -INFINITY;
+    const float Mx = fmaxf(M, sink);
+    const float Mu = (Mx == -INFINITY) ? 0.f : Mx;
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(m_sm[w * 16 + r] - Mu);
+      L += l_sm[w * 16 + r] * f;
+      acc += o_sm[(w * 16 + r) * D + d] * f;
+    }
+    if (num_splits == 1) {
+      const float denom = L + exp2f(sink - Mu);
+      out[(static_cast<size_t>(b) * Hq + head) * D + d] = __float2bfloat16(denom > 0.f ? acc / denom : 0.f);
+    } else {
       float* po = workspace;
       float* plse = workspace + static_cast<size_t>(gridDim.y) * Hq * num_splits * D;
       const size_t row = (static_cast<size_t>(b) * Hq + head) * num_splits + split;
@@ -521,6 +746,28 @@ PXL_EXPORT int pxl_attn_decode(const void* q, int64_t q_stride, const void* k_ca
   if (num_splits > 1 && workspace == nullptr) return PXL_ERR_INVALID_ARG;
   const float scale_log2 = scale * kLog2e;
   dim3 grid(Hkv, B, num_splits);
+  if (D == 128 && (page_size == 16 || page_size == 32 || page_size == 64) &&
+      num_blocks * Hkv * page_size < (1ll << 31)) {
+    // TMA-fed kernel: the cache is a 2-D matrix [blocks * Hkv * page, 128], one box = one page half
+    CUtensorMap tk, tv;
+    const uint64_t rows = static_cast<uint64_t>(num_blocks) * Hkv * page_size;
+    if (!pxl_host::make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_cache, rows, 128, 128, page_size, 64) ||
+        !pxl_host::make_tmap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v_cache, rows, 128, 128, page_size, 64))
+      return PXL_ERR_TENSORMAP;
+    constexpr int SMEM = 1024 + kDecStages * 2 * TILE * 128 * 2 + 64;
+    static bool done = false;
+    if (!done) {
+      if (set_smem(attn_decode_tma_kernel, SMEM)) return PXL_ERR_CUDA;
+      done = true;
+    }
+    attn_decode_tma_kernel<<<grid, 128, SMEM, stream>>>(
+        tk, tv, static_cast<const bf16*>(q), q_stride, block_tables, ctx_lens, static_cast<bf16*>(out), workspace,
+        sinks, Hq, Hkv, page_size, max_blocks, num_blocks, scale_log2, window, num_splits, status);
+    if (num_splits > 1)
+      attn_decode_reduce_kernel<128><<<dim3(Hq, B), 128, 0, stream>>>(workspace, sinks, static_cast<bf16*>(out), Hq,
+                                                                      num_splits);
+    return check_launch();
+  }
 #define PXL_DEC(DD)                                                                              \
   {                                                                                              \
     constexpr int SMEM = 4 * TILE * DD * 2 > (4 * 16 * DD + 128) * 4 ? 4 * TILE * DD * 2         \

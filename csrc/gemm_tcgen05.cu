@@ -649,19 +649,27 @@ int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const Ge
 
 }  // namespace
 
-// Tile width heuristic: the widest tile that still yields at least one tile per SM;
-// below that the narrowest, so that small-M (decode) problems spread their weight
-// traffic over as many SMs as possible.
+// Tile width heuristic: estimated time = waves over the SMs x tile width / relative efficiency of
+// that width. Small-M (decode) problems end up with the narrowest tile, which spreads the weight
+// traffic over the most SMs; large problems take the width that wastes the least of its last wave.
 PXL_EXPORT int pxl_gemm_bf16_pick_bn(int M, int N, int epi) {
   const int sms = pxl_host::num_sms();
   const int num_m = pxl::ceil_div(M, BM);
   const int cands[3] = {256, 128, 64};
+  const double eff[3] = {1.0, 0.92, 0.72};
+  int best = 0;
+  double best_cost = 1e300;
   for (int i = 0; i < 3; ++i) {
     const int bn = cands[i];
     if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) continue;
-    if (num_m * pxl::ceil_div(N, bn) >= sms) return bn;
+    const int tiles = num_m * pxl::ceil_div(N, bn);
+    const double cost = static_cast<double>(pxl::ceil_div(tiles, sms)) * bn / eff[i];
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
   }
-  return epi == PXL_EPI_SILU_MUL ? 128 : 64;
+  return best ? best : 128;
 }
 
 PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* residual,
