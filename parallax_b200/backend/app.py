@@ -48,6 +48,13 @@ def create_app(scheduler_manage: SchedulerManage, request_handler: Optional[Requ
                        allow_headers=["*"])
     app.state.scheduler_manage = sm
 
+    @app.get("/chat")
+    async def chat_ui():
+        from pathlib import Path
+
+        page = Path(__file__).resolve().parent.parent / "frontend" / "ui" / "index.html"
+        return HTMLResponse(page.read_text())
+
     @app.post("/weight/refit")
     async def weight_refit(req: HttpRequest):
         ok = sm.weight_refit(await req.json())

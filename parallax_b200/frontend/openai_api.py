@@ -69,6 +69,15 @@ def create_app(loop: EngineLoop, tokenizer: TokenizerWrapper, model_name: str, m
     app = FastAPI(title="parallax_b200 node")
     app.state.loop, app.state.tokenizer, app.state.model_name = loop, tokenizer, model_name
 
+    @app.get("/")
+    @app.get("/ui")
+    async def ui():
+        from pathlib import Path
+
+        from fastapi.responses import HTMLResponse
+
+        return HTMLResponse((Path(__file__).resolve().parent / "ui" / "index.html").read_text())
+
     @app.get("/health")
     async def health():
         return {"status": "ok", "inflight": loop.num_inflight, "steps": loop.steps}
@@ -122,8 +131,8 @@ def create_app(loop: EngineLoop, tokenizer: TokenizerWrapper, model_name: str, m
             d: dict[str, Any] = {}
             if first:
                 d["role"] = "assistant"
-            if delta:
-                d["content"] = delta
+            if delta is not None:
+                d["content"] = delta      # may be "" while a multi-byte character is still incomplete
             choice = {"index": 0, "delta": d, "finish_reason": finish}
             obj = "chat.completion.chunk"
         else:

@@ -1,0 +1,57 @@
+"""The serving benchmark client against a live node frontend (tiny CPU model, real HTTP + SSE)."""
+
+import importlib.util
+import os
+import time
+
+import pytest
+
+from parallax_b200.engine.engine import Engine
+from parallax_b200.engine.service import EngineLoop
+from parallax_b200.frontend.openai_api import create_app
+from parallax_b200.frontend.tokenizer import TokenizerWrapper
+from parallax_b200.launch import serve_http
+from parallax_b200.models.config import named_config
+from parallax_b200.parallel.launcher import free_port
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load_client():
+    spec = importlib.util.spec_from_file_location("benchmark_serving", os.path.join(ROOT, "benchmarks", "benchmark_serving.py"))
+    mod = importlib.util.module_from_spec(spec)
+    import sys
+
+    sys.modules["benchmark_serving"] = mod      # dataclasses look the module up by name
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("chat", [False, True])
+def test_benchmark_client_end_to_end(chat):
+    pytest.importorskip("aiohttp")
+    cfg = named_config("tiny")
+    eng = Engine(cfg, device="cpu", num_blocks=256, page_size=16, max_batch_size=8, max_total_length=512)
+    loop = EngineLoop(eng)
+    loop.start()
+    tok = TokenizerWrapper.from_pretrained(None, vocab_size=cfg.vocab_size)
+    app = create_app(loop, tok, "tiny", max_model_len=512)
+    port = free_port()
+    server, thread = serve_http(app, "127.0.0.1", port, "warning")
+    try:
+        for _ in range(100):
+            if server.started:
+                break
+            time.sleep(0.05)
+        client = _load_client()
+        argv = ["--base-url", f"http://127.0.0.1:{port}", "--model", "tiny", "--num-prompts", "6",
+                "--random-input-len", "24", "--random-output-len", "5", "--request-rate", "200", "--ignore-eos",
+                "--goodput", "ttft:60000", "e2el:120000"] + (["--chat"] if chat else [])
+        rep = client.main(argv)
+        assert rep["completed"] == 6 and rep["failed"] == 0, rep
+        assert rep["total_output_tokens"] >= 6 and rep["mean_ttft_ms"] > 0 and rep["output_throughput"] > 0
+        assert rep["request_goodput"] > 0
+    finally:
+        server.should_exit = True
+        thread.join(5)
+        loop.stop()
