@@ -456,7 +456,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
                 if (ep.bias) {
-                  const bf16x8 b = ld_bf16x8(ep.bias + col);
+                  // indexed by the row of W: with grouped experts every expert has its own bias
+                  const bf16x8 b = ld_bf16x8(ep.bias + tc.b_row + c0 + v * 8);
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
                     const float2 bb = unpack_bf16x2(b.u[j]);
@@ -707,10 +708,10 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
 // Grouped GEMM over experts: for every m-tile i listed on the device,
 //   C[rows of tile i, :] = A[rows of tile i, :] * W[expert_i]^T
 // A: [P, K] activations permuted so that each expert's tokens are contiguous; W: [E*N, K]
-// (expert matrices stacked); C: [P, N] (N/2 columns with PXL_EPI_SILU_MUL).
+// (expert matrices stacked); C: [P, N] (N/2 columns with PXL_EPI_SILU_MUL); bias: optional [E*N].
 // max_m_tiles bounds the device-side count and sizes the grid.
-PXL_EXPORT int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int P, int E, int N,
-                                     int K, int lda, int ldw, int ldc, const int* mt_expert,
+PXL_EXPORT int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, const void* bias, int P, int E,
+                                     int N, int K, int lda, int ldw, int ldc, const int* mt_expert,
                                      const int* mt_row0, const int* mt_row_end, const int* num_mt,
                                      int max_m_tiles, int epi, int bn, int* status,
                                      cudaStream_t stream) {
@@ -729,7 +730,7 @@ PXL_EXPORT int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int 
   ep.C = static_cast<pxl::bf16*>(C);
   ep.C_f32 = static_cast<float*>(C);
   ep.residual = nullptr;
-  ep.bias = nullptr;
+  ep.bias = static_cast<const pxl::bf16*>(bias);  // optional [E * N], applied with PXL_EPI_NONE / F32
   ep.ldc = ldc;
   GemmGroupArgs grp{mt_expert, mt_row0, mt_row_end, num_mt, N};
   const int max_tiles = max_m_tiles * pxl::ceil_div(N, bn);

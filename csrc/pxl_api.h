@@ -113,7 +113,7 @@ int pxl_moe_gather(const void* x, const int* src_tok, const int* n_rows, void* x
 int pxl_moe_combine(const void* y_perm, const int* pos_of, const float* w, const void* base,
                     void* out, int T, int k, int H, pxl_stream_t stream);
 // Grouped GEMM over experts (see gemm_tcgen05.cu).
-int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, int P, int E, int N, int K,
+int pxl_gemm_bf16_grouped(const void* A, const void* W, void* C, const void* bias, int P, int E, int N, int K,
                           int lda, int ldw, int ldc, const int* mt_expert, const int* mt_row0,
                           const int* mt_row_end, const int* num_mt, int max_m_tiles, int epi,
                           int bn, int* status, pxl_stream_t stream);

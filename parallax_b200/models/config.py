@@ -220,7 +220,7 @@ def config_from_hf(cfg: dict) -> ModelConfig:
         n_group=cfg.get("n_group") or 1,
         topk_group=cfg.get("topk_group") or 1,
         moe_router_bias=cfg.get("topk_method") == "noaux_tc" or bool(cfg.get("use_routing_bias", False)),
-        swiglu_limit=float(cfg.get("swiglu_limit", 0.0) or 0.0),
+        swiglu_limit=float(cfg.get("swiglu_limit") or (7.0 if mt == "gpt_oss" else 0.0)),
         q_lora_rank=cfg.get("q_lora_rank") or 0,
         kv_lora_rank=cfg.get("kv_lora_rank") or 0,
         qk_nope_head_dim=cfg.get("qk_nope_head_dim") or 0,

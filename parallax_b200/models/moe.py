@@ -32,13 +32,19 @@ class MoEWeights:
         self.shared_down: Optional[torch.Tensor] = None  # [H, Is]
         self.shared_gate: Optional[torch.Tensor] = None  # [1, H] sigmoid gate on the shared expert (Qwen2-MoE style)
         self.fp8: Optional[dict] = None                 # block-scaled e4m3 copies: name -> (q, scales per 64 rows)
+        self.router_bias: Optional[torch.Tensor] = None  # [E] (GPT-OSS)
+        self.b1: Optional[torch.Tensor] = None          # [E*2I] expert biases of the first projection
+        self.b2: Optional[torch.Tensor] = None          # [E*H]
+        # 0: SwiGLU fused into the GEMM epilogue (w1 interleaved); 1: clipped swigluoai (w1 = [gate | up] per expert)
+        self.act_mode = 1 if (cfg.swiglu_limit or cfg.hidden_act == "swigluoai") else 0
+        self.limit = float(cfg.swiglu_limit or 7.0)
         self.num_experts = cfg.num_experts
         self.top_k = cfg.num_experts_per_tok
         self.mode = 1 if cfg.scoring_func == "sigmoid" else 0
 
     def tensors(self):
         ts = [t for t in (self.router, self.e_bias, self.w1, self.w2, self.shared_gu, self.shared_down,
-                          self.shared_gate) if t is not None]
+                          self.shared_gate, self.router_bias, self.b1, self.b2) if t is not None]
         for q, s in (self.fp8 or {}).values():
             ts += [q, s]
         return ts
@@ -87,7 +93,12 @@ class MoEWeights:
             m.e_bias = torch.zeros(E, device=device, dtype=torch.float32)
         g = rnd(E * I, H, k=1).view(E, I, H)
         u = rnd(E * I, H, k=2).view(E, I, H)
-        m.w1 = torch.stack([ops.interleave_gate_up(g[e], u[e]) for e in range(E)]).view(E * 2 * I, H).contiguous()
+        if m.act_mode == 0:
+            m.w1 = torch.stack([ops.interleave_gate_up(g[e], u[e]) for e in range(E)]).view(E * 2 * I, H).contiguous()
+        else:
+            m.w1 = torch.cat([g, u], dim=1).reshape(E * 2 * I, H).contiguous()
+            m.b1, m.b2 = rnd(E * 2 * I, k=7), rnd(E * H, k=8)
+            m.router_bias = rnd(E, k=9)
         m.w2 = rnd(E * H, I, k=3)
         Is = cfg.shared_expert_intermediate_size or (cfg.n_shared_experts * I)
         if Is:
@@ -108,11 +119,28 @@ class MoEWeights:
                 return None
             return t.to(device=device, dtype=dt)
 
+        fused = get("experts.gate_up_proj", required=False)
+        if fused is not None and get("router.weight", required=False) is not None:
+            # GPT-OSS layout: gate_up_proj [E, H, 2I] with gate / up in even / odd columns, expert biases
+            m.router = get("router.weight").contiguous()
+            m.router_bias = get("router.bias", required=False)
+            I2 = fused.shape[2]
+            gate, up = fused[:, :, 0::2], fused[:, :, 1::2]                       # [E, H, I]
+            m.w1 = torch.cat([gate.transpose(1, 2), up.transpose(1, 2)], dim=1).reshape(E * I2, -1).contiguous()
+            b = get("experts.gate_up_proj_bias", required=False)
+            if b is not None:
+                m.b1 = torch.cat([b[:, 0::2], b[:, 1::2]], dim=1).reshape(-1).contiguous()
+            m.w2 = get("experts.down_proj").transpose(1, 2).reshape(E * fused.shape[1], -1).contiguous()   # [E*H, I]
+            b2 = get("experts.down_proj_bias", required=False)
+            m.b2 = None if b2 is None else b2.reshape(-1).contiguous()
+            m.act_mode = 1
+            return m
         m.router = get("gate.weight").contiguous()
         m.e_bias = get("gate.e_score_correction_bias", required=False, dt=torch.float32)
         w1, w2 = [], []
         for e in range(E):
-            w1.append(ops.interleave_gate_up(get(f"experts.{e}.gate_proj.weight"), get(f"experts.{e}.up_proj.weight")))
+            g_w, u_w = get(f"experts.{e}.gate_proj.weight"), get(f"experts.{e}.up_proj.weight")
+            w1.append(ops.interleave_gate_up(g_w, u_w) if m.act_mode == 0 else torch.cat([g_w, u_w], dim=0))
             w2.append(get(f"experts.{e}.down_proj.weight"))
         m.w1 = torch.cat(w1, dim=0).contiguous()
         m.w2 = torch.cat(w2, dim=0).contiguous()
@@ -127,7 +155,7 @@ class MoEWeights:
     # ------------------------------------------------------------------ forward
     def route(self, xn: torch.Tensor):
         cfg = self.cfg
-        logits = ops.linear(xn, self.router, epi=ops.EPI_F32)
+        logits = ops.linear(xn, self.router, bias=self.router_bias, epi=ops.EPI_F32)
         return ops.moe_route(logits, self.e_bias, self.top_k, self.mode, cfg.norm_topk_prob, cfg.n_group,
                              cfg.topk_group, cfg.routed_scaling_factor)
 
@@ -148,4 +176,7 @@ class MoEWeights:
             else:
                 gate = torch.sigmoid(xn.float() @ self.shared_gate.float().t()).to(h.dtype)  # [T, 1]: too thin for a tile
                 base = h + gate * ops.linear(act, self.shared_down)
+        if self.act_mode:
+            return ops.moe_ffn(xn, ids, w, self.w1, self.w2, self.num_experts, base=base, act_mode=self.act_mode,
+                               limit=self.limit, b1=self.b1, b2=self.b2)
         return ops.moe_ffn(xn, ids, w, self.w1, self.w2, self.num_experts, base=base)

@@ -40,8 +40,10 @@ def rope_inv_freq(cfg: ModelConfig) -> tuple[torch.Tensor, float]:
         old = float(sc.get("original_max_position_embeddings", cfg.max_position_embeddings))
         beta_fast = float(sc.get("beta_fast", 32))
         beta_slow = float(sc.get("beta_slow", 1))
-        lo = max(math.floor(_yarn_find_dim(beta_fast, rot, base, int(old))), 0)
-        hi = min(math.ceil(_yarn_find_dim(beta_slow, rot, base, int(old))), rot - 1)
+        lo, hi = _yarn_find_dim(beta_fast, rot, base, int(old)), _yarn_find_dim(beta_slow, rot, base, int(old))
+        if sc.get("truncate", True):
+            lo, hi = math.floor(lo), math.ceil(hi)
+        lo, hi = max(lo, 0), min(hi, rot - 1)
         ramp = ((torch.arange(rot // 2, dtype=torch.float64) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
         extrap = 1.0 - ramp
         inv_y = inv / factor * (1 - extrap) + inv * extrap

@@ -63,7 +63,7 @@ _SIGS = {
     "pxl_moe_align": [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, _P],
     "pxl_moe_gather": [_P, _P, _P, _P, c_int, c_int, _P],
     "pxl_moe_combine": [_P, _P, _P, _P, _P, c_int, c_int, c_int, _P],
-    "pxl_gemm_bf16_grouped": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
+    "pxl_gemm_bf16_grouped": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                               c_int, c_int, c_int, _P, _P],
     "pxl_mla_kv_prep": [_P, c_int64, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int64, c_float, _P, _P],
     "pxl_mla_q_prep": [_P, c_int64, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],

@@ -389,13 +389,13 @@ def moe_gather(x: torch.Tensor, plan: MoEPlan) -> torch.Tensor:
 
 
 def grouped_linear(a: torch.Tensor, w: torch.Tensor, plan: MoEPlan, num_local_experts: int,
-                   epi: int = EPI_NONE, bn: int = 0) -> torch.Tensor:
+                   epi: int = EPI_NONE, bn: int = 0, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``a [P, K]`` (expert-sorted rows) times stacked expert weights ``w [E*N, K]``."""
     P, K = a.shape
     N = w.shape[0] // num_local_experts
     n_out = N // 2 if epi == EPI_SILU_MUL else N
     out = torch.empty((P, n_out), dtype=a.dtype, device=a.device)
-    check(_lib.lib().pxl_gemm_bf16_grouped(a.data_ptr(), w.data_ptr(), out.data_ptr(), P, num_local_experts, N, K,
+    check(_lib.lib().pxl_gemm_bf16_grouped(a.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(bias), P, num_local_experts, N, K,
                                            a.stride(0), w.stride(0), out.stride(0), plan.mt_expert.data_ptr(),
                                            plan.mt_row0.data_ptr(), plan.mt_row_end.data_ptr(),
                                            plan.num_mt.data_ptr(), plan.max_mt, epi, bn,
@@ -416,14 +416,22 @@ def moe_combine(y_perm: torch.Tensor, plan: MoEPlan, weights: torch.Tensor, base
 
 
 def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
-            num_experts: int, base: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``base + sum_j weights[:, j] * FFN_{ids[:, j]}(x)`` with SwiGLU experts.
+            num_experts: int, base: Optional[torch.Tensor] = None, act_mode: int = 0, limit: float = 0.0,
+            b1: Optional[torch.Tensor] = None, b2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``base + sum_j weights[:, j] * FFN_{ids[:, j]}(x)``.
 
-    w1: ``[E * 2I, H]`` gate/up rows interleaved per expert; w2: ``[E * H, I]``."""
+    act_mode 0: SwiGLU fused into the first GEMM's epilogue; w1 ``[E * 2I, H]`` has gate/up rows
+    interleaved per expert. act_mode 1: clipped ``swigluoai`` (GPT-OSS, MiniMax-M3): w1 holds
+    ``[gate rows | up rows]`` per expert, optional expert biases b1 ``[E * 2I]`` / b2 ``[E * H]``.
+    w2: ``[E * H, I]``."""
     plan = moe_align(ids, num_experts)
     xp = moe_gather(x, plan)
-    act = grouped_linear(xp, w1, plan, num_experts, epi=EPI_SILU_MUL)
-    y = grouped_linear(act, w2, plan, num_experts)
+    if act_mode == 0:
+        act = grouped_linear(xp, w1, plan, num_experts, epi=EPI_SILU_MUL)
+    else:
+        gu = grouped_linear(xp, w1, plan, num_experts, bias=b1)
+        act = act_mul(gu, mode=act_mode, limit=limit)
+    y = grouped_linear(act, w2, plan, num_experts, bias=b2)
     return moe_combine(y, plan, weights, base, x.shape[0])
 
 

@@ -293,8 +293,9 @@ def moe_route(logits, e_bias, k, mode=0, renorm=True, n_group=1, topk_group=1, r
     return ids.to(torch.int32), (w * routed_scale).float()
 
 
-def moe_ffn(x, ids, weights, w1, w2, num_experts, base=None):
-    """Dense restatement: loop over experts. w1 ``[E*2I, H]`` (interleaved), w2 ``[E*H, I]``."""
+def moe_ffn(x, ids, weights, w1, w2, num_experts, base=None, act_mode: int = 0, limit: float = 0.0, b1=None, b2=None):
+    """Dense restatement: loop over experts. w1 ``[E*2I, H]`` (gate/up interleaved for act_mode 0,
+    ``[gate | up]`` per expert otherwise), w2 ``[E*H, I]``, optional expert biases b1 / b2."""
     T, H = x.shape
     two_i = w1.shape[0] // num_experts
     w1e = w1.view(num_experts, two_i, H)
@@ -304,8 +305,12 @@ def moe_ffn(x, ids, weights, w1, w2, num_experts, base=None):
         tok, slot = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue
-        a = linear(x[tok], w1e[e], epi=EPI_SILU_MUL)
-        y = linear(a, w2e[e])
+        if act_mode == 0:
+            a = linear(x[tok], w1e[e], epi=EPI_SILU_MUL)
+        else:
+            gu = linear(x[tok], w1e[e], bias=None if b1 is None else b1.view(num_experts, two_i)[e])
+            a = act_mul(gu, mode=act_mode, limit=limit)
+        y = linear(a, w2e[e], bias=None if b2 is None else b2.view(num_experts, H)[e])
         out.index_add_(0, tok, y.float() * weights[tok, slot][:, None])
     if base is not None:
         out = out + base.float()
