@@ -101,3 +101,22 @@ def test_moe_engine_gpu_matches_cpu():
     gpu, lg = first_logits(DEV, torch.bfloat16)
     _, lc = first_logits("cpu", torch.float32, gpu)
     assert _rel(lg, lc) < 5e-2
+
+
+def test_moe_ffn_swigluoai_with_expert_biases(cu):
+    """Clipped swigluoai experts (GPT-OSS / MiniMax-M3): plain [gate | up] rows, biases per expert."""
+    torch.manual_seed(4)
+    T, E, k, H, I = 333, 8, 2, 512, 256
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    base = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    w1 = (torch.randn(E * 2 * I, H, device=DEV) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E * H, I, device=DEV) * 0.05).to(torch.bfloat16)
+    b1 = (torch.randn(E * 2 * I, device=DEV) * 0.5).to(torch.bfloat16)
+    b2 = (torch.randn(E * H, device=DEV) * 0.5).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)]).int()
+    w = torch.rand(T, k, device=DEV)
+    got = cu.moe_ffn(x, ids, w, w1, w2, E, base=base, act_mode=1, limit=7.0, b1=b1, b2=b2)
+    want = ref.moe_ffn(x.cpu(), ids.cpu(), w.cpu(), w1.cpu().float(), w2.cpu().float(), E, base=base.cpu(), act_mode=1,
+                       limit=7.0, b1=b1.cpu().float(), b2=b2.cpu().float())
+    cu.check_status(torch.device(DEV))
+    assert _rel(got, want) < 1e-2
