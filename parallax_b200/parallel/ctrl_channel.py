@@ -17,7 +17,7 @@ from multiprocessing import shared_memory
 
 import numpy as np
 
-_HDR = 64            # bytes: [0:8] reserved, then 8 bytes per reader cursor (up to 7 readers)
+_HDR = 128           # bytes: [0:8] reserved, 7 reader cursors (int64), then 7 reader heartbeats (int64 ns)
 _SLOT_HDR = 16       # seq (int64), nbytes (int64)
 
 
@@ -42,6 +42,9 @@ class CtrlChannel:
                 pass
         self.owner = create
         self.cursors = np.ndarray((7,), dtype=np.int64, buffer=self.shm.buf, offset=8)
+        self.beats = np.ndarray((7,), dtype=np.int64, buffer=self.shm.buf, offset=64)
+        if not create:
+            self.beat()
         self.seq = 0      # writer: messages published; reader: messages consumed
 
     def _slot(self, seq: int):
@@ -76,16 +79,31 @@ class CtrlChannel:
             spins += 1
             if spins > 2000:             # stay hot for a moment, then yield the core
                 time.sleep(0.0001)
-                if time.monotonic() - t0 > timeout_s:
-                    raise TimeoutError("no control message from rank 0")
+                if spins % 512 == 0:
+                    self.beat()          # an idle reader is still alive
+                    if time.monotonic() - t0 > timeout_s:
+                        raise TimeoutError("no control message from rank 0")
         n = int(hdr[1])
         obj = pickle.loads(bytes(self.shm.buf[off:off + n]))
         self.seq = nxt
         self.cursors[self.reader_index] = nxt
+        self.beat()
         return obj
+
+    # ------------------------------------------------------------------ liveness
+    def beat(self) -> None:
+        """Reader: publish "alive now" (wall-clock ns; all processes share the box's clock)."""
+        if self.reader_index >= 0:
+            self.beats[self.reader_index] = time.time_ns()
+
+    def stale_readers(self, max_age_s: float) -> list[int]:
+        """Writer: indices of readers whose last heartbeat is older than ``max_age_s`` (0 = never seen)."""
+        now = time.time_ns()
+        return [i for i in range(self.n_readers) if now - int(self.beats[i]) > max_age_s * 1e9]
 
     def close(self) -> None:
         self.cursors = None
+        self.beats = None
         try:
             self.shm.close()
             if self.owner:

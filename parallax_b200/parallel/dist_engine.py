@@ -93,7 +93,8 @@ class DistEngine:
                  chunked_prefill_size: Optional[int] = 1024, enable_prefix_cache: bool = True,
                  max_total_length: int = 32768, request_timeout_s: Optional[float] = 600, eos_token_id=None,
                  seed: int = 0, weights: Optional[dict] = None, fused: Optional[bool] = None,
-                 max_in_flight: Optional[int] = None, weights_prefiltered: bool = False):
+                 max_in_flight: Optional[int] = None, weights_prefiltered: bool = False,
+                 liveness_timeout_s: float = 10.0, step_timeout_s: float = 600.0):
         assert dist.is_initialized(), "init the default process group first (nccl on GPUs, gloo on CPU)"
         self.cfg = cfg
         self.device = torch.device(device)
@@ -145,6 +146,7 @@ class DistEngine:
         dist.all_reduce(nb, op=dist.ReduceOp.MIN, group=self.ctrl)
         self.num_blocks = int(nb)
         self.max_in_flight = max_in_flight or pp
+        self.liveness_timeout_s, self.step_timeout_s = liveness_timeout_s, step_timeout_s
         self._ret_stream = torch.cuda.Stream(self.device) if on_gpu else None
         self._warm_links()
         ratio = micro_batch_ratio or pp
@@ -396,6 +398,50 @@ class DistEngine:
         self.in_flight.append((arrays, res))
         return True
 
+    def _wait_return(self, ev, work) -> None:
+        """Wait for the tokens of the oldest micro-batch while watching the other ranks' heartbeats:
+        a rank that stopped (crashed process, stuck host loop) turns into an exception here instead
+        of an endless wait, and the serving loop fails the affected requests."""
+        t0 = time.monotonic()
+        sleep = 0.0
+        waiter = None
+        if ev is None:
+            # gloo receive handles only complete inside wait(): block in a helper thread and watch it
+            import threading
+
+            err: list = []
+
+            def _wait():
+                try:
+                    work.wait()
+                except Exception as exc:      # e.g. the peer's connection was reset
+                    err.append(exc)
+
+            waiter = threading.Thread(target=_wait, daemon=True)
+            waiter.start()
+        while True:
+            if waiter is not None:
+                waiter.join(0.0 if sleep == 0.0 else 0.01)
+                done = not waiter.is_alive()
+            else:
+                done = ev.query()
+            if done:
+                if waiter is not None and err:
+                    raise RuntimeError(f"the last pipeline stage stopped responding: {err[0]}")
+                return
+            if sleep:
+                time.sleep(sleep)
+            waited = time.monotonic() - t0
+            if waited > 0.002:
+                sleep = 0.0002
+            if waited > self.liveness_timeout_s / 4:
+                stale = self.chan.stale_readers(self.liveness_timeout_s)
+                if stale:
+                    raise RuntimeError(f"rank(s) {[i + 1 for i in stale]} stopped responding "
+                                       f"(no heartbeat for {self.liveness_timeout_s:.0f} s)")
+            if waited > self.step_timeout_s:
+                raise TimeoutError(f"no tokens came back within {self.step_timeout_s:.0f} s")
+
     def _collect(self) -> list:
         arrays, res = self.in_flight.popleft()
         out = []
@@ -406,11 +452,9 @@ class DistEngine:
             tw = time.perf_counter()
             if kind == "recv":
                 t, work, host, ev = t
+                self._wait_return(ev, work)
                 if ev is not None:
-                    ev.synchronize()
                     t = host
-                else:
-                    work.wait()
             token_list = t.tolist()
             self.host_s["wait"] += time.perf_counter() - tw
         sched = self.scheduler

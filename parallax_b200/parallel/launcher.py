@@ -132,10 +132,11 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
     from parallax_b200.launch import serve_http
     from parallax_b200.utils.shared_state import SharedState
 
-    if getattr(args, "ep_size", 1) > 1:
-        raise NotImplementedError("expert parallelism is configured per MoE stage, not by the launcher")
+    # experts of MoE layers are sharded over the stage's tensor-parallel group, so an expert-parallel
+    # size simply asks for a group of that many ranks
+    tp_size = max(args.tp_size, getattr(args, "ep_size", 1))
     device_type = "cuda" if torch.cuda.is_available() else "cpu"
-    spec = dict(model_path=path, model_name=name.split("/")[-1], pp=args.pp_size, tp=args.tp_size, device_type=device_type,
+    spec = dict(model_path=path, model_name=name.split("/")[-1], pp=args.pp_size, tp=tp_size, device_type=device_type,
                 dtype=args.dtype if args.dtype in ("bfloat16", "float16") else "bfloat16",
                 page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
                 max_batch_size=args.max_batch_size, max_num_tokens_per_batch=args.max_num_tokens_per_batch,
@@ -145,13 +146,13 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
                 lora_paths=(args.lora_paths or []) if args.enable_lora else [], log_level=args.log_level)
     engine, procs = launch_dist_engine(spec)
     state = SharedState.create(in_process=True)
-    state.set_layer_allocation(name, 0, cfg.num_hidden_layers, args.tp_size, changed=False)
+    state.set_layer_allocation(name, 0, cfg.num_hidden_layers, tp_size, changed=False)
     loop = EngineLoop(engine, shared_state=state)
     loop.start()
     tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size)
     app = create_app(loop, tok, name, max_model_len=args.max_sequence_length)
     state.set_status("available")
-    logger.info("serving %s on http://%s:%d with pp=%d tp=%d", name, args.host, args.port, args.pp_size, args.tp_size)
+    logger.info("serving %s on http://%s:%d with pp=%d tp=%d", name, args.host, args.port, args.pp_size, tp_size)
     _server, thread = serve_http(app, args.host, args.port, args.log_level)
     try:
         while thread.is_alive():

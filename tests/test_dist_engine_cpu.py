@@ -71,3 +71,28 @@ def test_dist_engine_moe_expert_parallel(tmp_path):
     want = _single(model="tiny-moe")
     got = _run_group(1, 2, tmp_path, model="tiny-moe")
     assert got["outputs"] == want
+
+
+def test_rank_loss_is_detected_on_the_host(tmp_path):
+    """Failure detection without touching a device: the second pipeline rank exits between steps;
+    the scheduling rank sees its heartbeat stop and raises within seconds."""
+    spec = dict(model_name="tiny", pp=2, tp=1, device_type="cpu", num_blocks=256, page_size=16, max_batch_size=4,
+                max_num_tokens_per_batch=64, chunked_prefill_size=16, max_total_length=256, seed=0,
+                prompts=[[5, 9, 77, 3], [100, 101, 102]], plans_before_exit=6)
+    helper = os.path.join(os.path.dirname(__file__), "helpers", "dist_engine_fail_rank.py")
+    port = free_port()
+    out = tmp_path / "fail.json"
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   OMP_NUM_THREADS="2", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        procs.append(subprocess.Popen([sys.executable, helper, json.dumps(spec), str(out)], env=env))
+    for p in procs:
+        try:
+            p.wait(timeout=120)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            raise AssertionError("the scheduling rank kept waiting for a rank that had left")
+    res = json.loads(out.read_text())
+    assert res["error"] is not None and "stopped responding" in res["error"], res
+    assert res["steps"] >= 3 and res["seconds"] < 60, res
