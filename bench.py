@@ -169,9 +169,12 @@ def run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid) -> No
     # a couple of micro-batches more than stages, so that a stage always has one queued while the
     # scheduler on rank 0 commits the tokens of another and plans its next turn
     n_mb = 1 if pp == 1 else pp + (1 if pp <= 2 else 2)
+    # prompts are prefilled in slices so that every micro-batch carries a similar share of the
+    # ~1500 prompt tokens that arrive per rotation (an uneven micro-batch stalls the other stages)
+    chunk = 4096 if pp == 1 else (512 if n_mb <= 4 else 256)
     eng = DistEngine(cfg, pp, tp, device, torch.bfloat16, page_size=16, kv_fraction=0.85, max_batch_size=conc,
                      max_num_tokens_per_batch=8192 + conc, micro_batch_ratio=n_mb, max_in_flight=n_mb,
-                     chunked_prefill_size=4096,
+                     chunked_prefill_size=chunk,
                      enable_prefix_cache=True, max_total_length=IN_LEN + OUT_LEN + 64, request_timeout_s=None, seed=0)
     if rank != 0:
         eng.serve_forever()
