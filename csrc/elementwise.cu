@@ -58,6 +58,40 @@ rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __r
   }
 }
 
+// Row-strided variant (rows of a column slice of a wider matrix; in place when out == x).
+__global__ void __launch_bounds__(256)
+rmsnorm_strided_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restrict__ w, bf16* __restrict__ out,
+                       int64_t ldo, int H, float eps, float w_offset) {
+  __shared__ float red[32];
+  const size_t row = blockIdx.x;
+  const bf16* xr = x + row * ldx;
+  bf16* outr = out + row * ldo;
+  const int nvec = H >> 3;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const bf16x8 a = ld_bf16x8(xr + v * 8);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(a.u[j]);
+      ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  ss = block_reduce_sum(ss, red);
+  const float inv = rsqrtf(ss / static_cast<float>(H) + eps);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const bf16x8 a = ld_bf16x8(xr + v * 8);
+    const bf16x8 ww = ld_bf16x8(w + v * 8);
+    bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(a.u[j]);
+      const float2 g = unpack_bf16x2(ww.u[j]);
+      o.u[j] = pack_bf16x2(f.x * inv * (g.x + w_offset), f.y * inv * (g.y + w_offset));
+    }
+    st_bf16x8(outr + v * 8, o);
+  }
+}
+
 // ------------------------------------------------- q/k norm + RoPE + cache scatter
 // One warp per (token, head slot). Head slots: [0,Hq) q heads, [Hq,Hq+Hkv) k heads,
 // [Hq+Hkv, Hq+2Hkv) v heads. D <= 256, D % 32 == 0... each lane owns D/32 contiguous dims.
@@ -254,6 +288,15 @@ PXL_EXPORT int pxl_rmsnorm(const void* x, const void* weight, void* out, void* r
                                                  static_cast<const bf16*>(weight),
                                                  static_cast<bf16*>(out), nullptr, H, eps,
                                                  w_offset);
+  return check_launch();
+}
+
+PXL_EXPORT int pxl_rmsnorm_strided(const void* x, int64_t ldx, const void* weight, void* out, int64_t ldo, int T,
+                                   int H, float eps, float w_offset, pxl_stream_t stream) {
+  if (T <= 0) return PXL_OK;
+  if ((H % 8) || (ldx % 8) || (ldo % 8)) return PXL_ERR_INVALID_ARG;
+  rmsnorm_strided_kernel<<<T, 256, 0, stream>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(weight),
+                                                static_cast<bf16*>(out), ldo, H, eps, w_offset);
   return check_launch();
 }
 

@@ -39,6 +39,9 @@ int pxl_gemm_bf16_pick_bn(int M, int N, int epi);
 // residual += x first (in place) and the norm is taken of the sum.
 int pxl_rmsnorm(const void* x, const void* weight, void* out, void* residual, int T, int H,
                 float eps, float w_offset, pxl_stream_t stream);
+// Same without residual for rows with their own strides (a column slice of a wider matrix; out may be x).
+int pxl_rmsnorm_strided(const void* x, int64_t ldx, const void* weight, void* out, int64_t ldo, int T, int H,
+                        float eps, float w_offset, pxl_stream_t stream);
 // Per-head q/k RMSNorm (optional) + rotary embedding (neox pairing, first `rot_dim`
 // dims) on a packed qkv activation [T, (Hq + 2*Hkv) * D], writing q in place and
 // scattering k, v into the paged cache [blocks, Hkv, page, D] at slot_mapping[t]

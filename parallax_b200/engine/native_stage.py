@@ -72,6 +72,8 @@ class NativeDenseStage:
     def supported(stage) -> bool:
         if stage.device.type != "cuda" or not stage.layers or not stage.kv_caches:
             return False
+        if stage.cfg.qk_norm_full or any(getattr(lw, "w_g", None) is not None for lw in stage.layers):
+            return False
         return all(lw.moe is None and lw.w_gu is not None and isinstance(lw.w_gu, torch.Tensor) for lw in stage.layers)
 
     def _ensure(self, T: int, Bd: int, d_max_ctx: int) -> None:

@@ -195,6 +195,7 @@ def config_from_hf(cfg: dict) -> ModelConfig:
         rope_theta=float(rope_theta or 10000.0),
         rope_scaling=rope_scaling if isinstance(rope_scaling, dict) else None,
         partial_rotary_factor=float(cfg.get("partial_rotary_factor")
+                                    or (rope_scaling or {}).get("partial_rotary_factor")
                                     or (cfg["rotary_dim"] / head_dim if cfg.get("rotary_dim") else 1.0)),
         max_position_embeddings=cfg.get("max_position_embeddings", 32768),
         tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
@@ -215,11 +216,13 @@ def config_from_hf(cfg: dict) -> ModelConfig:
         first_k_dense_replace=cfg.get("first_k_dense_replace") or 0,
         moe_layer_freq=cfg.get("moe_layer_freq") or cfg.get("decoder_sparse_step") or 1,
         mlp_only_layers=list(cfg.get("mlp_only_layers") or []),
-        scoring_func=cfg.get("scoring_func", "softmax"),
+        scoring_func=cfg.get("scoring_func") or ("sigmoid" if mt in {"minimax_m2", "minimax_m3", "glm4_moe", "deepseek_v3",
+                                                                       "deepseek_v32", "kimi_k2"} else "softmax"),
         routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0)),
         n_group=cfg.get("n_group") or 1,
         topk_group=cfg.get("topk_group") or 1,
-        moe_router_bias=cfg.get("topk_method") == "noaux_tc" or bool(cfg.get("use_routing_bias", False)),
+        moe_router_bias=cfg.get("topk_method") == "noaux_tc" or bool(cfg.get("use_routing_bias", False))
+        or mt in {"minimax_m2", "minimax_m3", "glm4_moe"},
         swiglu_limit=float(cfg.get("swiglu_limit") or (7.0 if mt == "gpt_oss" else 0.0)),
         q_lora_rank=cfg.get("q_lora_rank") or 0,
         kv_lora_rank=cfg.get("kv_lora_rank") or 0,

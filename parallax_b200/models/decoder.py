@@ -29,7 +29,7 @@ from parallax_b200.models.rope import build_rope_table
 class LayerWeights:
     __slots__ = (
         "ln1", "ln2", "w_qkv", "b_qkv", "q_norm", "k_norm", "w_o", "b_o", "w_gu", "w_down", "sinks",
-        "moe", "window", "layer_idx",
+        "moe", "window", "layer_idx", "w_g",
     )
 
     def __init__(self):
@@ -92,9 +92,14 @@ class DecoderStage:
             lw.w_qkv = torch.cat([wq, wk, wv], dim=0).contiguous()
             if cfg.attention_bias:
                 lw.b_qkv = rnd((Hq + 2 * Hkv) * D, layer_seed=s + 4)
-            if cfg.qk_norm:
+            if cfg.qk_norm_full:      # one norm over the whole q / k projection (MiniMax-M2)
+                lw.q_norm = 1.0 + rnd(Hq * D, layer_seed=s + 30)
+                lw.k_norm = 1.0 + rnd(Hkv * D, layer_seed=s + 31)
+            elif cfg.qk_norm:
                 lw.q_norm = torch.ones(D, device=dev, dtype=dt)
                 lw.k_norm = torch.ones(D, device=dev, dtype=dt)
+            if (cfg.raw or {}).get("use_head_wise_attn_gate"):  # head-wise sigmoid gate on the attention output (Step-3.5)
+                lw.w_g = rnd(Hq, H, layer_seed=s + 32)
             lw.w_o = rnd(H, Hq * D, layer_seed=s + 5)
             if cfg.attention_sinks:
                 lw.sinks = rnd(Hq, layer_seed=s + 9).float()
@@ -143,6 +148,7 @@ class DecoderStage:
             lw.k_norm = get(p + "self_attn.k_norm.weight", required=False)
             lw.w_o = get(p + "self_attn.o_proj.weight").contiguous()
             lw.b_o = get(p + "self_attn.o_proj.bias", required=False)
+            lw.w_g = get(p + "self_attn.g_proj.weight", required=False)
             sk = tensors.get(p + "self_attn.sinks")
             if sk is not None:
                 lw.sinks = sk.to(device=dev, dtype=torch.float32)
@@ -234,7 +240,14 @@ class DecoderStage:
         T = xn.shape[0]
         qkv = ops.linear(xn, lw.w_qkv, bias=lw.b_qkv)
         kc, vc = self.kv_caches[li]
-        ops.qk_norm_rope_cache(qkv, lw.q_norm, lw.k_norm, self.cos_sin, fb.positions, fb.slot_mapping,
+        qn, kn = lw.q_norm, lw.k_norm
+        if cfg.qk_norm_full and qn is not None:
+            # norm over the whole projection, in place on the column slices of the packed activation
+            ops.rmsnorm(qkv[:, :Hq * D], qn, cfg.rms_norm_eps, w_offset=self.norm_offset, out=qkv[:, :Hq * D])
+            ops.rmsnorm(qkv[:, Hq * D:(Hq + Hkv) * D], kn, cfg.rms_norm_eps, w_offset=self.norm_offset,
+                        out=qkv[:, Hq * D:(Hq + Hkv) * D])
+            qn = kn = None
+        ops.qk_norm_rope_cache(qkv, qn, kn, self.cos_sin, fb.positions, fb.slot_mapping,
                                kc, vc, Hq, Hkv, D, cfg.rot_dim, cfg.rms_norm_eps, self.norm_offset)
         q = qkv.view(T, Hq + 2 * Hkv, D)[:, :Hq]
         attn = torch.empty((T, Hq, D), dtype=qkv.dtype, device=qkv.device)
@@ -245,6 +258,9 @@ class DecoderStage:
         if fb.num_decode:
             ops.attn_decode(q[Tp:], kc, vc, fb.d_block_tables, fb.d_ctx_lens, self.scale,
                             window=lw.window, sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:])
+        if lw.w_g is not None:
+            gate = torch.sigmoid(ops.linear(xn, lw.w_g).float()).to(attn.dtype)      # [T, Hq]
+            attn = attn * gate.unsqueeze(-1)
         return attn.view(T, Hq * D)
 
     def _mlp(self, lw: LayerWeights, xn: torch.Tensor, h: torch.Tensor) -> torch.Tensor:

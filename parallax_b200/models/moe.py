@@ -137,6 +137,8 @@ class MoEWeights:
             return m
         m.router = get("gate.weight").contiguous()
         m.e_bias = get("gate.e_score_correction_bias", required=False, dt=torch.float32)
+        if m.e_bias is None:      # MiniMax-M2 keeps the selection bias one level up
+            m.e_bias = get("e_score_correction_bias", required=False, dt=torch.float32)
         w1, w2 = [], []
         for e in range(E):
             g_w, u_w = get(f"experts.{e}.gate_proj.weight"), get(f"experts.{e}.up_proj.weight")

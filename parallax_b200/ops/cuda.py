@@ -111,9 +111,16 @@ def rmsnorm(
     out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     T, H = x.shape
-    assert x.is_contiguous() and x.dtype == torch.bfloat16
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
     if out is None:
-        out = torch.empty_like(x)
+        out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+    if not x.is_contiguous() or not out.is_contiguous():
+        # rows of a column slice (e.g. the q part of a packed qkv activation); out may alias x
+        assert residual is None and out.stride(1) == 1
+        check(_lib.lib().pxl_rmsnorm_strided(x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0),
+                                             T, H, eps, w_offset, _stream(x.device)), "pxl_rmsnorm_strided")
+        _count()
+        return out
     check(
         _lib.lib().pxl_rmsnorm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), _ptr(residual), T,
                                H, eps, w_offset, _stream(x.device)),
