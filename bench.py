@@ -168,10 +168,10 @@ def run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid) -> No
     conc = args.concurrency
     # a couple of micro-batches more than stages, so that a stage always has one queued while the
     # scheduler on rank 0 commits the tokens of another and plans its next turn
-    n_mb = 1 if pp == 1 else pp + (1 if pp <= 2 else 2)
+    n_mb = args.micro_batches or (1 if pp == 1 else pp + (1 if pp <= 2 else 2))
     # prompts are prefilled in slices so that every micro-batch carries a similar share of the
     # ~1500 prompt tokens that arrive per rotation (an uneven micro-batch stalls the other stages)
-    chunk = 4096 if pp == 1 else (512 if n_mb <= 4 else 256)
+    chunk = args.prefill_chunk or (4096 if pp == 1 else (512 if n_mb <= 4 else 256))
     eng = DistEngine(cfg, pp, tp, device, torch.bfloat16, page_size=16, kv_fraction=0.85, max_batch_size=conc,
                      max_num_tokens_per_batch=8192 + conc, micro_batch_ratio=n_mb, max_in_flight=n_mb,
                      chunked_prefill_size=chunk,
@@ -242,6 +242,8 @@ def main() -> None:
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--concurrency", type=int, default=CONCURRENCY)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the run invalid)")
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="pipeline modes: prompt tokens per prefill slice")
+    ap.add_argument("--micro-batches", type=int, default=0, help="pipeline modes: micro-batches in flight")
     ap.add_argument("--parallelism", default="auto", help="auto (single GPU, or ppN on N GPUs) | dp | pp | pp<P>tp<T>")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -63,7 +63,7 @@ __device__ __forceinline__ void load_kv_tile(const KVTileArgs& a, int tok0, int 
       const int blk = (bi < a.max_blocks) ? a.block_table[bi] : -1;
       if (blk < 0 || blk >= a.num_blocks) {
         pred = false;
-        if (status) atomicCAS(status, 0, PXL_DEV_BAD_INDEX);
+        if (status) atomicCAS(status, 0, PXL_DEV_BAD_BLOCK_PREFILL);
       } else {
         base = ((static_cast<int64_t>(blk) * a.Hkv + a.kvh) * a.page_size + (tok % a.page_size)) *
                    D +
@@ -354,7 +354,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
       if (bi * page_size >= hi) bi = (hi - 1) / page_size;  // beyond the context: re-read the last page (masked)
       int blk = bi < max_blocks ? bt[bi] : -1;
       if (blk < 0 || blk >= num_blocks) {
-        if (status) atomicCAS(status, 0, PXL_DEV_BAD_INDEX);
+        if (status) atomicCAS(status, 0, PXL_DEV_BAD_BLOCK_DECODE);
         blk = 0;
       }
       const int row0 = (blk * Hkv + kvh) * page_size;

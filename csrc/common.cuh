@@ -28,6 +28,10 @@ enum PxlStatus : int {
   PXL_DEV_TIMEOUT_TMEM_EMPTY = 104,// MMA warp waited too long for a drained accumulator
   PXL_DEV_TIMEOUT_PEER = 105,      // wait on a flag written by another GPU ran out
   PXL_DEV_BAD_INDEX = 106,         // a block-table / slot / expert index was out of range
+  PXL_DEV_BAD_SLOT = 107,          // KV-cache slot of a token outside the cache
+  PXL_DEV_BAD_ROW_ID = 108,        // row id of a gather (token id, logit row) outside the table
+  PXL_DEV_BAD_BLOCK_DECODE = 109,  // block-table entry read by decode attention outside the cache
+  PXL_DEV_BAD_BLOCK_PREFILL = 110, // block-table entry read by prefill attention outside the cache
 };
 
 namespace pxl {

@@ -163,7 +163,7 @@ qk_norm_rope_cache_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ q_nor
   }
   if (slot < 0) return;
   if (slot >= num_slots) {
-    if (status && lane == 0) atomicCAS(status, 0, PXL_DEV_BAD_INDEX);
+    if (status && lane == 0) atomicCAS(status, 0, PXL_DEV_BAD_SLOT);
     return;
   }
   const int kvh = is_k ? hs - Hq : hs - Hq - Hkv;
@@ -185,7 +185,7 @@ reshape_and_cache_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v,
   const int64_t slot = slot_mapping[t];
   if (slot < 0) return;
   if (slot >= num_slots) {
-    if (status && threadIdx.x == 0) atomicCAS(status, 0, PXL_DEV_BAD_INDEX);
+    if (status && threadIdx.x == 0) atomicCAS(status, 0, PXL_DEV_BAD_SLOT);
     return;
   }
   const int64_t blk = slot / page_size;
@@ -247,7 +247,7 @@ gather_rows_kernel(const bf16* __restrict__ table, const IdT* __restrict__ ids,
   const size_t t = blockIdx.x;
   int64_t id = static_cast<int64_t>(ids[t]);
   if (id < 0 || id >= num_rows) {
-    if (status && threadIdx.x == 0) atomicCAS(status, 0, PXL_DEV_BAD_INDEX);
+    if (status && threadIdx.x == 0) atomicCAS(status, 0, PXL_DEV_BAD_ROW_ID);
     id = 0;
   }
   const bf16* src = table + id * H;

@@ -6,6 +6,8 @@
 //
 // Counterpart in the reference: the per-layer Python loop of ShardedModel.__call__
 // (src/parallax/server/model.py:75-180), which dispatches framework ops layer by layer.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "pxl_api.h"
 
@@ -62,10 +64,26 @@ struct PxlStageWorkspace {
 
 }  // extern "C"
 
-#define PXL_TRY(expr)              \
-  do {                             \
-    const int rc_ = (expr);        \
-    if (rc_ != PXL_OK) return rc_; \
+// With PXL_STAGE_DEBUG set in the environment every launch is followed by a synchronising read of
+// the status word; the call then returns 1000 + 16 * layer + op so that the failing kernel is named.
+static bool stage_debug() {
+  static const bool on = getenv("PXL_STAGE_DEBUG") != nullptr;
+  return on;
+}
+static int stage_probe(int* status, cudaStream_t stream, int layer, int op) {
+  if (!stage_debug() || status == nullptr) return PXL_OK;
+  int code = 0;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return PXL_ERR_CUDA;
+  if (cudaMemcpy(&code, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return PXL_ERR_CUDA;
+  return code ? 1000 + 16 * layer + op : PXL_OK;
+}
+
+#define PXL_TRY(expr)                                  \
+  do {                                                 \
+    const int rc_ = (expr);                            \
+    if (rc_ != PXL_OK) return rc_;                     \
+    const int pr_ = stage_probe(status, stream, li, ++op_); \
+    if (pr_ != PXL_OK) return pr_;                     \
   } while (0)
 
 // h_in [T, H] -> returns the pointer that holds the stage's output hidden states in *h_out (one of
@@ -89,6 +107,7 @@ PXL_EXPORT int pxl_stage_forward_dense(const PxlStageDesc* st, const PxlStepDesc
   }
   for (int li = 0; li < st->n_layers; ++li) {
     const PxlDenseLayer& L = st->layers[li];
+    int op_ = 0;  // 1 norm, 2 qkv, 3 rope+cache, 4 prefill, 5 decode (4 if no prefill), then o_proj, norm, gate_up, down
     void* h_mid = (h == ws->h_a) ? ws->h_b : ws->h_a;
     PXL_TRY(pxl_rmsnorm(h, L.ln1, ws->xn, nullptr, T, H, st->eps, st->norm_offset, stream));
     PXL_TRY(pxl_gemm_bf16(ws->xn, L.w_qkv, qkv, nullptr, L.b_qkv, T, qkv_n, H, H, H, qkv_n, PXL_EPI_NONE, 0, status,

@@ -61,6 +61,7 @@ class BatchBuilder:
         self.host = torch.empty(words, dtype=torch.int32, pin_memory=pin)
         self.host_np = self.host.numpy()
         self.dev = torch.empty(words, dtype=torch.int32, device=device)
+        self._copied = None     # CUDA event: the last host-to-device copy out of the pinned buffer has run
 
     def build(
         self,
@@ -75,6 +76,10 @@ class BatchBuilder:
         logit_rows: np.ndarray,
         seq_rows: Optional[np.ndarray] = None,
     ) -> ForwardBatch:
+        if self._copied is not None:
+            # the pinned buffer is about to be rewritten: the asynchronous copy of its previous
+            # content must have executed (a caller may run several steps ahead of the device)
+            self._copied.synchronize()
         T = int(positions.shape[0])
         Bp, Bd = len(p_q_lens), int(d_ctx_lens.shape[0])
         Tp = int(sum(p_q_lens))
@@ -115,6 +120,10 @@ class BatchBuilder:
             spans["seq_slots"] = put(seq_rows.astype(np.int32, copy=False))
         total = off
         self.dev[:total].copy_(self.host[:total], non_blocking=True)
+        if self.device.type == "cuda":
+            if self._copied is None:
+                self._copied = torch.cuda.Event()
+            self._copied.record()
 
         def view(key):
             s, n = spans[key]

@@ -108,9 +108,15 @@ class NativeDenseStage:
         out_ptr = c_void_p()
         n = c_int()
         assert h_in.is_contiguous()
-        check(self._fn(ctypes.addressof(self.desc), ctypes.addressof(s), ctypes.addressof(self._ws), h_in.data_ptr(),
-                       ctypes.addressof(out_ptr), ctypes.addressof(n), cu.status_tensor(self.device).data_ptr(),
-                       cu._stream(self.device)), "pxl_stage_forward_dense")
+        rc = self._fn(ctypes.addressof(self.desc), ctypes.addressof(s), ctypes.addressof(self._ws), h_in.data_ptr(),
+                      ctypes.addressof(out_ptr), ctypes.addressof(n), cu.status_tensor(self.device).data_ptr(),
+                      cu._stream(self.device))
+        if rc >= 1000:      # debug mode of the executor: names the kernel that reported an error
+            raise _lib.KernelError(f"stage executor: layer {(rc - 1000) // 16} op {(rc - 1000) % 16} reported a device error; "
+                                   f"T={s.T} Tp={s.Tp} Bp={s.Bp} Bd={s.Bd} p_max_q={s.p_max_q} d_max_ctx={s.d_max_ctx} "
+                                   f"p_max_blocks={s.p_max_blocks} d_max_blocks={s.d_max_blocks} "
+                                   f"status={int(cu.status_tensor(self.device).item())}")
+        check(rc, "pxl_stage_forward_dense")
         cu._count(n.value)
         buf = self._bufs[4] if out_ptr.value == self._ws.h_a else self._bufs[5]
         return buf[:T]

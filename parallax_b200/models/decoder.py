@@ -275,7 +275,10 @@ class DecoderStage:
             from parallax_b200.engine.native_stage import NativeDenseStage
 
             # dense GQA stage on a GPU: all layers of a step run behind one call into the library
-            self._native = NativeDenseStage(self) if NativeDenseStage.supported(self) else False
+            import os
+
+            self._native = NativeDenseStage(self) if NativeDenseStage.supported(self) \
+                and not os.environ.get("PXL_NO_NATIVE_STAGE") else False
         if self._native:
             out = self._native.forward(h.contiguous(), fb)
             # the result lives in the executor's workspace: hand out a copy when it leaves the stage

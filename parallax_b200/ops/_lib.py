@@ -24,6 +24,10 @@ _ERRORS = {
     104: "device wait timed out (accumulator empty)",
     105: "device wait timed out (peer flag)",
     106: "index out of range (block table / slot / expert / row id)",
+    107: "KV-cache slot of a token outside the cache",
+    108: "row id of a gather (token id / logit row) outside the table",
+    109: "block-table entry read by decode attention outside the cache",
+    110: "block-table entry read by prefill attention (or the cp.async decode path) outside the cache",
 }
 
 EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32 = 0, 1, 2, 3

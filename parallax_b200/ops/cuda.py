@@ -7,6 +7,7 @@ tensors' device. Shapes and semantics are documented with the C ABI in ``csrc/px
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -19,9 +20,21 @@ _workspaces: dict[tuple[int, str], torch.Tensor] = {}
 launch_count = 0  # number of kernel-library launches issued (benchmarks report it)
 
 
+_CHECK_EACH_OP = bool(os.environ.get("PXL_CHECK_EACH_OP"))
+
+
 def _count(n: int = 1) -> None:
     global launch_count
     launch_count += n
+    if _CHECK_EACH_OP:
+        # debugging aid: synchronise after every op and name the op whose kernel reported an error
+        import sys
+
+        for idx, t in _status.items():
+            code = int(t.item())
+            if code:
+                t.zero_()
+                raise _lib.KernelError(f"{sys._getframe(1).f_code.co_name} on cuda:{idx}: {_lib.describe(code)}")
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -37,7 +50,8 @@ def status_tensor(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     t = _status.get(idx)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        with torch.inference_mode(False):      # a normal tensor: it is reset in place from any context
+            t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _status[idx] = t
     return t
 

@@ -332,14 +332,33 @@ class DistEngine:
             self.steps += 1
         for work, _ in self._pending_sends:
             work.wait()
-        dist.barrier(group=self.ctrl)
+        self._status_all_ranks()
         self.chan.close()
 
+    def _status_all_ranks(self) -> list[int]:
+        """Device status word of every rank (0 = healthy), gathered over the control group."""
+        code = 0
+        if self.device.type == "cuda":
+            from parallax_b200.ops import cuda as cu
+
+            torch.cuda.synchronize(self.device)
+            code = int(cu.status_tensor(self.device).item())
+        codes = torch.zeros(self.topo.world, dtype=torch.int64)
+        codes[self.topo.rank] = code
+        dist.all_reduce(codes, group=self.ctrl)
+        return codes.tolist()
+
     def shutdown(self) -> None:
+        """Rank 0: stop the other ranks; raises if any rank's kernels reported a device error."""
         if self.topo.rank == 0:
             self._bcast({"cmd": "stop"})
-            dist.barrier(group=self.ctrl)       # every reader has seen the stop message
+            codes = self._status_all_ranks()       # also a barrier: every reader has seen the stop message
             self.chan.close()
+            if any(codes):
+                from parallax_b200.ops import _lib
+
+                raise _lib.KernelError("device status per rank: " + ", ".join(
+                    f"rank {i}: {_lib.describe(c)}" for i, c in enumerate(codes) if c))
 
     # ------------------------------------------------------------------ rank-0 step
     def _drop(self, req: Request) -> None:

@@ -119,4 +119,4 @@ def test_moe_ffn_swigluoai_with_expert_biases(cu):
     want = ref.moe_ffn(x.cpu(), ids.cpu(), w.cpu(), w1.cpu().float(), w2.cpu().float(), E, base=base.cpu(), act_mode=1,
                        limit=7.0, b1=b1.cpu().float(), b2=b2.cpu().float())
     cu.check_status(torch.device(DEV))
-    assert _rel(got, want) < 1e-2
+    assert _rel(got.cpu(), want) < 1e-2
