@@ -160,6 +160,7 @@ class Engine:
         max_kv_tokens: Optional[int] = None,
         shared_state=None,
         wire_hook: Optional[Callable] = None,
+        trace=None,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -197,6 +198,9 @@ class Engine:
         self.total_steps = 0
         self.keep_logits = False
         self.last_logits: Optional[torch.Tensor] = None
+        from parallax_b200.utils.trace import StepTracer
+
+        self.tracer = StepTracer(trace) if isinstance(trace, str) else (trace or StepTracer.from_env())
 
     # ------------------------------------------------------------------ requests
     def add_request(self, req: Request) -> None:
@@ -245,6 +249,7 @@ class Engine:
         ``events``: optional ``(start, end)`` CUDA events recorded on the compute stream right
         before the step's host-to-device copy and right after sampling (device-time probes)."""
         out: list[tuple[Request, Optional[int]]] = []
+        t_step = time.perf_counter()
         sched = self.scheduler
         for req in sched.get_timed_out_requests():
             req.update_status(RequestStatus.FINISHED_ABORT)
@@ -275,6 +280,11 @@ class Engine:
         if arrays is None:
             return out
         t0 = time.perf_counter()
+        tr = self.tracer
+        if tr is not None:
+            tr.span("schedule+plan", t_step, t0)
+            if events is None and self.device.type == "cuda":
+                events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         if events is not None:
             events[0].record()
         fb = self.builder.build(arrays["ids"], arrays["pos"], arrays["slots"], arrays["p_q"],
@@ -294,6 +304,7 @@ class Engine:
             ids, probs = self._sample(h, owners)
         if events is not None:
             events[1].record()
+        t_launched = time.perf_counter()
         if owners:
             token_list = ids.tolist()  # device-to-host copy of the step's result (synchronises)
             if probs is not None:
@@ -306,6 +317,12 @@ class Engine:
             "h2d_bytes": fb.h2d_bytes, "d2h_bytes": 4 * len(token_list) * (2 if prob_list else 1),
             "new_tokens": len(token_list), "wall_s": time.perf_counter() - t0,
         }
+        if tr is not None:
+            t_synced = time.perf_counter()
+            tr.span("build+launch", t0, t_launched, tokens=fb.num_tokens, prefill=fb.num_prefill_tokens, decode=fb.num_decode)
+            tr.span("wait for tokens", t_launched, t_synced)
+            if events is not None:
+                tr.device_span(self.total_steps, events[0], events[1], t0, tokens=fb.num_tokens)
         # ---- commit
         owner_idx = {id(s): i for i, s in enumerate(owners)}
         for s in arrays["ordered"]:
@@ -326,6 +343,8 @@ class Engine:
                 sched.enque_request(req)
                 if tok is not None:
                     out.append((req, tok))
+        if tr is not None:
+            tr.span("commit", t_synced, time.perf_counter())
         return out
 
     # ------------------------------------------------------------------ convenience

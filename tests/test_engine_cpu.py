@@ -133,3 +133,16 @@ def test_tiny_moe_sharded_equals_unsharded():
     cfg = named_config("tiny-moe")
     prompts = _prompts(3, 30, cfg.vocab_size, seed=11)
     assert _run(cfg, prompts, max_new=5) == _run(cfg, prompts, max_new=5, stage_layers=[(0, 2), (2, 4)])
+
+
+def test_step_tracer_writes_chrome_trace(tmp_path):
+    import json
+
+    path = tmp_path / "trace.json"
+    eng = Engine(named_config("tiny"), device="cpu", num_blocks=64, page_size=16, max_batch_size=4, trace=str(path))
+    eng.generate(_prompts(2, 20, 1024, seed=3), SamplingParams(max_new_tokens=3, temperature=0.0, ignore_eos=True))
+    eng.tracer.save()
+    ev = json.loads(path.read_text())["traceEvents"]
+    names = {e["name"] for e in ev}
+    assert {"schedule+plan", "build+launch", "wait for tokens", "commit"} <= names
+    assert all(e["dur"] > 0 for e in ev)
