@@ -19,7 +19,7 @@ Two numbers come out of the same K timed steps:
     device-to-host read of the sampled token ids.
 With N GPUs the model runs as an N-stage pipeline (the layout BASELINE.json names: PP8 at
 N=8; ``--parallelism pp2tp4`` selects two stages of four tensor-parallel ranks, ``dp`` N engine
-replicas). Rank 0 schedules; ``N+1`` or ``N+2`` micro-batches are in flight; a step is
+replicas). Rank 0 schedules; ``N+2`` micro-batches are in flight; a step is
 one rotation (every running request advances one token). The same 512 requests are served at
 every N (strong scaling); times are the max over ranks.
 
@@ -168,10 +168,10 @@ def run_pipeline(args, cfg, par, world, rank, local_rank, device, invalid) -> No
     conc = args.concurrency
     # a couple of micro-batches more than stages, so that a stage always has one queued while the
     # scheduler on rank 0 commits the tokens of another and plans its next turn
-    n_mb = args.micro_batches or (1 if pp == 1 else pp + (1 if pp <= 2 else 2))
-    # prompts are prefilled in slices so that every micro-batch carries a similar share of the
-    # ~1500 prompt tokens that arrive per rotation (an uneven micro-batch stalls the other stages)
-    chunk = args.prefill_chunk or (4096 if pp == 1 else (512 if n_mb <= 4 else 256))
+    n_mb = args.micro_batches or (1 if pp == 1 else pp + 2)
+    # measured at pp2: slicing prompts finer (1024 / 512 tokens) to even out the micro-batches loses
+    # more in kernel efficiency than it gains in balance, so prompts are prefilled in one piece
+    chunk = args.prefill_chunk or 4096
     eng = DistEngine(cfg, pp, tp, device, torch.bfloat16, page_size=16, kv_fraction=0.85, max_batch_size=conc,
                      max_num_tokens_per_batch=8192 + conc, micro_batch_ratio=n_mb, max_in_flight=n_mb,
                      chunked_prefill_size=chunk,
