@@ -68,17 +68,20 @@ def bench_gemm(rows):
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         flops = 2.0 * M * N * K
         byts = 2.0 * (M * K + N * K + M * N)
-        best = None
-        for bn in (64, 128, 256):
+        best, per_bn = None, {}
+        for bn in (64, 128, 192, 256):
             ms = time_fn(lambda: cu.linear(x, w, out=out, bn=bn))
+            per_bn[bn] = round(ms, 4)
             if best is None or ms < best[1]:
                 best = (bn, ms)
+        picked = cu.gemm_pick_bn(M, N)
         ms_lib = time_fn(lambda: torch.matmul(x, w.t(), out=out))
         cu.check_status(x.device)
         bn, ms = best
         ideal = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3
         rows.append({
-            "kernel": "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "bn": bn, "ms": round(ms, 4),
+            "kernel": "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "bn": bn, "ms": round(ms, 4), "ms_per_bn": per_bn,
+            "bn_picked": picked,
             "tflops": round(flops / ms / 1e9, 1), "roofline_frac": round(ideal / ms, 3),
             "tag": tag, "torch_matmul_ms": round(ms_lib, 4),
         })

@@ -33,7 +33,8 @@ template <int BN>
 struct GemmCfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int STAGES = (192 * 1024) / (A_STAGE_BYTES + B_STAGE_BYTES);
-  static constexpr int TMEM_COLS = 2 * BN;
+  // two accumulators; tensor memory is allocated in powers of two (384 columns round up to 512)
+  static constexpr int TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);
   static constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
 };
 
@@ -699,6 +700,16 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
   GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
   switch (bn) {
     case 256: return dispatch_epi<256>(epi, ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
+    case 192:  // plain epilogues only: fills the last wave better when N / 256 leaves SMs idle
+      switch (epi) {
+        case PXL_EPI_NONE:
+          return launch_gemm<192, PXL_EPI_NONE>(ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
+        case PXL_EPI_RESIDUAL:
+          return launch_gemm<192, PXL_EPI_RESIDUAL>(ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
+        case PXL_EPI_F32:
+          return launch_gemm<192, PXL_EPI_F32>(ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
+        default: return PXL_ERR_INVALID_ARG;
+      }
     case 128: return dispatch_epi<128>(epi, ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
     case 64: return dispatch_epi<64>(epi, ta, tb, ep, grp, GemmCommArgs{}, 0, M, N, K, status, stream);
     default: return PXL_ERR_INVALID_ARG;

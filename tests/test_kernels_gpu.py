@@ -36,6 +36,8 @@ def _rel_err(a, b):
         (1, 4096, 4096, 0),       # decode-like
         (1000, 6144, 4096, 0),    # qkv-like, multi-tile persistent loop
         (2560, 4096, 4096, 256),
+        (2560, 4096, 4096, 192),  # 192-wide tiles: N is not a multiple of the tile (last tile partly masked)
+        (300, 200, 512, 192),
     ],
 )
 def test_gemm_bf16(cu, M, N, K, bn):
