@@ -5,6 +5,7 @@
     python benchmarks/profile_case.py attn_prefill # ragged prefill, 4 x 2048
     python benchmarks/profile_case.py step         # 2 engine steps of a 4-layer Qwen3-8B-shaped
                                                    # model at 64 concurrent (launch list)
+    python benchmarks/profile_case.py decode_step  # same, decode rows only (small-M GEMMs); decode_step_8: 8 rows
 
 Each case uses inputs larger than the 126 MB L2 so that DRAM counters are meaningful, warms
 up once, and brackets the launches of interest with cudaProfilerStart/Stop so that
@@ -82,14 +83,13 @@ def case_attn_prefill(iters: int = 3):
     cu.check_status(q.device)
 
 
-def case_step(steps: int = 2):
+def case_step(steps: int = 2, conc: int = 64, with_prefill: bool = True):
     from parallax_b200.engine.engine import Engine
     from parallax_b200.engine.request import Request, SamplingParams
     from parallax_b200.models.config import named_config
 
     cfg = named_config("qwen3-8b")
     cfg.num_hidden_layers = 4
-    conc = 64
     eng = Engine(cfg, device="cuda:0", max_batch_size=conc, max_num_tokens_per_batch=4096 + conc,
                  chunked_prefill_size=2048, max_total_length=1400, max_kv_tokens=conc * 1400,
                  request_timeout_s=None)
@@ -102,11 +102,13 @@ def case_step(steps: int = 2):
 
     for i in range(conc):
         admit(1024 + (i * 4) % 256, 256 - (i * 4) % 256)
+    eng.step()                                     # admits and starts prefilling
     for _ in range(40):
         if not any(r.is_prefill for r in eng.scheduler.running_requests()):
             break
         eng.step()
-    admit(1024, 256)
+    if with_prefill:
+        admit(1024, 256)                           # one prompt joins the decode batch in the captured steps
     torch.cuda.synchronize()
     torch.cuda.cudart().cudaProfilerStart()
     for _ in range(steps):
@@ -119,5 +121,6 @@ def case_step(steps: int = 2):
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": case_gemm, "attn_decode": case_attn_decode, "attn_prefill": case_attn_prefill,
-     "step": case_step}[which]()
+     "step": case_step, "decode_step": lambda: case_step(conc=64, with_prefill=False),
+     "decode_step_8": lambda: case_step(conc=8, with_prefill=False)}[which]()
     print(f"profile case {which}: ok")
