@@ -1,6 +1,6 @@
 """Micro-benchmarks of the hot kernels against the measured roofline denominators.
 
-Usage:  python benchmarks/bench_kernels.py [--which gemm,attn,norm] [--out FILE]
+Usage:  python benchmarks/bench_kernels.py [--which gemm,gemm_small,attn,norm] [--out FILE]
 
 Timing: CUDA events on the launching stream, 5 warm-up launches, an L2 flush (a 256 MB
 memset) before every timed launch, median of the timed launches. Fractions are reported
@@ -89,6 +89,45 @@ def bench_gemm(rows):
         del x, w, out
 
 
+def bench_gemm_small(rows):
+    """Decode-sized GEMMs (M <= 128): memory-bound, so the figure of merit is weight bytes per second.
+    Eight weight matrices are cycled so that no launch finds its weights in L2; the launches of one
+    variant run back to back between one pair of events (a short kernel timed alone would mostly
+    measure the launch)."""
+    hbm, _tf, tag = peaks()
+    reps = 8
+    for M in (8, 64, 128):
+        for N, K in [(4096, 4096), (6144, 4096), (4096, 12288)]:
+            x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(reps)]
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+
+            def run(fn):
+                for w in ws:
+                    fn(w)
+                torch.cuda.synchronize()
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(4):
+                    for w in ws:
+                        fn(w)
+                e.record()
+                torch.cuda.synchronize()
+                return s.elapsed_time(e) / (4 * reps)
+
+            ms_small = run(lambda w: cu.linear_small_m(x, w, out=out))
+            ms_tile = min(run(lambda w: cu.linear(x, w, out=out, bn=64)), run(lambda w: cu.linear(x, w, out=out, bn=128)))
+            ms_lib = run(lambda w: torch.matmul(x, w.t(), out=out))
+            cu.check_status(x.device)
+            byts = 2.0 * N * K
+            rows.append({"kernel": "gemm_bf16_small_m", "M": M, "N": N, "K": K, "us": round(ms_small * 1e3, 2),
+                         "us_plain_tiles": round(ms_tile * 1e3, 2), "us_torch_matmul": round(ms_lib * 1e3, 2),
+                         "weight_gbs": round(byts / ms_small / 1e6, 1),
+                         "roofline_frac": round(byts / (hbm * 1e9) * 1e3 / ms_small, 3), "tag": tag})
+            print(rows[-1], flush=True)
+            del ws
+
+
 def bench_attn(rows):
     hbm, tf, tag = peaks()
     Hq, Hkv, D, page = 32, 8, 128, 16
@@ -152,13 +191,15 @@ def bench_norm(rows):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm,attn,norm")
+    ap.add_argument("--which", default="gemm,gemm_small,attn,norm")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     rows = []
     which = args.which.split(",")
     if "gemm" in which:
         bench_gemm(rows)
+    if "gemm_small" in which:
+        bench_gemm_small(rows)
     if "attn" in which:
         bench_attn(rows)
     if "norm" in which:

@@ -1,6 +1,7 @@
 """Small, self-terminating cases for `ncu` captures (one kernel, a few launches, < 2 GB).
 
     python benchmarks/profile_case.py gemm         # bf16 tcgen05 GEMM, 4096 x 8192 x 8192
+    python benchmarks/profile_case.py gemm_small   # split-K small-M GEMM, 64 x 4096 x 4096
     python benchmarks/profile_case.py attn_decode  # paged GQA decode, 256 seqs x 2048 ctx
     python benchmarks/profile_case.py attn_prefill # ragged prefill, 4 x 2048
     python benchmarks/profile_case.py step         # 2 engine steps of a 4-layer Qwen3-8B-shaped
@@ -35,6 +36,22 @@ def case_gemm(iters: int = 3):
     torch.cuda.cudart().cudaProfilerStart()
     for _ in range(iters):
         cu.linear(x, w, out=out, bn=256)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    cu.check_status(x.device)
+
+
+def case_gemm_small(iters: int = 3, M: int = 64, N: int = 4096, K: int = 4096):
+    """Decode-sized GEMM on the split-K path; a fresh weight matrix per launch (8 x 33 MB > L2)."""
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(8)]
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    for w in ws:
+        cu.linear_small_m(x, w, out=out)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    for i in range(iters):
+        cu.linear_small_m(x, ws[i % 8], out=out)
     torch.cuda.synchronize()
     torch.cuda.cudart().cudaProfilerStop()
     cu.check_status(x.device)
@@ -121,6 +138,6 @@ def case_step(steps: int = 2, conc: int = 64, with_prefill: bool = True):
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": case_gemm, "attn_decode": case_attn_decode, "attn_prefill": case_attn_prefill,
-     "step": case_step, "decode_step": lambda: case_step(conc=64, with_prefill=False),
+     "gemm_small": case_gemm_small, "step": case_step, "decode_step": lambda: case_step(conc=64, with_prefill=False),
      "decode_step_8": lambda: case_step(conc=8, with_prefill=False)}[which]()
     print(f"profile case {which}: ok")

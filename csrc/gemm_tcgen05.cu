@@ -15,6 +15,9 @@
 //
 // Covers the dense projections reached through the reference's GPU backend
 // (src/parallax/sglang/model_runner.py:358-366; the reference itself ships no GPU GEMM).
+#include <cstdlib>
+#include <mutex>
+
 #include "common.cuh"
 #include "pxl_api.h"
 
@@ -55,6 +58,10 @@ struct GemmEpilogueArgs {
   int ldc;
   bf16* const* row_ptrs; // EPI_SCATTER: destination of every output row (null = drop), N elements each
   uint32_t* done_counter;  // EPI_SCATTER: local counter for the "last CTA publishes the flags" step
+  // EPI_SPLITK_T (operands swapped: accumulator row = output column, accumulator column = token)
+  float* ws;                 // [splitk][tokens][ldws] fp32 partial sums, one slab per K range
+  uint32_t* tile_counters;   // one per 128 output columns, zero between launches
+  int splitk, ldws;
 };
 
 // Grouped (per-expert) mode: the m-tiles are listed on the device, one entry per 128-row
@@ -142,6 +149,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);  // split-K: this CTA finishes the tile
   // reduce-scatter epilogue staging lines (allocated only for that epilogue)
   uint8_t* rs_stage = smem_b + STAGES * Cfg::B_STAGE_BYTES + 256;
 
@@ -250,6 +258,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_n = ceil_div(N, BN);
   const int num_tiles = num_m * num_n;
   const int num_kb = ceil_div(K, BK);
+  // split-K (small-M path only): work item = (tile, K range); every range holds at least one k-block
+  const int splitk = (EPI == PXL_EPI_SPLITK_T) ? ep.splitk : 1;
+  const int kb_per = ceil_div(num_kb, splitk);
+  const int num_items = num_tiles * splitk;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -281,7 +293,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gemm_ctas) {
+      for (int item = blockIdx.x; ok && item < num_items; item += gemm_ctas) {
+        const int tile = item % num_tiles;
+        const int kb0 = (item / num_tiles) * kb_per;
+        const int kb1 = kb0 + kb_per < num_kb ? kb0 + kb_per : num_kb;
         const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
         if (comm.ag_ncopy > 0 && tc.a_row / comm.rows_per_rank != comm.rank) {
           // rows of another rank: wait until the copy CTAs have landed this tile locally
@@ -291,7 +306,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!ok) break;
           fence_proxy_async_all();
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1, abort_flag, status,
                                  PXL_DEV_TIMEOUT_EMPTY);
           if (!ok) break;
@@ -316,13 +331,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gemm_ctas) {
+      for (int item = blockIdx.x; ok && item < num_items; item += gemm_ctas) {
+        const int kb0 = (item / num_tiles) * kb_per;
+        const int kb1 = kb0 + kb_per < num_kb ? kb0 + kb_per : num_kb;
         ok = mbar_wait_bounded(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status,
                                PXL_DEV_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, status,
                                  PXL_DEV_TIMEOUT_FULL);
           if (!ok) break;
@@ -333,7 +350,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t da = umma_desc_k_sw128(a_addr + k * UMMA_K * 2);
             const uint64_t db = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
-            tc_mma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_mma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(empty0 + 8 * stage);  // stage reusable once these MMAs retire
           if (++stage == STAGES) {
@@ -353,7 +370,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gemm_ctas) {
+    for (int item = blockIdx.x; ok && item < num_items; item += gemm_ctas) {
+      const int tile = item % num_tiles;
       const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
       const int n_blk = tc.n_blk;
       const int M_end = tc.row_end;
@@ -439,6 +457,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (row < M_end && col0 + c0 < N && dst_row != nullptr) bulk_store_s2g(dst_row + c0, line, 128);
           bulk_commit();
         }
+      } else if constexpr (EPI == PXL_EPI_SPLITK_T) {
+        // operands swapped: this thread's accumulator row is output column `row`, accumulator
+        // column j is token j (N = number of tokens). Every K range has its own slab of the
+        // scratch, so the sums are formed in a fixed order; a warp stores 32 neighbouring floats.
+        float* slab = ep.ws + static_cast<size_t>(item / num_tiles) * N * ep.ldws;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN && c0 < N; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c0, r);
+          tmem_ld_wait();
+          if (row < M_end) {
+            float* w = slab + static_cast<size_t>(c0) * ep.ldws + row;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < N) __stcg(w + static_cast<size_t>(j) * ep.ldws, __uint_as_float(r[j]));
+          }
+        }
       } else {
         const int col0 = n_blk * BN;
 #pragma unroll 1
@@ -493,6 +528,84 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      if constexpr (EPI == PXL_EPI_SPLITK_T) {
+        // the CTA whose partial sums arrive last adds the slabs of the tile in K order (+ bias,
+        // + residual), writes bf16 and resets the tile's counter for the next launch
+        __threadfence();
+        named_bar_sync(1, 128);
+        if (threadIdx.x == 64) {
+          const uint32_t old = atomicAdd(ep.tile_counters + tile, 1u);
+          const int last = old == static_cast<uint32_t>(splitk - 1) ? 1 : 0;
+          if (last) ep.tile_counters[tile] = 0;
+          *last_flag = last;
+        }
+        named_bar_sync(1, 128);
+        if (*last_flag) {
+          __threadfence();
+          // four outputs (of four floats) per thread and up to four K ranges per round: sixteen
+          // independent loads are in flight before the first add, always summed in K order
+          const size_t slab_stride = static_cast<size_t>(N) * ep.ldws;
+          const int n_items = N * 32;
+          constexpr int U = 4;
+          for (int i0 = threadIdx.x - 64; i0 < n_items; i0 += 128 * U) {
+            const float* wp[U];
+            size_t c_off[U];
+            int col[U];
+            bool valid[U];
+            float4 acc[U];
+            uint2 res[U], bia[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int i = i0 + u * 128;
+              const int t = i >> 5;
+              col[u] = tc.a_row + (i & 31) * 4;
+              valid[u] = i < n_items && col[u] < M_end;
+              wp[u] = ep.ws + static_cast<size_t>(t) * ep.ldws + col[u];
+              c_off[u] = static_cast<size_t>(t) * ep.ldc + col[u];
+              acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+              res[u] = make_uint2(0u, 0u);
+              bia[u] = make_uint2(0u, 0u);
+              if (valid[u] && ep.residual) res[u] = *reinterpret_cast<const uint2*>(ep.residual + c_off[u]);
+              if (valid[u] && ep.bias) bia[u] = *reinterpret_cast<const uint2*>(ep.bias + col[u]);
+            }
+            for (int ks = 0; ks < splitk; ks += 4) {
+              float4 v[U][4];
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                  v[u][k4] = (valid[u] && ks + k4 < splitk)
+                                 ? __ldcg(reinterpret_cast<const float4*>(wp[u] + (ks + k4) * slab_stride))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                  acc[u].x += v[u][k4].x, acc[u].y += v[u][k4].y, acc[u].z += v[u][k4].z, acc[u].w += v[u][k4].w;
+                }
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              if (!valid[u]) continue;
+              float4 a = acc[u];
+              const float2 b0 = unpack_bf16x2(bia[u].x), b1 = unpack_bf16x2(bia[u].y);
+              const float2 r0 = unpack_bf16x2(res[u].x), r1 = unpack_bf16x2(res[u].y);
+              a.x += b0.x + r0.x, a.y += b0.y + r0.y, a.z += b1.x + r1.x, a.w += b1.y + r1.y;
+              if (ep.C_f32 != nullptr) {
+                *reinterpret_cast<float4*>(ep.C_f32 + c_off[u]) = a;
+              } else {
+                uint2 o;
+                o.x = pack_bf16x2(a.x, a.y);
+                o.y = pack_bf16x2(a.z, a.w);
+                *reinterpret_cast<uint2*>(ep.C + c_off[u]) = o;
+              }
+            }
+          }
+        }
+      }
       if constexpr (EPI == PXL_EPI_RS) {
         // all 128 epilogue threads have stored their rows of the tile: publish it to the owner
         bulk_wait_all();
@@ -651,19 +764,22 @@ int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const Ge
 
 }  // namespace
 
-// Tile width heuristic: estimated time = waves over the SMs x tile width / relative efficiency of
-// that width. Small-M (decode) problems end up with the narrowest tile, which spreads the weight
-// traffic over the most SMs; large problems take the width that wastes the least of its last wave.
+// Tile width heuristic: estimated time = waves over the SMs x tile width / relative throughput of
+// that width (measured on compute-bound shapes: a 256-wide tile keeps the tensor pipe busiest, a
+// 64-wide one reaches about a third of it). Large problems take the width that wastes the least of
+// the last wave; problems with few tiles end up with narrow ones, which put more SMs to work.
 PXL_EXPORT int pxl_gemm_bf16_pick_bn(int M, int N, int epi) {
   const int sms = pxl_host::num_sms();
   const int num_m = pxl::ceil_div(M, BM);
-  const int cands[3] = {256, 128, 64};
-  const double eff[3] = {1.0, 0.8, 0.72};  // fitted to the best measured width on the Qwen3-8B shapes
+  const int cands[4] = {256, 192, 128, 64};
+  const double eff[4] = {1.0, 0.87, 0.68, 0.37};
+  const bool plain = epi == PXL_EPI_NONE || epi == PXL_EPI_RESIDUAL || epi == PXL_EPI_F32;
   int best = 0;
   double best_cost = 1e300;
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i < 4; ++i) {
     const int bn = cands[i];
-    if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) continue;
+    if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128 || bn == 192)) continue;
+    if (bn == 192 && !plain) continue;
     const int tiles = num_m * pxl::ceil_div(N, bn);
     const double cost = static_cast<double>(pxl::ceil_div(tiles, sms)) * bn / eff[i];
     if (cost < best_cost) {
@@ -672,6 +788,133 @@ PXL_EXPORT int pxl_gemm_bf16_pick_bn(int M, int N, int epi) {
     }
   }
   return best ? best : 128;
+}
+
+namespace {
+// fp32 scratch of the small-M path: one per (device, stream) so that GEMMs on different streams
+// never share partial sums. Allocated on first use; the arrival counters behind it are zeroed once
+// and every launch leaves them zeroed.
+constexpr int kSmallMaxM = 128;
+constexpr int kSmallMaxN = 32768;
+constexpr size_t kSmallScratchFloats = static_cast<size_t>(kSmallMaxM) * kSmallMaxN;  // 16 MB
+struct SmallMScratch {
+  int dev;
+  cudaStream_t stream;
+  float* ws;
+  uint32_t* counters;
+};
+constexpr int kSmallMaxScratch = 64;
+SmallMScratch g_small[kSmallMaxScratch];
+int g_small_n = 0;
+std::mutex g_small_mu;
+
+bool small_m_scratch(cudaStream_t stream, float** ws, uint32_t** counters) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(g_small_mu);
+  for (int i = 0; i < g_small_n; ++i) {
+    if (g_small[i].dev == dev && g_small[i].stream == stream) {
+      *ws = g_small[i].ws;
+      *counters = g_small[i].counters;
+      return true;
+    }
+  }
+  if (g_small_n == kSmallMaxScratch) return false;
+  const size_t ws_bytes = kSmallScratchFloats * sizeof(float);
+  const size_t cnt_bytes = (kSmallMaxN / BM) * sizeof(uint32_t);
+  void* p = nullptr;
+  if (cudaMalloc(&p, ws_bytes + cnt_bytes) != cudaSuccess) return false;
+  if (cudaMemset(p, 0, ws_bytes + cnt_bytes) != cudaSuccess) {
+    cudaFree(p);
+    return false;
+  }
+  SmallMScratch& e = g_small[g_small_n++];
+  e.dev = dev;
+  e.stream = stream;
+  e.ws = static_cast<float*>(p);
+  e.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(p) + ws_bytes);
+  *ws = e.ws;
+  *counters = e.counters;
+  return true;
+}
+
+bool small_m_disabled() {
+  static const bool off = getenv("PXL_NO_SMALL_M_GEMM") != nullptr;
+  return off;
+}
+
+// K ranges per 128 output columns: as many as fill the SMs once, at least four k-blocks each.
+int small_m_splitk(int N, int K) {
+  const int tiles = pxl::ceil_div(N, BM);
+  const int num_kb = pxl::ceil_div(K, BK);
+  int s = pxl_host::num_sms() / tiles;
+  if (s > num_kb / 4) s = num_kb / 4;
+  if (s > 32) s = 32;
+  if (s < 1) s = 1;
+  return s;
+}
+}  // namespace
+
+PXL_EXPORT int pxl_gemm_bf16_uses_small_m(int M, int N, int K, int epi) {
+  if (small_m_disabled()) return 0;
+  if (M <= 0 || M > kSmallMaxM || N > kSmallMaxN || (N % 8) || K <= 0) return 0;
+  if (epi != PXL_EPI_NONE && epi != PXL_EPI_RESIDUAL && epi != PXL_EPI_F32) return 0;
+  // with at least one 128-column tile per SM the plain kernel already streams from every SM
+  return pxl::ceil_div(N, BM) <= pxl_host::num_sms() ? 1 : 0;
+}
+
+namespace {
+int gemm_small_m(const void* A, const void* W, void* C, bool f32_out, const void* residual, const void* bias, int M,
+                 int N, int K, int lda, int ldw, int ldc, int splitk, int* status, cudaStream_t stream) {
+  if (M <= 0 || M > kSmallMaxM || N <= 0 || N > kSmallMaxN || K <= 0) return PXL_ERR_INVALID_ARG;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || (ldc % 8) || (N % 8)) return PXL_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) & 15)
+    return PXL_ERR_INVALID_ARG;
+  const int num_kb = pxl::ceil_div(K, BK);
+  if (splitk <= 0) splitk = small_m_splitk(N, K);
+  if (splitk > num_kb) splitk = num_kb;
+  // no empty K range: an accumulator that no MMA wrote would be added as is
+  while (splitk > 1 && static_cast<size_t>(splitk) * M * N > kSmallScratchFloats) --splitk;
+  splitk = pxl::ceil_div(num_kb, pxl::ceil_div(num_kb, splitk));
+  float* ws = nullptr;
+  uint32_t* counters = nullptr;
+  if (!small_m_scratch(stream, &ws, &counters)) return PXL_ERR_CUDA;
+  const int bn_tok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  // swapped operand slots: the weights take the 128-row slot, the tokens the narrow one
+  CUtensorMap ta, tb;
+  if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, ldw, BM, BK))
+    return PXL_ERR_TENSORMAP;
+  if (!pxl_host::make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, lda, bn_tok, BK))
+    return PXL_ERR_TENSORMAP;
+  GemmEpilogueArgs ep{};
+  ep.C = static_cast<pxl::bf16*>(C);
+  ep.C_f32 = f32_out ? static_cast<float*>(C) : nullptr;
+  ep.residual = static_cast<const pxl::bf16*>(residual);
+  ep.bias = static_cast<const pxl::bf16*>(bias);
+  ep.ldc = ldc;
+  ep.ws = ws;
+  ep.ldws = N;
+  ep.tile_counters = counters;
+  ep.splitk = splitk;
+  GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
+  const int items = pxl::ceil_div(N, BM) * splitk;
+  // kernel view: M' = output columns, N' = tokens
+  switch (bn_tok) {
+    case 32:
+      return launch_gemm<32, PXL_EPI_SPLITK_T>(ta, tb, ep, grp, GemmCommArgs{}, items, N, M, K, status, stream);
+    case 64:
+      return launch_gemm<64, PXL_EPI_SPLITK_T>(ta, tb, ep, grp, GemmCommArgs{}, items, N, M, K, status, stream);
+    default:
+      return launch_gemm<128, PXL_EPI_SPLITK_T>(ta, tb, ep, grp, GemmCommArgs{}, items, N, M, K, status, stream);
+  }
+}
+}  // namespace
+
+PXL_EXPORT int pxl_gemm_bf16_small_m(const void* A, const void* W, void* C, const void* residual,
+                                     const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
+                                     int splitk, int* status, cudaStream_t stream) {
+  return gemm_small_m(A, W, C, false, residual, bias, M, N, K, lda, ldw, ldc, splitk, status, stream);
 }
 
 PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* residual,
@@ -683,6 +926,10 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
        reinterpret_cast<uintptr_t>(C)) & 15)
     return PXL_ERR_INVALID_ARG;
   if (epi == PXL_EPI_RESIDUAL && residual == nullptr) return PXL_ERR_INVALID_ARG;
+  if (bn == 0 && pxl_gemm_bf16_uses_small_m(M, N, K, epi) &&
+      !((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) & 15))
+    return gemm_small_m(A, W, C, epi == PXL_EPI_F32, epi == PXL_EPI_RESIDUAL ? residual : nullptr, bias, M, N, K,
+                        lda, ldw, ldc, 0, status, stream);
   if (bn == 0) bn = pxl_gemm_bf16_pick_bn(M, N, epi);
   if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;
 

@@ -64,3 +64,51 @@ def dequant_if_needed(tensors: dict, name: str, cfg=None, dtype: Optional[torch.
         return t.to(dtype or torch.bfloat16)
     block = tuple((getattr(cfg, "weight_block_size", None) or [128, 128]))
     return dequant_fp8_block(t, scale, block, dtype or torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------------ mxfp4
+# GPT-OSS checkpoints store the expert matrices as MXFP4: groups of 32 values along the input
+# dimension share one power-of-two scale (e8m0, bias 127) and each value is a 4-bit e2m1 float,
+# two per byte with the low nibble first (``<name>_blocks`` uint8 [..., rows, K/32, 16] and
+# ``<name>_scales`` uint8 [..., rows, K/32]). The reference passes these checkpoints to its
+# backends untouched (``src/parallax/sglang/model_runner.py:358-366``); here they are expanded
+# to bf16 when the shard is loaded.
+_FP4_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
+
+
+def dequant_mxfp4(blocks: torch.Tensor, scales: torch.Tensor, dtype: torch.dtype = torch.bfloat16,
+                  rows_per_chunk: int = 1 << 16) -> torch.Tensor:
+    """``blocks [..., rows, G, 16]`` + ``scales [..., rows, G]`` -> ``[..., rows, G * 32]``."""
+    assert blocks.dtype == torch.uint8 and scales.dtype == torch.uint8
+    assert blocks.shape[:-1] == scales.shape, (blocks.shape, scales.shape)
+    *prefix, G, B = blocks.shape
+    lut = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=blocks.device)
+    flat_b = blocks.reshape(-1, B)
+    flat_s = scales.reshape(-1, 1).to(torch.int32) - 127
+    out = torch.empty((flat_b.shape[0], 2 * B), dtype=dtype, device=blocks.device)
+    for r0 in range(0, flat_b.shape[0], rows_per_chunk):      # bounded temporaries for 100-GB checkpoints
+        blk = flat_b[r0:r0 + rows_per_chunk]
+        sub = torch.empty((blk.shape[0], 2 * B), dtype=torch.float32, device=blocks.device)
+        sub[:, 0::2] = lut[(blk & 0x0F).long()]
+        sub[:, 1::2] = lut[(blk >> 4).long()]
+        out[r0:r0 + rows_per_chunk] = torch.ldexp(sub, flat_s[r0:r0 + rows_per_chunk]).to(dtype)
+    return out.view(*prefix, G * 2 * B)
+
+
+def quantize_mxfp4(w: torch.Tensor):
+    """Inverse of :func:`dequant_mxfp4` (round to nearest): ``w [..., rows, K]`` with K % 32 == 0 ->
+    (``blocks`` uint8 ``[..., rows, K/32, 16]``, ``scales`` uint8 ``[..., rows, K/32]``)."""
+    *prefix, K = w.shape
+    assert K % 32 == 0
+    g = w.float().reshape(-1, K // 32, 32)
+    amax = g.abs().amax(dim=-1).clamp_min(2.0 ** -126)
+    # the largest e2m1 magnitude is 6 = 1.5 * 2^2: pick the scale that maps the group maximum below 8
+    exp = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+    scaled = g / torch.exp2(exp)[..., None]
+    mags = torch.tensor(_FP4_VALUES[:8], dtype=torch.float32, device=w.device)
+    idx = (scaled.abs()[..., None] - mags).abs().argmin(dim=-1)
+    idx = idx + 8 * (scaled < 0)
+    idx = idx.to(torch.uint8)
+    blocks = (idx[..., 0::2] | (idx[..., 1::2] << 4)).reshape(*prefix, K // 32, 16)
+    scales = (exp + 127).to(torch.uint8).reshape(*prefix, K // 32)
+    return blocks.contiguous(), scales.contiguous()

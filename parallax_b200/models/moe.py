@@ -119,6 +119,29 @@ class MoEWeights:
                 return None
             return t.to(device=device, dtype=dt)
 
+        if prefix + "experts.gate_up_proj_blocks" in tensors:
+            # GPT-OSS as published: MXFP4 expert matrices, expanded to bf16 here. The rows of gate_up
+            # alternate gate / up; [E, rows, K] is already the [N, K] layout of the grouped GEMM.
+            from parallax_b200.loader.quant import dequant_mxfp4
+
+            def expand(name):
+                return dequant_mxfp4(tensors[prefix + name + "_blocks"], tensors[prefix + name + "_scales"],
+                                     dtype).to(device)
+
+            m.router = get("router.weight").contiguous()
+            m.router_bias = get("router.bias", required=False)
+            gu = expand("experts.gate_up_proj")                                   # [E, 2I, H]
+            m.w1 = torch.cat([gu[:, 0::2], gu[:, 1::2]], dim=1).reshape(E * gu.shape[1], -1).contiguous()
+            del gu
+            b = get("experts.gate_up_proj_bias", required=False)
+            if b is not None:
+                m.b1 = torch.cat([b[:, 0::2], b[:, 1::2]], dim=1).reshape(-1).contiguous()
+            dn = expand("experts.down_proj")                                      # [E, H, I]
+            m.w2 = dn.reshape(E * dn.shape[1], -1).contiguous()
+            b2 = get("experts.down_proj_bias", required=False)
+            m.b2 = None if b2 is None else b2.reshape(-1).contiguous()
+            m.act_mode = 1
+            return m
         fused = get("experts.gate_up_proj", required=False)
         if fused is not None and get("router.weight", required=False) is not None:
             # GPT-OSS layout: gate_up_proj [E, H, 2I] with gate / up in even / odd columns, expert biases

@@ -115,6 +115,31 @@ def gemm_pick_bn(M: int, N: int, epi: int = EPI_NONE) -> int:
     return _lib.lib().pxl_gemm_bf16_pick_bn(M, N, epi)
 
 
+def gemm_uses_small_m(M: int, N: int, K: int, epi: int = EPI_NONE) -> bool:
+    """Whether :func:`linear` (automatic tile choice) runs this shape on the small-M split-K path."""
+    return bool(_lib.lib().pxl_gemm_bf16_uses_small_m(M, N, K, epi))
+
+
+def linear_small_m(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   residual: Optional[torch.Tensor] = None, splitk: int = 0,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T`` for M <= 128 on the swapped-operand split-K kernel (``splitk`` 0 = automatic).
+    :func:`linear` picks this path by itself; the explicit entry exists for tests and benchmarks."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] == w.shape[1]
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if residual is not None:
+        assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
+    code = _lib.lib().pxl_gemm_bf16_small_m(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(bias), M, N, K, x.stride(0), w.stride(0),
+        out.stride(0), splitk, status_tensor(x.device).data_ptr(), _stream(x.device))
+    check(code, "pxl_gemm_bf16_small_m")
+    _count()
+    return out
+
+
 # ---------------------------------------------------------------------- elementwise
 def rmsnorm(
     x: torch.Tensor,
