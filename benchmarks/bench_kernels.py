@@ -116,11 +116,14 @@ def bench_gemm_small(rows):
                 return s.elapsed_time(e) / (4 * reps)
 
             ms_small = run(lambda w: cu.linear_small_m(x, w, out=out))
+            ms_scratch = run(lambda w: cu.linear_small_m(x, w, out=out, mode=1))
+            ms_cluster = run(lambda w: cu.linear_small_m(x, w, out=out, mode=2))
             ms_tile = min(run(lambda w: cu.linear(x, w, out=out, bn=64)), run(lambda w: cu.linear(x, w, out=out, bn=128)))
             ms_lib = run(lambda w: torch.matmul(x, w.t(), out=out))
             cu.check_status(x.device)
             byts = 2.0 * N * K
             rows.append({"kernel": "gemm_bf16_small_m", "M": M, "N": N, "K": K, "us": round(ms_small * 1e3, 2),
+                         "us_scratch": round(ms_scratch * 1e3, 2), "us_cluster": round(ms_cluster * 1e3, 2),
                          "us_plain_tiles": round(ms_tile * 1e3, 2), "us_torch_matmul": round(ms_lib * 1e3, 2),
                          "weight_gbs": round(byts / ms_small / 1e6, 1),
                          "roofline_frac": round(byts / (hbm * 1e9) * 1e3 / ms_small, 3), "tag": tag})

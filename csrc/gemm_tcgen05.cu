@@ -259,9 +259,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = num_m * num_n;
   const int num_kb = ceil_div(K, BK);
   // split-K (small-M path only): work item = (tile, K range); every range holds at least one k-block
-  const int splitk = (EPI == PXL_EPI_SPLITK_T) ? ep.splitk : 1;
+  constexpr bool kSplit = EPI == PXL_EPI_SPLITK_T || EPI == PXL_EPI_SPLITK_C;
+  const int splitk = kSplit ? ep.splitk : 1;
   const int kb_per = ceil_div(num_kb, splitk);
   const int num_items = num_tiles * splitk;
+  // item -> (tile, K range). Cluster variant: the CTAs of a cluster (consecutive block ids) share a
+  // tile, the cluster rank is the K range, and the grid holds exactly one CTA per item.
+  auto item_tile = [&](int item) { return EPI == PXL_EPI_SPLITK_C ? item / splitk : item % num_tiles; };
+  auto item_ks = [&](int item) { return EPI == PXL_EPI_SPLITK_C ? item % splitk : item / num_tiles; };
+  bool acc_ready = false;  // cluster variant: this CTA's accumulator is complete
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -294,8 +300,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gemm_ctas) {
-        const int tile = item % num_tiles;
-        const int kb0 = (item / num_tiles) * kb_per;
+        const int tile = item_tile(item);
+        const int kb0 = item_ks(item) * kb_per;
         const int kb1 = kb0 + kb_per < num_kb ? kb0 + kb_per : num_kb;
         const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
         if (comm.ag_ncopy > 0 && tc.a_row / comm.rows_per_rank != comm.rank) {
@@ -332,7 +338,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; ok && item < num_items; item += gemm_ctas) {
-        const int kb0 = (item / num_tiles) * kb_per;
+        const int kb0 = item_ks(item) * kb_per;
         const int kb1 = kb0 + kb_per < num_kb ? kb0 + kb_per : num_kb;
         ok = mbar_wait_bounded(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status,
                                PXL_DEV_TIMEOUT_TMEM_EMPTY);
@@ -371,7 +377,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < num_items; item += gemm_ctas) {
-      const int tile = item % num_tiles;
+      const int tile = item_tile(item);
       const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
       const int n_blk = tc.n_blk;
       const int M_end = tc.row_end;
@@ -380,6 +386,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if constexpr (EPI == PXL_EPI_SPLITK_C) {
+        acc_ready = true;  // drained after the cluster barrier below
+        break;
+      }
       const int row = tc.a_row + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       if constexpr (EPI == PXL_EPI_SILU_MUL) {
@@ -461,7 +471,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // operands swapped: this thread's accumulator row is output column `row`, accumulator
         // column j is token j (N = number of tokens). Every K range has its own slab of the
         // scratch, so the sums are formed in a fixed order; a warp stores 32 neighbouring floats.
-        float* slab = ep.ws + static_cast<size_t>(item / num_tiles) * N * ep.ldws;
+        float* slab = ep.ws + static_cast<size_t>(item_ks(item)) * N * ep.ldws;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN && c0 < N; c0 += 32) {
           uint32_t r[32];
@@ -637,6 +647,85 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
+  if constexpr (EPI == PXL_EPI_SPLITK_C) {
+    // ------------------------------------- split-K reduction inside the cluster (DSMEM)
+    // Every thread of every CTA passes both cluster barriers, also after a failed wait (all other
+    // waits are bounded). Barrier 1: all accumulators of the cluster are complete, so nobody's
+    // pipeline stages are in use any more and can receive partial sums: CTA r collects, from every
+    // CTA of the cluster, the tokens [r*S, (r+1)*S) as [source][S][128 columns] floats. Barrier 2:
+    // the partial sums have landed; each CTA adds its tokens in K order and writes the result.
+    __syncwarp();
+    cluster_sync_all();
+    const uint32_t my_rank = cluster_cta_rank();
+    const int n_tok = N;
+    const int S = ceil_div(n_tok, splitk);
+    const uint32_t recv0 = smem_u32(smem);
+    if (warp >= 2 && acc_ready) {
+      const int q = warp & 3;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t col_off = (my_rank * S * 128 + q * 32 + lane) * 4;
+      int owner = 0, tl = 0;
+      uint32_t dst = cluster_map_shared(recv0, 0) + col_off;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN && c0 < n_tok; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (c0 + j < n_tok) {
+            st_shared_cluster_f32(dst + tl * 512, __uint_as_float(r[j]));
+            if (++tl == S) {
+              tl = 0;
+              ++owner;
+              if (owner < splitk) dst = cluster_map_shared(recv0, owner) + col_off;
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2 && acc_ready) {
+      const int tile = blockIdx.x / splitk;
+      const int n0 = tile * BM;  // first output column of the tile (num_n == 1)
+      const int t0 = my_rank * S;
+      const int s_valid = n_tok - t0 < S ? n_tok - t0 : S;
+      for (int i = threadIdx.x - 64; i < s_valid * 32; i += 128) {
+        const int tl = i >> 5, c4 = (i & 31) * 4;
+        const int n = n0 + c4;
+        if (n < M) {
+          const uint32_t src = recv0 + (tl * 128 + c4) * 4;
+          float4 a = ld_shared_f32x4(src);
+          for (int r = 1; r < splitk; ++r) {
+            const float4 b = ld_shared_f32x4(src + r * S * 512);
+            a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+          }
+          const size_t c_off = static_cast<size_t>(t0 + tl) * ep.ldc + n;
+          if (ep.bias) {
+            const uint2 b = *reinterpret_cast<const uint2*>(ep.bias + n);
+            const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+            a.x += b0.x, a.y += b0.y, a.z += b1.x, a.w += b1.y;
+          }
+          if (ep.residual) {
+            const uint2 b = *reinterpret_cast<const uint2*>(ep.residual + c_off);
+            const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+            a.x += b0.x, a.y += b0.y, a.z += b1.x, a.w += b1.y;
+          }
+          if (ep.C_f32 != nullptr) {
+            *reinterpret_cast<float4*>(ep.C_f32 + c_off) = a;
+          } else {
+            uint2 o;
+            o.x = pack_bf16x2(a.x, a.y);
+            o.y = pack_bf16x2(a.z, a.w);
+            *reinterpret_cast<uint2*>(ep.C + c_off) = o;
+          }
+        }
+      }
+    }
+  }
+
   if constexpr (EPI == PXL_EPI_RS) {
     if (warp >= 2) {
       // ---------------------------------------------- reduce the rows this rank owns
@@ -742,6 +831,52 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue
   }
   kern<<<grid, kGemmThreads, gemm_smem_bytes<BN, EPI>(), stream>>>(ta, tb, ep, grp, comm, M, N, K, status);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
+}
+
+// Cluster variant of the small-M path: one CTA per (tile, K range), the K ranges of a tile in one
+// cluster. max_clusters (optional) receives how many such clusters the device runs at once.
+template <int BN>
+int launch_gemm_cluster(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogueArgs& ep, int items,
+                        int cluster, int M, int N, int K, int* status, cudaStream_t stream, int* max_clusters) {
+  auto kern = gemm_bf16_tcgen05_kernel<BN, PXL_EPI_SPLITK_C>;
+  constexpr int smem = gemm_smem_bytes<BN, PXL_EPI_SPLITK_C>();
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return PXL_ERR_CUDA;
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(items), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_clusters != nullptr) {
+    cfg.gridDim = dim3(static_cast<unsigned>(cluster) * 64u, 1, 1);  // the query only needs a legal grid
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    *max_clusters = n;
+    return PXL_OK;
+  }
+  GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
+  GemmCommArgs comm{};
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, ep, grp, comm, M, N, K, status) != cudaSuccess) {
+    cudaGetLastError();
+    return PXL_ERR_CUDA;
+  }
+  return PXL_OK;
 }
 
 template <int BN>
@@ -864,23 +999,70 @@ PXL_EXPORT int pxl_gemm_bf16_uses_small_m(int M, int N, int K, int epi) {
 }
 
 namespace {
+// How many clusters of `cluster` CTAs of the small-M kernel the device keeps resident at once
+// (cached per device, token-slot width and cluster size; 0 = unknown or not launchable).
+int small_m_max_clusters(int bn_tok, int cluster) {
+  static int cache[64][3][9];
+  static bool known[64][3][9] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cluster < 1 || cluster > 8) return 0;
+  const int bi = bn_tok == 32 ? 0 : (bn_tok == 64 ? 1 : 2);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!known[dev][bi][cluster]) {
+    int n = 0;
+    CUtensorMap dummy{};
+    GemmEpilogueArgs ep{};
+    switch (bn_tok) {
+      case 32: launch_gemm_cluster<32>(dummy, dummy, ep, 0, cluster, 0, 0, 0, nullptr, nullptr, &n); break;
+      case 64: launch_gemm_cluster<64>(dummy, dummy, ep, 0, cluster, 0, 0, 0, nullptr, nullptr, &n); break;
+      default: launch_gemm_cluster<128>(dummy, dummy, ep, 0, cluster, 0, 0, 0, nullptr, nullptr, &n); break;
+    }
+    cache[dev][bi][cluster] = n;
+    known[dev][bi][cluster] = true;
+  }
+  return cache[dev][bi][cluster];
+}
+
+// mode 0 = automatic, 1 = scratch slabs + last-CTA finish, 2 = cluster reduction over DSMEM
 int gemm_small_m(const void* A, const void* W, void* C, bool f32_out, const void* residual, const void* bias, int M,
-                 int N, int K, int lda, int ldw, int ldc, int splitk, int* status, cudaStream_t stream) {
+                 int N, int K, int lda, int ldw, int ldc, int splitk, int mode, int* status, cudaStream_t stream) {
   if (M <= 0 || M > kSmallMaxM || N <= 0 || N > kSmallMaxN || K <= 0) return PXL_ERR_INVALID_ARG;
   if ((K % 8) || (lda % 8) || (ldw % 8) || (ldc % 8) || (N % 8)) return PXL_ERR_INVALID_ARG;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C) |
        reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) & 15)
     return PXL_ERR_INVALID_ARG;
+  if (mode < 0 || mode > 2) return PXL_ERR_INVALID_ARG;
   const int num_kb = pxl::ceil_div(K, BK);
-  if (splitk <= 0) splitk = small_m_splitk(N, K);
-  if (splitk > num_kb) splitk = num_kb;
-  // no empty K range: an accumulator that no MMA wrote would be added as is
-  while (splitk > 1 && static_cast<size_t>(splitk) * M * N > kSmallScratchFloats) --splitk;
-  splitk = pxl::ceil_div(num_kb, pxl::ceil_div(num_kb, splitk));
-  float* ws = nullptr;
-  uint32_t* counters = nullptr;
-  if (!small_m_scratch(stream, &ws, &counters)) return PXL_ERR_CUDA;
+  const int tiles = pxl::ceil_div(N, BM);
   const int bn_tok = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  const bool auto_split = splitk <= 0;
+  if (auto_split) splitk = small_m_splitk(N, K);
+  if (splitk > num_kb) splitk = num_kb;
+  if (mode != 1) {
+    // the widest cluster (at most 8 CTAs, at most the K ranges asked for) of which all tiles' clusters
+    // are resident at once; an explicit splitk is only narrowed by the hardware limit of 8
+    int c = splitk < 8 ? splitk : 8;
+    if (auto_split) {
+      while (c > 1 && small_m_max_clusters(bn_tok, c) < tiles) --c;
+    }
+    const bool launchable = small_m_max_clusters(bn_tok, c) > 0;
+    // few tiles and a long K: more K ranges than a cluster holds put more SMs to work
+    const bool prefer_scratch = auto_split && splitk > c && tiles * c * 2 < pxl_host::num_sms();
+    if (launchable && (mode == 2 || !prefer_scratch)) {
+      splitk = c;
+      mode = 2;
+    } else if (mode == 2) {
+      return PXL_ERR_CUDA;
+    } else {
+      mode = 1;
+    }
+  }
+  // no empty K range: an accumulator that no MMA wrote would be added as is
+  if (mode == 1) {
+    while (splitk > 1 && static_cast<size_t>(splitk) * M * N > kSmallScratchFloats) --splitk;
+  }
+  splitk = pxl::ceil_div(num_kb, pxl::ceil_div(num_kb, splitk));
   // swapped operand slots: the weights take the 128-row slot, the tokens the narrow one
   CUtensorMap ta, tb;
   if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, ldw, BM, BK))
@@ -893,13 +1075,19 @@ int gemm_small_m(const void* A, const void* W, void* C, bool f32_out, const void
   ep.residual = static_cast<const pxl::bf16*>(residual);
   ep.bias = static_cast<const pxl::bf16*>(bias);
   ep.ldc = ldc;
-  ep.ws = ws;
   ep.ldws = N;
-  ep.tile_counters = counters;
   ep.splitk = splitk;
-  GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
-  const int items = pxl::ceil_div(N, BM) * splitk;
+  const int items = tiles * splitk;
   // kernel view: M' = output columns, N' = tokens
+  if (mode == 2) {
+    switch (bn_tok) {
+      case 32: return launch_gemm_cluster<32>(ta, tb, ep, items, splitk, N, M, K, status, stream, nullptr);
+      case 64: return launch_gemm_cluster<64>(ta, tb, ep, items, splitk, N, M, K, status, stream, nullptr);
+      default: return launch_gemm_cluster<128>(ta, tb, ep, items, splitk, N, M, K, status, stream, nullptr);
+    }
+  }
+  if (!small_m_scratch(stream, &ep.ws, &ep.tile_counters)) return PXL_ERR_CUDA;
+  GemmGroupArgs grp{nullptr, nullptr, nullptr, nullptr, 0};
   switch (bn_tok) {
     case 32:
       return launch_gemm<32, PXL_EPI_SPLITK_T>(ta, tb, ep, grp, GemmCommArgs{}, items, N, M, K, status, stream);
@@ -913,8 +1101,8 @@ int gemm_small_m(const void* A, const void* W, void* C, bool f32_out, const void
 
 PXL_EXPORT int pxl_gemm_bf16_small_m(const void* A, const void* W, void* C, const void* residual,
                                      const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
-                                     int splitk, int* status, cudaStream_t stream) {
-  return gemm_small_m(A, W, C, false, residual, bias, M, N, K, lda, ldw, ldc, splitk, status, stream);
+                                     int splitk, int mode, int* status, cudaStream_t stream) {
+  return gemm_small_m(A, W, C, false, residual, bias, M, N, K, lda, ldw, ldc, splitk, mode, status, stream);
 }
 
 PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* residual,
@@ -929,7 +1117,7 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
   if (bn == 0 && pxl_gemm_bf16_uses_small_m(M, N, K, epi) &&
       !((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) & 15))
     return gemm_small_m(A, W, C, epi == PXL_EPI_F32, epi == PXL_EPI_RESIDUAL ? residual : nullptr, bias, M, N, K,
-                        lda, ldw, ldc, 0, status, stream);
+                        lda, ldw, ldc, 0, 0, status, stream);
   if (bn == 0) bn = pxl_gemm_bf16_pick_bn(M, N, epi);
   if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;
 

@@ -24,7 +24,8 @@ typedef struct CUstream_st* pxl_stream_t;
 #define PXL_EPI_F32 3       // C = A W^T (+bias)                      fp32 out
 #define PXL_EPI_RS 4        // partial sums scattered to the owning rank + reduce (pxl_gemm_bf16_rs)
 #define PXL_EPI_SCATTER 5   // every output row stored through its own pointer, possibly on a peer GPU
-#define PXL_EPI_SPLITK_T 6  // internal: small-M path (operands swapped, split along K, fp32 atomics + last-CTA finish)
+#define PXL_EPI_SPLITK_T 6  // internal: small-M path (operands swapped, split along K, fp32 slabs + last-CTA finish)
+#define PXL_EPI_SPLITK_C 7  // internal: small-M path, the K ranges of a tile form a cluster and reduce over DSMEM
 
 // ---- gemm_tcgen05.cu -------------------------------------------------------
 // C[M,N] = A[M,K] * W[N,K]^T. lda/ldw/ldc in elements. `bn` = tile width (64/128/256)
@@ -36,11 +37,14 @@ int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* residual, c
 int pxl_gemm_bf16_pick_bn(int M, int N, int epi);
 // Small-M (decode) GEMM, M <= 128: the weight matrix takes the 128-row operand slot of the tensor
 // core, the few activation rows the narrow one, and K is split over `splitk` CTAs per 128 output
-// columns (0 = automatic) so that every SM streams weights. Partial sums meet in an fp32 scratch
-// owned by the library (one per stream); the CTA that arrives last adds bias / residual and writes
-// bf16. pxl_gemm_bf16 takes this path by itself when bn == 0 and the shape qualifies.
+// columns (0 = automatic) so that every SM streams weights. mode 2: the CTAs of one tile form a
+// thread-block cluster (splitk <= 8), exchange their fp32 partial sums through distributed shared
+// memory and each finishes a slice of the tokens (+ bias, + residual, bf16 out). mode 1: partial
+// sums meet in an fp32 scratch owned by the library (one per stream) and the CTA that arrives last
+// finishes the tile. mode 0 picks. Sums are formed in K order either way (bitwise repeatable).
+// pxl_gemm_bf16 takes this path by itself when bn == 0 and the shape qualifies.
 int pxl_gemm_bf16_small_m(const void* A, const void* W, void* C, const void* residual, const void* bias,
-                          int M, int N, int K, int lda, int ldw, int ldc, int splitk, int* status,
+                          int M, int N, int K, int lda, int ldw, int ldc, int splitk, int mode, int* status,
                           pxl_stream_t stream);
 // 1 when pxl_gemm_bf16(bn = 0) would use the small-M path for this shape and epilogue.
 int pxl_gemm_bf16_uses_small_m(int M, int N, int K, int epi);

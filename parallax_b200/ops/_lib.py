@@ -50,7 +50,7 @@ _P = c_void_p
 _SIGS = {
     "pxl_gemm_bf16": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "pxl_gemm_bf16_pick_bn": [c_int, c_int, c_int],
-    "pxl_gemm_bf16_small_m": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "pxl_gemm_bf16_small_m": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "pxl_gemm_bf16_uses_small_m": [c_int, c_int, c_int, c_int],
     "pxl_rmsnorm": [_P, _P, _P, _P, c_int, c_int, c_float, c_float, _P],
     "pxl_qk_norm_rope_cache": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,

@@ -122,9 +122,11 @@ def gemm_uses_small_m(M: int, N: int, K: int, epi: int = EPI_NONE) -> bool:
 
 def linear_small_m(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                    residual: Optional[torch.Tensor] = None, splitk: int = 0,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x[M,K] @ w[N,K]^T`` for M <= 128 on the swapped-operand split-K kernel (``splitk`` 0 = automatic).
-    :func:`linear` picks this path by itself; the explicit entry exists for tests and benchmarks."""
+                   out: Optional[torch.Tensor] = None, mode: int = 0) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T`` for M <= 128 on the swapped-operand split-K kernel (``splitk`` 0 = automatic;
+    ``mode`` 1 = partial sums through a global scratch, 2 = reduced inside a thread-block cluster over
+    distributed shared memory, 0 = automatic). :func:`linear` picks this path by itself; the explicit
+    entry exists for tests and benchmarks."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] == w.shape[1]
     M, K = x.shape
     N = w.shape[0]
@@ -134,7 +136,7 @@ def linear_small_m(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     code = _lib.lib().pxl_gemm_bf16_small_m(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(bias), M, N, K, x.stride(0), w.stride(0),
-        out.stride(0), splitk, status_tensor(x.device).data_ptr(), _stream(x.device))
+        out.stride(0), splitk, mode, status_tensor(x.device).data_ptr(), _stream(x.device))
     check(code, "pxl_gemm_bf16_small_m")
     _count()
     return out

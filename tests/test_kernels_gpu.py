@@ -90,28 +90,30 @@ def test_gemm_epilogues(cu):
         (128, 12288, 4096, 5),
     ],
 )
-def test_gemm_small_m_splitk(cu, M, N, K, splitk):
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemm_small_m_splitk(cu, M, N, K, splitk, mode):
+    """mode 1: partial sums through the global scratch; mode 2: reduced inside a thread-block cluster."""
     torch.manual_seed(5)
     x = torch.randn(M, K, device=_dev(), dtype=torch.bfloat16)
     w = torch.randn(N, K, device=_dev(), dtype=torch.bfloat16) * 0.05
     bias = torch.randn(N, device=_dev(), dtype=torch.bfloat16)
     res = torch.randn(M, N, device=_dev(), dtype=torch.bfloat16)
     want = x.float() @ w.float().t()
-    y = cu.linear_small_m(x, w, splitk=splitk)
+    y = cu.linear_small_m(x, w, splitk=splitk, mode=mode)
     assert _rel_err(y, want) < 5e-3
-    y2 = cu.linear_small_m(x, w, bias=bias, residual=res, splitk=splitk)
+    y2 = cu.linear_small_m(x, w, bias=bias, residual=res, splitk=splitk, mode=mode)
     assert _rel_err(y2, want + bias.float() + res.float()) < 5e-3
     # partial sums are added in a fixed order: repeated launches agree bit for bit
-    y3 = cu.linear_small_m(x, w, splitk=splitk)
+    y3 = cu.linear_small_m(x, w, splitk=splitk, mode=mode)
     assert torch.equal(y, y3)
-    # the automatic path of linear() takes the same kernel for these shapes
+    # the automatic path of linear() takes the same kernel family for these shapes
     assert cu.gemm_uses_small_m(M, N, K)
     assert _rel_err(cu.linear(x, w, bias=bias, residual=res), want + bias.float() + res.float()) < 5e-3
     y32 = cu.linear(x, w, epi=ref.EPI_F32)     # fp32 output (router logits) through the same path
     assert y32.dtype == torch.float32 and _rel_err(y32, want) < 1e-3
     # a strided output (column slice of a wider buffer)
     wide = torch.zeros(M, N + 64, device=_dev(), dtype=torch.bfloat16)
-    cu.linear_small_m(x, w, splitk=splitk, out=wide[:, 64:])
+    cu.linear_small_m(x, w, splitk=splitk, out=wide[:, 64:], mode=mode)
     assert torch.equal(wide[:, 64:], y) and float(wide[:, :64].abs().sum()) == 0.0
     cu.check_status(_dev())
 
