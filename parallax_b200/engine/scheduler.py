@@ -58,12 +58,17 @@ class BatchScheduler:
         is_first_peer: bool = True,
         prefill_priority: int = 0,
         shared_state=None,
+        max_prefill_tokens_per_batch: Optional[int] = None,
     ):
         self.max_batch_size = max_batch_size
         self.max_num_tokens_per_batch = max_num_tokens_per_batch
         self.micro_batch_size = max(1, max_batch_size // max(1, micro_batch_ratio))
         self.cache_manager = cache_manager
         self.chunked_prefill_size = chunked_prefill_size
+        # prompt tokens one batch may carry in total (None = only the token budget limits them): with
+        # micro-batches rotating through a pipeline this keeps them even, a long prompt is spread over
+        # consecutive micro-batches instead of stalling every stage behind one heavy batch
+        self.max_prefill_tokens_per_batch = max_prefill_tokens_per_batch
         self.request_timeout_s = request_timeout_s
         self.eos_token_ids = _normalize_token_ids(eos_token_id)
         self.max_total_length = max_total_length
@@ -185,8 +190,11 @@ class BatchScheduler:
             (prefills if req.is_prefill else decodes).append(req)
         used = 0
         chunk = self.chunked_prefill_size
+        prefill_cap = self.max_prefill_tokens_per_batch
         for req in prefills:
             if len(batch) >= self.micro_batch_size:
+                break
+            if prefill_cap is not None and used >= prefill_cap:
                 break
             remaining = req.remaining_prefill
             if remaining <= 0:
@@ -195,10 +203,12 @@ class BatchScheduler:
                 remaining = 1
             cost = remaining if not chunk else min(remaining, chunk)
             room = budget - used
+            if prefill_cap is not None:
+                room = min(room, prefill_cap - used)
             if room <= 0:
                 break
             if cost > room:
-                if not chunk:
+                if not chunk and prefill_cap is None:
                     continue
                 cost = room
             last = cost == remaining

@@ -90,7 +90,8 @@ class DistEngine:
     def __init__(self, cfg: ModelConfig, pp: int, tp: int, device, dtype=None, page_size: int = 16,
                  num_blocks: Optional[int] = None, kv_fraction: float = 0.85, max_batch_size: int = 8,
                  max_num_tokens_per_batch: int = 16384, micro_batch_ratio: Optional[int] = None,
-                 chunked_prefill_size: Optional[int] = 1024, enable_prefix_cache: bool = True,
+                 chunked_prefill_size: Optional[int] = 1024, max_prefill_tokens_per_batch: Optional[int] = None,
+                 enable_prefix_cache: bool = True,
                  max_total_length: int = 32768, request_timeout_s: Optional[float] = 600, eos_token_id=None,
                  seed: int = 0, weights: Optional[dict] = None, fused: Optional[bool] = None,
                  max_in_flight: Optional[int] = None, weights_prefiltered: bool = False,
@@ -155,6 +156,7 @@ class DistEngine:
             self.planner = Planner(cfg, self.num_blocks, page_size, max_batch_size, max_num_tokens_per_batch, ratio,
                                    chunked_prefill_size, enable_prefix_cache, max_total_length, request_timeout_s,
                                    eos_token_id)
+            self.planner.scheduler.max_prefill_tokens_per_batch = max_prefill_tokens_per_batch
         max_blocks = (max_total_length + page_size - 1) // page_size + 1
         self.builders = [BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size, max_batch_size,
                                       max_blocks) for _ in range(self.max_in_flight + 1)]
@@ -167,6 +169,7 @@ class DistEngine:
         self.keep_logits = False
         self.last_logits = None
         self.marks: list = []
+        self._busy_events: list = []     # (start, end, rows) of every micro-batch's compute since the last mark
         self.h2d_bytes = 0
         self.host_s = {"plan": 0.0, "publish": 0.0, "launch": 0.0, "wait": 0.0, "commit": 0.0}
 
@@ -242,8 +245,16 @@ class DistEngine:
             rows = w.model.comm.rows_per_rank(T) if topo.tp > 1 else T
             hidden = torch.empty((rows, H), dtype=w.dtype, device=self.device)
             dist.recv(hidden, src=topo.rank - topo.tp)
+        ev0 = ev1 = None
+        if self.device.type == "cuda" and self.marks and len(self._busy_events) < 100000:
+            ev0 = torch.cuda.Event(enable_timing=True)      # only between benchmark marks
+            ev0.record()
         with torch.inference_mode():
             out = w.run(fb, hidden)
+        if ev0 is not None:
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev1.record()
+            self._busy_events.append((ev0, ev1, T))
         tokens = None
         if self.keep_logits and topo.is_last_stage:
             self.last_logits = out
@@ -291,6 +302,7 @@ class DistEngine:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
         self.marks.append((ev, time.perf_counter(), cu_launch_count(), self.h2d_bytes))
+        self._busy_prev, self._busy_events = self._busy_events, []
 
     def _on_elapsed(self) -> dict:
         """Device time between the last two marks (max over ranks) and the kernels launched /
@@ -303,7 +315,17 @@ class DistEngine:
         dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=self.ctrl)
         sm = torch.tensor([float(l1 - l0), float(h1 - h0)], dtype=torch.float64)
         dist.all_reduce(sm, op=dist.ReduceOp.SUM, group=self.ctrl)
-        return {"device_ms": float(mx[0]), "launches": int(sm[0]), "h2d_bytes": int(sm[1]), "wall_s": t1 - t0}
+        # how long each rank's GPU computed between the marks (the rest of device_ms it waited for its
+        # neighbours or its host) and the largest micro-batch it saw
+        busy = torch.zeros(self.topo.world, dtype=torch.float64)
+        rows = torch.zeros(self.topo.world, dtype=torch.float64)
+        for a, b, n_rows in getattr(self, "_busy_prev", []):
+            busy[self.topo.rank] += a.elapsed_time(b)
+            rows[self.topo.rank] = max(float(rows[self.topo.rank]), float(n_rows))
+        dist.all_reduce(busy, op=dist.ReduceOp.SUM, group=self.ctrl)
+        dist.all_reduce(rows, op=dist.ReduceOp.SUM, group=self.ctrl)
+        return {"device_ms": float(mx[0]), "launches": int(sm[0]), "h2d_bytes": int(sm[1]), "wall_s": t1 - t0,
+                "busy_ms_per_rank": [round(float(x), 2) for x in busy], "max_rows_per_rank": [int(x) for x in rows]}
 
     def mark(self) -> None:
         """Rank 0: every rank records a CUDA event at this point of its stream."""

@@ -146,3 +146,37 @@ def test_step_tracer_writes_chrome_trace(tmp_path):
     names = {e["name"] for e in ev}
     assert {"schedule+plan", "build+launch", "wait for tokens", "commit"} <= names
     assert all(e["dur"] > 0 for e in ev)
+
+
+def test_scheduler_prefill_cap_spreads_a_prompt_over_batches():
+    """With a per-batch cap on prompt tokens a long prompt is prefilled in consecutive slices while the
+    decode rows of the other requests ride along in every batch."""
+    from parallax_b200.engine.request import Request, SamplingParams
+    from parallax_b200.engine.scheduler import BatchScheduler
+
+    sched = BatchScheduler(max_batch_size=8, max_num_tokens_per_batch=4096, chunked_prefill_size=None,
+                           max_prefill_tokens_per_batch=100)
+    sp = SamplingParams(max_new_tokens=4, temperature=0.0, ignore_eos=True)
+    long_req = Request(input_ids=list(range(250)), sampling_params=sp)
+    short = Request(input_ids=list(range(40)), sampling_params=sp)
+    sched.enque_request(long_req)
+    sched.enque_request(short)
+    seen = []
+    for _ in range(5):
+        batch = sched.form_batch()
+        seen.append([(s.req is long_req, s.num_tokens, s.is_prefill) for s in batch])
+        for s in batch:
+            if s.is_prefill:
+                s.req.num_computed_tokens = s.start + s.num_tokens
+                if s.produces_token:
+                    s.req.commit_new_token(1)
+            else:
+                s.req.commit_new_token(1)
+            sched.enque_request(s.req)
+    for batch in seen:
+        assert sum(n for _, n, p in batch if p) <= 100
+    slices = [n for batch in seen for is_long, n, p in batch if is_long and p]
+    assert sum(slices) == 250 and len(slices) >= 3
+    assert sum(n for batch in seen for is_long, n, p in batch if not is_long and p) == 40
+    # once the short prompt is done its decode rows share batches with the long prompt's slices
+    assert any(any(p for _, _, p in batch) and any(not p for _, _, p in batch) for batch in seen)
