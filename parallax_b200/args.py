@@ -43,6 +43,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--disable-prefix-cache", dest="enable_prefix_cache", action="store_false", default=True,
                    help="Disable the radix prefix cache")
     p.add_argument("--chunked-prefill-size", type=int, default=1024, help="Max prompt tokens per prefill chunk (0: off)")
+    p.add_argument("--max-prefill-tokens-per-batch", type=int, default=0,
+                   help="Prompt tokens one (micro-)batch carries over all requests; evens out the micro-batches "
+                        "of an in-box pipeline (0: only the token budget limits them)")
     # batching
     p.add_argument("--max-batch-size", type=int, default=8, help="Maximum number of in-flight requests")
     p.add_argument("--max-num-tokens-per-batch", type=int, default=16384, help="Token budget of one forward pass")

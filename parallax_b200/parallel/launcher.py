@@ -141,6 +141,7 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
                 page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
                 max_batch_size=args.max_batch_size, max_num_tokens_per_batch=args.max_num_tokens_per_batch,
                 micro_batch_ratio=args.micro_batch_ratio, chunked_prefill_size=args.chunked_prefill_size,
+                max_prefill_tokens_per_batch=getattr(args, "max_prefill_tokens_per_batch", 0) or None,
                 enable_prefix_cache=args.enable_prefix_cache, max_total_length=args.max_sequence_length,
                 request_timeout_s=args.request_timeout_s, num_blocks=None if device_type == "cuda" else 1024,
                 lora_paths=(args.lora_paths or []) if args.enable_lora else [], log_level=args.log_level)
