@@ -300,12 +300,16 @@ attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __r
 // ---- decode, TMA-fed variant (D = 128; page_size 16, 32 or 64) ------------------------------------
 // A (block, kv head) page of the cache is one contiguous [page, 128] matrix, so a KV tile of 64
 // tokens is 64 / page box loads per operand half: one thread issues them through the TMA engine
-// (128-byte swizzle, completion on an mbarrier) two tiles ahead of the four consumer warps. This
-// removes the per-thread address arithmetic and the 2048 cp.async instructions per tile of the
-// kernel above, which was issue-bound at half of the DRAM bandwidth.
+// (128-byte swizzle, completion on an mbarrier) up to three tiles ahead of the four consumer warps.
+// This removes the per-thread address arithmetic and the 2048 cp.async instructions per tile of the
+// kernel above, which was issue-bound at half of the DRAM bandwidth. The issuing lane sits in a warp
+// of its own (warp 4) and the stages are handed back through "empty" mbarriers (one arrival per
+// consumer warp), so the consumer warps never meet at a CTA-wide barrier inside the loop: with the
+// producer inside warp 0 and a __syncthreads per tile the top stall was that barrier.
 constexpr int kDecStages = 3;
+constexpr int kDecThreads = 160;  // 4 consumer warps + 1 producer warp
 
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(kDecThreads, 2)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                        const bf16* __restrict__ q, int64_t q_stride, const int* __restrict__ block_tables,
                        const int* __restrict__ ctx_lens, bf16* __restrict__ out, float* __restrict__ workspace,
@@ -316,9 +320,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t stage0 = smem_u32(smem);  // stage s: K tile at s * 2 * TILE_BYTES, V tile behind it
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecStages * 2 * TILE_BYTES);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kDecStages);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecStages * 2 * TILE_BYTES);  // full[S], empty[S]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kDecStages);
   const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = smem_u32(bars + kDecStages);
 
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int G = Hq / Hkv;
@@ -337,7 +342,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < kDecStages; ++s) mbar_init(full0 + 8 * s, 1);
+    for (int s = 0; s < kDecStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 4);  // one arrival per consumer warp
+    }
     mbar_fence_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tm_k);
@@ -365,8 +373,22 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
       tma_load_2d(v_dst + TILE * 128 + off, &tm_v, bar, 64, row0);
     }
   };
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kDecStages - 1 && i < n_tiles; ++i) issue(t_begin + i, i);
+  int failed = 0;
+  if (warp == 4) {
+    // ---- producer warp: one lane runs up to kDecStages tiles ahead of the consumers
+    if (lane == 0) {
+      for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it % kDecStages;
+        if (it >= kDecStages &&
+            !mbar_wait_bounded(empty0 + 8 * stage, ((it / kDecStages) - 1) & 1, abort_flag, status,
+                               PXL_DEV_TIMEOUT_EMPTY)) {
+          failed = 1;
+          break;
+        }
+        issue(t_begin + it, stage);
+      }
+    }
+    __syncwarp();
   }
 
   uint32_t qf[D / 16][4];
@@ -389,19 +411,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
 
-  int failed = 0;
-  for (int it = 0; it < n_tiles; ++it) {
+  for (int it = 0; warp < 4 && it < n_tiles; ++it) {
     const int stage = it % kDecStages;
-    // everyone is done with tile it-1, whose buffer is the one refilled below
-    if (__syncthreads_or(failed)) {
-      failed = 1;
-      break;
-    }
-    if (threadIdx.x == 0 && it + kDecStages - 1 < n_tiles)
-      issue(t_begin + it + kDecStages - 1, (it + kDecStages - 1) % kDecStages);
     if (!mbar_wait_bounded(full0 + 8 * stage, (it / kDecStages) & 1, abort_flag, status, PXL_DEV_TIMEOUT_FULL)) {
       failed = 1;
-      continue;  // reported to the whole CTA at the next barrier
+      break;  // reported to the whole CTA at the barrier behind the loop
     }
     const int t = t_begin + it;
     const uint32_t k_smem = stage0 + stage * 2 * TILE_BYTES, v_smem = k_smem + TILE_BYTES;
@@ -456,6 +470,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
       pf[3] = pack_bf16x2(s[1][2], s[1][3]);
       pv_16x16<D, true>(pf, v_smem, r0, o);
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + 8 * stage);  // this warp is done with the stage
   }
   if (__syncthreads_or(failed)) {
     // loads that are still in flight must land before the CTA's shared memory is released
@@ -469,7 +485,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
   float* l_sm = m_sm + 4 * 16;                           // [4][16]
   l_run[0] = quad_sum(l_run[0]);
   l_run[1] = quad_sum(l_run[1]);
-  {
+  if (warp < 4) {
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
     float* ow = o_sm + warp * 16 * D;
 #pragma unroll
@@ -488,7 +504,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += 128) {
+  for (int idx = threadIdx.x; warp < 4 && idx < G * D; idx += 128) {
     const int r = idx / D, d = idx % D;
     float M = -INFINITY;
 #pragma unroll
@@ -754,13 +770,13 @@ PXL_EXPORT int pxl_attn_decode(const void* q, int64_t q_stride, const void* k_ca
     if (!pxl_host::make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_cache, rows, 128, 128, page_size, 64) ||
         !pxl_host::make_tmap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v_cache, rows, 128, 128, page_size, 64))
       return PXL_ERR_TENSORMAP;
-    constexpr int SMEM = 1024 + kDecStages * 2 * TILE * 128 * 2 + 64;
+    constexpr int SMEM = 1024 + kDecStages * 2 * TILE * 128 * 2 + 128;
     static bool done = false;
     if (!done) {
       if (set_smem(attn_decode_tma_kernel, SMEM)) return PXL_ERR_CUDA;
       done = true;
     }
-    attn_decode_tma_kernel<<<grid, 128, SMEM, stream>>>(
+    attn_decode_tma_kernel<<<grid, kDecThreads, SMEM, stream>>>(
         tk, tv, static_cast<const bf16*>(q), q_stride, block_tables, ctx_lens, static_cast<bf16*>(out), workspace,
         sinks, Hq, Hkv, page_size, max_blocks, num_blocks, scale_log2, window, num_splits, status);
     if (num_splits > 1)
