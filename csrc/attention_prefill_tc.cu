@@ -1,0 +1,346 @@
+// Ragged causal prefill attention over the paged KV cache on the 5th-generation tensor cores
+// (head dim 128, page 16 / 32 / 64).
+//
+// One CTA = 128 query tokens of one (sequence, query head); it walks the keys it may see in tiles
+// of 128:
+//   warp 4   : TMA producer. Q tile once, then K and V tiles (page boxes of the cache, 128-byte
+//              swizzle) through a two-stage ring guarded by full / empty mbarriers.
+//   warp 5   : MMA issuer. S = Q K^T (tcgen05.mma 128x128x16, both operands K-major) into one of
+//              two TMEM score buffers, so the scores of tile i+1 are computed while the softmax
+//              warps work on tile i; then O_tile = P V with V taken MN-major straight from the
+//              [token, dim] layout of the cache (two 64-wide halves of the head dim).
+//   warps 0-3: softmax. Thread = query row = TMEM lane: reads its score row with tcgen05.ld,
+//              masks (causal, context end, sliding window), keeps the running max / sum, writes
+//              P as bf16 into the swizzled A-operand tile, and after the second MMA adds
+//              O_tile (TMEM) into the output row held in registers with the usual rescale.
+// Every wait is bounded; on expiry the kernel records a status code, all roles unwind, TMEM is freed.
+//
+// Reference counterpart: the MLX SDPA call with a gathered KV prefix
+// (src/parallax/server/cache/prefix_cache_utils.py:11-91, src/parallax/models/qwen3.py:84-120).
+#include "common.cuh"
+#include "pxl_api.h"
+
+namespace {
+using namespace pxl;
+
+constexpr int kQ = 128;         // query rows per CTA
+constexpr int kT = 128;         // keys per tile
+constexpr int kD = 128;         // head dim
+constexpr int kHalf = kQ * 128; // bytes of one 64-column half of a 128-row operand tile
+constexpr int kTileBytes = 2 * kHalf;
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+constexpr float kLog2eF = 1.4426950408889634f;
+
+// shared memory map (after 1024-byte alignment)
+constexpr int kOffQ = 0;
+constexpr int kOffP = kTileBytes;
+constexpr int kOffKV = 2 * kTileBytes;                       // stage s: K at +s*2*tile, V behind it
+constexpr int kOffBars = kOffKV + kStages * 2 * kTileBytes;  // 196608
+constexpr int kSmemBytes = 1024 + kOffBars + 256;
+
+// B operand stored [key rows, 64 dims] (MN-major: the dim index is contiguous), 128-byte swizzle:
+// rows of 128 B, groups of 8 key rows 1024 B apart. Only one 64-wide chunk of the MN extent is
+// addressed per instruction (N = 64), so the leading-dimension offset is not used.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+constexpr uint32_t kIdescS = umma_idesc(kQ, kT, 1, 1);
+constexpr uint32_t kIdescPV = umma_idesc(kQ, 64, 1, 1) | (1u << 16);  // B (V) is MN-major
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const int* __restrict__ block_tables,
+                       const int* __restrict__ cu_q, const int* __restrict__ ctx_lens, bf16* __restrict__ out,
+                       int64_t out_stride, const float* __restrict__ sinks, int Hq, int Hkv, int page_size,
+                       int max_blocks, int64_t num_blocks, float scale_log2, int window, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sm0 = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7 p_ready | 8 o_full
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = bar0 + 24, s_full = bar0 + 40, p_ready = bar0 + 56,
+                 o_full = bar0 + 64;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, head = blockIdx.y;
+  const int kvh = head / (Hq / Hkv);
+  const int q_begin = cu_q[b], L = cu_q[b + 1] - q_begin;
+  const int ctx = ctx_lens[b];
+  // heavy blocks (late queries see the most keys) are scheduled first
+  const int qb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  const int q0 = qb * kQ;
+  if (q0 >= L) return;  // uniform for the CTA, before any barrier or allocation
+  const int pos0 = ctx - L + q0;                        // position of query row 0
+  const int rows = L - q0 < kQ ? L - q0 : kQ;           // valid query rows
+  const int hi = pos0 + rows;                           // keys [lo, hi) are visible to some row
+  const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int t_begin = lo / kT;
+  const int n_tiles = ceil_div(hi, kT) - t_begin;
+  const int* bt = block_tables + static_cast<size_t>(b) * max_blocks;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(kv_full + 8 * s, 1);
+      mbar_init(kv_empty + 8 * s, 1);
+      mbar_init(s_full + 8 * s, 1);
+    }
+    mbar_init(p_ready, 4);  // one arrival per softmax warp
+    mbar_init(o_full, 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(tmem_slot), 512);  // S0 | S1 | O_tile (384 columns, allocated as a power of two)
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_o = tmem_base + 2 * kT;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, kTileBytes);
+      tma_load_2d(sm0 + kOffQ, &tm_q, q_full, head * kD, q_begin + q0);
+      tma_load_2d(sm0 + kOffQ + kHalf, &tm_q, q_full, head * kD + 64, q_begin + q0);
+      const int ppt = kT / page_size;
+      for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it % kStages;
+        if (it >= kStages && !mbar_wait_bounded(kv_empty + 8 * stage, ((it / kStages) - 1) & 1, abort_flag, status,
+                                                PXL_DEV_TIMEOUT_EMPTY))
+          break;
+        const uint32_t bar = kv_full + 8 * stage;
+        const uint32_t k_dst = sm0 + kOffKV + stage * 2 * kTileBytes, v_dst = k_dst + kTileBytes;
+        mbar_arrive_expect_tx(bar, 2 * kTileBytes);
+        const int t = t_begin + it;
+        for (int p = 0; p < ppt; ++p) {
+          int bi = t * ppt + p;
+          if (bi * page_size >= ctx) bi = (ctx - 1) / page_size;  // beyond the context: re-read the last page (masked)
+          int blk = bi < max_blocks ? bt[bi] : -1;
+          if (blk < 0 || blk >= num_blocks) {
+            if (status) atomicCAS(status, 0, PXL_DEV_BAD_BLOCK_PREFILL);
+            blk = 0;
+          }
+          const int row0 = (blk * Hkv + kvh) * page_size;
+          const uint32_t off = p * page_size * 128;
+          tma_load_2d(k_dst + off, &tm_k, bar, 0, row0);
+          tma_load_2d(k_dst + kHalf + off, &tm_k, bar, 64, row0);
+          tma_load_2d(v_dst + off, &tm_v, bar, 0, row0);
+          tma_load_2d(v_dst + kHalf + off, &tm_v, bar, 64, row0);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      auto issue_s = [&](int it) {  // S[it % 2] = Q K(it)^T
+        const int stage = it % kStages;
+        const uint32_t k_addr = sm0 + kOffKV + stage * 2 * kTileBytes;
+        const uint32_t d_tmem = tmem_base + (it & 1) * kT;
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * kHalf + (ks & 3) * 32;
+          tc_mma_f16(d_tmem, umma_desc_k_sw128(sm0 + kOffQ + off), umma_desc_k_sw128(k_addr + off), kIdescS,
+                     ks > 0 ? 1u : 0u);
+        }
+        tc_commit(s_full + 8 * (it & 1));
+      };
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag, status, PXL_DEV_TIMEOUT_FULL);
+      ok = ok && mbar_wait_bounded(kv_full, 0, abort_flag, status, PXL_DEV_TIMEOUT_FULL);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_s(0);
+      }
+      for (int it = 0; ok && it < n_tiles; ++it) {
+        const int stage = it % kStages;
+        if (it + 1 < n_tiles) {
+          // scores of the next tile while the softmax warps work on this one
+          ok = mbar_wait_bounded(kv_full + 8 * ((it + 1) % kStages), ((it + 1) / kStages) & 1, abort_flag, status,
+                                 PXL_DEV_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_s(it + 1);
+        }
+        ok = mbar_wait_bounded(p_ready, it & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t v_addr = sm0 + kOffKV + stage * 2 * kTileBytes + kTileBytes;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int ks = 0; ks < kT / 16; ++ks) {
+            const uint64_t da = umma_desc_k_sw128(sm0 + kOffP + (ks >> 2) * kHalf + (ks & 3) * 32);
+            const uint64_t db = umma_desc_mn_sw128(v_addr + h * kHalf + ks * 2048);
+            tc_mma_f16(tm_o + h * 64, da, db, kIdescPV, ks > 0 ? 1u : 0u);
+          }
+        }
+        tc_commit(o_full);
+        tc_commit(kv_empty + 8 * stage);  // K and V of this stage are no longer read
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps
+    const int r = warp * 32 + lane;          // query row = TMEM lane
+    const int q_pos = pos0 + r;
+    const bool row_valid = r < rows;
+    const int key_lo = (window > 0 && q_pos - window + 1 > 0) ? q_pos - window + 1 : 0;
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t p_row = sm0 + kOffP + r * 128;
+    float o[kD];
+#pragma unroll
+    for (int i = 0; i < kD; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+      ok = mbar_wait_bounded(s_full + 8 * (it & 1), (it >> 1) & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t t_s = tmem_base + (it & 1) * kT + lane_sel;
+      const int key0 = (t_begin + it) * kT;
+      // keys this row may see inside the tile: [a, e)
+      const int a = key_lo - key0, e = (row_valid ? q_pos + 1 : 0) - key0;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kT; c += 32) {
+        uint32_t s[32];
+        tmem_ld_32x32b_x32(t_s + c, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c + j >= a && c + j < e) mx = fmaxf(mx, __uint_as_float(s[j]));
+      }
+      mx *= scale_log2;  // scale > 0: the maximum of the scaled scores
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = exp2f(m_run - m_use);
+      m_run = m_new;
+      // pass 2: probabilities -> bf16 A-operand tile (K-major, 128-byte swizzle), row sum
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kT; c += 32) {
+        uint32_t s[32];
+        tmem_ld_32x32b_x32(t_s + c, s);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float p0 = (c + j >= a && c + j < e) ? exp2f(__uint_as_float(s[j]) * scale_log2 - m_use) : 0.f;
+          const float p1 = (c + j + 1 >= a && c + j + 1 < e) ? exp2f(__uint_as_float(s[j + 1]) * scale_log2 - m_use) : 0.f;
+          sum += p0 + p1;
+          pk[j >> 1] = pack_bf16x2(p0, p1);
+        }
+        const uint32_t half = p_row + (c >> 6) * kHalf;
+        const int chunk0 = (c & 63) >> 3;  // first 16-byte chunk of these 32 keys inside the 128-byte row
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half + (((chunk0 + v) ^ (r & 7)) << 4)),
+                       "r"(pk[4 * v]), "r"(pk[4 * v + 1]), "r"(pk[4 * v + 2]), "r"(pk[4 * v + 3])
+                       : "memory");
+        }
+      }
+      l_run = l_run * corr + sum;
+      tc_fence_before_sync();
+      fence_proxy_async_smem();  // P was written through the generic proxy, the MMA reads it through the async one
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+      // O += P V
+      ok = mbar_wait_bounded(o_full, it & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < kD; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tm_o + lane_sel + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * corr + __uint_as_float(v[j]);
+      }
+      tc_fence_before_sync();
+    }
+    if (ok && row_valid) {
+      float denom = l_run;
+      float f = 1.f;
+      if (sinks) {
+        const float sink = sinks[head] * kLog2eF;
+        const float M = fmaxf(m_run, sink);
+        f = exp2f(m_run - M);
+        denom = l_run * f + exp2f(sink - M);
+      }
+      const float inv = denom > 0.f ? f / denom : 0.f;
+      bf16* dst = out + static_cast<size_t>(q_begin + q0 + r) * out_stride + head * kD;
+#pragma unroll
+      for (int c = 0; c < kD; c += 8) {
+        bf16x8 ov;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ov.u[j] = pack_bf16x2(o[c + 2 * j] * inv, o[c + 2 * j + 1] * inv);
+        st_bf16x8(dst + c, ov);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);  // loads that are still in flight must land before smem is released
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+}  // namespace
+
+// Same contract as pxl_attn_prefill plus total_q = rows of q / out (sum of the new lengths): the
+// query tile is fetched with TMA boxes of 128 rows and rows past total_q must read as zeros.
+PXL_EXPORT int pxl_attn_prefill_tc(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                                   const int* block_tables, const int* cu_q, const int* ctx_lens, void* out,
+                                   int64_t out_stride, const float* sinks, int B, int max_q_len, int total_q, int Hq,
+                                   int Hkv, int D, int page_size, int max_blocks, int64_t num_blocks, float scale,
+                                   int window, int* status, cudaStream_t stream) {
+  if (B <= 0 || max_q_len <= 0 || total_q <= 0) return PXL_OK;
+  if (D != kD || Hkv <= 0 || Hq % Hkv) return PXL_ERR_INVALID_ARG;
+  if (page_size != 16 && page_size != 32 && page_size != 64) return PXL_ERR_INVALID_ARG;
+  if ((q_stride % 8) || (out_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return PXL_ERR_INVALID_ARG;
+  if (num_blocks * Hkv * page_size >= (1ll << 31) || scale <= 0.f) return PXL_ERR_INVALID_ARG;
+  CUtensorMap tq, tk, tv;
+  const uint64_t rows = static_cast<uint64_t>(num_blocks) * Hkv * page_size;
+  if (!pxl_host::make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, total_q, static_cast<uint64_t>(Hq) * kD,
+                              q_stride, kQ, 64) ||
+      !pxl_host::make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_cache, rows, 128, 128, page_size, 64) ||
+      !pxl_host::make_tmap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v_cache, rows, 128, 128, page_size, 64))
+    return PXL_ERR_TENSORMAP;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+        cudaSuccess)
+      return PXL_ERR_CUDA;
+    configured[dev] = true;
+  }
+  dim3 grid(pxl::ceil_div(max_q_len, kQ), Hq, B);
+  attn_prefill_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(
+      tq, tk, tv, block_tables, cu_q, ctx_lens, static_cast<pxl::bf16*>(out), out_stride, sinks, Hq, Hkv, page_size,
+      max_blocks, num_blocks, scale * kLog2eF, window, status);
+  return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
+}

@@ -104,6 +104,14 @@ int pxl_attn_prefill(const void* q, int64_t q_stride, const void* k_cache, const
                      int D, int page_size, int max_blocks, int64_t num_blocks, float scale,
                      int window, int* status, pxl_stream_t stream);
 
+// ---- attention_prefill_tc.cu ------------------------------------------------------
+// Same contract on the tcgen05 tensor cores (D = 128, page 16 / 32 / 64). total_q = rows of q / out.
+int pxl_attn_prefill_tc(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                        const int* block_tables, const int* cu_q, const int* ctx_lens, void* out,
+                        int64_t out_stride, const float* sinks, int B, int max_q_len, int total_q, int Hq,
+                        int Hkv, int D, int page_size, int max_blocks, int64_t num_blocks, float scale,
+                        int window, int* status, pxl_stream_t stream);
+
 // ---- sampler.cu ----------------------------------------------------------------
 // Greedy arg-max over logits [B, V] (bf16 if logits_bf16 else fp32, row stride ld).
 int pxl_argmax(const void* logits, int logits_bf16, int64_t ld, int B, int V, int* out_ids,

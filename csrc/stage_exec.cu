@@ -100,6 +100,11 @@ PXL_EXPORT int pxl_stage_forward_dense(const PxlStageDesc* st, const PxlStepDesc
   int n = 0;
   pxl::bf16* qkv = static_cast<pxl::bf16*>(ws->qkv);
   pxl::bf16* attn = static_cast<pxl::bf16*>(ws->attn);
+  // tcgen05 prefill attention where its layout rules hold, else the mma.sync kernel
+  static const bool prefill_legacy = getenv("PXL_PREFILL_LEGACY") != nullptr;
+  const bool prefill_tc = !prefill_legacy && D == 128 && (st->page == 16 || st->page == 32 || st->page == 64) &&
+                          (qkv_n % 8) == 0 && (reinterpret_cast<uintptr_t>(ws->qkv) & 15) == 0 &&
+                          st->num_blocks * Hkv * st->page < (1ll << 31);
   int splits = 0;
   if (sp->Bd > 0) {
     splits = pxl_attn_decode_splits(sp->Bd, Hkv, sp->d_max_ctx);
@@ -117,9 +122,15 @@ PXL_EXPORT int pxl_stage_forward_dense(const PxlStageDesc* st, const PxlStepDesc
                                    st->norm_offset, status, stream));
     n += 3;
     if (sp->Tp > 0) {
-      PXL_TRY(pxl_attn_prefill(qkv, qkv_n, L.k_cache, L.v_cache, sp->p_bt, sp->p_cu_q, sp->p_ctx, attn,
-                               static_cast<int64_t>(Hq) * D, L.sinks, sp->Bp, sp->p_max_q, Hq, Hkv, D, st->page,
-                               sp->p_max_blocks, st->num_blocks, st->scale, L.window, status, stream));
+      if (prefill_tc) {
+        PXL_TRY(pxl_attn_prefill_tc(qkv, qkv_n, L.k_cache, L.v_cache, sp->p_bt, sp->p_cu_q, sp->p_ctx, attn,
+                                    static_cast<int64_t>(Hq) * D, L.sinks, sp->Bp, sp->p_max_q, sp->Tp, Hq, Hkv, D,
+                                    st->page, sp->p_max_blocks, st->num_blocks, st->scale, L.window, status, stream));
+      } else {
+        PXL_TRY(pxl_attn_prefill(qkv, qkv_n, L.k_cache, L.v_cache, sp->p_bt, sp->p_cu_q, sp->p_ctx, attn,
+                                 static_cast<int64_t>(Hq) * D, L.sinks, sp->Bp, sp->p_max_q, Hq, Hkv, D, st->page,
+                                 sp->p_max_blocks, st->num_blocks, st->scale, L.window, status, stream));
+      }
       ++n;
     }
     if (sp->Bd > 0) {

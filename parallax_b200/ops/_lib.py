@@ -65,6 +65,8 @@ _SIGS = {
     "pxl_attn_decode_splits": [c_int, c_int, c_int],
     "pxl_attn_prefill": [_P, c_int64, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int,
                          c_int, c_int, c_int, c_int, c_int64, c_float, c_int, _P, _P],
+    "pxl_attn_prefill_tc": [_P, c_int64, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int, c_int,
+                            c_int, c_int, c_int, c_int, c_int64, c_float, c_int, _P, _P],
     "pxl_moe_route": [_P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P],
     "pxl_moe_align": [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, _P],
     "pxl_moe_gather": [_P, _P, _P, _P, c_int, c_int, _P],

@@ -21,6 +21,7 @@ launch_count = 0  # number of kernel-library launches issued (benchmarks report 
 
 
 _CHECK_EACH_OP = bool(os.environ.get("PXL_CHECK_EACH_OP"))
+_PREFILL_LEGACY = bool(os.environ.get("PXL_PREFILL_LEGACY"))    # mma.sync prefill attention instead of tcgen05
 
 
 def _count(n: int = 1) -> None:
@@ -325,6 +326,22 @@ def attn_prefill(
     if out is None:
         out = torch.empty((T, Hq, D), dtype=q.dtype, device=q.device)
     B = ctx_lens.numel()
+    if T == 0 or B == 0:
+        return out
+    if D == 128 and page in (16, 32, 64) and not _PREFILL_LEGACY and q.stride(0) % 8 == 0 \
+            and q.data_ptr() % 16 == 0 and out.stride(1) == D and k_cache.shape[0] * Hkv * page < (1 << 31):
+        # tcgen05 kernel: query tile, K and V pages through TMA, scores and P V on the tensor cores
+        check(
+            _lib.lib().pxl_attn_prefill_tc(
+                q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                block_tables.data_ptr(), cu_q.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(),
+                out.stride(0), _ptr(sinks), B, max_q_len, T, Hq, Hkv, D, page, block_tables.shape[1],
+                k_cache.shape[0], scale, window, status_tensor(q.device).data_ptr(),
+                _stream(q.device)),
+            "pxl_attn_prefill_tc",
+        )
+        _count()
+        return out
     check(
         _lib.lib().pxl_attn_prefill(
             q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),

@@ -253,6 +253,29 @@ def test_attn_prefill(cu, Hq, Hkv, D, page, window, use_sinks):
         assert _rel_err(y[s:e], want[s:e]) < 3e-2, f"seq {b} {seqs[b]}"
 
 
+@pytest.mark.parametrize("page,window", [(16, 0), (64, 0), (32, 300)])
+def test_attn_prefill_long(cu, page, window):
+    """Several 128-key tiles per query block, several query blocks per sequence, long cached prefixes."""
+    torch.manual_seed(7)
+    Hq, Hkv, D = 8, 2, 128
+    seqs = [(700, 0), (300, 900), (129, 127), (1024, 512)]
+    B = len(seqs)
+    ctx = [a + b for a, b in seqs]
+    kc, vc, bt = _make_paged(B, ctx, Hkv, D, page)
+    T = sum(a for a, _ in seqs)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=_dev(), dtype=torch.bfloat16)
+    q = qkv.view(T, Hq + 2 * Hkv, D)[:, :Hq]
+    cu_q = torch.tensor([0] + list(torch.tensor([a for a, _ in seqs]).cumsum(0)), dtype=torch.int32, device=_dev())
+    cl = torch.tensor(ctx, dtype=torch.int32, device=_dev())
+    scale = 1.0 / math.sqrt(D)
+    y = cu.attn_prefill(q, kc, vc, bt, cu_q, cl, max(a for a, _ in seqs), scale, window=window)
+    want = ref.attn_prefill(q, kc, vc, bt, cu_q, cl, 0, scale, window=window)
+    cu.check_status(_dev())
+    for b in range(B):
+        s, e = int(cu_q[b]), int(cu_q[b + 1])
+        assert _rel_err(y[s:e], want[s:e]) < 2e-2, f"seq {b} {seqs[b]}"
+
+
 def test_argmax_and_sample(cu):
     torch.manual_seed(7)
     B, V = 9, 151936
