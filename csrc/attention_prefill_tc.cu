@@ -3,16 +3,19 @@
 //
 // One CTA = 128 query tokens of one (sequence, query head); it walks the keys it may see in tiles
 // of 128:
-//   warp 4   : TMA producer. Q tile once, then K and V tiles (page boxes of the cache, 128-byte
+//   warp 8   : TMA producer. Q tile once, then K and V tiles (page boxes of the cache, 128-byte
 //              swizzle) through a two-stage ring guarded by full / empty mbarriers.
-//   warp 5   : MMA issuer. S = Q K^T (tcgen05.mma 128x128x16, both operands K-major) into one of
+//   warp 9   : MMA issuer. S = Q K^T (tcgen05.mma 128x128x16, both operands K-major) into one of
 //              two TMEM score buffers, so the scores of tile i+1 are computed while the softmax
 //              warps work on tile i; then O_tile = P V with V taken MN-major straight from the
 //              [token, dim] layout of the cache (two 64-wide halves of the head dim).
-//   warps 0-3: softmax. Thread = query row = TMEM lane: reads its score row with tcgen05.ld,
-//              masks (causal, context end, sliding window), keeps the running max / sum, writes
-//              P as bf16 into the swizzled A-operand tile, and after the second MMA adds
-//              O_tile (TMEM) into the output row held in registers with the usual rescale.
+//   warps 0-7: softmax. A query row is one TMEM lane; warps w and w + 4 share a lane quarter and
+//              split the columns: each thread reads 64 scores of its row with tcgen05.ld, masks
+//              (causal, context end, sliding window), the two halves exchange their row maximum
+//              through shared memory, each writes its half of P as bf16 into the swizzled
+//              A-operand tile, and after the second MMA adds its 64 columns of O_tile (TMEM) into
+//              the output half-row it keeps in registers, with the usual rescale. Two warps per
+//              scheduler instead of one hide the tcgen05.ld and exp2 latencies.
 // Every wait is bounded; on expiry the kernel records a status code, all roles unwind, TMEM is freed.
 //
 // Reference counterpart: the MLX SDPA call with a gathered KV prefix
@@ -29,7 +32,9 @@ constexpr int kD = 128;         // head dim
 constexpr int kHalf = kQ * 128; // bytes of one 64-column half of a 128-row operand tile
 constexpr int kTileBytes = 2 * kHalf;
 constexpr int kStages = 2;
-constexpr int kThreads = 192;
+constexpr int kSoftmaxWarps = 8;   // two per TMEM lane quarter: each takes one half of the columns
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 320;
 constexpr float kLog2eF = 1.4426950408889634f;
 
 // shared memory map (after 1024-byte alignment)
@@ -37,7 +42,8 @@ constexpr int kOffQ = 0;
 constexpr int kOffP = kTileBytes;
 constexpr int kOffKV = 2 * kTileBytes;                       // stage s: K at +s*2*tile, V behind it
 constexpr int kOffBars = kOffKV + kStages * 2 * kTileBytes;  // 196608
-constexpr int kSmemBytes = 1024 + kOffBars + 256;
+constexpr int kOffXchg = kOffBars + 256;                     // row max [2 tiles][2 halves][128], row sum [2][128]
+constexpr int kSmemBytes = 1024 + kOffXchg + 3 * 2 * 128 * 4;
 
 // B operand stored [key rows, 64 dims] (MN-major: the dim index is contiguous), 128-byte swizzle:
 // rows of 128 B, groups of 8 key rows 1024 B apart. Only one 64-wide chunk of the MN extent is
@@ -50,6 +56,11 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t addr) {
   d |= static_cast<uint64_t>(1) << 46;
   d |= static_cast<uint64_t>(2) << 61;
   return d;
+}
+__device__ __forceinline__ float fast_exp2(float x) {  // 2^x, -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 constexpr uint32_t kIdescS = umma_idesc(kQ, kT, 1, 1);
 constexpr uint32_t kIdescPV = umma_idesc(kQ, 64, 1, 1) | (1u << 16);  // B (V) is MN-major
@@ -96,7 +107,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(kv_empty + 8 * s, 1);
       mbar_init(s_full + 8 * s, 1);
     }
-    mbar_init(p_ready, 4);  // one arrival per softmax warp
+    mbar_init(p_ready, kSoftmaxWarps);  // one arrival per softmax warp
     mbar_init(o_full, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -104,7 +115,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(tmem_slot), 512);  // S0 | S1 | O_tile (384 columns, allocated as a power of two)
     tmem_relinquish();
   }
@@ -114,40 +125,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_o = tmem_base + 2 * kT;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
+    // The whole warp works: lane p looks up the block of page p of the tile and issues that page's
+    // four box loads, so the block-table reads of a tile are in flight together (one lane doing them
+    // one after the other cost more than the tile's math) and are issued before the wait for the stage.
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, kTileBytes);
       tma_load_2d(sm0 + kOffQ, &tm_q, q_full, head * kD, q_begin + q0);
       tma_load_2d(sm0 + kOffQ + kHalf, &tm_q, q_full, head * kD + 64, q_begin + q0);
-      const int ppt = kT / page_size;
-      for (int it = 0; it < n_tiles; ++it) {
-        const int stage = it % kStages;
-        if (it >= kStages && !mbar_wait_bounded(kv_empty + 8 * stage, ((it / kStages) - 1) & 1, abort_flag, status,
-                                                PXL_DEV_TIMEOUT_EMPTY))
-          break;
-        const uint32_t bar = kv_full + 8 * stage;
-        const uint32_t k_dst = sm0 + kOffKV + stage * 2 * kTileBytes, v_dst = k_dst + kTileBytes;
-        mbar_arrive_expect_tx(bar, 2 * kTileBytes);
-        const int t = t_begin + it;
-        for (int p = 0; p < ppt; ++p) {
-          int bi = t * ppt + p;
-          if (bi * page_size >= ctx) bi = (ctx - 1) / page_size;  // beyond the context: re-read the last page (masked)
-          int blk = bi < max_blocks ? bt[bi] : -1;
-          if (blk < 0 || blk >= num_blocks) {
-            if (status) atomicCAS(status, 0, PXL_DEV_BAD_BLOCK_PREFILL);
-            blk = 0;
-          }
-          const int row0 = (blk * Hkv + kvh) * page_size;
-          const uint32_t off = p * page_size * 128;
-          tma_load_2d(k_dst + off, &tm_k, bar, 0, row0);
-          tma_load_2d(k_dst + kHalf + off, &tm_k, bar, 64, row0);
-          tma_load_2d(v_dst + off, &tm_v, bar, 0, row0);
-          tma_load_2d(v_dst + kHalf + off, &tm_v, bar, 64, row0);
+    }
+    const int ppt = kT / page_size;
+    for (int it = 0; it < n_tiles; ++it) {
+      const int stage = it % kStages;
+      int blk = 0;
+      if (lane < ppt) {
+        int bi = (t_begin + it) * ppt + lane;
+        if (bi * page_size >= ctx) bi = (ctx - 1) / page_size;  // beyond the context: re-read the last page (masked)
+        blk = bi < max_blocks ? bt[bi] : -1;
+        if (blk < 0 || blk >= num_blocks) {
+          if (status) atomicCAS(status, 0, PXL_DEV_BAD_BLOCK_PREFILL);
+          blk = 0;
         }
       }
+      int okf = 1;
+      if (it >= kStages && lane == 0)
+        okf = mbar_wait_bounded(kv_empty + 8 * stage, ((it / kStages) - 1) & 1, abort_flag, status,
+                                PXL_DEV_TIMEOUT_EMPTY) ? 1 : 0;
+      okf = __shfl_sync(0xffffffffu, okf, 0);
+      if (!okf) break;
+      const uint32_t bar = kv_full + 8 * stage;
+      const uint32_t k_dst = sm0 + kOffKV + stage * 2 * kTileBytes, v_dst = k_dst + kTileBytes;
+      if (lane == 0) mbar_arrive_expect_tx(bar, 2 * kTileBytes);
+      __syncwarp();
+      if (lane < ppt) {
+        const int row0 = (blk * Hkv + kvh) * page_size;
+        const uint32_t off = lane * page_size * 128;
+        tma_load_2d(k_dst + off, &tm_k, bar, 0, row0);
+        tma_load_2d(k_dst + kHalf + off, &tm_k, bar, 64, row0);
+        tma_load_2d(v_dst + off, &tm_v, bar, 0, row0);
+        tma_load_2d(v_dst + kHalf + off, &tm_v, bar, 64, row0);
+      }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       auto issue_s = [&](int it) {  // S[it % 2] = Q K(it)^T
@@ -197,99 +217,129 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
   } else {
     // ------------------------------------------------------------------ softmax warps
-    const int r = warp * 32 + lane;          // query row = TMEM lane
+    const int q4 = warp & 3, hc = warp >> 2;  // TMEM lane quarter, column half
+    const int r = q4 * 32 + lane;             // query row = TMEM lane
     const int q_pos = pos0 + r;
     const bool row_valid = r < rows;
     const int key_lo = (window > 0 && q_pos - window + 1 > 0) ? q_pos - window + 1 : 0;
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t p_row = sm0 + kOffP + r * 128;
-    float o[kD];
+    const uint32_t lane_sel = static_cast<uint32_t>(q4 * 32) << 16;
+    const uint32_t p_row = sm0 + kOffP + hc * kHalf + r * 128;  // this thread's 64 keys = one swizzled 128-byte row
+    float* mx_sm = reinterpret_cast<float*>(smem + kOffXchg);    // [tile parity][half][row]
+    float* l_sm = mx_sm + 2 * 2 * 128;                           // [half][row]
+    float o[64];
 #pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
-    bool ok = true;
+    // 1 after a wait ran out; agreed among the 256 softmax threads at the barrier of every tile, so
+    // that they all leave the loop at the same place
+    int failed = 0;
+    auto agree = [&](int f) {
+      int r_out;
+      asm volatile(
+          "{\n\t"
+          ".reg .pred pin, pout;\n\t"
+          "setp.ne.b32 pin, %1, 0;\n\t"
+          "bar.red.or.pred pout, 1, 256, pin;\n\t"
+          "selp.b32 %0, 1, 0, pout;\n\t"
+          "}\n"
+          : "=r"(r_out)
+          : "r"(f)
+          : "memory");
+      return r_out;
+    };
     for (int it = 0; it < n_tiles; ++it) {
-      ok = mbar_wait_bounded(s_full + 8 * (it & 1), (it >> 1) & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t t_s = tmem_base + (it & 1) * kT + lane_sel;
-      const int key0 = (t_begin + it) * kT;
-      // keys this row may see inside the tile: [a, e)
-      const int a = key_lo - key0, e = (row_valid ? q_pos + 1 : 0) - key0;
-      // pass 1: row maximum
+      if (!failed)
+        failed = mbar_wait_bounded(s_full + 8 * (it & 1), (it >> 1) & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL) ? 0 : 1;
+      const uint32_t t_s = tmem_base + (it & 1) * kT + hc * 64 + lane_sel;
+      const int tile_key0 = (t_begin + it) * kT;
+      // interior tile: every key is visible to every row of the block, no masking needed
+      const bool interior = tile_key0 + kT - 1 <= pos0 && (window <= 0 || tile_key0 >= pos0 + kQ - window);
+      // this thread's 64 scores stay in registers between the maximum and the exponentials
+      uint32_t sc[64];
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kT; c += 32) {
-        uint32_t s[32];
-        tmem_ld_32x32b_x32(t_s + c, s);
+      if (!failed) {
+        tc_fence_after_sync();
+        tmem_ld_32x32b_x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&sc[0]));
+        tmem_ld_32x32b_x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sc[32]));
         tmem_ld_wait();
+        if (!interior) {
+          // keys this thread's row may see among its 64 columns: [a, e)
+          const int key0 = tile_key0 + hc * 64;
+          const int a = key_lo - key0, e = (row_valid ? q_pos + 1 : 0) - key0;
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c + j >= a && c + j < e) mx = fmaxf(mx, __uint_as_float(s[j]));
+          for (int j = 0; j < 64; ++j)
+            if (j < a || j >= e) sc[j] = 0xff800000u;  // -inf
+        }
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 64; j += 4) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) m4[k] = fmaxf(m4[k], __uint_as_float(sc[j + k]));
+        }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
-      mx *= scale_log2;  // scale > 0: the maximum of the scaled scores
+      mx_sm[((it & 1) * 2 + hc) * 128 + r] = mx;
+      failed = agree(failed);
+      if (failed) break;
+      mx = fmaxf(mx, mx_sm[((it & 1) * 2 + (hc ^ 1)) * 128 + r]) * scale_log2;  // scale > 0
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = exp2f(m_run - m_use);
+      const float corr = fast_exp2(m_run - m_use);
       m_run = m_new;
-      // pass 2: probabilities -> bf16 A-operand tile (K-major, 128-byte swizzle), row sum
-      float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kT; c += 32) {
-        uint32_t s[32];
-        tmem_ld_32x32b_x32(t_s + c, s);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      // probabilities -> bf16 A-operand tile (K-major, 128-byte swizzle), partial row sum
+      float sum2[2] = {0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float p0 = (c + j >= a && c + j < e) ? exp2f(__uint_as_float(s[j]) * scale_log2 - m_use) : 0.f;
-          const float p1 = (c + j + 1 >= a && c + j + 1 < e) ? exp2f(__uint_as_float(s[j + 1]) * scale_log2 - m_use) : 0.f;
-          sum += p0 + p1;
+      for (int c = 0; c < 64; c += 8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sc[c + j]), scale_log2, -m_use));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sc[c + j + 1]), scale_log2, -m_use));
+          sum2[0] += p0;
+          sum2[1] += p1;
           pk[j >> 1] = pack_bf16x2(p0, p1);
         }
-        const uint32_t half = p_row + (c >> 6) * kHalf;
-        const int chunk0 = (c & 63) >> 3;  // first 16-byte chunk of these 32 keys inside the 128-byte row
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half + (((chunk0 + v) ^ (r & 7)) << 4)),
-                       "r"(pk[4 * v]), "r"(pk[4 * v + 1]), "r"(pk[4 * v + 2]), "r"(pk[4 * v + 3])
-                       : "memory");
-        }
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((c >> 3) ^ (r & 7)) << 4)), "r"(pk[0]),
+                     "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                     : "memory");
       }
+      const float sum = sum2[0] + sum2[1];
       l_run = l_run * corr + sum;
       tc_fence_before_sync();
       fence_proxy_async_smem();  // P was written through the generic proxy, the MMA reads it through the async one
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
-      // O += P V
-      ok = mbar_wait_bounded(o_full, it & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
+      // O += P V: this thread's 64 columns of the output row
+      failed = mbar_wait_bounded(o_full, it & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL) ? 0 : 1;
+      if (!failed) {
+        tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < kD; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tm_o + lane_sel + c, v);
-        tmem_ld_wait();
+        for (int c = 0; c < 64; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tm_o + lane_sel + hc * 64 + c, v);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * corr + __uint_as_float(v[j]);
+          for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * corr + __uint_as_float(v[j]);
+        }
+        tc_fence_before_sync();
       }
-      tc_fence_before_sync();
     }
-    if (ok && row_valid) {
-      float denom = l_run;
+    // the two halves of a row saw the same maxima, so their partial sums just add up
+    l_sm[hc * 128 + r] = l_run;
+    failed = agree(failed);
+    if (!failed && row_valid) {
+      float denom = l_run + l_sm[(hc ^ 1) * 128 + r];
       float f = 1.f;
       if (sinks) {
         const float sink = sinks[head] * kLog2eF;
         const float M = fmaxf(m_run, sink);
         f = exp2f(m_run - M);
-        denom = l_run * f + exp2f(sink - M);
+        denom = denom * f + exp2f(sink - M);
       }
       const float inv = denom > 0.f ? f / denom : 0.f;
-      bf16* dst = out + static_cast<size_t>(q_begin + q0 + r) * out_stride + head * kD;
+      bf16* dst = out + static_cast<size_t>(q_begin + q0 + r) * out_stride + head * kD + hc * 64;
 #pragma unroll
-      for (int c = 0; c < kD; c += 8) {
+      for (int c = 0; c < 64; c += 8) {
         bf16x8 ov;
 #pragma unroll
         for (int j = 0; j < 4; ++j) ov.u[j] = pack_bf16x2(o[c + 2 * j] * inv, o[c + 2 * j + 1] * inv);
@@ -304,7 +354,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 5) tmem_dealloc(tmem_base, 512);
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, 512);
 }
 
 }  // namespace
