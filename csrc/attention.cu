@@ -353,42 +353,45 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
   }
   __syncthreads();
 
-  auto issue = [&](int t, int stage) {
-    const uint32_t bar = full0 + 8 * stage;
-    const uint32_t k_dst = stage0 + stage * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
-    mbar_arrive_expect_tx(bar, 2 * TILE_BYTES);
-    for (int p = 0; p < ppt; ++p) {
-      int bi = t * ppt + p;
-      if (bi * page_size >= hi) bi = (hi - 1) / page_size;  // beyond the context: re-read the last page (masked)
-      int blk = bi < max_blocks ? bt[bi] : -1;
-      if (blk < 0 || blk >= num_blocks) {
-        if (status) atomicCAS(status, 0, PXL_DEV_BAD_BLOCK_DECODE);
-        blk = 0;
-      }
-      const int row0 = (blk * Hkv + kvh) * page_size;
-      const uint32_t off = p * page_size * 128;
-      tma_load_2d(k_dst + off, &tm_k, bar, 0, row0);
-      tma_load_2d(k_dst + TILE * 128 + off, &tm_k, bar, 64, row0);
-      tma_load_2d(v_dst + off, &tm_v, bar, 0, row0);
-      tma_load_2d(v_dst + TILE * 128 + off, &tm_v, bar, 64, row0);
-    }
-  };
   int failed = 0;
   if (warp == 4) {
-    // ---- producer warp: one lane runs up to kDecStages tiles ahead of the consumers
-    if (lane == 0) {
-      for (int it = 0; it < n_tiles; ++it) {
-        const int stage = it % kDecStages;
-        if (it >= kDecStages &&
-            !mbar_wait_bounded(empty0 + 8 * stage, ((it / kDecStages) - 1) & 1, abort_flag, status,
-                               PXL_DEV_TIMEOUT_EMPTY)) {
-          failed = 1;
-          break;
+    // ---- producer warp, up to kDecStages tiles ahead of the consumers. Lane p looks up the block of
+    // page p of the tile and issues that page's four box loads: the block-table reads of a tile are in
+    // flight together and are issued before the wait for the stage.
+    for (int it = 0; it < n_tiles; ++it) {
+      const int stage = it % kDecStages;
+      int blk = 0;
+      if (lane < ppt) {
+        int bi = (t_begin + it) * ppt + lane;
+        if (bi * page_size >= hi) bi = (hi - 1) / page_size;  // beyond the context: re-read the last page (masked)
+        blk = bi < max_blocks ? bt[bi] : -1;
+        if (blk < 0 || blk >= num_blocks) {
+          if (status) atomicCAS(status, 0, PXL_DEV_BAD_BLOCK_DECODE);
+          blk = 0;
         }
-        issue(t_begin + it, stage);
+      }
+      int okf = 1;
+      if (it >= kDecStages && lane == 0)
+        okf = mbar_wait_bounded(empty0 + 8 * stage, ((it / kDecStages) - 1) & 1, abort_flag, status,
+                                PXL_DEV_TIMEOUT_EMPTY) ? 1 : 0;
+      okf = __shfl_sync(0xffffffffu, okf, 0);
+      if (!okf) {
+        failed = 1;
+        break;
+      }
+      const uint32_t bar = full0 + 8 * stage;
+      const uint32_t k_dst = stage0 + stage * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
+      if (lane == 0) mbar_arrive_expect_tx(bar, 2 * TILE_BYTES);
+      __syncwarp();
+      if (lane < ppt) {
+        const int row0 = (blk * Hkv + kvh) * page_size;
+        const uint32_t off = lane * page_size * 128;
+        tma_load_2d(k_dst + off, &tm_k, bar, 0, row0);
+        tma_load_2d(k_dst + TILE * 128 + off, &tm_k, bar, 64, row0);
+        tma_load_2d(v_dst + off, &tm_v, bar, 0, row0);
+        tma_load_2d(v_dst + TILE * 128 + off, &tm_v, bar, 64, row0);
       }
     }
-    __syncwarp();
   }
 
   uint32_t qf[D / 16][4];
