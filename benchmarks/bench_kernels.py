@@ -183,6 +183,30 @@ def bench_norm(rows):
     rows.append({"kernel": "rmsnorm", "T": T, "H": H, "ms": round(ms, 4), "gbs": round(byts / ms / 1e6, 1),
                  "roofline_frac": round(byts / (hbm * 1e9) * 1e3 / ms, 3), "tag": tag})
     print(rows[-1], flush=True)
+    # engine-sized launches (one step of the headline workload has about 2500 rows)
+    T = 2560
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(x)
+    ms = time_fn(lambda: cu.rmsnorm(x, w, 1e-6, out=out))
+    byts = 2.0 * T * H * 2
+    rows.append({"kernel": "rmsnorm", "T": T, "H": H, "ms": round(ms, 4), "gbs": round(byts / ms / 1e6, 1),
+                 "roofline_frac": round(byts / (hbm * 1e9) * 1e3 / ms, 3), "tag": tag})
+    print(rows[-1], flush=True)
+    Hq, Hkv, D, page = 32, 8, 128, 16
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    qn = torch.randn(D, device="cuda", dtype=torch.bfloat16)
+    kn = torch.randn(D, device="cuda", dtype=torch.bfloat16)
+    cs = ref.build_cos_sin(4096, D, 1e6, device="cuda")
+    pos = torch.randint(0, 4096, (T,), device="cuda", dtype=torch.int32)
+    blocks = 4096
+    slots = torch.randperm(blocks * page, device="cuda")[:T].to(torch.int64)
+    kc = torch.zeros(blocks, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    ms = time_fn(lambda: cu.qk_norm_rope_cache(qkv, qn, kn, cs, pos, slots, kc, vc, Hq, Hkv, D, D))
+    byts = 2.0 * T * D * ((Hq + Hkv) * 2 + Hkv + 2 * Hkv)   # q, k read + written, v read, k and v cache writes
+    rows.append({"kernel": "qk_norm_rope_cache", "T": T, "ms": round(ms, 4), "gbs": round(byts / ms / 1e6, 1),
+                 "roofline_frac": round(byts / (hbm * 1e9) * 1e3 / ms, 3), "tag": tag})
+    print(rows[-1], flush=True)
     logits = torch.randn(512, 151936, device="cuda").to(torch.bfloat16)
     ms = time_fn(lambda: cu.argmax(logits))
     byts = logits.numel() * 2.0

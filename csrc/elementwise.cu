@@ -58,6 +58,72 @@ rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __r
   }
 }
 
+// One warp per row, the row held in registers between the sum of squares and the scaling: one read
+// and one write of every element, no block-wide barrier. NV = 16-byte vectors per lane (H <= NV * 256).
+template <bool HAS_RES, int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ out,
+                    bf16* __restrict__ residual, int T, int H, float eps, float w_offset) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const bf16* xr = x + static_cast<size_t>(row) * H;
+  bf16* rr = HAS_RES ? residual + static_cast<size_t>(row) * H : nullptr;
+  bf16* outr = out + static_cast<size_t>(row) * H;
+  const int nvec = H >> 3;
+  bf16x8 a[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) a[i] = ld_bf16x8(xr + v * 8);
+  }
+  if constexpr (HAS_RES) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        const bf16x8 b = ld_bf16x8(rr + v * 8);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fa = unpack_bf16x2(a[i].u[j]);
+          const float2 fb = unpack_bf16x2(b.u[j]);
+          a[i].u[j] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+        }
+        st_bf16x8(rr + v * 8, a[i]);  // the sum (rounded to bf16) is the new residual stream
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + 32 * i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(a[i].u[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = rsqrtf(ss / static_cast<float>(H) + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      const bf16x8 ww = ld_bf16x8(w + v * 8);
+      bf16x8 o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(a[i].u[j]);
+        const float2 g = unpack_bf16x2(ww.u[j]);
+        o.u[j] = pack_bf16x2(f.x * inv * (g.x + w_offset), f.y * inv * (g.y + w_offset));
+      }
+      st_bf16x8(outr + v * 8, o);
+    }
+  }
+}
+
 // Row-strided variant (rows of a column slice of a wider matrix; in place when out == x).
 __global__ void __launch_bounds__(256)
 rmsnorm_strided_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restrict__ w, bf16* __restrict__ out,
@@ -278,16 +344,30 @@ PXL_EXPORT int pxl_rmsnorm(const void* x, const void* weight, void* out, void* r
                            int H, float eps, float w_offset, pxl_stream_t stream) {
   if (T <= 0) return PXL_OK;
   if (H % 8) return PXL_ERR_INVALID_ARG;
+  const bf16* xp = static_cast<const bf16*>(x);
+  const bf16* wp = static_cast<const bf16*>(weight);
+  bf16* op = static_cast<bf16*>(out);
+  bf16* rp = static_cast<bf16*>(residual);
+  if (H <= 8192 && T >= 64) {
+    // many rows: one warp per row with the row in registers
+    const unsigned grid = static_cast<unsigned>((T + 7) / 8);
+#define PXL_RMS_WARP(NV)                                                                          \
+  do {                                                                                            \
+    if (residual)                                                                                 \
+      rmsnorm_warp_kernel<true, NV><<<grid, 256, 0, stream>>>(xp, wp, op, rp, T, H, eps, w_offset); \
+    else                                                                                          \
+      rmsnorm_warp_kernel<false, NV><<<grid, 256, 0, stream>>>(xp, wp, op, rp, T, H, eps, w_offset); \
+  } while (0)
+    if (H <= 2048) PXL_RMS_WARP(8);
+    else if (H <= 4096) PXL_RMS_WARP(16);
+    else PXL_RMS_WARP(32);
+#undef PXL_RMS_WARP
+    return check_launch();
+  }
   if (residual)
-    rmsnorm_kernel<true><<<T, 256, 0, stream>>>(static_cast<const bf16*>(x),
-                                                static_cast<const bf16*>(weight),
-                                                static_cast<bf16*>(out),
-                                                static_cast<bf16*>(residual), H, eps, w_offset);
+    rmsnorm_kernel<true><<<T, 256, 0, stream>>>(xp, wp, op, rp, H, eps, w_offset);
   else
-    rmsnorm_kernel<false><<<T, 256, 0, stream>>>(static_cast<const bf16*>(x),
-                                                 static_cast<const bf16*>(weight),
-                                                 static_cast<bf16*>(out), nullptr, H, eps,
-                                                 w_offset);
+    rmsnorm_kernel<false><<<T, 256, 0, stream>>>(xp, wp, op, nullptr, H, eps, w_offset);
   return check_launch();
 }
 
