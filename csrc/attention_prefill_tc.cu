@@ -7,15 +7,16 @@
 //              swizzle) through a two-stage ring guarded by full / empty mbarriers.
 //   warp 9   : MMA issuer. S = Q K^T (tcgen05.mma 128x128x16, both operands K-major) into one of
 //              two TMEM score buffers, so the scores of tile i+1 are computed while the softmax
-//              warps work on tile i; then O_tile = P V with V taken MN-major straight from the
+//              warps work on tile i; then O += P V with V taken MN-major straight from the
 //              [token, dim] layout of the cache (two 64-wide halves of the head dim).
 //   warps 0-7: softmax. A query row is one TMEM lane; warps w and w + 4 share a lane quarter and
 //              split the columns: each thread reads 64 scores of its row with tcgen05.ld, masks
 //              (causal, context end, sliding window), the two halves exchange their row maximum
 //              through shared memory, each writes its half of P as bf16 into the swizzled
-//              A-operand tile, and after the second MMA adds its 64 columns of O_tile (TMEM) into
-//              the output half-row it keeps in registers, with the usual rescale. Two warps per
-//              scheduler instead of one hide the tcgen05.ld and exp2 latencies.
+//              A-operand tile. The output accumulates in TMEM over all tiles (the second MMA
+//              adds to it) relative to a reference maximum that only moves, with a rescale of the
+//              TMEM rows by tcgen05.ld / st, when a row maximum grew by more than 2^8; so the
+//              softmax of tile i+1 does not wait for the P V product of tile i.
 // Every wait is bounded; on expiry the kernel records a status code, all roles unwind, TMEM is freed.
 //
 // Reference counterpart: the MLX SDPA call with a gathered KV prefix
@@ -116,7 +117,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     tma_prefetch_desc(&tm_v);
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(tmem_slot), 512);  // S0 | S1 | O_tile (384 columns, allocated as a power of two)
+    tmem_alloc(smem_u32(tmem_slot), 512);  // S0 | S1 | O (384 columns, allocated as a power of two)
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -208,7 +209,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           for (int ks = 0; ks < kT / 16; ++ks) {
             const uint64_t da = umma_desc_k_sw128(sm0 + kOffP + (ks >> 2) * kHalf + (ks & 3) * 32);
             const uint64_t db = umma_desc_mn_sw128(v_addr + h * kHalf + ks * 2048);
-            tc_mma_f16(tm_o + h * 64, da, db, kIdescPV, ks > 0 ? 1u : 0u);
+            tc_mma_f16(tm_o + h * 64, da, db, kIdescPV, (it > 0 || ks > 0) ? 1u : 0u);  // O stays in TMEM
           }
         }
         tc_commit(o_full);
@@ -226,9 +227,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const uint32_t p_row = sm0 + kOffP + hc * kHalf + r * 128;  // this thread's 64 keys = one swizzled 128-byte row
     float* mx_sm = reinterpret_cast<float*>(smem + kOffXchg);    // [tile parity][half][row]
     float* l_sm = mx_sm + 2 * 2 * 128;                           // [half][row]
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     // 1 after a wait ran out; agreed among the 256 softmax threads at the barrier of every tile, so
     // that they all leave the loop at the same place
@@ -250,6 +248,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     for (int it = 0; it < n_tiles; ++it) {
       if (!failed)
         failed = mbar_wait_bounded(s_full + 8 * (it & 1), (it >> 1) & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL) ? 0 : 1;
+      failed = __any_sync(0xffffffffu, failed);  // warp-uniform: the TMEM loads below are warp-wide
       const uint32_t t_s = tmem_base + (it & 1) * kT + hc * 64 + lane_sel;
       const int tile_key0 = (t_begin + it) * kT;
       // interior tile: every key is visible to every row of the block, no masking needed
@@ -283,9 +282,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (failed) break;
       mx = fmaxf(mx, mx_sm[((it & 1) * 2 + (hc ^ 1)) * 128 + r]) * scale_log2;  // scale > 0
       const float m_new = fmaxf(m_run, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = fast_exp2(m_run - m_use);
-      m_run = m_new;
+      // The output accumulates in TMEM across tiles, relative to the reference maximum m_run. The
+      // reference only moves (and O is rescaled) when some row of this lane quarter grew by more
+      // than 2^8: until then the stale reference keeps every probability below 256, which bf16 and
+      // the fp32 sums hold without trouble. Both warps of a lane quarter see the same 32 rows and
+      // the same maxima, so they take the same decision.
+      const bool grow = __any_sync(0xffffffffu, m_new > m_run + 8.f);
+      // P of the previous tile must have been consumed (and O be complete) before either is touched
+      if (it > 0) failed = mbar_wait_bounded(o_full, (it - 1) & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL) ? 0 : 1;
+      failed = __any_sync(0xffffffffu, failed);
+      if (it == 0) {
+        m_run = m_new;
+      } else if (grow && !failed) {
+        const float corr = fast_exp2(m_run - (m_new == -INFINITY ? 0.f : m_new));
+        m_run = m_new;
+        l_run *= corr;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < 64; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tm_o + lane_sel + hc * 64 + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+          tmem_st_32x32b_x32(tm_o + lane_sel + hc * 64 + c, v);
+        }
+        tmem_st_wait();
+      }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
       // probabilities -> bf16 A-operand tile (K-major, 128-byte swizzle), partial row sum
       float sum2[2] = {0.f, 0.f};
 #pragma unroll
@@ -303,31 +327,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                      "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                      : "memory");
       }
-      const float sum = sum2[0] + sum2[1];
-      l_run = l_run * corr + sum;
+      l_run += sum2[0] + sum2[1];
       tc_fence_before_sync();
       fence_proxy_async_smem();  // P was written through the generic proxy, the MMA reads it through the async one
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
-      // O += P V: this thread's 64 columns of the output row
-      failed = mbar_wait_bounded(o_full, it & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL) ? 0 : 1;
-      if (!failed) {
-        tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < 64; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tm_o + lane_sel + hc * 64 + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[c + j] = o[c + j] * corr + __uint_as_float(v[j]);
-        }
-        tc_fence_before_sync();
-      }
     }
+    // the last P V
+    if (!failed && n_tiles > 0)
+      failed = mbar_wait_bounded(o_full, (n_tiles - 1) & 1, abort_flag, status, PXL_DEV_TIMEOUT_TMEM_FULL) ? 0 : 1;
+    failed = __any_sync(0xffffffffu, failed);
     // the two halves of a row saw the same maxima, so their partial sums just add up
     l_sm[hc * 128 + r] = l_run;
     failed = agree(failed);
-    if (!failed && row_valid) {
+    if (!failed) {  // the same for all softmax threads: the TMEM loads below are warp-wide
       float denom = l_run + l_sm[(hc ^ 1) * 128 + r];
       float f = 1.f;
       if (sinks) {
@@ -338,13 +351,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       }
       const float inv = denom > 0.f ? f / denom : 0.f;
       bf16* dst = out + static_cast<size_t>(q_begin + q0 + r) * out_stride + head * kD + hc * 64;
+      tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-        bf16x8 ov;
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tm_o + lane_sel + hc * 64 + c, v);
+        tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 4; ++j) ov.u[j] = pack_bf16x2(o[c + 2 * j] * inv, o[c + 2 * j + 1] * inv);
-        st_bf16x8(dst + c, ov);
+        for (int c8 = 0; c8 < 32; c8 += 8) {
+          bf16x8 ov;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            ov.u[j] = pack_bf16x2(__uint_as_float(v[c8 + 2 * j]) * inv, __uint_as_float(v[c8 + 2 * j + 1]) * inv);
+          if (row_valid) st_bf16x8(dst + c + c8, ov);
+        }
       }
+      tc_fence_before_sync();
     }
   }
 
