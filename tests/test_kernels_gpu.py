@@ -132,6 +132,21 @@ def test_rmsnorm(cu):
     assert _rel_err(r1, r2) < 1e-3
 
 
+@pytest.mark.parametrize("T,H", [(200, 4096), (64, 1024), (333, 5120), (70, 2048)])
+def test_rmsnorm_many_rows(cu, T, H):
+    """From 64 rows on a warp normalises a whole row held in registers (8 / 16 / 32 vectors per lane)."""
+    torch.manual_seed(12)
+    x = torch.randn(T, H, device=_dev(), dtype=torch.bfloat16)
+    w = torch.randn(H, device=_dev(), dtype=torch.bfloat16)
+    assert _rel_err(cu.rmsnorm(x, w, 1e-6), ref.rmsnorm(x, w, 1e-6)) < 5e-3
+    r1 = torch.randn_like(x)
+    r2 = r1.clone()
+    y = cu.rmsnorm(x, w, 1e-5, residual=r1, w_offset=1.0)
+    want = ref.rmsnorm(x, w, 1e-5, residual=r2, w_offset=1.0)
+    assert _rel_err(y, want) < 5e-3
+    assert _rel_err(r1, r2) < 1e-3
+
+
 @pytest.mark.parametrize("D,rot", [(128, 128), (64, 64), (128, 64)])
 def test_qk_norm_rope_cache(cu, D, rot):
     torch.manual_seed(3)
