@@ -257,6 +257,12 @@ class CacheManager:
         if st is not None and st.tokens is not None:
             st.tokens.extend(int(t) for t in new_token_ids)
 
+    def append_request_token(self, rid: str, token_id: int) -> None:
+        """One generated token (the per-step case of :meth:`update_request_tokens`)."""
+        st = self.reqs.get(rid)
+        if st is not None and st.tokens is not None:
+            st.tokens.append(token_id)
+
     def insert_full_blocks_to_cache(self, rid: str, num_computed_tokens: Optional[int] = None,
                                     snapshot_linear=None) -> int:
         """Publish every full block whose KV is computed. Returns number of new nodes.

@@ -113,19 +113,22 @@ class Planner:
                 logit_rows.append(o + n - 1)
                 owners.append(s)
             o += n
-        d_rows = np.empty(len(decode), dtype=np.int32)
-        d_ctx = np.empty(len(decode), dtype=np.int32)
-        for i, s in enumerate(decode):
-            r = s.req
-            ids[o] = r.output_ids[-1]
-            pos[o] = r.total_length - 1
-            row = cache.get_row(r.request_id)
-            rows_of_tok[o] = row
-            d_rows[i] = row
-            d_ctx[i] = r.total_length
-            logit_rows.append(o)
-            owners.append(s)
-            o += 1
+        # decode rows: one Python pass collecting plain lists, then whole-array numpy stores (a numpy
+        # scalar store per field and request costs several times more with hundreds of requests)
+        nd = len(decode)
+        if nd:
+            reqs_d = [s.req for s in decode]
+            d_ctx = np.fromiter((r.prompt_len + len(r.output_ids) for r in reqs_d), dtype=np.int32, count=nd)
+            d_rows = np.fromiter((cache.get_row(r.request_id) for r in reqs_d), dtype=np.int32, count=nd)
+            ids[o:o + nd] = np.fromiter((r.output_ids[-1] for r in reqs_d), dtype=np.int32, count=nd)
+            pos[o:o + nd] = d_ctx - 1
+            rows_of_tok[o:o + nd] = d_rows
+            logit_rows.extend(range(o, o + nd))
+            owners.extend(decode)
+            o += nd
+        else:
+            d_rows = np.empty(0, dtype=np.int32)
+            d_ctx = np.empty(0, dtype=np.int32)
         slots = cache.tables[rows_of_tok, pos // bs].astype(np.int64) * bs + (pos % bs)
         maxb_p = (max(p_ctx) + bs - 1) // bs if prefill else 0
         maxb_d = (int(d_ctx.max()) + bs - 1) // bs if len(decode) else 0
@@ -325,22 +328,24 @@ class Engine:
                 tr.device_span(self.total_steps, events[0], events[1], t0, tokens=fb.num_tokens)
         # ---- commit
         owner_idx = {id(s): i for i, s in enumerate(owners)}
+        now = time.time()
+        cache = self.cache
         for s in arrays["ordered"]:
             req = s.req
             if s.is_prefill:
                 req.num_computed_tokens = s.start + s.num_tokens
-                self.cache.insert_full_blocks_to_cache(req.request_id, req.num_computed_tokens)
+                cache.insert_full_blocks_to_cache(req.request_id, req.num_computed_tokens)
             tok = None
             i = owner_idx.get(id(s))
             if i is not None:
                 tok = int(token_list[i])
-                req.commit_new_token(tok, prob_list[i] if prob_list else None)
-                self.cache.update_request_tokens(req.request_id, [tok])
+                req.commit_new_token(tok, prob_list[i] if prob_list else None, now=now)
+                cache.append_request_token(req.request_id, tok)
             if sched.check_and_update_request_status(req):
                 self._release(req)
                 out.append((req, tok))
             else:
-                sched.enque_request(req)
+                sched.enque_request(req, now=now)
                 if tok is not None:
                     out.append((req, tok))
         if tr is not None:

@@ -182,18 +182,21 @@ class Request:
         if status in _FINISHED and self.finish_time is None:
             self.finish_time = time.time()
 
-    def commit_new_token(self, token_id: int, prob: Optional[float] = None) -> None:
-        """Append a sampled token; the first one moves the request to DECODING."""
-        if self.is_finished:
+    def commit_new_token(self, token_id: int, prob: Optional[float] = None, now: Optional[float] = None) -> None:
+        """Append a sampled token; the first one moves the request to DECODING. ``now``: the caller's
+        clock reading when it commits many requests at once."""
+        if self.status in _FINISHED:
             return
         self.output_ids.append(int(token_id))
         if prob is not None:
             self.output_probs.append(float(prob))
+        if now is None:
+            now = time.time()
         if self.first_token_time is None:
-            self.first_token_time = time.time()
+            self.first_token_time = now
         if self.status == RequestStatus.PREFILLING:
             self.status = RequestStatus.DECODING
-        self.last_updated_time = time.time()
+        self.last_updated_time = now
 
     @property
     def all_token_ids(self) -> list[int]:

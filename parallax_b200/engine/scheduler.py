@@ -22,6 +22,7 @@ from collections import OrderedDict, deque
 from dataclasses import dataclass
 from typing import Iterable, Optional
 
+from parallax_b200.engine.request import _FINISHED as _FINISHED_STATES
 from parallax_b200.engine.request import Request, RequestStatus
 
 logger = logging.getLogger(__name__)
@@ -35,7 +36,7 @@ def _normalize_token_ids(x) -> set[int]:
     return {int(t) for t in x}
 
 
-@dataclass
+@dataclass(slots=True)
 class ScheduledSeq:
     req: Request
     num_tokens: int        # tokens run in this step
@@ -95,18 +96,20 @@ class BatchScheduler:
     def get_running_request(self, rid: str) -> Optional[Request]:
         return self._running.get(rid)
 
-    def enque_request(self, req: Request) -> None:
+    def enque_request(self, req: Request, now: Optional[float] = None) -> None:
         """New requests go to the wait queue; a running request coming back from the
         pipeline becomes ready for its next step (and moves to the end of the ready order)."""
         if req.is_finished:
             return
+        if now is None:
+            now = time.time()
         running = self._running.get(req.request_id)
         if running is not None:
             running.ready_for_next_step = True
-            running.last_updated_time = time.time()
+            running.last_updated_time = now
             self._running.move_to_end(req.request_id)
             return
-        req.last_updated_time = time.time()
+        req.last_updated_time = now
         self._wait_queue.append(req)
 
     def evict_request(self, rid: str) -> Optional[Request]:
@@ -185,9 +188,10 @@ class BatchScheduler:
         batch: list[ScheduledSeq] = []
         prefills, decodes = [], []
         for req in self._running.values():
-            if not req.ready_for_next_step or req.is_finished:
+            st = req.status
+            if not req.ready_for_next_step or st in _FINISHED_STATES:
                 continue
-            (prefills if req.is_prefill else decodes).append(req)
+            (prefills if st == RequestStatus.PREFILLING else decodes).append(req)
         used = 0
         chunk = self.chunked_prefill_size
         prefill_cap = self.max_prefill_tokens_per_batch
@@ -216,11 +220,10 @@ class BatchScheduler:
                 req.is_chunked = True
             batch.append(ScheduledSeq(req, cost, req.num_computed_tokens, True, last))
             used += cost
-        for req in decodes:
-            if len(batch) >= self.micro_batch_size or used + 1 > budget:
-                break
-            batch.append(ScheduledSeq(req, 1, req.total_length - 1, False, True))
-            used += 1
+        room = min(self.micro_batch_size - len(batch), budget - used)
+        if room > 0:
+            for req in decodes[:room]:
+                batch.append(ScheduledSeq(req, 1, req.prompt_len + len(req.output_ids) - 1, False, True))
         now = time.time()
         for s in batch:
             s.req.ready_for_next_step = False
@@ -230,7 +233,7 @@ class BatchScheduler:
     # ------------------------------------------------------------------ finish rules
     def check_and_update_request_status(self, req: Request) -> bool:
         """EOS / stop ids (honouring ``min_new_tokens``) / max_new / max_total / abort."""
-        if req.is_finished:
+        if req.status in _FINISHED_STATES:
             self.evict_request(req.request_id)
             return True
         if req.abort:
@@ -239,20 +242,17 @@ class BatchScheduler:
             return True
         if not self.is_first_peer:
             return False
+        # runs once per request and step: plain attribute reads instead of the Request properties
         sp = req.sampling_params
-        last = req.output_ids[-1] if req.output_ids else None
-        can_stop = req.output_length > sp.min_new_tokens
+        out = req.output_ids
+        n_out = len(out)
         finished = False
-        if can_stop and not sp.ignore_eos and last is not None and last in self.eos_token_ids:
-            req.update_status(RequestStatus.FINISHED_EOS)
-            finished = True
-        elif can_stop and last is not None and sp.stop_token_ids and last in sp.stop_token_ids:
-            req.update_status(RequestStatus.FINISHED_EOS)
-            finished = True
-        elif req.output_length >= req.max_new_tokens:
-            req.update_status(RequestStatus.FINISHED_MAX_LENGTH)
-            finished = True
-        elif req.total_length >= req.max_total_length:
+        if n_out > sp.min_new_tokens and n_out:
+            last = out[-1]
+            if (not sp.ignore_eos and last in self.eos_token_ids) or (sp.stop_token_ids and last in sp.stop_token_ids):
+                req.update_status(RequestStatus.FINISHED_EOS)
+                finished = True
+        if not finished and (n_out >= sp.max_new_tokens or req.prompt_len + n_out >= req.max_total_length):
             req.update_status(RequestStatus.FINISHED_MAX_LENGTH)
             finished = True
         if finished:
