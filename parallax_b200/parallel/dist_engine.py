@@ -500,15 +500,17 @@ class DistEngine:
             self.host_s["wait"] += time.perf_counter() - tw
         sched = self.scheduler
         tc = time.perf_counter()
+        now = time.time()
         for s, tok in zip(owners, token_list):
             req = s.req
-            req.commit_new_token(int(tok))
-            self.cache.update_request_tokens(req.request_id, [int(tok)])
+            tok = int(tok)
+            req.commit_new_token(tok, now=now)
+            self.cache.append_request_token(req.request_id, tok)
             if sched.check_and_update_request_status(req):
                 self.cache.free_request(req.request_id)
             else:
-                sched.enque_request(req)
-            out.append((req, int(tok)))
+                sched.enque_request(req, now=now)
+            out.append((req, tok))
         self.host_s["commit"] += time.perf_counter() - tc
         return out
 
