@@ -308,6 +308,14 @@ class Engine:
         if events is not None:
             events[1].record()
         t_launched = time.perf_counter()
+        # prompt bookkeeping that does not depend on the sampled tokens runs while the GPU works: chunk
+        # progress and publishing the chunk's full KV blocks to the prefix cache (a request that matches
+        # them can only be scheduled in a later step, which the stream orders after this one)
+        cache = self.cache
+        for s in arrays["ordered"]:
+            if s.is_prefill:
+                s.req.num_computed_tokens = s.start + s.num_tokens
+                cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens)
         if owners:
             token_list = ids.tolist()  # device-to-host copy of the step's result (synchronises)
             if probs is not None:
@@ -329,12 +337,8 @@ class Engine:
         # ---- commit
         owner_idx = {id(s): i for i, s in enumerate(owners)}
         now = time.time()
-        cache = self.cache
         for s in arrays["ordered"]:
             req = s.req
-            if s.is_prefill:
-                req.num_computed_tokens = s.start + s.num_tokens
-                cache.insert_full_blocks_to_cache(req.request_id, req.num_computed_tokens)
             tok = None
             i = owner_idx.get(id(s))
             if i is not None:
