@@ -10,8 +10,9 @@ throughput, time to first token, time per output token, inter-token latency, end
 (mean / median / p99) and goodput against optional SLOs. Same role as the reference's
 ``src/backend/benchmark/benchmark_serving.py`` (datasets ``:147-318``, arrivals ``:320``, metrics
 ``:363-477``) with its own, smaller implementation; datasets here are ``random`` (uniform token ids
-decoded by the model's tokenizer, or synthetic words when no tokenizer is given) and ``jsonl``
-(one ``{"prompt": ..., "max_tokens": ...}`` per line).
+decoded by the model's tokenizer, or synthetic words when no tokenizer is given), ``jsonl``
+(one ``{"prompt": ..., "max_tokens": ...}`` per line) and ``sharegpt`` (a ShareGPT-style conversation
+dump: first human turn as prompt, length of the first reply as output budget).
 """
 
 from __future__ import annotations
@@ -73,6 +74,34 @@ def load_jsonl_dataset(path: str, n: int, default_out: int) -> list[Sample]:
             out.append(Sample(p, max(1, len(p.split())), int(d.get("max_tokens", default_out))))
             if len(out) >= n:
                 break
+    return out
+
+
+def load_sharegpt_dataset(path: str, n: int, default_out: int, seed: int, tokenizer=None) -> list[Sample]:
+    """ShareGPT-style JSON: a list of ``{"conversations": [{"from": "human", "value": ...}, {"from": "gpt",
+    "value": ...}, ...]}``. The first human turn is the prompt and the length of the first reply sets the
+    output budget (the reference's ``sample_sharegpt_requests``, ``benchmark_serving.py:147-208``);
+    conversations with fewer than two turns or with very short / very long turns are skipped."""
+    with open(path) as f:
+        data = json.load(f)
+    rng = random.Random(seed)
+    rng.shuffle(data)
+
+    def length(text: str) -> int:
+        return len(tokenizer.encode(text)) if tokenizer is not None else max(1, len(text.split()))
+
+    out = []
+    for item in data:
+        conv = item.get("conversations") or item.get("conversation") or []
+        if len(conv) < 2:
+            continue
+        prompt, reply = conv[0].get("value", ""), conv[1].get("value", "")
+        lp, lr = length(prompt), length(reply)
+        if lp < 4 or lr < 4 or lp > 1024 or lp + lr > 2048:
+            continue
+        out.append(Sample(prompt, lp, lr if lr > 0 else default_out))
+        if len(out) >= n:
+            break
     return out
 
 
@@ -213,7 +242,7 @@ def main(argv: Optional[list[str]] = None) -> dict:
     ap.add_argument("--base-url", default="http://127.0.0.1:3000")
     ap.add_argument("--model", default="default")
     ap.add_argument("--chat", action="store_true", help="use /v1/chat/completions instead of /v1/completions")
-    ap.add_argument("--dataset", default="random", choices=["random", "jsonl"])
+    ap.add_argument("--dataset", default="random", choices=["random", "jsonl", "sharegpt"])
     ap.add_argument("--dataset-path", default="")
     ap.add_argument("--tokenizer", default="", help="local tokenizer directory for the random dataset")
     ap.add_argument("--num-prompts", type=int, default=1000)
@@ -239,6 +268,8 @@ def main(argv: Optional[list[str]] = None) -> dict:
     if args.dataset == "random":
         samples = make_random_dataset(args.num_prompts, args.random_input_len, args.random_output_len,
                                       args.random_range_ratio, args.seed, tok, args.random_prefix_len)
+    elif args.dataset == "sharegpt":
+        samples = load_sharegpt_dataset(args.dataset_path, args.num_prompts, args.random_output_len, args.seed, tok)
     else:
         samples = load_jsonl_dataset(args.dataset_path, args.num_prompts, args.random_output_len)
     report = asyncio.run(run(args, samples))

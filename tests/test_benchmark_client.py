@@ -55,3 +55,25 @@ def test_benchmark_client_end_to_end(chat):
         server.should_exit = True
         thread.join(5)
         loop.stop()
+
+
+def test_sharegpt_dataset_loader(tmp_path):
+    import json
+
+    client = _load_client()
+    data = [
+        {"conversations": [{"from": "human", "value": "tell me about paged attention in detail please"},
+                           {"from": "gpt", "value": "it keeps the cache in fixed size blocks " * 3}]},
+        {"conversations": [{"from": "human", "value": "hi"}, {"from": "gpt", "value": "hello"}]},          # too short
+        {"conversations": [{"from": "human", "value": "only one turn here, no reply at all"}]},             # no reply
+        {"conversations": [{"from": "human", "value": "how do pipeline stages hand activations over"},
+                           {"from": "gpt", "value": "with point to point sends between neighbouring ranks"}]},
+    ]
+    path = tmp_path / "sharegpt.json"
+    path.write_text(json.dumps(data))
+    samples = client.load_sharegpt_dataset(str(path), 10, 64, seed=0)
+    assert len(samples) == 2
+    by_prompt = {s.prompt: s for s in samples}
+    s = by_prompt["how do pipeline stages hand activations over"]
+    assert s.prompt_len == 7 and s.max_tokens == 9
+    assert len(client.load_sharegpt_dataset(str(path), 1, 64, seed=0)) == 1
