@@ -75,5 +75,5 @@ def test_sharegpt_dataset_loader(tmp_path):
     assert len(samples) == 2
     by_prompt = {s.prompt: s for s in samples}
     s = by_prompt["how do pipeline stages hand activations over"]
-    assert s.prompt_len == 7 and s.max_tokens == 9
+    assert s.prompt_len == 7 and s.max_tokens == 8
     assert len(client.load_sharegpt_dataset(str(path), 1, 64, seed=0)) == 1
