@@ -1,6 +1,6 @@
 """Micro-benchmarks of the hot kernels against the measured roofline denominators.
 
-Usage:  python benchmarks/bench_kernels.py [--which gemm,gemm_small,attn,norm] [--out FILE]
+Usage:  python benchmarks/bench_kernels.py [--which gemm,gemm_small,gemm_mid,attn,norm] [--out FILE]
 
 Timing: CUDA events on the launching stream, 5 warm-up launches, an L2 flush (a 256 MB
 memset) before every timed launch, median of the timed launches. Fractions are reported
@@ -131,6 +131,46 @@ def bench_gemm_small(rows):
             del ws
 
 
+def bench_gemm_mid(rows):
+    """Pipeline-stage micro-batches (129 to 512 rows): both weight streaming and tensor throughput matter.
+    Eight weight matrices are cycled so that no launch finds its weights in L2; launches run back to
+    back between one pair of events."""
+    hbm, tf, tag = peaks()
+    reps = 8
+    for M in (192, 320, 512):
+        for N, K in [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)]:
+            x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(reps)]
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+
+            def run(fn):
+                for w in ws:
+                    fn(w)
+                torch.cuda.synchronize()
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                for _ in range(4):
+                    for w in ws:
+                        fn(w)
+                e.record()
+                torch.cuda.synchronize()
+                return s.elapsed_time(e) / (4 * reps)
+
+            ms_auto = run(lambda w: cu.linear(x, w, out=out))
+            ms_plain = min(run(lambda w: cu.linear(x, w, out=out, bn=128)), run(lambda w: cu.linear(x, w, out=out, bn=256)))
+            ms_lib = run(lambda w: torch.matmul(x, w.t(), out=out))
+            cu.check_status(x.device)
+            flops = 2.0 * M * N * K
+            byts = 2.0 * (M * K + N * K + M * N)
+            ideal = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3
+            rows.append({"kernel": "gemm_bf16_mid_m", "M": M, "N": N, "K": K, "plan_bn_splitk": cu.gemm_mid_m_plan(M, N, K),
+                         "us": round(ms_auto * 1e3, 2), "us_plain_tiles": round(ms_plain * 1e3, 2),
+                         "us_torch_matmul": round(ms_lib * 1e3, 2), "vs_torch": round(ms_lib / ms_auto, 3),
+                         "roofline_frac": round(ideal / ms_auto, 3), "tag": tag})
+            print(rows[-1], flush=True)
+            del ws
+
+
 def bench_attn(rows):
     hbm, tf, tag = peaks()
     Hq, Hkv, D, page = 32, 8, 128, 16
@@ -218,7 +258,7 @@ def bench_norm(rows):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm,gemm_small,attn,norm")
+    ap.add_argument("--which", default="gemm,gemm_small,gemm_mid,attn,norm")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     rows = []
@@ -227,6 +267,8 @@ def main():
         bench_gemm(rows)
     if "gemm_small" in which:
         bench_gemm_small(rows)
+    if "gemm_mid" in which:
+        bench_gemm_mid(rows)
     if "attn" in which:
         bench_attn(rows)
     if "norm" in which:

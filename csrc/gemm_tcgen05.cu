@@ -259,14 +259,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = num_m * num_n;
   const int num_kb = ceil_div(K, BK);
   // split-K (small-M path only): work item = (tile, K range); every range holds at least one k-block
-  constexpr bool kSplit = EPI == PXL_EPI_SPLITK_T || EPI == PXL_EPI_SPLITK_C;
+  constexpr bool kCluster = EPI == PXL_EPI_SPLITK_C || EPI == PXL_EPI_SPLITK_CN;
+  constexpr bool kSplit = EPI == PXL_EPI_SPLITK_T || kCluster;
   const int splitk = kSplit ? ep.splitk : 1;
   const int kb_per = ceil_div(num_kb, splitk);
   const int num_items = num_tiles * splitk;
   // item -> (tile, K range). Cluster variant: the CTAs of a cluster (consecutive block ids) share a
   // tile, the cluster rank is the K range, and the grid holds exactly one CTA per item.
-  auto item_tile = [&](int item) { return EPI == PXL_EPI_SPLITK_C ? item / splitk : item % num_tiles; };
-  auto item_ks = [&](int item) { return EPI == PXL_EPI_SPLITK_C ? item % splitk : item / num_tiles; };
+  auto item_tile = [&](int item) { return kCluster ? item / splitk : item % num_tiles; };
+  auto item_ks = [&](int item) { return kCluster ? item % splitk : item / num_tiles; };
   bool acc_ready = false;  // cluster variant: this CTA's accumulator is complete
 
   if (threadIdx.x == 0) {
@@ -386,7 +387,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if constexpr (EPI == PXL_EPI_SPLITK_C) {
+      if constexpr (kCluster) {
         acc_ready = true;  // drained after the cluster barrier below
         break;
       }
@@ -726,6 +727,96 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
+  if constexpr (EPI == PXL_EPI_SPLITK_CN) {
+    // ------------------------- split-K reduction inside the cluster, operands NOT swapped
+    // (129 to about a thousand tokens: too few 128-row tiles to fill the SMs, too many rows for the
+    // swapped path). Accumulator row = token, column = output column. Reducer r of the cluster owns
+    // the columns [r*cs, (r+1)*cs) of the tile; every CTA sends it those columns of its partial sums as
+    // [source][column][128 tokens] floats (lanes are consecutive tokens: conflict-free remote stores
+    // and local loads). Same barrier protocol as the swapped variant above.
+    __syncwarp();
+    cluster_sync_all();
+    const uint32_t my_rank = cluster_cta_rank();
+    const int cs = ceil_div(BN / 8, splitk) * 8;
+    const uint32_t recv0 = smem_u32(smem);
+    if (warp >= 2 && acc_ready) {
+      const int q = warp & 3;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t row_off = (q * 32 + lane) * 4;
+      int owner = 0, cl = 0;
+      uint32_t dst = cluster_map_shared(recv0, 0) + (my_rank * cs) * 512 + row_off;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          st_shared_cluster_f32(dst + cl * 512, __uint_as_float(r[j]));
+          if (++cl == cs) {
+            cl = 0;
+            ++owner;
+            if (owner < splitk) dst = cluster_map_shared(recv0, owner) + (my_rank * cs) * 512 + row_off;
+          }
+        }
+      }
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2 && acc_ready) {
+      const int tile = blockIdx.x / splitk;
+      const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
+      const int t = threadIdx.x - 64;           // token row of the tile
+      const int row = tc.a_row + t;
+      const int c_begin = my_rank * cs;
+      const int c_end = c_begin + cs < BN ? c_begin + cs : BN;
+      if (row < tc.row_end) {
+        for (int c = c_begin; c < c_end; c += 8) {
+          const int col = tc.n_blk * BN + c;
+          if (col >= N) break;
+          float f[8];
+          const uint32_t src = recv0 + ((c - c_begin) * 128 + t) * 4;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = ld_shared_f32(src + j * 512);
+          for (int r = 1; r < splitk; ++r) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] += ld_shared_f32(src + (r * cs + j) * 512);
+          }
+          const size_t c_off = static_cast<size_t>(row) * ep.ldc + col;
+          if (ep.bias) {
+            const bf16x8 b = ld_bf16x8(ep.bias + col);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 bb = unpack_bf16x2(b.u[j]);
+              f[2 * j] += bb.x;
+              f[2 * j + 1] += bb.y;
+            }
+          }
+          if (ep.residual) {
+            const bf16x8 b = ld_bf16x8(ep.residual + c_off);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 bb = unpack_bf16x2(b.u[j]);
+              f[2 * j] += bb.x;
+              f[2 * j + 1] += bb.y;
+            }
+          }
+          if (ep.C_f32 != nullptr) {
+            float4* d4 = reinterpret_cast<float4*>(ep.C_f32 + c_off);
+            d4[0] = make_float4(f[0], f[1], f[2], f[3]);
+            d4[1] = make_float4(f[4], f[5], f[6], f[7]);
+          } else {
+            bf16x8 o;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+            st_bf16x8(ep.C + c_off, o);
+          }
+        }
+      }
+    }
+  }
+
   if constexpr (EPI == PXL_EPI_RS) {
     if (warp >= 2) {
       // ---------------------------------------------- reduce the rows this rank owns
@@ -835,11 +926,11 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue
 
 // Cluster variant of the small-M path: one CTA per (tile, K range), the K ranges of a tile in one
 // cluster. max_clusters (optional) receives how many such clusters the device runs at once.
-template <int BN>
+template <int BN, int EPI = PXL_EPI_SPLITK_C>
 int launch_gemm_cluster(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogueArgs& ep, int items,
                         int cluster, int M, int N, int K, int* status, cudaStream_t stream, int* max_clusters) {
-  auto kern = gemm_bf16_tcgen05_kernel<BN, PXL_EPI_SPLITK_C>;
-  constexpr int smem = gemm_smem_bytes<BN, PXL_EPI_SPLITK_C>();
+  auto kern = gemm_bf16_tcgen05_kernel<BN, EPI>;
+  constexpr int smem = gemm_smem_bytes<BN, EPI>();
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1099,6 +1190,114 @@ int gemm_small_m(const void* A, const void* W, void* C, bool f32_out, const void
 }
 }  // namespace
 
+namespace {
+// ---- mid-M path: 129 .. kMidMaxM tokens, operands in their usual slots, K split inside a cluster ----
+constexpr int kMidMaxM = 1024;
+
+int mid_m_max_clusters(int bn, int cluster) {
+  static int cache[64][2][9];
+  static bool known[64][2][9] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cluster < 1 || cluster > 8) return 0;
+  const int bi = bn == 128 ? 0 : 1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!known[dev][bi][cluster]) {
+    int n = 0;
+    CUtensorMap dummy{};
+    GemmEpilogueArgs ep{};
+    if (bn == 128)
+      launch_gemm_cluster<128, PXL_EPI_SPLITK_CN>(dummy, dummy, ep, 0, cluster, 0, 0, 0, nullptr, nullptr, &n);
+    else
+      launch_gemm_cluster<256, PXL_EPI_SPLITK_CN>(dummy, dummy, ep, 0, cluster, 0, 0, 0, nullptr, nullptr, &n);
+    cache[dev][bi][cluster] = n;
+    known[dev][bi][cluster] = true;
+  }
+  return cache[dev][bi][cluster];
+}
+
+// Cost model (microseconds) of one launch: rounds of co-resident clusters x (k-blocks per CTA x time of
+// one 64-deep k-block at this tile width + fixed cost of the cluster exchange). The k-block times are
+// the measured steady-state rates of the plain kernel (a 128 x 256 tile keeps the tensor pipe busiest).
+struct MidPlan {
+  int bn, splitk;
+  double cost;
+};
+
+MidPlan mid_m_plan(int M, int N, int K) {
+  const int num_kb = pxl::ceil_div(K, BK);
+  const int num_m = pxl::ceil_div(M, BM);
+  const int sms = pxl_host::num_sms();
+  MidPlan best{0, 1, 1e300};
+  const int bns[2] = {256, 128};
+  const double t_kb[2] = {0.42, 0.30};
+  for (int i = 0; i < 2; ++i) {
+    const int tiles = num_m * pxl::ceil_div(N, bns[i]);
+    for (int sk = 1; sk <= 8; ++sk) {
+      if (sk > 1 && num_kb / sk < 4) break;
+      const int kb_per = pxl::ceil_div(num_kb, sk);
+      if (sk > 1 && pxl::ceil_div(num_kb, kb_per) != sk) continue;  // no empty K range
+      int slots = sk == 1 ? sms : mid_m_max_clusters(bns[i], sk);
+      if (slots <= 0) continue;
+      const double cost = pxl::ceil_div(tiles, slots) * (kb_per * t_kb[i] + (sk > 1 ? 5.0 : 3.0));
+      if (cost < best.cost) best = MidPlan{bns[i], sk, cost};
+    }
+  }
+  return best;
+}
+
+bool mid_m_disabled() {
+  static const bool off = getenv("PXL_NO_MID_M_GEMM") != nullptr;
+  return off;
+}
+
+int gemm_mid_m(const void* A, const void* W, void* C, bool f32_out, const void* residual, const void* bias, int M,
+               int N, int K, int lda, int ldw, int ldc, int bn, int splitk, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || splitk < 2 || splitk > 8) return PXL_ERR_INVALID_ARG;
+  if (bn != 128 && bn != 256) return PXL_ERR_INVALID_ARG;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || (ldc % 8) || (N % 8)) return PXL_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) & 15)
+    return PXL_ERR_INVALID_ARG;
+  const int num_kb = pxl::ceil_div(K, BK);
+  if (splitk > num_kb) return PXL_ERR_INVALID_ARG;
+  splitk = pxl::ceil_div(num_kb, pxl::ceil_div(num_kb, splitk));  // no empty K range
+  if (splitk < 2) return PXL_ERR_INVALID_ARG;
+  CUtensorMap ta, tb;
+  if (!pxl_host::make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, M, K, lda, BM, BK))
+    return PXL_ERR_TENSORMAP;
+  if (!pxl_host::make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, N, K, ldw, bn, BK))
+    return PXL_ERR_TENSORMAP;
+  GemmEpilogueArgs ep{};
+  ep.C = static_cast<pxl::bf16*>(C);
+  ep.C_f32 = f32_out ? static_cast<float*>(C) : nullptr;
+  ep.residual = static_cast<const pxl::bf16*>(residual);
+  ep.bias = static_cast<const pxl::bf16*>(bias);
+  ep.ldc = ldc;
+  ep.splitk = splitk;
+  const int items = pxl::ceil_div(M, BM) * pxl::ceil_div(N, bn) * splitk;
+  if (bn == 128)
+    return launch_gemm_cluster<128, PXL_EPI_SPLITK_CN>(ta, tb, ep, items, splitk, M, N, K, status, stream, nullptr);
+  return launch_gemm_cluster<256, PXL_EPI_SPLITK_CN>(ta, tb, ep, items, splitk, M, N, K, status, stream, nullptr);
+}
+}  // namespace
+
+// Which (tile width, K ranges) pxl_gemm_bf16 picks for a shape with 128 < M <= 1024: returns
+// bn * 16 + splitk, splitk == 1 meaning the plain persistent kernel.
+PXL_EXPORT int pxl_gemm_bf16_mid_m_plan(int M, int N, int K, int epi) {
+  if (mid_m_disabled() || M <= BM || M > kMidMaxM) return 0;
+  if (epi != PXL_EPI_NONE && epi != PXL_EPI_RESIDUAL && epi != PXL_EPI_F32) return 0;
+  const MidPlan p = mid_m_plan(M, N, K);
+  return p.bn * 16 + p.splitk;
+}
+
+// Explicit entry to the mid-M cluster split-K kernel (tests and benchmarks; pxl_gemm_bf16 picks it by itself).
+PXL_EXPORT int pxl_gemm_bf16_mid_m(const void* A, const void* W, void* C, const void* residual, const void* bias,
+                                   int M, int N, int K, int lda, int ldw, int ldc, int bn, int splitk, int f32_out,
+                                   int* status, cudaStream_t stream) {
+  return gemm_mid_m(A, W, C, f32_out != 0, residual, bias, M, N, K, lda, ldw, ldc, bn, splitk, status, stream);
+}
+
 PXL_EXPORT int pxl_gemm_bf16_small_m(const void* A, const void* W, void* C, const void* residual,
                                      const void* bias, int M, int N, int K, int lda, int ldw, int ldc,
                                      int splitk, int mode, int* status, cudaStream_t stream) {
@@ -1118,6 +1317,12 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
       !((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) & 15))
     return gemm_small_m(A, W, C, epi == PXL_EPI_F32, epi == PXL_EPI_RESIDUAL ? residual : nullptr, bias, M, N, K,
                         lda, ldw, ldc, 0, 0, status, stream);
+  if (bn == 0 && !((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(bias)) & 15)) {
+    const int plan = pxl_gemm_bf16_mid_m_plan(M, N, K, epi);
+    if (plan > 0 && (plan & 15) > 1)
+      return gemm_mid_m(A, W, C, epi == PXL_EPI_F32, epi == PXL_EPI_RESIDUAL ? residual : nullptr, bias, M, N, K, lda,
+                        ldw, ldc, plan >> 4, plan & 15, status, stream);
+  }
   if (bn == 0) bn = pxl_gemm_bf16_pick_bn(M, N, epi);
   if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;
 

@@ -26,6 +26,7 @@ typedef struct CUstream_st* pxl_stream_t;
 #define PXL_EPI_SCATTER 5   // every output row stored through its own pointer, possibly on a peer GPU
 #define PXL_EPI_SPLITK_T 6  // internal: small-M path (operands swapped, split along K, fp32 slabs + last-CTA finish)
 #define PXL_EPI_SPLITK_C 7  // internal: small-M path, the K ranges of a tile form a cluster and reduce over DSMEM
+#define PXL_EPI_SPLITK_CN 8 // internal: mid-M path (operands not swapped), K ranges of a tile reduce inside a cluster
 
 // ---- gemm_tcgen05.cu -------------------------------------------------------
 // C[M,N] = A[M,K] * W[N,K]^T. lda/ldw/ldc in elements. `bn` = tile width (64/128/256)

@@ -146,9 +146,13 @@ sample_kernel(const void* logits, int64_t ld, int V, const float* __restrict__ t
       if (keep) hi = mid; else lo = mid;
     }
   } else {
-    hi = -INFINITY;
+    lo = -INFINITY;
   }
-  const float tau = hi;
+  // The filters keep token i exactly when the condition above holds at mid = z_i (the tokens
+  // strictly above it are fewer than k and weigh at most top_p). The condition flips at the
+  // scaled logit of the last kept token: `hi` closes in on it from above and would leave that
+  // token out, `lo` ends at most 88 / 2^26 below it, so the draw takes everything above `lo`.
+  const float tau = lo;
 
   // draw: contiguous chunk per thread, block scan of chunk masses
   const int chunk = ceil_div(V, static_cast<int>(blockDim.x));

@@ -40,6 +40,12 @@ from parallax_b200.models.config import ModelConfig
 logger = logging.getLogger(__name__)
 
 
+def _describe_status(code: int) -> str:
+    from parallax_b200.ops import _lib
+
+    return _lib.describe(code)
+
+
 class StepPlan:
     """Host-side description of one step, kept until its tokens come back."""
 
@@ -240,6 +246,29 @@ class Engine:
             return ops.sample(logits, temperature, top_k, top_p, min_p, u, want_prob=True)
         return ops.sample(logits, temperature, top_k, top_p, min_p, u), None
 
+    # ------------------------------------------------------------------ device status word
+    def _queue_status_read(self) -> None:
+        """The kernels' status word rides back with the step's tokens (one pinned int, no extra
+        synchronisation)."""
+        if self.device.type == "cuda":
+            from parallax_b200.ops import cuda as _cuda
+
+            _cuda.status_copy_async(self.device)
+
+    def _step_status(self) -> int:
+        """Status word as of the end of the step that was just read back (0 = healthy); clears it."""
+        if self.device.type != "cuda":
+            return 0
+        from parallax_b200.ops import cuda as _cuda
+
+        code = _cuda.status_mirror(self.device)
+        if code:
+            try:
+                _cuda.raise_if_status(self.device)
+            except ops.KernelError:
+                pass
+        return code
+
     # ------------------------------------------------------------------ one step
     def _release(self, req: Request) -> None:
         self.cache.free_request(req.request_id)
@@ -316,12 +345,18 @@ class Engine:
             if s.is_prefill:
                 s.req.num_computed_tokens = s.start + s.num_tokens
                 cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens)
+        self._queue_status_read()
         if owners:
             token_list = ids.tolist()  # device-to-host copy of the step's result (synchronises)
             if probs is not None:
                 prob_list = probs.tolist()
         elif self.device.type == "cuda":
             torch.cuda.current_stream(self.device).synchronize()
+        code = self._step_status()
+        if code:
+            # a kernel of this step gave up (bounded wait ran out, bad table entry): its outputs are
+            # undefined, so nothing of the step is committed and the serving loop fails the batch
+            raise ops.KernelError(f"device status after step {self.total_steps}: {_describe_status(code)}")
         self.total_steps += 1
         self.last_step_stats = {
             "tokens": fb.num_tokens, "prefill_tokens": fb.num_prefill_tokens, "decode": fb.num_decode,

@@ -52,6 +52,8 @@ _SIGS = {
     "pxl_gemm_bf16_pick_bn": [c_int, c_int, c_int],
     "pxl_gemm_bf16_small_m": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "pxl_gemm_bf16_uses_small_m": [c_int, c_int, c_int, c_int],
+    "pxl_gemm_bf16_mid_m_plan": [c_int, c_int, c_int, c_int],
+    "pxl_gemm_bf16_mid_m": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "pxl_rmsnorm": [_P, _P, _P, _P, c_int, c_int, c_float, c_float, _P],
     "pxl_qk_norm_rope_cache": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int64, c_float, c_float, _P, _P],

@@ -65,6 +65,39 @@ def check_status(device: torch.device) -> None:
         raise _lib.KernelError(f"device status: {_lib.describe(code)}")
 
 
+_status_host: dict[int, torch.Tensor] = {}
+
+
+def status_copy_async(device: torch.device) -> None:
+    """Enqueue a copy of the status word into a pinned host mirror on the current stream. The
+    serving loops call this right before the step's device-to-host token copy, so the mirror is
+    valid once the tokens are: reading it costs no synchronisation of its own."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    h = _status_host.get(idx)
+    if h is None:
+        with torch.inference_mode(False):
+            h = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        _status_host[idx] = h
+    h.copy_(status_tensor(device), non_blocking=True)
+
+
+def status_mirror(device: torch.device) -> int:
+    """Value that the last completed :func:`status_copy_async` brought back (0 = healthy)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    h = _status_host.get(idx)
+    return int(h[0]) if h is not None else 0
+
+
+def raise_if_status(device: torch.device) -> None:
+    """Raise (and clear the word) if the mirrored status is non-zero. After a non-zero status the
+    output of the kernels of that step is undefined: the caller fails the batch."""
+    code = status_mirror(device)
+    if code != 0:
+        status_tensor(device).zero_()
+        _status_host[device.index if device.index is not None else torch.cuda.current_device()].zero_()
+        raise _lib.KernelError(f"device status: {_lib.describe(code)}")
+
+
 def workspace(device: torch.device, tag: str, nbytes: int) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     key = (idx, tag)
@@ -139,6 +172,34 @@ def linear_small_m(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
         x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(bias), M, N, K, x.stride(0), w.stride(0),
         out.stride(0), splitk, mode, status_tensor(x.device).data_ptr(), _stream(x.device))
     check(code, "pxl_gemm_bf16_small_m")
+    _count()
+    return out
+
+
+def gemm_mid_m_plan(M: int, N: int, K: int, epi: int = EPI_NONE) -> tuple[int, int]:
+    """``(tile width, K ranges)`` that :func:`linear` picks for 128 < M <= 1024 rows; K ranges == 1 means the
+    plain persistent kernel, ``(0, 0)`` that the shape is outside the mid-M range."""
+    code = _lib.lib().pxl_gemm_bf16_mid_m_plan(M, N, K, epi)
+    return (code >> 4, code & 15)
+
+
+def linear_mid_m(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 residual: Optional[torch.Tensor] = None, bn: int = 256, splitk: int = 2,
+                 out: Optional[torch.Tensor] = None, f32: bool = False) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T`` on the mid-M kernel: 128-row token tiles, the K ranges of a tile spread over
+    a thread-block cluster and reduced through distributed shared memory. :func:`linear` picks this path
+    by itself; the explicit entry exists for tests and benchmarks."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] == w.shape[1]
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+    if residual is not None:
+        assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
+    code = _lib.lib().pxl_gemm_bf16_mid_m(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(bias), M, N, K, x.stride(0), w.stride(0),
+        out.stride(0), bn, splitk, 1 if f32 else 0, status_tensor(x.device).data_ptr(), _stream(x.device))
+    check(code, "pxl_gemm_bf16_mid_m")
     _count()
     return out
 

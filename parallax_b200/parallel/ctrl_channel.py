@@ -17,7 +17,9 @@ from multiprocessing import shared_memory
 
 import numpy as np
 
-_HDR = 128           # bytes: [0:8] reserved, 7 reader cursors (int64), then 7 reader heartbeats (int64 ns)
+# header bytes: [0:8] reserved, 7 reader cursors (int64), 7 reader heartbeats (int64 ns) from byte 64,
+# 7 reader device-status words (int64, 0 = healthy) from byte 128
+_HDR = 256
 _SLOT_HDR = 16       # seq (int64), nbytes (int64)
 
 
@@ -43,6 +45,7 @@ class CtrlChannel:
         self.owner = create
         self.cursors = np.ndarray((7,), dtype=np.int64, buffer=self.shm.buf, offset=8)
         self.beats = np.ndarray((7,), dtype=np.int64, buffer=self.shm.buf, offset=64)
+        self.status = np.ndarray((7,), dtype=np.int64, buffer=self.shm.buf, offset=128)
         if not create:
             self.beat()
         self.seq = 0      # writer: messages published; reader: messages consumed
@@ -101,9 +104,25 @@ class CtrlChannel:
         now = time.time_ns()
         return [i for i in range(self.n_readers) if now - int(self.beats[i]) > max_age_s * 1e9]
 
+    def report_status(self, code: int) -> None:
+        """Reader: publish a non-zero device status word (kept until the writer clears it)."""
+        if self.reader_index >= 0 and code:
+            self.status[self.reader_index] = code
+
+    def failed_readers(self) -> dict[int, int]:
+        """Writer: {reader index: status code} of the readers that reported a device error; clears them."""
+        out = {}
+        for i in range(self.n_readers):
+            c = int(self.status[i])
+            if c:
+                out[i] = c
+                self.status[i] = 0
+        return out
+
     def close(self) -> None:
         self.cursors = None
         self.beats = None
+        self.status = None
         try:
             self.shm.close()
             if self.owner:

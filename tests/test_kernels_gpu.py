@@ -314,7 +314,77 @@ def test_argmax_and_sample(cu):
         # the draw is a prefix-sum walk: rounding may move it across a token boundary, so
         # accept any token whose kept-set probability interval is within rounding of u
         same = (got == want)
-        assert same.float().mean() >= 0.75, (got, want)
+        assert same.float().mean() >= 0.85, (got, want)
         assert torch.allclose(pr[same], wpr[same], rtol=5e-2, atol=1e-6)
     # top_k = 1 and temperature 0 rows are exact
     assert int(got[0]) == int(lf[0].argmax()) and int(got[4]) == int(lf[4].argmax())
+
+
+@pytest.mark.parametrize("probs,k,p,n_kept", [
+    ([0.4, 0.3, 0.2, 0.1], 2, 1.0, 2),       # top-k keeps exactly k tokens
+    ([0.4, 0.3, 0.2, 0.1], 3, 1.0, 3),
+    ([0.4, 0.3, 0.2, 0.1], 0, 0.5, 2),       # the token that crosses top_p stays in
+    ([0.5, 0.3, 0.15, 0.05], 0, 0.9, 3),
+    ([0.5, 0.3, 0.15, 0.05], 0, 0.01, 1),    # the best token always survives
+    ([0.1, 0.2, 0.3, 0.4], 3, 0.65, 2),      # both filters, unsorted vocabulary
+])
+def test_sample_kept_set_matches_reference(cu, probs, k, p, n_kept):
+    """The kept set (size and which tokens) equals the sort-based reference's: a sweep of the
+    uniform number over [0, 1) must reach every kept token and no other."""
+    dev = _dev()
+    n_u = 200
+    logits = torch.tensor(probs, device=dev).log().repeat(n_u, 1).contiguous()
+    u = (torch.arange(n_u, device=dev, dtype=torch.float32) + 0.5) / n_u
+    t = torch.ones(n_u, device=dev)
+    tk = torch.full((n_u,), k, dtype=torch.int32, device=dev)
+    tp = torch.full((n_u,), p, device=dev)
+    mp = torch.zeros(n_u, device=dev)
+    got = cu.sample(logits, t, tk, tp, mp, u)
+    want = ref.sample(logits, t, tk, tp, mp, u)
+    cu.check_status(dev)
+    assert len(set(want.tolist())) == n_kept
+    assert set(got.tolist()) == set(want.tolist())
+    # same token for the same uniform number, except within rounding of a boundary of the walk
+    assert (got == want).float().mean() >= 0.98
+    if k == 2:
+        # u close to 1 must land on the second-best token (a top-k that keeps k-1 tokens never would)
+        second = int(torch.tensor(probs).argsort(descending=True)[1])
+        assert int(got[-1]) == second
+
+
+@pytest.mark.parametrize("M,N,K,bn,splitk", [
+    (192, 4096, 4096, 256, 2), (300, 4096, 4096, 256, 3), (320, 6144, 4096, 256, 2), (512, 4096, 12288, 128, 4),
+    (129, 1000, 520, 128, 2), (384, 4096, 4096, 256, 7), (257, 2048, 2048, 128, 8),
+])
+def test_gemm_mid_m_cluster_splitk(cu, M, N, K, bn, splitk):
+    """Mid-M path (K ranges of a tile reduced inside a thread-block cluster) against fp32 matmul,
+    with bias and residual, ragged M / N / K and uneven column slices."""
+    torch.manual_seed(M + N)
+    dev = _dev()
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device=dev) * 0.03).to(torch.bfloat16)
+    b = torch.randn(N, device=dev, dtype=torch.bfloat16)
+    r = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+    want = x.float() @ w.float().t()
+    y = cu.linear_mid_m(x, w, bn=bn, splitk=splitk)
+    assert _rel_err(y, want) < 6e-3
+    y = cu.linear_mid_m(x, w, bias=b, residual=r, bn=bn, splitk=splitk)
+    assert _rel_err(y, want + b.float() + r.float()) < 6e-3
+    y32 = cu.linear_mid_m(x, w, bn=bn, splitk=splitk, f32=True)
+    assert _rel_err(y32, want) < 2e-3
+    cu.check_status(dev)
+
+
+def test_linear_picks_mid_m_and_matches(cu):
+    """The automatic choice of cu.linear for 128 < M <= 1024 gives the same result as fp32 matmul on the
+    four projection shapes of Qwen3-8B."""
+    dev = _dev()
+    torch.manual_seed(3)
+    for M in (192, 320, 512):
+        for N, K in [(6144, 4096), (4096, 4096), (4096, 12288)]:
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            w = (torch.randn(N, K, device=dev) * 0.03).to(torch.bfloat16)
+            r = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+            y = cu.linear(x, w, residual=r)
+            assert _rel_err(y, x.float() @ w.float().t() + r.float()) < 6e-3, (M, N, K, cu.gemm_mid_m_plan(M, N, K))
+    cu.check_status(dev)
