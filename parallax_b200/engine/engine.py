@@ -391,6 +391,11 @@ class Engine:
             tr.span("commit", t_synced, time.perf_counter())
         return out
 
+    def flush(self) -> list:
+        """Finish whatever the engine still has in flight on the device (nothing, while steps are
+        synchronous); returns the events of that work like :meth:`step`."""
+        return []
+
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: Iterable[list[int]], sampling_params: Optional[SamplingParams] = None,
                  max_steps: int = 1 << 30) -> list[list[int]]:

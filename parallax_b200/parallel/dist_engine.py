@@ -1,14 +1,18 @@
 """Multi-GPU engine inside one box: pipeline stages x tensor-parallel ranks, one process per GPU.
 
 Rank layout: ``rank = pp_rank * tp + tp_rank``. Rank 0 owns the scheduler and the logical KV
-plan; every step it broadcasts the packed step inputs (a few hundred KB of indices) to all
-ranks over a CPU control group, so that every rank can enqueue its kernels without waiting on
-a device-to-host copy. Activations move stage to stage with NCCL point-to-point on NVLink -
+plan; every step it publishes the packed step inputs (a few hundred KB of indices) to all
+ranks through a shared-memory ring, so that every rank can enqueue its kernels without waiting
+on a device-to-host copy. Activations move stage to stage with NCCL point-to-point on NVLink -
 each tensor-parallel rank sends its own row shard to its counterpart in the next stage - and
-only the sampled token ids travel back to rank 0, on a separate communicator so that the
-return path never queues behind the forward path. Several micro-batches are kept in flight
-(``pp`` by default) to fill the pipeline: rank 0 issues plan k+1 before it reads the tokens of
-plan k.
+only the sampled token ids travel back to rank 0.
+
+Every hop has a two-rank communicator of its own (forward hops and the token return never
+queue behind one another), receives are posted on a side stream into a ring of buffers as soon
+as the plan is known, and the compute stream only waits for the event that marks the arrival.
+Several micro-batches are kept in flight (``pp`` by default): rank 0 issues plan k+1 before it
+reads the tokens of plan k. On rank 0 the stage's kernel launches run in a thread of their own,
+so planning and committing micro-batches overlaps with enqueuing the stage's work.
 
 This replaces the reference's stage transport (hidden states -> safetensors bytes -> protobuf
 -> ZMQ -> libp2p RPC -> ZMQ, with a GPU<->CPU copy on every hop;
@@ -20,6 +24,8 @@ from __future__ import annotations
 
 import logging
 import os
+import queue
+import threading
 import time
 from collections import deque
 from dataclasses import dataclass
@@ -47,12 +53,17 @@ def cu_launch_count() -> int:
 
 
 def split_layers(num_layers: int, pp: int) -> list[tuple[int, int]]:
-    """Even contiguous split (what water-filling yields for identical GPUs); earlier stages get
-    the remainder layers because the last stage also runs the lm_head."""
+    """Contiguous split, as even as the layer count allows (what water-filling yields for identical
+    GPUs). The remainder layers go to the stages in the middle: the first stage also hosts the
+    scheduler and the embedding, the last one the lm_head and the sampler."""
     base, rem = divmod(num_layers, pp)
+    extra = [0] * pp
+    order = list(range(1, pp - 1)) + [0, pp - 1] if pp > 2 else list(range(pp))
+    for i in order[:rem]:
+        extra[i] = 1
     out, s = [], 0
     for i in range(pp):
-        n = base + (1 if i < rem else 0)
+        n = base + extra[i]
         out.append((s, s + n))
         s += n
     return out
@@ -86,6 +97,16 @@ class Topology:
         return (self.pp - 1) * self.tp
 
 
+class _RecvSlot:
+    """One buffer of the receive ring and the event after which it may be overwritten."""
+
+    __slots__ = ("buf", "free")
+
+    def __init__(self):
+        self.buf: Optional[torch.Tensor] = None
+        self.free = None
+
+
 class DistEngine:
     def __init__(self, cfg: ModelConfig, pp: int, tp: int, device, dtype=None, page_size: int = 16,
                  num_blocks: Optional[int] = None, kv_fraction: float = 0.85, max_batch_size: int = 8,
@@ -95,42 +116,66 @@ class DistEngine:
                  max_total_length: int = 32768, request_timeout_s: Optional[float] = 600, eos_token_id=None,
                  seed: int = 0, weights: Optional[dict] = None, fused: Optional[bool] = None,
                  max_in_flight: Optional[int] = None, weights_prefiltered: bool = False,
-                 liveness_timeout_s: float = 10.0, step_timeout_s: float = 600.0):
+                 liveness_timeout_s: float = 10.0, step_timeout_s: float = 600.0, align_rows: int = 0,
+                 executor_thread: Optional[bool] = None):
         assert dist.is_initialized(), "init the default process group first (nccl on GPUs, gloo on CPU)"
         self.cfg = cfg
         self.device = torch.device(device)
         world, rank = dist.get_world_size(), dist.get_rank()
         assert world == pp * tp, f"world size {world} != pp*tp = {pp * tp}"
-        self.topo = Topology(world, rank, pp, tp)
+        self.topo = topo = Topology(world, rank, pp, tp)
         on_gpu = self.device.type == "cuda"
-        # groups (every rank creates every group, in the same order)
+        data_backend = "nccl" if on_gpu else "gloo"
+        # ---- groups (every rank creates every group, in the same order)
         self.ctrl = dist.new_group(list(range(world)), backend="gloo")
-        self.ret = dist.new_group(list(range(world)), backend="nccl" if on_gpu else "gloo")
+        # one two-rank communicator per stage hop and tensor-parallel lane, one for the token return
+        self.hop_in = self.hop_out = self.ret = None
+        for s in range(pp - 1):
+            for t in range(tp):
+                a, b = s * tp + t, (s + 1) * tp + t
+                g = dist.new_group([a, b], backend=data_backend)
+                if rank == a:
+                    self.hop_out = g
+                elif rank == b:
+                    self.hop_in = g
+        if topo.last_stage_root != 0:
+            g = dist.new_group([0, topo.last_stage_root], backend=data_backend)
+            if rank in (0, topo.last_stage_root):
+                self.ret = g
         self.tp_group = None
         for s in range(pp if tp > 1 else 0):
-            g = dist.new_group(list(range(s * tp, (s + 1) * tp)), backend="nccl" if on_gpu else "gloo")
-            if s == self.topo.pp_rank:
+            g = dist.new_group(list(range(s * tp, (s + 1) * tp)), backend=data_backend)
+            if s == topo.pp_rank:
                 self.tp_group = g
-        # step plans travel through shared memory (all ranks live on one box); the name is agreed once
+        self.max_in_flight = max_in_flight or pp
+        # ---- step plans travel through shared memory (all ranks live on one box); the name is agreed once
         from parallax_b200.parallel.ctrl_channel import CtrlChannel
 
+        max_blocks = (max_total_length + page_size - 1) // page_size + 1
+        ratio = micro_batch_ratio or pp
+        micro_seqs = max(1, max_batch_size // max(1, ratio))
+        # the largest plan: ids, positions (4 B) and slots (8 B) per token, one block table row per sequence
+        slot_bytes = 16 * (max_num_tokens_per_batch + max_batch_size) + 4 * micro_seqs * (max_blocks + 8) + (64 << 10)
+        slot_bytes = max(1 << 18, (slot_bytes + 4095) // 4096 * 4096)
+        n_slots = max(8, self.max_in_flight + 6)
         box = [None]
         if rank == 0:
             box[0] = f"pxl_ctrl_{os.getpid()}_{int(time.time() * 1e3) % 100000000}"
-            self.chan = CtrlChannel(box[0], create=True, n_readers=world - 1)
+            self.chan = CtrlChannel(box[0], create=True, n_readers=world - 1, slots=n_slots, slot_bytes=slot_bytes)
         dist.broadcast_object_list(box, src=0, group=self.ctrl)      # also orders attach after create
         if rank != 0:
-            self.chan = CtrlChannel(box[0], create=False, n_readers=world - 1, reader_index=rank - 1)
-        start, end = split_layers(cfg.num_hidden_layers, pp)[self.topo.pp_rank]
+            self.chan = CtrlChannel(box[0], create=False, n_readers=world - 1, reader_index=rank - 1, slots=n_slots,
+                                    slot_bytes=slot_bytes)
+        start, end = split_layers(cfg.num_hidden_layers, pp)[topo.pp_rank]
         comm = None
         if tp > 1:
             use_fused = on_gpu if fused is None else fused
             if use_fused:
-                comm = FusedTPComm(self.tp_group, tp, self.topo.tp_rank, self.device, max_num_tokens_per_batch,
+                comm = FusedTPComm(self.tp_group, tp, topo.tp_rank, self.device, max_num_tokens_per_batch,
                                    cfg.hidden_size, max_n=cfg.hidden_size,
                                    max_k=max(cfg.hidden_size, cfg.intermediate_size // tp, cfg.q_size // tp))
             else:
-                comm = CollectiveTPComm(self.tp_group, tp, self.topo.tp_rank, align=128 if on_gpu else 1)
+                comm = CollectiveTPComm(self.tp_group, tp, topo.tp_rank, align=128 if on_gpu else 1)
         if weights is not None and not weights_prefiltered:
             from parallax_b200.loader.filter import filter_weights_for_range
 
@@ -138,7 +183,7 @@ class DistEngine:
         max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
         self.worker = StageWorker(cfg, start, end, self.device, dtype, page_size, num_blocks=num_blocks,
                                   kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
-                                  tp_rank=self.topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm,
+                                  tp_rank=topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm,
                                   num_linear_slots=max(max_batch_size * 2, 16) if cfg.has_linear_layers else 0)
         if cfg.has_linear_layers:
             enable_prefix_cache = False
@@ -146,18 +191,19 @@ class DistEngine:
         nb = torch.tensor([self.worker.num_blocks], dtype=torch.int64)
         dist.all_reduce(nb, op=dist.ReduceOp.MIN, group=self.ctrl)
         self.num_blocks = int(nb)
-        self.max_in_flight = max_in_flight or pp
         self.liveness_timeout_s, self.step_timeout_s = liveness_timeout_s, step_timeout_s
+        self._recv_stream = torch.cuda.Stream(self.device) if on_gpu else None
         self._ret_stream = torch.cuda.Stream(self.device) if on_gpu else None
+        self._recv_ring = [_RecvSlot() for _ in range(self.max_in_flight + 2)]
+        self._recv_n = 0
         self._warm_links()
-        ratio = micro_batch_ratio or pp
         self.planner = None
         if rank == 0:
             self.planner = Planner(cfg, self.num_blocks, page_size, max_batch_size, max_num_tokens_per_batch, ratio,
                                    chunked_prefill_size, enable_prefix_cache, max_total_length, request_timeout_s,
                                    eos_token_id)
             self.planner.scheduler.max_prefill_tokens_per_batch = max_prefill_tokens_per_batch
-        max_blocks = (max_total_length + page_size - 1) // page_size + 1
+            self.planner.scheduler.align_rows = align_rows
         self.builders = [BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size, max_batch_size,
                                       max_blocks) for _ in range(self.max_in_flight + 1)]
         self._bi = 0
@@ -172,6 +218,25 @@ class DistEngine:
         self._busy_events: list = []     # (start, end, rows) of every micro-batch's compute since the last mark
         self.h2d_bytes = 0
         self.host_s = {"plan": 0.0, "publish": 0.0, "launch": 0.0, "wait": 0.0, "commit": 0.0}
+        # token return: pinned host buffers (tokens + the last stage's status word), reused round-robin
+        self._ret_host = [torch.empty(max_batch_size + 1, dtype=torch.int32, pin_memory=on_gpu)
+                          for _ in range(self.max_in_flight + 2)] if rank == 0 else []
+        self._ret_n = 0
+        # rank 0: the stage's launches run in their own thread (on GPUs; CPU ranks keep one thread)
+        self._exec_thread = None
+        self._exec_q: "queue.Queue" = queue.Queue()
+        self._exec_err: list = []
+        use_thread = on_gpu if executor_thread is None else executor_thread
+        if rank == 0 and use_thread and world > 1:
+            self._exec_thread = threading.Thread(target=self._executor_loop, name="pxl-stage0-exec", daemon=True)
+            self._exec_thread.start()
+
+    # ------------------------------------------------------------------ links
+    def _prev(self) -> int:
+        return self.topo.rank - self.topo.tp
+
+    def _next(self) -> int:
+        return self.topo.rank + self.topo.tp
 
     def _warm_links(self) -> None:
         """Open every point-to-point connection once, in an order that all ranks share, so that
@@ -180,9 +245,9 @@ class DistEngine:
         topo = self.topo
         x = torch.zeros(8, dtype=self.worker.dtype, device=self.device)
         if not topo.is_first_stage:
-            dist.recv(x, src=topo.rank - topo.tp)
+            dist.recv(x, src=self._prev(), group=self.hop_in)
         if not topo.is_last_stage:
-            dist.send(x, dst=topo.rank + topo.tp)
+            dist.send(x, dst=self._next(), group=self.hop_out)
         if topo.last_stage_root != 0:
             t = torch.zeros(8, dtype=torch.int32, device=self.device)
             if topo.rank == topo.last_stage_root:
@@ -191,6 +256,31 @@ class DistEngine:
                 dist.recv(t, src=topo.last_stage_root, group=self.ret)
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
+
+    def _recv_hidden(self, rows: int) -> torch.Tensor:
+        """Post the receive of a micro-batch's activations into the next ring buffer. On a GPU the
+        receive lives on a side stream (it can complete while earlier micro-batches still compute)
+        and the compute stream waits for its event only."""
+        H = self.cfg.hidden_size
+        slot = self._recv_ring[self._recv_n % len(self._recv_ring)]
+        self._recv_n += 1
+        if slot.buf is None or slot.buf.shape[0] < rows:
+            slot.buf = torch.empty((max(rows, 256), H), dtype=self.worker.dtype, device=self.device)
+            slot.free = None
+        hidden = slot.buf[:rows]
+        if self.device.type != "cuda":
+            dist.recv(hidden, src=self._prev(), group=self.hop_in)
+            return hidden
+        arrived = torch.cuda.Event()
+        with torch.cuda.stream(self._recv_stream):
+            if slot.free is not None:
+                self._recv_stream.wait_event(slot.free)     # the compute that last read this buffer is done
+            work = dist.irecv(hidden, src=self._prev(), group=self.hop_in)
+            work.wait()
+            arrived.record()
+        torch.cuda.current_stream(self.device).wait_event(arrived)
+        slot.free = torch.cuda.Event()       # recorded by the caller after the compute that reads the buffer
+        return hidden
 
     # ------------------------------------------------------------------ rank-0 API
     @property
@@ -222,45 +312,45 @@ class DistEngine:
     def has_work(self) -> bool:
         return bool(self.in_flight) or self.scheduler.num_queued_requests > 0 or self.scheduler.num_running_requests > 0
 
-    # ------------------------------------------------------------------ plan broadcast
-    def _bcast(self, plan: Optional[dict]) -> dict:
-        if self.topo.rank == 0:
-            self.chan.publish(plan)
-            return plan
-        return self.chan.receive()
-
+    # ------------------------------------------------------------------ one micro-batch on this rank
     def _execute(self, plan: dict):
-        """Run this rank's part of one planned micro-batch. Returns the sampled-token tensor on
-        rank 0 (after the return hop) or None."""
+        """Run this rank's part of one planned micro-batch. Returns, on rank 0, a handle on the
+        sampled tokens (see :meth:`_tokens_of`), else None."""
         topo, w = self.topo, self.worker
+        on_gpu = self.device.type == "cuda"
         b = self.builders[self._bi]
         self._bi = (self._bi + 1) % len(self.builders)
         fb = b.build(plan["ids"] if topo.is_first_stage else None, plan["pos"], plan["slots"], plan["p_q"],
                      plan["p_ctx"], plan["p_tables"], plan["d_ctx"], plan["d_tables"], plan["logit_rows"],
                      plan.get("seq_rows"))
         self.h2d_bytes += fb.h2d_bytes
-        T, H = fb.num_tokens, self.cfg.hidden_size
+        T = fb.num_tokens
         hidden = None
+        slot_free = None
         if not topo.is_first_stage:
             rows = w.model.comm.rows_per_rank(T) if topo.tp > 1 else T
-            hidden = torch.empty((rows, H), dtype=w.dtype, device=self.device)
-            dist.recv(hidden, src=topo.rank - topo.tp)
-        ev0 = ev1 = None
-        if self.device.type == "cuda" and self.marks and len(self._busy_events) < 100000:
+            hidden = self._recv_hidden(rows)
+            slot_free = self._recv_ring[(self._recv_n - 1) % len(self._recv_ring)].free
+        ev0 = None
+        if on_gpu and self.marks and len(self._busy_events) < 100000:
             ev0 = torch.cuda.Event(enable_timing=True)      # only between benchmark marks
             ev0.record()
         with torch.inference_mode():
             out = w.run(fb, hidden)
+        if slot_free is not None:
+            slot_free.record()
         if ev0 is not None:
             ev1 = torch.cuda.Event(enable_timing=True)
             ev1.record()
             self._busy_events.append((ev0, ev1, T))
+        n_logits = plan["n_logits"]
         tokens = None
         if self.keep_logits and topo.is_last_stage:
             self.last_logits = out
         if not topo.is_last_stage:
-            self._pending_sends.append((dist.isend(out.contiguous(), dst=topo.rank + topo.tp), out))
-        elif plan["n_logits"] > 0:
+            out = out if out.is_contiguous() else out.contiguous()
+            self._pending_sends.append((dist.isend(out, dst=self._next(), group=self.hop_out), out))
+        elif n_logits > 0:
             if plan["greedy"]:
                 tokens = ops.argmax(out)
             else:
@@ -271,29 +361,106 @@ class DistEngine:
                                     torch.tensor(sp["p"], dtype=torch.float32, device=dev),
                                     torch.tensor(sp["mp"], dtype=torch.float32, device=dev),
                                     torch.tensor(sp["u"], dtype=torch.float32, device=dev))
-            if topo.rank == topo.last_stage_root and topo.last_stage_root != 0:
-                self._pending_sends.append((dist.isend(tokens, dst=0, group=self.ret), tokens))
-        while len(self._pending_sends) > 2 * self.max_in_flight:
+            if topo.rank == topo.last_stage_root:
+                # the status word of the sampling rank rides with the tokens
+                packed = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)
+                packed[:n_logits].copy_(tokens)
+                if on_gpu:
+                    from parallax_b200.ops import cuda as cu
+
+                    packed[n_logits:].copy_(cu.status_tensor(self.device))
+                else:
+                    packed[n_logits:].zero_()
+                tokens = packed
+                if topo.last_stage_root != 0:
+                    self._pending_sends.append((dist.isend(packed, dst=0, group=self.ret), packed))
+        while len(self._pending_sends) > 2 * self.max_in_flight + 2:
             self._pending_sends.popleft()[0].wait()
-        if topo.rank != 0 or plan["n_logits"] == 0:
+        if on_gpu and topo.rank != topo.last_stage_root:
+            # middle ranks: mirror the status word to the host; it is looked at one step later
+            from parallax_b200.ops import cuda as cu
+
+            code = cu.status_mirror(self.device)
+            if code and topo.rank != 0:
+                self.chan.report_status(code)
+            cu.status_copy_async(self.device)
+        if topo.rank != 0 or n_logits == 0:
             return None
+        host = self._ret_host[self._ret_n % len(self._ret_host)]
+        self._ret_n += 1
         if topo.last_stage_root != 0:
             # post the receive now, in the same order in which the last stage posts its sends
-            if self.device.type != "cuda":
-                t = torch.empty(plan["n_logits"], dtype=torch.int32, device=self.device)
+            if not on_gpu:
+                t = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)
                 return ("recv", (t, dist.irecv(t, src=topo.last_stage_root, group=self.ret), None, None))
             # on a side stream: reading the tokens later must not wait for the compute of the
             # micro-batches that were queued behind this one
-            host = torch.empty(plan["n_logits"], dtype=torch.int32, pin_memory=True)
             ev = torch.cuda.Event()
             with torch.cuda.stream(self._ret_stream):
-                t = torch.empty(plan["n_logits"], dtype=torch.int32, device=self.device)   # from the side stream's pool
+                t = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)   # from the side stream's pool
                 work = dist.irecv(t, src=topo.last_stage_root, group=self.ret)
                 work.wait()
-                host.copy_(t, non_blocking=True)
+                host[:n_logits + 1].copy_(t, non_blocking=True)
                 ev.record()
-            return ("recv", (t, None, host, ev))
+            return ("recv", (t, None, host[:n_logits + 1], ev))
+        if on_gpu:
+            ev = torch.cuda.Event()
+            host[:n_logits + 1].copy_(tokens, non_blocking=True)
+            ev.record()
+            return ("recv", (tokens, None, host[:n_logits + 1], ev))
         return ("have", tokens)
+
+    # ------------------------------------------------------------------ rank 0: executor thread
+    def _executor_loop(self) -> None:
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        while True:
+            item = self._exec_q.get()
+            if item is None:
+                return
+            kind, payload, box = item
+            try:
+                if kind == "step":
+                    box.append(self._execute(payload))
+                elif kind == "mark":
+                    self._on_mark()
+                    box.append(None)
+                else:       # "drain": everything queued before has been enqueued on the device
+                    box.append(None)
+            except BaseException as exc:      # surfaced by the scheduling thread at its next collect
+                self._exec_err.append(exc)
+                box.append(("error", exc))
+            finally:
+                done = getattr(box, "done", None)
+                if done is not None:
+                    done.set()
+
+    class _Box(list):
+        """Result slot of a queued executor job."""
+
+        def __init__(self):
+            super().__init__()
+            self.done = threading.Event()
+
+    def _submit(self, kind: str, payload=None) -> "_Box":
+        box = DistEngine._Box()
+        if self._exec_thread is None:
+            if kind == "step":
+                box.append(self._execute(payload))
+            elif kind == "mark":
+                self._on_mark()
+                box.append(None)
+            else:
+                box.append(None)
+            box.done.set()
+        else:
+            self._exec_q.put((kind, payload, box))
+        return box
+
+    def _drain_executor(self) -> None:
+        self._submit("drain").done.wait()
+        if self._exec_err:
+            raise self._exec_err.pop(0)
 
     # ------------------------------------------------------------------ device-time probes
     def _on_mark(self) -> None:
@@ -329,31 +496,41 @@ class DistEngine:
 
     def mark(self) -> None:
         """Rank 0: every rank records a CUDA event at this point of its stream."""
-        self._bcast({"cmd": "mark"})
-        self._on_mark()
+        self.chan.publish({"cmd": "mark"})
+        self._submit("mark").done.wait()
 
     def elapsed(self) -> dict:
-        self._bcast({"cmd": "elapsed"})
+        self._drain_executor()
+        self.chan.publish({"cmd": "elapsed"})
         return self._on_elapsed()
 
     # ------------------------------------------------------------------ follower loop
-    def serve_forever(self) -> None:
-        """Ranks other than 0: execute broadcast plans until rank 0 says stop."""
-        assert self.topo.rank != 0
-        while True:
-            plan = self._bcast(None)
-            if plan.get("cmd") == "stop":
-                break
-            if plan.get("cmd") == "mark":
-                self._on_mark()
-                continue
-            if plan.get("cmd") == "elapsed":
-                self._on_elapsed()
-                continue
+    def serve_one(self) -> bool:
+        """Ranks other than 0: take the next message of rank 0 and act on it. False after "stop"."""
+        plan = self.chan.receive()
+        cmd = plan.get("cmd")
+        if cmd == "stop":
+            return False
+        if cmd == "mark":
+            self._on_mark()
+        elif cmd == "elapsed":
+            self._on_elapsed()
+        else:
             self._execute(plan)
             self.steps += 1
+        return True
+
+    def finish_sends(self) -> None:
         for work, _ in self._pending_sends:
             work.wait()
+        self._pending_sends.clear()
+
+    def serve_forever(self) -> None:
+        """Ranks other than 0: execute published plans until rank 0 says stop."""
+        assert self.topo.rank != 0
+        while self.serve_one():
+            pass
+        self.finish_sends()
         self._status_all_ranks()
         self.chan.close()
 
@@ -373,7 +550,12 @@ class DistEngine:
     def shutdown(self) -> None:
         """Rank 0: stop the other ranks; raises if any rank's kernels reported a device error."""
         if self.topo.rank == 0:
-            self._bcast({"cmd": "stop"})
+            if self._exec_thread is not None:
+                self._drain_executor()
+                self._exec_q.put(None)
+                self._exec_thread.join(10.0)
+                self._exec_thread = None
+            self.chan.publish({"cmd": "stop"})
             codes = self._status_all_ranks()       # also a barrier: every reader has seen the stop message
             self.chan.close()
             if any(codes):
@@ -420,9 +602,9 @@ class DistEngine:
                                 "k": [sp.top_k if sp.top_k > 0 else 0 for sp in sps], "p": [sp.top_p for sp in sps],
                                 "mp": [sp.min_p for sp in sps], "u": self._rng.random(len(sps)).tolist()}
         t1 = time.perf_counter()
-        self._bcast(plan)
+        self.chan.publish(plan)
         t2 = time.perf_counter()
-        res = self._execute(plan)
+        res = self._submit("step", plan)
         t3 = time.perf_counter()
         hs = self.host_s
         hs["plan"] += t1 - t0
@@ -448,8 +630,6 @@ class DistEngine:
         waiter = None
         if ev is None:
             # gloo receive handles only complete inside wait(): block in a helper thread and watch it
-            import threading
-
             err: list = []
 
             def _wait():
@@ -483,21 +663,50 @@ class DistEngine:
             if waited > self.step_timeout_s:
                 raise TimeoutError(f"no tokens came back within {self.step_timeout_s:.0f} s")
 
+    def _check_device_status(self, last_stage_code: int) -> None:
+        """Fail the step if any rank's kernels gave up (bounded wait ran out, bad table entry)."""
+        bad = {}
+        if last_stage_code:
+            bad[self.topo.last_stage_root] = last_stage_code
+        for idx, code in self.chan.failed_readers().items():
+            bad[idx + 1] = code
+        if self.device.type == "cuda" and self.topo.last_stage_root != 0:
+            from parallax_b200.ops import cuda as cu
+
+            code = cu.status_mirror(self.device)
+            if code:
+                bad[0] = code
+                try:
+                    cu.raise_if_status(self.device)
+                except ops.KernelError:
+                    pass
+        if bad:
+            from parallax_b200.ops import _lib
+
+            raise ops.KernelError("device status: " + ", ".join(f"rank {r}: {_lib.describe(c)}"
+                                                                for r, c in sorted(bad.items())))
+
     def _collect(self) -> list:
-        arrays, res = self.in_flight.popleft()
+        arrays, box = self.in_flight.popleft()
         out = []
         owners = arrays["owners"]
         token_list = []
+        tw = time.perf_counter()
+        box.done.wait()
+        if self._exec_err:
+            raise self._exec_err.pop(0)
+        res = box[0]
         if owners:
             kind, t = res
-            tw = time.perf_counter()
             if kind == "recv":
                 t, work, host, ev = t
                 self._wait_return(ev, work)
                 if ev is not None:
                     t = host
             token_list = t.tolist()
+            status_code = int(token_list.pop())
             self.host_s["wait"] += time.perf_counter() - tw
+            self._check_device_status(status_code)
         sched = self.scheduler
         tc = time.perf_counter()
         now = time.time()

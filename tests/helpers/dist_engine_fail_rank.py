@@ -22,10 +22,8 @@ def main() -> None:
     eng = launcher.build_dist_engine(spec)
     if rank == 1:
         for _ in range(spec["plans_before_exit"]):
-            plan = eng._bcast(None)
-            eng._execute(plan)
-        for work, _ in eng._pending_sends:
-            work.wait()
+            eng.serve_one()
+        eng.finish_sends()
         os._exit(0)          # between steps, nothing of this rank in flight
     eng.liveness_timeout_s = 2.0
     eng.step_timeout_s = 60.0

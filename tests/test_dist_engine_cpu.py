@@ -21,10 +21,10 @@ HELPER = os.path.join(os.path.dirname(__file__), "helpers", "dist_engine_rank.py
 PROMPTS = [[5, 9, 77, 3, 250, 12, 8], [100, 101, 102], list(range(20, 75)), [7] * 19, [1, 2, 3, 4, 5, 6, 7, 8, 9]]
 
 
-def _run_group(pp, tp, tmp_path, max_new=6, chunk=16, model="tiny"):
+def _run_group(pp, tp, tmp_path, max_new=6, chunk=16, model="tiny", **extra):
     spec = dict(model_name=model, pp=pp, tp=tp, device_type="cpu", num_blocks=256, page_size=16, max_batch_size=4,
                 max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256, prompts=PROMPTS,
-                max_new=max_new, seed=0)
+                max_new=max_new, seed=0, **extra)
     world, port = pp * tp, free_port()
     out = tmp_path / f"out_{pp}_{tp}.json"
     procs = []
@@ -52,7 +52,8 @@ def _single(max_new=6, chunk=16, model="tiny"):
 
 def test_split_layers_and_padding():
     assert split_layers(28, 4) == [(0, 7), (7, 14), (14, 21), (21, 28)]
-    assert split_layers(10, 3) == [(0, 4), (4, 7), (7, 10)]
+    assert split_layers(10, 3) == [(0, 3), (3, 7), (7, 10)]      # the remainder goes to a middle stage
+    assert [b - a for a, b in split_layers(36, 8)] == [4, 5, 5, 5, 5, 4, 4, 4]
     assert padded_rows_per_rank(1, 2, 128) == 128
     assert padded_rows_per_rank(300, 2, 128) == 256
     assert padded_rows_per_rank(7, 2, 1) == 4
@@ -64,6 +65,15 @@ def test_dist_engine_matches_single_process(pp, tp, tmp_path):
     got = _run_group(pp, tp, tmp_path)
     assert got["outputs"] == want
     assert got["probe"]["device_ms"] > 0 and got["probe"]["h2d_bytes"] > 0
+
+
+def test_rank0_executor_thread_and_aligned_rows(tmp_path):
+    """Rank 0 launching its stage from a thread of its own, three micro-batches in flight and prompt
+    slices trimmed to a row multiple: same tokens as the single-process engine."""
+    want = _single()
+    got = _run_group(2, 1, tmp_path, executor_thread=True, micro_batch_ratio=2, max_in_flight=3,
+                     max_prefill_tokens_per_batch=24, align_rows=8)
+    assert got["outputs"] == want
 
 
 def test_dist_engine_moe_expert_parallel(tmp_path):
