@@ -154,31 +154,37 @@ def percentile(xs: list, q: float):
 
 
 class LatencyLog:
-    """Per-request time to first token and time per output token over the timed region."""
+    """Per-request time to first token and time per output token, from the tokens that came out
+    inside the timed region: TTFT of every request admitted in the region whose first token arrived in
+    it, TPOT = (time of last token - time of first token in the region) / (tokens in between) of every
+    request with at least two tokens in the region."""
 
     def __init__(self):
         self.t_start = None
         self.ttft: list[float] = []
-        self.tpot: list[float] = []
+        self.span: dict = {}      # request id -> [time of first token in the region, time of last, count]
 
     def start(self) -> None:
         self.t_start = time.time()
 
-    def saw(self, req) -> None:
-        """Call for every request that finished inside the timed region."""
-        if self.t_start is None or req.first_token_time is None:
+    def token(self, req, now: float) -> None:
+        if self.t_start is None:
             return
-        if req.arrival_time >= self.t_start:
-            self.ttft.append((req.first_token_time - req.arrival_time) * 1e3)
-        n = len(req.output_ids)
-        if n > 1 and req.finish_time is not None and req.first_token_time >= self.t_start:
-            self.tpot.append((req.finish_time - req.first_token_time) / (n - 1) * 1e3)
+        rec = self.span.get(req.request_id)
+        if rec is None:
+            self.span[req.request_id] = [now, now, 1]
+            if len(req.output_ids) == 1 and req.arrival_time >= self.t_start:
+                self.ttft.append((now - req.arrival_time) * 1e3)
+        else:
+            rec[1] = now
+            rec[2] += 1
 
     def summary(self) -> dict:
+        tpot = [(b - a) / (n - 1) * 1e3 for a, b, n in self.span.values() if n > 1]
         r = lambda v: None if v is None else round(v, 2)  # noqa: E731
         return {"ttft_ms_p50": r(percentile(self.ttft, 0.5)), "ttft_ms_p99": r(percentile(self.ttft, 0.99)),
-                "tpot_ms_p50": r(percentile(self.tpot, 0.5)), "tpot_ms_p99": r(percentile(self.tpot, 0.99)),
-                "latency_samples": {"ttft": len(self.ttft), "tpot": len(self.tpot)}}
+                "tpot_ms_p50": r(percentile(tpot, 0.5)), "tpot_ms_p99": r(percentile(tpot, 0.99)),
+                "latency_samples": {"ttft": len(self.ttft), "tpot": len(tpot)}}
 
 
 def result_line(args, wl, world, parallelism, tokens, dev_s, wall_s, launches, h2d, d2h, clocks, invalid, extra=None):
@@ -300,11 +306,12 @@ def run_group(args, wl, cfg, par, world, rank, local_rank, device, invalid) -> N
         """One engine iteration per micro-batch: every running request advances by one token."""
         toks = 0
         for _ in range(n_mb):
+            now = time.time()
             for req, tok in eng.step():
                 if tok is not None:
                     toks += 1
+                    lat.token(req, req.last_updated_time or now)
                 if req.is_finished:
-                    lat.saw(req)
                     admit(out_len)
         return toks
 
@@ -541,11 +548,12 @@ def main() -> None:
     def one_step(ev=None):
         done = eng.step(events=ev)
         toks = 0
+        now = time.time()
         for req, tok in done:
             if tok is not None:
                 toks += 1
+                lat.token(req, req.last_updated_time or now)
             if req.is_finished:
-                lat.saw(req)
                 admit(out_len)
         return toks
 

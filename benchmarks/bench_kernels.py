@@ -159,11 +159,18 @@ def bench_gemm_mid(rows):
             ms_auto = run(lambda w: cu.linear(x, w, out=out))
             ms_plain = min(run(lambda w: cu.linear(x, w, out=out, bn=128)), run(lambda w: cu.linear(x, w, out=out, bn=256)))
             ms_lib = run(lambda w: torch.matmul(x, w.t(), out=out))
+            sweep = {}
+            for bn in (128, 256):
+                for sk in (2, 3, 4, 6, 8):
+                    if (K // 64) // sk < 4:
+                        continue
+                    sweep[f"{bn}x{sk}"] = round(run(lambda w: cu.linear_mid_m(x, w, bn=bn, splitk=sk, out=out)) * 1e3, 2)
             cu.check_status(x.device)
             flops = 2.0 * M * N * K
             byts = 2.0 * (M * K + N * K + M * N)
             ideal = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3
             rows.append({"kernel": "gemm_bf16_mid_m", "M": M, "N": N, "K": K, "plan_bn_splitk": cu.gemm_mid_m_plan(M, N, K),
+                         "us_cluster_bn_x_splitk": sweep,
                          "us": round(ms_auto * 1e3, 2), "us_plain_tiles": round(ms_plain * 1e3, 2),
                          "us_torch_matmul": round(ms_lib * 1e3, 2), "vs_torch": round(ms_lib / ms_auto, 3),
                          "roofline_frac": round(ideal / ms_auto, 3), "tag": tag})

@@ -731,32 +731,38 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------- split-K reduction inside the cluster, operands NOT swapped
     // (129 to about a thousand tokens: too few 128-row tiles to fill the SMs, too many rows for the
     // swapped path). Accumulator row = token, column = output column. Reducer r of the cluster owns
-    // the columns [r*cs, (r+1)*cs) of the tile; every CTA sends it those columns of its partial sums as
-    // [source][column][128 tokens] floats (lanes are consecutive tokens: conflict-free remote stores
-    // and local loads). Same barrier protocol as the swapped variant above.
+    // the columns [r*cs, (r+1)*cs) of the tile; every OTHER CTA sends it those columns of its partial
+    // sums as [source][column / 4][128 tokens][4 columns] floats: one 16-byte remote store per thread
+    // and four columns, a warp writes 512 contiguous bytes (scalar remote stores cost about as much per
+    // instruction and made the exchange the longest phase of the kernel). The reducer's own partial
+    // sums never leave its tensor memory. Same barrier protocol as the swapped variant above.
     __syncwarp();
     cluster_sync_all();
     const uint32_t my_rank = cluster_cta_rank();
     const int cs = ceil_div(BN / 8, splitk) * 8;
     const uint32_t recv0 = smem_u32(smem);
+    const int q = warp & 3;
+    const int trow = q * 32 + lane;  // token row of the tile = this thread's TMEM lane
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     if (warp >= 2 && acc_ready) {
-      const int q = warp & 3;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      const uint32_t row_off = (q * 32 + lane) * 4;
-      int owner = 0, cl = 0;
-      uint32_t dst = cluster_map_shared(recv0, 0) + (my_rank * cs) * 512 + row_off;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
+        // skip the chunk if it lies entirely in this CTA's own slice
+        const int o_first = c0 / cs, o_last = (c0 + 31) / cs;
+        if (o_first == static_cast<int>(my_rank) && o_last == static_cast<int>(my_rank)) continue;
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + c0, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          st_shared_cluster_f32(dst + cl * 512, __uint_as_float(r[j]));
-          if (++cl == cs) {
-            cl = 0;
-            ++owner;
-            if (owner < splitk) dst = cluster_map_shared(recv0, owner) + (my_rank * cs) * 512 + row_off;
+        for (int g = 0; g < 8; ++g) {
+          const int col = c0 + 4 * g;
+          const int owner = col / cs;
+          if (owner != static_cast<int>(my_rank) && owner < splitk) {
+            const int cl = col - owner * cs;
+            const uint32_t dst = cluster_map_shared(recv0, owner) +
+                                 ((my_rank * (cs / 4) + cl / 4) * 128 + trow) * 16;
+            st_shared_cluster_f32x4(dst, __uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                    __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
           }
         }
       }
@@ -764,55 +770,62 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tc_fence_before_sync();
     __syncwarp();
     cluster_sync_all();
+    tc_fence_after_sync();
     if (warp >= 2 && acc_ready) {
       const int tile = blockIdx.x / splitk;
       const TileCoord tc = tile_coord<BN>(tile, num_m, num_n, M, grp, comm);
-      const int t = threadIdx.x - 64;           // token row of the tile
-      const int row = tc.a_row + t;
+      const int row = tc.a_row + trow;
       const int c_begin = my_rank * cs;
       const int c_end = c_begin + cs < BN ? c_begin + cs : BN;
-      if (row < tc.row_end) {
-        for (int c = c_begin; c < c_end; c += 8) {
-          const int col = tc.n_blk * BN + c;
-          if (col >= N) break;
-          float f[8];
-          const uint32_t src = recv0 + ((c - c_begin) * 128 + t) * 4;
+#pragma unroll 1
+      for (int c = c_begin; c < c_end; c += 8) {
+        const int col = tc.n_blk * BN + c;
+        uint32_t own[8];
+        tmem_ld_32x32b_x8(t_row + c, own);   // warp-collective: every lane takes part
+        tmem_ld_wait();
+        if (col < N && row < tc.row_end) {
+        float f[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = ld_shared_f32(src + j * 512);
-          for (int r = 1; r < splitk; ++r) {
+        for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(own[j]);
+        const int cg = (c - c_begin) / 4;
+        for (int r = 0; r < splitk; ++r) {
+          if (r == static_cast<int>(my_rank)) continue;
+          const uint32_t src = recv0 + ((r * (cs / 4) + cg) * 128 + trow) * 16;
+          const float4 a = ld_shared_f32x4(src);
+          const float4 b = ld_shared_f32x4(src + 128 * 16);
+          f[0] += a.x, f[1] += a.y, f[2] += a.z, f[3] += a.w;
+          f[4] += b.x, f[5] += b.y, f[6] += b.z, f[7] += b.w;
+        }
+        const size_t c_off = static_cast<size_t>(row) * ep.ldc + col;
+        if (ep.bias) {
+          const bf16x8 bb8 = ld_bf16x8(ep.bias + col);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] += ld_shared_f32(src + (r * cs + j) * 512);
-          }
-          const size_t c_off = static_cast<size_t>(row) * ep.ldc + col;
-          if (ep.bias) {
-            const bf16x8 b = ld_bf16x8(ep.bias + col);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 bb = unpack_bf16x2(b.u[j]);
-              f[2 * j] += bb.x;
-              f[2 * j + 1] += bb.y;
-            }
-          }
-          if (ep.residual) {
-            const bf16x8 b = ld_bf16x8(ep.residual + c_off);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 bb = unpack_bf16x2(b.u[j]);
-              f[2 * j] += bb.x;
-              f[2 * j + 1] += bb.y;
-            }
-          }
-          if (ep.C_f32 != nullptr) {
-            float4* d4 = reinterpret_cast<float4*>(ep.C_f32 + c_off);
-            d4[0] = make_float4(f[0], f[1], f[2], f[3]);
-            d4[1] = make_float4(f[4], f[5], f[6], f[7]);
-          } else {
-            bf16x8 o;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
-            st_bf16x8(ep.C + c_off, o);
+          for (int j = 0; j < 4; ++j) {
+            const float2 bb = unpack_bf16x2(bb8.u[j]);
+            f[2 * j] += bb.x;
+            f[2 * j + 1] += bb.y;
           }
         }
+        if (ep.residual) {
+          const bf16x8 bb8 = ld_bf16x8(ep.residual + c_off);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 bb = unpack_bf16x2(bb8.u[j]);
+            f[2 * j] += bb.x;
+            f[2 * j + 1] += bb.y;
+          }
+        }
+        if (ep.C_f32 != nullptr) {
+          float4* d4 = reinterpret_cast<float4*>(ep.C_f32 + c_off);
+          d4[0] = make_float4(f[0], f[1], f[2], f[3]);
+          d4[1] = make_float4(f[4], f[5], f[6], f[7]);
+        } else {
+          bf16x8 o;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o.u[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+          st_bf16x8(ep.C + c_off, o);
+        }
+        }  // valid row and column
       }
     }
   }
@@ -1230,7 +1243,7 @@ MidPlan mid_m_plan(int M, int N, int K) {
   const int sms = pxl_host::num_sms();
   MidPlan best{0, 1, 1e300};
   const int bns[2] = {256, 128};
-  const double t_kb[2] = {0.42, 0.30};
+  const double t_kb[2] = {0.43, 0.29};
   for (int i = 0; i < 2; ++i) {
     const int tiles = num_m * pxl::ceil_div(N, bns[i]);
     for (int sk = 1; sk <= 8; ++sk) {
@@ -1239,7 +1252,9 @@ MidPlan mid_m_plan(int M, int N, int K) {
       if (sk > 1 && pxl::ceil_div(num_kb, kb_per) != sk) continue;  // no empty K range
       int slots = sk == 1 ? sms : mid_m_max_clusters(bns[i], sk);
       if (slots <= 0) continue;
-      const double cost = pxl::ceil_div(tiles, slots) * (kb_per * t_kb[i] + (sk > 1 ? 5.0 : 3.0));
+      // fixed part per round: launch, pipeline fill and drain (7 us measured for the plain kernel), plus
+      // the two cluster barriers and the exchange of partial sums for the split variant
+      const double cost = pxl::ceil_div(tiles, slots) * (kb_per * t_kb[i] + (sk > 1 ? 11.0 : 7.0));
       if (cost < best.cost) best = MidPlan{bns[i], sk, cost};
     }
   }

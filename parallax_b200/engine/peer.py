@@ -61,10 +61,22 @@ class PeerExecutor:
         self._gen.manual_seed(seed + 777)
 
     # ------------------------------------------------------------------ shared forward
-    def _run(self, seqs: list[ScheduledSeq], hidden: Optional[torch.Tensor]):
+    def _run(self, seqs: list[ScheduledSeq], hidden_of: Optional[dict]):
+        """Plan and run one batch. ``hidden_of`` (later peers) maps ``id(seq)`` to that sequence's
+        incoming activations: the batch's hidden states are assembled AFTER planning, from the
+        sequences that planning kept, so a decode request dropped for lack of KV memory takes its row
+        with it instead of shifting every row behind it."""
+        on_gpu = self.device.type == "cuda"
+        if on_gpu:
+            from parallax_b200.ops import cuda as _cuda
+
+            _cuda.raise_if_status(self.device)      # word mirrored after the previous batch
         arrays = self.planner.plan_arrays(seqs)
         if arrays is None:
             return None, None
+        hidden = None
+        if hidden_of is not None:
+            hidden = torch.cat([hidden_of[id(s)] for s in arrays["ordered"]], dim=0)
         fb = self.builder.build(arrays["ids"] if self.is_first else None, arrays["pos"], arrays["slots"],
                                 arrays["p_q"], arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"],
                                 arrays["d_tables"], arrays["logit_rows"])
@@ -75,13 +87,17 @@ class PeerExecutor:
                 out = (h, self.worker.model.logits(h, fb) if arrays["owners"] else None)
             else:
                 out = (self.worker.run(fb, hidden), None)
+        if on_gpu:
+            _cuda.status_copy_async(self.device)    # read back with this batch's outputs
         return arrays, out
 
     def _sample(self, logits: torch.Tensor, owners: list[ScheduledSeq]):
         sps = [s.req.sampling_params for s in owners]
         if all(sp.is_greedy for sp in sps):
             ids, lp = ops.argmax(logits, want_logprob=True)
-            return ids.tolist(), lp.exp().tolist()
+            out = ids.tolist(), lp.exp().tolist()
+            self._raise_if_device_error()
+            return out
         dev = logits.device
         t = torch.tensor([0.0 if sp.is_greedy else sp.temperature for sp in sps], dtype=torch.float32, device=dev)
         k = torch.tensor([sp.top_k if sp.top_k > 0 else 0 for sp in sps], dtype=torch.int32, device=dev)
@@ -89,7 +105,16 @@ class PeerExecutor:
         mp = torch.tensor([sp.min_p for sp in sps], dtype=torch.float32, device=dev)
         u = torch.rand(len(sps), generator=self._gen, device=dev, dtype=torch.float32)
         ids, pr = ops.sample(logits, t, k, p, mp, u, want_prob=True)
-        return ids.tolist(), pr.tolist()
+        out = ids.tolist(), pr.tolist()
+        self._raise_if_device_error()
+        return out
+
+    def _raise_if_device_error(self) -> None:
+        """After a synchronising read of a batch's outputs: fail the batch if one of its kernels gave up."""
+        if self.device.type == "cuda":
+            from parallax_b200.ops import cuda as _cuda
+
+            _cuda.raise_if_status(self.device)
 
     def _hidden_packets(self, arrays, h: torch.Tensor) -> list[IntermediateRequest]:
         """One packet per sequence carrying its slice of the stage output."""
@@ -242,7 +267,7 @@ class PeerExecutor:
         the first peer. Requests this peer cannot serve come back as abort packets."""
         assert not self.is_first
         out: list[IntermediateRequest] = []
-        seqs, hidden = [], []
+        seqs = []
         for pk in packets:
             if pk.abort or pk.is_finished:
                 self.release([pk.request_id])
@@ -260,9 +285,8 @@ class PeerExecutor:
             return out
         # plan order is prefill first, then decode: order the hidden states the same way
         seqs.sort(key=lambda sp: 0 if sp[0].is_prefill else 1)
-        for s, pk in seqs:
-            hidden.append(pk.hidden_states.to(device=self.device, dtype=self.worker.dtype))
-        arrays, res = self._run([s for s, _ in seqs], torch.cat(hidden, dim=0))
+        hidden_of = {id(s): pk.hidden_states.to(device=self.device, dtype=self.worker.dtype) for s, pk in seqs}
+        arrays, res = self._run([s for s, _ in seqs], hidden_of)
         for s, pk in seqs:
             if s.req.is_finished:   # KV exhausted while appending a decode slot
                 bad = IntermediateRequest(pk.request_id, pk.current_position, RequestStatus.FINISHED_ABORT,

@@ -180,3 +180,62 @@ def test_scheduler_prefill_cap_spreads_a_prompt_over_batches():
     assert sum(n for batch in seen for is_long, n, p in batch if not is_long and p) == 40
     # once the short prompt is done its decode rows share batches with the long prompt's slices
     assert any(any(p for _, _, p in batch) and any(not p for _, _, p in batch) for batch in seen)
+
+
+def test_nonzero_device_status_fails_the_batch():
+    """A kernel that gave up (here: a faked status word) must not let the step commit tokens: the
+    step raises and the serving loop releases the running requests with an error event."""
+    import time
+
+    from parallax_b200.engine.service import EngineLoop
+    from parallax_b200.ops import KernelError
+
+    cfg = named_config("tiny")
+    eng = Engine(cfg, device="cpu", num_blocks=64, max_batch_size=4)
+    calls = {"n": 0}
+
+    def fake_status():
+        calls["n"] += 1
+        return 105 if calls["n"] == 3 else 0      # the third step reports "wait on a peer flag ran out"
+
+    eng._step_status = fake_status
+    r = Request(input_ids=[1, 2, 3, 4, 5], sampling_params=SamplingParams(max_new_tokens=8, temperature=0.0, ignore_eos=True))
+    eng.add_request(r)
+    eng.step()
+    eng.step()
+    n_before = len(r.output_ids)
+    with pytest.raises(KernelError, match="peer flag"):
+        eng.step()
+    assert len(r.output_ids) == n_before          # nothing of the failed step was committed
+
+    # through the serving loop: the request ends with an ERROR event, the loop keeps running
+    eng2 = Engine(cfg, device="cpu", num_blocks=64, max_batch_size=4)
+    calls2 = {"n": 0}
+
+    def fake_status2():
+        calls2["n"] += 1
+        return 106 if calls2["n"] == 2 else 0
+
+    eng2._step_status = fake_status2
+    loop = EngineLoop(eng2)
+    loop.start()
+    q = loop.submit(Request(input_ids=[7, 8, 9], sampling_params=SamplingParams(max_new_tokens=20, temperature=0.0, ignore_eos=True)))
+    evs = []
+    t0 = time.time()
+    while time.time() - t0 < 30:
+        ev = q.get(timeout=30)
+        evs.append(ev)
+        if ev.finished:
+            break
+    assert evs[-1].finished and evs[-1].error and "index out of range" in evs[-1].error
+    # a new request after the failure is served normally
+    q2 = loop.submit(Request(input_ids=[3, 4], sampling_params=SamplingParams(max_new_tokens=3, temperature=0.0, ignore_eos=True)))
+    toks = []
+    while True:
+        ev = q2.get(timeout=30)
+        if ev.token_id is not None:
+            toks.append(ev.token_id)
+        if ev.finished:
+            break
+    loop.stop()
+    assert len(toks) == 3 and ev.error is None

@@ -100,3 +100,35 @@ def test_peer_without_the_prefix_aborts_the_request():
     assert back and back[0].abort
     events, releases = first.receive_tokens(_wire(back))
     assert again.is_finished and releases == [again.request_id]
+
+
+def test_later_peer_out_of_kv_drops_only_that_request():
+    """The second peer runs out of KV blocks while decoding: the request that cannot get a block is
+    aborted, and the requests behind it in the batch keep their own activations (same tokens as an
+    engine with enough memory)."""
+    cfg = named_config("tiny")
+    prompts = _prompts(3, 15, cfg.vocab_size, seed=11)      # one 16-token page each
+    sp = dict(max_new_tokens=6, temperature=0.0, ignore_eos=True)
+    want = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=8).generate(prompts, SamplingParams(**sp))
+    peers = [PeerExecutor(cfg, 0, 2, device="cpu", node_id="n0", num_blocks=128, max_batch_size=8),
+             PeerExecutor(cfg, 2, 4, device="cpu", node_id="n1", num_blocks=5, max_batch_size=8, enable_prefix_cache=False)]
+    table = [p.node_id for p in peers]
+    reqs = [Request(input_ids=p, routing_table=table, sampling_params=SamplingParams(**sp)) for p in prompts]
+    for r in reqs:
+        peers[0].add_request(r)
+    steps = 0
+    while peers[0].has_work() and steps < 100:
+        steps += 1
+        packets, _events, releases = peers[0].step_first()
+        peers[1].release(releases)
+        back = peers[1].process_packets(_wire(packets))
+        _events, releases = peers[0].receive_tokens(_wire([p for p in back if p.hidden_states is None]))
+        peers[1].release(releases)
+    aborted = [r for r in reqs if r.status.value == "FINISHED_ABORT"]
+    done = [r for r in reqs if r.status.value == "FINISHED_MAX_LENGTH"]
+    assert len(aborted) == 1 and len(done) == 2, [r.status for r in reqs]
+    for r in done:
+        assert r.output_ids == want[reqs.index(r)]
+    # the aborted request produced correct tokens up to the point where it was dropped
+    a = aborted[0]
+    assert a.output_ids == want[reqs.index(a)][:len(a.output_ids)]
