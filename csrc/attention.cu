@@ -324,6 +324,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kDecStages);
   const uint32_t full0 = smem_u32(bars);
   const uint32_t empty0 = smem_u32(bars + kDecStages);
+  pdl_wait();
+  pdl_launch_dependents();
 
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int G = Hq / Hkv;
@@ -540,6 +542,8 @@ template <int D>
 __global__ void __launch_bounds__(D)
 attn_decode_reduce_kernel(const float* __restrict__ workspace, const float* __restrict__ sinks,
                           bf16* __restrict__ out, int Hq, int num_splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const float* po = workspace;
   const float* plse = workspace + static_cast<size_t>(gridDim.y) * Hq * num_splits * D;
@@ -774,27 +778,29 @@ PXL_EXPORT int pxl_attn_decode(const void* q, int64_t q_stride, const void* k_ca
         !pxl_host::make_tmap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v_cache, rows, 128, 128, page_size, 64))
       return PXL_ERR_TENSORMAP;
     constexpr int SMEM = 1024 + kDecStages * 2 * TILE * 128 * 2 + 128;
-    static bool done = false;
-    if (!done) {
+    static bool done[64] = {false};      // function attributes are per device
+    const int dev = pxl_host::current_device_slot();
+    if (!done[dev]) {
       if (set_smem(attn_decode_tma_kernel, SMEM)) return PXL_ERR_CUDA;
-      done = true;
+      done[dev] = true;
     }
-    attn_decode_tma_kernel<<<grid, kDecThreads, SMEM, stream>>>(
+    pxl_host::launch(attn_decode_tma_kernel, grid, kDecThreads, SMEM, stream,
         tk, tv, static_cast<const bf16*>(q), q_stride, block_tables, ctx_lens, static_cast<bf16*>(out), workspace,
         sinks, Hq, Hkv, page_size, max_blocks, num_blocks, scale_log2, window, num_splits, status);
     if (num_splits > 1)
-      attn_decode_reduce_kernel<128><<<dim3(Hq, B), 128, 0, stream>>>(workspace, sinks, static_cast<bf16*>(out), Hq,
-                                                                      num_splits);
+      pxl_host::launch(attn_decode_reduce_kernel<128>, dim3(Hq, B), 128, 0, stream, workspace, sinks,
+                       static_cast<bf16*>(out), Hq, num_splits);
     return check_launch();
   }
 #define PXL_DEC(DD)                                                                              \
   {                                                                                              \
     constexpr int SMEM = 4 * TILE * DD * 2 > (4 * 16 * DD + 128) * 4 ? 4 * TILE * DD * 2         \
                                                                      : (4 * 16 * DD + 128) * 4;  \
-    static bool done = false;                                                                    \
-    if (!done) {                                                                                 \
+    static bool done[64] = {false};                                                              \
+    const int dev = pxl_host::current_device_slot();                                                       \
+    if (!done[dev]) {                                                                            \
       if (set_smem(attn_decode_kernel<DD>, SMEM)) return PXL_ERR_CUDA;                           \
-      done = true;                                                                               \
+      done[dev] = true;                                                                          \
     }                                                                                            \
     attn_decode_kernel<DD><<<grid, 128, SMEM, stream>>>(                                         \
         static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(k_cache),                \
@@ -827,10 +833,11 @@ PXL_EXPORT int pxl_attn_prefill(const void* q, int64_t q_stride, const void* k_c
 #define PXL_PRE(DD)                                                                              \
   {                                                                                              \
     constexpr int SMEM = 4 * TILE * DD * 2;                                                      \
-    static bool done = false;                                                                    \
-    if (!done) {                                                                                 \
+    static bool done[64] = {false};                                                              \
+    const int dev = pxl_host::current_device_slot();                                             \
+    if (!done[dev]) {                                                                            \
       if (set_smem(attn_prefill_kernel<DD>, SMEM)) return PXL_ERR_CUDA;                          \
-      done = true;                                                                               \
+      done[dev] = true;                                                                          \
     }                                                                                            \
     attn_prefill_kernel<DD><<<grid, 128, SMEM, stream>>>(                                        \
         static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(k_cache),                \

@@ -82,6 +82,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                  o_full = bar0 + 64;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  pdl_wait();
+  pdl_launch_dependents();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, head = blockIdx.y;
@@ -411,7 +413,7 @@ PXL_EXPORT int pxl_attn_prefill_tc(const void* q, int64_t q_stride, const void* 
     configured[dev] = true;
   }
   dim3 grid(pxl::ceil_div(max_q_len, kQ), Hq, B);
-  attn_prefill_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(
+  pxl_host::launch(attn_prefill_tc_kernel, grid, kThreads, kSmemBytes, stream,
       tq, tk, tv, block_tables, cu_q, ctx_lens, static_cast<pxl::bf16*>(out), out_stride, sinks, Hq, Hkv, page_size,
       max_blocks, num_blocks, scale * kLog2eF, window, status);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;

@@ -426,6 +426,17 @@ __device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t
   }
 }
 
+// --- programmatic dependent launch ------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still draining. pdl_wait() blocks until that kernel has
+// completed and its writes are visible (a no-op for launches without the attribute), so it must
+// run before the first access to global memory that an earlier kernel wrote or still reads.
+// pdl_launch_dependents() lets the next kernel of the stream begin its own prologue early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // --- legacy tensor path used by the attention kernels ------------------------
 __device__ __forceinline__ void mma_m16n8k16_bf16(float (&d)[4], const uint32_t (&a)[4],
                                                   const uint32_t (&b)[2]) {
@@ -462,6 +473,36 @@ __device__ __forceinline__ void cp_async_wait() {
 // host helpers
 // ---------------------------------------------------------------------------
 namespace pxl_host {
+
+// Launches issued by this thread while the flag is set carry the programmatic-stream-serialization
+// attribute (the stage executor sets it around a layer sequence whose kernels all call pdl_wait()).
+inline bool& pdl_flag() {
+  static thread_local bool on = false;
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_flag() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// Index of the current device into per-device caches of up to 64 entries.
+inline int current_device_slot() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev < 0 || dev >= 64) ? 0 : dev;
+}
 
 inline int num_sms() {
   static int cached[64] = {0};

@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ out,
                bf16* __restrict__ residual, int H, float eps, float w_offset) {
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t row = blockIdx.x;
   const bf16* xr = x + row * H;
   bf16* rr = HAS_RES ? residual + row * H : nullptr;
@@ -64,6 +66,8 @@ template <bool HAS_RES, int NV>
 __global__ void __launch_bounds__(256)
 rmsnorm_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ out,
                     bf16* __restrict__ residual, int T, int H, float eps, float w_offset) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= T) return;
@@ -172,6 +176,8 @@ qk_norm_rope_cache_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ q_nor
                           int* status) {
   constexpr int EPL = D / 32;  // elements per lane
   __shared__ float sh[8][D];
+  pdl_wait();
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = Hq + 2 * Hkv;
   const int64_t gw = static_cast<int64_t>(blockIdx.x) * 8 + warp;
@@ -354,9 +360,9 @@ PXL_EXPORT int pxl_rmsnorm(const void* x, const void* weight, void* out, void* r
 #define PXL_RMS_WARP(NV)                                                                          \
   do {                                                                                            \
     if (residual)                                                                                 \
-      rmsnorm_warp_kernel<true, NV><<<grid, 256, 0, stream>>>(xp, wp, op, rp, T, H, eps, w_offset); \
+      pxl_host::launch(rmsnorm_warp_kernel<true, NV>, grid, 256, 0, stream, xp, wp, op, rp, T, H, eps, w_offset); \
     else                                                                                          \
-      rmsnorm_warp_kernel<false, NV><<<grid, 256, 0, stream>>>(xp, wp, op, rp, T, H, eps, w_offset); \
+      pxl_host::launch(rmsnorm_warp_kernel<false, NV>, grid, 256, 0, stream, xp, wp, op, rp, T, H, eps, w_offset); \
   } while (0)
     if (H <= 2048) PXL_RMS_WARP(8);
     else if (H <= 4096) PXL_RMS_WARP(16);
@@ -365,9 +371,9 @@ PXL_EXPORT int pxl_rmsnorm(const void* x, const void* weight, void* out, void* r
     return check_launch();
   }
   if (residual)
-    rmsnorm_kernel<true><<<T, 256, 0, stream>>>(xp, wp, op, rp, H, eps, w_offset);
+    pxl_host::launch(rmsnorm_kernel<true>, T, 256, 0, stream, xp, wp, op, rp, H, eps, w_offset);
   else
-    rmsnorm_kernel<false><<<T, 256, 0, stream>>>(xp, wp, op, nullptr, H, eps, w_offset);
+    pxl_host::launch(rmsnorm_kernel<false>, T, 256, 0, stream, xp, wp, op, static_cast<bf16*>(nullptr), H, eps, w_offset);
   return check_launch();
 }
 
@@ -391,7 +397,7 @@ PXL_EXPORT int pxl_qk_norm_rope_cache(void* qkv, const void* q_norm_w, const voi
   const int64_t warps = static_cast<int64_t>(T) * (Hq + 2 * Hkv);
   const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
 #define PXL_QKROPE(DD)                                                                        \
-  qk_norm_rope_cache_kernel<DD><<<grid, 256, 0, stream>>>(                                    \
+  pxl_host::launch(qk_norm_rope_cache_kernel<DD>, grid, 256, 0, stream,                        \
       static_cast<bf16*>(qkv), static_cast<const bf16*>(q_norm_w),                            \
       static_cast<const bf16*>(k_norm_w), cos_sin, positions, slot_mapping,                   \
       static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), T, Hq, Hkv, rot_dim,          \

@@ -171,6 +171,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // them work on the first tiles first; one flag per chunk tells the producer what landed.
     __shared__ uint64_t cbar[3];
     __shared__ int c_abort;
+    pdl_wait();
+    pdl_launch_dependents();
     if (warp != 0) return;
     const int c = blockIdx.x - gemm_ctas;
     if (lane == 0) {
@@ -293,6 +295,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched only this CTA's shared and tensor memory: with a programmatic dependent
+  // launch it overlaps the tail of the previous kernel, whose results are needed from here on
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -933,7 +939,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue
     grid = grid + comm.ag_ncopy <= pxl_host::num_sms() ? grid + comm.ag_ncopy : pxl_host::num_sms();
     if (grid <= comm.ag_ncopy) return PXL_ERR_INVALID_ARG;
   }
-  kern<<<grid, kGemmThreads, gemm_smem_bytes<BN, EPI>(), stream>>>(ta, tb, ep, grp, comm, M, N, K, status);
+  pxl_host::launch(kern, grid, kGemmThreads, gemm_smem_bytes<BN, EPI>(), stream, ta, tb, ep, grp, comm, M, N, K, status);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
 }
 
@@ -957,13 +963,15 @@ int launch_gemm_cluster(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = (pxl_host::pdl_flag() && max_clusters == nullptr) ? 2 : 1;
   if (max_clusters != nullptr) {
     cfg.gridDim = dim3(static_cast<unsigned>(cluster) * 64u, 1, 1);  // the query only needs a legal grid
     int n = 0;
@@ -1229,9 +1237,14 @@ int mid_m_max_clusters(int bn, int cluster) {
   return cache[dev][bi][cluster];
 }
 
-// Cost model (microseconds) of one launch: rounds of co-resident clusters x (k-blocks per CTA x time of
-// one 64-deep k-block at this tile width + fixed cost of the cluster exchange). The k-block times are
-// the measured steady-state rates of the plain kernel (a 128 x 256 tile keeps the tensor pipe busiest).
+// Cost model (microseconds) of one launch, fitted to CUDA-event timings of the four Qwen3-8B projection
+// shapes at 192 / 320 / 512 rows (weights streamed from HBM):
+//   plain persistent kernel   rounds x (k-blocks x t_kb) + 7
+//   cluster split-K           k-blocks per CTA x t_kb + 8 + splitk x bn / 128   (exchange of partial sums)
+// t_kb = time of one 64-deep k-block per CTA, set by what the SM can pull from L2 (48 KB per k-block for a
+// 128 x 256 tile, 32 KB for 128 x 128). Split variants are only considered when all clusters are resident at
+// once (a second round pays the fixed cost again and was always slower) and for 2 or 4 K ranges (clusters of
+// 3 pack the GPCs badly: 144 CTAs in clusters of 3 ran as slowly as two rounds).
 struct MidPlan {
   int bn, splitk;
   double cost;
@@ -1246,15 +1259,14 @@ MidPlan mid_m_plan(int M, int N, int K) {
   const double t_kb[2] = {0.43, 0.29};
   for (int i = 0; i < 2; ++i) {
     const int tiles = num_m * pxl::ceil_div(N, bns[i]);
-    for (int sk = 1; sk <= 8; ++sk) {
-      if (sk > 1 && num_kb / sk < 4) break;
+    const double plain = pxl::ceil_div(tiles, sms) * (num_kb * t_kb[i]) + 7.0;
+    if (plain < best.cost) best = MidPlan{bns[i], 1, plain};
+    for (int sk = 2; sk <= 4; sk += 2) {
+      if (num_kb / sk < 4) break;
       const int kb_per = pxl::ceil_div(num_kb, sk);
-      if (sk > 1 && pxl::ceil_div(num_kb, kb_per) != sk) continue;  // no empty K range
-      int slots = sk == 1 ? sms : mid_m_max_clusters(bns[i], sk);
-      if (slots <= 0) continue;
-      // fixed part per round: launch, pipeline fill and drain (7 us measured for the plain kernel), plus
-      // the two cluster barriers and the exchange of partial sums for the split variant
-      const double cost = pxl::ceil_div(tiles, slots) * (kb_per * t_kb[i] + (sk > 1 ? 11.0 : 7.0));
+      if (pxl::ceil_div(num_kb, kb_per) != sk) continue;  // no empty K range
+      if (tiles > mid_m_max_clusters(bns[i], sk)) continue;
+      const double cost = kb_per * t_kb[i] + 8.0 + sk * (bns[i] / 128);
       if (cost < best.cost) best = MidPlan{bns[i], sk, cost};
     }
   }
@@ -1337,6 +1349,7 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
     if (plan > 0 && (plan & 15) > 1)
       return gemm_mid_m(A, W, C, epi == PXL_EPI_F32, epi == PXL_EPI_RESIDUAL ? residual : nullptr, bias, M, N, K, lda,
                         ldw, ldc, plan >> 4, plan & 15, status, stream);
+    if (plan > 0) bn = plan >> 4;
   }
   if (bn == 0) bn = pxl_gemm_bf16_pick_bn(M, N, epi);
   if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;

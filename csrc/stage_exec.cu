@@ -110,6 +110,14 @@ PXL_EXPORT int pxl_stage_forward_dense(const PxlStageDesc* st, const PxlStepDesc
     splits = pxl_attn_decode_splits(sp->Bd, Hkv, sp->d_max_ctx);
     if (splits > 1 && static_cast<int64_t>(sp->Bd) * Hq * splits * (D + 2) > ws->decode_floats) return PXL_ERR_TOO_LARGE;
   }
+  // every kernel of the sequence waits (griddepcontrol.wait) before it touches global memory, so each
+  // launch may overlap its prologue with the tail of the kernel before it
+  static const bool no_pdl = getenv("PXL_NO_PDL") != nullptr;
+  struct PdlScope {
+    bool prev;
+    explicit PdlScope(bool on) : prev(pxl_host::pdl_flag()) { pxl_host::pdl_flag() = on; }
+    ~PdlScope() { pxl_host::pdl_flag() = prev; }
+  } pdl_scope(!no_pdl && !stage_debug());
   for (int li = 0; li < st->n_layers; ++li) {
     const PxlDenseLayer& L = st->layers[li];
     int op_ = 0;  // 1 norm, 2 qkv, 3 rope+cache, 4 prefill, 5 decode (4 if no prefill), then o_proj, norm, gate_up, down
