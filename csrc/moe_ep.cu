@@ -103,6 +103,10 @@ struct EpCombPtrs {
   bf16* comb[8];  // rank s: [rows][k][H]
 };
 
+struct EpRetFlags {
+  uint32_t* ret[8];  // rank r: [ep] return flags
+};
+
 __global__ void __launch_bounds__(256) ep_row_ptrs_kernel(const int* __restrict__ src_slot, const int* __restrict__ n_rows,
                                                           const int* __restrict__ recv_meta, int cap, int H,
                                                           const EpCombPtrs comb, bf16** __restrict__ row_ptrs,
@@ -167,7 +171,53 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const bf16* __restrict_
   }
 }
 
+// Return trip as a kernel of its own (used when the down projection cannot store through row pointers,
+// e.g. the block-scaled fp8 grouped GEMM): row p of the expert-sorted result goes to row_ptrs[p]; the CTA
+// that finishes last raises the return flag of every peer.
+__global__ void __launch_bounds__(256) ep_return_rows_kernel(const bf16* __restrict__ y, int64_t ldy,
+                                                             bf16* const* __restrict__ row_ptrs,
+                                                             const int* __restrict__ n_rows, int max_rows, int H,
+                                                             EpRetFlags flags, uint32_t* __restrict__ done_counter,
+                                                             int rank, int ep, uint32_t epoch) {
+  const int n = min(*n_rows, max_rows);
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; p < n; p += warps) {
+    bf16* dst = row_ptrs[p];
+    if (dst == nullptr) continue;
+    const bf16* src = y + static_cast<size_t>(p) * ldy;
+    for (int c = lane; c < H / 8; c += 32) st_bf16x8(dst + c * 8, ld_bf16x8(src + c * 8));
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t old = atomicAdd(done_counter, 1u);
+    if (old == gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < ep; ++r) st_release_sys_u32(flags.ret[r] + rank, epoch);
+    }
+  }
+}
+
 }  // namespace
+
+// y [>= *n_rows, H] expert-sorted rows (row stride ldy); row_ptrs as written by pxl_ep_row_ptrs; flag_ptrs[r]:
+// rank r's return-flag array; done_counter: local scratch, zero on entry (left zero).
+PXL_EXPORT int pxl_ep_return_rows(const void* y, int64_t ldy, void* const* row_ptrs, const int* n_rows, int max_rows,
+                                  int H, void* const* flag_ptrs, uint32_t* done_counter, int rank, int ep,
+                                  uint32_t epoch, cudaStream_t stream) {
+  if (ep < 1 || ep > 8 || rank < 0 || rank >= ep || H % 8 || ldy % 8 || max_rows <= 0) return PXL_ERR_INVALID_ARG;
+  EpRetFlags f{};
+  for (int i = 0; i < ep; ++i) f.ret[i] = static_cast<uint32_t*>(flag_ptrs[i]);
+  int grid = pxl::ceil_div(max_rows, 8);
+  const int max_grid = 2 * pxl_host::num_sms();
+  if (grid > max_grid) grid = max_grid;
+  ep_return_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const pxl::bf16*>(y), ldy,
+                                                  reinterpret_cast<pxl::bf16* const*>(row_ptrs), n_rows, max_rows, H, f,
+                                                  done_counter, rank, ep, epoch);
+  return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
+}
 
 // x [n_rows, H] (row stride ldx), ids [n_rows, k] global expert ids. recv_x_ptrs / recv_meta_ptrs /
 // recv_cnt_ptrs / flag_ptrs: per-rank peer-mapped addresses of the receive regions. cursor [ep] and

@@ -37,7 +37,8 @@ class StageWorker:
                  page_size: int = 16, num_blocks: Optional[int] = None, kv_fraction: float = 0.8,
                  max_kv_tokens: Optional[int] = None, seed: int = 0, weights: Optional[dict] = None,
                  max_positions: Optional[int] = None, tp_rank: int = 0, tp_size: int = 1,
-                 tp_group=None, num_linear_slots: int = 0, comm=None):
+                 tp_group=None, num_linear_slots: int = 0, comm=None, ep_rank: int = 0, ep_size: int = 1,
+                 ep_comm=None, ep_local_init: bool = False):
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
@@ -45,7 +46,8 @@ class StageWorker:
         self.page_size = page_size
         self.model = build_stage(cfg, start_layer, end_layer, self.device, self.dtype,
                                  max_positions=max_positions, tp_rank=tp_rank, tp_size=tp_size,
-                                 tp_group=tp_group, comm=comm)
+                                 tp_group=tp_group, comm=comm, ep_rank=ep_rank, ep_size=ep_size, ep_comm=ep_comm,
+                                 ep_local_init=ep_local_init)
         if weights is not None:
             self.model.load_weights(weights)
         else:

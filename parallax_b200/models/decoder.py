@@ -38,7 +38,10 @@ class LayerWeights:
         self.window = 0
 
 
-class DecoderStage:
+from parallax_b200.models.moe import ExpertParallelMixin  # noqa: E402
+
+
+class DecoderStage(ExpertParallelMixin):
     def __init__(self, cfg: ModelConfig, start_layer: int, end_layer: int, device, dtype=None,
                  max_positions: Optional[int] = None):
         self.cfg = cfg
@@ -106,7 +109,9 @@ class DecoderStage:
             if cfg.layer_is_moe(gi):
                 from parallax_b200.models.moe import MoEWeights
 
-                lw.moe = MoEWeights.random(cfg, dev, dt, lambda *sh, k: rnd(*sh, layer_seed=s + 10 + k))
+                lw.moe = MoEWeights.random(cfg, dev, dt, lambda *sh, k: rnd(*sh, layer_seed=s + 10 + k),
+                                           expert_shard=self._ep_shard_arg())
+                self._ep_finish(lw.moe)
             else:
                 wg = rnd(I, H, layer_seed=s + 6)
                 wu = rnd(I, H, layer_seed=s + 7)
@@ -156,6 +161,7 @@ class DecoderStage:
                 from parallax_b200.models.moe import MoEWeights
 
                 lw.moe = MoEWeights.from_hf(cfg, tensors, p + "mlp.", dev, dt)
+                self._ep_finish(lw.moe)
             else:
                 lw.w_gu = ops.interleave_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"))
                 lw.w_down = get(p + "mlp.down_proj.weight").contiguous()
@@ -300,6 +306,11 @@ class DecoderStage:
     def forward(self, fb: ForwardBatch, hidden: Optional[torch.Tensor] = None) -> torch.Tensor:
         """First stage: ``hidden`` is ignored and tokens are embedded. Returns hidden states
         ``[T, H]`` (non-last stage) or logits ``[num_logits, V]`` (last stage)."""
+        if fb.num_tokens == 0:
+            # expert parallelism with data-parallel attention: no token on this rank in this step
+            self.ep_idle_step()
+            n_out = self.cfg.vocab_size if self.is_last else self.cfg.hidden_size
+            return torch.empty((0, n_out), dtype=self.dtype, device=self.device)
         h = self.embed_tokens(fb) if self.is_first else hidden
         h = self.forward_layers(h, fb)
         if self.is_last:

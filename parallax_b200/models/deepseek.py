@@ -126,12 +126,16 @@ class DeepseekStage(DecoderStage):
             if cfg.layer_is_moe(gi):
                 from parallax_b200.models.moe import MoEWeights
 
-                lw.moe = MoEWeights.random(cfg, dev, dt, lambda *sh, k: rnd(*sh, layer_seed=s + 10 + k))
+                lw.moe = MoEWeights.random(cfg, dev, dt, lambda *sh, k: rnd(*sh, layer_seed=s + 10 + k),
+                                           expert_shard=self._ep_shard_arg())
+                self._ep_finish(lw.moe)
             else:
                 lw.w_gu = ops.interleave_gate_up(rnd(I, Hd, layer_seed=s + 6), rnd(I, Hd, layer_seed=s + 7))
                 lw.w_down = rnd(Hd, I, layer_seed=s + 8)
+            if cfg.quant_method == "fp8":
+                self._quantize_layer(lw)      # layer by layer: the bf16 copy of a 671B model never exists at once
         if cfg.quant_method == "fp8":
-            self.quantize_fp8()
+            self.fp8 = True
 
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
         cfg, dev, dt = self.cfg, self.device, self.dtype
@@ -178,6 +182,7 @@ class DeepseekStage(DecoderStage):
                 from parallax_b200.models.moe import MoEWeights
 
                 lw.moe = MoEWeights.from_hf(cfg, tensors, p + "mlp.", dev, dt)
+                self._ep_finish(lw.moe)
             else:
                 lw.w_gu = ops.interleave_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"))
                 lw.w_down = get(p + "mlp.down_proj.weight").contiguous()
@@ -187,16 +192,20 @@ class DeepseekStage(DecoderStage):
     def quantize_fp8(self) -> None:
         """Keep the large projections (q_b, o, dense FFN, experts) as block-scaled e4m3; the narrow
         down-projections into the latents, norms, router and embeddings stay bf16."""
+        for lw in self.layers:
+            self._quantize_layer(lw)
+        self.fp8 = True
+
+    @staticmethod
+    def _quantize_layer(lw) -> None:
         from parallax_b200.loader.quant import quantize_fp8_block
 
-        for lw in self.layers:
-            for name in ("w_q_b", "w_o", "w_gu", "w_down"):
-                w = getattr(lw, name)
-                if isinstance(w, torch.Tensor) and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
-                    setattr(lw, name, quantize_fp8_block(w, (64, 128)))
-            if lw.moe is not None and lw.moe.fp8 is None:
-                lw.moe.quantize_fp8()
-        self.fp8 = True
+        for name in ("w_q_b", "w_o", "w_gu", "w_down"):
+            w = getattr(lw, name)
+            if isinstance(w, torch.Tensor) and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+                setattr(lw, name, quantize_fp8_block(w, (64, 128)))
+        if lw.moe is not None and lw.moe.fp8 is None:
+            lw.moe.quantize_fp8()
 
     @staticmethod
     def _lin(x, w, residual=None, epi=ops.EPI_NONE):

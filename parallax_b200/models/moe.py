@@ -21,6 +21,32 @@ from parallax_b200 import ops
 from parallax_b200.models.config import ModelConfig
 
 
+class ExpertParallelMixin:
+    """Stage-side switch for expert parallelism with data-parallel attention: every rank of the group
+    keeps the whole attention stack and ``E / ep`` experts of each MoE layer, and runs its own token rows."""
+
+    ep_rank, ep_size, ep_comm, ep_local_init = 0, 1, None, False
+
+    def set_expert_parallel(self, rank: int, size: int, comm, local_init: bool = False) -> None:
+        """Call before the weights are created. ``local_init``: random initialisation generates only this
+        rank's experts (for models whose full expert set does not fit one device)."""
+        self.ep_rank, self.ep_size, self.ep_comm, self.ep_local_init = rank, size, comm, local_init
+
+    def _ep_shard_arg(self):
+        return (self.ep_rank, self.ep_size) if self.ep_size > 1 and self.ep_local_init else None
+
+    def _ep_finish(self, moe: "MoEWeights") -> None:
+        if self.ep_size > 1:
+            moe.shard_experts(self.ep_rank, self.ep_size)
+            moe.ep = self.ep_comm
+
+    def ep_idle_step(self) -> None:
+        """A step in which this rank has no token: it still takes part in every MoE layer's exchange."""
+        for lw in self.layers:
+            if getattr(lw, "moe", None) is not None and lw.moe.ep is not None:
+                lw.moe.idle(self.device, self.dtype)
+
+
 class MoEWeights:
     def __init__(self, cfg: ModelConfig):
         self.cfg = cfg
@@ -41,6 +67,10 @@ class MoEWeights:
         self.num_experts = cfg.num_experts
         self.top_k = cfg.num_experts_per_tok
         self.mode = 1 if cfg.scoring_func == "sigmoid" else 0
+        self.experts_per_rank = cfg.num_experts
+        # expert parallelism with data-parallel attention: set to the group's exchange object
+        # (parallax_b200.parallel.ep.EPComm); the local expert weights then hold `experts_per_rank` experts
+        self.ep = None
 
     def tensors(self):
         ts = [t for t in (self.router, self.e_bias, self.w1, self.w2, self.shared_gu, self.shared_down,
@@ -56,9 +86,21 @@ class MoEWeights:
         if E % ep:
             raise ValueError("the number of experts must divide by the expert-parallel size")
         epr = E // ep
-        n1, n2 = self.w1.shape[0] // E, self.w2.shape[0] // E
-        self.w1 = self.w1[rank * epr * n1:(rank + 1) * epr * n1].contiguous()
-        self.w2 = self.w2[rank * epr * n2:(rank + 1) * epr * n2].contiguous()
+        if self.experts_per_rank == epr:      # already built with this rank's experts only
+            return epr
+
+        def rows(t):
+            n = t.shape[0] // E
+            return t[rank * epr * n:(rank + 1) * epr * n].contiguous()
+
+        for name in ("w1", "w2", "b1", "b2"):
+            t = getattr(self, name)
+            if t is not None:
+                setattr(self, name, rows(t))
+        if self.fp8 is not None:
+            for name in ("w1", "w2"):
+                q, sc = self.fp8[name]
+                self.fp8[name] = (rows(q), rows(sc))
         self.experts_per_rank = epr
         return epr
 
@@ -85,12 +127,21 @@ class MoEWeights:
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def random(cls, cfg: ModelConfig, device, dtype, rnd: Callable) -> "MoEWeights":
+    def random(cls, cfg: ModelConfig, device, dtype, rnd: Callable, expert_shard=None) -> "MoEWeights":
+        """``expert_shard=(rank, ep)``: generate only that rank's experts (models whose full expert set
+        does not fit one device). The values then differ from a slice of the unsharded generation."""
         m = cls(cfg)
-        E, H, I = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
-        m.router = rnd(E, H, k=0)
+        E_all, H, I = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
+        m.router = rnd(E_all, H, k=0)
         if cfg.moe_router_bias:
-            m.e_bias = torch.zeros(E, device=device, dtype=torch.float32)
+            m.e_bias = torch.zeros(E_all, device=device, dtype=torch.float32)
+        E = E_all
+        shared_rnd = rnd          # router, router bias and shared expert are replicated: same on every rank
+        if expert_shard is not None:
+            r, ep = expert_shard
+            E = E_all // ep
+            m.experts_per_rank = E
+            rnd = lambda *sh, k: shared_rnd(*sh, k=k + 100 * (r + 1))  # noqa: E731
         g = rnd(E * I, H, k=1).view(E, I, H)
         u = rnd(E * I, H, k=2).view(E, I, H)
         if m.act_mode == 0:
@@ -98,12 +149,12 @@ class MoEWeights:
         else:
             m.w1 = torch.cat([g, u], dim=1).reshape(E * 2 * I, H).contiguous()
             m.b1, m.b2 = rnd(E * 2 * I, k=7), rnd(E * H, k=8)
-            m.router_bias = rnd(E, k=9)
+            m.router_bias = shared_rnd(E_all, k=9)
         m.w2 = rnd(E * H, I, k=3)
         Is = cfg.shared_expert_intermediate_size or (cfg.n_shared_experts * I)
         if Is:
-            m.shared_gu = ops.interleave_gate_up(rnd(Is, H, k=4), rnd(Is, H, k=5))
-            m.shared_down = rnd(H, Is, k=6)
+            m.shared_gu = ops.interleave_gate_up(shared_rnd(Is, H, k=4), shared_rnd(Is, H, k=5))
+            m.shared_down = shared_rnd(H, Is, k=6)
         return m
 
     @classmethod
@@ -178,6 +229,13 @@ class MoEWeights:
         return m
 
     # ------------------------------------------------------------------ forward
+    def idle(self, device, dtype) -> None:
+        H, k = self.cfg.hidden_size, self.top_k
+        xn = torch.empty((0, H), dtype=dtype, device=device)
+        ids = torch.empty((0, k), dtype=torch.int32, device=device)
+        w = torch.empty((0, k), dtype=torch.float32, device=device)
+        self.ep.moe_ffn(self, xn, ids, w, base=None)
+
     def route(self, xn: torch.Tensor):
         cfg = self.cfg
         logits = ops.linear(xn, self.router, bias=self.router_bias, epi=ops.EPI_F32)
@@ -193,6 +251,8 @@ class MoEWeights:
             if "shared_gu" in f:
                 act = ops.linear_fp8(xn, *f["shared_gu"], epi=ops.EPI_SILU_MUL)
                 base = ops.linear_fp8(act, *f["shared_down"], residual=h)
+            if self.ep is not None:
+                return self.ep.moe_ffn(self, xn, ids, w, base=base)
             return ops.moe_ffn_fp8(xn, ids, w, *f["w1"], *f["w2"], self.num_experts, base=base)
         if self.shared_gu is not None:
             act = ops.linear(xn, self.shared_gu, epi=ops.EPI_SILU_MUL)
@@ -201,6 +261,8 @@ class MoEWeights:
             else:
                 gate = torch.sigmoid(xn.float() @ self.shared_gate.float().t()).to(h.dtype)  # [T, 1]: too thin for a tile
                 base = h + gate * ops.linear(act, self.shared_down)
+        if self.ep is not None:
+            return self.ep.moe_ffn(self, xn, ids, w, base=base)
         if self.act_mode:
             return ops.moe_ffn(xn, ids, w, self.w1, self.w2, self.num_experts, base=base, act_mode=self.act_mode,
                                limit=self.limit, b1=self.b1, b2=self.b2)

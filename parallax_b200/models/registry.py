@@ -49,8 +49,22 @@ def family_of(arch: str) -> str:
 
 
 def build_stage(cfg: ModelConfig, start_layer: int, end_layer: int, device, dtype, max_positions=None,
-                tp_rank: int = 0, tp_size: int = 1, tp_group=None, comm=None):
+                tp_rank: int = 0, tp_size: int = 1, tp_group=None, comm=None, ep_rank: int = 0, ep_size: int = 1,
+                ep_comm=None, ep_local_init: bool = False):
+    stage = _build_stage(cfg, start_layer, end_layer, device, dtype, max_positions, tp_rank, tp_size, tp_group, comm)
+    if ep_size > 1:
+        if not cfg.is_moe or not hasattr(stage, "set_expert_parallel") or family_of(cfg.architecture) not in ("decoder", "deepseek"):
+            raise ValueError(f"expert parallelism is not available for {cfg.architecture}")
+        stage.set_expert_parallel(ep_rank, ep_size, ep_comm, ep_local_init)
+    return stage
+
+
+def _build_stage(cfg: ModelConfig, start_layer: int, end_layer: int, device, dtype, max_positions, tp_rank, tp_size,
+                 tp_group, comm):
     fam = family_of(cfg.architecture)
+    if tp_size > 1 and fam != "decoder":
+        raise ValueError(f"tensor parallelism inside a stage is implemented for the GQA decoder families, not for "
+                         f"{cfg.architecture}; use pipeline stages (and expert parallelism for its MoE layers)")
     if fam == "decoder":
         if tp_size > 1:
             from parallax_b200.models.decoder_tp import TPDecoderStage

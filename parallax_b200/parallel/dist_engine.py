@@ -1,6 +1,9 @@
-"""Multi-GPU engine inside one box: pipeline stages x tensor-parallel ranks, one process per GPU.
+"""Multi-GPU engine inside one box: pipeline stages x lanes, one process per GPU. The lanes of a stage
+are either tensor-parallel ranks (one batch, sharded weights) or expert-parallel ranks with
+data-parallel attention (every lane runs its own requests with the whole attention stack and a slice
+of the experts; the MoE layers exchange token rows over NVLink peer memory).
 
-Rank layout: ``rank = pp_rank * tp + tp_rank``. Rank 0 owns the scheduler and the logical KV
+Rank layout: ``rank = pp_rank * lanes + lane``. Rank 0 owns the scheduler and the logical KV
 plan; every step it publishes the packed step inputs (a few hundred KB of indices) to all
 ranks through a shared-memory ring, so that every rank can enqueue its kernels without waiting
 on a device-to-host copy. Activations move stage to stage with NCCL point-to-point on NVLink -
@@ -75,14 +78,27 @@ class Topology:
     rank: int
     pp: int
     tp: int
+    ep: int = 1
+
+    @property
+    def lanes(self) -> int:
+        return self.tp * self.ep
 
     @property
     def pp_rank(self) -> int:
-        return self.rank // self.tp
+        return self.rank // self.lanes
+
+    @property
+    def lane(self) -> int:
+        return self.rank % self.lanes
 
     @property
     def tp_rank(self) -> int:
-        return self.rank % self.tp
+        return self.lane if self.tp > 1 else 0
+
+    @property
+    def ep_rank(self) -> int:
+        return self.lane if self.ep > 1 else 0
 
     @property
     def is_first_stage(self) -> bool:
@@ -94,7 +110,16 @@ class Topology:
 
     @property
     def last_stage_root(self) -> int:
-        return (self.pp - 1) * self.tp
+        return (self.pp - 1) * self.lanes
+
+    @property
+    def token_senders(self) -> list[int]:
+        """Ranks that sample and return tokens to rank 0: the first lane of the last stage with tensor
+        parallelism (all its lanes hold the same logits), every lane of the last stage with expert
+        parallelism (each lane runs its own requests)."""
+        if self.ep > 1:
+            return [self.last_stage_root + l for l in range(self.lanes)]
+        return [self.last_stage_root]
 
 
 class _RecvSlot:
@@ -107,6 +132,41 @@ class _RecvSlot:
         self.free = None
 
 
+class _SchedulerGroup:
+    """The schedulers of all expert-parallel lanes behind the few calls a serving loop makes."""
+
+    def __init__(self, scheds):
+        self.scheds = scheds
+
+    @property
+    def num_running_requests(self) -> int:
+        return sum(s.num_running_requests for s in self.scheds)
+
+    @property
+    def num_queued_requests(self) -> int:
+        return sum(s.num_queued_requests for s in self.scheds)
+
+    def running_requests(self):
+        return [r for s in self.scheds for r in s.running_requests()]
+
+    def evict_request(self, rid: str):
+        for s in self.scheds:
+            r = s.evict_request(rid)
+            if r is not None:
+                return r
+        return None
+
+
+class _CacheGroup:
+    def __init__(self, caches):
+        self.caches = caches
+
+    def free_request(self, rid: str) -> None:
+        for c in self.caches:
+            if c.has_request(rid):
+                c.free_request(rid)
+
+
 class DistEngine:
     def __init__(self, cfg: ModelConfig, pp: int, tp: int, device, dtype=None, page_size: int = 16,
                  num_blocks: Optional[int] = None, kv_fraction: float = 0.85, max_batch_size: int = 8,
@@ -117,45 +177,56 @@ class DistEngine:
                  seed: int = 0, weights: Optional[dict] = None, fused: Optional[bool] = None,
                  max_in_flight: Optional[int] = None, weights_prefiltered: bool = False,
                  liveness_timeout_s: float = 10.0, step_timeout_s: float = 600.0, align_rows: int = 0,
-                 executor_thread: Optional[bool] = None):
+                 executor_thread: Optional[bool] = None, ep: int = 1, ep_local_init: Optional[bool] = None):
         assert dist.is_initialized(), "init the default process group first (nccl on GPUs, gloo on CPU)"
         self.cfg = cfg
         self.device = torch.device(device)
         world, rank = dist.get_world_size(), dist.get_rank()
-        assert world == pp * tp, f"world size {world} != pp*tp = {pp * tp}"
-        self.topo = topo = Topology(world, rank, pp, tp)
+        assert tp == 1 or ep == 1, "a stage's lanes are either tensor-parallel or expert-parallel"
+        assert world == pp * tp * ep, f"world size {world} != pp*tp*ep = {pp * tp * ep}"
+        self.topo = topo = Topology(world, rank, pp, tp, ep)
+        lanes = topo.lanes
         on_gpu = self.device.type == "cuda"
         data_backend = "nccl" if on_gpu else "gloo"
         # ---- groups (every rank creates every group, in the same order)
         self.ctrl = dist.new_group(list(range(world)), backend="gloo")
         # one two-rank communicator per stage hop and tensor-parallel lane, one for the token return
-        self.hop_in = self.hop_out = self.ret = None
+        self.hop_in = self.hop_out = None
         for s in range(pp - 1):
-            for t in range(tp):
-                a, b = s * tp + t, (s + 1) * tp + t
+            for t in range(lanes):
+                a, b = s * lanes + t, (s + 1) * lanes + t
                 g = dist.new_group([a, b], backend=data_backend)
                 if rank == a:
                     self.hop_out = g
                 elif rank == b:
                     self.hop_in = g
-        if topo.last_stage_root != 0:
-            g = dist.new_group([0, topo.last_stage_root], backend=data_backend)
-            if rank in (0, topo.last_stage_root):
-                self.ret = g
-        self.tp_group = None
-        for s in range(pp if tp > 1 else 0):
-            g = dist.new_group(list(range(s * tp, (s + 1) * tp)), backend=data_backend)
+        self.ret: dict = {}          # token-return communicators: sender rank -> group (on rank 0 and on the sender)
+        for snd in topo.token_senders:
+            if snd != 0:
+                g = dist.new_group([0, snd], backend=data_backend)
+                if rank in (0, snd):
+                    self.ret[snd] = g
+        self.tp_group = self.ep_group = None
+        for s in range(pp if lanes > 1 else 0):
+            g = dist.new_group(list(range(s * lanes, (s + 1) * lanes)), backend=data_backend)
             if s == topo.pp_rank:
-                self.tp_group = g
+                if tp > 1:
+                    self.tp_group = g
+                else:
+                    self.ep_group = g
         self.max_in_flight = max_in_flight or pp
         # ---- step plans travel through shared memory (all ranks live on one box); the name is agreed once
         from parallax_b200.parallel.ctrl_channel import CtrlChannel
 
         max_blocks = (max_total_length + page_size - 1) // page_size + 1
         ratio = micro_batch_ratio or pp
+        # expert-parallel lanes split the requests and the per-step token budget among them
+        self.n_plans = ep
+        lane_batch = -(-max_batch_size // ep)
+        lane_tokens = max(-(-max_num_tokens_per_batch // ep), lane_batch + 256) if ep > 1 else max_num_tokens_per_batch
         micro_seqs = max(1, max_batch_size // max(1, ratio))
         # the largest plan: ids, positions (4 B) and slots (8 B) per token, one block table row per sequence
-        slot_bytes = 16 * (max_num_tokens_per_batch + max_batch_size) + 4 * micro_seqs * (max_blocks + 8) + (64 << 10)
+        slot_bytes = 16 * (ep * lane_tokens + max_batch_size) + 4 * micro_seqs * (max_blocks + 8) + (64 << 10)
         slot_bytes = max(1 << 18, (slot_bytes + 4095) // 4096 * 4096)
         n_slots = max(8, self.max_in_flight + 6)
         box = [None]
@@ -176,6 +247,17 @@ class DistEngine:
                                    max_k=max(cfg.hidden_size, cfg.intermediate_size // tp, cfg.q_size // tp))
             else:
                 comm = CollectiveTPComm(self.tp_group, tp, topo.tp_rank, align=128 if on_gpu else 1)
+        ep_comm = None
+        if ep > 1:
+            from parallax_b200.parallel.ep import EPComm
+
+            ep_comm = EPComm(self.ep_group, ep, topo.ep_rank, self.device, max_rows=lane_tokens + lane_batch,
+                             fused=on_gpu if fused is None else fused)
+            if ep_local_init is None:
+                # generate only the local experts when the full expert set would not fit beside the KV cache
+                per_layer = cfg.num_experts * 3 * cfg.moe_intermediate_size * cfg.hidden_size * 2
+                ep_local_init = per_layer * (end - start) > (48 << 30)
+        self.ep_comm = ep_comm
         if weights is not None and not weights_prefiltered:
             from parallax_b200.loader.filter import filter_weights_for_range
 
@@ -184,7 +266,9 @@ class DistEngine:
         self.worker = StageWorker(cfg, start, end, self.device, dtype, page_size, num_blocks=num_blocks,
                                   kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
                                   tp_rank=topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm,
-                                  num_linear_slots=max(max_batch_size * 2, 16) if cfg.has_linear_layers else 0)
+                                  num_linear_slots=max(max_batch_size * 2, 16) if cfg.has_linear_layers else 0,
+                                  ep_rank=topo.ep_rank, ep_size=ep, ep_comm=ep_comm,
+                                  ep_local_init=bool(ep_local_init) and weights is None)
         if cfg.has_linear_layers:
             enable_prefix_cache = False
         # every rank must agree on the number of KV blocks
@@ -198,13 +282,17 @@ class DistEngine:
         self._recv_n = 0
         self._warm_links()
         self.planner = None
+        self.planners: list = []
         if rank == 0:
-            self.planner = Planner(cfg, self.num_blocks, page_size, max_batch_size, max_num_tokens_per_batch, ratio,
-                                   chunked_prefill_size, enable_prefix_cache, max_total_length, request_timeout_s,
-                                   eos_token_id)
-            self.planner.scheduler.max_prefill_tokens_per_batch = max_prefill_tokens_per_batch
-            self.planner.scheduler.align_rows = align_rows
-        self.builders = [BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size, max_batch_size,
+            for _ in range(self.n_plans):
+                pl = Planner(cfg, self.num_blocks, page_size, lane_batch if ep > 1 else max_batch_size, lane_tokens,
+                             ratio, chunked_prefill_size, enable_prefix_cache, max_total_length, request_timeout_s,
+                             eos_token_id)
+                pl.scheduler.max_prefill_tokens_per_batch = max_prefill_tokens_per_batch
+                pl.scheduler.align_rows = align_rows
+                self.planners.append(pl)
+            self.planner = self.planners[0]
+        self.builders = [BatchBuilder(self.device, lane_tokens + max_batch_size, max_batch_size,
                                       max_blocks) for _ in range(self.max_in_flight + 1)]
         self._bi = 0
         self.in_flight: deque = deque()
@@ -220,7 +308,7 @@ class DistEngine:
         self.host_s = {"plan": 0.0, "publish": 0.0, "launch": 0.0, "wait": 0.0, "commit": 0.0}
         # token return: pinned host buffers (tokens + the last stage's status word), reused round-robin
         self._ret_host = [torch.empty(max_batch_size + 1, dtype=torch.int32, pin_memory=on_gpu)
-                          for _ in range(self.max_in_flight + 2)] if rank == 0 else []
+                          for _ in range((self.max_in_flight + 2) * self.n_plans)] if rank == 0 else []
         self._ret_n = 0
         # rank 0: the stage's launches run in their own thread (on GPUs; CPU ranks keep one thread)
         self._exec_thread = None
@@ -233,10 +321,10 @@ class DistEngine:
 
     # ------------------------------------------------------------------ links
     def _prev(self) -> int:
-        return self.topo.rank - self.topo.tp
+        return self.topo.rank - self.topo.lanes
 
     def _next(self) -> int:
-        return self.topo.rank + self.topo.tp
+        return self.topo.rank + self.topo.lanes
 
     def _warm_links(self) -> None:
         """Open every point-to-point connection once, in an order that all ranks share, so that
@@ -248,12 +336,14 @@ class DistEngine:
             dist.recv(x, src=self._prev(), group=self.hop_in)
         if not topo.is_last_stage:
             dist.send(x, dst=self._next(), group=self.hop_out)
-        if topo.last_stage_root != 0:
-            t = torch.zeros(8, dtype=torch.int32, device=self.device)
-            if topo.rank == topo.last_stage_root:
-                dist.send(t, dst=0, group=self.ret)
+        t = torch.zeros(8, dtype=torch.int32, device=self.device)
+        for snd in topo.token_senders:
+            if snd == 0:
+                continue
+            if topo.rank == snd:
+                dist.send(t, dst=0, group=self.ret[snd])
             elif topo.rank == 0:
-                dist.recv(t, src=topo.last_stage_root, group=self.ret)
+                dist.recv(t, src=snd, group=self.ret[snd])
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
 
@@ -285,22 +375,26 @@ class DistEngine:
     # ------------------------------------------------------------------ rank-0 API
     @property
     def scheduler(self):
-        return self.planner.scheduler
+        return self.planner.scheduler if self.n_plans == 1 else _SchedulerGroup([p.scheduler for p in self.planners])
 
     @property
     def cache(self):
-        return self.planner.cache
+        return self.planner.cache if self.n_plans == 1 else _CacheGroup([p.cache for p in self.planners])
 
     def add_request(self, req: Request) -> None:
         req.sampling_params.verify()
         req.max_total_length = min(req.max_total_length, self.planner.max_total_length)
-        self.scheduler.enque_request(req)
+        # expert-parallel lanes: the request stays with the least loaded lane for its whole life
+        pl = min(self.planners, key=lambda p: p.scheduler.num_queued_requests + p.scheduler.num_running_requests)
+        pl.scheduler.enque_request(req)
 
     def abort_request(self, rid: str) -> None:
-        try:
-            self.scheduler.cancel_request(rid)
-        except ValueError:
-            pass
+        for pl in self.planners:
+            try:
+                pl.scheduler.cancel_request(rid)
+                return
+            except ValueError:
+                pass
 
     @property
     def stages(self):
@@ -310,105 +404,129 @@ class DistEngine:
         return [_Span]
 
     def has_work(self) -> bool:
-        return bool(self.in_flight) or self.scheduler.num_queued_requests > 0 or self.scheduler.num_running_requests > 0
+        return bool(self.in_flight) or any(p.scheduler.num_queued_requests > 0 or p.scheduler.num_running_requests > 0
+                                           for p in self.planners)
 
     # ------------------------------------------------------------------ one micro-batch on this rank
+    def _sample(self, lp: dict, out: torch.Tensor) -> torch.Tensor:
+        if lp["greedy"]:
+            return ops.argmax(out)
+        dev = out.device
+        sp = lp["sampling"]
+        return ops.sample(out, torch.tensor(sp["t"], dtype=torch.float32, device=dev),
+                          torch.tensor(sp["k"], dtype=torch.int32, device=dev),
+                          torch.tensor(sp["p"], dtype=torch.float32, device=dev),
+                          torch.tensor(sp["mp"], dtype=torch.float32, device=dev),
+                          torch.tensor(sp["u"], dtype=torch.float32, device=dev))
+
     def _execute(self, plan: dict):
-        """Run this rank's part of one planned micro-batch. Returns, on rank 0, a handle on the
-        sampled tokens (see :meth:`_tokens_of`), else None."""
+        """Run this rank's part of one planned micro-batch. Returns, on rank 0, one handle per plan of
+        the step on its sampled tokens (see :meth:`_collect`), else None."""
         topo, w = self.topo, self.worker
         on_gpu = self.device.type == "cuda"
-        b = self.builders[self._bi]
-        self._bi = (self._bi + 1) % len(self.builders)
-        fb = b.build(plan["ids"] if topo.is_first_stage else None, plan["pos"], plan["slots"], plan["p_q"],
-                     plan["p_ctx"], plan["p_tables"], plan["d_ctx"], plan["d_tables"], plan["logit_rows"],
-                     plan.get("seq_rows"))
-        self.h2d_bytes += fb.h2d_bytes
-        T = fb.num_tokens
-        hidden = None
-        slot_free = None
-        if not topo.is_first_stage:
-            rows = w.model.comm.rows_per_rank(T) if topo.tp > 1 else T
-            hidden = self._recv_hidden(rows)
-            slot_free = self._recv_ring[(self._recv_n - 1) % len(self._recv_ring)].free
-        ev0 = None
-        if on_gpu and self.marks and len(self._busy_events) < 100000:
-            ev0 = torch.cuda.Event(enable_timing=True)      # only between benchmark marks
-            ev0.record()
-        with torch.inference_mode():
-            out = w.run(fb, hidden)
-        if slot_free is not None:
-            slot_free.record()
-        if ev0 is not None:
-            ev1 = torch.cuda.Event(enable_timing=True)
-            ev1.record()
-            self._busy_events.append((ev0, ev1, T))
-        n_logits = plan["n_logits"]
+        lane_plans = plan["lanes"]
+        lp = lane_plans[topo.lane if self.n_plans > 1 else 0]
+        if self.ep_comm is not None:
+            self.ep_comm.step_max_rows = plan.get("max_rows")
         tokens = None
-        if self.keep_logits and topo.is_last_stage:
-            self.last_logits = out
-        if not topo.is_last_stage:
-            out = out if out.is_contiguous() else out.contiguous()
-            self._pending_sends.append((dist.isend(out, dst=self._next(), group=self.hop_out), out))
-        elif n_logits > 0:
-            if plan["greedy"]:
-                tokens = ops.argmax(out)
-            else:
-                dev = out.device
-                sp = plan["sampling"]
-                tokens = ops.sample(out, torch.tensor(sp["t"], dtype=torch.float32, device=dev),
-                                    torch.tensor(sp["k"], dtype=torch.int32, device=dev),
-                                    torch.tensor(sp["p"], dtype=torch.float32, device=dev),
-                                    torch.tensor(sp["mp"], dtype=torch.float32, device=dev),
-                                    torch.tensor(sp["u"], dtype=torch.float32, device=dev))
-            if topo.rank == topo.last_stage_root:
-                # the status word of the sampling rank rides with the tokens
-                packed = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)
-                packed[:n_logits].copy_(tokens)
-                if on_gpu:
-                    from parallax_b200.ops import cuda as cu
+        is_sender = topo.rank in topo.token_senders
+        if lp is None:
+            # expert-parallel lane without a token in this step: it still joins every MoE exchange
+            with torch.inference_mode():
+                w.model.ep_idle_step()
+        else:
+            b = self.builders[self._bi]
+            self._bi = (self._bi + 1) % len(self.builders)
+            fb = b.build(lp["ids"] if topo.is_first_stage else None, lp["pos"], lp["slots"], lp["p_q"],
+                         lp["p_ctx"], lp["p_tables"], lp["d_ctx"], lp["d_tables"], lp["logit_rows"],
+                         lp.get("seq_rows"))
+            self.h2d_bytes += fb.h2d_bytes
+            T = fb.num_tokens
+            hidden = None
+            slot_free = None
+            if not topo.is_first_stage:
+                rows = w.model.comm.rows_per_rank(T) if topo.tp > 1 else T
+                hidden = self._recv_hidden(rows)
+                slot_free = self._recv_ring[(self._recv_n - 1) % len(self._recv_ring)].free
+            ev0 = None
+            if on_gpu and self.marks and len(self._busy_events) < 100000:
+                ev0 = torch.cuda.Event(enable_timing=True)      # only between benchmark marks
+                ev0.record()
+            with torch.inference_mode():
+                out = w.run(fb, hidden)
+            if slot_free is not None:
+                slot_free.record()
+            if ev0 is not None:
+                ev1 = torch.cuda.Event(enable_timing=True)
+                ev1.record()
+                self._busy_events.append((ev0, ev1, T))
+            n_logits = lp["n_logits"]
+            if self.keep_logits and topo.is_last_stage:
+                self.last_logits = out
+            if not topo.is_last_stage:
+                out = out if out.is_contiguous() else out.contiguous()
+                self._pending_sends.append((dist.isend(out, dst=self._next(), group=self.hop_out), out))
+            elif n_logits > 0:
+                tokens = self._sample(lp, out)
+                if is_sender:
+                    # the status word of the sampling rank rides with the tokens
+                    packed = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)
+                    packed[:n_logits].copy_(tokens)
+                    if on_gpu:
+                        from parallax_b200.ops import cuda as cu
 
-                    packed[n_logits:].copy_(cu.status_tensor(self.device))
-                else:
-                    packed[n_logits:].zero_()
-                tokens = packed
-                if topo.last_stage_root != 0:
-                    self._pending_sends.append((dist.isend(packed, dst=0, group=self.ret), packed))
+                        packed[n_logits:].copy_(cu.status_tensor(self.device))
+                    else:
+                        packed[n_logits:].zero_()
+                    tokens = packed
+                    if topo.rank != 0:
+                        self._pending_sends.append((dist.isend(packed, dst=0, group=self.ret[topo.rank]), packed))
         while len(self._pending_sends) > 2 * self.max_in_flight + 2:
             self._pending_sends.popleft()[0].wait()
-        if on_gpu and topo.rank != topo.last_stage_root:
-            # middle ranks: mirror the status word to the host; it is looked at one step later
+        if on_gpu and not (is_sender and lp is not None and lp["n_logits"] > 0):
+            # ranks whose status word does not ride with tokens: mirror it to the host, look one step later
             from parallax_b200.ops import cuda as cu
 
             code = cu.status_mirror(self.device)
             if code and topo.rank != 0:
                 self.chan.report_status(code)
             cu.status_copy_async(self.device)
-        if topo.rank != 0 or n_logits == 0:
+        if topo.rank != 0:
             return None
-        host = self._ret_host[self._ret_n % len(self._ret_host)]
-        self._ret_n += 1
-        if topo.last_stage_root != 0:
-            # post the receive now, in the same order in which the last stage posts its sends
-            if not on_gpu:
-                t = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)
-                return ("recv", (t, dist.irecv(t, src=topo.last_stage_root, group=self.ret), None, None))
-            # on a side stream: reading the tokens later must not wait for the compute of the
-            # micro-batches that were queued behind this one
-            ev = torch.cuda.Event()
-            with torch.cuda.stream(self._ret_stream):
-                t = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)   # from the side stream's pool
-                work = dist.irecv(t, src=topo.last_stage_root, group=self.ret)
-                work.wait()
-                host[:n_logits + 1].copy_(t, non_blocking=True)
+        # ---- rank 0: one handle per plan of the step
+        handles = []
+        for i, p_i in enumerate(lane_plans):
+            if p_i is None or p_i["n_logits"] == 0:
+                handles.append(None)
+                continue
+            n = p_i["n_logits"]
+            snd = topo.token_senders[i]
+            host = self._ret_host[self._ret_n % len(self._ret_host)]
+            self._ret_n += 1
+            if snd != 0:
+                # post the receive now, in the same order in which the sender posts its sends
+                if not on_gpu:
+                    t = torch.empty(n + 1, dtype=torch.int32, device=self.device)
+                    handles.append(("recv", (t, dist.irecv(t, src=snd, group=self.ret[snd]), None, None)))
+                    continue
+                # on a side stream: reading the tokens later must not wait for the compute of the
+                # micro-batches that were queued behind this one
+                ev = torch.cuda.Event()
+                with torch.cuda.stream(self._ret_stream):
+                    t = torch.empty(n + 1, dtype=torch.int32, device=self.device)   # from the side stream's pool
+                    work = dist.irecv(t, src=snd, group=self.ret[snd])
+                    work.wait()
+                    host[:n + 1].copy_(t, non_blocking=True)
+                    ev.record()
+                handles.append(("recv", (t, None, host[:n + 1], ev)))
+            elif on_gpu:
+                ev = torch.cuda.Event()
+                host[:n + 1].copy_(tokens, non_blocking=True)
                 ev.record()
-            return ("recv", (t, None, host[:n_logits + 1], ev))
-        if on_gpu:
-            ev = torch.cuda.Event()
-            host[:n_logits + 1].copy_(tokens, non_blocking=True)
-            ev.record()
-            return ("recv", (tokens, None, host[:n_logits + 1], ev))
-        return ("have", tokens)
+                handles.append(("recv", (tokens, None, host[:n + 1], ev)))
+            else:
+                handles.append(("have", tokens))
+        return handles
 
     # ------------------------------------------------------------------ rank 0: executor thread
     def _executor_loop(self) -> None:
@@ -565,14 +683,14 @@ class DistEngine:
                     f"rank {i}: {_lib.describe(c)}" for i, c in enumerate(codes) if c))
 
     # ------------------------------------------------------------------ rank-0 step
-    def _drop(self, req: Request) -> None:
-        self.scheduler.evict_request(req.request_id)
-        self.cache.free_request(req.request_id)
+    def _drop(self, pl, req: Request) -> None:
+        pl.scheduler.evict_request(req.request_id)
+        pl.cache.free_request(req.request_id)
         self._side_events.append((req, None))
 
-    def _issue(self) -> bool:
-        t0 = time.perf_counter()
-        sched = self.scheduler
+    def _plan_one(self, pl):
+        """Form and plan the next micro-batch of one planner: ``(arrays, lane plan)`` or None."""
+        sched = pl.scheduler
         seqs = sched.form_batch()
         for req in sched.pop_rejected():
             self._side_events.append((req, None))
@@ -580,27 +698,37 @@ class DistEngine:
         for s in seqs:
             if s.req.abort:
                 s.req.update_status(RequestStatus.FINISHED_ABORT)
-                self._drop(s.req)
+                self._drop(pl, s.req)
             else:
                 live.append(s)
         if not live:
-            return False
-        arrays = self.planner.plan_arrays(live)
+            return None
+        arrays = pl.plan_arrays(live)
         for s in live:
             if s.req.is_finished:      # aborted by KV exhaustion during planning
-                self._drop(s.req)
+                self._drop(pl, s.req)
         if arrays is None:
-            return False
+            return None
         owners = arrays["owners"]
         sps = [s.req.sampling_params for s in owners]
         greedy = all(sp.is_greedy for sp in sps)
-        plan = {k: arrays[k] for k in ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables",
-                                       "logit_rows", "seq_rows")}
-        plan.update(cmd="step", n_logits=len(owners), greedy=greedy)
+        lp = {k: arrays[k] for k in ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables",
+                                     "logit_rows", "seq_rows")}
+        lp.update(n_logits=len(owners), greedy=greedy)
         if not greedy:
-            plan["sampling"] = {"t": [0.0 if sp.is_greedy else sp.temperature for sp in sps],
-                                "k": [sp.top_k if sp.top_k > 0 else 0 for sp in sps], "p": [sp.top_p for sp in sps],
-                                "mp": [sp.min_p for sp in sps], "u": self._rng.random(len(sps)).tolist()}
+            lp["sampling"] = {"t": [0.0 if sp.is_greedy else sp.temperature for sp in sps],
+                              "k": [sp.top_k if sp.top_k > 0 else 0 for sp in sps], "p": [sp.top_p for sp in sps],
+                              "mp": [sp.min_p for sp in sps], "u": self._rng.random(len(sps)).tolist()}
+        return arrays, lp
+
+    def _issue(self) -> bool:
+        t0 = time.perf_counter()
+        planned = [self._plan_one(pl) for pl in self.planners]
+        if all(x is None for x in planned):
+            return False
+        lane_plans = [None if x is None else x[1] for x in planned]
+        plan = {"cmd": "step", "lanes": lane_plans,
+                "max_rows": max(int(lp["pos"].shape[0]) for lp in lane_plans if lp is not None)}
         t1 = time.perf_counter()
         self.chan.publish(plan)
         t2 = time.perf_counter()
@@ -612,13 +740,16 @@ class DistEngine:
         hs["launch"] += t3 - t2
         # prefill bookkeeping that does not depend on the sampled token: the next chunk of a long
         # prompt may enter the pipeline right behind this one
-        for s in arrays["ordered"]:
-            if s.is_prefill:
-                s.req.num_computed_tokens = s.start + s.num_tokens
-                self.cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens)
-                if not s.produces_token:
-                    sched.enque_request(s.req)
-        self.in_flight.append((arrays, res))
+        for pl, x in zip(self.planners, planned):
+            if x is None:
+                continue
+            for s in x[0]["ordered"]:
+                if s.is_prefill:
+                    s.req.num_computed_tokens = s.start + s.num_tokens
+                    pl.cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens)
+                    if not s.produces_token:
+                        pl.scheduler.enque_request(s.req)
+        self.in_flight.append(([None if x is None else x[0] for x in planned], res))
         return True
 
     def _wait_return(self, ev, work) -> None:
@@ -663,14 +794,12 @@ class DistEngine:
             if waited > self.step_timeout_s:
                 raise TimeoutError(f"no tokens came back within {self.step_timeout_s:.0f} s")
 
-    def _check_device_status(self, last_stage_code: int) -> None:
+    def _check_device_status(self, sender_codes: dict) -> None:
         """Fail the step if any rank's kernels gave up (bounded wait ran out, bad table entry)."""
-        bad = {}
-        if last_stage_code:
-            bad[self.topo.last_stage_root] = last_stage_code
+        bad = {r: c for r, c in sender_codes.items() if c}
         for idx, code in self.chan.failed_readers().items():
             bad[idx + 1] = code
-        if self.device.type == "cuda" and self.topo.last_stage_root != 0:
+        if self.device.type == "cuda":
             from parallax_b200.ops import cuda as cu
 
             code = cu.status_mirror(self.device)
@@ -687,39 +816,45 @@ class DistEngine:
                                                                 for r, c in sorted(bad.items())))
 
     def _collect(self) -> list:
-        arrays, box = self.in_flight.popleft()
+        arrays_list, box = self.in_flight.popleft()
         out = []
-        owners = arrays["owners"]
-        token_list = []
         tw = time.perf_counter()
         box.done.wait()
         if self._exec_err:
             raise self._exec_err.pop(0)
-        res = box[0]
-        if owners:
-            kind, t = res
-            if kind == "recv":
-                t, work, host, ev = t
-                self._wait_return(ev, work)
-                if ev is not None:
-                    t = host
-            token_list = t.tolist()
-            status_code = int(token_list.pop())
-            self.host_s["wait"] += time.perf_counter() - tw
-            self._check_device_status(status_code)
-        sched = self.scheduler
+        handles = box[0]
+        tokens_of: list = []
+        codes = {}
+        for i, arrays in enumerate(arrays_list):
+            toks = []
+            if arrays is not None and arrays["owners"]:
+                kind, t = handles[i]
+                if kind == "recv":
+                    t, work, host, ev = t
+                    self._wait_return(ev, work)
+                    if ev is not None:
+                        t = host
+                toks = t.tolist()
+                codes[self.topo.token_senders[i]] = int(toks.pop())
+            tokens_of.append(toks)
+        self.host_s["wait"] += time.perf_counter() - tw
+        self._check_device_status(codes)
         tc = time.perf_counter()
         now = time.time()
-        for s, tok in zip(owners, token_list):
-            req = s.req
-            tok = int(tok)
-            req.commit_new_token(tok, now=now)
-            self.cache.append_request_token(req.request_id, tok)
-            if sched.check_and_update_request_status(req):
-                self.cache.free_request(req.request_id)
-            else:
-                sched.enque_request(req, now=now)
-            out.append((req, tok))
+        for pl, arrays, toks in zip(self.planners, arrays_list, tokens_of):
+            if arrays is None:
+                continue
+            sched, cache = pl.scheduler, pl.cache
+            for s, tok in zip(arrays["owners"], toks):
+                req = s.req
+                tok = int(tok)
+                req.commit_new_token(tok, now=now)
+                cache.append_request_token(req.request_id, tok)
+                if sched.check_and_update_request_status(req):
+                    cache.free_request(req.request_id)
+                else:
+                    sched.enque_request(req, now=now)
+                out.append((req, tok))
         self.host_s["commit"] += time.perf_counter() - tc
         return out
 
@@ -727,11 +862,12 @@ class DistEngine:
         """Rank 0: issue micro-batches while the pipeline has room, then collect the oldest."""
         assert self.topo.rank == 0
         out = []
-        for req in self.scheduler.get_timed_out_requests():
-            req.update_status(RequestStatus.FINISHED_ABORT)
-            self.scheduler.evict_request(req.request_id)
-            self.cache.free_request(req.request_id)
-            out.append((req, None))
+        for pl in self.planners:
+            for req in pl.scheduler.get_timed_out_requests():
+                req.update_status(RequestStatus.FINISHED_ABORT)
+                pl.scheduler.evict_request(req.request_id)
+                pl.cache.free_request(req.request_id)
+                out.append((req, None))
         issued = False
         while len(self.in_flight) < self.max_in_flight:
             if not self._issue():

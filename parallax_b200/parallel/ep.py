@@ -53,6 +53,10 @@ def _scatter_fn():
                                                  P, P, c_int, c_int, c_uint32, P, P])
 
 
+def _return_rows_fn():
+    return _fn("pxl_ep_return_rows", [P, c_int64, P, P, c_int, c_int, P, P, c_int, c_int, c_uint32, P])
+
+
 def _combine_fn():
     return _fn("pxl_ep_combine", [P, P, P, c_int64, P, c_int64, P, c_int, c_uint32, c_int, c_int, c_int, P, P])
 
@@ -92,37 +96,60 @@ class EPWorkspace:
 
 
 def ep_moe_ffn(ws: EPWorkspace, x: torch.Tensor, n_valid: int, ids: torch.Tensor, weights: torch.Tensor,
-               w1: torch.Tensor, w2: torch.Tensor, experts_per_rank: int, base: Optional[torch.Tensor] = None,
-               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               w1, w2, experts_per_rank: int, base: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None, max_rows: Optional[int] = None, fp8: Optional[dict] = None,
+               act_mode: int = 0, limit: float = 0.0, b1=None, b2=None) -> torch.Tensor:
     """``out[:n_valid] = base + sum_j weights[:, j] * FFN_{ids[:, j]}(x)`` for this rank's rows.
 
     x ``[rows, H]``, ids/weights ``[rows, k]`` (global expert ids); w1 ``[E_local * 2I, H]``
-    (gate/up interleaved), w2 ``[E_local * H, I]`` hold this rank's experts only."""
+    (gate/up interleaved), w2 ``[E_local * H, I]`` hold this rank's experts only.
+
+    ``max_rows``: an upper bound of ``n_valid`` over ALL ranks of the group for this call (every rank must
+    pass the same value); it sizes the receive regions of the call, so a decode step does not scan the
+    regions of the largest prefill batch. ``fp8``: ``{"w1": (q, scales), "w2": (q, scales)}`` block-scaled
+    e4m3 expert weights; the expert outputs then return through a copy kernel instead of the GEMM epilogue.
+    ``act_mode`` 1: clipped ``swigluoai`` experts with biases (the activation is its own kernel)."""
     dev = x.device
     H, k = ws.H, ws.k
     assert x.shape[1] == H and ids.shape[1] == k and n_valid <= ws.max_rows
+    cap = ws.cap if max_rows is None else max(min(max_rows, ws.max_rows), 1) * k
+    assert n_valid * k <= cap
+    n_recv = ws.ep * cap
     ws.epoch += 1
     epoch = ws.epoch
     st = cu.status_tensor(dev).data_ptr()
     stream = cu._stream(dev)
-    check(_dispatch_fn()(x.data_ptr(), x.stride(0), ids.data_ptr(), n_valid, k, H, experts_per_rank, ws.cap, ws.rank,
+    check(_dispatch_fn()(x.data_ptr(), x.stride(0), ids.data_ptr(), n_valid, k, H, experts_per_rank, cap, ws.rank,
                          ws.ep, ws._p["recv_x"], ws._p["meta"], ws._p["cnt"], ws._p["dflag"], ws.cursor.data_ptr(),
                          ws.counters[0:].data_ptr(), epoch, st, stream), "pxl_ep_dispatch")
-    check(_recv_ids_fn()(ws.recv_meta.data_ptr(), ws.recv_cnt.data_ptr(), ws.disp_flag.data_ptr(), ws.ep, ws.cap,
-                         epoch, ws.ids_local.data_ptr(), st, stream), "pxl_ep_recv_ids")
+    ids_local = ws.ids_local[:n_recv]
+    check(_recv_ids_fn()(ws.recv_meta.data_ptr(), ws.recv_cnt.data_ptr(), ws.disp_flag.data_ptr(), ws.ep, cap,
+                         epoch, ids_local.data_ptr(), st, stream), "pxl_ep_recv_ids")
     cu._count(2)
-    plan = cu.moe_align(ws.ids_local.view(-1, 1), experts_per_rank)
+    plan = cu.moe_align(ids_local.view(-1, 1), experts_per_rank)
     xp = cu.moe_gather(ws.recv_x, plan)
-    act = cu.grouped_linear(xp, w1, plan, experts_per_rank, epi=EPI_SILU_MUL)
     n_rows_dev = plan.offsets[plan.n_local:]
-    check(_row_ptrs_fn()(plan.src_tok.data_ptr(), n_rows_dev.data_ptr(), ws.recv_meta.data_ptr(), ws.cap, H, ws.ep,
+    check(_row_ptrs_fn()(plan.src_tok.data_ptr(), n_rows_dev.data_ptr(), ws.recv_meta.data_ptr(), cap, H, ws.ep,
                          ws._p["comb"], ws.row_ptrs.data_ptr(), plan.max_rows, stream), "pxl_ep_row_ptrs")
-    N = w2.shape[0] // experts_per_rank
-    check(_scatter_fn()(act.data_ptr(), w2.data_ptr(), ws.row_ptrs.data_ptr(), act.shape[0], experts_per_rank, N,
-                        act.shape[1], act.stride(0), w2.stride(0), plan.mt_expert.data_ptr(), plan.mt_row0.data_ptr(),
-                        plan.mt_row_end.data_ptr(), plan.num_mt.data_ptr(), plan.max_mt, ws._p["rflag"],
-                        ws.counters[1:].data_ptr(), ws.rank, ws.ep, epoch, st, stream),
-          "pxl_gemm_bf16_grouped_scatter")
+    if fp8 is None and act_mode == 0:
+        act = cu.grouped_linear(xp, w1, plan, experts_per_rank, epi=EPI_SILU_MUL)
+        N = w2.shape[0] // experts_per_rank
+        check(_scatter_fn()(act.data_ptr(), w2.data_ptr(), ws.row_ptrs.data_ptr(), act.shape[0], experts_per_rank, N,
+                            act.shape[1], act.stride(0), w2.stride(0), plan.mt_expert.data_ptr(),
+                            plan.mt_row0.data_ptr(), plan.mt_row_end.data_ptr(), plan.num_mt.data_ptr(), plan.max_mt,
+                            ws._p["rflag"], ws.counters[1:].data_ptr(), ws.rank, ws.ep, epoch, st, stream),
+              "pxl_gemm_bf16_grouped_scatter")
+    else:
+        if fp8 is not None:
+            act = cu.grouped_linear_fp8(xp, *fp8["w1"], plan, experts_per_rank, epi=EPI_SILU_MUL)
+            y = cu.grouped_linear_fp8(act, *fp8["w2"], plan, experts_per_rank)
+        else:
+            gu = cu.grouped_linear(xp, w1, plan, experts_per_rank, bias=b1)
+            act = cu.act_mul(gu, mode=act_mode, limit=limit)
+            y = cu.grouped_linear(act, w2, plan, experts_per_rank, bias=b2)
+        check(_return_rows_fn()(y.data_ptr(), y.stride(0), ws.row_ptrs.data_ptr(), n_rows_dev.data_ptr(), plan.max_rows,
+                                H, ws._p["rflag"], ws.counters[1:].data_ptr(), ws.rank, ws.ep, epoch, stream),
+              "pxl_ep_return_rows")
     if out is None:
         out = torch.empty_like(x)
     check(_combine_fn()(ws.comb.data_ptr(), weights.data_ptr(), None if base is None else base.data_ptr(),
@@ -173,3 +200,77 @@ def ep_moe_ffn_nccl(group, x: torch.Tensor, n_valid: int, ids: torch.Tensor, wei
     if base is not None:
         outp = outp + base.float()
     return outp.to(x.dtype)
+
+
+def ep_moe_ffn_ragged(group, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, local_ffn, experts_per_rank: int,
+                      base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Library formulation for ranks that hold DIFFERENT numbers of rows (attention data-parallel):
+    rows, routing and weights are padded to the largest rank and all-gathered, every rank applies its own
+    experts to all rows (``local_ffn(x_all, local_ids, local_weights) -> [rows, H]`` with weight 0 on the
+    pairs of other ranks), the partial sums are all-reduced and each rank keeps its own rows. Used on CPU
+    ranks (gloo) and as the baseline; serving on GPUs takes :func:`ep_moe_ffn`."""
+    ep = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    T, H = x.shape
+    k = ids.shape[1]
+    sizes = torch.zeros(ep, dtype=torch.int64, device=x.device)
+    sizes[rank] = T
+    dist.all_reduce(sizes, group=group)
+    t_max = max(int(sizes.max()), 1)
+
+    def padded(t, fill=0):
+        out = t.new_full((t_max,) + tuple(t.shape[1:]), fill)
+        out[:T] = t
+        return out
+
+    xa = torch.empty((ep * t_max, H), dtype=x.dtype, device=x.device)
+    ia = torch.empty((ep * t_max, k), dtype=ids.dtype, device=x.device)
+    wa = torch.empty((ep * t_max, k), dtype=weights.dtype, device=x.device)
+    dist.all_gather_into_tensor(xa, padded(x), group=group)
+    dist.all_gather_into_tensor(ia, padded(ids, -1), group=group)
+    dist.all_gather_into_tensor(wa, padded(weights), group=group)
+    lo = rank * experts_per_rank
+    local = (ia >= lo) & (ia < lo + experts_per_rank)
+    ids_l = torch.where(local, ia - lo, torch.zeros_like(ia))
+    w_l = torch.where(local, wa.float(), torch.zeros_like(wa, dtype=torch.float32))
+    part = local_ffn(xa, ids_l.to(torch.int32), w_l).float()
+    dist.all_reduce(part, group=group)
+    out = part[rank * t_max:rank * t_max + T]
+    if base is not None:
+        out = out + base.float()
+    return out.to(x.dtype)
+
+
+class EPComm:
+    """Expert parallelism for a group whose ranks run attention data-parallel: every rank brings its own
+    token rows (any number, also none), experts are sharded over the group. On B200 the exchange is the
+    peer-memory dispatch / combine of :func:`ep_moe_ffn`; on CPU ranks the library formulation."""
+
+    def __init__(self, group, ep: int, rank: int, device, max_rows: int, fused: Optional[bool] = None):
+        self.group, self.ep, self.rank = group, ep, rank
+        self.device = torch.device(device)
+        self.max_rows = max_rows
+        self.fused = (self.device.type == "cuda") if fused is None else fused
+        self._ws: Optional[EPWorkspace] = None
+        self.step_max_rows: Optional[int] = None     # set by the engine per step: largest row count over the ranks
+
+    def moe_ffn(self, moe, xn: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, base=None) -> torch.Tensor:
+        """``base + MoE(xn)`` for this rank's rows; ``moe`` is the layer's (expert-sharded) MoEWeights."""
+        from parallax_b200 import ops
+
+        epr = moe.experts_per_rank
+        if not self.fused:
+            def local_ffn(xa, ids_l, w_l):
+                if moe.fp8 is not None:
+                    return ops.moe_ffn_fp8(xa, ids_l, w_l, *moe.fp8["w1"], *moe.fp8["w2"], epr)
+                if moe.act_mode:
+                    return ops.moe_ffn(xa, ids_l, w_l, moe.w1, moe.w2, epr, act_mode=moe.act_mode, limit=moe.limit,
+                                       b1=moe.b1, b2=moe.b2)
+                return ops.moe_ffn(xa, ids_l, w_l, moe.w1, moe.w2, epr)
+
+            return ep_moe_ffn_ragged(self.group, xn, ids, weights, local_ffn, epr, base=base)
+        if self._ws is None:
+            self._ws = EPWorkspace(self.group, self.device, self.ep, self.rank, self.max_rows, ids.shape[1], xn.shape[1])
+        return ep_moe_ffn(self._ws, xn, xn.shape[0], ids.contiguous(), weights.contiguous(), moe.w1, moe.w2, epr,
+                          base=base, max_rows=self.step_max_rows, fp8=moe.fp8, act_mode=moe.act_mode,
+                          limit=moe.limit, b1=moe.b1, b2=moe.b2)

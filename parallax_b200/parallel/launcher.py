@@ -22,7 +22,7 @@ logger = logging.getLogger(__name__)
 
 _ENGINE_KEYS = ("page_size", "kv_fraction", "max_batch_size", "max_num_tokens_per_batch", "micro_batch_ratio",
                 "chunked_prefill_size", "max_prefill_tokens_per_batch", "enable_prefix_cache", "max_total_length", "request_timeout_s", "num_blocks",
-                "seed", "fused", "executor_thread", "align_rows", "max_in_flight")
+                "seed", "fused", "executor_thread", "align_rows", "max_in_flight", "ep")
 
 
 def free_port() -> int:
@@ -69,7 +69,7 @@ def build_dist_engine(spec: dict):
     if spec.get("model_path"):
         from parallax_b200.loader.shard_loader import ShardLoader, apply_lora_adapter
 
-        start, end = split_layers(cfg.num_hidden_layers, pp)[rank // tp]
+        start, end = split_layers(cfg.num_hidden_layers, pp)[rank // (tp * spec.get("ep", 1))]
         weights = ShardLoader(spec["model_path"], start, end).load_weights("cpu", None)
         for lp in spec.get("lora_paths") or []:
             apply_lora_adapter(weights, lp)
@@ -113,7 +113,7 @@ def stop_workers(procs: list[subprocess.Popen], timeout: float = 20.0) -> None:
 
 def launch_dist_engine(spec: dict):
     """Spawn ranks 1..N-1, become rank 0. Returns ``(engine, child processes)``."""
-    world = spec["pp"] * spec["tp"]
+    world = spec["pp"] * spec["tp"] * spec.get("ep", 1)
     port = spec.get("port") or free_port()
     procs = spawn_workers(spec, world, port)
     os.environ.update(RANK="0", WORLD_SIZE=str(world), LOCAL_RANK="0")

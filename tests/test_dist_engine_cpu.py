@@ -25,7 +25,7 @@ def _run_group(pp, tp, tmp_path, max_new=6, chunk=16, model="tiny", **extra):
     spec = dict(model_name=model, pp=pp, tp=tp, device_type="cpu", num_blocks=256, page_size=16, max_batch_size=4,
                 max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256, prompts=PROMPTS,
                 max_new=max_new, seed=0, **extra)
-    world, port = pp * tp, free_port()
+    world, port = pp * tp * extra.get("ep", 1), free_port()
     out = tmp_path / f"out_{pp}_{tp}.json"
     procs = []
     for r in range(world):
@@ -80,6 +80,16 @@ def test_dist_engine_moe_expert_parallel(tmp_path):
     """Attention tensor-parallel, experts expert-parallel over the same two ranks."""
     want = _single(model="tiny-moe")
     got = _run_group(1, 2, tmp_path, model="tiny-moe")
+    assert got["outputs"] == want
+
+
+@pytest.mark.parametrize("pp,ep", [(1, 2), (2, 2)])
+def test_expert_parallel_with_data_parallel_attention(pp, ep, tmp_path):
+    """Every lane keeps the whole attention stack and half of the experts and serves its own requests
+    (five prompts over two lanes: the lanes run different row counts, and a lane goes idle while the
+    other still decodes). Same tokens as the single-process engine."""
+    want = _single(model="tiny-moe", max_new=7)
+    got = _run_group(pp, 1, tmp_path, model="tiny-moe", ep=ep, max_new=7)
     assert got["outputs"] == want
 
 
