@@ -1255,12 +1255,13 @@ MidPlan mid_m_plan(int M, int N, int K) {
   const int num_m = pxl::ceil_div(M, BM);
   const int sms = pxl_host::num_sms();
   MidPlan best{0, 1, 1e300};
-  const int bns[2] = {256, 128};
-  const double t_kb[2] = {0.43, 0.29};
-  for (int i = 0; i < 2; ++i) {
+  const int bns[3] = {256, 128, 192};
+  const double t_kb[3] = {0.43, 0.29, 0.36};
+  for (int i = 0; i < 3; ++i) {
     const int tiles = num_m * pxl::ceil_div(N, bns[i]);
     const double plain = pxl::ceil_div(tiles, sms) * (num_kb * t_kb[i]) + 7.0;
     if (plain < best.cost) best = MidPlan{bns[i], 1, plain};
+    if (bns[i] == 192) continue;  // the cluster variant exists for 128- and 256-wide tiles
     for (int sk = 2; sk <= 4; sk += 2) {
       if (num_kb / sk < 4) break;
       const int kb_per = pxl::ceil_div(num_kb, sk);
@@ -1349,7 +1350,6 @@ PXL_EXPORT int pxl_gemm_bf16(const void* A, const void* W, void* C, const void* 
     if (plan > 0 && (plan & 15) > 1)
       return gemm_mid_m(A, W, C, epi == PXL_EPI_F32, epi == PXL_EPI_RESIDUAL ? residual : nullptr, bias, M, N, K, lda,
                         ldw, ldc, plan >> 4, plan & 15, status, stream);
-    if (plan > 0) bn = plan >> 4;
   }
   if (bn == 0) bn = pxl_gemm_bf16_pick_bn(M, N, epi);
   if (epi == PXL_EPI_SILU_MUL && ((N % bn) != 0 || bn < 128)) return PXL_ERR_INVALID_ARG;

@@ -1,18 +1,21 @@
-"""Thread-safe node registry with ACTIVE / STANDBY lifecycle and fixed-pipeline bookkeeping.
+"""Registry of the cluster's nodes and of the fixed pipelines built from them.
 
-Counterpart of ``src/scheduling/node_management.py:18-520``. A *pipeline* is an ordered list
-of nodes whose layer ranges tile ``[0, num_layers)`` without gap or overlap; its request
-capacity is that of its tightest stage. When a member leaves, the whole pipeline is dissolved
-and the remaining members return to STANDBY with their allocation cleared.
+A node is either STANDBY (known, hosting nothing) or ACTIVE (hosting a layer span). A *pipeline* is a
+chain of nodes whose spans tile ``[0, num_layers)``; it serves as many requests as its tightest member.
+Losing one member ends the pipeline: the others drop their layers and wait in STANDBY for the next
+allocation. All state sits behind one re-entrant lock; node objects themselves are only touched outside
+of it when that cannot race with a lookup (clearing a node that was just removed from every table).
+
+Behavioural counterpart of ``src/scheduling/node_management.py:18-520`` (same states, same pipeline rule,
+same capacity report), organised around one record per node instead of parallel tables.
 """
 
 from __future__ import annotations
 
 import logging
 import threading
-from dataclasses import dataclass, field
 from enum import Enum
-from typing import Mapping, Optional, Sequence
+from typing import Iterable, Mapping, Optional, Sequence
 
 from parallax_b200.scheduling.node import Node
 
@@ -24,50 +27,49 @@ class NodeState(str, Enum):
     STANDBY = "standby"
 
 
-@dataclass
-class Pipeline:
-    nodes: list[Node]
-    min_node_capacity: int = field(init=False, default=0)
-    min_remaining_capacity: int = field(init=False, default=0)
+def _span_of(node: Node) -> tuple[int, int]:
+    if node.start_layer is None or node.end_layer is None:
+        raise ValueError(f"node {node.node_id} hosts no layers and cannot be a pipeline stage")
+    return int(node.start_layer), int(node.end_layer)
 
-    def __post_init__(self):
-        if not self.nodes:
-            raise ValueError("Pipeline is empty")
-        inf = float("inf")
-        self.nodes.sort(key=lambda n: (inf if n.start_layer is None else n.start_layer,
-                                       inf if n.end_layer is None else n.end_layer))
-        total = int(self.nodes[0].model_info.num_layers)
-        pos = 0
+
+class Pipeline:
+    """Nodes ordered by layer span. Construction checks that the spans tile the model exactly."""
+
+    def __init__(self, nodes: list[Node]):
+        if not nodes:
+            raise ValueError("a pipeline needs at least one node")
+        depth = {int(n.model_info.num_layers) for n in nodes}
+        if len(depth) != 1:
+            raise ValueError(f"pipeline members were built for models of different depth: {sorted(depth)}")
+        total = depth.pop()
+        self.nodes = sorted(nodes, key=_span_of)
+        cursor = 0
         for n in self.nodes:
-            if int(n.model_info.num_layers) != total:
-                raise ValueError(f"Pipeline nodes disagree on model num_layers ({n.node_id})")
-            if n.start_layer is None or n.end_layer is None:
-                raise ValueError(f"Pipeline node {n.node_id} missing layer allocation")
-            s, e = int(n.start_layer), int(n.end_layer)
-            if s < 0 or e <= s or e > total:
-                raise ValueError(f"Pipeline node {n.node_id} has invalid layer range [{s}, {e})")
-            if s != pos:
-                if pos == 0:
-                    raise ValueError(f"Pipeline must start at layer 0; got {s} on node {n.node_id}")
-                raise ValueError(f"Pipeline is not contiguous at node {n.node_id}: expected start {pos}, got {s}")
-            pos = e
-        if pos != total:
-            raise ValueError(f"Pipeline must end at total_layers={total}; got {pos}")
+            lo, hi = _span_of(n)
+            if not 0 <= lo < hi <= total:
+                raise ValueError(f"node {n.node_id} hosts [{lo}, {hi}), which is not a span of a {total}-layer model")
+            if lo != cursor:
+                kind = "gap" if lo > cursor else "overlap"
+                raise ValueError(f"{kind} in the pipeline before node {n.node_id}: layers up to {cursor} are "
+                                 f"covered, its span starts at {lo}")
+            cursor = hi
+        if cursor != total:
+            raise ValueError(f"the pipeline stops at layer {cursor} of {total}")
+        self.min_node_capacity = 0
+        self.min_remaining_capacity = 0
         self.recompute_capacity()
+
+    @classmethod
+    def from_node_ids(cls, node_ids: Sequence[str], *, nodes_by_id: Mapping[str, Node]) -> "Pipeline":
+        missing = [nid for nid in node_ids if nid not in nodes_by_id]
+        if missing:
+            raise ValueError(f"unknown node(s) {missing}")
+        return cls([nodes_by_id[nid] for nid in node_ids])
 
     @property
     def node_ids(self) -> tuple[str, ...]:
         return tuple(n.node_id for n in self.nodes)
-
-    @classmethod
-    def from_node_ids(cls, node_ids: Sequence[str], *, nodes_by_id: Mapping[str, Node]) -> "Pipeline":
-        nodes = []
-        for nid in node_ids:
-            n = nodes_by_id.get(nid)
-            if n is None:
-                raise ValueError(f"Node {nid} not found in registry")
-            nodes.append(n)
-        return cls(nodes=nodes)
 
     @property
     def num_stages(self) -> int:
@@ -75,125 +77,151 @@ class Pipeline:
 
     @property
     def is_ready(self) -> bool:
-        return all(bool(getattr(n, "is_active", False)) for n in self.nodes)
+        """Every member reports itself able to serve."""
+        return all(getattr(n, "is_active", False) for n in self.nodes)
 
     def recompute_capacity(self) -> None:
-        caps = [int(n.max_requests) for n in self.nodes]
-        rem = [max(0, c - int(n.current_requests)) for c, n in zip(caps, self.nodes)]
-        self.min_node_capacity = min(caps) if caps else 0
-        self.min_remaining_capacity = min(rem) if rem else 0
+        """The tightest member sets the pipeline's capacity and what is left of it."""
+        limits = [int(n.max_requests) for n in self.nodes]
+        self.min_node_capacity = min(limits)
+        self.min_remaining_capacity = min(max(lim - int(n.current_requests), 0) for lim, n in zip(limits, self.nodes))
 
     def capacity_report(self) -> tuple[int, int]:
         self.recompute_capacity()
         return self.min_node_capacity, self.min_remaining_capacity
 
 
+class _Member:
+    """Registry record of one node."""
+
+    __slots__ = ("node", "state", "pipeline")
+
+    def __init__(self, node: Node, state: NodeState):
+        self.node = node
+        self.state = state
+        self.pipeline: Optional[int] = None      # id of the fixed pipeline the node belongs to
+
+
 class NodeManager:
     def __init__(self, *, initial_nodes: Optional[list[Node]] = None):
         self._lock = threading.RLock()
-        self._nodes: dict[str, Node] = {}
-        self._state: dict[str, NodeState] = {}
-        self._registered_pipelines: dict[int, Pipeline] = {}
-        self._node_to_pipeline: dict[str, int] = {}
+        self._members: dict[str, _Member] = {}
+        self._pipelines: dict[int, Pipeline] = {}
+        # requests routed through each node since it was last activated (read by the router's log line)
         self.node_assigned_request_count: dict[str, int] = {}
         for n in initial_nodes or []:
             self.upsert(n, state=NodeState.STANDBY)
 
-    # ---- membership
+    # ------------------------------------------------------------------ membership
     def upsert(self, node: Node, *, state: Optional[NodeState] = None) -> None:
+        """Add a node or replace its object; the state is kept unless one is given (new nodes start
+        in STANDBY)."""
         with self._lock:
-            self._nodes[node.node_id] = node
-            if state is None:
-                self._state.setdefault(node.node_id, NodeState.STANDBY)
+            rec = self._members.get(node.node_id)
+            if rec is None:
+                self._members[node.node_id] = _Member(node, state or NodeState.STANDBY)
             else:
-                self._state[node.node_id] = state
+                rec.node = node
+                if state is not None:
+                    rec.state = state
 
     def get(self, node_id: str) -> Optional[Node]:
         with self._lock:
-            return self._nodes.get(node_id)
+            rec = self._members.get(node_id)
+            return rec.node if rec else None
 
     def state_of(self, node_id: str) -> Optional[NodeState]:
         with self._lock:
-            return self._state.get(node_id)
+            rec = self._members.get(node_id)
+            return rec.state if rec else None
 
-    def _standby_locked(self, node_ids, *, allow_missing: bool = False) -> list[Node]:
-        out = []
+    def _require(self, node_id: str) -> _Member:
+        rec = self._members.get(node_id)
+        if rec is None:
+            raise ValueError(f"node {node_id} is not registered")
+        return rec
+
+    def _to_standby_locked(self, node_ids: Iterable[str], skip_unknown: bool = False) -> list[Node]:
+        """ACTIVE -> STANDBY for the given nodes (lock held). Returns the node objects, whose serving
+        state the caller clears after releasing the lock."""
+        moved = []
         for nid in node_ids:
-            node = self._nodes.get(nid)
-            if node is None:
-                if allow_missing:
+            rec = self._members.get(nid)
+            if rec is None:
+                if skip_unknown:
                     continue
-                raise ValueError(f"Node {nid} not found in registry")
-            prev = self._state.get(nid)
-            if prev is not None and prev != NodeState.ACTIVE:
-                raise ValueError(f"Node {nid} is not ACTIVE, current state: {prev}")
-            self._state[nid] = NodeState.STANDBY
+                raise ValueError(f"node {nid} is not registered")
+            if rec.state is not NodeState.ACTIVE:
+                raise ValueError(f"node {nid} cannot go to standby from state {rec.state.value}")
+            rec.state = NodeState.STANDBY
             self.node_assigned_request_count.pop(nid, None)
-            out.append(node)
-        return out
+            moved.append(rec.node)
+        return moved
 
     def remove(self, node_id: str) -> Optional[Node]:
-        """Drop a node; if it belonged to a fixed pipeline the pipeline is dissolved."""
-        to_clear: list[Node] = []
+        """Forget a node. The fixed pipeline it was part of (if any) ends with it: its other members go
+        back to STANDBY without layers."""
+        orphans: list[Node] = []
         with self._lock:
-            self._state.pop(node_id, None)
-            removed = self._nodes.pop(node_id, None)
-            if removed is None:
+            rec = self._members.pop(node_id, None)
+            if rec is None:
                 return None
             self.node_assigned_request_count.pop(node_id, None)
-            pid = self._node_to_pipeline.pop(node_id, None)
-            if pid is not None:
-                pipeline = self._registered_pipelines.pop(pid, None)
-                if pipeline is not None:
-                    members = list(pipeline.node_ids)
-                    logger.warning("Node %s left; dissolving pipeline %s with members %s", node_id, pid, members)
-                    for nid in members:
-                        self._node_to_pipeline.pop(nid, None)
-                    rest = [nid for nid in members if nid != node_id]
-                    to_clear = self._standby_locked(rest, allow_missing=True)
-        for n in to_clear:
+            if rec.pipeline is not None:
+                pipe = self._pipelines.pop(rec.pipeline, None)
+                if pipe is not None:
+                    others = [nid for nid in pipe.node_ids if nid != node_id]
+                    logger.warning("node %s left: pipeline %d (%s) is dissolved", node_id, rec.pipeline,
+                                   ", ".join(pipe.node_ids))
+                    for nid in others:
+                        other = self._members.get(nid)
+                        if other is not None:
+                            other.pipeline = None
+                    orphans = self._to_standby_locked(others, skip_unknown=True)
+        for n in orphans:
             n.clear_serving_state()
-        removed.clear_serving_state()
-        return removed
+        rec.node.clear_serving_state()
+        return rec.node
 
     def activate(self, node_ids) -> None:
         with self._lock:
             for nid in node_ids:
-                if nid not in self._nodes:
-                    raise ValueError(f"Node {nid} not found in registry")
-                if self._state.get(nid) != NodeState.STANDBY:
-                    raise ValueError(f"Node {nid} is not STANDBY")
-                self._state[nid] = NodeState.ACTIVE
+                rec = self._require(nid)
+                if rec.state is not NodeState.STANDBY:
+                    raise ValueError(f"node {nid} is already {rec.state.value}; only standby nodes can be activated")
+                rec.state = NodeState.ACTIVE
 
     def standby(self, node_ids) -> None:
         with self._lock:
-            nodes = self._standby_locked(list(node_ids))
-        for n in nodes:
+            moved = self._to_standby_locked(list(node_ids))
+        for n in moved:
             n.clear_serving_state()
 
     def ids_to_nodes(self, node_ids) -> list[Node]:
         with self._lock:
-            return [self._nodes[nid] for nid in node_ids]
+            return [self._members[nid].node for nid in node_ids]
 
-    # ---- views
+    # ------------------------------------------------------------------ views
+    def _select(self, state: Optional[NodeState]) -> list[Node]:
+        with self._lock:
+            return [m.node for m in self._members.values() if state is None or m.state is state]
+
     @property
     def nodes(self) -> list[Node]:
-        with self._lock:
-            return list(self._nodes.values())
+        return self._select(None)
 
     @property
     def active_nodes(self) -> list[Node]:
-        with self._lock:
-            return [n for n in self._nodes.values() if self._state.get(n.node_id) == NodeState.ACTIVE]
+        return self._select(NodeState.ACTIVE)
 
     @property
     def standby_nodes(self) -> list[Node]:
-        with self._lock:
-            return [n for n in self._nodes.values() if self._state.get(n.node_id) == NodeState.STANDBY]
+        return self._select(NodeState.STANDBY)
 
     @property
     def num_nodes(self) -> int:
-        return len(self.nodes)
+        with self._lock:
+            return len(self._members)
 
     @property
     def num_active_nodes(self) -> int:
@@ -204,105 +232,119 @@ class NodeManager:
         return len(self.standby_nodes)
 
     def list_node_allocations(self, total_layers: int, ready_only: bool = False) -> list[tuple[str, int, int]]:
+        """``(node id, start, end)`` of every ACTIVE node that hosts layers (``ready_only``: and reports
+        itself able to serve)."""
         if total_layers <= 0:
             return []
-        out = []
+        spans = []
         with self._lock:
-            for nid, node in self._nodes.items():
-                if self._state.get(nid) != NodeState.ACTIVE or (ready_only and not node.is_active):
+            for nid, rec in self._members.items():
+                node = rec.node
+                if rec.state is not NodeState.ACTIVE or node.start_layer is None or node.end_layer is None:
                     continue
-                s, e = node.start_layer, node.end_layer
-                if s is None or e is None:
+                if ready_only and not node.is_active:
                     continue
-                if s < 0 or e <= s or e > total_layers:
-                    raise ValueError(f"Invalid layer range: {s}, {e} for node {nid}")
-                out.append((nid, int(s), int(e)))
-        return out
+                lo, hi = int(node.start_layer), int(node.end_layer)
+                if not 0 <= lo < hi <= total_layers:
+                    raise ValueError(f"node {nid} hosts [{lo}, {hi}), outside a {total_layers}-layer model")
+                spans.append((nid, lo, hi))
+        return spans
 
     def num_full_pipelines(self, total_layers: int, ready_only: bool = False) -> int:
-        """Number of distinct node sequences covering [0, total_layers): a path count over
-        layer boundaries (each ACTIVE allocation is an edge start -> end)."""
-        segs = self.list_node_allocations(total_layers, ready_only)
-        if not segs:
-            return 0
-        ways = {0: 1}
-        for s, e in sorted((s, e) for _, s, e in segs):
-            w = ways.get(s, 0)
-            if w:
-                ways[e] = ways.get(e, 0) + w
-        return int(ways.get(total_layers, 0))
+        """How many different chains of ACTIVE nodes cover ``[0, total_layers)``: spans are edges between
+        layer boundaries, and the chains are the paths from boundary 0 to boundary ``total_layers``."""
+        paths_to = {0: 1}
+        for _nid, lo, hi in sorted(self.list_node_allocations(total_layers, ready_only), key=lambda t: (t[1], t[2])):
+            reach = paths_to.get(lo)
+            if reach:
+                paths_to[hi] = paths_to.get(hi, 0) + reach
+        return paths_to.get(total_layers, 0) if total_layers > 0 else 0
 
     def has_full_pipeline(self, num_total_layers: int, ready_only: bool = False) -> bool:
         return self.num_full_pipelines(num_total_layers, ready_only) > 0
 
     def add_request(self, node_id: str) -> None:
         with self._lock:
-            node = self._nodes.get(node_id)
-            if node is None:
-                raise ValueError(f"Node {node_id} not found in registry")
-            if self._state.get(node_id) != NodeState.ACTIVE:
-                raise ValueError(f"Node {node_id} is not ACTIVE")
+            rec = self._require(node_id)
+            if rec.state is not NodeState.ACTIVE:
+                raise ValueError(f"node {node_id} is {rec.state.value} and takes no requests")
             self.node_assigned_request_count[node_id] = self.node_assigned_request_count.get(node_id, 0) + 1
-            node.add_request()
+            rec.node.add_request()
 
-    # ---- fixed pipelines (round-robin routing)
-    def _register_locked(self, pid: int, p: Sequence[str], force_active: bool) -> None:
-        self._registered_pipelines[pid] = Pipeline.from_node_ids(p, nodes_by_id=self._nodes)
-        for nid in p:
-            if nid in self._node_to_pipeline:
-                raise ValueError(f"Node {nid} is already registered to pipeline {self._node_to_pipeline[nid]}")
-            if force_active and self._state.get(nid) != NodeState.ACTIVE:
-                logger.warning("Node %s is not ACTIVE.", nid)
-                self._state[nid] = NodeState.ACTIVE
-            self._node_to_pipeline[nid] = pid
+    # ------------------------------------------------------------------ fixed pipelines (round-robin routing)
+    def _add_pipeline_locked(self, pid: int, node_ids: Sequence[str], promote: bool) -> None:
+        by_id = {nid: m.node for nid, m in self._members.items()}
+        pipe = Pipeline.from_node_ids(node_ids, nodes_by_id=by_id)
+        taken = [nid for nid in node_ids if self._members[nid].pipeline is not None]
+        if taken:
+            raise ValueError(f"node(s) {taken} already belong to a pipeline")
+        for nid in node_ids:
+            rec = self._members[nid]
+            if promote and rec.state is not NodeState.ACTIVE:
+                logger.warning("node %s joins a pipeline while %s; marking it active", nid, rec.state.value)
+                rec.state = NodeState.ACTIVE
+            rec.pipeline = pid
+        self._pipelines[pid] = pipe
+
+    def _pipeline_ids_locked(self) -> dict[int, list[str]]:
+        return {pid: list(p.node_ids) for pid, p in self._pipelines.items()}
+
+    def _forget_pipelines_locked(self) -> None:
+        self._pipelines = {}
+        for rec in self._members.values():
+            rec.pipeline = None
 
     def register_pipelines(self, pipelines: list[list[str]]) -> dict[int, list[str]]:
+        """Replace the set of fixed pipelines (ids 0..n-1). Members are promoted to ACTIVE."""
         with self._lock:
-            self._registered_pipelines, self._node_to_pipeline = {}, {}
-            for pid, p in enumerate(pipelines):
-                self._register_locked(pid, p, force_active=True)
-            return {pid: list(p.node_ids) for pid, p in self._registered_pipelines.items()}
+            self._forget_pipelines_locked()
+            for pid, ids in enumerate(pipelines):
+                self._add_pipeline_locked(pid, ids, promote=True)
+            return self._pipeline_ids_locked()
 
     def extend_registered_pipelines(self, pipelines: list[list[str]]) -> dict[int, list[str]]:
+        """Add pipelines (empty ones are skipped) with ids following the existing ones."""
         with self._lock:
-            nxt = max(self._registered_pipelines) + 1 if self._registered_pipelines else 0
-            for p in pipelines:
-                if not p:
-                    continue
-                self._register_locked(nxt, p, force_active=False)
-                nxt += 1
-            return {pid: list(p.node_ids) for pid, p in self._registered_pipelines.items()}
+            pid = max(self._pipelines, default=-1) + 1
+            for ids in pipelines:
+                if ids:
+                    self._add_pipeline_locked(pid, ids, promote=False)
+                    pid += 1
+            return self._pipeline_ids_locked()
 
     def clear_registered_pipelines(self) -> None:
+        """Dissolve every fixed pipeline; members that were ACTIVE return to STANDBY without layers."""
         with self._lock:
-            still_active = [nid for nid in self._node_to_pipeline if self._state.get(nid) == NodeState.ACTIVE]
-        self.standby(still_active)
+            to_release = [nid for nid, m in self._members.items()
+                          if m.pipeline is not None and m.state is NodeState.ACTIVE]
+        self.standby(to_release)
         with self._lock:
-            self._registered_pipelines, self._node_to_pipeline = {}, {}
+            self._forget_pipelines_locked()
 
     def get_registered_pipelines(self) -> dict[int, Pipeline]:
         with self._lock:
-            return dict(self._registered_pipelines)
+            return dict(self._pipelines)
 
     def get_registered_pipeline_node_ids(self) -> dict[int, list[str]]:
         with self._lock:
-            return {pid: list(p.node_ids) for pid, p in self._registered_pipelines.items()}
+            return self._pipeline_ids_locked()
 
     def pipeline_id_of_node(self, node_id: str) -> Optional[int]:
         with self._lock:
-            return self._node_to_pipeline.get(node_id)
+            rec = self._members.get(node_id)
+            return rec.pipeline if rec else None
 
     def report_pipeline_capacity(self, ready_only: bool = True):
-        """(per-pipeline (capacity, remaining), total capacity, total remaining)."""
+        """``({pipeline id: (capacity, remaining)}, total capacity, total remaining)``; a pipeline that is
+        not ready counts with zero remaining when ``ready_only``. ``(None, 0, 0)`` without pipelines."""
         with self._lock:
-            if not self._registered_pipelines:
+            if not self._pipelines:
                 return None, 0, 0
-            per, total, cur = {}, 0, 0
-            for pid in sorted(self._registered_pipelines):
-                p = self._registered_pipelines[pid]
-                p.recompute_capacity()
-                remaining = 0 if (ready_only and not p.is_ready) else int(p.min_remaining_capacity)
-                per[pid] = (int(p.min_node_capacity), remaining)
-                total += int(p.min_node_capacity)
-                cur += remaining
-            return per, total, cur
+            report = {}
+            for pid in sorted(self._pipelines):
+                pipe = self._pipelines[pid]
+                cap, left = pipe.capacity_report()
+                if ready_only and not pipe.is_ready:
+                    left = 0
+                report[pid] = (int(cap), int(left))
+            return report, sum(c for c, _ in report.values()), sum(r for _, r in report.values())

@@ -1,11 +1,14 @@
-"""Cluster scheduler: owns the node registry, the layer allocator and the request router.
+"""Cluster scheduler: one object that owns the node registry, the layer allocator and the request router.
 
-Event-driven like ``src/scheduling/scheduler.py:29-649`` of the reference: joins, leaves and
-heartbeat updates are queued and applied by one event thread; a dispatcher thread assigns a
-routing table to every queued request signal; nodes silent for ``heartbeat_timeout`` seconds
-are evicted; after a leave the cluster is globally re-allocated when no full pipeline is left
-(or layer loads became too uneven). The ``_process_*`` methods can be called directly, which
-is how the tests drive it without threads.
+Everything that changes the cluster arrives as an event - a node joins, a node leaves, a node reports
+its load - and is applied by ONE thread in arrival-class order (reports, joins, leaves), so the allocator
+never sees a half-applied change. A second thread hands every queued request a routing table as soon as
+the router has a pipeline to offer. Nodes whose heartbeat stopped are turned into leave events; when a
+departure leaves no complete pipeline (or skews the layer loads beyond the configured threshold) all
+automatically placed nodes are sent back to standby and allocated afresh.
+
+The event methods (`join`, `leave`, `apply_pending`) are plain calls, which is how the tests drive the
+scheduler without threads. Behavioural counterpart of ``src/scheduling/scheduler.py:29-649``.
 """
 
 from __future__ import annotations
@@ -15,7 +18,8 @@ import queue
 import threading
 import time
 from collections import deque
-from typing import Literal, Optional
+from dataclasses import dataclass
+from typing import Any, Literal, Optional
 
 from parallax_b200.scheduling.layer_allocation import DynamicProgrammingLayerAllocator, GreedyLayerAllocator
 from parallax_b200.scheduling.model_info import ModelInfo
@@ -25,6 +29,40 @@ from parallax_b200.scheduling.request_routing import (DynamicProgrammingRouting,
                                                       RoundRobinOverFixedPipelinesRouting)
 
 logger = logging.getLogger(__name__)
+
+_REPORT, _JOIN, _LEAVE = "report", "join", "leave"
+
+
+@dataclass
+class _NodeReport:
+    """Load / health figures a node sends with its heartbeat; None = field not reported."""
+
+    node_id: str
+    current_requests: Optional[int] = None
+    layer_latency_ms: Optional[float] = None
+    new_rtt_to_nodes: Optional[dict] = None
+    is_active: Optional[bool] = None
+    last_refit_time: Optional[float] = 0.0
+
+
+class _Mailbox:
+    """Cluster events waiting for the event thread, one FIFO per kind."""
+
+    def __init__(self):
+        self._boxes: dict[str, "queue.SimpleQueue[Any]"] = {k: queue.SimpleQueue() for k in (_REPORT, _JOIN, _LEAVE)}
+        self.bell = threading.Event()
+
+    def post(self, kind: str, item: Any) -> None:
+        self._boxes[kind].put(item)
+        self.bell.set()
+
+    def drain(self, kind: str) -> list:
+        box, items = self._boxes[kind], []
+        while True:
+            try:
+                items.append(box.get_nowait())
+            except queue.Empty:
+                return items
 
 
 class Scheduler:
@@ -36,42 +74,39 @@ class Scheduler:
                  trim_layers_on_turning_points: bool = False):
         self.model_info = model_info
         self.num_layers = model_info.num_layers
-        self.routing_strategy = routing_strategy
+        self.min_nodes_bootstrapping = min_nodes_bootstrapping
         self.enable_weight_refit = enable_weight_refit
         self.weight_refit_mode = weight_refit_mode
-        self.node_manager = NodeManager(initial_nodes=nodes)
+        self.routing_strategy = routing_strategy
         self.dynamic_pipelines_router = routing_strategy == "dp"
-        alloc_cls = GreedyLayerAllocator if strategy == "greedy" else DynamicProgrammingLayerAllocator
-        self.layer_allocator = alloc_cls(
-            model_info=model_info, node_management=self.node_manager,
-            dynamic_pipelines_router=self.dynamic_pipelines_router, rebalance_threshold=rebalance_threshold,
-            water_filling_max_iterations=water_filling_max_iterations,
-            trim_layers_on_turning_points=trim_layers_on_turning_points)
-        self.min_nodes_bootstrapping = min_nodes_bootstrapping
-        if routing_strategy == "dp":
+        self.request_arrival_horizon_sec = request_arrival_horizon_sec
+        self.heartbeat_timeout = heartbeat_timeout
+        self.node_manager = NodeManager(initial_nodes=nodes)
+        allocator = {"greedy": GreedyLayerAllocator}.get(strategy, DynamicProgrammingLayerAllocator)
+        self.layer_allocator = allocator(model_info=model_info, node_management=self.node_manager,
+                                         dynamic_pipelines_router=self.dynamic_pipelines_router,
+                                         rebalance_threshold=rebalance_threshold,
+                                         water_filling_max_iterations=water_filling_max_iterations,
+                                         trim_layers_on_turning_points=trim_layers_on_turning_points)
+        if self.dynamic_pipelines_router:
             self.request_router = DynamicProgrammingRouting(self.node_manager, self.num_layers)
         else:
             self.request_router = RoundRobinOverFixedPipelinesRouting(self.node_manager, self.num_layers,
                                                                       self.layer_allocator)
-        self._request_queue: "queue.Queue[RequestSignal]" = queue.Queue()
-        self.request_arrival_horizon_sec = request_arrival_horizon_sec
-        self.heartbeat_timeout = heartbeat_timeout
-        self._arrival_ts: deque = deque()
-        self._pending_joins: "queue.Queue[Node]" = queue.Queue()
-        self._pending_leaves: "queue.Queue[str]" = queue.Queue()
-        self._pending_node_updates: queue.Queue = queue.Queue()
-        self._stop_event = threading.Event()
-        self._wake_event = threading.Event()
-        self._bootstrapped_event = threading.Event()
-        self._node_count_cv = threading.Condition()
-        self._threads: list[threading.Thread] = []
+        self._mail = _Mailbox()
+        self._requests: "queue.Queue[RequestSignal]" = queue.Queue()
+        self._recent_arrivals: deque = deque()          # arrival times within the horizon (rate estimate)
+        self._ready = threading.Event()                 # a full pipeline has been allocated
+        self._halt = threading.Event()
+        self._membership_changed = threading.Condition()
+        self._workers: list[threading.Thread] = []
         self.alloc_log_snapshot = ""
         # online weight refit (RL): the newest request and which nodes have applied it
         self.refit_request: dict = {}
         self.refit_set: set = set()
         self.last_refit_time = 0.0
 
-    # ---- views
+    # ------------------------------------------------------------------ views
     def list_node_allocations(self, total_layers: Optional[int] = None):
         return self.node_manager.list_node_allocations(total_layers or self.num_layers)
 
@@ -86,36 +121,119 @@ class Scheduler:
 
     @property
     def bootstrapped(self) -> bool:
-        return self._bootstrapped_event.is_set()
+        return self._ready.is_set()
 
     def need_more_nodes(self) -> bool:
-        return not self._bootstrapped_event.is_set() and not self.has_full_pipeline()
+        return not (self.bootstrapped or self.has_full_pipeline())
 
-    # ---- allocation
+    def wait_bootstrapped(self, timeout: Optional[float] = None) -> bool:
+        return self._ready.wait(timeout)
+
+    def emit_alloc_log_snapshot(self, *, reason: Optional[str] = None) -> str:
+        """Refresh (and at debug level log) the router's table of who hosts what."""
+        try:
+            text = self.request_router.scheduler_format_snapshot()
+        except Exception as exc:      # a log line must never break scheduling
+            text = f"(no allocation snapshot: {exc})"
+        self.alloc_log_snapshot = text
+        if reason:
+            logger.debug("allocation %s:\n%s", reason, text)
+        return text
+
+    # ------------------------------------------------------------------ allocation
     def bootstrap(self, reboot: bool = False) -> bool:
+        """Allocate layers to the standby nodes and let the router build its pipelines. Returns whether
+        the cluster can serve afterwards. ``reboot`` first dissolves the existing pipelines and ignores
+        the minimum node count (used for a global re-allocation)."""
         if reboot:
             self.node_manager.clear_registered_pipelines()
-            self._bootstrapped_event.clear()
-        elif self._bootstrapped_event.is_set():
-            return True
-        if self.node_manager.num_nodes < self.min_nodes_bootstrapping and not reboot:
-            return False
+            self._ready.clear()
+        else:
+            if self.bootstrapped:
+                return True
+            if self.node_manager.num_nodes < self.min_nodes_bootstrapping:
+                return False
         if not self.layer_allocator.allocate_from_standby():
-            self._bootstrapped_event.clear()
+            self._ready.clear()
             return False
         self.request_router.bootstrap()
-        self._bootstrapped_event.set()
-        self.emit_alloc_log_snapshot(reason="Post Bootstrap")
+        self._ready.set()
+        self.emit_alloc_log_snapshot(reason="after bootstrap")
         return True
 
-    def update_last_refit_time(self) -> float:
-        times = [n.last_refit_time for n in self.node_manager.nodes if n.last_refit_time >= self.last_refit_time]
-        if times:
-            self.last_refit_time = min(times)
-        return self.last_refit_time
+    def _release_layers(self, nodes: list[Node]) -> None:
+        """Take the nodes' hosting power out of the allocator's per-layer load table."""
+        table = self.layer_allocator.layer_to_load
+        for node in nodes:
+            if node.start_layer is None or node.end_layer is None:
+                continue
+            for layer in range(node.start_layer, node.end_layer):
+                entry = table.get(layer)
+                if entry is not None:
+                    entry.remove_node(node)
+        self.layer_allocator._update_layer_loads_heap()
 
+    def _reallocate_everything(self) -> None:
+        active = self.node_manager.active_nodes
+        self._release_layers(active)
+        self.node_manager.standby([n.node_id for n in active])
+        try:
+            self.bootstrap(reboot=True)
+        finally:
+            self.emit_alloc_log_snapshot(reason="after global re-allocation")
+
+    # ------------------------------------------------------------------ membership (direct calls)
+    def join(self, node: Node) -> None:
+        """Register a node. Before the first allocation it just waits in standby; afterwards the
+        allocator places it (dynamic routing) or the router tries to form one more pipeline with it.
+        A node that brings its own layer range is placed there at once."""
+        serving = self.bootstrapped
+        is_new = self.node_manager.get(node.node_id) is None
+        if is_new:
+            self.node_manager.upsert(node)
+            if serving:
+                if self.dynamic_pipelines_router:
+                    self.layer_allocator.dynamic_join(node)
+                try:
+                    self.request_router.expand_pipelines()
+                except NotImplementedError:
+                    pass
+        if node.manual_layer_assignment:
+            if node.start_layer is None or node.end_layer is None:
+                raise ValueError(f"node {node.node_id} wants a manual placement but names no layer range")
+            self.layer_allocator.allocate(node, node.start_layer, node.end_layer)
+            if not self.bootstrapped and self.has_full_pipeline():
+                self._ready.set()
+        elif serving and not is_new:
+            self.node_manager.upsert(node)      # a re-join replaces the node object
+        self.emit_alloc_log_snapshot(reason=f"after {node.node_id} joined")
+        self._notify_membership()
+
+    def leave(self, node_id: str) -> None:
+        """Remove a node and, with it, the fixed pipeline it belonged to: the other members lose their
+        layers too (they return to standby), so their share of the layer loads is released as well."""
+        node = self.node_manager.get(node_id)
+        if node is None:
+            raise ValueError(f"cannot remove {node_id}: no such node")
+        losing_layers = [node]
+        pipeline = self.node_manager.pipeline_id_of_node(node_id)
+        if pipeline is not None:
+            mates = [nid for nid in self.node_manager.get_registered_pipeline_node_ids().get(pipeline, ())
+                     if nid != node_id]
+            losing_layers.extend(self.node_manager.ids_to_nodes(mates))
+        self._release_layers(losing_layers)
+        self.node_manager.remove(node_id)
+        self.emit_alloc_log_snapshot(reason=f"after {node_id} left")
+        self._notify_membership()
+
+    def _notify_membership(self) -> None:
+        with self._membership_changed:
+            self._membership_changed.notify_all()
+
+    # ------------------------------------------------------------------ node reports
     def update_node_info(self, node: Node, *, current_requests=None, layer_latency_ms=None,
                          new_rtt_to_nodes=None, is_active=None, last_refit_time: Optional[float] = 0.0) -> None:
+        """Apply a heartbeat's figures to the node object and stamp the heartbeat time."""
         if current_requests is not None:
             node.current_requests = current_requests
         if layer_latency_ms is not None:
@@ -128,219 +246,153 @@ class Scheduler:
             node.last_refit_time = last_refit_time
         node.last_heartbeat = time.time()
 
-    # ---- event intake
+    def update_last_refit_time(self) -> float:
+        """The cluster's refit time is that of the node furthest behind among the nodes that are at or
+        past the current value."""
+        caught_up = [n.last_refit_time for n in self.node_manager.nodes if n.last_refit_time >= self.last_refit_time]
+        if caught_up:
+            self.last_refit_time = min(caught_up)
+        return self.last_refit_time
+
+    def checking_node_heartbeat(self) -> None:
+        """Queue a leave for every active node that has been silent for longer than the timeout."""
+        now = time.time()
+        for node in self.node_manager.active_nodes:
+            silent = now - node.last_heartbeat
+            if silent > self.heartbeat_timeout:
+                logger.warning("no heartbeat from node %s for %.1f s: removing it", node.node_id, silent)
+                self.enqueue_leave(node.node_id)
+
+    # ------------------------------------------------------------------ event intake (any thread)
     def enqueue_join(self, node: Node) -> None:
-        self._pending_joins.put(node)
-        self._wake_event.set()
+        self._mail.post(_JOIN, node)
 
     def enqueue_leave(self, node_id: str) -> None:
-        self._pending_leaves.put(node_id)
-        self._wake_event.set()
+        self._mail.post(_LEAVE, node_id)
 
     def enqueue_node_update(self, node_id: str, *, current_requests=None, layer_latency_ms=None,
                             new_rtt_to_nodes=None, is_active=None, last_refit_time: Optional[float] = 0.0) -> None:
-        self._pending_node_updates.put((node_id, current_requests, layer_latency_ms, new_rtt_to_nodes,
-                                        is_active, last_refit_time))
-        self._wake_event.set()
+        self._mail.post(_REPORT, _NodeReport(node_id, current_requests, layer_latency_ms, new_rtt_to_nodes,
+                                             is_active, last_refit_time))
 
-    def checking_node_heartbeat(self) -> None:
-        now = time.time()
-        for node in self.node_manager.active_nodes:
-            if now - node.last_heartbeat > self.heartbeat_timeout:
-                logger.warning("node %s missed heartbeats for %.1fs; evicting", node.node_id,
-                               now - node.last_heartbeat)
-                self.enqueue_leave(node.node_id)
+    # ------------------------------------------------------------------ event application (event thread or tests)
+    def _apply_reports(self) -> None:
+        for rep in self._mail.drain(_REPORT):
+            node = self.node_manager.get(rep.node_id)
+            if node is None:
+                logger.warning("report from unknown node %s dropped", rep.node_id)
+                continue
+            self.update_node_info(node, current_requests=rep.current_requests, layer_latency_ms=rep.layer_latency_ms,
+                                  new_rtt_to_nodes=rep.new_rtt_to_nodes, is_active=rep.is_active,
+                                  last_refit_time=rep.last_refit_time)
 
-    def join(self, node: Node) -> None:
-        booted = self._bootstrapped_event.is_set()
-        if self.node_manager.get(node.node_id) is None:
-            self.node_manager.upsert(node)
-            if booted:
-                if self.dynamic_pipelines_router:
-                    self.layer_allocator.dynamic_join(node)
-                try:
-                    self.request_router.expand_pipelines()
-                except NotImplementedError:
-                    pass
-        if node.manual_layer_assignment:
-            if node.start_layer is None or node.end_layer is None:
-                raise ValueError(f"node {node.node_id} asks for manual assignment without a layer range")
-            self.layer_allocator.allocate(node, node.start_layer, node.end_layer)
-            if self.has_full_pipeline() and not self._bootstrapped_event.is_set():
-                self._bootstrapped_event.set()
-        elif booted:
-            self.node_manager.upsert(node)
-        self.emit_alloc_log_snapshot(reason=f"after join {node.node_id}")
-        with self._node_count_cv:
-            self._node_count_cv.notify_all()
-
-    def _drop_layer_loads(self, node: Node) -> None:
-        if node.start_layer is None or node.end_layer is None:
+    def _apply_joins(self) -> None:
+        newcomers = self._mail.drain(_JOIN)
+        for node in newcomers:
+            self.join(node)
+        if not newcomers or self.bootstrapped or any(n.manual_layer_assignment for n in newcomers):
             return
-        for l in range(node.start_layer, node.end_layer):
-            ll = self.layer_allocator.layer_to_load.get(l)
-            if ll is not None:
-                ll.remove_node(node)
+        if self.node_manager.num_standby_nodes < self.min_nodes_bootstrapping:
+            return
+        try:
+            if not self.bootstrap():
+                logger.info("not enough capacity for a full pipeline yet; waiting for more nodes")
+        except Exception as exc:
+            logger.warning("allocation after a join failed: %s", exc)
 
-    def leave(self, node_id: str) -> None:
-        """Remove a node. A fixed pipeline it belonged to is dissolved: the other members go
-        back to STANDBY with their allocation cleared, so their hosting power is dropped too."""
-        node = self.node_manager.get(node_id)
-        if node is None:
-            raise ValueError(f"Node {node_id} not found in nodes")
-        affected = [node]
-        pid = self.node_manager.pipeline_id_of_node(node_id)
-        if pid is not None:
-            members = self.node_manager.get_registered_pipeline_node_ids().get(pid, [])
-            affected += [m for m in self.node_manager.ids_to_nodes([x for x in members if x != node_id])]
-        for n in affected:
-            self._drop_layer_loads(n)
-        self.layer_allocator._update_layer_loads_heap()
-        self.node_manager.remove(node_id)
-        self.emit_alloc_log_snapshot(reason=f"after leave {node_id}")
-        with self._node_count_cv:
-            self._node_count_cv.notify_all()
+    def _apply_leaves(self) -> None:
+        gone = 0
+        for node_id in self._mail.drain(_LEAVE):
+            try:
+                self.leave(node_id)
+                gone += 1
+            except Exception as exc:
+                logger.warning("could not remove node %s: %s", node_id, exc)
+        if not gone or not self.layer_allocator.should_global_rebalance():
+            return
+        remaining = self.node_manager.nodes
+        if not remaining or any(n.manual_layer_assignment for n in remaining):
+            return      # manually placed nodes are never moved: an operator has to close the gap
+        self._reallocate_everything()
 
-    # ---- requests
+    def apply_pending(self) -> None:
+        """Apply every queued event: reports first (so decisions see fresh loads), then joins, then leaves."""
+        self._apply_reports()
+        self._apply_joins()
+        self._apply_leaves()
+
+    # names under which the steps are also reachable one by one
+    _process_node_updates = _apply_reports
+    _process_joins = _apply_joins
+    _process_leaves = _apply_leaves
+
+    # ------------------------------------------------------------------ requests
     def receive_request(self, request: RequestSignal) -> None:
-        self._request_queue.put(request)
-        self._wake_event.set()
+        self._requests.put(request)
+        self._mail.bell.set()
         now = time.time()
-        self._arrival_ts.append(now)
-        while self._arrival_ts and now - self._arrival_ts[0] > self.request_arrival_horizon_sec:
-            self._arrival_ts.popleft()
+        arrivals = self._recent_arrivals
+        arrivals.append(now)
+        oldest_kept = now - self.request_arrival_horizon_sec
+        while arrivals and arrivals[0] < oldest_kept:
+            arrivals.popleft()
 
     def dispatch_next_request(self, *, timeout: Optional[float] = None):
-        """Pop one request signal and give it a routing table: (request_id, path, latency)."""
+        """Give the oldest queued request a routing table. Returns ``(request id, path, latency)`` or
+        None when the router has no pipeline yet or no request is waiting."""
         if not self.request_router.routing_ready():
             return None
         try:
-            req = self._request_queue.get(timeout=timeout) if timeout is not None else self._request_queue.get_nowait()
+            request = self._requests.get(timeout=timeout) if timeout is not None else self._requests.get_nowait()
         except queue.Empty:
             return None
         path, latency = self.request_router.find_optimal_path(self.last_refit_time)
-        req.routing_table = path
-        for nid in path:
-            self.node_manager.add_request(nid)
-        return req.request_id, path, latency
+        request.routing_table = path
+        for node_id in path:
+            self.node_manager.add_request(node_id)
+        return request.request_id, path, latency
 
-    def emit_alloc_log_snapshot(self, *, reason: Optional[str] = None) -> str:
-        try:
-            snap = self.request_router.scheduler_format_snapshot()
-        except Exception as exc:
-            snap = f"(failed to build allocation snapshot: {exc})"
-        self.alloc_log_snapshot = snap
-        if reason:
-            logger.debug("allocation snapshot (%s)\n%s", reason, snap)
-        return snap
-
-    # ---- queued-event processing (also called directly by tests)
-    def _process_node_updates(self) -> None:
-        while True:
-            try:
-                nid, cur, lat, rtts, active, refit = self._pending_node_updates.get_nowait()
-            except queue.Empty:
-                return
-            node = self.node_manager.get(nid)
-            if node is None:
-                logger.warning("update for unknown node %s ignored", nid)
-                continue
-            self.update_node_info(node, current_requests=cur, layer_latency_ms=lat, new_rtt_to_nodes=rtts,
-                                  is_active=active, last_refit_time=refit)
-
-    def _process_joins(self) -> None:
-        joined = manual = False
-        while True:
-            try:
-                node = self._pending_joins.get_nowait()
-            except queue.Empty:
-                break
-            self.join(node)
-            joined = True
-            manual = manual or node.manual_layer_assignment
-        if joined and not self._bootstrapped_event.is_set() and not manual:
-            if self.node_manager.num_standby_nodes >= self.min_nodes_bootstrapping:
-                try:
-                    if not self.bootstrap():
-                        logger.info("bootstrap after join produced no full pipeline yet; waiting for more nodes")
-                except Exception as exc:
-                    logger.warning("bootstrap attempt failed: %s", exc)
-
-    def _process_leaves(self) -> None:
-        removed = False
-        while True:
-            try:
-                nid = self._pending_leaves.get_nowait()
-            except queue.Empty:
-                break
-            try:
-                self.leave(nid)
-                removed = True
-            except Exception as exc:
-                logger.warning("leave of %s failed: %s", nid, exc)
-        if not removed or not self.layer_allocator.should_global_rebalance():
-            return
-        nodes = self.node_manager.nodes
-        manual = sum(1 for n in nodes if n.manual_layer_assignment)
-        if not nodes or manual:
-            # manually placed nodes are never moved; an operator has to fix the gap
-            return
-        for n in self.node_manager.active_nodes:
-            self._drop_layer_loads(n)
-        self.layer_allocator._update_layer_loads_heap()
-        self.node_manager.standby([n.node_id for n in self.node_manager.active_nodes])
-        try:
-            self.bootstrap(reboot=True)
-        finally:
-            self.emit_alloc_log_snapshot(reason="after global rebalance")
-
-    # ---- threads
-    def _event_loop(self, poll_interval: float) -> None:
-        last_hb = 0.0
-        while not self._stop_event.is_set():
-            self._process_node_updates()
-            self._process_joins()
-            self._process_leaves()
+    # ------------------------------------------------------------------ threads
+    def _event_worker(self, poll_interval: float) -> None:
+        heartbeat_every = max(0.5, poll_interval)
+        next_check = 0.0
+        while not self._halt.is_set():
+            self.apply_pending()
             now = time.time()
-            if now - last_hb >= max(0.5, poll_interval):
+            if now >= next_check:
                 self.checking_node_heartbeat()
-                last_hb = now
-            self._wake_event.wait(timeout=poll_interval)
-            self._wake_event.clear()
+                next_check = now + heartbeat_every
+            self._mail.bell.wait(timeout=poll_interval)
+            self._mail.bell.clear()
 
-    def _dispatch_loop(self, poll_interval: float) -> None:
-        while not self._stop_event.is_set():
-            if not self.request_router.routing_ready():
+    def _dispatch_worker(self, poll_interval: float) -> None:
+        while not self._halt.is_set():
+            if self.request_router.routing_ready():
+                self.dispatch_next_request(timeout=poll_interval)
+            else:
                 time.sleep(max(0.0, poll_interval))
-                continue
-            self.dispatch_next_request(timeout=poll_interval)
 
     def start(self, *, poll_interval: float = 0.05) -> None:
-        """Start the event and dispatcher threads without blocking (dispatch waits for bootstrap
-        through ``routing_ready``)."""
-        self._stop_event.clear()
-        for name, fn in (("SchedulerEventLoop", self._event_loop), ("SchedulerDispatcher", self._dispatch_loop)):
-            t = threading.Thread(target=fn, args=(poll_interval,), name=name, daemon=True)
-            t.start()
-            self._threads.append(t)
+        """Start the event thread and the dispatcher without blocking; dispatching begins by itself
+        once the router reports a ready pipeline."""
+        self._halt.clear()
+        for name, body in (("SchedulerEventLoop", self._event_worker), ("SchedulerDispatcher", self._dispatch_worker)):
+            worker = threading.Thread(target=body, args=(poll_interval,), name=name, daemon=True)
+            worker.start()
+            self._workers.append(worker)
 
     def run(self, *, poll_interval: float = 0.05, allocation_log_interval: float = 5.0) -> None:
-        """Blocking variant: start the threads and log allocation snapshots until ``stop()``."""
+        """Blocking variant of :meth:`start`: refreshes the allocation snapshot until :meth:`stop`."""
         self.start(poll_interval=poll_interval)
         try:
-            while not self._stop_event.is_set():
+            while not self._halt.wait(timeout=max(1.0, allocation_log_interval)):
                 self.emit_alloc_log_snapshot()
-                self._stop_event.wait(timeout=max(1.0, allocation_log_interval))
         finally:
-            for t in self._threads:
-                t.join(timeout=2.0)
-            self._threads.clear()
-
-    def wait_bootstrapped(self, timeout: Optional[float] = None) -> bool:
-        return self._bootstrapped_event.wait(timeout)
+            for worker in self._workers:
+                worker.join(timeout=2.0)
+            self._workers.clear()
 
     def stop(self) -> None:
-        self._stop_event.set()
-        self._wake_event.set()
-        with self._node_count_cv:
-            self._node_count_cv.notify_all()
+        self._halt.set()
+        self._mail.bell.set()
+        self._notify_membership()
