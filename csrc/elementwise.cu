@@ -413,6 +413,29 @@ PXL_EXPORT int pxl_qk_norm_rope_cache(void* qkv, const void* q_norm_w, const voi
   return check_launch();
 }
 
+// dst[dst_idx[i]] = src[src_idx[i]]: the decode rows of a step take their input ids from the token
+// tensor that the previous step sampled on the device (the host has not read those tokens yet).
+__global__ void patch_i32_kernel(int* __restrict__ dst, const int* __restrict__ dst_idx, const int* __restrict__ src,
+                                 const int* __restrict__ src_idx, int n, int dst_len, int src_len, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int d = dst_idx[i], s = src_idx[i];
+  if (d < 0 || d >= dst_len || s < 0 || s >= src_len) {
+    if (status) atomicCAS(status, 0, PXL_DEV_BAD_ROW_ID);
+    return;
+  }
+  dst[d] = src[s];
+}
+
+PXL_EXPORT int pxl_patch_i32(int* dst, const int* dst_idx, const int* src, const int* src_idx, int n, int dst_len,
+                             int src_len, int* status, pxl_stream_t stream) {
+  if (n <= 0) return PXL_OK;
+  patch_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, dst_idx, src, src_idx, n, dst_len, src_len, status);
+  return check_launch();
+}
+
 PXL_EXPORT int pxl_reshape_and_cache(const void* k, const void* v, int64_t k_stride,
                                      int64_t v_stride, const int64_t* slot_mapping, void* k_cache,
                                      void* v_cache, int T, int Hkv, int Dk, int Dv, int page_size,

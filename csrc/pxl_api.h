@@ -78,6 +78,9 @@ int pxl_act_mul(const void* x, void* out, int T, int I, int mode, float limit, p
 // out[t, :] = table[ids[t], :]  (ids int32 or int64 per `ids_are_i64`)
 int pxl_gather_rows(const void* table, const void* ids, void* out, int T, int H, int64_t num_rows,
                     int ids_are_i64, int* status, pxl_stream_t stream);
+// dst[dst_idx[i]] = src[src_idx[i]] for i < n (int32 words; indices checked against dst_len / src_len)
+int pxl_patch_i32(int* dst, const int* dst_idx, const int* src, const int* src_idx, int n, int dst_len, int src_len,
+                  int* status, pxl_stream_t stream);
 // y += x (bf16), n elements (multiple of 8)
 int pxl_add_inplace(void* y, const void* x, int64_t n, pxl_stream_t stream);
 

@@ -75,6 +75,7 @@ class BatchBuilder:
         d_tables: Optional[np.ndarray],
         logit_rows: np.ndarray,
         seq_rows: Optional[np.ndarray] = None,
+        extra: Optional[dict] = None,
     ) -> ForwardBatch:
         if self._copied is not None:
             # the pinned buffer is about to be rewritten: the asynchronous copy of its previous
@@ -118,6 +119,8 @@ class BatchBuilder:
             np.cumsum(lens, out=scu[1:])
             spans["seq_cu"] = put(scu)
             spans["seq_slots"] = put(seq_rows.astype(np.int32, copy=False))
+        for name, arr in (extra or {}).items():      # further int32 arrays that ride in the same copy
+            spans["x_" + name] = put(np.asarray(arr, dtype=np.int32))
         total = off
         self.dev[:total].copy_(self.host[:total], non_blocking=True)
         if self.device.type == "cuda":
@@ -150,4 +153,6 @@ class BatchBuilder:
             fb.seq_cu = view("seq_cu")
             fb.seq_slots = view("seq_slots")
         fb.num_logits = int(logit_rows.shape[0])
+        for name in (extra or {}):
+            fb.extras[name] = view("x_" + name)
         return fb

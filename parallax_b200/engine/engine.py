@@ -32,7 +32,7 @@ import torch
 from parallax_b200 import ops
 from parallax_b200.cache.manager import CacheManager
 from parallax_b200.engine.batch import BatchBuilder, ForwardBatch
-from parallax_b200.engine.request import Request, RequestStatus, SamplingParams
+from parallax_b200.engine.request import PENDING_TOKEN, Request, RequestStatus, SamplingParams
 from parallax_b200.engine.scheduler import BatchScheduler, ScheduledSeq
 from parallax_b200.engine.worker import StageWorker
 from parallax_b200.models.config import ModelConfig
@@ -46,18 +46,17 @@ def _describe_status(code: int) -> str:
     return _lib.describe(code)
 
 
-class StepPlan:
-    """Host-side description of one step, kept until its tokens come back."""
+class _InFlightStep:
+    """A launched step whose sampled tokens have not been read yet."""
 
-    __slots__ = ("seqs", "fb", "logit_owner", "t_start", "greedy", "sampling")
+    __slots__ = ("arrays", "ids", "probs", "fb", "t0", "serial", "slot_index", "index", "host", "trace_events")
 
-    def __init__(self):
-        self.seqs: list[ScheduledSeq] = []
-        self.fb: Optional[ForwardBatch] = None
-        self.logit_owner: list[ScheduledSeq] = []
-        self.t_start = 0.0
-        self.greedy = True
-        self.sampling = None
+    def __init__(self, arrays, ids, probs, fb, t0, serial):
+        self.arrays, self.ids, self.probs, self.fb, self.t0, self.serial = arrays, ids, probs, fb, t0, serial
+        self.slot_index: list[int] = []      # per owner: index of its placeholder in the request's output_ids
+        self.index: dict[str, int] = {}      # request id -> position of its token in `ids`
+        self.host = None
+        self.trace_events = None
 
 
 class Planner:
@@ -81,8 +80,12 @@ class Planner:
             eos_token_id=eos_token_id, max_total_length=max_total_length, shared_state=shared_state)
         self.max_total_length = max_total_length
 
-    def plan_arrays(self, seqs: list[ScheduledSeq]):
-        """Numpy inputs of a step. Returns None if nothing can run (e.g. all aborted by OOM)."""
+    def plan_arrays(self, seqs: list[ScheduledSeq], pending_index: Optional[dict] = None):
+        """Numpy inputs of a step. Returns None if nothing can run (e.g. all aborted by OOM).
+
+        ``pending_index``: request id -> position of that request's token in the token tensor that the
+        previous (still unread) step sampled. Decode rows of those requests get their input id on the
+        device: the result carries ``patch_rows`` / ``patch_src`` for :func:`ops.patch_ids`."""
         cache, bs = self.cache, self.page_size
         prefill = [s for s in seqs if s.is_prefill]
         decode = []
@@ -106,6 +109,7 @@ class Planner:
         logit_rows, owners = [], []
         o = 0
         p_q, p_ctx, p_rows = [], [], []
+        patch_rows = patch_src = None
         for s in prefill:
             n, st = s.num_tokens, s.start
             ids[o:o + n] = s.req.input_ids[st:st + n]
@@ -127,6 +131,11 @@ class Planner:
             d_ctx = np.fromiter((r.prompt_len + len(r.output_ids) for r in reqs_d), dtype=np.int32, count=nd)
             d_rows = np.fromiter((cache.get_row(r.request_id) for r in reqs_d), dtype=np.int32, count=nd)
             ids[o:o + nd] = np.fromiter((r.output_ids[-1] for r in reqs_d), dtype=np.int32, count=nd)
+            if pending_index:
+                hit = [(o + i, pending_index[r.request_id]) for i, r in enumerate(reqs_d)
+                       if r.output_ids[-1] == PENDING_TOKEN and r.request_id in pending_index]
+                if hit:
+                    patch_rows, patch_src = (np.asarray(x, dtype=np.int32) for x in zip(*hit))
             pos[o:o + nd] = d_ctx - 1
             rows_of_tok[o:o + nd] = d_rows
             logit_rows.extend(range(o, o + nd))
@@ -143,7 +152,8 @@ class Planner:
         seq_rows = np.concatenate([np.asarray(p_rows, dtype=np.int32), d_rows])
         return dict(ordered=ordered, ids=ids, pos=pos, slots=slots, p_q=p_q, p_ctx=p_ctx,
                     p_tables=p_tables, d_ctx=d_ctx, d_tables=d_tables,
-                    logit_rows=np.asarray(logit_rows, dtype=np.int32), owners=owners, seq_rows=seq_rows)
+                    logit_rows=np.asarray(logit_rows, dtype=np.int32), owners=owners, seq_rows=seq_rows,
+                    patch_rows=patch_rows, patch_src=patch_src)
 
 
 class Engine:
@@ -170,6 +180,7 @@ class Engine:
         shared_state=None,
         wire_hook: Optional[Callable] = None,
         trace=None,
+        async_scheduling: Optional[bool] = None,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -200,6 +211,19 @@ class Engine:
         max_blocks = self.cache.max_blocks_per_seq
         self.builder = BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size,
                                     max_batch_size, max_blocks)
+        # launch step s before reading the tokens of step s-1 (GPU devices by default; PXL_SYNC_ENGINE=1 turns it off)
+        import os as _os
+
+        if async_scheduling is None:
+            async_scheduling = self.device.type == "cuda" and not _os.environ.get("PXL_SYNC_ENGINE")
+        self.async_scheduling = bool(async_scheduling)
+        self._in_flight: Optional[_InFlightStep] = None
+        self._host_slots = []
+        if self.device.type == "cuda":
+            for _ in range(3):
+                self._host_slots.append({"ids": torch.empty(max(max_batch_size, 16), dtype=torch.int32, pin_memory=True),
+                                         "probs": torch.empty(max(max_batch_size, 16), dtype=torch.float32, pin_memory=True),
+                                         "event": torch.cuda.Event()})
         self.wire_hook = wire_hook  # optional transform applied to hidden states between stages
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(seed + 12345)
@@ -224,7 +248,8 @@ class Engine:
             pass
 
     def has_work(self) -> bool:
-        return self.scheduler.num_queued_requests > 0 or self.scheduler.num_running_requests > 0
+        return (self._in_flight is not None or self.scheduler.num_queued_requests > 0
+                or self.scheduler.num_running_requests > 0)
 
     # ------------------------------------------------------------------ sampling
     def _sample(self, logits: torch.Tensor, owners: list[ScheduledSeq]):
@@ -276,7 +301,14 @@ class Engine:
     @torch.inference_mode()
     def step(self, events=None) -> list[tuple[Request, Optional[int]]]:
         """Run one engine iteration. Returns ``(request, new_token or None)`` for every
-        request that produced a token or finished in this step.
+        request that produced a token or finished.
+
+        With ``async_scheduling`` the step that is launched here is NOT the one whose tokens are
+        returned: the engine plans and launches step s from sequence lengths alone (the decode rows take
+        their input ids on the device from the tokens step s-1 sampled), and only then reads and commits
+        the tokens of step s-1, while the GPU already works on step s. The events of a call therefore lag
+        one step; :meth:`flush` returns the last ones. A request that ends on an EOS / stop token has
+        one wasted row in the step that was launched before the token was read.
 
         ``events``: optional ``(start, end)`` CUDA events recorded on the compute stream right
         before the step's host-to-device copy and right after sampling (device-time probes)."""
@@ -301,15 +333,17 @@ class Engine:
                 out.append((s.req, None))
             else:
                 live.append(s)
-        if not live:
-            return out
-        arrays = self.planner.plan_arrays(live)
+        prev = self._in_flight
+        arrays = self.planner.plan_arrays(live, prev.index if prev is not None else None) if live else None
         for s in live:
             if s.req.is_finished:  # aborted by KV exhaustion during planning
                 sched.evict_request(s.req.request_id)
                 self._release(s.req)
                 out.append((s.req, None))
         if arrays is None:
+            if prev is not None:
+                self._in_flight = None
+                out += self._commit(prev)
             return out
         t0 = time.perf_counter()
         tr = self.tracer
@@ -319,16 +353,20 @@ class Engine:
                 events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         if events is not None:
             events[0].record()
+        extra = None
+        if arrays["patch_rows"] is not None:
+            extra = {"patch_rows": arrays["patch_rows"], "patch_src": arrays["patch_src"]}
         fb = self.builder.build(arrays["ids"], arrays["pos"], arrays["slots"], arrays["p_q"],
                                 arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"], arrays["d_tables"],
-                                arrays["logit_rows"], arrays["seq_rows"])
+                                arrays["logit_rows"], arrays["seq_rows"], extra=extra)
+        if extra is not None:
+            ops.patch_ids(fb.input_ids, fb.extras["patch_rows"], prev.ids, fb.extras["patch_src"])
         owners = arrays["owners"]
         h = None
         for i, st in enumerate(self.stages):
             h = st.run(fb, h)
             if self.wire_hook is not None and i + 1 < len(self.stages):
                 h = self.wire_hook(h)
-        token_list, prob_list = [], None
         if self.keep_logits:
             self.last_logits = h
         ids = probs = None
@@ -336,65 +374,133 @@ class Engine:
             ids, probs = self._sample(h, owners)
         if events is not None:
             events[1].record()
+        cur = _InFlightStep(arrays, ids, probs, fb, t0, self.total_steps)
+        self._read_back(cur)
         t_launched = time.perf_counter()
-        # prompt bookkeeping that does not depend on the sampled tokens runs while the GPU works: chunk
-        # progress and publishing the chunk's full KV blocks to the prefix cache (a request that matches
-        # them can only be scheduled in a later step, which the stream orders after this one)
-        cache = self.cache
-        for s in arrays["ordered"]:
-            if s.is_prefill:
-                s.req.num_computed_tokens = s.start + s.num_tokens
-                cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens)
-        self._queue_status_read()
-        if owners:
-            token_list = ids.tolist()  # device-to-host copy of the step's result (synchronises)
-            if probs is not None:
-                prob_list = probs.tolist()
-        elif self.device.type == "cuda":
-            torch.cuda.current_stream(self.device).synchronize()
-        code = self._step_status()
-        if code:
-            # a kernel of this step gave up (bounded wait ran out, bad table entry): its outputs are
-            # undefined, so nothing of the step is committed and the serving loop fails the batch
-            raise ops.KernelError(f"device status after step {self.total_steps}: {_describe_status(code)}")
+        self._advance_requests(cur)
         self.total_steps += 1
         self.last_step_stats = {
             "tokens": fb.num_tokens, "prefill_tokens": fb.num_prefill_tokens, "decode": fb.num_decode,
-            "h2d_bytes": fb.h2d_bytes, "d2h_bytes": 4 * len(token_list) * (2 if prob_list else 1),
-            "new_tokens": len(token_list), "wall_s": time.perf_counter() - t0,
+            "h2d_bytes": fb.h2d_bytes, "d2h_bytes": 4 * len(owners) * (2 if probs is not None else 1) + 4,
+            "new_tokens": len(owners),
         }
         if tr is not None:
-            t_synced = time.perf_counter()
             tr.span("build+launch", t0, t_launched, tokens=fb.num_tokens, prefill=fb.num_prefill_tokens, decode=fb.num_decode)
-            tr.span("wait for tokens", t_launched, t_synced)
             if events is not None:
-                tr.device_span(self.total_steps, events[0], events[1], t0, tokens=fb.num_tokens)
-        # ---- commit
-        owner_idx = {id(s): i for i, s in enumerate(owners)}
+                cur.trace_events = events
+        # the tokens of the step before this one (its GPU work ended when this step's began)
+        self._in_flight = cur
+        if prev is not None:
+            out += self._commit(prev)
+        if not self.async_scheduling:
+            self._in_flight = None
+            out += self._commit(cur)
+        self.last_step_stats["wall_s"] = time.perf_counter() - t0
+        return out
+
+    # ------------------------------------------------------------------ the two halves of a step's bookkeeping
+    def _read_back(self, cur: "_InFlightStep") -> None:
+        """Enqueue the device-to-host copy of the step's tokens (and probabilities) and of the status
+        word; an event marks their arrival."""
+        n = len(cur.arrays["owners"])
+        if self.device.type != "cuda":
+            return
+        from parallax_b200.ops import cuda as _cuda
+
+        slot = self._host_slots[cur.serial % len(self._host_slots)]
+        if n:
+            if slot["ids"].numel() < n:
+                slot["ids"] = torch.empty(max(n, 2 * slot["ids"].numel()), dtype=torch.int32, pin_memory=True)
+                slot["probs"] = torch.empty(slot["ids"].numel(), dtype=torch.float32, pin_memory=True)
+            slot["ids"][:n].copy_(cur.ids, non_blocking=True)
+            if cur.probs is not None:
+                slot["probs"][:n].copy_(cur.probs, non_blocking=True)
+        _cuda.status_copy_async(self.device)
+        slot["event"].record()
+        cur.host = slot
+
+    def _advance_requests(self, cur: "_InFlightStep") -> None:
+        """Everything about the launched step that does not need the sampled values: prompt progress,
+        publishing the chunk's full KV blocks to the prefix cache (a request that matches them can only be
+        scheduled in a later step, which the stream orders after this one), a placeholder for each token
+        that is on its way, and the requests' readiness for the next step."""
+        sched, cache = self.scheduler, self.cache
         now = time.time()
-        for s in arrays["ordered"]:
+        owner_ids = {id(s) for s in cur.arrays["owners"]}
+        for s in cur.arrays["ordered"]:
             req = s.req
-            tok = None
-            i = owner_idx.get(id(s))
-            if i is not None:
-                tok = int(token_list[i])
-                req.commit_new_token(tok, prob_list[i] if prob_list else None, now=now)
-                cache.append_request_token(req.request_id, tok)
-            if sched.check_and_update_request_status(req):
-                self._release(req)
-                out.append((req, tok))
+            if s.is_prefill:
+                req.num_computed_tokens = s.start + s.num_tokens
+                cache.insert_full_blocks_to_cache(req.request_id, req.num_computed_tokens)
+            if id(s) in owner_ids:
+                k = req.reserve_token()
+                cur.slot_index.append(k)
+                cur.index[req.request_id] = len(cur.slot_index) - 1
+                if not sched.ends_by_length_after(req, k + 1):
+                    sched.enque_request(req, now=now)      # decodes on: ready for the next step
             else:
-                sched.enque_request(req, now=now)
-                if tok is not None:
-                    out.append((req, tok))
+                sched.enque_request(req, now=now)          # next prompt chunk
+
+    def _commit(self, st: "_InFlightStep") -> list:
+        """Read the tokens of a launched step, fill them in and finish the requests that end on them."""
+        out = []
+        owners = st.arrays["owners"]
+        tr = self.tracer
+        t_wait = time.perf_counter()
+        token_list, prob_list = [], None
+        if self.device.type == "cuda":
+            st.host["event"].synchronize()
+            if owners:
+                token_list = st.host["ids"][:len(owners)].tolist()
+                if st.probs is not None:
+                    prob_list = st.host["probs"][:len(owners)].tolist()
+        elif owners:
+            token_list = st.ids.tolist()
+            prob_list = st.probs.tolist() if st.probs is not None else None
+        code = self._step_status()
+        sched, cache = self.scheduler, self.cache
+        if code:
+            # a kernel of the step gave up (bounded wait ran out, bad table entry): its outputs are
+            # undefined. Nothing of it is committed; the serving loop fails the batch.
+            for s, k in zip(owners, st.slot_index):
+                del s.req.output_ids[k:]
+            self._in_flight = None
+            raise ops.KernelError(f"device status after step {st.serial}: {_describe_status(code)}")
+        t_synced = time.perf_counter()
+        now = time.time()
+        for i, s in enumerate(owners):
+            req = s.req
+            if req.is_finished:           # ended earlier (EOS seen after this row was launched, abort)
+                continue
+            k = st.slot_index[i]
+            tok = int(token_list[i])
+            req.fill_token(k, tok, prob_list[i] if prob_list else None, now=now)
+            cache.append_request_token(req.request_id, tok)
+            why = sched.finish_reason(req, k + 1, tok)
+            if why is not None:
+                del req.output_ids[k + 1:]      # a placeholder of the step that is already running
+                req.update_status(why)
+                sched.evict_request(req.request_id)
+                self._release(req)
+            out.append((req, tok))
+        for s in st.arrays["ordered"]:
+            if s.is_prefill and not s.produces_token and s.req.abort and not s.req.is_finished:
+                s.req.update_status(RequestStatus.FINISHED_ABORT)
+                sched.evict_request(s.req.request_id)
+                self._release(s.req)
+                out.append((s.req, None))
         if tr is not None:
+            tr.span("wait for tokens", t_wait, t_synced)
             tr.span("commit", t_synced, time.perf_counter())
+            if st.trace_events is not None:
+                tr.device_span(st.serial + 1, st.trace_events[0], st.trace_events[1], st.t0, tokens=st.fb.num_tokens)
         return out
 
     def flush(self) -> list:
-        """Finish whatever the engine still has in flight on the device (nothing, while steps are
-        synchronous); returns the events of that work like :meth:`step`."""
-        return []
+        """Read and commit the step that is still in flight (asynchronous scheduling); returns its events
+        like :meth:`step`. A no-op otherwise."""
+        st, self._in_flight = self._in_flight, None
+        return self._commit(st) if st is not None else []
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: Iterable[list[int]], sampling_params: Optional[SamplingParams] = None,

@@ -109,6 +109,11 @@ _FINISHED = {
 }
 
 
+# Stands in ``output_ids`` for a token that has been sampled on the device but not read back yet (the
+# engine launches the next step before it reads the previous step's tokens).
+PENDING_TOKEN = -1
+
+
 class Request:
     """Generation request as tracked by the first pipeline stage."""
 
@@ -196,6 +201,25 @@ class Request:
             self.first_token_time = now
         if self.status == RequestStatus.PREFILLING:
             self.status = RequestStatus.DECODING
+        self.last_updated_time = now
+
+    def reserve_token(self) -> int:
+        """Append a placeholder for the token that the step just launched will produce; returns its
+        index in ``output_ids``. The request counts as DECODING from here on."""
+        self.output_ids.append(PENDING_TOKEN)
+        if self.status == RequestStatus.PREFILLING:
+            self.status = RequestStatus.DECODING
+        return len(self.output_ids) - 1
+
+    def fill_token(self, index: int, token_id: int, prob: Optional[float] = None, now: Optional[float] = None) -> None:
+        """The value of a reserved token arrived."""
+        self.output_ids[index] = int(token_id)
+        if prob is not None:
+            self.output_probs.append(float(prob))
+        if now is None:
+            now = time.time()
+        if self.first_token_time is None:
+            self.first_token_time = now
         self.last_updated_time = now
 
     @property

@@ -247,6 +247,24 @@ class BatchScheduler:
         return batch
 
     # ------------------------------------------------------------------ finish rules
+    def finish_reason(self, req: Request, n_out: int, last_token: Optional[int]) -> Optional[RequestStatus]:
+        """Why the request ends after its ``n_out``-th generated token ``last_token`` (None = it goes on):
+        abort, EOS / stop ids (honouring ``min_new_tokens``), ``max_new_tokens``, total length."""
+        if req.abort:
+            return RequestStatus.FINISHED_ABORT
+        sp = req.sampling_params
+        if n_out and n_out > sp.min_new_tokens and last_token is not None:
+            if (not sp.ignore_eos and last_token in self.eos_token_ids) or \
+                    (sp.stop_token_ids and last_token in sp.stop_token_ids):
+                return RequestStatus.FINISHED_EOS
+        if n_out >= sp.max_new_tokens or req.prompt_len + n_out >= req.max_total_length:
+            return RequestStatus.FINISHED_MAX_LENGTH
+        return None
+
+    def ends_by_length_after(self, req: Request, n_out: int) -> bool:
+        """Whether the request is over after ``n_out`` generated tokens whatever those tokens are."""
+        return n_out >= req.sampling_params.max_new_tokens or req.prompt_len + n_out >= req.max_total_length
+
     def check_and_update_request_status(self, req: Request) -> bool:
         """EOS / stop ids (honouring ``min_new_tokens``) / max_new / max_total / abort."""
         if req.status in _FINISHED_STATES:

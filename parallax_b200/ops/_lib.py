@@ -62,6 +62,7 @@ _SIGS = {
     "pxl_act_mul": [_P, _P, c_int, c_int, c_int, c_float, _P],
     "pxl_gather_rows": [_P, _P, _P, c_int, c_int, c_int64, c_int, _P, _P],
     "pxl_add_inplace": [_P, _P, c_int64, _P],
+    "pxl_patch_i32": [_P, _P, _P, _P, c_int, c_int, c_int, _P, _P],
     "pxl_attn_decode": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_int64, c_float, c_int, c_int, c_int, _P, _P],
     "pxl_attn_decode_splits": [c_int, c_int, c_int],

@@ -304,6 +304,18 @@ def act_mul(x: torch.Tensor, mode: int = 0, limit: float = 7.0) -> torch.Tensor:
     return out
 
 
+def patch_ids(dst: torch.Tensor, dst_idx: torch.Tensor, src: torch.Tensor, src_idx: torch.Tensor) -> None:
+    """``dst[dst_idx] = src[src_idx]`` on int32 tensors (token ids that never left the device)."""
+    n = dst_idx.numel()
+    if n == 0:
+        return
+    assert dst.dtype == src.dtype == dst_idx.dtype == src_idx.dtype == torch.int32
+    check(_lib.lib().pxl_patch_i32(dst.data_ptr(), dst_idx.data_ptr(), src.data_ptr(), src_idx.data_ptr(), n,
+                                   dst.numel(), src.numel(), status_tensor(dst.device).data_ptr(), _stream(dst.device)),
+          "pxl_patch_i32")
+    _count()
+
+
 def gather_rows(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     T, H = ids.numel(), table.shape[1]
     assert table.is_contiguous() and ids.dtype in (torch.int32, torch.int64)

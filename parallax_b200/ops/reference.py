@@ -235,6 +235,12 @@ def argmax(logits, want_logprob: bool = False):
     return ids
 
 
+def patch_ids(dst, dst_idx, src, src_idx) -> None:
+    """``dst[dst_idx] = src[src_idx]`` (in place)."""
+    if dst_idx.numel():
+        dst[dst_idx.long()] = src[src_idx.long()]
+
+
 def sample(logits, temperature, top_k, top_p, min_p, uniform, want_prob: bool = False):
     """Sort-based sampler with the reference's filter order; one uniform number per row."""
     B, V = logits.shape

@@ -783,9 +783,13 @@ class DistEngine:
                 return
             if sleep:
                 time.sleep(sleep)
+            elif self._exec_thread is not None:
+                time.sleep(0)          # hand the interpreter to the thread that launches rank 0's stage
             waited = time.monotonic() - t0
             if waited > 0.002:
                 sleep = 0.0002
+            elif self._exec_thread is not None:
+                sleep = 0.00005
             if waited > self.liveness_timeout_s / 4:
                 stale = self.chan.stale_readers(self.liveness_timeout_s)
                 if stale:

@@ -239,3 +239,51 @@ def test_nonzero_device_status_fails_the_batch():
             break
     loop.stop()
     assert len(toks) == 3 and ev.error is None
+
+
+def test_async_scheduling_matches_synchronous_steps():
+    """Launching step s before reading the tokens of step s-1 (decode input ids patched on the device,
+    placeholders on the host) must not change any result: same tokens, same finish reasons, also when a
+    request ends on an EOS / stop token that is only seen one step late, with chunked prompts, shared
+    prefixes and more requests than batch slots."""
+    cfg = named_config("tiny")
+    g = torch.Generator().manual_seed(5)
+    shared = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 33, 70, 18, 9, 50, 3)]
+    prompts[2][:40] = shared
+    prompts[5][:40] = shared
+
+    def run(async_mode, eos=None, stop=None, min_new=0):
+        eng = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=4, max_num_tokens_per_batch=96,
+                     chunked_prefill_size=32, eos_token_id=eos, async_scheduling=async_mode)
+        reqs = [Request(input_ids=p, sampling_params=SamplingParams(max_new_tokens=12, temperature=0.0,
+                                                                    stop_token_ids=stop, min_new_tokens=min_new))
+                for p in prompts]
+        for r in reqs:
+            eng.add_request(r)
+        events, steps = [], 0
+        while eng.has_work() and steps < 400:
+            events += eng.step()
+            steps += 1
+        events += eng.flush()
+        assert not eng.cache.reqs, "every request released its KV blocks"
+        streamed = {}
+        for req, tok in events:
+            if tok is not None:
+                streamed.setdefault(req.request_id, []).append(tok)
+        for r in reqs:
+            assert streamed.get(r.request_id, []) == r.output_ids      # every token was reported exactly once
+            assert -1 not in r.output_ids
+        return [r.output_ids for r in reqs], [r.status.value for r in reqs]
+
+    base, status = run(False)
+    assert run(True) == (base, status)
+    # an EOS that really occurs: the token request 1 produced third
+    eos = base[1][2]
+    want = run(False, eos=eos)
+    assert any(s == "FINISHED_EOS" for s in want[1])
+    assert run(True, eos=eos) == want
+    # stop ids and min_new_tokens
+    stop = [base[0][1], base[3][4]]
+    want = run(False, stop=stop, min_new=2)
+    assert run(True, stop=stop, min_new=2) == want
