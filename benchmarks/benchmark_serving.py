@@ -11,8 +11,9 @@ throughput, time to first token, time per output token, inter-token latency, end
 ``src/backend/benchmark/benchmark_serving.py`` (datasets ``:147-318``, arrivals ``:320``, metrics
 ``:363-477``) with its own, smaller implementation; datasets here are ``random`` (uniform token ids
 decoded by the model's tokenizer, or synthetic words when no tokenizer is given), ``jsonl``
-(one ``{"prompt": ..., "max_tokens": ...}`` per line) and ``sharegpt`` (a ShareGPT-style conversation
-dump: first human turn as prompt, length of the first reply as output budget).
+(one ``{"prompt": ..., "max_tokens": ...}`` per line), ``sharegpt`` (a ShareGPT-style conversation
+dump: first human turn as prompt, length of the first reply as output budget), ``hf`` (a local parquet /
+jsonl copy of a Hugging Face text dataset) and ``wildchat`` (rows with a ``conversation`` list).
 """
 
 from __future__ import annotations
@@ -46,7 +47,9 @@ class Result:
 
 
 def make_random_dataset(n: int, in_len: int, out_len: int, range_ratio: float, seed: int, tokenizer=None,
-                        prefix_len: int = 0) -> list[Sample]:
+                        prefix_len: int = 0, byte_level: bool = False) -> list[Sample]:
+    """``byte_level``: prompts of exactly the asked number of ASCII characters, for servers that run the
+    byte-level fallback tokenizer (random-init models): one character is one token there."""
     rng = random.Random(seed)
     vocab = tokenizer.vocab_size if tokenizer is not None else 0
     prefix = [rng.randrange(vocab) for _ in range(prefix_len)] if tokenizer is not None else []
@@ -57,9 +60,82 @@ def make_random_dataset(n: int, in_len: int, out_len: int, range_ratio: float, s
         if tokenizer is not None:
             ids = prefix + [rng.randrange(vocab) for _ in range(max(li - prefix_len, 1))]
             text = tokenizer.decode(ids)
+        elif byte_level:
+            text = "".join(rng.choice("abcdefghijklmnopqrstuvwxyz      ") for _ in range(li))
         else:
             text = " ".join(f"w{rng.randrange(50000)}" for _ in range(li))
         out.append(Sample(text, li, lo))
+    return out
+
+
+def _read_records(path: str) -> list[dict]:
+    """Rows of a local dataset file: ``.parquet`` (as published on the Hugging Face hub), ``.jsonl`` or ``.json``."""
+    if path.endswith(".parquet"):
+        import pyarrow.parquet as pq
+
+        return pq.read_table(path).to_pylist()
+    with open(path) as f:
+        if path.endswith(".jsonl"):
+            return [json.loads(line) for line in f if line.strip()]
+        data = json.load(f)
+    return data if isinstance(data, list) else data.get("data", [])
+
+
+def load_hf_dataset(path: str, n: int, default_out: int, seed: int, tokenizer=None, text_column: str = "",
+                    output_column: str = "") -> list[Sample]:
+    """A local copy of a Hugging Face text dataset: the prompt is ``text_column`` (default: the first of
+    ``prompt`` / ``question`` / ``instruction`` / ``text`` that the rows have); when ``output_column`` (default
+    ``response`` / ``answer`` / ``output``) exists, its length is the output budget. Counterpart of the
+    reference's ``hf`` dataset option (``src/backend/benchmark/benchmark_serving.py:210-318``) without the
+    download step."""
+    rows = _read_records(path)
+    rng = random.Random(seed)
+    rng.shuffle(rows)
+
+    def pick(row, wanted, candidates):
+        if wanted:
+            return row.get(wanted)
+        return next((row[c] for c in candidates if row.get(c)), None)
+
+    def length(text: str) -> int:
+        return len(tokenizer.encode(text)) if tokenizer is not None else max(1, len(text.split()))
+
+    out = []
+    for row in rows:
+        prompt = pick(row, text_column, ("prompt", "question", "instruction", "text"))
+        if not isinstance(prompt, str) or not prompt.strip():
+            continue
+        reply = pick(row, output_column, ("response", "answer", "output"))
+        lo = length(reply) if isinstance(reply, str) and reply else default_out
+        out.append(Sample(prompt, length(prompt), max(1, lo)))
+        if len(out) >= n:
+            break
+    return out
+
+
+def load_wildchat_dataset(path: str, n: int, default_out: int, seed: int, tokenizer=None) -> list[Sample]:
+    """WildChat-style rows: ``{"conversation": [{"role": "user", "content": ...}, {"role": "assistant", ...}]}``.
+    First user turn = prompt, length of the first assistant turn = output budget."""
+    rows = _read_records(path)
+    rng = random.Random(seed)
+    rng.shuffle(rows)
+
+    def length(text: str) -> int:
+        return len(tokenizer.encode(text)) if tokenizer is not None else max(1, len(text.split()))
+
+    out = []
+    for row in rows:
+        conv = row.get("conversation") or []
+        user = next((t.get("content") for t in conv if t.get("role") == "user"), None)
+        reply = next((t.get("content") for t in conv if t.get("role") == "assistant"), None)
+        if not user:
+            continue
+        lp = length(user)
+        if lp > 4096:
+            continue
+        out.append(Sample(user, lp, max(1, length(reply)) if reply else default_out))
+        if len(out) >= n:
+            break
     return out
 
 
@@ -242,7 +318,11 @@ def main(argv: Optional[list[str]] = None) -> dict:
     ap.add_argument("--base-url", default="http://127.0.0.1:3000")
     ap.add_argument("--model", default="default")
     ap.add_argument("--chat", action="store_true", help="use /v1/chat/completions instead of /v1/completions")
-    ap.add_argument("--dataset", default="random", choices=["random", "jsonl", "sharegpt"])
+    ap.add_argument("--dataset", default="random", choices=["random", "jsonl", "sharegpt", "hf", "wildchat"])
+    ap.add_argument("--hf-text-column", default="", help="hf dataset: column that holds the prompt")
+    ap.add_argument("--hf-output-column", default="", help="hf dataset: column whose length sets the output budget")
+    ap.add_argument("--byte-tokens", action="store_true",
+                    help="random dataset: prompts of exactly N characters (servers with the byte-level tokenizer)")
     ap.add_argument("--dataset-path", default="")
     ap.add_argument("--tokenizer", default="", help="local tokenizer directory for the random dataset")
     ap.add_argument("--num-prompts", type=int, default=1000)
@@ -267,7 +347,13 @@ def main(argv: Optional[list[str]] = None) -> dict:
         tok = TokenizerWrapper.from_pretrained(args.tokenizer)
     if args.dataset == "random":
         samples = make_random_dataset(args.num_prompts, args.random_input_len, args.random_output_len,
-                                      args.random_range_ratio, args.seed, tok, args.random_prefix_len)
+                                      args.random_range_ratio, args.seed, tok, args.random_prefix_len,
+                                      byte_level=args.byte_tokens)
+    elif args.dataset == "hf":
+        samples = load_hf_dataset(args.dataset_path, args.num_prompts, args.random_output_len, args.seed, tok,
+                                  args.hf_text_column, args.hf_output_column)
+    elif args.dataset == "wildchat":
+        samples = load_wildchat_dataset(args.dataset_path, args.num_prompts, args.random_output_len, args.seed, tok)
     elif args.dataset == "sharegpt":
         samples = load_sharegpt_dataset(args.dataset_path, args.num_prompts, args.random_output_len, args.seed, tok)
     else:

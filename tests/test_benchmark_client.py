@@ -77,3 +77,30 @@ def test_sharegpt_dataset_loader(tmp_path):
     s = by_prompt["how do pipeline stages hand activations over"]
     assert s.prompt_len == 7 and s.max_tokens == 8
     assert len(client.load_sharegpt_dataset(str(path), 1, 64, seed=0)) == 1
+
+
+def test_hf_and_wildchat_loaders(tmp_path):
+    import json
+
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    from benchmarks.benchmark_serving import load_hf_dataset, load_wildchat_dataset, make_random_dataset
+
+    rows = [{"question": f"what is {i} plus {i}", "answer": "it is " + " ".join(["x"] * (i + 1))} for i in range(6)]
+    pq.write_table(pa.Table.from_pylist(rows), tmp_path / "d.parquet")
+    got = load_hf_dataset(str(tmp_path / "d.parquet"), 4, 32, seed=0)
+    assert len(got) == 4 and all(s.prompt.startswith("what is") and s.max_tokens >= 3 for s in got)
+    with open(tmp_path / "d.jsonl", "w") as f:
+        for r in rows:
+            f.write(json.dumps({"text": r["question"]}) + "\n")
+    got = load_hf_dataset(str(tmp_path / "d.jsonl"), 10, 17, seed=1)
+    assert len(got) == 6 and all(s.max_tokens == 17 for s in got)
+    chats = [{"conversation": [{"role": "user", "content": f"hello {i}"}, {"role": "assistant", "content": "a b c d"}]}
+             for i in range(3)] + [{"conversation": []}]
+    with open(tmp_path / "w.json", "w") as f:
+        json.dump(chats, f)
+    got = load_wildchat_dataset(str(tmp_path / "w.json"), 5, 9, seed=0)
+    assert len(got) == 3 and all(s.max_tokens == 4 for s in got)
+    b = make_random_dataset(3, 50, 5, 0.0, seed=0, byte_level=True)
+    assert all(len(s.prompt) == 50 == s.prompt_len for s in b)
