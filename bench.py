@@ -173,7 +173,7 @@ class LatencyLog:
         rec = self.span.get(req.request_id)
         if rec is None:
             self.span[req.request_id] = [now, now, 1]
-            if len(req.output_ids) == 1 and req.arrival_time >= self.t_start:
+            if req.arrival_time >= self.t_start:      # admitted in the region: this is its first token
                 self.ttft.append((now - req.arrival_time) * 1e3)
         else:
             rec[1] = now

@@ -197,7 +197,48 @@ sample_kernel(const void* logits, int64_t ld, int V, const float* __restrict__ t
   }
 }
 
+// Repetition / presence / frequency penalties, in place on the logits of the rows that are about to be
+// sampled. The host lists, per row, the distinct tokens the request has seen (CSR: row_off [B + 1], tok_ids,
+// out_cnt = how often the token was GENERATED, 0 for tokens that only occur in the prompt):
+//   repetition (prompt and output tokens):  l > 0 ? l / rep : l * rep
+//   frequency, presence (output tokens):    l -= freq * count + pres
+// Every (row, token) pair is listed once, so no two threads touch the same logit.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+penalties_kernel(void* logits, int64_t ld, int V, const int* __restrict__ row_off, const int* __restrict__ tok_ids,
+                 const int* __restrict__ out_cnt, const float* __restrict__ rep, const float* __restrict__ pres,
+                 const float* __restrict__ freq, int* status) {
+  const int b = blockIdx.x;
+  const float r = rep[b], p = pres[b], f = freq[b];
+  for (int j = row_off[b] + threadIdx.x; j < row_off[b + 1]; j += blockDim.x) {
+    const int t = tok_ids[j];
+    if (t < 0 || t >= V) {
+      if (status) atomicCAS(status, 0, PXL_DEV_BAD_ROW_ID);
+      continue;
+    }
+    const size_t at = static_cast<size_t>(b) * ld + t;
+    float l = BF16 ? __bfloat162float(static_cast<bf16*>(logits)[at]) : static_cast<float*>(logits)[at];
+    if (r != 1.f) l = l > 0.f ? l / r : l * r;
+    const int c = out_cnt[j];
+    if (c > 0) l -= f * static_cast<float>(c) + p;
+    if (BF16) static_cast<bf16*>(logits)[at] = __float2bfloat16(l);
+    else static_cast<float*>(logits)[at] = l;
+  }
+}
+
 }  // namespace
+
+PXL_EXPORT int pxl_apply_penalties(void* logits, int logits_bf16, int64_t ld, int B, int V, const int* row_off,
+                                   const int* tok_ids, const int* out_cnt, const float* rep, const float* pres,
+                                   const float* freq, int* status, pxl_stream_t stream) {
+  if (B <= 0) return PXL_OK;
+  if (!row_off || !tok_ids || !out_cnt || !rep || !pres || !freq) return PXL_ERR_INVALID_ARG;
+  if (logits_bf16)
+    penalties_kernel<true><<<B, 256, 0, stream>>>(logits, ld, V, row_off, tok_ids, out_cnt, rep, pres, freq, status);
+  else
+    penalties_kernel<false><<<B, 256, 0, stream>>>(logits, ld, V, row_off, tok_ids, out_cnt, rep, pres, freq, status);
+  return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
+}
 
 PXL_EXPORT int pxl_argmax(const void* logits, int logits_bf16, int64_t ld, int B, int V,
                           int* out_ids, float* out_logprob, pxl_stream_t stream) {

@@ -253,8 +253,11 @@ class Engine:
 
     # ------------------------------------------------------------------ sampling
     def _sample(self, logits: torch.Tensor, owners: list[ScheduledSeq]):
+        from parallax_b200.engine.sampling import apply_penalties, build_penalties
+
         sps = [s.req.sampling_params for s in owners]
         want_prob = any(s.req.return_probs for s in owners)
+        logits = apply_penalties(logits, build_penalties([s.req for s in owners]))
         if all(sp.is_greedy for sp in sps):
             if want_prob:
                 ids, lp = ops.argmax(logits, want_logprob=True)
@@ -334,6 +337,14 @@ class Engine:
             else:
                 live.append(s)
         prev = self._in_flight
+        # penalties count the tokens a request has produced: their rows need the previous step's values on
+        # the host, so such a step is not launched ahead of them
+        needs_values = any(s.req.sampling_params.has_penalties for s in live)
+        if needs_values and prev is not None:
+            self._in_flight = None
+            out += self._commit(prev)
+            prev = None
+            live = [s for s in live if not s.req.is_finished]      # ended on the token that was just read
         arrays = self.planner.plan_arrays(live, prev.index if prev is not None else None) if live else None
         for s in live:
             if s.req.is_finished:  # aborted by KV exhaustion during planning
@@ -392,7 +403,7 @@ class Engine:
         self._in_flight = cur
         if prev is not None:
             out += self._commit(prev)
-        if not self.async_scheduling:
+        if not self.async_scheduling or needs_values:
             self._in_flight = None
             out += self._commit(cur)
         self.last_step_stats["wall_s"] = time.perf_counter() - t0

@@ -92,6 +92,10 @@ class PeerExecutor:
         return arrays, out
 
     def _sample(self, logits: torch.Tensor, owners: list[ScheduledSeq]):
+        from parallax_b200.engine.sampling import apply_penalties, build_penalties
+
+        # on the last peer the mirror requests know the prompt; generated tokens arrive with the packets
+        logits = apply_penalties(logits, build_penalties([s.req for s in owners]))
         sps = [s.req.sampling_params for s in owners]
         if all(sp.is_greedy for sp in sps):
             ids, lp = ops.argmax(logits, want_logprob=True)

@@ -56,6 +56,10 @@ class SamplingParams:
     def is_greedy(self) -> bool:
         return self.top_k == 1
 
+    @property
+    def has_penalties(self) -> bool:
+        return self.repetition_penalty != 1.0 or self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
+
     def verify(self) -> None:
         if self.temperature < 0.0:
             raise ValueError(f"temperature must be non-negative, got {self.temperature}.")
@@ -202,6 +206,17 @@ class Request:
         if self.status == RequestStatus.PREFILLING:
             self.status = RequestStatus.DECODING
         self.last_updated_time = now
+
+    def penalty_entries(self) -> tuple[list[int], list[int]]:
+        """Distinct tokens this request has seen and how often each was GENERATED (0 = prompt only): the
+        per-row input of the penalty kernel. Tokens still on the device are not counted."""
+        counts: dict[int, int] = {}
+        for t in self.output_ids:
+            if t != PENDING_TOKEN:
+                counts[t] = counts.get(t, 0) + 1
+        prompt_only = set(self.input_ids).difference(counts)
+        toks = list(counts) + list(prompt_only)
+        return toks, list(counts.values()) + [0] * len(prompt_only)
 
     def reserve_token(self) -> int:
         """Append a placeholder for the token that the step just launched will produce; returns its

@@ -96,6 +96,7 @@ _SIGS = {
     "pxl_msa_select": [_P, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P],
     "pxl_rmsnorm_strided": [_P, c_int64, _P, _P, c_int64, c_int, c_int, c_float, c_float, _P],
     "pxl_argmax": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P],
+    "pxl_apply_penalties": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
     "pxl_sample": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
 }
 

@@ -441,6 +441,19 @@ def argmax(logits: torch.Tensor, want_logprob: bool = False):
     return (ids, lp) if want_logprob else ids
 
 
+def apply_penalties(logits: torch.Tensor, row_off: torch.Tensor, tok_ids: torch.Tensor, out_cnt: torch.Tensor,
+                    rep: torch.Tensor, pres: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+    """Repetition / presence / frequency penalties in place on ``logits [B, V]`` (see ``csrc/sampler.cu``)."""
+    B, V = logits.shape
+    assert logits.stride(1) == 1 and logits.dtype in (torch.bfloat16, torch.float32)
+    check(_lib.lib().pxl_apply_penalties(logits.data_ptr(), int(logits.dtype == torch.bfloat16), logits.stride(0), B, V,
+                                         row_off.data_ptr(), tok_ids.data_ptr(), out_cnt.data_ptr(), rep.data_ptr(),
+                                         pres.data_ptr(), freq.data_ptr(), status_tensor(logits.device).data_ptr(),
+                                         _stream(logits.device)), "pxl_apply_penalties")
+    _count()
+    return logits
+
+
 def sample(
     logits: torch.Tensor,
     temperature: torch.Tensor,

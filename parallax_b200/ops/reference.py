@@ -235,6 +235,26 @@ def argmax(logits, want_logprob: bool = False):
     return ids
 
 
+def apply_penalties(logits, row_off, tok_ids, out_cnt, rep, pres, freq):
+    """In place: repetition penalty on every listed token of a row (``l > 0 ? l / rep : l * rep``), frequency and
+    presence penalties on the tokens that were generated (``l -= freq * count + pres``). Same rules as the GPU
+    backends the reference forwards these parameters to (``src/parallax/sglang/batch_info.py:43-59``)."""
+    B = logits.shape[0]
+    for b in range(B):
+        lo, hi = int(row_off[b]), int(row_off[b + 1])
+        if hi <= lo:
+            continue
+        t = tok_ids[lo:hi].long()
+        c = out_cnt[lo:hi].float()
+        l = logits[b, t].float()
+        r = float(rep[b])
+        if r != 1.0:
+            l = torch.where(l > 0, l / r, l * r)
+        l = l - (c > 0).float() * (float(freq[b]) * c + float(pres[b]))
+        logits[b, t] = l.to(logits.dtype)
+    return logits
+
+
 def patch_ids(dst, dst_idx, src, src_idx) -> None:
     """``dst[dst_idx] = src[src_idx]`` (in place)."""
     if dst_idx.numel():

@@ -409,6 +409,10 @@ class DistEngine:
 
     # ------------------------------------------------------------------ one micro-batch on this rank
     def _sample(self, lp: dict, out: torch.Tensor) -> torch.Tensor:
+        if lp.get("pen") is not None:
+            from parallax_b200.engine.sampling import apply_penalties
+
+            out = apply_penalties(out, lp["pen"])
         if lp["greedy"]:
             return ops.argmax(out)
         dev = out.device
@@ -715,6 +719,11 @@ class DistEngine:
         lp = {k: arrays[k] for k in ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables",
                                      "logit_rows", "seq_rows")}
         lp.update(n_logits=len(owners), greedy=greedy)
+        from parallax_b200.engine.sampling import build_penalties
+
+        pen = build_penalties([s.req for s in owners])
+        if pen is not None:
+            lp["pen"] = pen
         if not greedy:
             lp["sampling"] = {"t": [0.0 if sp.is_greedy else sp.temperature for sp in sps],
                               "k": [sp.top_k if sp.top_k > 0 else 0 for sp in sps], "p": [sp.top_p for sp in sps],

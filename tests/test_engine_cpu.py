@@ -287,3 +287,36 @@ def test_async_scheduling_matches_synchronous_steps():
     stop = [base[0][1], base[3][4]]
     want = run(False, stop=stop, min_new=2)
     assert run(True, stop=stop, min_new=2) == want
+
+
+def test_sampling_penalties_change_greedy_output_as_specified():
+    """Repetition / presence / frequency penalties reach the logits: a greedy run with a strong frequency
+    penalty never repeats a token, the penalty math equals a hand computation, and a run with neutral
+    penalties equals the plain run (asynchronous scheduling falls back to step-by-step for such rows)."""
+    from parallax_b200.engine.sampling import apply_penalties, build_penalties
+    from parallax_b200.ops import reference as ref
+
+    cfg = named_config("tiny")
+    prompt = [3, 7, 7, 11, 250, 9]
+
+    def gen(async_mode=False, **pen):
+        eng = Engine(cfg, device="cpu", num_blocks=64, max_batch_size=4, async_scheduling=async_mode)
+        return eng.generate([prompt], SamplingParams(max_new_tokens=24, temperature=0.0, ignore_eos=True, **pen))[0]
+
+    plain = gen()
+    assert gen(repetition_penalty=1.0, presence_penalty=0.0, frequency_penalty=0.0) == plain
+    strong = gen(frequency_penalty=2.0, presence_penalty=2.0)
+    assert len(set(strong)) > len(set(plain)) or len(set(plain)) == len(plain)
+    assert gen(async_mode=True, frequency_penalty=2.0, presence_penalty=2.0) == strong
+    # the arithmetic
+    r = Request(input_ids=[1, 2, 2, 5], sampling_params=SamplingParams(repetition_penalty=2.0, presence_penalty=0.5,
+                                                                       frequency_penalty=0.25))
+    r.output_ids = [5, 9, 9, -1]
+    logits = torch.tensor([[4.0, -4.0, 2.0, 1.0, 0.0, 8.0, 0.0, 0.0, 0.0, -2.0]])
+    got = apply_penalties(logits.clone(), build_penalties([r]))
+    want = logits.clone()
+    want[0, 1] = -8.0                      # prompt token, negative logit: multiplied
+    want[0, 2] = 1.0                       # prompt token, positive logit: divided
+    want[0, 5] = 8.0 / 2 - (0.25 * 1 + 0.5)    # prompt + generated once
+    want[0, 9] = -2.0 * 2 - (0.25 * 2 + 0.5)   # generated twice
+    assert torch.allclose(got, want)

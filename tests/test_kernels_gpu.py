@@ -391,3 +391,33 @@ def test_linear_picks_mid_m_and_matches(cu):
             y = cu.linear(x, w, residual=r)
             assert _rel_err(y, x.float() @ w.float().t() + r.float()) < 6e-3, (M, N, K, cu.gemm_mid_m_plan(M, N, K))
     cu.check_status(dev)
+
+
+def test_apply_penalties_matches_reference(cu):
+    torch.manual_seed(11)
+    dev = _dev()
+    B, V = 5, 4096
+    for dtype in (torch.float32, torch.bfloat16):
+        logits = (torch.randn(B, V, device=dev) * 3).to(dtype)
+        n_per = [0, 17, 300, 1, 64]
+        row_off = torch.tensor([0] + list(torch.tensor(n_per).cumsum(0)), dtype=torch.int32, device=dev)
+        toks = torch.cat([torch.randperm(V, device=dev)[:n] for n in n_per]).to(torch.int32)
+        cnt = torch.randint(0, 4, (toks.numel(),), dtype=torch.int32, device=dev)
+        rep = torch.tensor([1.0, 1.3, 1.0, 2.0, 0.8], device=dev)
+        pres = torch.tensor([0.0, 0.5, -0.5, 0.0, 1.5], device=dev)
+        freq = torch.tensor([0.0, 0.1, 0.2, 0.0, -0.3], device=dev)
+        want = ref.apply_penalties(logits.clone(), row_off, toks, cnt, rep, pres, freq)
+        got = cu.apply_penalties(logits.clone(), row_off, toks, cnt, rep, pres, freq)
+        assert torch.allclose(got.float(), want.float(), rtol=1e-2 if dtype == torch.bfloat16 else 1e-6, atol=1e-2 if dtype == torch.bfloat16 else 1e-6)
+    cu.check_status(dev)
+
+
+def test_patch_ids(cu):
+    dev = _dev()
+    dst = torch.full((20,), -1, dtype=torch.int32, device=dev)
+    src = torch.arange(100, 110, dtype=torch.int32, device=dev)
+    di = torch.tensor([3, 19, 0], dtype=torch.int32, device=dev)
+    si = torch.tensor([9, 0, 4], dtype=torch.int32, device=dev)
+    cu.patch_ids(dst, di, src, si)
+    assert dst[3] == 109 and dst[19] == 100 and dst[0] == 104 and int((dst == -1).sum()) == 17
+    cu.check_status(dev)
