@@ -184,6 +184,46 @@ class CacheManager:
                 self.on_zero_slot(slot)
         return True, st.matched
 
+    def rematch_request(self, rid: str) -> int:
+        """Probe the prefix cache again for a request whose prompt has not started to run: blocks that
+        another request published since this one was admitted replace its private (still empty) blocks.
+        Hybrid models keep their admission-time match (their state slot was initialised from it).
+        Returns the matched token count."""
+        st = self.reqs.get(rid)
+        if st is None or self.prefix_cache is None or st.tokens is None or self.needs_slots:
+            return st.matched if st is not None else 0
+        have = len(st.nodes)
+        if have * self.block_size != st.matched:
+            return st.matched          # its own blocks are being published already
+        probe = st.tokens[:st.ctx_len - 1] if st.ctx_len else st.tokens[:-1]
+        path = self.prefix_cache.get_path(probe)
+        if len(path) <= have:
+            return st.matched
+        fresh = path[have:]
+        if any(a is not b for a, b in zip(path[:have], st.nodes)):
+            return st.matched          # the tree changed under the old match (evicted and rebuilt): keep it
+        self.allocator.free(self.tables[st.row, have:len(path)].tolist())
+        self.tables[st.row, have:len(path)] = [n.block_id for n in fresh]
+        self.prefix_cache.register_request(rid, fresh)
+        self.prefix_cache.match_prefix(probe)      # statistics and time stamps
+        st.nodes = list(path)
+        st.matched = len(path) * self.block_size
+        return st.matched
+
+    def next_block_key(self, rid: str, computed: int):
+        """Identity of the first block the request still has to compute: (parent tree node, tokens of the
+        block); None when less than a full block is left. Two requests with the same key would compute
+        the same KV block."""
+        st = self.reqs.get(rid)
+        if st is None or st.tokens is None or self.prefix_cache is None:
+            return None
+        bs = self.block_size
+        i = computed // bs
+        if computed % bs or (i + 1) * bs > len(st.tokens) - 1 or i != len(st.nodes):
+            return None
+        parent = st.nodes[-1] if st.nodes else None
+        return (id(parent), tuple(st.tokens[i * bs:(i + 1) * bs]))
+
     def _abort_alloc(self, rid: str, st: _ReqState) -> None:
         if self.prefix_cache is not None:
             self.prefix_cache.release_request(rid)

@@ -6,6 +6,12 @@ nodes they use through lock reference counts; unpinned leaves are evicted in LRU
 report the freed block (and, for hybrid linear-attention models, the state slot snapshot)
 through callbacks. Behavioural counterpart:
 ``src/parallax/server/block_radix_cache.py:74-310``.
+
+Eviction does not walk the tree: the number of unpinned nodes is kept as a counter, and a lazy
+min-heap holds every node at the moment it becomes an unpinned leaf (inserted, unpinned, or left
+without children). Entries are checked when popped - a node that was touched, pinned, extended or
+deleted since is skipped or pushed back with its current time stamp - so evicting k blocks costs
+O(k log n) however large the tree is.
 """
 
 from __future__ import annotations
@@ -50,6 +56,28 @@ class BlockRadixCache:
         self._clock = itertools.count()
         self.hits = 0
         self.queries = 0
+        self._unpinned = 0                 # nodes with lock_ref == 0 (what eviction could free)
+        self._lru: list = []               # lazy heap of (last_access, tie, node) candidates
+        self._tie = itertools.count()
+
+    def _offer(self, node: BlockNode) -> None:
+        """The node may have become an unpinned leaf: make it a candidate for eviction."""
+        if node is not self.root and node.alive and node.lock_ref == 0 and not node.children:
+            heapq.heappush(self._lru, (node.last_access, next(self._tie), node))
+            if len(self._lru) > 4 * self.num_nodes + 4096:
+                self._compact()
+
+    def _compact(self) -> None:
+        """Drop stale heap entries (a node is offered again every time it is unpinned; without eviction
+        pressure nothing pops the old entries). Linear, but only after the heap grew to several times the
+        tree, so its cost is amortised over that many offers."""
+        seen, keep = set(), []
+        for _stamp, tie, n in self._lru:
+            if n.alive and n.lock_ref == 0 and not n.children and id(n) not in seen:
+                seen.add(id(n))
+                keep.append((n.last_access, tie, n))
+        heapq.heapify(keep)
+        self._lru = keep
 
     # ------------------------------------------------------------------ lookup
     def _tick(self) -> float:
@@ -114,17 +142,24 @@ class BlockRadixCache:
         node.linear_slot = linear_slot
         parent.children[key] = node
         self.num_nodes += 1
+        self._unpinned += 1
+        self._offer(node)
         return node, True
 
     # ------------------------------------------------------------------ pinning
     def increase_lock_ref(self, nodes: list[BlockNode]) -> None:
         for n in nodes:
+            if n.lock_ref == 0:
+                self._unpinned -= 1
             n.lock_ref += 1
 
     def decrease_lock_ref(self, nodes: list[BlockNode]) -> None:
         for n in nodes:
             if n.lock_ref > 0:
                 n.lock_ref -= 1
+                if n.lock_ref == 0:
+                    self._unpinned += 1
+                    self._offer(n)
 
     def register_request(self, request_id: str, nodes: list[BlockNode]) -> None:
         self.increase_lock_ref(nodes)
@@ -139,36 +174,29 @@ class BlockRadixCache:
             self.decrease_lock_ref(nodes)
 
     # ------------------------------------------------------------------ eviction
-    def _evictable_leaves(self) -> list[BlockNode]:
-        out, stack = [], [self.root]
-        while stack:
-            n = stack.pop()
-            if n.children:
-                stack.extend(n.children.values())
-            elif n is not self.root and n.lock_ref == 0:
-                out.append(n)
-        return out
-
     def evict_lru_blocks(self, num_blocks: int) -> int:
         """Evict up to ``num_blocks`` unpinned leaf blocks, least recently used first."""
-        heap = [(n.last_access, id(n), n) for n in self._evictable_leaves()]
-        heapq.heapify(heap)
         evicted = 0
+        heap = self._lru
         while heap and evicted < num_blocks:
-            _, _, n = heapq.heappop(heap)
+            stamp, _, n = heapq.heappop(heap)
             if not n.alive or n.children or n.lock_ref > 0:
+                continue                          # deleted, extended or pinned since it was offered
+            if stamp != n.last_access:
+                self._offer(n)                    # touched since: back in line with its current time
                 continue
             parent = n.parent
             self._delete_leaf(n)
             evicted += 1
-            if parent is not self.root and not parent.children and parent.lock_ref == 0:
-                heapq.heappush(heap, (parent.last_access, id(parent), parent))
+            if parent is not self.root:
+                self._offer(parent)               # it may have become a leaf
         return evicted
 
     def _delete_leaf(self, node: BlockNode) -> None:
         node.alive = False
         del node.parent.children[node.key]
         self.num_nodes -= 1
+        self._unpinned -= 1
         if self.on_evict_block is not None:
             self.on_evict_block(node.block_id)
         if node.linear_slot is not None and self.on_evict_linear_slot is not None:
@@ -176,14 +204,8 @@ class BlockRadixCache:
 
     def evictable_size(self) -> int:
         """Blocks that eviction could free. Requests pin whole root-to-node paths, so an
-        unpinned node never has a pinned descendant and counting unpinned nodes is exact."""
-        n_free, stack = 0, list(self.root.children.values())
-        while stack:
-            n = stack.pop()
-            stack.extend(n.children.values())
-            if n.lock_ref == 0:
-                n_free += 1
-        return n_free
+        unpinned node never has a pinned descendant and the count of unpinned nodes is exact."""
+        return self._unpinned
 
     def get_stats(self) -> dict:
         return {
@@ -206,4 +228,6 @@ class BlockRadixCache:
             if n.linear_slot is not None and self.on_evict_linear_slot is not None:
                 self.on_evict_linear_slot(n.linear_slot)
         self.num_nodes = 0
+        self._unpinned = 0
+        self._lru = []
         self.request_to_nodes.clear()

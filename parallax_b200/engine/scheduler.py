@@ -200,11 +200,27 @@ class BatchScheduler:
         used = 0
         chunk = self.chunked_prefill_size
         prefill_cap = self.max_prefill_tokens_per_batch
+        cm = self.cache_manager
+        starting: set = set()      # first blocks that prompts of this batch are about to compute
         for req in prefills:
             if len(batch) >= self.micro_batch_size:
                 break
             if prefill_cap is not None and used >= prefill_cap:
                 break
+            if cm is not None and cm.prefix_cache is not None and req.num_computed_tokens == req.num_cached_tokens \
+                    and not req.output_ids:
+                # a prompt that has not started: blocks published since its admission are reused, and if
+                # another prompt of this very batch computes its first missing block it waits one step
+                # (the block is published when that batch is launched) instead of computing it twice
+                matched = cm.rematch_request(req.request_id)
+                if matched > req.num_cached_tokens:
+                    req.num_cached_tokens = matched
+                    req.num_computed_tokens = max(req.num_computed_tokens, matched)
+                key = cm.next_block_key(req.request_id, req.num_computed_tokens)
+                if key is not None:
+                    if key in starting:
+                        continue
+                    starting.add(key)
             remaining = req.remaining_prefill
             if remaining <= 0:
                 # whole prompt is cached: recompute the last token to obtain logits
