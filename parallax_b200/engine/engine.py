@@ -66,13 +66,18 @@ class Planner:
                  max_num_tokens_per_batch: int, micro_batch_ratio: int = 1,
                  chunked_prefill_size: Optional[int] = 1024, enable_prefix_cache: bool = True,
                  max_total_length: int = 32768, request_timeout_s: Optional[float] = 600,
-                 eos_token_id=None, shared_state=None):
+                 eos_token_id=None, shared_state=None, linear_prefix_slots: int = 0):
         self.cfg = cfg
         self.page_size = page_size
         max_blocks_per_seq = (max_total_length + page_size - 1) // page_size + 1
-        self.cache = CacheManager(num_blocks, page_size, max_requests=max(max_batch_size * 2, 16),
+        max_requests = max(max_batch_size * 2, 16)
+        # hybrid models: a request's recurrent state lives in a slot of its own, and the prefix cache keeps
+        # snapshots of that state at block boundaries (`linear_prefix_slots` of them) to resume from
+        hybrid_slots = max_requests if (cfg.has_linear_layers and enable_prefix_cache and linear_prefix_slots > 0) else 0
+        self.cache = CacheManager(num_blocks, page_size, max_requests=max_requests,
                                   max_blocks_per_seq=max_blocks_per_seq,
-                                  enable_prefix_cache=enable_prefix_cache)
+                                  enable_prefix_cache=enable_prefix_cache, num_linear_slots=hybrid_slots,
+                                  num_prefix_linear_slots=linear_prefix_slots if hybrid_slots else 0)
         self.scheduler = BatchScheduler(
             max_batch_size=max_batch_size, max_num_tokens_per_batch=max_num_tokens_per_batch,
             micro_batch_ratio=micro_batch_ratio, cache_manager=self.cache,
@@ -87,6 +92,7 @@ class Planner:
         previous (still unread) step sampled. Decode rows of those requests get their input id on the
         device: the result carries ``patch_rows`` / ``patch_src`` for :func:`ops.patch_ids`."""
         cache, bs = self.cache, self.page_size
+        state_slot = cache.get_slot if cache.needs_slots else cache.get_row     # slot of the recurrent state
         prefill = [s for s in seqs if s.is_prefill]
         decode = []
         for s in seqs:
@@ -149,7 +155,10 @@ class Planner:
         maxb_d = (int(d_ctx.max()) + bs - 1) // bs if len(decode) else 0
         p_tables = cache.tables[np.asarray(p_rows, dtype=np.int64), :maxb_p] if prefill else None
         d_tables = cache.tables[d_rows, :maxb_d] if len(decode) else None
-        seq_rows = np.concatenate([np.asarray(p_rows, dtype=np.int32), d_rows])
+        if cache.needs_slots:
+            seq_rows = np.fromiter((state_slot(s.req.request_id) for s in ordered), dtype=np.int32, count=len(ordered))
+        else:
+            seq_rows = np.concatenate([np.asarray(p_rows, dtype=np.int32), d_rows])
         return dict(ordered=ordered, ids=ids, pos=pos, slots=slots, p_q=p_q, p_ctx=p_ctx,
                     p_tables=p_tables, d_ctx=d_ctx, d_tables=d_tables,
                     logit_rows=np.asarray(logit_rows, dtype=np.int32), owners=owners, seq_rows=seq_rows,
@@ -181,6 +190,7 @@ class Engine:
         wire_hook: Optional[Callable] = None,
         trace=None,
         async_scheduling: Optional[bool] = None,
+        linear_prefix_slots: Optional[int] = None,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -189,9 +199,14 @@ class Engine:
         max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
         self.stages: list[StageWorker] = []
         max_requests = max(max_batch_size * 2, 16)
-        if cfg.has_linear_layers:
-            # a recurrent state cannot be rebuilt from cached KV pages of a shared prefix
-            enable_prefix_cache = False
+        # hybrid models resume a shared prefix from a snapshot of the recurrent state taken at a block
+        # boundary (a recurrent state cannot be rebuilt from cached KV pages); the snapshots live in extra
+        # state slots behind the requests' own
+        self.linear_prefix_slots = 0
+        if cfg.has_linear_layers and enable_prefix_cache:
+            self.linear_prefix_slots = linear_prefix_slots if linear_prefix_slots is not None else 32
+            if self.linear_prefix_slots <= 0:
+                enable_prefix_cache = False
         for (s, e) in stage_layers:
             w = None
             if weights is not None:
@@ -201,13 +216,18 @@ class Engine:
             self.stages.append(StageWorker(cfg, s, e, self.device, dtype, page_size, num_blocks=num_blocks,
                                            kv_fraction=kv_fraction / len(stage_layers), seed=seed, weights=w,
                                            max_kv_tokens=max_kv_tokens, max_positions=max_positions,
-                                           num_linear_slots=max_requests if cfg.has_linear_layers else 0))
+                                           num_linear_slots=(max_requests + self.linear_prefix_slots)
+                                           if cfg.has_linear_layers else 0))
         nb = min(st.num_blocks for st in self.stages)
         self.planner = Planner(cfg, nb, page_size, max_batch_size, max_num_tokens_per_batch,
                                micro_batch_ratio, chunked_prefill_size, enable_prefix_cache,
-                               max_total_length, request_timeout_s, eos_token_id, shared_state)
+                               max_total_length, request_timeout_s, eos_token_id, shared_state,
+                               linear_prefix_slots=self.linear_prefix_slots)
         self.scheduler = self.planner.scheduler
         self.cache = self.planner.cache
+        if self.cache.needs_slots:
+            # a request that matched a snapshot starts from a copy of it (enqueued before its first step)
+            self.cache.on_copy_slot = self._copy_state_slot
         max_blocks = self.cache.max_blocks_per_seq
         self.builder = BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size,
                                     max_batch_size, max_blocks)
@@ -273,6 +293,14 @@ class Engine:
         if want_prob:
             return ops.sample(logits, temperature, top_k, top_p, min_p, u, want_prob=True)
         return ops.sample(logits, temperature, top_k, top_p, min_p, u), None
+
+    def _copy_state_slot(self, dst: int, src: int) -> None:
+        for st in self.stages:
+            st.pool.copy_slot(dst, src)
+
+    def _snapshot_state(self, src_slot: int, dst_slot: int) -> None:
+        """Keep the recurrent state of a request as of the block boundary it just reached."""
+        self._copy_state_slot(dst_slot, src_slot)
 
     # ------------------------------------------------------------------ device status word
     def _queue_status_read(self) -> None:
@@ -442,7 +470,8 @@ class Engine:
             req = s.req
             if s.is_prefill:
                 req.num_computed_tokens = s.start + s.num_tokens
-                cache.insert_full_blocks_to_cache(req.request_id, req.num_computed_tokens)
+                cache.insert_full_blocks_to_cache(req.request_id, req.num_computed_tokens,
+                                                  snapshot_linear=self._snapshot_state if cache.needs_slots else None)
             if id(s) in owner_ids:
                 k = req.reserve_token()
                 cur.slot_index.append(k)

@@ -66,27 +66,68 @@ def test_gpu_engine_matches_cpu_engine():
         assert g.shape == c.shape
         rel = (g - c).norm() / c.norm()
         assert rel < 3e-2, rel
-        agree = (g.argmax(-1) == c.argmax(-1)).float().mean()
-        assert agree >= 0.7
+        # margin-aware arg-max check: with N(0, 0.02) weights many rows are near-ties, so a row counts when
+        # the fp32 gap between its two best tokens exceeds four times the largest logit error of that row;
+        # every such row must agree
+        top2 = c.topk(2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 4 * (g - c).abs().amax(dim=-1)
+        assert clear.float().mean() >= 0.4, clear
+        assert bool((g.argmax(-1) == c.argmax(-1))[clear].all())
+
+
+def _generate_with_margins(eng, prompts, sp):
+    """Tokens per prompt and, per generated token, the gap between the two best logits it was chosen from."""
+    reqs = [Request(input_ids=list(p), sampling_params=SamplingParams.from_dict(sp.to_dict())) for p in prompts]
+    for r in reqs:
+        eng.add_request(r)
+    eng.keep_logits = True
+    gaps = {r.request_id: [] for r in reqs}
+    noise = 0.0
+    while eng.has_work():
+        results = eng.step()
+        lg = eng.last_logits.float()
+        produced = [rq for rq, tok in results if tok is not None]
+        assert len(produced) == lg.shape[0]
+        top2 = lg.topk(2, dim=-1).values
+        noise = max(noise, 0.04 * float(lg.std()))
+        for rq, gap in zip(produced, (top2[:, 0] - top2[:, 1]).tolist()):
+            gaps[rq.request_id].append(gap)
+    return [r.output_ids for r in reqs], [gaps[r.request_id] for r in reqs], noise
+
+
+def _agree_where_clear(a, b, gaps_b, noise):
+    """(tokens compared, tokens equal): each sequence is compared up to its first step whose margin in run b
+    is below the noise of a different summation order (after such a step the runs may legitimately part)."""
+    compared = equal = 0
+    for x, y, gp in zip(a, b, gaps_b):
+        for i, (u, v) in enumerate(zip(x, y)):
+            if gp[i] < noise:
+                break
+            compared += 1
+            equal += int(u == v)
+    return compared, equal
 
 
 def test_gpu_sharded_chunked_prefix_consistency():
     prompts = _prompts(6, 150, 2048, seed=2)
     sp = SamplingParams(max_new_tokens=12, temperature=0.0, ignore_eos=True)
-    base = Engine(_cfg(), device="cuda:0", num_blocks=256, max_batch_size=8, chunked_prefill_size=None,
-                  enable_prefix_cache=False).generate(prompts, sp)
-    shard = Engine(_cfg(), device="cuda:0", num_blocks=256, max_batch_size=8, chunked_prefill_size=None,
-                   enable_prefix_cache=False, stage_layers=[(0, 2), (2, 4)]).generate(prompts, sp)
+    kw = dict(device="cuda:0", num_blocks=256, max_batch_size=8, async_scheduling=False)
+    base, base_gaps, noise = _generate_with_margins(
+        Engine(_cfg(), chunked_prefill_size=None, enable_prefix_cache=False, **kw), prompts, sp)
+    shard = Engine(_cfg(), chunked_prefill_size=None, enable_prefix_cache=False, stage_layers=[(0, 2), (2, 4)],
+                   **kw).generate(prompts, sp)
     assert base == shard
-    eng = Engine(_cfg(), device="cuda:0", num_blocks=256, max_batch_size=8, chunked_prefill_size=64)
+    eng = Engine(_cfg(), chunked_prefill_size=64, **kw)
     a = eng.generate(prompts, sp)
     b = eng.generate(prompts, sp)  # served from the prefix cache
     assert eng.cache.prefix_cache.hits >= 6
-    # chunking and cached prefixes change the reduction order slightly; most sequences agree
-    same = sum(x == y for x, y in zip(a, b))
-    assert same >= 4
-    match_base = sum(x[:4] == y[:4] for x, y in zip(a, base))
-    assert match_base >= 4
+    # chunking and cached prefixes change the reduction order: tokens chosen with a clear margin must not move
+    for other in (a, b):
+        compared, equal = _agree_where_clear(other, base, base_gaps, noise)
+        assert compared >= 12 and equal == compared, (compared, equal)
+    # and the asynchronous schedule produces exactly what the step-by-step schedule does
+    assert Engine(_cfg(), device="cuda:0", num_blocks=256, max_batch_size=8, chunked_prefill_size=None,
+                  enable_prefix_cache=False, async_scheduling=True).generate(prompts, sp) == base
 
 
 def test_gpu_sampling_requests_finish():
@@ -124,3 +165,44 @@ def test_native_stage_executor_equals_python_layer_loop():
     eng.step()
     p2 = eng.last_logits.float().cpu()
     assert torch.equal(n1, p1) and torch.equal(n2, p2)
+
+
+def test_long_context_chunked_prefill_32k():
+    """A 32768-token prompt on a two-layer Qwen3-32B-shaped model: prefilled in 8192-token chunks (each chunk
+    attends to the chunks before it through the block table) it must give the logits and tokens of the same
+    prompt prefilled in one pass, and decode attention over the 32k context must continue from there."""
+    from parallax_b200.models.config import named_config
+    from parallax_b200.ops import cuda as cu
+
+    cfg = named_config("qwen3-32b")
+    cfg.num_hidden_layers = 2
+    n_ctx = 32768
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab_size, (n_ctx,), generator=g).tolist()
+    sp = SamplingParams(max_new_tokens=6, temperature=0.0, ignore_eos=True)
+
+    def run(chunk):
+        eng = Engine(cfg, device="cuda:0", page_size=16, num_blocks=2200, max_batch_size=2,
+                     max_num_tokens_per_batch=n_ctx + 64, chunked_prefill_size=chunk, enable_prefix_cache=False,
+                     max_total_length=n_ctx + 64, async_scheduling=False, seed=1)
+        eng.keep_logits = True
+        r = Request(input_ids=prompt, sampling_params=SamplingParams.from_dict(sp.to_dict()), max_total_length=n_ctx + 64)
+        eng.add_request(r)
+        steps, first = 0, None
+        while eng.has_work():
+            res = eng.step()
+            steps += 1
+            if first is None and any(tok is not None for _rq, tok in res):
+                first = eng.last_logits.float().cpu()
+        cu.check_status(torch.device("cuda:0"))
+        return r.output_ids, first, steps
+
+    one, lg_one, steps_one = run(n_ctx)
+    four, lg_four, steps_four = run(8192)
+    assert steps_four == steps_one + 3                       # four prompt slices instead of one
+    rel = float((lg_four - lg_one).norm() / lg_one.norm())
+    assert rel < 3e-2, rel
+    top2 = lg_one.topk(2, dim=-1).values
+    if float(top2[0, 0] - top2[0, 1]) > 4 * float((lg_four - lg_one).abs().max()):
+        assert four[0] == one[0]
+    assert len(four) == len(one) == 6

@@ -68,5 +68,30 @@ def test_hybrid_chunked_prefill_and_slots_are_consistent():
     b = Engine(cfg, device="cpu", num_blocks=64, page_size=16, max_batch_size=2, max_num_tokens_per_batch=256,
                chunked_prefill_size=None, max_total_length=256).generate(prompts, sp)
     assert a == b
-    eng = Engine(cfg, device="cpu", num_blocks=64, page_size=16, max_batch_size=4)
-    assert eng.cache.prefix_cache is None      # recurrent state cannot be restored from cached pages
+    eng = Engine(cfg, device="cpu", num_blocks=64, page_size=16, max_batch_size=4, linear_prefix_slots=0)
+    assert eng.cache.prefix_cache is None      # without snapshot slots a recurrent state cannot be resumed
+
+
+def test_hybrid_prefix_cache_resumes_from_state_snapshots():
+    """Requests that share a prefix reuse its KV pages AND the recurrent state as of the end of the prefix:
+    the state is snapshotted when a prompt slice ends on a block boundary, and a later request starts from a
+    copy of the snapshot. Outputs must equal a run without any prefix caching."""
+    cfg = named_config("tiny-hybrid")
+    g = torch.Generator().manual_seed(9)
+    shared = torch.randint(0, cfg.vocab_size, (64,), generator=g).tolist()
+    tails = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 21, 3, 40)]
+    prompts = [shared + t for t in tails]
+    sp = SamplingParams(max_new_tokens=5, temperature=0.0, ignore_eos=True)
+    kw = dict(device="cpu", num_blocks=128, page_size=16, max_batch_size=4, max_num_tokens_per_batch=256,
+              chunked_prefill_size=32, max_total_length=256)
+    want = Engine(cfg, linear_prefix_slots=0, **kw).generate(prompts, sp)
+    eng = Engine(cfg, linear_prefix_slots=8, **kw)
+    assert eng.cache.prefix_cache is not None and eng.cache.needs_slots
+    first = eng.generate(prompts[:1], sp)             # computes the prefix, snapshots at 32 and 64 tokens
+    rest = eng.generate(prompts[1:], sp)              # resume from the snapshot at 64 tokens
+    assert first + rest == want
+    assert eng.cache.prefix_cache.hits >= 3
+    snap = [n for n in eng.cache.prefix_cache.get_path(shared) if n.linear_slot is not None]
+    assert len(snap) >= 1 and snap[-1] is eng.cache.prefix_cache.get_path(shared)[-1]
+    again = eng.generate(prompts, sp)                 # everything cached now, still the same tokens
+    assert again == want
