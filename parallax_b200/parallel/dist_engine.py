@@ -358,8 +358,12 @@ class DistEngine:
             slot.buf = torch.empty((max(rows, 256), H), dtype=self.worker.dtype, device=self.device)
             slot.free = None
         hidden = slot.buf[:rows]
-        if self.device.type != "cuda":
+        if self.device.type != "cuda" or self.topo.tp > 1:
+            # tensor-parallel stages keep the receive in stream order: their fused GEMM + collective kernels
+            # spread one CTA over every SM and wait on each other, so no other kernel may sit on an SM
+            # beside them (a receive that waits for its sender would)
             dist.recv(hidden, src=self._prev(), group=self.hop_in)
+            slot.free = None
             return hidden
         arrived = torch.cuda.Event()
         with torch.cuda.stream(self._recv_stream):

@@ -254,6 +254,21 @@ class EPComm:
         self._ws: Optional[EPWorkspace] = None
         self.step_max_rows: Optional[int] = None     # set by the engine per step: largest row count over the ranks
 
+    def _warm_up(self, moe, dtype) -> None:
+        """First use: one exchange without rows, between two host barriers. The kernels of an exchange wait
+        for their peers on the device for at most a second or so; loading the kernels and allocating their
+        scratch for the first time can take a rank longer than that, so this first round is run with every
+        rank known to be at the same point, and serving starts with everything resident."""
+        H, k = self._ws.H, self._ws.k
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        x0 = torch.empty((0, H), dtype=dtype, device=self.device)
+        ep_moe_ffn(self._ws, x0, 0, torch.empty((0, k), dtype=torch.int32, device=self.device),
+                   torch.empty((0, k), dtype=torch.float32, device=self.device), moe.w1, moe.w2, moe.experts_per_rank,
+                   max_rows=1, fp8=moe.fp8, act_mode=moe.act_mode, limit=moe.limit, b1=moe.b1, b2=moe.b2)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
     def moe_ffn(self, moe, xn: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, base=None) -> torch.Tensor:
         """``base + MoE(xn)`` for this rank's rows; ``moe`` is the layer's (expert-sharded) MoEWeights."""
         from parallax_b200 import ops
@@ -271,6 +286,7 @@ class EPComm:
             return ep_moe_ffn_ragged(self.group, xn, ids, weights, local_ffn, epr, base=base)
         if self._ws is None:
             self._ws = EPWorkspace(self.group, self.device, self.ep, self.rank, self.max_rows, ids.shape[1], xn.shape[1])
+            self._warm_up(moe, xn.dtype)
         return ep_moe_ffn(self._ws, xn, xn.shape[0], ids.contiguous(), weights.contiguous(), moe.w1, moe.w2, epr,
                           base=base, max_rows=self.step_max_rows, fp8=moe.fp8, act_mode=moe.act_mode,
                           limit=moe.limit, b1=moe.b1, b2=moe.b2)

@@ -116,4 +116,11 @@ def main() -> None:
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        import traceback
+
+        with open(f"{sys.argv[2]}.rank{os.environ.get('RANK', '0')}.err", "w") as f:
+            traceback.print_exc(file=f)
+        raise

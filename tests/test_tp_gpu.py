@@ -33,7 +33,11 @@ def _run_dist(mode, tmp_path, port, nproc=2):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", str(nproc), "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "tests", "helpers", "dist_engine_gpu_rank.py"), mode, str(out)]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
-    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    if res.returncode != 0:
+        import glob
+
+        errs = "".join(f"\n--- {p}\n" + open(p).read()[-2500:] for p in sorted(glob.glob(f"{out}.rank*.err")))
+        raise AssertionError(errs + res.stderr[-1500:])
     return json.loads(out.read_text())
 
 
