@@ -2,6 +2,7 @@
 
     python benchmarks/profile_case.py gemm         # bf16 tcgen05 GEMM, 4096 x 8192 x 8192
     python benchmarks/profile_case.py gemm_small   # split-K small-M GEMM, 64 x 4096 x 4096
+    python benchmarks/profile_case.py gemm_mid     # mid-M cluster split-K GEMM, 320 x 4096 x 12288
     python benchmarks/profile_case.py attn_decode  # paged GQA decode, 256 seqs x 2048 ctx
     python benchmarks/profile_case.py attn_prefill # ragged prefill, 4 x 2048
     python benchmarks/profile_case.py step         # 2 engine steps of a 4-layer Qwen3-8B-shaped
@@ -52,6 +53,24 @@ def case_gemm_small(iters: int = 3, M: int = 64, N: int = 4096, K: int = 4096):
     torch.cuda.cudart().cudaProfilerStart()
     for i in range(iters):
         cu.linear_small_m(x, ws[i % 8], out=out)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    cu.check_status(x.device)
+
+
+def case_gemm_mid(iters: int = 3, M: int = 320, N: int = 4096, K: int = 12288):
+    """Pipeline-stage micro-batch GEMM on the cluster split-K path (what ``linear`` picks for this shape);
+    a fresh weight matrix per launch (8 x 100 MB > L2)."""
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(8)]
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    print("plan (tile width, K ranges):", cu.gemm_mid_m_plan(M, N, K))
+    for w in ws:
+        cu.linear(x, w, out=out)
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStart()
+    for i in range(iters):
+        cu.linear(x, ws[i % 8], out=out)
     torch.cuda.synchronize()
     torch.cuda.cudart().cudaProfilerStop()
     cu.check_status(x.device)
@@ -138,6 +157,6 @@ def case_step(steps: int = 2, conc: int = 64, with_prefill: bool = True):
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": case_gemm, "attn_decode": case_attn_decode, "attn_prefill": case_attn_prefill,
-     "gemm_small": case_gemm_small, "step": case_step, "decode_step": lambda: case_step(conc=64, with_prefill=False),
+     "gemm_small": case_gemm_small, "gemm_mid": case_gemm_mid, "step": case_step, "decode_step": lambda: case_step(conc=64, with_prefill=False),
      "decode_step_8": lambda: case_step(conc=8, with_prefill=False)}[which]()
     print(f"profile case {which}: ok")

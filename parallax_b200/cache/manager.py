@@ -27,7 +27,7 @@ logger = logging.getLogger(__name__)
 
 
 class _ReqState:
-    __slots__ = ("row", "num_blocks", "ctx_len", "matched", "tokens", "nodes", "linear_slot")
+    __slots__ = ("row", "num_blocks", "ctx_len", "matched", "tokens", "nodes", "linear_slot", "namespace")
 
     def __init__(self, row: int):
         self.row = row
@@ -37,6 +37,7 @@ class _ReqState:
         self.tokens: Optional[list[int]] = None
         self.nodes: list[BlockNode] = []   # tree nodes backing the first len(nodes) blocks
         self.linear_slot = -1
+        self.namespace = None              # prefix-cache namespace (e.g. the LoRA adapter the request runs under)
 
 
 class CacheManager:
@@ -125,8 +126,9 @@ class CacheManager:
         return len(self.prefix_cache.get_path(token_ids[:-1])) * self.block_size
 
     # ------------------------------------------------------------------ allocation
-    def allocate_request(self, rid: str, prompt_len: int, token_ids=None) -> tuple[bool, int]:
-        """Reserve blocks for the whole prompt. Returns (ok, tokens matched in prefix cache)."""
+    def allocate_request(self, rid: str, prompt_len: int, token_ids=None, namespace=None) -> tuple[bool, int]:
+        """Reserve blocks for the whole prompt. Returns (ok, tokens matched in prefix cache). ``namespace``:
+        requests only share cached blocks with requests of the same namespace."""
         st = self.reqs.get(rid)
         if st is not None:
             return True, st.matched
@@ -137,13 +139,14 @@ class CacheManager:
         if row < 0:
             return False, 0
         st = _ReqState(row)
+        st.namespace = namespace
         matched_blocks: list[int] = []
         if self.prefix_cache is not None and token_ids is not None:
             st.tokens = list(token_ids)
             probe = st.tokens[:-1]
-            matched_blocks, matched = self.prefix_cache.match_prefix(probe)
+            matched_blocks, matched = self.prefix_cache.match_prefix(probe, namespace)
             if matched:
-                nodes = self.prefix_cache.get_path(probe[:matched])
+                nodes = self.prefix_cache.get_path(probe[:matched], namespace)
                 if len(nodes) != len(matched_blocks):
                     matched_blocks, matched = [], 0
                 else:
@@ -196,7 +199,7 @@ class CacheManager:
         if have * self.block_size != st.matched:
             return st.matched          # its own blocks are being published already
         probe = st.tokens[:st.ctx_len - 1] if st.ctx_len else st.tokens[:-1]
-        path = self.prefix_cache.get_path(probe)
+        path = self.prefix_cache.get_path(probe, st.namespace)
         if len(path) <= have:
             return st.matched
         fresh = path[have:]
@@ -205,7 +208,7 @@ class CacheManager:
         self.allocator.free(self.tables[st.row, have:len(path)].tolist())
         self.tables[st.row, have:len(path)] = [n.block_id for n in fresh]
         self.prefix_cache.register_request(rid, fresh)
-        self.prefix_cache.match_prefix(probe)      # statistics and time stamps
+        self.prefix_cache.match_prefix(probe, st.namespace)      # statistics and time stamps
         st.nodes = list(path)
         st.matched = len(path) * self.block_size
         return st.matched
@@ -222,7 +225,7 @@ class CacheManager:
         if computed % bs or (i + 1) * bs > len(st.tokens) - 1 or i != len(st.nodes):
             return None
         parent = st.nodes[-1] if st.nodes else None
-        return (id(parent), tuple(st.tokens[i * bs:(i + 1) * bs]))
+        return (id(parent) if parent is not None else ("root", st.namespace), tuple(st.tokens[i * bs:(i + 1) * bs]))
 
     def _abort_alloc(self, rid: str, st: _ReqState) -> None:
         if self.prefix_cache is not None:
@@ -322,7 +325,8 @@ class CacheManager:
         while len(st.nodes) < full:
             i = len(st.nodes)
             block_id = int(self.tables[st.row, i])
-            node, is_new = self.prefix_cache.insert_block(st.nodes, st.tokens[i * bs:(i + 1) * bs], block_id)
+            node, is_new = self.prefix_cache.insert_block(st.nodes, st.tokens[i * bs:(i + 1) * bs], block_id,
+                                                          namespace=st.namespace)
             if not is_new:
                 if node.block_id != block_id:
                     # same content already cached by someone else: keep our private copy

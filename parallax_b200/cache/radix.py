@@ -83,10 +83,24 @@ class BlockRadixCache:
     def _tick(self) -> float:
         return time.monotonic() + next(self._clock) * 1e-9
 
-    def get_path(self, token_ids) -> list[BlockNode]:
+    def root_of(self, namespace=None) -> BlockNode:
+        """Root of the tree for a namespace. KV blocks depend on everything that shaped them, not only on the
+        tokens: requests that run under a LoRA adapter must not share blocks with the base model or with
+        another adapter, so each adapter name gets a tree of its own under a permanent pseudo-node."""
+        if namespace is None:
+            return self.root
+        key = ("namespace", namespace)
+        node = self.root.children.get(key)
+        if node is None:
+            node = BlockNode(key, -1, self.root)
+            node.lock_ref = 1                      # never evicted, never counted
+            self.root.children[key] = node
+        return node
+
+    def get_path(self, token_ids, namespace=None) -> list[BlockNode]:
         """Nodes along the longest fully matching block path (no side effects)."""
         bs = self.block_size
-        node, path = self.root, []
+        node, path = self.root_of(namespace), []
         for i in range(0, len(token_ids) - bs + 1, bs):
             child = node.children.get(tuple(token_ids[i:i + bs]))
             if child is None:
@@ -95,14 +109,14 @@ class BlockRadixCache:
             node = child
         return path
 
-    def match_prefix(self, token_ids) -> tuple[list[int], int]:
+    def match_prefix(self, token_ids, namespace=None) -> tuple[list[int], int]:
         """Longest cached prefix in whole blocks: (block ids, matched token count).
 
         With ``require_linear_slot`` the match is cut back to the deepest node that carries
         a linear-state snapshot, because a hybrid model can only resume from such a node.
         """
         self.queries += 1
-        path = self.get_path(token_ids)
+        path = self.get_path(token_ids, namespace)
         if self.require_linear_slot:
             while path and path[-1].linear_slot is None:
                 path.pop()
@@ -121,14 +135,14 @@ class BlockRadixCache:
 
     # ------------------------------------------------------------------ insert
     def insert_block(self, prefix_nodes: list[BlockNode], block_tokens, block_id: int,
-                     linear_slot: Optional[int] = None) -> tuple[BlockNode, bool]:
+                     linear_slot: Optional[int] = None, namespace=None) -> tuple[BlockNode, bool]:
         """Insert one full block under the path ``prefix_nodes``.
 
         Returns (node, inserted). If the block is already cached the existing node is
         returned with ``inserted=False`` and the caller keeps ownership of ``block_id``.
         """
         assert len(block_tokens) == self.block_size
-        parent = prefix_nodes[-1] if prefix_nodes else self.root
+        parent = prefix_nodes[-1] if prefix_nodes else self.root_of(namespace)
         key = tuple(block_tokens)
         node = parent.children.get(key)
         if node is not None:
@@ -188,7 +202,7 @@ class BlockRadixCache:
             parent = n.parent
             self._delete_leaf(n)
             evicted += 1
-            if parent is not self.root:
+            if parent is not self.root and parent.block_id >= 0:
                 self._offer(parent)               # it may have become a leaf
         return evicted
 
@@ -223,6 +237,8 @@ class BlockRadixCache:
             n = stack.pop()
             stack.extend(n.children.values())
             n.alive = False
+            if n.block_id < 0:
+                continue                          # namespace pseudo-node
             if self.on_evict_block is not None:
                 self.on_evict_block(n.block_id)
             if n.linear_slot is not None and self.on_evict_linear_slot is not None:

@@ -191,6 +191,7 @@ class Engine:
         trace=None,
         async_scheduling: Optional[bool] = None,
         linear_prefix_slots: Optional[int] = None,
+        lora: Optional[dict] = None,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -244,6 +245,18 @@ class Engine:
                 self._host_slots.append({"ids": torch.empty(max(max_batch_size, 16), dtype=torch.int32, pin_memory=True),
                                          "probs": torch.empty(max(max_batch_size, 16), dtype=torch.float32, pin_memory=True),
                                          "event": torch.cuda.Event()})
+        # per-request LoRA adapters: {"max_loaded": slots, "max_rank": r, "paths": {name: dir}}
+        self.lora = None
+        if lora:
+            from parallax_b200.loader.lora import LoRAManager, LoRAStack
+
+            stacks = []
+            for st in self.stages:
+                if not hasattr(st.model, "lora"):
+                    raise ValueError(f"per-request LoRA adapters are not available for {cfg.architecture}")
+                st.model.lora = LoRAStack(st.model, int(lora.get("max_loaded") or 4), int(lora.get("max_rank") or 64))
+                stacks.append(st.model.lora)
+            self.lora = LoRAManager(stacks, int(lora.get("max_loaded") or 4), lora.get("paths"))
         self.wire_hook = wire_hook  # optional transform applied to hidden states between stages
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(seed + 12345)
@@ -259,6 +272,11 @@ class Engine:
     def add_request(self, req: Request) -> None:
         req.sampling_params.verify()
         req.max_total_length = min(req.max_total_length, self.planner.max_total_length)
+        req.lora_slot = -1
+        if req.lora_path:
+            if self.lora is None:
+                raise ValueError("this engine was started without LoRA support (--enable-lora)")
+            req.lora_slot = self.lora.acquire(req.lora_path)     # loads the adapter if it is not resident
         self.scheduler.enque_request(req)
 
     def abort_request(self, rid: str) -> None:
@@ -328,6 +346,9 @@ class Engine:
     # ------------------------------------------------------------------ one step
     def _release(self, req: Request) -> None:
         self.cache.free_request(req.request_id)
+        if self.lora is not None and getattr(req, "lora_slot", -1) >= 0:
+            self.lora.release(req.lora_path)
+            req.lora_slot = -1
 
     @torch.inference_mode()
     def step(self, events=None) -> list[tuple[Request, Optional[int]]]:
@@ -395,10 +416,17 @@ class Engine:
         extra = None
         if arrays["patch_rows"] is not None:
             extra = {"patch_rows": arrays["patch_rows"], "patch_src": arrays["patch_src"]}
+        if self.lora is not None and any(getattr(s.req, "lora_slot", -1) >= 0 for s in arrays["ordered"]):
+            rows = np.full(arrays["pos"].shape[0], -1, dtype=np.int32)     # adapter slot of every token row
+            o = 0
+            for s in arrays["ordered"]:
+                rows[o:o + s.num_tokens] = getattr(s.req, "lora_slot", -1)
+                o += s.num_tokens
+            extra = dict(extra or {}, lora_ids=rows)
         fb = self.builder.build(arrays["ids"], arrays["pos"], arrays["slots"], arrays["p_q"],
                                 arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"], arrays["d_tables"],
                                 arrays["logit_rows"], arrays["seq_rows"], extra=extra)
-        if extra is not None:
+        if "patch_rows" in fb.extras:
             ops.patch_ids(fb.input_ids, fb.extras["patch_rows"], prev.ids, fb.extras["patch_src"])
         owners = arrays["owners"]
         h = None

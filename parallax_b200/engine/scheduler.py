@@ -145,7 +145,8 @@ class BatchScheduler:
                 self._rejected.append(req)
                 continue
             if self.cache_manager is not None and not self.cache_manager.has_request(rid):
-                ok, matched = self.cache_manager.allocate_request(rid, req.total_length, token_ids=req.input_ids)
+                ok, matched = self.cache_manager.allocate_request(rid, req.total_length, token_ids=req.input_ids,
+                                                                  namespace=getattr(req, "lora_path", None))
                 if not ok:
                     # out of KV memory: keep FIFO order and stop admitting
                     self._wait_queue.appendleft(req)

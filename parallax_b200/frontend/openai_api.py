@@ -121,7 +121,8 @@ def create_app(loop: EngineLoop, tokenizer: TokenizerWrapper, model_name: str, m
         r = Request(request_id=body.get("request_id") or f"{'chatcmpl' if chat else 'cmpl'}-{uuid.uuid4().hex}",
                     input_ids=ids, sampling_params=sp, routing_table=xargs.get("parallax_routing_table") or [],
                     max_total_length=min(max_model_len, len(ids) + sp.max_new_tokens),
-                    return_probs=bool(body.get("return_probs", False)))
+                    return_probs=bool(body.get("return_probs", False)),
+                    lora_path=body.get("lora_path") or xargs.get("lora_path") or None)
         r.scheduler_request_id = xargs.get("parallax_scheduler_request_id")
         return r
 

@@ -59,8 +59,11 @@ def build_engine(args, cfg, loader, start: int, end: int, shared_state=None):
         weights = loader.load_weights("cpu", None)
         from parallax_b200.loader.shard_loader import apply_lora_adapter
 
+        # a single adapter without a name is folded into the weights; named adapters ("name=path") are
+        # kept apart and chosen per request
         for lp in (args.lora_paths or []) if args.enable_lora else []:
-            apply_lora_adapter(weights, lp)
+            if "=" not in lp and len(args.lora_paths) == 1:
+                apply_lora_adapter(weights, lp)
     if (start, end) != (0, cfg.num_hidden_layers):
         raise ValueError("a partial layer range is served by a pipeline peer; use scheduler mode")
     return Engine(cfg, device=device, dtype=dtype, page_size=args.kv_block_size,
@@ -69,7 +72,20 @@ def build_engine(args, cfg, loader, start: int, end: int, shared_state=None):
                   chunked_prefill_size=args.chunked_prefill_size, enable_prefix_cache=args.enable_prefix_cache,
                   max_total_length=args.max_sequence_length, request_timeout_s=args.request_timeout_s,
                   weights=weights, shared_state=shared_state,
-                  num_blocks=None if device != "cpu" else 1024)
+                  num_blocks=None if device != "cpu" else 1024, lora=_lora_spec(args))
+
+
+def _lora_spec(args):
+    """Per-request adapters: on with --enable-lora unless the only adapter given is unnamed (merged instead)."""
+    if not getattr(args, "enable_lora", False):
+        return None
+    paths = args.lora_paths or []
+    if len(paths) == 1 and "=" not in paths[0]:
+        return None
+    from parallax_b200.loader.lora import parse_lora_paths
+
+    return {"max_loaded": args.max_loaded_loras or max(args.max_loras_per_batch, len(paths), 2),
+            "max_rank": args.max_lora_rank or 64, "paths": parse_lora_paths(paths)}
 
 
 def serve_http(app, host: str, port: int, log_level: str = "info"):

@@ -1,0 +1,201 @@
+"""Batched LoRA: several adapters resident at once, each request of a batch using its own.
+
+The reference loads PEFT adapters into its GPU backend and serves ``lora_path`` per request with a
+segmented-GEMV kernel (``src/parallax/server/shard_loader.py:114-226``,
+``src/parallax/server/executor/sglang_executor.py:249-333``, flags ``server_args.py:202-269``). Here the
+low-rank update of a batch is two GROUPED tcgen05 GEMMs with the adapters in the role of experts: the rows
+that use an adapter are gathered adapter by adapter, multiplied by the stacked ``A`` matrices, then by the
+stacked ``B`` matrices, and added to the base projection's output with the adapter's scale. Rows without an
+adapter are not touched.
+
+Targets: ``q_proj / k_proj / v_proj`` (applied to the fused qkv projection as one update of rank 3r),
+``o_proj`` and ``down_proj``. ``gate_proj`` / ``up_proj`` adapters cannot ride on the fused SiLU epilogue
+and are only supported by merging an adapter into the weights at load time.
+
+Ranks are padded to a multiple of 64 (one tile of the grouped GEMM), so the update costs a few per cent of
+the base projection whatever the true rank.
+"""
+
+from __future__ import annotations
+
+import json
+import logging
+import re
+from collections import OrderedDict
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+logger = logging.getLogger(__name__)
+
+_KEY = re.compile(r"^(?:base_model\.model\.)?(?:model\.)?layers\.(\d+)\.(?:self_attn|mlp)\.(\w+)\.lora_([AB])"
+                  r"(?:\.default)?\.weight$")
+TARGETS = ("q_proj", "k_proj", "v_proj", "o_proj", "down_proj")
+
+
+class LoRAAdapter:
+    """One PEFT adapter on the host: ``{(layer, module): (A [r, in], B [out, r])}`` and its scale."""
+
+    def __init__(self, name: str, rank: int, scaling: float, tensors: dict):
+        self.name, self.rank, self.scaling, self.tensors = name, rank, scaling, tensors
+
+    @classmethod
+    def load(cls, path: str, name: Optional[str] = None) -> "LoRAAdapter":
+        from safetensors.torch import load_file
+
+        p = Path(path)
+        cfg = json.loads((p / "adapter_config.json").read_text()) if (p / "adapter_config.json").exists() else {}
+        rank = int(cfg.get("r") or cfg.get("lora_rank") or 8)
+        scaling = float(cfg.get("lora_alpha", rank)) / rank
+        raw = load_file(str(p / "adapter_model.safetensors" if p.is_dir() else p))
+        halves: dict = {}
+        for k, v in raw.items():
+            m = _KEY.match(k)
+            if m and m.group(2) in TARGETS + ("gate_proj", "up_proj"):
+                halves.setdefault((int(m.group(1)), m.group(2)), {})[m.group(3)] = v
+        unsupported = sorted({mod for (_l, mod) in halves if mod not in TARGETS})
+        if unsupported:
+            raise ValueError(f"adapter {path}: per-request serving covers {TARGETS}; it also has {unsupported} "
+                             "(merge such an adapter into the weights at load time instead)")
+        tensors = {k: (ab["A"].float(), ab["B"].float()) for k, ab in halves.items() if "A" in ab and "B" in ab}
+        return cls(name or p.name, rank, scaling, tensors)
+
+
+def _pad64(n: int) -> int:
+    return (n + 63) // 64 * 64
+
+
+class LoRAStack:
+    """Device-side slots of one pipeline stage: for every local layer and fused target the ``A`` matrices of
+    all slots stacked as ``[slots * R, in]`` and the ``B`` matrices as ``[slots * out, R]`` (R = padded rank),
+    which is the weight layout of the grouped GEMM with one "expert" per slot."""
+
+    def __init__(self, stage, max_slots: int, max_rank: int):
+        cfg = stage.cfg
+        self.stage = stage
+        self.slots = max_slots
+        self.device, self.dtype = stage.device, stage.dtype
+        D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+        H, I = cfg.hidden_size, cfg.intermediate_size
+        self.r = max_rank
+        self.dims = {"qkv": (H, (Hq + 2 * Hkv) * D, _pad64(3 * max_rank)), "o": (Hq * D, H, _pad64(max_rank)),
+                     "down": (I, H, _pad64(max_rank))}
+        self.q_out, self.kv_out = Hq * D, Hkv * D
+        self.layers = []
+        for lw in stage.layers:
+            per = {}
+            for tgt, (n_in, n_out, R) in self.dims.items():
+                if tgt == "down" and lw.moe is not None:
+                    continue
+                per[tgt] = (torch.zeros((max_slots * R, n_in), dtype=self.dtype, device=self.device),
+                            torch.zeros((max_slots * n_out, R), dtype=self.dtype, device=self.device))
+            self.layers.append(per)
+        self.scale = torch.zeros(max_slots, dtype=torch.float32, device=self.device)
+
+    def load(self, slot: int, adapter: LoRAAdapter) -> None:
+        if adapter.rank > self.r:
+            raise ValueError(f"adapter {adapter.name} has rank {adapter.rank} > --max-lora-rank {self.r}")
+        r = adapter.rank
+        first = self.stage.start_layer
+        for li, per in enumerate(self.layers):
+            gl = first + li
+            for tgt, (a_stack, b_stack) in per.items():
+                n_in, n_out, R = self.dims[tgt]
+                A = a_stack[slot * R:(slot + 1) * R]
+                B = b_stack[slot * n_out:(slot + 1) * n_out]
+                A.zero_()
+                B.zero_()
+                if tgt == "qkv":
+                    row = 0
+                    for j, (mod, width) in enumerate((("q_proj", self.q_out), ("k_proj", self.kv_out),
+                                                      ("v_proj", self.kv_out))):
+                        ab = adapter.tensors.get((gl, mod))
+                        if ab is not None:
+                            A[j * r:(j + 1) * r].copy_(ab[0])
+                            B[row:row + width, j * r:(j + 1) * r].copy_(ab[1])
+                        row += width
+                else:
+                    ab = adapter.tensors.get((gl, "o_proj" if tgt == "o" else "down_proj"))
+                    if ab is not None:
+                        A[:r].copy_(ab[0])
+                        B[:, :r].copy_(ab[1])
+        self.scale[slot] = adapter.scaling
+
+    def apply(self, tgt: str, li: int, x: torch.Tensor, y: torch.Tensor, slot_of_row: torch.Tensor,
+              plan=None) -> torch.Tensor:
+        """``y + scale[slot] * (x A_slot^T) B_slot^T`` on the rows whose slot is >= 0 (``slot_of_row`` int32 [T])."""
+        per = self.layers[li].get(tgt)
+        if per is None:
+            return y
+        a_stack, b_stack = per
+        _n_in, n_out, R = self.dims[tgt]
+        if x.is_cuda:
+            from parallax_b200.ops import cuda as cu
+
+            plan = plan or cu.moe_align(slot_of_row.view(-1, 1), self.slots)
+            xp = cu.moe_gather(x.contiguous(), plan)
+            t = cu.grouped_linear(xp, a_stack, plan, self.slots, bn=64)
+            d = cu.grouped_linear(t, b_stack, plan, self.slots)
+            w = self.scale[slot_of_row.clamp_min(0).long()].view(-1, 1).contiguous()
+            return cu.moe_combine(d, plan, w, y.contiguous(), x.shape[0])
+        out = y.clone()
+        for s in range(self.slots):
+            rows = (slot_of_row == s).nonzero().flatten()
+            if rows.numel():
+                A = a_stack[s * R:(s + 1) * R].float()
+                B = b_stack[s * n_out:(s + 1) * n_out].float()
+                out[rows] = (out[rows].float() + float(self.scale[s]) * (x[rows].float() @ A.t()) @ B.t()).to(y.dtype)
+        return out
+
+
+class LoRAManager:
+    """Adapters by name: which are resident in which slot, least recently used ones make room. A slot that a
+    running request uses is pinned."""
+
+    def __init__(self, stacks: list[LoRAStack], max_loaded: int, paths: Optional[dict] = None):
+        self.stacks = stacks
+        self.max_loaded = max_loaded
+        self.paths: dict[str, str] = dict(paths or {})
+        self.slot_of: "OrderedDict[str, int]" = OrderedDict()       # resident adapters, least recently used first
+        self.pins: dict[str, int] = {}
+        self.free = list(range(max_loaded))
+
+    def register(self, name: str, path: str) -> None:
+        self.paths[name] = path
+
+    def acquire(self, name_or_path: str) -> int:
+        """Slot of the adapter (loading it if needed) with one more pin. Raises when every slot is pinned."""
+        name = name_or_path
+        if name not in self.paths:
+            self.paths[name] = name_or_path          # a path used as its own name
+        if name in self.slot_of:
+            self.slot_of.move_to_end(name)
+        else:
+            if not self.free:
+                victim = next((n for n in self.slot_of if not self.pins.get(n)), None)
+                if victim is None:
+                    raise RuntimeError("every LoRA slot is in use by a running request")
+                self.free.append(self.slot_of.pop(victim))
+            slot = self.free.pop()
+            adapter = LoRAAdapter.load(self.paths[name], name)
+            for st in self.stacks:
+                st.load(slot, adapter)
+            self.slot_of[name] = slot
+        self.pins[name] = self.pins.get(name, 0) + 1
+        return self.slot_of[name]
+
+    def release(self, name: str) -> None:
+        if self.pins.get(name, 0) > 0:
+            self.pins[name] -= 1
+
+
+def parse_lora_paths(items) -> dict[str, str]:
+    """``["name=path", "path", ...]`` -> ``{name: path}`` (a bare path is named after its last component)."""
+    out = {}
+    for it in items or []:
+        name, _, path = it.partition("=")
+        if not path:
+            path, name = name, Path(name).name
+        out[name] = path
+    return out

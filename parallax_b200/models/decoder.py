@@ -61,6 +61,7 @@ class DecoderStage(ExpertParallelMixin):
         self.kv_caches: list = []  # per local layer: (k_cache, v_cache)
         self.norm_offset = 0.0
         self._native = None     # native stage executor (built on first use) or False if not applicable
+        self.lora = None        # parallax_b200.loader.lora.LoRAStack when per-request adapters are enabled
 
     # ------------------------------------------------------------------ weights
     def num_local_layers(self) -> int:
@@ -245,6 +246,9 @@ class DecoderStage(ExpertParallelMixin):
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         T = xn.shape[0]
         qkv = ops.linear(xn, lw.w_qkv, bias=lw.b_qkv)
+        rows_lora = fb.extras.get("lora_ids") if self.lora is not None else None
+        if rows_lora is not None:
+            qkv = self.lora.apply("qkv", li, xn, qkv, rows_lora, fb.extras.get("lora_plan"))
         kc, vc = self.kv_caches[li]
         qn, kn = lw.q_norm, lw.k_norm
         if cfg.qk_norm_full and qn is not None:
@@ -269,11 +273,15 @@ class DecoderStage(ExpertParallelMixin):
             attn = attn * gate.unsqueeze(-1)
         return attn.view(T, Hq * D)
 
-    def _mlp(self, lw: LayerWeights, xn: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+    def _mlp(self, lw: LayerWeights, xn: torch.Tensor, h: torch.Tensor, li: int = 0, fb=None) -> torch.Tensor:
         if lw.moe is not None:
             return lw.moe.forward(xn, h)
         act = ops.linear(xn, lw.w_gu, epi=ops.EPI_SILU_MUL)
-        return ops.linear(act, lw.w_down, residual=h)
+        out = ops.linear(act, lw.w_down, residual=h)
+        rows_lora = fb.extras.get("lora_ids") if (self.lora is not None and fb is not None) else None
+        if rows_lora is not None:
+            out = self.lora.apply("down", li, act, out, rows_lora, fb.extras.get("lora_plan"))
+        return out
 
     def forward_layers(self, h: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
         if self._native is None and type(self).forward_layers is DecoderStage.forward_layers \
@@ -285,7 +293,13 @@ class DecoderStage(ExpertParallelMixin):
 
             self._native = NativeDenseStage(self) if NativeDenseStage.supported(self) \
                 and not os.environ.get("PXL_NO_NATIVE_STAGE") else False
-        if self._native:
+        rows_lora = fb.extras.get("lora_ids") if self.lora is not None else None
+        if rows_lora is not None and h.is_cuda and "lora_plan" not in fb.extras:
+            from parallax_b200.ops import cuda as _cu
+
+            # which rows go to which adapter: the same grouping serves every projection of every layer
+            fb.extras["lora_plan"] = _cu.moe_align(rows_lora.view(-1, 1), self.lora.slots)
+        if self._native and rows_lora is None:
             out = self._native.forward(h.contiguous(), fb)
             # the result lives in the executor's workspace: hand out a copy when it leaves the stage
             return out if self.is_last else out.clone()
@@ -294,8 +308,10 @@ class DecoderStage(ExpertParallelMixin):
             xn = ops.rmsnorm(h, lw.ln1, eps, w_offset=self.norm_offset)
             a = self._attention(lw, li, xn, fb)
             h = ops.linear(a, lw.w_o, bias=lw.b_o, residual=h)
+            if rows_lora is not None:
+                h = self.lora.apply("o", li, a, h, rows_lora, fb.extras.get("lora_plan"))
             xn = ops.rmsnorm(h, lw.ln2, eps, w_offset=self.norm_offset)
-            h = self._mlp(lw, xn, h)
+            h = self._mlp(lw, xn, h, li, fb)
         return h
 
     def logits(self, h: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:

@@ -1,0 +1,82 @@
+"""Per-request LoRA adapters: a batch in which every request uses its own adapter (or none) must produce what
+separate engines with the adapter merged into their weights produce."""
+
+import json
+
+import torch
+from safetensors.torch import save_file
+
+from parallax_b200.engine.engine import Engine
+from parallax_b200.engine.request import Request, SamplingParams
+from parallax_b200.loader.lora import LoRAAdapter, parse_lora_paths
+from parallax_b200.loader.shard_loader import apply_lora_adapter
+from parallax_b200.models.config import named_config
+
+
+def _make_adapter(cfg, path, seed, rank=4, alpha=8):
+    g = torch.Generator().manual_seed(seed)
+    D, Hq, Hkv, H, I = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.hidden_size, cfg.intermediate_size
+    dims = {"self_attn.q_proj": (H, Hq * D), "self_attn.k_proj": (H, Hkv * D), "self_attn.v_proj": (H, Hkv * D),
+            "self_attn.o_proj": (Hq * D, H), "mlp.down_proj": (I, H)}
+    t = {}
+    for li in range(cfg.num_hidden_layers):
+        for mod, (n_in, n_out) in dims.items():
+            if li == 1 and mod == "self_attn.k_proj":
+                continue          # an adapter need not cover every module
+            base = f"base_model.model.model.layers.{li}.{mod}"
+            t[base + ".lora_A.weight"] = torch.randn(rank, n_in, generator=g) * 0.2
+            t[base + ".lora_B.weight"] = torch.randn(n_out, rank, generator=g) * 0.2
+    path.mkdir()
+    save_file(t, str(path / "adapter_model.safetensors"))
+    (path / "adapter_config.json").write_text(json.dumps({"r": rank, "lora_alpha": alpha}))
+    return str(path)
+
+
+def _export(eng):
+    from tests.test_engine_gpu import _export_weights
+
+    return _export_weights(eng)
+
+
+def test_batched_adapters_match_merged_weights(tmp_path):
+    cfg = named_config("tiny")
+    a1 = _make_adapter(cfg, tmp_path / "a1", 1)
+    a2 = _make_adapter(cfg, tmp_path / "a2", 2, rank=8, alpha=4)
+    assert LoRAAdapter.load(a1).rank == 4 and parse_lora_paths(["x=" + a1, a2]) == {"x": a1, "a2": a2}
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (21, 9, 33)]
+    sp = dict(max_new_tokens=6, temperature=0.0, ignore_eos=True)
+    kw = dict(device="cpu", num_blocks=64, max_batch_size=4, chunked_prefill_size=16)
+    base = Engine(cfg, **kw)
+    weights = _export(base)
+
+    def merged(adapter):
+        w = {k: v.clone() for k, v in weights.items()}
+        if adapter:
+            assert apply_lora_adapter(w, adapter) > 0
+        return Engine(cfg, weights=w, **kw)
+
+    want = [merged(a1).generate([prompts[0]], SamplingParams(**sp))[0],
+            merged(a2).generate([prompts[1]], SamplingParams(**sp))[0],
+            merged(None).generate([prompts[2]], SamplingParams(**sp))[0]]
+    eng = Engine(cfg, weights={k: v.clone() for k, v in weights.items()},
+                 lora={"max_loaded": 2, "max_rank": 8, "paths": {"one": a1, "two": a2}}, **kw)
+    reqs = [Request(input_ids=prompts[0], sampling_params=SamplingParams(**sp), lora_path="one"),
+            Request(input_ids=prompts[1], sampling_params=SamplingParams(**sp), lora_path="two"),
+            Request(input_ids=prompts[2], sampling_params=SamplingParams(**sp))]
+    for r in reqs:
+        eng.add_request(r)
+    while eng.has_work():
+        eng.step()
+    eng.flush()
+    assert [r.output_ids for r in reqs] == want
+    assert want[0] != want[2] or want[1] != want[2]        # the adapters do change the model
+    assert all(v == 0 for v in eng.lora.pins.values())     # finished requests unpinned their adapters
+    # a third adapter takes the slot of the least recently used one
+    a3 = _make_adapter(cfg, tmp_path / "a3", 3)
+    r = Request(input_ids=prompts[0], sampling_params=SamplingParams(**sp), lora_path=a3)
+    eng.add_request(r)
+    while eng.has_work():
+        eng.step()
+    assert len(eng.lora.slot_of) == 2 and a3 in eng.lora.slot_of and "one" not in eng.lora.slot_of
+    assert r.output_ids == merged(a3).generate([prompts[0]], SamplingParams(**sp))[0]
