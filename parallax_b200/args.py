@@ -88,6 +88,11 @@ def build_parser() -> argparse.ArgumentParser:
                    help="Accepted for compatibility; the sm_100a engine is always used")
     p.add_argument("--use-hfcache", action="store_true", default=False)
     p.add_argument("--random-init", action="store_true", help="Random N(0, 0.02) weights instead of a checkpoint")
+    # engine-core wire protocol: serve an external frontend (e.g. vLLM's Rust HTTP frontend) over ZMQ
+    p.add_argument("--engine-core-input-addr", type=str, default=None,
+                   help="ZMQ endpoint of the frontend's request ROUTER (the engine connects a DEALER)")
+    p.add_argument("--engine-core-output-addr", type=str, default=None,
+                   help="ZMQ endpoint of the frontend's output PULL (the engine connects a PUSH)")
     return p
 
 

@@ -118,6 +118,15 @@ def run_standalone(args) -> None:
     loop.start()
     tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size)
     app = create_app(loop, tok, name, max_model_len=args.max_sequence_length)
+    if args.engine_core_input_addr and args.engine_core_output_addr:
+        from parallax_b200.frontend.engine_core_server import EngineCoreServer
+
+        core = EngineCoreServer(loop, args.engine_core_input_addr, args.engine_core_output_addr,
+                                max_model_len=args.max_sequence_length, dtype=args.dtype,
+                                block_size=args.kv_block_size, num_gpu_blocks=engine.cache.num_blocks)
+        core.start()
+        logger.info("engine-core protocol: requests from %s, outputs to %s", args.engine_core_input_addr,
+                    args.engine_core_output_addr)
     state.set_status("available")
     logger.info("serving %s on http://%s:%d (layers [%d, %d))", name, args.host, args.port, start, end)
     server, thread = serve_http(app, args.host, args.port, args.log_level)

@@ -98,3 +98,54 @@ def test_forward_request_round_trip_prefill_decode_chunked():
     assert b.routing_table == ["n0", "n1"] and b.input_ids is None
     assert mu.forward_mode_of(mu.request_to_proto([dec])) == mu.FORWARD_MODE_DECODE
     assert mu.proto_to_abort_request(mu.abort_request_to_proto(["x"])) == ["x"]
+
+
+def test_engine_core_protocol_over_sockets(tmp_path):
+    """The codec on a wire: a frontend-side client binds the two ZMQ endpoints, the engine registers, takes an
+    ADD frame, streams one outputs frame per token and a finish reason; an ABORT frame ends a second request."""
+    from parallax_b200.engine.engine import Engine
+    from parallax_b200.engine.request import SamplingParams
+    from parallax_b200.engine.service import EngineLoop
+    from parallax_b200.frontend.engine_core_server import EngineCoreClient, EngineCoreServer
+    from parallax_b200.models.config import named_config
+
+    cfg = named_config("tiny")
+    prompt = [5, 9, 77, 3, 250, 12]
+    want = Engine(cfg, device="cpu", num_blocks=64, max_batch_size=4).generate(
+        [prompt], SamplingParams(max_new_tokens=7, temperature=0.0, ignore_eos=True))[0]
+    inp, out = f"ipc://{tmp_path}/in.sock", f"ipc://{tmp_path}/out.sock"
+    client = EngineCoreClient(inp, out)
+    loop = EngineLoop(Engine(cfg, device="cpu", num_blocks=64, max_batch_size=4))
+    loop.start()
+    server = EngineCoreServer(loop, inp, out, max_model_len=256, dtype="float32", num_gpu_blocks=64)
+    server.start()
+    try:
+        info = client.wait_ready()
+        assert info["max_model_len"] == 256 and info["vllm_version"] == "parallax"
+        client.add("r1", prompt, {"max_tokens": 7, "temperature": 0.0})
+        toks, reason = [], None
+        while reason is None:
+            frame = client.read(30)
+            assert frame is not None, "the engine stopped answering"
+            for o in frame[1]:
+                assert o[0] == "r1"
+                toks += o[1]
+                reason = o[5] if o[5] is not None else reason
+        assert toks == want and reason == 1          # finished by length
+        client.add("r2", prompt, {"max_tokens": 200, "temperature": 0.0})
+        assert client.read(30) is not None
+        client.abort(["r2"])
+        reason = None
+        for _ in range(400):
+            frame = client.read(30)
+            assert frame is not None
+            for o in frame[1]:
+                if o[5] is not None:
+                    reason = o[5]
+            if reason is not None:
+                break
+        assert reason == 2                            # aborted
+    finally:
+        server.stop()
+        loop.stop()
+        client.close()
