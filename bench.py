@@ -494,6 +494,11 @@ def main() -> None:
 
     # every stage hop has its own two-rank communicator, which is what this warning asks for
     os.environ.setdefault("TORCH_NCCL_SHOW_EAGER_INIT_P2P_SERIALIZATION_WARNING", "false")
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        # kernels of different ranks wait for one another (NCCL receives, peer-memory flags); loading a
+        # kernel for the first time needs the whole context to drain, which a waiting kernel never lets
+        # happen in time. Load every kernel when the context is created instead of on first launch.
+        os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
     import torch
     import torch.distributed as dist
 

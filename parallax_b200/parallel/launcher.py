@@ -34,6 +34,11 @@ def free_port() -> int:
 def init_process_group(rank: int, world: int, port: int, device_type: str) -> None:
     import datetime
 
+    # Ranks run kernels that wait for each other (NCCL receives, peer-memory flags). CUDA loads a kernel on
+    # its first launch and that load waits for the context to drain, which such a waiting kernel may not
+    # allow for seconds: load everything when the context is created (must be set before CUDA starts).
+    os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+
     import torch
     import torch.distributed as dist
 
