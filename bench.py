@@ -25,7 +25,7 @@ micro-batches than stages are in flight; a step is one rotation (every running r
 token). The same requests are served at every N (strong scaling); times are the max over ranks.
 
 ``--config`` selects the other named workloads (same JSON schema): ``qwen3-8b-pp2tp4``,
-``qwen3-30b-a3b-ep8``, ``qwen3-32b-long-pp2tp4``. ``--impl vllm-stock`` runs the image's stock vLLM
+``qwen3-30b-a3b-ep8``, ``deepseek-v3-pp2ep4``, ``qwen3-32b-long-pp2tp4``. ``--impl vllm-stock`` runs the image's stock vLLM
 on the headline workload as a labelled context arm (it is NOT the reference arm: ``--impl reference``
 reports the reference as unavailable).
 
@@ -55,6 +55,9 @@ WORKLOADS = {
     "qwen3-30b-a3b-ep8": dict(model="qwen3-30b-a3b", label="Qwen3-30B-A3B-shaped MoE", conc=1024, in_len=2048,
                               out_len=512, prefixes=None, chunk=4096, layout="ep",
                               metric="output tok/s (Qwen3-30B-A3B-shaped bf16, 1024 concurrent, 2048 in / 512 out, closed loop)"),
+    "deepseek-v3-pp2ep4": dict(model="deepseek-v3.2", label="DeepSeek-V3-shaped 671B fp8 (MLA + sparse indexer)", conc=256,
+                               in_len=4096, out_len=1024, prefixes=None, chunk=4096, layout="pp2ep",
+                               metric="output tok/s (DeepSeek-V3-shaped fp8, 256 concurrent, 4096 in / 1024 out, closed loop)"),
     "qwen3-32b-long-pp2tp4": dict(model="qwen3-32b", label="Qwen3-32B-shaped", conc=64, in_len=32768, out_len=128,
                                   prefixes=None, chunk=8192, layout="pp2tp",
                                   metric="output tok/s (Qwen3-32B-shaped bf16, 64 concurrent, 32768 in / 128 out, 8192-token chunks, closed loop)"),
@@ -192,7 +195,8 @@ def result_line(args, wl, world, parallelism, tokens, dev_s, wall_s, launches, h
     out = {
         "metric": wl["metric"], "value": round(tokens / dev_s, 1), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_s / args.steps * 1e3, 3),
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8 (block-scaled e4m3 weights, bf16 activations)" if "fp8" in wl["label"] else "bf16",
         "data": "synthetic uniform-random token ids, random-init N(0,0.02) weights",
         "config": {"model": wl["label"], "global_batch": args.concurrency, "seq_len": wl["in_len"] + wl["out_len"],
                    "input_len": wl["in_len"], "output_len": wl["out_len"],
@@ -222,6 +226,8 @@ def pick_layout(wl: dict, par: str, world: int) -> tuple[str, int, int, int]:
             par = f"pp2tp{world // 2}" if world >= 4 else (f"pp1tp{world}" if world > 1 else "pp1tp1")
         elif kind == "ep":
             par = f"ep{world}"
+        elif kind == "pp2ep":
+            par = f"pp2ep{world // 2}" if world >= 4 else f"ep{world}"
         else:
             par = f"pp{world}"
     m = re.fullmatch(r"pp(\d+)tp(\d+)", par)

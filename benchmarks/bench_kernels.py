@@ -219,6 +219,35 @@ def bench_attn(rows):
         del kc, vc
 
 
+def bench_attn_small(rows):
+    """Decode attention at pipeline micro-batch sizes (tens of sequences): how the split-KV factor trades
+    a fuller machine against the extra partial results. Context lengths vary per sequence as in serving."""
+    hbm, _tf, tag = peaks()
+    Hq, Hkv, D, page = 32, 8, 128, 16
+    for B in (57, 102, 128, 256):
+        ctx_max = 1280
+        nb = (ctx_max + page - 1) // page
+        total = B * nb
+        kc = torch.randn(total, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(total, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+        bt = torch.randperm(total, device="cuda").to(torch.int32).view(B, nb)
+        cl = torch.randint(1024, ctx_max + 1, (B,), device="cuda").to(torch.int32)
+        q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        sc = 1.0 / math.sqrt(D)
+        byts = 2.0 * float(cl.sum()) * Hkv * D * 2
+        per = {}
+        for s in (0, 1, 2, 3, 4, 6):
+            ms = time_fn(lambda: cu.attn_decode(q, kc, vc, bt, cl, sc, max_ctx=ctx_max, num_splits=s, out=out))
+            per["auto" if s == 0 else s] = round(ms * 1e3, 1)
+        best = min(per.values())
+        rows.append({"kernel": "attn_decode (micro-batch sizes)", "B": B, "ctx": "1024..1280", "us_per_splits": per,
+                     "ideal_us": round(byts / (hbm * 1e9) * 1e6, 1), "best_frac": round(byts / (hbm * 1e9) * 1e6 / best, 3),
+                     "auto_frac": round(byts / (hbm * 1e9) * 1e6 / per["auto"], 3), "tag": tag})
+        print(rows[-1], flush=True)
+        del kc, vc
+
+
 def bench_norm(rows):
     hbm, tf, tag = peaks()
     T, H = 65536, 4096
@@ -278,6 +307,8 @@ def main():
         bench_gemm_mid(rows)
     if "attn" in which:
         bench_attn(rows)
+    if "attn_small" in which:
+        bench_attn_small(rows)
     if "norm" in which:
         bench_norm(rows)
     if args.out:

@@ -93,6 +93,14 @@ def test_expert_parallel_with_data_parallel_attention(pp, ep, tmp_path):
     assert got["outputs"] == want
 
 
+def test_deepseek_stage_under_expert_parallelism(tmp_path):
+    """MLA attention data-parallel, routed experts sharded over two lanes (sigmoid routing with groups, shared
+    expert replicated): same tokens as the single-process engine."""
+    want = _single(model="tiny-mla", max_new=5)
+    got = _run_group(1, 1, tmp_path, model="tiny-mla", ep=2, max_new=5)
+    assert got["outputs"] == want
+
+
 def test_rank_loss_is_detected_on_the_host(tmp_path):
     """Failure detection without touching a device: the second pipeline rank exits between steps;
     the scheduling rank sees its heartbeat stop and raises within seconds."""
