@@ -12,6 +12,8 @@
 // window and attention sinks and its split-KV variant
 // (src/parallax_extensions/kernels/paged_attention/paged_attention.metal:794-1347),
 // and the prefix-aware prefill (src/parallax/utils/prefix_cache_utils.py:11-144).
+#include <atomic>
+
 #include "common.cuh"
 #include "pxl_api.h"
 #include "pxl_noalloc.h"
@@ -861,21 +863,25 @@ static __device__ __align__(256) float g_decode_static_scratch[PXL_DECODE_STATIC
 
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_static_scratch_addr[kMaxDevices] = {nullptr};
+// Written by whichever host thread asks first; two threads racing on the first call store the
+// same value, and the atomic makes that store and the later loads well defined.
+std::atomic<float*> g_static_scratch_addr[kMaxDevices];
 
 // Device address of the scratch array on the current device, or nullptr on error.
 float* static_scratch_ptr() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-  if (g_static_scratch_addr[dev] == nullptr) {
+  float* known = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (known == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_decode_static_scratch) != cudaSuccess || p == nullptr) {
       cudaGetLastError();  // leave no sticky error behind for the caller
       return nullptr;
     }
-    g_static_scratch_addr[dev] = static_cast<float*>(p);
+    known = static_cast<float*>(p);
+    g_static_scratch_addr[dev].store(known, std::memory_order_release);
   }
-  return g_static_scratch_addr[dev];
+  return known;
 }
 }  // namespace
 

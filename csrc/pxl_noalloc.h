@@ -38,6 +38,14 @@ extern "C" {
 //    so stale contents from an earlier call are harmless and nothing has to be cleared; but
 //    two calls whose kernels overlap on the GPU (different streams, or different host threads)
 //    would race on it. Issue calls on one stream, or serialise them yourself.
+//  * Return value 0 means the kernels were enqueued. After a non-zero return nothing was
+//    launched and `out` is untouched. When the kernels ran but the device status word
+//    (`status`) is non-zero afterwards - a bounded wait inside the kernel gave up - the
+//    contents of `out` are undefined for that call: read the status word before using them.
+//  * The per-device address cache is an atomic pointer written without a lock. Two host threads that make
+//    their first call on the same device at the same moment both look the address up and
+//    both store the same value through an atomic, which is harmless; nothing else in the call is shared
+//    between threads except the scratch array itself (previous item).
 int pxl_attn_decode_static_scratch(const void* q, int64_t q_stride, const void* k_cache,
                                    const void* v_cache, const int* block_tables,
                                    const int* ctx_lens, void* out, const float* sinks, int B,

@@ -16,6 +16,7 @@ The same code runs on CPU (fp32, reference ops) and on B200 (bf16, sm_100a kerne
 from __future__ import annotations
 
 import math
+import re
 from typing import Optional
 
 import torch
@@ -36,6 +37,43 @@ class LayerWeights:
         for s in self.__slots__:
             setattr(self, s, None)
         self.window = 0
+
+
+def _adopt(old, new):
+    """Move ``new`` (a tensor, a tuple / dict of tensors, or a weights object) into ``old``'s storage where the
+    two are congruent. Returns ``(value to keep, replaced)``; ``replaced`` is True when some storage changed."""
+    if isinstance(new, torch.Tensor):
+        if isinstance(old, torch.Tensor) and old.shape == new.shape and old.dtype == new.dtype \
+                and old.device == new.device:
+            old.copy_(new)
+            return old, False
+        return new, True
+    if isinstance(new, (tuple, list)):
+        if isinstance(old, (tuple, list)) and len(old) == len(new):
+            pairs = [_adopt(o, n) for o, n in zip(old, new)]
+            return type(new)(v for v, _r in pairs), any(r for _v, r in pairs)
+        return new, True
+    if isinstance(new, dict):
+        if not isinstance(old, dict):
+            return new, True
+        replaced = set(old) != set(new)
+        out = {}
+        for k, v in new.items():
+            out[k], r = _adopt(old.get(k), v)
+            replaced |= r
+        return out, replaced
+    slots = [s for c in type(new).__mro__ for s in getattr(c, "__slots__", ())]
+    names = slots or (list(vars(new)) if hasattr(new, "__dict__") and hasattr(new, "tensors") else None)
+    if names and old is not None and type(old) is type(new):
+        replaced = False
+        for name in names:
+            if not hasattr(new, name):
+                continue
+            val, r = _adopt(getattr(old, name, None), getattr(new, name))
+            setattr(old, name, val)
+            replaced |= r
+        return old, replaced
+    return new, (old is not None and new is not old and isinstance(old, (torch.Tensor, tuple, list, dict)))
 
 
 from parallax_b200.models.moe import ExpertParallelMixin  # noqa: E402
@@ -167,11 +205,100 @@ class DecoderStage(ExpertParallelMixin):
                 lw.w_gu = ops.interleave_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"))
                 lw.w_down = get(p + "mlp.down_proj.weight").contiguous()
 
+    # ------------------------------------------------------------------ online refit
+    _LAYER_KEY = re.compile(r"(?:^|\.)layers\.(\d+)\.")
+    _GLOBAL_KEYS = ("embed_tokens.weight", ".norm.weight", "lm_head.weight")
+
+    @classmethod
+    def _layer_of_key(cls, key: str) -> Optional[int]:
+        m = cls._LAYER_KEY.search(key)
+        return int(m.group(1)) if m else None
+
+    @torch.no_grad()
+    def reload_layers(self, tensors: dict[str, torch.Tensor], only: Optional[set] = None) -> int:
+        """Refit by re-running this family's own loader on every local layer that ``tensors`` names, then
+        moving the result into the live weights (copied in place wherever shape and dtype are unchanged, so
+        pointers that kernels or the native executor hold stay valid). Works for every family, sharding and
+        quantisation because it is the loader itself that builds the new layer: fused layouts, expert shards,
+        tensor-parallel slices and fp8 blocks come out the way ``load_weights`` makes them. A layer must be
+        complete in ``tensors`` (the reference's refit ships whole checkpoints:
+        ``src/parallax/server/shard_loader.py:557-651``); an incomplete one raises ``ValueError`` before anything
+        is changed. ``only`` restricts the reload to a set of global layer numbers. Returns the number of
+        tensors used."""
+        import copy
+
+        by_layer: dict[int, int] = {}
+        n_global = 0
+        for key in tensors:
+            gi = self._layer_of_key(key)
+            if gi is not None:
+                if self.start_layer <= gi < self.end_layer and (only is None or gi in only):
+                    by_layer[gi] = by_layer.get(gi, 0) + 1
+            elif only is None and key.endswith(self._GLOBAL_KEYS):
+                n_global += 1
+        built = []
+        for gi in sorted(by_layer):
+            shadow = copy.copy(self)
+            shadow.start_layer, shadow.end_layer = gi, gi + 1
+            shadow.is_first = shadow.is_last = False
+            shadow.embed = shadow.norm_w = shadow.lm_head = None
+            shadow.layers = [type(self.layers[gi - self.start_layer])()]
+            shadow.kv_caches, shadow._native, shadow.lora = [], False, None
+            self._prepare_shadow(shadow)
+            try:
+                shadow.load_weights(tensors)
+            except KeyError as e:
+                raise ValueError(f"refit of layer {gi} needs every tensor of that layer: {e}") from e
+            built.append((gi, shadow))
+        glob = None
+        wants_embed = self.is_first or (self.is_last and self.cfg.tie_word_embeddings)
+        if n_global and (wants_embed or self.is_last):
+            glob = copy.copy(self)
+            glob.start_layer = glob.end_layer = self.start_layer
+            glob.layers, glob.kv_caches, glob._native, glob.lora = [], [], False, None
+            glob.embed = glob.norm_w = glob.lm_head = None
+            self._prepare_shadow(glob)
+            try:
+                glob.load_weights(tensors)
+            except KeyError as e:
+                raise ValueError(f"refit of the embedding / head needs all of their tensors: {e}") from e
+        replaced = False
+        for gi, shadow in built:
+            replaced |= self._adopt_layer(gi - self.start_layer, shadow)
+        if glob is not None:
+            tied = self.embed is not None and self.lm_head is not None and self.embed.data_ptr() == self.lm_head.data_ptr()
+            for name in ("embed", "norm_w", "lm_head"):
+                new = getattr(glob, name)
+                if new is None or (tied and name == "lm_head"):
+                    continue
+                val, rep = _adopt(getattr(self, name), new)
+                setattr(self, name, val)
+                replaced |= rep
+            if tied:
+                self.lm_head = self.embed
+        if replaced and self._native:
+            self._native = None            # rebuilt on the next step with the new pointers
+        return sum(by_layer.values()) + (n_global if glob is not None else 0)
+
+    def _prepare_shadow(self, shadow) -> None:
+        """Hook for subclasses: reset per-stage loader state on the temporary stage that reloads one layer."""
+
+    def _adopt_layer(self, li: int, shadow) -> bool:
+        """Move layer 0 of ``shadow`` into local layer ``li``. True when some tensor had to be replaced."""
+        _val, replaced = _adopt(self.layers[li], shadow.layers[0])
+        return replaced
+
     @torch.no_grad()
     def update_weights(self, tensors: dict[str, torch.Tensor]) -> int:
         """Patch weights in place from HF-named tensors (online refit). Tensors of layers that
-        this stage does not own are ignored. Returns the number of tensors applied."""
+        this stage does not own are ignored. Returns the number of tensors applied. Dense layers take single
+        tensors; a layer with experts is reloaded whole when any of its ``mlp.`` tensors is present."""
         cfg = self.cfg
+        moe_layers = {lw.layer_idx for lw in self.layers if lw.moe is not None}
+        reload = {gi for gi in moe_layers if any(k.startswith(f"model.layers.{gi}.mlp.") for k in tensors)}
+        n_reloaded = self.reload_layers(tensors, only=reload) if reload else 0
+        if reload:
+            tensors = {k: t for k, t in tensors.items() if self._layer_of_key(k) not in reload}
         Hq, Hkv, D, I = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
         by_layer = {lw.layer_idx: lw for lw in self.layers}
         n = 0
@@ -212,7 +339,7 @@ class DecoderStage(ExpertParallelMixin):
                               "self_attn.q_norm.weight": "q_norm", "self_attn.k_norm.weight": "k_norm"}.get(name)
                     if simple and getattr(lw, simple) is not None:
                         cp(getattr(lw, simple), t); n += 1
-        return n
+        return n + n_reloaded
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

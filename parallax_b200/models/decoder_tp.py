@@ -48,6 +48,13 @@ class TPDecoderStage(DecoderStage):
         super().load_weights(tensors)
         self.shard_weights()
 
+    def update_weights(self, tensors) -> int:
+        """Online refit: full tensors arrive, so every named layer goes through load + shard again."""
+        return self.reload_layers(tensors)
+
+    def _prepare_shadow(self, shadow) -> None:
+        shadow._sharded = False
+
     def shard_weights(self) -> None:
         if self._sharded:
             return

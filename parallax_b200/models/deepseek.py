@@ -219,7 +219,9 @@ class DeepseekStage(DecoderStage):
         return self._lin(self._lin(xn, lw.w_gu, epi=ops.EPI_SILU_MUL), lw.w_down, residual=h)
 
     def update_weights(self, tensors) -> int:
-        raise NotImplementedError("online weight refit is implemented for the GQA decoder families")
+        """Online refit: every local layer named in ``tensors`` is rebuilt by the loader above (fused and
+        absorbed layouts, expert shards, fp8 blocks) and moved into the live weights in place."""
+        return self.reload_layers(tensors)
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -23,7 +23,7 @@ import torch
 from parallax_b200 import ops
 from parallax_b200.engine.batch import ForwardBatch
 from parallax_b200.models.config import MSA_ATTENTION, ModelConfig
-from parallax_b200.models.decoder import DecoderStage
+from parallax_b200.models.decoder import DecoderStage, _adopt
 
 
 def _norm_rope_neox(x, w, cos_sin, positions, rot_dim: int, eps: float, offset: float):
@@ -92,6 +92,20 @@ class MSAStage(DecoderStage):
             self.idx[li] = dict(w=w.to(device=dev, dtype=dt).contiguous(),
                                 q_norm=tensors[a + "index_q_norm.weight"].to(device=dev, dtype=dt),
                                 k_norm=tensors[a + "index_k_norm.weight"].to(device=dev, dtype=dt))
+
+    def update_weights(self, tensors) -> int:
+        """Online refit by layer reload, so that the index heads follow their layers."""
+        return self.reload_layers(tensors)
+
+    def _prepare_shadow(self, shadow) -> None:
+        shadow.idx = {}
+
+    def _adopt_layer(self, li: int, shadow) -> bool:
+        replaced = super()._adopt_layer(li, shadow)
+        if 0 in shadow.idx:
+            self.idx[li], r = _adopt(self.idx.get(li), shadow.idx[0])
+            replaced |= r
+        return replaced
 
     def weight_bytes(self) -> int:
         extra = sum(t.numel() * t.element_size() for d in self.idx.values() for t in d.values())
