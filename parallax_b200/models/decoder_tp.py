@@ -24,19 +24,14 @@ from parallax_b200.models.config import ModelConfig
 from parallax_b200.models.decoder import DecoderStage
 
 
-class TPDecoderStage(DecoderStage):
-    def __init__(self, cfg: ModelConfig, start_layer: int, end_layer: int, device, dtype=None,
-                 max_positions: Optional[int] = None, tp_rank: int = 0, tp_size: int = 1, tp_group=None,
-                 comm=None):
-        super().__init__(cfg, start_layer, end_layer, device, dtype, max_positions)
+class TPStageMixin:
+    """What every tensor-parallel stage shares, whatever its family: the sequence-sharded residual stream
+    (rank r owns token rows ``[r*Rp, (r+1)*Rp)``), the embedding of the own rows, the vocabulary-parallel head
+    and refit by reload. A family adds ``shard_weights`` and ``forward_layers_tp``."""
+
+    def _tp_setup(self, tp_rank: int, tp_size: int, tp_group, comm) -> None:
         self.tp_rank, self.tp_size, self.tp_group = tp_rank, tp_size, tp_group
         self.comm = comm
-        if cfg.num_attention_heads % tp_size or cfg.num_key_value_heads % tp_size:
-            raise ValueError("attention heads must divide by the tensor-parallel size")
-        if not cfg.is_moe and cfg.intermediate_size % (64 * tp_size):
-            raise ValueError("intermediate size must divide by 64 * tp")
-        self.hq_l = cfg.num_attention_heads // tp_size
-        self.hkv_l = cfg.num_key_value_heads // tp_size
         self._sharded = False
 
     # ------------------------------------------------------------------ weights
@@ -54,6 +49,62 @@ class TPDecoderStage(DecoderStage):
 
     def _prepare_shadow(self, shadow) -> None:
         shadow._sharded = False
+
+    def _shard_head(self) -> None:
+        if self.lm_head is None:
+            return
+        r, tp = self.tp_rank, self.tp_size
+        V = self.lm_head.shape[0]
+        self.v_pad = (V + tp * 8 - 1) // (tp * 8) * (tp * 8)
+        vl = self.v_pad // tp
+        lo, hi = r * vl, min((r + 1) * vl, V)
+        part = self.lm_head[lo:hi]
+        if part.shape[0] < vl:   # last rank: pad with zero rows (cut off after the gather)
+            part = torch.cat([part, part.new_zeros(vl - part.shape[0], part.shape[1])])
+        tied = self.embed is not None and self.lm_head.data_ptr() == self.embed.data_ptr()
+        self.lm_head = part.contiguous()
+        self.vocab = V
+        if tied and not self.is_first:
+            self.embed = None
+
+    # ------------------------------------------------------------------ forward
+    def _embed_shard(self, fb: ForwardBatch, Rp: int) -> torch.Tensor:
+        T, r = fb.num_tokens, self.tp_rank
+        lo, hi = min(r * Rp, T), min((r + 1) * Rp, T)
+        h = torch.zeros((Rp, self.cfg.hidden_size), dtype=self.dtype, device=self.device)
+        if hi > lo:
+            ops.gather_rows(self.embed, fb.input_ids[lo:hi], out=h[:hi - lo])
+        return h
+
+    def logits_tp(self, h_shard: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        """Vocabulary-parallel head: every rank ends up with the full logits of the wanted rows."""
+        hn = ops.rmsnorm(h_shard, self.norm_w, self.cfg.rms_norm_eps, w_offset=self.norm_offset)
+        full = self.comm.all_gather_rows(hn)
+        rows = ops.gather_rows(full, fb.logit_rows)
+        local = ops.linear(rows, self.lm_head)
+        return self.comm.all_gather_cols(local)[:, :self.vocab]
+
+    def forward(self, fb: ForwardBatch, hidden: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``hidden`` (non-first stages) is this rank's row shard ``[Rp, H]``. Returns the shard
+        (non-last stage) or logits ``[num_logits, V]`` (last stage)."""
+        Rp = self.comm.rows_per_rank(fb.num_tokens)
+        h = self._embed_shard(fb, Rp) if self.is_first else hidden
+        h = self.forward_layers_tp(h, fb)
+        return self.logits_tp(h, fb) if self.is_last else h
+
+
+class TPDecoderStage(TPStageMixin, DecoderStage):
+    def __init__(self, cfg: ModelConfig, start_layer: int, end_layer: int, device, dtype=None,
+                 max_positions: Optional[int] = None, tp_rank: int = 0, tp_size: int = 1, tp_group=None,
+                 comm=None):
+        DecoderStage.__init__(self, cfg, start_layer, end_layer, device, dtype, max_positions)
+        self._tp_setup(tp_rank, tp_size, tp_group, comm)
+        if cfg.num_attention_heads % tp_size or cfg.num_key_value_heads % tp_size:
+            raise ValueError("attention heads must divide by the tensor-parallel size")
+        if not cfg.is_moe and cfg.intermediate_size % (64 * tp_size):
+            raise ValueError("intermediate size must divide by 64 * tp")
+        self.hq_l = cfg.num_attention_heads // tp_size
+        self.hkv_l = cfg.num_key_value_heads // tp_size
 
     def shard_weights(self) -> None:
         if self._sharded:
@@ -79,30 +130,10 @@ class TPDecoderStage(DecoderStage):
                 lw.w_down = lw.w_down[:, r * il:(r + 1) * il].contiguous()
             if lw.sinks is not None:
                 lw.sinks = lw.sinks[r * hq:(r + 1) * hq].contiguous()
-        if self.lm_head is not None:
-            V = self.lm_head.shape[0]
-            self.v_pad = (V + tp * 8 - 1) // (tp * 8) * (tp * 8)
-            vl = self.v_pad // tp
-            lo, hi = r * vl, min((r + 1) * vl, V)
-            part = self.lm_head[lo:hi]
-            if part.shape[0] < vl:   # last rank: pad with zero rows (masked to -inf after the GEMM)
-                part = torch.cat([part, part.new_zeros(vl - part.shape[0], part.shape[1])])
-            tied = self.embed is not None and self.lm_head.data_ptr() == self.embed.data_ptr()
-            self.lm_head = part.contiguous()
-            self.vocab = V
-            if tied and not self.is_first:
-                self.embed = None
+        self._shard_head()
         self._sharded = True
 
     # ------------------------------------------------------------------ forward
-    def _embed_shard(self, fb: ForwardBatch, Rp: int) -> torch.Tensor:
-        T, r = fb.num_tokens, self.tp_rank
-        lo, hi = min(r * Rp, T), min((r + 1) * Rp, T)
-        h = torch.zeros((Rp, self.cfg.hidden_size), dtype=self.dtype, device=self.device)
-        if hi > lo:
-            ops.gather_rows(self.embed, fb.input_ids[lo:hi], out=h[:hi - lo])
-        return h
-
     def forward_layers_tp(self, h_shard: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
         cfg, comm = self.cfg, self.comm
         eps, D, T = cfg.rms_norm_eps, cfg.head_dim, fb.num_tokens
@@ -137,19 +168,3 @@ class TPDecoderStage(DecoderStage):
             act = comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, epi=ops.EPI_SILU_MUL, w_offset=self.norm_offset)
             h_shard = comm.linear_rs(act, lw.w_down, residual=h_shard)
         return h_shard
-
-    def logits_tp(self, h_shard: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
-        """Vocabulary-parallel head: every rank ends up with the full logits of the wanted rows."""
-        hn = ops.rmsnorm(h_shard, self.norm_w, self.cfg.rms_norm_eps, w_offset=self.norm_offset)
-        full = self.comm.all_gather_rows(hn)
-        rows = ops.gather_rows(full, fb.logit_rows)
-        local = ops.linear(rows, self.lm_head)
-        return self.comm.all_gather_cols(local)[:, :self.vocab]
-
-    def forward(self, fb: ForwardBatch, hidden: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``hidden`` (non-first stages) is this rank's row shard ``[Rp, H]``. Returns the shard
-        (non-last stage) or logits ``[num_logits, V]`` (last stage)."""
-        Rp = self.comm.rows_per_rank(fb.num_tokens)
-        h = self._embed_shard(fb, Rp) if self.is_first else hidden
-        h = self.forward_layers_tp(h, fb)
-        return self.logits_tp(h, fb) if self.is_last else h

@@ -53,7 +53,10 @@ def build_stage(cfg: ModelConfig, start_layer: int, end_layer: int, device, dtyp
                 ep_comm=None, ep_local_init: bool = False):
     stage = _build_stage(cfg, start_layer, end_layer, device, dtype, max_positions, tp_rank, tp_size, tp_group, comm)
     if ep_size > 1:
-        if not cfg.is_moe or not hasattr(stage, "set_expert_parallel") or family_of(cfg.architecture) not in ("decoder", "deepseek"):
+        # experts over a group of their own (data-parallel attention): GQA decoders and the MLA families; the
+        # other families split their experts over the tensor-parallel group of the stage
+        own_group = family_of(cfg.architecture) in ("decoder", "deepseek")
+        if not cfg.is_moe or not hasattr(stage, "set_expert_parallel") or not (own_group or tp_size > 1):
             raise ValueError(f"expert parallelism is not available for {cfg.architecture}")
         stage.set_expert_parallel(ep_rank, ep_size, ep_comm, ep_local_init)
     return stage
@@ -63,8 +66,12 @@ def _build_stage(cfg: ModelConfig, start_layer: int, end_layer: int, device, dty
                  tp_group, comm):
     fam = family_of(cfg.architecture)
     if tp_size > 1 and fam != "decoder":
-        raise ValueError(f"tensor parallelism inside a stage is implemented for the GQA decoder families, not for "
-                         f"{cfg.architecture}; use pipeline stages (and expert parallelism for its MoE layers)")
+        from parallax_b200.models import tp_families
+
+        cls = {"deepseek": tp_families.TPDeepseekStage, "hybrid": tp_families.TPHybridStage,
+               "msa": tp_families.TPMSAStage}[fam]
+        return cls(cfg, start_layer, end_layer, device, dtype, max_positions=max_positions, tp_rank=tp_rank,
+                   tp_size=tp_size, tp_group=tp_group, comm=comm)
     if fam == "decoder":
         if tp_size > 1:
             from parallax_b200.models.decoder_tp import TPDecoderStage

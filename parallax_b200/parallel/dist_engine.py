@@ -239,8 +239,13 @@ class DistEngine:
                                     slot_bytes=slot_bytes)
         start, end = split_layers(cfg.num_hidden_layers, pp)[topo.pp_rank]
         comm = None
+        from parallax_b200.models.registry import family_of
+
+        family = family_of(cfg.architecture)
         if tp > 1:
-            use_fused = on_gpu if fused is None else fused
+            # the fused all-gather / reduce-scatter GEMMs are built for the GQA decoder's shapes; the other
+            # families run the same layout over library collectives
+            use_fused = (on_gpu if fused is None else fused) and family == "decoder"
             if use_fused:
                 comm = FusedTPComm(self.tp_group, tp, topo.tp_rank, self.device, max_num_tokens_per_batch,
                                    cfg.hidden_size, max_n=cfg.hidden_size,
@@ -258,6 +263,15 @@ class DistEngine:
                 per_layer = cfg.num_experts * 3 * cfg.moe_intermediate_size * cfg.hidden_size * 2
                 ep_local_init = per_layer * (end - start) > (48 << 30)
         self.ep_comm = ep_comm
+        stage_ep = (topo.ep_rank, ep, ep_comm)
+        if tp > 1 and family != "decoder" and cfg.is_moe:
+            from parallax_b200.parallel.ep import EPComm
+            from parallax_b200.parallel.tp_comm import padded_rows_per_rank
+
+            # the experts of such a stage are split over its tensor-parallel ranks; each rank brings its own rows
+            rows = padded_rows_per_rank(max_num_tokens_per_batch, tp, 128 if on_gpu else 1)
+            stage_ep = (topo.tp_rank, tp, EPComm(self.tp_group, tp, topo.tp_rank, self.device, max_rows=rows,
+                                                 fused=on_gpu if fused is None else fused))
         if weights is not None and not weights_prefiltered:
             from parallax_b200.loader.filter import filter_weights_for_range
 
@@ -267,7 +281,7 @@ class DistEngine:
                                   kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
                                   tp_rank=topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm,
                                   num_linear_slots=max(max_batch_size * 2, 16) if cfg.has_linear_layers else 0,
-                                  ep_rank=topo.ep_rank, ep_size=ep, ep_comm=ep_comm,
+                                  ep_rank=stage_ep[0], ep_size=stage_ep[1], ep_comm=stage_ep[2],
                                   ep_local_init=bool(ep_local_init) and weights is None)
         if cfg.has_linear_layers:
             enable_prefix_cache = False

@@ -43,15 +43,20 @@ class CollectiveTPComm:
         xs = ops.rmsnorm(h_shard, norm_w, eps, w_offset=w_offset)
         full = torch.empty((xs.shape[0] * self.tp, xs.shape[1]), dtype=xs.dtype, device=xs.device)
         dist.all_gather_into_tensor(full, xs.contiguous(), group=self.group)
+        if isinstance(w, tuple):      # block-scaled e4m3 weight with its scales
+            return ops.linear_fp8(full, w[0], w[1], epi=epi)
         return ops.linear(full, w, bias=bias, epi=epi)
 
     def linear_rs(self, a, w, residual=None):
         """``reduce_scatter(a @ w^T) (+ residual)`` -> ``[Rp, N]``."""
-        partial = ops.linear(a, w, epi=ops.EPI_F32 if a.is_cuda else ops.EPI_NONE)
+        if isinstance(w, tuple):
+            partial = ops.linear_fp8(a, w[0], w[1])
+        else:
+            partial = ops.linear(a, w, epi=ops.EPI_F32 if a.is_cuda else ops.EPI_NONE)
         partial = partial.float().contiguous()
         rp = a.shape[0] // self.tp
         if a.is_cuda:
-            out = torch.empty((rp, w.shape[0]), dtype=torch.float32, device=a.device)
+            out = torch.empty((rp, partial.shape[1]), dtype=torch.float32, device=a.device)
             dist.reduce_scatter_tensor(out, partial, group=self.group)
         else:   # gloo has no reduce-scatter: all-reduce and keep the rows this rank owns
             dist.all_reduce(partial, group=self.group)

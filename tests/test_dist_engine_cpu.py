@@ -21,9 +21,10 @@ HELPER = os.path.join(os.path.dirname(__file__), "helpers", "dist_engine_rank.py
 PROMPTS = [[5, 9, 77, 3, 250, 12, 8], [100, 101, 102], list(range(20, 75)), [7] * 19, [1, 2, 3, 4, 5, 6, 7, 8, 9]]
 
 
-def _run_group(pp, tp, tmp_path, max_new=6, chunk=16, model="tiny", **extra):
+def _run_group(pp, tp, tmp_path, max_new=6, chunk=16, model="tiny", prompts=None, **extra):
     spec = dict(model_name=model, pp=pp, tp=tp, device_type="cpu", num_blocks=256, page_size=16, max_batch_size=4,
-                max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256, prompts=PROMPTS,
+                max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256,
+                prompts=prompts or PROMPTS,
                 max_new=max_new, seed=0, **extra)
     world, port = pp * tp * extra.get("ep", 1), free_port()
     out = tmp_path / f"out_{pp}_{tp}.json"
@@ -43,11 +44,11 @@ def _run_group(pp, tp, tmp_path, max_new=6, chunk=16, model="tiny", **extra):
     return json.loads(out.read_text())
 
 
-def _single(max_new=6, chunk=16, model="tiny"):
+def _single(max_new=6, chunk=16, model="tiny", prompts=None):
     torch.manual_seed(0)
     eng = Engine(named_config(model), device="cpu", num_blocks=256, page_size=16, max_batch_size=4,
                  max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256, seed=0)
-    return eng.generate(PROMPTS, SamplingParams(max_new_tokens=max_new, temperature=0.0, ignore_eos=True))
+    return eng.generate(prompts or PROMPTS, SamplingParams(max_new_tokens=max_new, temperature=0.0, ignore_eos=True))
 
 
 def test_split_layers_and_padding():
@@ -98,6 +99,20 @@ def test_deepseek_stage_under_expert_parallelism(tmp_path):
     expert replicated): same tokens as the single-process engine."""
     want = _single(model="tiny-mla", max_new=5)
     got = _run_group(1, 1, tmp_path, model="tiny-mla", ep=2, max_new=5)
+    assert got["outputs"] == want
+
+
+@pytest.mark.parametrize("model,pp", [("tiny-mla", 1), ("tiny-dsa", 1), ("tiny-hybrid", 1), ("tiny-msa", 1),
+                                      ("tiny-hybrid", 2)])
+def test_tensor_parallel_stages_of_the_other_families(model, pp, tmp_path):
+    """Heads split over two ranks for latent attention (dense and indexer-sparse), gated delta-net / gated
+    attention and block-sparse attention; sequence-sharded residual stream; experts (where the model has
+    them) split over the same two ranks. Same tokens as the single-process engine."""
+    # one prompt long enough that block selection (more than 2 blocks of 32 tokens) and top-k key selection
+    # (more than 16 keys) really select
+    prompts = PROMPTS + [[(7 * i + 3) % 1000 for i in range(100)]]
+    want = _single(model=model, max_new=5, prompts=prompts)
+    got = _run_group(pp, 2, tmp_path, model=model, max_new=5, prompts=prompts)
     assert got["outputs"] == want
 
 

@@ -115,3 +115,26 @@ def test_refit_of_a_tensor_parallel_stage_goes_through_the_sharding_again():
     for k in want:
         assert torch.equal(got[k], want[k]), k
         assert got[k].data_ptr() == ptrs[k], k
+
+
+@pytest.mark.parametrize("name", ["tiny-mla", "tiny-hybrid", "tiny-msa"])
+def test_refit_of_tensor_parallel_family_stages(name):
+    cfg = named_config(name)
+    fam = family_of(cfg.architecture)
+    a, b = hf_state_dict(cfg, fam, seed=1), hf_state_dict(cfg, fam, seed=2)
+    n_layers = cfg.num_hidden_layers
+    kw = dict(tp_rank=1, tp_size=2, tp_group=None, comm=None)
+    if cfg.is_moe:
+        kw.update(ep_rank=1, ep_size=2, ep_comm=None)
+    st = build_stage(cfg, 0, n_layers, "cpu", torch.float32, **kw)
+    st.load_weights(a)
+    ptrs = {k: t.data_ptr() for k, t in _flat(st).items()}
+    assert st.update_weights(b) == len(b)
+    fresh = build_stage(cfg, 0, n_layers, "cpu", torch.float32, **kw)
+    fresh.load_weights(b)
+    got, want = _flat(st), _flat(fresh)
+    assert set(got) == set(want)
+    for k in want:
+        assert torch.equal(got[k], want[k]), k
+        assert got[k].data_ptr() == ptrs[k], k
+    assert st.cfg.num_attention_heads == cfg.num_attention_heads // 2
