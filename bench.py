@@ -266,9 +266,10 @@ def run_group(args, wl, cfg, par, world, rank, local_rank, device, invalid) -> N
     # more micro-batches than stages, so that a stage always has one queued while the scheduler on rank 0
     # commits the tokens of another and plans its next turn; every micro-batch re-reads the stage's weights
     # and runs its GEMMs on fewer rows, so as few extra ones as keep the stages busy (measured: 4 at two
-    # stages, where prompts run whole and the micro-batches are uneven; stages + 1 in deeper pipelines,
-    # whose prompt slices are capped: 26.1 k tok/s with 5 against 23.3 k with 6 at four stages)
-    n_mb = args.micro_batches or (1 if pp == 1 else (pp + 2 if pp <= 2 else pp + 1))
+    # stages, where prompts run whole and the micro-batches are uneven; 5 at four stages, whose prompt
+    # slices are capped: 26.1 k tok/s against 23.3 k with 6; 10 at eight stages: 32.5 k tok/s against
+    # 27.9 k with 9, because one spare micro-batch no longer covers the scheduler's turn-around there)
+    n_mb = args.micro_batches or (1 if pp == 1 else {2: 4, 4: 5, 8: 10}.get(pp, pp + 2))
     chunk = args.prefill_chunk or wl["chunk"]
     # deep pipelines: a micro-batch that carries whole prompts is several times heavier than the others
     # and every stage behind it runs dry. A cap on the prompt tokens per micro-batch, about 1.7x the
