@@ -99,6 +99,11 @@ class DecoderStage(ExpertParallelMixin):
         self.kv_caches: list = []  # per local layer: (k_cache, v_cache)
         self.norm_offset = 0.0
         self._native = None     # native stage executor (built on first use) or False if not applicable
+        # dense FFN activation: 0 = SwiGLU fused into the gate/up GEMM's epilogue (rows interleaved in groups
+        # of 64); 1 = the clipped "swigluoai" of GPT-OSS / MiniMax-M3 (``src/parallax/models/minimax_m3.py:176-180``),
+        # gate rows then up rows, activation as its own kernel between the two GEMMs
+        self.dense_act_mode = 1 if (cfg.swiglu_limit or cfg.hidden_act == "swigluoai") else 0
+        self.dense_limit = float(cfg.swiglu_limit or 7.0)
         self.lora = None        # parallax_b200.loader.lora.LoRAStack when per-request adapters are enabled
 
     # ------------------------------------------------------------------ weights
@@ -154,7 +159,7 @@ class DecoderStage(ExpertParallelMixin):
             else:
                 wg = rnd(I, H, layer_seed=s + 6)
                 wu = rnd(I, H, layer_seed=s + 7)
-                lw.w_gu = ops.interleave_gate_up(wg, wu)
+                lw.w_gu = self._pack_gate_up(wg, wu)
                 lw.w_down = rnd(H, I, layer_seed=s + 8)
 
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -202,8 +207,13 @@ class DecoderStage(ExpertParallelMixin):
                 lw.moe = MoEWeights.from_hf(cfg, tensors, p + "mlp.", dev, dt)
                 self._ep_finish(lw.moe)
             else:
-                lw.w_gu = ops.interleave_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"))
+                lw.w_gu = self._pack_gate_up(get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"))
                 lw.w_down = get(p + "mlp.down_proj.weight").contiguous()
+
+    def _pack_gate_up(self, wg: torch.Tensor, wu: torch.Tensor) -> torch.Tensor:
+        if self.dense_act_mode:
+            return torch.cat([wg, wu], dim=0).contiguous()
+        return ops.interleave_gate_up(wg, wu)
 
     # ------------------------------------------------------------------ online refit
     _LAYER_KEY = re.compile(r"(?:^|\.)layers\.(\d+)\.")
@@ -294,6 +304,8 @@ class DecoderStage(ExpertParallelMixin):
         this stage does not own are ignored. Returns the number of tensors applied. Dense layers take single
         tensors; a layer with experts is reloaded whole when any of its ``mlp.`` tensors is present."""
         cfg = self.cfg
+        if self.dense_act_mode:
+            return self.reload_layers(tensors)
         moe_layers = {lw.layer_idx for lw in self.layers if lw.moe is not None}
         reload = {gi for gi in moe_layers if any(k.startswith(f"model.layers.{gi}.mlp.") for k in tensors)}
         n_reloaded = self.reload_layers(tensors, only=reload) if reload else 0
@@ -403,7 +415,10 @@ class DecoderStage(ExpertParallelMixin):
     def _mlp(self, lw: LayerWeights, xn: torch.Tensor, h: torch.Tensor, li: int = 0, fb=None) -> torch.Tensor:
         if lw.moe is not None:
             return lw.moe.forward(xn, h)
-        act = ops.linear(xn, lw.w_gu, epi=ops.EPI_SILU_MUL)
+        if self.dense_act_mode:
+            act = ops.act_mul(ops.linear(xn, lw.w_gu), self.dense_act_mode, self.dense_limit)
+        else:
+            act = ops.linear(xn, lw.w_gu, epi=ops.EPI_SILU_MUL)
         out = ops.linear(act, lw.w_down, residual=h)
         rows_lora = fb.extras.get("lora_ids") if (self.lora is not None and fb is not None) else None
         if rows_lora is not None:

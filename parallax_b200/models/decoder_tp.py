@@ -124,9 +124,12 @@ class TPDecoderStage(TPStageMixin, DecoderStage):
                                       bv[r * hkv * D:(r + 1) * hkv * D]]).contiguous()
             lw.w_o = lw.w_o[:, r * hq * D:(r + 1) * hq * D].contiguous()
             if lw.moe is None:
-                # gate/up are interleaved in groups of 64 outputs: a contiguous slice of groups is a slice of I
-                g = lw.w_gu.view(I // 64, 128, -1)
-                lw.w_gu = g[r * il // 64:(r + 1) * il // 64].reshape(2 * il, -1).contiguous()
+                if self.dense_act_mode:     # [gate rows | up rows]
+                    lw.w_gu = torch.cat([lw.w_gu[r * il:(r + 1) * il], lw.w_gu[I + r * il:I + (r + 1) * il]]).contiguous()
+                else:
+                    # gate/up are interleaved in groups of 64 outputs: a contiguous slice of groups is a slice of I
+                    g = lw.w_gu.view(I // 64, 128, -1)
+                    lw.w_gu = g[r * il // 64:(r + 1) * il // 64].reshape(2 * il, -1).contiguous()
                 lw.w_down = lw.w_down[:, r * il:(r + 1) * il].contiguous()
             if lw.sinks is not None:
                 lw.sinks = lw.sinks[r * hq:(r + 1) * hq].contiguous()
@@ -165,6 +168,10 @@ class TPDecoderStage(TPStageMixin, DecoderStage):
                 base = lw.moe.shared_base(xn, h_shard)
                 h_shard = comm.moe_ffn(xn, n_valid, ids, w, lw.moe.w1, lw.moe.w2, lw.moe.experts_per_rank, base=base)
                 continue
-            act = comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, epi=ops.EPI_SILU_MUL, w_offset=self.norm_offset)
+            if self.dense_act_mode:
+                act = ops.act_mul(comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, w_offset=self.norm_offset),
+                                  self.dense_act_mode, self.dense_limit)
+            else:
+                act = comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, epi=ops.EPI_SILU_MUL, w_offset=self.norm_offset)
             h_shard = comm.linear_rs(act, lw.w_down, residual=h_shard)
         return h_shard

@@ -11,7 +11,8 @@ used because the selection would keep everything.
 Reference: ``src/parallax/models/minimax_m3.py:428-446`` (index projections), ``:456-565`` (block
 top-k mask for prefill), ``:612-654`` (sparse decode), Gemma-style norms ``:194-203``. The clipped
 ``swigluoai`` activation of that family (``:176-180``) runs as a separate kernel between the two
-grouped expert GEMMs (:mod:`parallax_b200.models.moe`); dense layers with it are refused.
+grouped expert GEMMs (:mod:`parallax_b200.models.moe`) and between the gate/up and down projections of a dense
+layer (:mod:`parallax_b200.models.decoder`).
 """
 
 from __future__ import annotations
@@ -46,8 +47,6 @@ class MSAStage(DecoderStage):
         super().__init__(cfg, start_layer, end_layer, device, dtype, max_positions)
         raw = cfg.raw or {}
         sp = raw.get("sparse_attention_config") or {}
-        if cfg.swiglu_limit and not cfg.is_moe:
-            raise NotImplementedError("the clipped swigluoai activation is wired for MoE experts only")
         self.norm_offset = 1.0 if raw.get("use_gemma_norm") else 0.0
         self.sparse_block = int(sp.get("sparse_block_size", raw.get("index_block_size") or 128))
         self.topk_blocks = int(sp.get("sparse_topk_blocks", raw.get("index_topk_blocks") or 16))

@@ -88,8 +88,11 @@ class FamilyTPMixin(TPStageMixin):
         r, tp = self.tp_rank, self.tp_size
         if isinstance(lw.w_gu, torch.Tensor) and lw.w_gu.shape[0] == 2 * I:
             il = I // tp
-            # gate/up are interleaved in groups of 64 outputs: a contiguous run of groups is a slice of I
-            lw.w_gu = lw.w_gu.view(I // 64, 128, -1)[r * il // 64:(r + 1) * il // 64].reshape(2 * il, -1).contiguous()
+            if self.dense_act_mode:     # [gate rows | up rows]
+                lw.w_gu = torch.cat([lw.w_gu[r * il:(r + 1) * il], lw.w_gu[I + r * il:I + (r + 1) * il]]).contiguous()
+            else:
+                # gate/up are interleaved in groups of 64 outputs: a contiguous run of groups is a slice of I
+                lw.w_gu = lw.w_gu.view(I // 64, 128, -1)[r * il // 64:(r + 1) * il // 64].reshape(2 * il, -1).contiguous()
             lw.w_down = _part(lw.w_down, r, tp, dim=1)
 
     def shard_weights(self) -> None:
@@ -107,14 +110,15 @@ class FamilyTPMixin(TPStageMixin):
         self._sharded = True
 
     # ------------------------------------------------------------------ forward
-    def _lin_w(self, w):
-        return w
-
     def _tp_mlp(self, lw, h_shard: torch.Tensor, n_valid: int) -> torch.Tensor:
         eps = self.cfg.rms_norm_eps
         if lw.moe is None:
-            act = self.comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, epi=ops.EPI_SILU_MUL,
-                                           w_offset=self.norm_offset)
+            if self.dense_act_mode:
+                act = ops.act_mul(self.comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, w_offset=self.norm_offset),
+                                  self.dense_act_mode, self.dense_limit)
+            else:
+                act = self.comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, epi=ops.EPI_SILU_MUL,
+                                               w_offset=self.norm_offset)
             return self.comm.linear_rs(act, lw.w_down, residual=h_shard)
         if lw.moe.ep is not None:
             lw.moe.ep.step_max_rows = h_shard.shape[0]

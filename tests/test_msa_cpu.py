@@ -94,3 +94,34 @@ def test_msa_select_forced_blocks_and_order():
     # kept: block 0 (initial), block 5 (local), then the best two of the rest: 1 and 2
     assert vt[0].tolist() == [100, 101, 102, 103, 104, 105, 110, 111]
     assert int(vctx[0]) == 3 * 32 + 8
+
+
+def test_dense_layers_with_the_clipped_activation():
+    """A dense FFN with ``swiglu_limit``: gate clipped from above, up clipped on both sides, ``g * sigmoid(1.702 g) * (u + 1)``."""
+    import copy
+
+    from helpers.hf_weights import hf_state_dict
+    from parallax_b200.models.registry import build_stage
+
+    cfg = copy.copy(named_config("tiny-msa"))
+    cfg.swiglu_limit = 0.05            # small enough that the clipping really bites with these weights
+    sd = hf_state_dict(cfg, "msa", seed=3)
+    st = build_stage(cfg, 0, cfg.num_hidden_layers, "cpu", torch.float32)
+    st.load_weights(sd)
+    assert st.dense_act_mode == 1
+    x = torch.randn(5, cfg.hidden_size)
+    h = torch.randn(5, cfg.hidden_size)
+    got = st._mlp(st.layers[1], x, h)
+    g = x @ sd["model.layers.1.mlp.gate_proj.weight"].t()
+    u = x @ sd["model.layers.1.mlp.up_proj.weight"].t()
+    assert (g > 0.05).any() and (u.abs() > 0.05).any()
+    g, u = g.clamp(max=0.05), u.clamp(-0.05, 0.05)
+    want = h + (g * torch.sigmoid(1.702 * g) * (u + 1)) @ sd["model.layers.1.mlp.down_proj.weight"].t()
+    assert torch.allclose(got, want, atol=1e-5)
+    # the tensor-parallel cut of [gate rows | up rows] keeps the pairs together
+    tp = build_stage(cfg, 0, cfg.num_hidden_layers, "cpu", torch.float32, tp_rank=1, tp_size=2)
+    tp.load_weights(sd)
+    I = cfg.intermediate_size
+    assert torch.equal(tp.layers[1].w_gu[:I // 2], sd["model.layers.1.mlp.gate_proj.weight"][I // 2:])
+    assert torch.equal(tp.layers[1].w_gu[I // 2:], sd["model.layers.1.mlp.up_proj.weight"][I // 2:])
+    assert torch.equal(tp.layers[1].w_down, sd["model.layers.1.mlp.down_proj.weight"][:, I // 2:])
