@@ -12,6 +12,8 @@
 // window and attention sinks and its split-KV variant
 // (src/parallax_extensions/kernels/paged_attention/paged_attention.metal:794-1347),
 // and the prefix-aware prefill (src/parallax/utils/prefix_cache_utils.py:11-144).
+#include <cuda_fp8.h>
+
 #include <atomic>
 
 #include "common.cuh"
@@ -25,8 +27,8 @@ constexpr int TILE = 64;  // KV tokens per shared-memory tile
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct KVTileArgs {
-  const bf16* k_cache;
-  const bf16* v_cache;
+  const void* k_cache;   // bf16 elements, or e4m3 bytes for the FP8 kernels
+  const void* v_cache;
   const int* block_table;  // row of this sequence
   int max_blocks;
   int64_t num_blocks;
@@ -46,11 +48,29 @@ __device__ __forceinline__ uint32_t tile_off_sw128(int row, int chunk) {
   return static_cast<uint32_t>((chunk >> 3) * (64 * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-// Issue cp.async loads of K and V rows for tokens [tok0, tok0+TILE) ∩ [0, hi).
-template <int D>
+// Eight e4m3 bytes -> eight bf16 (exact: every e4m3 value is a bf16 value), as one 16-byte vector.
+__device__ __forceinline__ uint4 e4m3x8_to_bf16x8(uint2 raw) {
+  uint4 out;
+  uint32_t* o = &out.x;
+  const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_fp8x2_storage_t pair = static_cast<__nv_fp8x2_storage_t>((w[i >> 1] >> ((i & 1) * 16)) & 0xffffu);
+    const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+    o[i] = pack_bf16x2(f.x, f.y);
+  }
+  return out;
+}
+
+// Issue the loads of K and V rows for tokens [tok0, tok0+TILE) ∩ [0, hi): cp.async for a bf16 cache;
+// for an e4m3 cache (FP8) each thread reads 8 bytes, widens them to bf16 and stores the 16-byte
+// chunk itself, so that the MMA code behind it is the same. The scales of an e4m3 cache are applied
+// by the caller (K: folded into the score scale, V: into the output normalisation).
+template <int D, bool FP8 = false>
 __device__ __forceinline__ void load_kv_tile(const KVTileArgs& a, int tok0, int hi, uint32_t k_smem,
                                              uint32_t v_smem, int* status) {
-  constexpr int CPR = D / 8;  // 16-byte chunks per row
+  constexpr int CPR = D / 8;  // 8-element chunks per row
   constexpr int ITERS = TILE * CPR / 128;
 #pragma unroll
   for (int i = 0; i < ITERS; ++i) {
@@ -73,8 +93,21 @@ __device__ __forceinline__ void load_kv_tile(const KVTileArgs& a, int tok0, int 
       }
     }
     const uint32_t off = tile_off<D>(row, chunk);
-    cp_async_16(k_smem + off, a.k_cache + base, pred);
-    cp_async_16(v_smem + off, a.v_cache + base, pred);
+    if constexpr (FP8) {
+      uint2 kr = make_uint2(0u, 0u), vr = make_uint2(0u, 0u);
+      if (pred) {
+        kr = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(a.k_cache) + base));
+        vr = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(a.v_cache) + base));
+      }
+      const uint4 kb = e4m3x8_to_bf16x8(kr), vb = e4m3x8_to_bf16x8(vr);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(k_smem + off), "r"(kb.x), "r"(kb.y),
+                   "r"(kb.z), "r"(kb.w) : "memory");
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(v_smem + off), "r"(vb.x), "r"(vb.y),
+                   "r"(vb.z), "r"(vb.w) : "memory");
+    } else {
+      cp_async_16(k_smem + off, static_cast<const bf16*>(a.k_cache) + base, pred);
+      cp_async_16(v_smem + off, static_cast<const bf16*>(a.v_cache) + base, pred);
+    }
   }
 }
 
@@ -126,14 +159,14 @@ __device__ __forceinline__ float quad_sum(float v) {
 }
 
 // =============================================================================== decode
-template <int D>
+template <int D, bool FP8 = false>
 __global__ void __launch_bounds__(128)
-attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __restrict__ k_cache,
-                   const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
+attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const void* __restrict__ k_cache,
+                   const void* __restrict__ v_cache, const int* __restrict__ block_tables,
                    const int* __restrict__ ctx_lens, bf16* __restrict__ out,
                    float* __restrict__ workspace, const float* __restrict__ sinks, int Hq, int Hkv,
                    int page_size, int max_blocks, int64_t num_blocks, float scale_log2, int window,
-                   int num_splits, int* status) {
+                   int num_splits, float v_scale, int* status) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int TILE_BYTES = TILE * D * 2;
   const uint32_t k_smem0 = smem_u32(smem);
@@ -177,13 +210,13 @@ attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __r
   float l_run[2] = {0.f, 0.f};
 
   int buf = 0;
-  if (t_begin < t_end) load_kv_tile<D>(ka, t_begin * TILE, hi, k_smem0, v_smem0, status);
+  if (t_begin < t_end) load_kv_tile<D, FP8>(ka, t_begin * TILE, hi, k_smem0, v_smem0, status);
   cp_async_commit();
   for (int t = t_begin; t < t_end; ++t) {
     cp_async_wait<0>();
     __syncthreads();
     if (t + 1 < t_end)
-      load_kv_tile<D>(ka, (t + 1) * TILE, hi, k_smem0 + (buf ^ 1) * TILE_BYTES,
+      load_kv_tile<D, FP8>(ka, (t + 1) * TILE, hi, k_smem0 + (buf ^ 1) * TILE_BYTES,
                       v_smem0 + (buf ^ 1) * TILE_BYTES, status);
     cp_async_commit();
 
@@ -287,13 +320,13 @@ attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __r
     if (num_splits == 1) {
       const float denom = L + exp2f(sink - Mu);
       out[(static_cast<size_t>(b) * Hq + head) * D + d] =
-          __float2bfloat16(denom > 0.f ? acc / denom : 0.f);
+          __float2bfloat16(denom > 0.f ? acc / denom * v_scale : 0.f);
     } else {
       // partial: normalised output + log2-sum-exp
       float* po = workspace;
       float* plse = workspace + static_cast<size_t>(gridDim.y) * Hq * num_splits * D;
       const size_t row = (static_cast<size_t>(b) * Hq + head) * num_splits + split;
-      po[row * D + d] = L > 0.f ? acc / L : 0.f;
+      po[row * D + d] = L > 0.f ? acc / L * v_scale : 0.f;
       if (d == 0) plse[row] = L > 0.f ? Mu + log2f(L) : -INFINITY;
     }
   }
@@ -565,14 +598,14 @@ attn_decode_reduce_kernel(const float* __restrict__ workspace, const float* __re
 }
 
 // ============================================================================== prefill
-template <int D>
+template <int D, bool FP8 = false>
 __global__ void __launch_bounds__(128)
-attn_prefill_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __restrict__ k_cache,
-                    const bf16* __restrict__ v_cache, const int* __restrict__ block_tables,
+attn_prefill_kernel(const bf16* __restrict__ q, int64_t q_stride, const void* __restrict__ k_cache,
+                    const void* __restrict__ v_cache, const int* __restrict__ block_tables,
                     const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                     bf16* __restrict__ out, int64_t out_stride, const float* __restrict__ sinks,
                     int Hq, int Hkv, int page_size, int max_blocks, int64_t num_blocks,
-                    float scale_log2, int window, int* status) {
+                    float scale_log2, int window, float v_scale, int* status) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int TILE_BYTES = TILE * D * 2;
   const uint32_t k_smem0 = smem_u32(smem);
@@ -643,13 +676,13 @@ attn_prefill_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __
   float l_run[2] = {0.f, 0.f};
 
   int buf = 0;
-  load_kv_tile<D>(ka, t_begin * TILE, c_hi, k_smem0, v_smem0, status);
+  load_kv_tile<D, FP8>(ka, t_begin * TILE, c_hi, k_smem0, v_smem0, status);
   cp_async_commit();
   for (int t = t_begin; t < t_end; ++t) {
     cp_async_wait<0>();
     __syncthreads();
     if (t + 1 < t_end)
-      load_kv_tile<D>(ka, (t + 1) * TILE, c_hi, k_smem0 + (buf ^ 1) * TILE_BYTES,
+      load_kv_tile<D, FP8>(ka, (t + 1) * TILE, c_hi, k_smem0 + (buf ^ 1) * TILE_BYTES,
                       v_smem0 + (buf ^ 1) * TILE_BYTES, status);
     cp_async_commit();
 
@@ -724,7 +757,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __
     const float Mu = (Mx == -INFINITY) ? 0.f : Mx;
     const float f = exp2f(M - Mu);
     const float denom = L * f + exp2f(sink - Mu);
-    const float inv = denom > 0.f ? f / denom : 0.f;
+    const float inv = denom > 0.f ? f / denom * v_scale : 0.f;
     bf16* dst = out + static_cast<size_t>(q0 + rtok[h]) * out_stride + rhead[h] * D;
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
@@ -758,20 +791,19 @@ PXL_EXPORT int pxl_attn_decode_splits(int B, int Hkv, int max_ctx) {
   return s;
 }
 
-PXL_EXPORT int pxl_attn_decode(const void* q, int64_t q_stride, const void* k_cache,
-                               const void* v_cache,
-                               const int* block_tables, const int* ctx_lens, void* out,
-                               float* workspace, const float* sinks, int B, int Hq, int Hkv, int D,
-                               int page_size, int max_blocks, int64_t num_blocks, float scale,
-                               int window, int num_splits, int max_ctx, int* status,
-                               pxl_stream_t stream) {
+namespace {
+int attn_decode_impl(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                     const int* block_tables, const int* ctx_lens, void* out, float* workspace,
+                     const float* sinks, int B, int Hq, int Hkv, int D, int page_size, int max_blocks,
+                     int64_t num_blocks, float scale, int window, int num_splits, int max_ctx,
+                     bool cache_fp8, float k_scale, float v_scale, int* status, pxl_stream_t stream) {
   if (B <= 0) return PXL_OK;
   if (Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16 || page_size <= 0) return PXL_ERR_INVALID_ARG;
   if (num_splits <= 0) num_splits = pxl_attn_decode_splits(B, Hkv, max_ctx);
   if (num_splits > 1 && workspace == nullptr) return PXL_ERR_INVALID_ARG;
   const float scale_log2 = scale * kLog2e;
   dim3 grid(Hkv, B, num_splits);
-  if (D == 128 && (page_size == 16 || page_size == 32 || page_size == 64) &&
+  if (!cache_fp8 && D == 128 && (page_size == 16 || page_size == 32 || page_size == 64) &&
       num_blocks * Hkv * page_size < (1ll << 31)) {
     // TMA-fed kernel: the cache is a 2-D matrix [blocks * Hkv * page, 128], one box = one page half
     CUtensorMap tk, tv;
@@ -794,31 +826,106 @@ PXL_EXPORT int pxl_attn_decode(const void* q, int64_t q_stride, const void* k_ca
                        static_cast<bf16*>(out), Hq, num_splits);
     return check_launch();
   }
-#define PXL_DEC(DD)                                                                              \
+#define PXL_DEC(DD, F8)                                                                          \
   {                                                                                              \
     constexpr int SMEM = 4 * TILE * DD * 2 > (4 * 16 * DD + 128) * 4 ? 4 * TILE * DD * 2         \
                                                                      : (4 * 16 * DD + 128) * 4;  \
     static bool done[64] = {false};                                                              \
     const int dev = pxl_host::current_device_slot();                                                       \
     if (!done[dev]) {                                                                            \
-      if (set_smem(attn_decode_kernel<DD>, SMEM)) return PXL_ERR_CUDA;                           \
+      if (set_smem(attn_decode_kernel<DD, F8>, SMEM)) return PXL_ERR_CUDA;                       \
       done[dev] = true;                                                                          \
     }                                                                                            \
-    attn_decode_kernel<DD><<<grid, 128, SMEM, stream>>>(                                         \
-        static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(k_cache),                \
-        static_cast<const bf16*>(v_cache), block_tables, ctx_lens, static_cast<bf16*>(out),      \
-        workspace, sinks, Hq, Hkv, page_size, max_blocks, num_blocks, scale_log2, window,        \
-        num_splits, status);                                                                     \
+    attn_decode_kernel<DD, F8><<<grid, 128, SMEM, stream>>>(                                     \
+        static_cast<const bf16*>(q), q_stride, k_cache, v_cache, block_tables, ctx_lens,         \
+        static_cast<bf16*>(out), workspace, sinks, Hq, Hkv, page_size, max_blocks, num_blocks,   \
+        scale_log2 * k_scale, window, num_splits, v_scale, status);                              \
     if (num_splits > 1)                                                                          \
       attn_decode_reduce_kernel<DD><<<dim3(Hq, B), DD, 0, stream>>>(                             \
           workspace, sinks, static_cast<bf16*>(out), Hq, num_splits);                            \
   }
-  if (D == 128) PXL_DEC(128)
-  else if (D == 64) PXL_DEC(64)
-  else return PXL_ERR_INVALID_ARG;
+  if (cache_fp8) {
+    if (D == 128) PXL_DEC(128, true)
+    else if (D == 64) PXL_DEC(64, true)
+    else return PXL_ERR_INVALID_ARG;
+  } else {
+    if (D == 128) PXL_DEC(128, false)
+    else if (D == 64) PXL_DEC(64, false)
+    else return PXL_ERR_INVALID_ARG;
+  }
 #undef PXL_DEC
   return check_launch();
 }
+}  // namespace
+
+PXL_EXPORT int pxl_attn_decode(const void* q, int64_t q_stride, const void* k_cache,
+                               const void* v_cache,
+                               const int* block_tables, const int* ctx_lens, void* out,
+                               float* workspace, const float* sinks, int B, int Hq, int Hkv, int D,
+                               int page_size, int max_blocks, int64_t num_blocks, float scale,
+                               int window, int num_splits, int max_ctx, int* status,
+                               pxl_stream_t stream) {
+  return attn_decode_impl(q, q_stride, k_cache, v_cache, block_tables, ctx_lens, out, workspace, sinks,
+                          B, Hq, Hkv, D, page_size, max_blocks, num_blocks, scale, window, num_splits,
+                          max_ctx, false, 1.f, 1.f, status, stream);
+}
+
+// Decode attention over e4m3 caches written by pxl_qk_norm_rope_cache_fp8 / pxl_reshape_and_cache_fp8
+// with the same scales. The cache bytes are widened to bf16 on their way into shared memory, the K
+// scale is folded into the score scale and the V scale into the output normalisation.
+PXL_EXPORT int pxl_attn_decode_fp8(const void* q, int64_t q_stride, const void* k_cache,
+                                   const void* v_cache, const int* block_tables,
+                                   const int* ctx_lens, void* out, float* workspace,
+                                   const float* sinks, int B, int Hq, int Hkv, int D, int page_size,
+                                   int max_blocks, int64_t num_blocks, float scale, int window,
+                                   int num_splits, int max_ctx, float k_scale, float v_scale,
+                                   int* status, pxl_stream_t stream) {
+  if (!(k_scale > 0.f) || !(v_scale > 0.f)) return PXL_ERR_INVALID_ARG;
+  return attn_decode_impl(q, q_stride, k_cache, v_cache, block_tables, ctx_lens, out, workspace, sinks,
+                          B, Hq, Hkv, D, page_size, max_blocks, num_blocks, scale, window, num_splits,
+                          max_ctx, true, k_scale, v_scale, status, stream);
+}
+
+namespace {
+int attn_prefill_impl(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                      const int* block_tables, const int* cu_q, const int* ctx_lens, void* out,
+                      int64_t out_stride, const float* sinks, int B, int max_q_len, int Hq, int Hkv,
+                      int D, int page_size, int max_blocks, int64_t num_blocks, float scale,
+                      int window, bool cache_fp8, float k_scale, float v_scale, int* status,
+                      pxl_stream_t stream) {
+  if (B <= 0 || max_q_len <= 0) return PXL_OK;
+  if (Hkv <= 0 || Hq % Hkv || Hq / Hkv > 64 || page_size <= 0) return PXL_ERR_INVALID_ARG;
+  const int G = Hq / Hkv;
+  const int TQ = 64 / G;
+  const float scale_log2 = scale * kLog2e;
+  dim3 grid(pxl::ceil_div(max_q_len, TQ), Hkv, B);
+#define PXL_PRE(DD, F8)                                                                          \
+  {                                                                                              \
+    constexpr int SMEM = 4 * TILE * DD * 2;                                                      \
+    static bool done[64] = {false};                                                              \
+    const int dev = pxl_host::current_device_slot();                                             \
+    if (!done[dev]) {                                                                            \
+      if (set_smem(attn_prefill_kernel<DD, F8>, SMEM)) return PXL_ERR_CUDA;                      \
+      done[dev] = true;                                                                          \
+    }                                                                                            \
+    attn_prefill_kernel<DD, F8><<<grid, 128, SMEM, stream>>>(                                    \
+        static_cast<const bf16*>(q), q_stride, k_cache, v_cache, block_tables, cu_q, ctx_lens,   \
+        static_cast<bf16*>(out), out_stride, sinks, Hq, Hkv, page_size, max_blocks, num_blocks,  \
+        scale_log2 * k_scale, window, v_scale, status);                                          \
+  }
+  if (cache_fp8) {
+    if (D == 128) PXL_PRE(128, true)
+    else if (D == 64) PXL_PRE(64, true)
+    else return PXL_ERR_INVALID_ARG;
+  } else {
+    if (D == 128) PXL_PRE(128, false)
+    else if (D == 64) PXL_PRE(64, false)
+    else return PXL_ERR_INVALID_ARG;
+  }
+#undef PXL_PRE
+  return check_launch();
+}
+}  // namespace
 
 PXL_EXPORT int pxl_attn_prefill(const void* q, int64_t q_stride, const void* k_cache,
                                 const void* v_cache, const int* block_tables, const int* cu_q,
@@ -826,32 +933,23 @@ PXL_EXPORT int pxl_attn_prefill(const void* q, int64_t q_stride, const void* k_c
                                 const float* sinks, int B, int max_q_len, int Hq, int Hkv, int D,
                                 int page_size, int max_blocks, int64_t num_blocks, float scale,
                                 int window, int* status, pxl_stream_t stream) {
-  if (B <= 0 || max_q_len <= 0) return PXL_OK;
-  if (Hkv <= 0 || Hq % Hkv || Hq / Hkv > 64 || page_size <= 0) return PXL_ERR_INVALID_ARG;
-  const int G = Hq / Hkv;
-  const int TQ = 64 / G;
-  const float scale_log2 = scale * kLog2e;
-  dim3 grid(pxl::ceil_div(max_q_len, TQ), Hkv, B);
-#define PXL_PRE(DD)                                                                              \
-  {                                                                                              \
-    constexpr int SMEM = 4 * TILE * DD * 2;                                                      \
-    static bool done[64] = {false};                                                              \
-    const int dev = pxl_host::current_device_slot();                                             \
-    if (!done[dev]) {                                                                            \
-      if (set_smem(attn_prefill_kernel<DD>, SMEM)) return PXL_ERR_CUDA;                          \
-      done[dev] = true;                                                                          \
-    }                                                                                            \
-    attn_prefill_kernel<DD><<<grid, 128, SMEM, stream>>>(                                        \
-        static_cast<const bf16*>(q), q_stride, static_cast<const bf16*>(k_cache),                \
-        static_cast<const bf16*>(v_cache), block_tables, cu_q, ctx_lens,                         \
-        static_cast<bf16*>(out), out_stride, sinks, Hq, Hkv, page_size, max_blocks, num_blocks,  \
-        scale_log2, window, status);                                                             \
-  }
-  if (D == 128) PXL_PRE(128)
-  else if (D == 64) PXL_PRE(64)
-  else return PXL_ERR_INVALID_ARG;
-#undef PXL_PRE
-  return check_launch();
+  return attn_prefill_impl(q, q_stride, k_cache, v_cache, block_tables, cu_q, ctx_lens, out, out_stride,
+                           sinks, B, max_q_len, Hq, Hkv, D, page_size, max_blocks, num_blocks, scale,
+                           window, false, 1.f, 1.f, status, stream);
+}
+
+// Prefix-aware prefill over e4m3 caches (see pxl_attn_decode_fp8).
+PXL_EXPORT int pxl_attn_prefill_fp8(const void* q, int64_t q_stride, const void* k_cache,
+                                    const void* v_cache, const int* block_tables, const int* cu_q,
+                                    const int* ctx_lens, void* out, int64_t out_stride,
+                                    const float* sinks, int B, int max_q_len, int Hq, int Hkv, int D,
+                                    int page_size, int max_blocks, int64_t num_blocks, float scale,
+                                    int window, float k_scale, float v_scale, int* status,
+                                    pxl_stream_t stream) {
+  if (!(k_scale > 0.f) || !(v_scale > 0.f)) return PXL_ERR_INVALID_ARG;
+  return attn_prefill_impl(q, q_stride, k_cache, v_cache, block_tables, cu_q, ctx_lens, out, out_stride,
+                           sinks, B, max_q_len, Hq, Hkv, D, page_size, max_blocks, num_blocks, scale,
+                           window, true, k_scale, v_scale, status, stream);
 }
 
 // ----------------------------------------------------------------------------------------

@@ -5,6 +5,10 @@
 // (RMSNorm / RoPE / SiLU-mul, src/parallax/server/executor/sglang_executor.py:419-452)
 // and its own Metal cache-scatter kernel
 // (src/parallax_extensions/kernels/reshape_and_cache/reshape_and_cache.metal:32-96).
+#include <cuda_fp8.h>
+
+#include <type_traits>
+
 #include "common.cuh"
 #include "pxl_api.h"
 
@@ -165,15 +169,22 @@ rmsnorm_strided_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __re
 // ------------------------------------------------- q/k norm + RoPE + cache scatter
 // One warp per (token, head slot). Head slots: [0,Hq) q heads, [Hq,Hq+Hkv) k heads,
 // [Hq+Hkv, Hq+2Hkv) v heads. D <= 256, D % 32 == 0... each lane owns D/32 contiguous dims.
-template <int D>
+// FP8: the caches hold e4m3 bytes; a value is stored as value * inv_scale (saturating), the
+// attention kernels multiply by the scale again when they read it (the reference's optional
+// fp8 cache: src/parallax_extensions/kernels/reshape_and_cache/reshape_and_cache.metal:32-96).
+__device__ __forceinline__ uint8_t to_e4m3(float x) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+}
+
+template <int D, bool FP8 = false>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_cache_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ q_norm_w,
                           const bf16* __restrict__ k_norm_w, const float* __restrict__ cos_sin,
                           const int* __restrict__ positions,
-                          const int64_t* __restrict__ slot_mapping, bf16* __restrict__ k_cache,
-                          bf16* __restrict__ v_cache, int T, int Hq, int Hkv, int rot_dim,
+                          const int64_t* __restrict__ slot_mapping, void* __restrict__ k_cache,
+                          void* __restrict__ v_cache, int T, int Hq, int Hkv, int rot_dim,
                           int page_size, int64_t num_slots, float eps, float w_offset,
-                          int* status) {
+                          float k_inv_scale, float v_inv_scale, int* status) {
   constexpr int EPL = D / 32;  // elements per lane
   __shared__ float sh[8][D];
   pdl_wait();
@@ -239,20 +250,36 @@ qk_norm_rope_cache_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ q_nor
     return;
   }
   const int kvh = is_k ? hs - Hq : hs - Hq - Hkv;
-  bf16* cache = is_k ? k_cache : v_cache;
   const int64_t blk = slot / page_size;
   const int off = static_cast<int>(slot % page_size);
-  bf16* dst = cache + ((blk * Hkv + kvh) * page_size + off) * static_cast<int64_t>(D);
+  const int64_t at = ((blk * Hkv + kvh) * page_size + off) * static_cast<int64_t>(D);
+  if constexpr (FP8) {
+    uint8_t* dst = static_cast<uint8_t*>(is_k ? k_cache : v_cache) + at;
+    const float inv = is_k ? k_inv_scale : v_inv_scale;
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) dst[lane * EPL + j] = __float2bfloat16(v[j]);
+    for (int j = 0; j < EPL; ++j) dst[lane * EPL + j] = to_e4m3(v[j] * inv);
+  } else {
+    bf16* dst = static_cast<bf16*>(is_k ? k_cache : v_cache) + at;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) dst[lane * EPL + j] = __float2bfloat16(v[j]);
+  }
 }
 
 // ------------------------------------------------------------ plain cache scatter
+template <bool FP8>
 __global__ void __launch_bounds__(256)
 reshape_and_cache_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, int64_t k_stride,
                          int64_t v_stride, const int64_t* __restrict__ slot_mapping,
-                         bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int Hkv, int Dk,
-                         int Dv, int page_size, int64_t num_slots, int* status) {
+                         void* __restrict__ k_cache_v, void* __restrict__ v_cache_v, int Hkv, int Dk,
+                         int Dv, int page_size, int64_t num_slots, float k_inv_scale,
+                         float v_inv_scale, int* status) {
+  using CT = typename std::conditional<FP8, uint8_t, bf16>::type;
+  CT* k_cache = static_cast<CT*>(k_cache_v);
+  CT* v_cache = static_cast<CT*>(v_cache_v);
+  auto conv = [](bf16 x, float inv) -> CT {
+    if constexpr (FP8) return to_e4m3(__bfloat162float(x) * inv);
+    else return x;
+  };
   const int t = blockIdx.x;
   const int64_t slot = slot_mapping[t];
   if (slot < 0) return;
@@ -266,14 +293,14 @@ reshape_and_cache_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v,
     for (int i = threadIdx.x; i < Hkv * Dk; i += blockDim.x) {
       const int h = i / Dk, d = i % Dk;
       k_cache[((blk * Hkv + h) * page_size + off) * static_cast<int64_t>(Dk) + d] =
-          k[t * k_stride + i];
+          conv(k[t * k_stride + i], k_inv_scale);
     }
   }
   if (v_cache) {
     for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
       const int h = i / Dv, d = i % Dv;
       v_cache[((blk * Hkv + h) * page_size + off) * static_cast<int64_t>(Dv) + d] =
-          v[t * v_stride + i];
+          conv(v[t * v_stride + i], v_inv_scale);
     }
   }
 }
@@ -386,22 +413,30 @@ PXL_EXPORT int pxl_rmsnorm_strided(const void* x, int64_t ldx, const void* weigh
   return check_launch();
 }
 
-PXL_EXPORT int pxl_qk_norm_rope_cache(void* qkv, const void* q_norm_w, const void* k_norm_w,
-                                      const float* cos_sin, const int* positions,
-                                      const int64_t* slot_mapping, void* k_cache, void* v_cache,
-                                      int T, int Hq, int Hkv, int D, int rot_dim, int page_size,
-                                      int64_t num_slots, float eps, float norm_w_offset,
-                                      int* status, pxl_stream_t stream) {
+namespace {
+int qk_norm_rope_cache_impl(void* qkv, const void* q_norm_w, const void* k_norm_w,
+                            const float* cos_sin, const int* positions,
+                            const int64_t* slot_mapping, void* k_cache, void* v_cache, int T, int Hq,
+                            int Hkv, int D, int rot_dim, int page_size, int64_t num_slots, float eps,
+                            float norm_w_offset, bool cache_fp8, float k_inv_scale,
+                            float v_inv_scale, int* status, pxl_stream_t stream) {
   if (T <= 0) return PXL_OK;
   if (rot_dim > D || (rot_dim & 1)) return PXL_ERR_INVALID_ARG;
   const int64_t warps = static_cast<int64_t>(T) * (Hq + 2 * Hkv);
   const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
 #define PXL_QKROPE(DD)                                                                        \
-  pxl_host::launch(qk_norm_rope_cache_kernel<DD>, grid, 256, 0, stream,                        \
-      static_cast<bf16*>(qkv), static_cast<const bf16*>(q_norm_w),                            \
-      static_cast<const bf16*>(k_norm_w), cos_sin, positions, slot_mapping,                   \
-      static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), T, Hq, Hkv, rot_dim,          \
-      page_size, num_slots, eps, norm_w_offset, status)
+  if (cache_fp8)                                                                              \
+    pxl_host::launch(qk_norm_rope_cache_kernel<DD, true>, grid, 256, 0, stream,                \
+        static_cast<bf16*>(qkv), static_cast<const bf16*>(q_norm_w),                          \
+        static_cast<const bf16*>(k_norm_w), cos_sin, positions, slot_mapping, k_cache,        \
+        v_cache, T, Hq, Hkv, rot_dim, page_size, num_slots, eps, norm_w_offset, k_inv_scale,  \
+        v_inv_scale, status);                                                                 \
+  else                                                                                        \
+    pxl_host::launch(qk_norm_rope_cache_kernel<DD, false>, grid, 256, 0, stream,               \
+        static_cast<bf16*>(qkv), static_cast<const bf16*>(q_norm_w),                          \
+        static_cast<const bf16*>(k_norm_w), cos_sin, positions, slot_mapping, k_cache,        \
+        v_cache, T, Hq, Hkv, rot_dim, page_size, num_slots, eps, norm_w_offset, 1.f, 1.f,     \
+        status)
   switch (D) {
     case 64: PXL_QKROPE(64); break;
     case 96: PXL_QKROPE(96); break;
@@ -411,6 +446,32 @@ PXL_EXPORT int pxl_qk_norm_rope_cache(void* qkv, const void* q_norm_w, const voi
   }
 #undef PXL_QKROPE
   return check_launch();
+}
+}  // namespace
+
+PXL_EXPORT int pxl_qk_norm_rope_cache(void* qkv, const void* q_norm_w, const void* k_norm_w,
+                                      const float* cos_sin, const int* positions,
+                                      const int64_t* slot_mapping, void* k_cache, void* v_cache,
+                                      int T, int Hq, int Hkv, int D, int rot_dim, int page_size,
+                                      int64_t num_slots, float eps, float norm_w_offset,
+                                      int* status, pxl_stream_t stream) {
+  return qk_norm_rope_cache_impl(qkv, q_norm_w, k_norm_w, cos_sin, positions, slot_mapping, k_cache,
+                                 v_cache, T, Hq, Hkv, D, rot_dim, page_size, num_slots, eps,
+                                 norm_w_offset, false, 1.f, 1.f, status, stream);
+}
+
+// Same with e4m3 caches: K is stored as k / k_scale, V as v / v_scale (scales > 0).
+PXL_EXPORT int pxl_qk_norm_rope_cache_fp8(void* qkv, const void* q_norm_w, const void* k_norm_w,
+                                          const float* cos_sin, const int* positions,
+                                          const int64_t* slot_mapping, void* k_cache, void* v_cache,
+                                          int T, int Hq, int Hkv, int D, int rot_dim, int page_size,
+                                          int64_t num_slots, float eps, float norm_w_offset,
+                                          float k_scale, float v_scale, int* status,
+                                          pxl_stream_t stream) {
+  if (!(k_scale > 0.f) || !(v_scale > 0.f)) return PXL_ERR_INVALID_ARG;
+  return qk_norm_rope_cache_impl(qkv, q_norm_w, k_norm_w, cos_sin, positions, slot_mapping, k_cache,
+                                 v_cache, T, Hq, Hkv, D, rot_dim, page_size, num_slots, eps,
+                                 norm_w_offset, true, 1.f / k_scale, 1.f / v_scale, status, stream);
 }
 
 // dst[dst_idx[i]] = src[src_idx[i]]: the decode rows of a step take their input ids from the token
@@ -441,10 +502,22 @@ PXL_EXPORT int pxl_reshape_and_cache(const void* k, const void* v, int64_t k_str
                                      void* v_cache, int T, int Hkv, int Dk, int Dv, int page_size,
                                      int64_t num_slots, int* status, pxl_stream_t stream) {
   if (T <= 0) return PXL_OK;
-  reshape_and_cache_kernel<<<T, 256, 0, stream>>>(
+  reshape_and_cache_kernel<false><<<T, 256, 0, stream>>>(
       static_cast<const bf16*>(k), static_cast<const bf16*>(v), k_stride, v_stride, slot_mapping,
-      static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), Hkv, Dk, Dv, page_size, num_slots,
-      status);
+      k_cache, v_cache, Hkv, Dk, Dv, page_size, num_slots, 1.f, 1.f, status);
+  return check_launch();
+}
+
+PXL_EXPORT int pxl_reshape_and_cache_fp8(const void* k, const void* v, int64_t k_stride,
+                                         int64_t v_stride, const int64_t* slot_mapping,
+                                         void* k_cache, void* v_cache, int T, int Hkv, int Dk, int Dv,
+                                         int page_size, int64_t num_slots, float k_scale,
+                                         float v_scale, int* status, pxl_stream_t stream) {
+  if (T <= 0) return PXL_OK;
+  if (!(k_scale > 0.f) || !(v_scale > 0.f)) return PXL_ERR_INVALID_ARG;
+  reshape_and_cache_kernel<true><<<T, 256, 0, stream>>>(
+      static_cast<const bf16*>(k), static_cast<const bf16*>(v), k_stride, v_stride, slot_mapping,
+      k_cache, v_cache, Hkv, Dk, Dv, page_size, num_slots, 1.f / k_scale, 1.f / v_scale, status);
   return check_launch();
 }
 

@@ -72,6 +72,30 @@ int pxl_reshape_and_cache(const void* k, const void* v, int64_t k_stride, int64_
                           const int64_t* slot_mapping, void* k_cache, void* v_cache, int T,
                           int Hkv, int Dk, int Dv, int page_size, int64_t num_slots, int* status,
                           pxl_stream_t stream);
+// e4m3 KV cache ("fp8 KV"): the caches hold one byte per element; K is stored as k / k_scale and V as
+// v / v_scale (saturating, scales > 0) and the *_fp8 attention entry points undo the scaling. Same
+// arguments as the bf16 functions plus the two scales.
+int pxl_qk_norm_rope_cache_fp8(void* qkv, const void* q_norm_w, const void* k_norm_w,
+                               const float* cos_sin, const int* positions,
+                               const int64_t* slot_mapping, void* k_cache, void* v_cache, int T,
+                               int Hq, int Hkv, int D, int rot_dim, int page_size, int64_t num_slots,
+                               float eps, float norm_w_offset, float k_scale, float v_scale,
+                               int* status, pxl_stream_t stream);
+int pxl_reshape_and_cache_fp8(const void* k, const void* v, int64_t k_stride, int64_t v_stride,
+                              const int64_t* slot_mapping, void* k_cache, void* v_cache, int T,
+                              int Hkv, int Dk, int Dv, int page_size, int64_t num_slots,
+                              float k_scale, float v_scale, int* status, pxl_stream_t stream);
+int pxl_attn_decode_fp8(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                        const int* block_tables, const int* ctx_lens, void* out, float* workspace,
+                        const float* sinks, int B, int Hq, int Hkv, int D, int page_size,
+                        int max_blocks, int64_t num_blocks, float scale, int window, int num_splits,
+                        int max_ctx, float k_scale, float v_scale, int* status, pxl_stream_t stream);
+int pxl_attn_prefill_fp8(const void* q, int64_t q_stride, const void* k_cache, const void* v_cache,
+                         const int* block_tables, const int* cu_q, const int* ctx_lens, void* out,
+                         int64_t out_stride, const float* sinks, int B, int max_q_len, int Hq,
+                         int Hkv, int D, int page_size, int max_blocks, int64_t num_blocks,
+                         float scale, int window, float k_scale, float v_scale, int* status,
+                         pxl_stream_t stream);
 // out[T, I] = act(x[:, :I]) * x[:, I:]; mode 0 = silu, 1 = clipped swiglu-oai
 // (alpha 1.702, limit), 2 = gelu-tanh.
 int pxl_act_mul(const void* x, void* out, int T, int I, int mode, float limit, pxl_stream_t stream);

@@ -40,6 +40,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--kv-cache-memory-fraction", type=float, default=0.8,
                    help="Fraction of the free device memory given to the KV cache")
     p.add_argument("--kv-block-size", type=int, default=16, help="Block size for KV cache management")
+    p.add_argument("--kv-cache-dtype", type=str, default="auto", choices=["auto", "bf16", "fp8_e4m3"],
+                   help="Storage type of the K / V pages of softmax-attention layers (auto: the model's dtype)")
     p.add_argument("--disable-prefix-cache", dest="enable_prefix_cache", action="store_false", default=True,
                    help="Disable the radix prefix cache")
     p.add_argument("--chunked-prefill-size", type=int, default=1024, help="Max prompt tokens per prefill chunk (0: off)")

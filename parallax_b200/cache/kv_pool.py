@@ -32,10 +32,28 @@ class LayerCache:
     index_k: Optional[torch.Tensor] = None  # DSA / MSA indexer keys
     conv_state: Optional[torch.Tensor] = None
     rec_state: Optional[torch.Tensor] = None
+    # e4m3 K / V caches hold value / scale; the attention kernels multiply by the scale again
+    k_scale: float = 1.0
+    v_scale: float = 1.0
+
+    @property
+    def kv_scale(self) -> tuple:
+        return (self.k_scale, self.v_scale)
 
     def __iter__(self):  # lets attention layers unpack ``k, v = cache``
         yield self.k
         yield self.v
+
+
+def kv_cache_torch_dtype(name: Optional[str], model_dtype):
+    """Storage dtype of the K / V pages for a ``--kv-cache-dtype`` value."""
+    if name in (None, "", "auto"):
+        return model_dtype
+    if name in ("fp8", "fp8_e4m3", "float8_e4m3fn"):
+        return torch.float8_e4m3fn
+    if name in ("bf16", "bfloat16"):
+        return torch.bfloat16
+    raise ValueError(f"unknown KV cache dtype {name!r} (auto, bf16, fp8_e4m3)")
 
 
 def linear_dims(cfg: ModelConfig, tp: int = 1) -> tuple[int, int, int, int, int]:
@@ -46,13 +64,16 @@ def linear_dims(cfg: ModelConfig, tp: int = 1) -> tuple[int, int, int, int, int]
     return conv_dim, max(cfg.linear_conv_kernel_dim - 1, 0), hv, dv, dk
 
 
-def bytes_per_block(cfg: ModelConfig, start: int, end: int, page: int, elem: int = 2, tp: int = 1) -> int:
+def bytes_per_block(cfg: ModelConfig, start: int, end: int, page: int, elem: int = 2, tp: int = 1,
+                    kv_elem: Optional[int] = None) -> int:
+    """``kv_elem``: bytes per element of the K / V pages when they differ from the model's (e4m3: 1)."""
     total = 0
+    kv_elem = kv_elem or elem
     for li in range(start, end):
         kind = cfg.layer_kind(li)
         if kind in (ATTENTION, MSA_ATTENTION):
             hkv = max(1, cfg.num_key_value_heads // tp)
-            total += 2 * hkv * page * cfg.head_dim * elem
+            total += 2 * hkv * page * cfg.head_dim * kv_elem
             if kind == MSA_ATTENTION:
                 total += page * int(cfg.raw.get("index_head_dim") or 0) * elem
         elif kind in (MLA_ATTENTION, DSA_ATTENTION):
@@ -73,7 +94,13 @@ def bytes_per_linear_slot(cfg: ModelConfig, start: int, end: int, elem: int = 2,
 
 class KVPool:
     def __init__(self, cfg: ModelConfig, start_layer: int, end_layer: int, num_blocks: int,
-                 page_size: int, device, dtype, tp: int = 1, num_linear_slots: int = 0):
+                 page_size: int, device, dtype, tp: int = 1, num_linear_slots: int = 0,
+                 kv_cache_dtype: Optional[str] = None, kv_scale: tuple = (1.0, 1.0)):
+        """``kv_cache_dtype="fp8_e4m3"`` keeps the K / V pages of the softmax-attention layers as e4m3 bytes
+        (half the memory and half the bytes a decode step reads); latent, indexer and recurrent caches stay in
+        the model's dtype."""
+        kv_dt = kv_cache_torch_dtype(kv_cache_dtype, dtype)
+        self.kv_cache_dtype = kv_dt
         self.cfg = cfg
         self.num_blocks = num_blocks
         self.page_size = page_size
@@ -86,8 +113,10 @@ class KVPool:
             if kind in (ATTENTION, MSA_ATTENTION):
                 hkv = max(1, cfg.num_key_value_heads // tp)
                 shape = (num_blocks, hkv, page_size, cfg.head_dim)
-                lc.k = torch.zeros(shape, device=self.device, dtype=dtype)
-                lc.v = torch.zeros(shape, device=self.device, dtype=dtype)
+                lc.k = torch.zeros(shape, device=self.device, dtype=kv_dt)
+                lc.v = torch.zeros(shape, device=self.device, dtype=kv_dt)
+                if kv_dt == torch.float8_e4m3fn:
+                    lc.k_scale, lc.v_scale = float(kv_scale[0]), float(kv_scale[1])
                 if kind == MSA_ATTENTION:
                     lc.index_k = torch.zeros((num_blocks, 1, page_size, int(cfg.raw.get("index_head_dim") or 0)),
                                              device=self.device, dtype=dtype)
@@ -126,9 +155,10 @@ class KVPool:
 
 
 def plan_num_blocks(cfg: ModelConfig, start: int, end: int, page: int, free_bytes: int,
-                    fraction: float, elem: int = 2, tp: int = 1, max_tokens: Optional[int] = None) -> int:
+                    fraction: float, elem: int = 2, tp: int = 1, max_tokens: Optional[int] = None,
+                    kv_elem: Optional[int] = None) -> int:
     """Number of KV blocks that fit into ``fraction`` of the free device memory."""
-    per_block = bytes_per_block(cfg, start, end, page, elem, tp)
+    per_block = bytes_per_block(cfg, start, end, page, elem, tp, kv_elem)
     if per_block == 0:
         return 0
     n = int(free_bytes * fraction) // per_block

@@ -192,6 +192,7 @@ class Engine:
         async_scheduling: Optional[bool] = None,
         linear_prefix_slots: Optional[int] = None,
         lora: Optional[dict] = None,
+        kv_cache_dtype: Optional[str] = None,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -218,7 +219,7 @@ class Engine:
                                            kv_fraction=kv_fraction / len(stage_layers), seed=seed, weights=w,
                                            max_kv_tokens=max_kv_tokens, max_positions=max_positions,
                                            num_linear_slots=(max_requests + self.linear_prefix_slots)
-                                           if cfg.has_linear_layers else 0))
+                                           if cfg.has_linear_layers else 0, kv_cache_dtype=kv_cache_dtype))
         nb = min(st.num_blocks for st in self.stages)
         self.planner = Planner(cfg, nb, page_size, max_batch_size, max_num_tokens_per_batch,
                                micro_batch_ratio, chunked_prefill_size, enable_prefix_cache,

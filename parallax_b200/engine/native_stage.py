@@ -72,6 +72,8 @@ class NativeDenseStage:
     def supported(stage) -> bool:
         if stage.device.type != "cuda" or not stage.layers or not stage.kv_caches:
             return False
+        if any(getattr(c, "k", None) is not None and c.k.dtype != stage.dtype for c in stage.kv_caches):
+            return False            # e4m3 KV pages: the per-layer path picks the fp8 kernels
         if getattr(stage, "dense_act_mode", 0) or stage.cfg.qk_norm_full or any(getattr(lw, "w_g", None) is not None for lw in stage.layers):
             return False
         return all(lw.moe is None and lw.w_gu is not None and isinstance(lw.w_gu, torch.Tensor) for lw in stage.layers)

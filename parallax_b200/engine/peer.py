@@ -43,12 +43,13 @@ class PeerExecutor:
                  micro_batch_ratio: int = 1, chunked_prefill_size: Optional[int] = 1024,
                  enable_prefix_cache: bool = True, max_total_length: int = 32768,
                  request_timeout_s: Optional[float] = 600, eos_token_id=None, seed: int = 0,
-                 weights: Optional[dict] = None, shared_state=None):
+                 weights: Optional[dict] = None, shared_state=None, kv_cache_dtype: Optional[str] = None):
         self.cfg, self.node_id = cfg, node_id
         self.device = torch.device(device)
         max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
         self.worker = StageWorker(cfg, start_layer, end_layer, self.device, dtype, page_size, num_blocks=num_blocks,
-                                  kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions)
+                                  kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
+                                  kv_cache_dtype=kv_cache_dtype)
         self.is_first, self.is_last = self.worker.is_first, self.worker.is_last
         self.planner = Planner(cfg, self.worker.num_blocks, page_size, max_batch_size, max_num_tokens_per_batch,
                                micro_batch_ratio, chunked_prefill_size, enable_prefix_cache, max_total_length,

@@ -17,9 +17,13 @@ logger = logging.getLogger(__name__)
 
 def plan_kv_blocks(cfg: ModelConfig, start: int, end: int, page_size: int, device: torch.device,
                    fraction: float, dtype: torch.dtype, tp: int = 1,
-                   max_tokens: Optional[int] = None, cpu_default_blocks: int = 256) -> int:
+                   max_tokens: Optional[int] = None, cpu_default_blocks: int = 256,
+                   kv_cache_dtype: Optional[str] = None) -> int:
     """KV blocks for a stage: ``fraction`` of the memory left after the weights are loaded."""
-    per_block = bytes_per_block(cfg, start, end, page_size, torch.empty(0, dtype=dtype).element_size(), tp)
+    from parallax_b200.cache.kv_pool import kv_cache_torch_dtype
+
+    kv_elem = torch.empty(0, dtype=kv_cache_torch_dtype(kv_cache_dtype, dtype)).element_size()
+    per_block = bytes_per_block(cfg, start, end, page_size, torch.empty(0, dtype=dtype).element_size(), tp, kv_elem)
     if per_block == 0:
         return 0
     if device.type != "cuda":
@@ -38,7 +42,8 @@ class StageWorker:
                  max_kv_tokens: Optional[int] = None, seed: int = 0, weights: Optional[dict] = None,
                  max_positions: Optional[int] = None, tp_rank: int = 0, tp_size: int = 1,
                  tp_group=None, num_linear_slots: int = 0, comm=None, ep_rank: int = 0, ep_size: int = 1,
-                 ep_comm=None, ep_local_init: bool = False):
+                 ep_comm=None, ep_local_init: bool = False, kv_cache_dtype: Optional[str] = None,
+                 kv_scale: tuple = (1.0, 1.0)):
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
@@ -54,10 +59,12 @@ class StageWorker:
             self.model.init_random(seed)
         if num_blocks is None:
             num_blocks = plan_kv_blocks(cfg, start_layer, end_layer, page_size, self.device,
-                                        kv_fraction, self.dtype, tp_size, max_kv_tokens)
+                                        kv_fraction, self.dtype, tp_size, max_kv_tokens,
+                                        kv_cache_dtype=kv_cache_dtype)
         self.num_blocks = num_blocks
         self.pool = KVPool(cfg, start_layer, end_layer, num_blocks, page_size, self.device, self.dtype,
-                           tp=tp_size, num_linear_slots=num_linear_slots)
+                           tp=tp_size, num_linear_slots=num_linear_slots, kv_cache_dtype=kv_cache_dtype,
+                           kv_scale=kv_scale)
         self.model.attach_kv(self.pool.layers)
         logger.info("stage [%d,%d) on %s: %.2f GB weights, %d KV blocks (%.2f GB)", start_layer,
                     end_layer, self.device, self.model.weight_bytes() / 1e9, num_blocks,

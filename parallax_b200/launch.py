@@ -72,7 +72,8 @@ def build_engine(args, cfg, loader, start: int, end: int, shared_state=None):
                   chunked_prefill_size=args.chunked_prefill_size, enable_prefix_cache=args.enable_prefix_cache,
                   max_total_length=args.max_sequence_length, request_timeout_s=args.request_timeout_s,
                   weights=weights, shared_state=shared_state,
-                  num_blocks=None if device != "cpu" else 1024, lora=_lora_spec(args))
+                  num_blocks=None if device != "cpu" else 1024, lora=_lora_spec(args),
+                  kv_cache_dtype=getattr(args, "kv_cache_dtype", None))
 
 
 def _lora_spec(args):

@@ -389,6 +389,7 @@ class DecoderStage(ExpertParallelMixin):
         if rows_lora is not None:
             qkv = self.lora.apply("qkv", li, xn, qkv, rows_lora, fb.extras.get("lora_plan"))
         kc, vc = self.kv_caches[li]
+        kvs = getattr(self.kv_caches[li], "kv_scale", (1.0, 1.0))
         qn, kn = lw.q_norm, lw.k_norm
         if cfg.qk_norm_full and qn is not None:
             # norm over the whole projection, in place on the column slices of the packed activation
@@ -397,16 +398,16 @@ class DecoderStage(ExpertParallelMixin):
                         out=qkv[:, Hq * D:(Hq + Hkv) * D])
             qn = kn = None
         ops.qk_norm_rope_cache(qkv, qn, kn, self.cos_sin, fb.positions, fb.slot_mapping,
-                               kc, vc, Hq, Hkv, D, cfg.rot_dim, cfg.rms_norm_eps, self.norm_offset)
+                               kc, vc, Hq, Hkv, D, cfg.rot_dim, cfg.rms_norm_eps, self.norm_offset, kv_scale=kvs)
         q = qkv.view(T, Hq + 2 * Hkv, D)[:, :Hq]
         attn = torch.empty((T, Hq, D), dtype=qkv.dtype, device=qkv.device)
         Tp = fb.num_prefill_tokens
         if Tp:
             ops.attn_prefill(q[:Tp], kc, vc, fb.p_block_tables, fb.p_cu_q, fb.p_ctx_lens, fb.p_max_q,
-                             self.scale, window=lw.window, sinks=lw.sinks, out=attn[:Tp])
+                             self.scale, window=lw.window, sinks=lw.sinks, out=attn[:Tp], kv_scale=kvs)
         if fb.num_decode:
             ops.attn_decode(q[Tp:], kc, vc, fb.d_block_tables, fb.d_ctx_lens, self.scale,
-                            window=lw.window, sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:])
+                            window=lw.window, sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:], kv_scale=kvs)
         if lw.w_g is not None:
             gate = torch.sigmoid(ops.linear(xn, lw.w_g).float()).to(attn.dtype)      # [T, Hq]
             attn = attn * gate.unsqueeze(-1)

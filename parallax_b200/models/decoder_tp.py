@@ -146,17 +146,18 @@ class TPDecoderStage(TPStageMixin, DecoderStage):
             qkv = comm.norm_ag_linear(h_shard, lw.ln1, eps, lw.w_qkv, bias=lw.b_qkv, w_offset=self.norm_offset)
             T_pad = qkv.shape[0]
             kc, vc = self.kv_caches[li]
+            kvs = getattr(self.kv_caches[li], "kv_scale", (1.0, 1.0))
             real = qkv[:T]
             ops.qk_norm_rope_cache(real, lw.q_norm, lw.k_norm, self.cos_sin, fb.positions, fb.slot_mapping, kc, vc,
-                                   hq, hkv, D, cfg.rot_dim, eps, self.norm_offset)
+                                   hq, hkv, D, cfg.rot_dim, eps, self.norm_offset, kv_scale=kvs)
             q = real.view(T, hq + 2 * hkv, D)[:, :hq]
             attn = torch.zeros((T_pad, hq, D), dtype=qkv.dtype, device=qkv.device)
             if Tp:
                 ops.attn_prefill(q[:Tp], kc, vc, fb.p_block_tables, fb.p_cu_q, fb.p_ctx_lens, fb.p_max_q,
-                                 self.scale, window=lw.window, sinks=lw.sinks, out=attn[:Tp])
+                                 self.scale, window=lw.window, sinks=lw.sinks, out=attn[:Tp], kv_scale=kvs)
             if fb.num_decode:
                 ops.attn_decode(q[Tp:], kc, vc, fb.d_block_tables, fb.d_ctx_lens, self.scale, window=lw.window,
-                                sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:T])
+                                sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:T], kv_scale=kvs)
             h_shard = comm.linear_rs(attn.view(T_pad, hq * D), lw.w_o, residual=h_shard)
             if lw.moe is not None:
                 # attention is tensor parallel, the experts are expert parallel: every rank routes its

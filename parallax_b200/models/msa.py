@@ -133,8 +133,9 @@ class MSAStage(DecoderStage):
                              self.norm_offset).contiguous()
         qkv = ops.linear(xn, lw.w_qkv, bias=lw.b_qkv)
         kc, vc = cache.k, cache.v
+        kvs = cache.kv_scale
         ops.qk_norm_rope_cache(qkv, lw.q_norm, lw.k_norm, self.cos_sin, fb.positions, fb.slot_mapping, kc, vc, Hq, Hkv,
-                               D, cfg.rot_dim, eps, self.norm_offset)
+                               D, cfg.rot_dim, eps, self.norm_offset, kv_scale=kvs)
         q = qkv.view(T, Hq + 2 * Hkv, D)[:, :Hq]
         attn = torch.empty((T, Hq, D), dtype=qkv.dtype, device=qkv.device)
         page = kc.shape[-2]
@@ -144,18 +145,18 @@ class MSAStage(DecoderStage):
             sc = ops.msa_block_scores(iq[part], cache.index_k, tables, cu_q, pos, max_ctx, self.sparse_block, self.scale)
             vt, vctx = ops.msa_select(sc, pos, tables, cu_q, page, self.sparse_block, self.topk_blocks, self.init_blocks,
                                       self.local_blocks)
-            ops.attn_decode(q[part], kc, vc, vt, vctx, self.scale, max_ctx=limit, out=attn[part])
+            ops.attn_decode(q[part], kc, vc, vt, vctx, self.scale, max_ctx=limit, out=attn[part], kv_scale=kvs)
 
         if Tp:
             if sparse_p:
                 sparse(slice(0, Tp), fb.p_block_tables, fb.p_cu_q, fb.p_max_ctx)
             else:
                 ops.attn_prefill(q[:Tp], kc, vc, fb.p_block_tables, fb.p_cu_q, fb.p_ctx_lens, fb.p_max_q, self.scale,
-                                 out=attn[:Tp])
+                                 out=attn[:Tp], kv_scale=kvs)
         if fb.num_decode:
             if sparse_d:
                 sparse(slice(Tp, T), fb.d_block_tables, None, fb.d_max_ctx)
             else:
                 ops.attn_decode(q[Tp:], kc, vc, fb.d_block_tables, fb.d_ctx_lens, self.scale, max_ctx=fb.d_max_ctx,
-                                out=attn[Tp:])
+                                out=attn[Tp:], kv_scale=kvs)
         return attn.view(T, Hq * D)

@@ -59,6 +59,14 @@ _SIGS = {
                                c_int, c_int64, c_float, c_float, _P, _P],
     "pxl_reshape_and_cache": [_P, _P, c_int64, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int,
                               c_int, c_int64, _P, _P],
+    "pxl_qk_norm_rope_cache_fp8": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_int64, c_float, c_float, c_float, c_float, _P, _P],
+    "pxl_reshape_and_cache_fp8": [_P, _P, c_int64, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int,
+                                  c_int, c_int64, c_float, c_float, _P, _P],
+    "pxl_attn_decode_fp8": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_int64, c_float, c_int, c_int, c_int, c_float, c_float, _P, _P],
+    "pxl_attn_prefill_fp8": [_P, c_int64, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_float, c_float, _P, _P],
     "pxl_act_mul": [_P, _P, c_int, c_int, c_int, c_float, _P],
     "pxl_gather_rows": [_P, _P, _P, c_int, c_int, c_int64, c_int, _P, _P],
     "pxl_add_inplace": [_P, _P, c_int64, _P],

@@ -233,6 +233,10 @@ def rmsnorm(
     return out
 
 
+def _is_fp8_cache(t: Optional[torch.Tensor]) -> bool:
+    return t is not None and t.dtype == torch.float8_e4m3fn
+
+
 def qk_norm_rope_cache(
     qkv: torch.Tensor,
     q_norm_w: Optional[torch.Tensor],
@@ -248,8 +252,10 @@ def qk_norm_rope_cache(
     rot_dim: int,
     eps: float = 1e-6,
     norm_w_offset: float = 0.0,
+    kv_scale: tuple = (1.0, 1.0),
 ) -> None:
-    """In place on ``qkv``: per-head norm + RoPE for q and k; k, v scattered to the cache."""
+    """In place on ``qkv``: per-head norm + RoPE for q and k; k, v scattered to the cache (bf16, or e4m3
+    bytes divided by ``kv_scale`` when the cache tensors are ``float8_e4m3fn``)."""
     T = qkv.shape[0]
     assert qkv.is_contiguous() and qkv.shape[1] == (num_q_heads + 2 * num_kv_heads) * head_dim
     assert positions.dtype == torch.int32
@@ -259,6 +265,17 @@ def qk_norm_rope_cache(
     slots = k_cache.shape[0] * page if k_cache is not None else 0
     if cos_sin is None:
         rot_dim = 0
+    if _is_fp8_cache(k_cache):
+        check(
+            _lib.lib().pxl_qk_norm_rope_cache_fp8(
+                qkv.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin), positions.data_ptr(),
+                _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), T, num_q_heads, num_kv_heads,
+                head_dim, rot_dim, page, slots, eps, norm_w_offset, float(kv_scale[0]), float(kv_scale[1]),
+                status_tensor(qkv.device).data_ptr(), _stream(qkv.device)),
+            "pxl_qk_norm_rope_cache_fp8",
+        )
+        _count()
+        return
     check(
         _lib.lib().pxl_qk_norm_rope_cache(
             qkv.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin), positions.data_ptr(),
@@ -276,14 +293,26 @@ def reshape_and_cache(
     slot_mapping: torch.Tensor,
     k_cache: Optional[torch.Tensor],
     v_cache: Optional[torch.Tensor],
+    kv_scale: tuple = (1.0, 1.0),
 ) -> None:
-    """Scatter k, v ``[T, H, D]`` into paged caches ``[blocks, H, page, D]``."""
+    """Scatter k, v ``[T, H, D]`` into paged caches ``[blocks, H, page, D]`` (bf16 or scaled e4m3)."""
     ref = k if k is not None else v
     T = ref.shape[0]
     cache = k_cache if k_cache is not None else v_cache
     Hkv, page = cache.shape[1], cache.shape[2]
     Dk = k_cache.shape[3] if k_cache is not None else 0
     Dv = v_cache.shape[3] if v_cache is not None else 0
+    if _is_fp8_cache(cache):
+        check(
+            _lib.lib().pxl_reshape_and_cache_fp8(
+                _ptr(k), _ptr(v), k.stride(0) if k is not None else 0,
+                v.stride(0) if v is not None else 0, slot_mapping.data_ptr(), _ptr(k_cache),
+                _ptr(v_cache), T, Hkv, Dk, Dv, page, cache.shape[0] * page, float(kv_scale[0]),
+                float(kv_scale[1]), status_tensor(ref.device).data_ptr(), _stream(ref.device)),
+            "pxl_reshape_and_cache_fp8",
+        )
+        _count()
+        return
     check(
         _lib.lib().pxl_reshape_and_cache(
             _ptr(k), _ptr(v), k.stride(0) if k is not None else 0,
@@ -352,8 +381,10 @@ def attn_decode(
     max_ctx: int = 0,
     num_splits: int = 0,
     out: Optional[torch.Tensor] = None,
+    kv_scale: tuple = (1.0, 1.0),
 ) -> torch.Tensor:
-    """q ``[B, Hq, D]`` (may be a strided view into a packed qkv buffer) vs the paged cache."""
+    """q ``[B, Hq, D]`` (may be a strided view into a packed qkv buffer) vs the paged cache (bf16, or e4m3
+    with ``kv_scale``)."""
     B, Hq, D = q.shape
     assert q.stride(2) == 1 and q.stride(1) == D
     Hkv, page = k_cache.shape[1], k_cache.shape[2]
@@ -366,6 +397,17 @@ def attn_decode(
     ws = None
     if num_splits > 1:
         ws = workspace(q.device, "attn_decode", B * Hq * num_splits * (D + 2) * 4)
+    if _is_fp8_cache(k_cache):
+        check(
+            _lib.lib().pxl_attn_decode_fp8(
+                q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                block_tables.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(), _ptr(ws), _ptr(sinks),
+                B, Hq, Hkv, D, page, block_tables.shape[1], k_cache.shape[0], scale, window, num_splits, max_ctx,
+                float(kv_scale[0]), float(kv_scale[1]), status_tensor(q.device).data_ptr(), _stream(q.device)),
+            "pxl_attn_decode_fp8",
+        )
+        _count(2 if num_splits > 1 else 1)
+        return out
     check(
         _lib.lib().pxl_attn_decode(
             q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
@@ -391,6 +433,7 @@ def attn_prefill(
     window: int = 0,
     sinks: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
+    kv_scale: tuple = (1.0, 1.0),
 ) -> torch.Tensor:
     """q ``[T, Hq, D]`` (may be a strided view into a packed qkv buffer)."""
     T, Hq, D = q.shape
@@ -400,6 +443,18 @@ def attn_prefill(
         out = torch.empty((T, Hq, D), dtype=q.dtype, device=q.device)
     B = ctx_lens.numel()
     if T == 0 or B == 0:
+        return out
+    if _is_fp8_cache(k_cache):
+        check(
+            _lib.lib().pxl_attn_prefill_fp8(
+                q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                block_tables.data_ptr(), cu_q.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(),
+                out.stride(0), _ptr(sinks), B, max_q_len, Hq, Hkv, D, page, block_tables.shape[1],
+                k_cache.shape[0], scale, window, float(kv_scale[0]), float(kv_scale[1]),
+                status_tensor(q.device).data_ptr(), _stream(q.device)),
+            "pxl_attn_prefill_fp8",
+        )
+        _count()
         return out
     if D == 128 and page in (16, 32, 64) and not _PREFILL_LEGACY and q.stride(0) % 8 == 0 \
             and q.data_ptr() % 16 == 0 and out.stride(1) == D and k_cache.shape[0] * Hkv * page < (1 << 31):

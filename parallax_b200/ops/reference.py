@@ -77,8 +77,11 @@ def build_cos_sin(max_pos: int, rot_dim: int, base: float, device=None, inv_freq
     return tab.float().to(device) if device is not None else tab.float()
 
 
-def _scatter_cache(cache, x, slot_mapping):
-    # cache [blocks, H, page, D]; x [T, H, D]
+_E4M3_MAX = 448.0
+
+
+def _scatter_cache(cache, x, slot_mapping, scale: float = 1.0):
+    # cache [blocks, H, page, D]; x [T, H, D]. An e4m3 cache stores x / scale, saturating.
     page = cache.shape[2]
     valid = slot_mapping >= 0
     if not bool(valid.any()):
@@ -86,12 +89,16 @@ def _scatter_cache(cache, x, slot_mapping):
     slots = slot_mapping[valid]
     blk = slots // page
     off = slots % page
-    cache[blk, :, off, :] = x[valid].to(cache.dtype)
+    if cache.dtype == torch.float8_e4m3fn:
+        val = (x[valid].float() / scale).clamp(-_E4M3_MAX, _E4M3_MAX).to(cache.dtype)
+        cache.view(torch.uint8)[blk, :, off, :] = val.view(torch.uint8)
+    else:
+        cache[blk, :, off, :] = x[valid].to(cache.dtype)
 
 
 def qk_norm_rope_cache(qkv, q_norm_w, k_norm_w, cos_sin, positions, slot_mapping, k_cache,
                        v_cache, num_q_heads, num_kv_heads, head_dim, rot_dim, eps=1e-6,
-                       norm_w_offset: float = 0.0):
+                       norm_w_offset: float = 0.0, kv_scale=(1.0, 1.0)):
     T = qkv.shape[0]
     Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
     x = qkv.view(T, Hq + 2 * Hkv, D)
@@ -120,17 +127,17 @@ def qk_norm_rope_cache(qkv, q_norm_w, k_norm_w, cos_sin, positions, slot_mapping
     kn = rope(norm(k, k_norm_w)).to(qkv.dtype)
     q.copy_(qn)
     if k_cache is not None and slot_mapping is not None:
-        _scatter_cache(k_cache, kn, slot_mapping)
-        _scatter_cache(v_cache, v, slot_mapping)
+        _scatter_cache(k_cache, kn, slot_mapping, kv_scale[0])
+        _scatter_cache(v_cache, v, slot_mapping, kv_scale[1])
     else:
         k.copy_(kn)
 
 
-def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache):
+def reshape_and_cache(k, v, slot_mapping, k_cache, v_cache, kv_scale=(1.0, 1.0)):
     if k is not None and k_cache is not None:
-        _scatter_cache(k_cache, k, slot_mapping)
+        _scatter_cache(k_cache, k, slot_mapping, kv_scale[0])
     if v is not None and v_cache is not None:
-        _scatter_cache(v_cache, v, slot_mapping)
+        _scatter_cache(v_cache, v, slot_mapping, kv_scale[1])
 
 
 def act_mul(x, mode: int = 0, limit: float = 7.0):
@@ -160,11 +167,14 @@ def add_inplace(y, x):
     return y
 
 
-def _gather_kv(cache, block_table, n):
-    # cache [blocks, H, page, D] -> [H, n, D]
+def _gather_kv(cache, block_table, n, scale: float = 1.0):
+    # cache [blocks, H, page, D] -> [H, n, D]; an e4m3 cache is widened and multiplied by its scale
     page = cache.shape[2]
     nb = (n + page - 1) // page
-    blocks = cache[block_table[:nb].long()]  # [nb, H, page, D]
+    if cache.dtype == torch.float8_e4m3fn:
+        blocks = cache.view(torch.uint8)[block_table[:nb].long()].view(torch.float8_e4m3fn).float() * scale
+    else:
+        blocks = cache[block_table[:nb].long()]  # [nb, H, page, D]
     return blocks.permute(1, 0, 2, 3).reshape(cache.shape[1], nb * page, cache.shape[3])[:, :n]
 
 
@@ -193,7 +203,7 @@ def _attend(q, k, v, scale, q_pos, window, sinks):
 
 
 def attn_decode(q, k_cache, v_cache, block_tables, ctx_lens, scale, window=0, sinks=None,
-                max_ctx=0, num_splits=0, out=None):
+                max_ctx=0, num_splits=0, out=None, kv_scale=(1.0, 1.0)):
     B = q.shape[0]
     res = torch.zeros_like(q) if out is None else out
     for b in range(B):
@@ -201,15 +211,15 @@ def attn_decode(q, k_cache, v_cache, block_tables, ctx_lens, scale, window=0, si
         if n <= 0:
             res[b] = 0
             continue
-        k = _gather_kv(k_cache, block_tables[b], n)
-        v = _gather_kv(v_cache, block_tables[b], n)
+        k = _gather_kv(k_cache, block_tables[b], n, kv_scale[0])
+        v = _gather_kv(v_cache, block_tables[b], n, kv_scale[1])
         pos = torch.tensor([n - 1], device=q.device)
         res[b] = _attend(q[b:b + 1], k, v, scale, pos, window, sinks)[0]
     return res
 
 
 def attn_prefill(q, k_cache, v_cache, block_tables, cu_q, ctx_lens, max_q_len, scale, window=0,
-                 sinks=None, out=None):
+                 sinks=None, out=None, kv_scale=(1.0, 1.0)):
     T, Hq, D = q.shape
     res = torch.zeros((T, Hq, D), dtype=q.dtype, device=q.device) if out is None else out
     B = ctx_lens.numel()
@@ -219,8 +229,8 @@ def attn_prefill(q, k_cache, v_cache, block_tables, cu_q, ctx_lens, max_q_len, s
             continue
         n = int(ctx_lens[b])
         prefix = n - (e - s)
-        k = _gather_kv(k_cache, block_tables[b], n)
-        v = _gather_kv(v_cache, block_tables[b], n)
+        k = _gather_kv(k_cache, block_tables[b], n, kv_scale[0])
+        v = _gather_kv(v_cache, block_tables[b], n, kv_scale[1])
         pos = prefix + torch.arange(e - s, device=q.device)
         res[s:e] = _attend(q[s:e], k, v, scale, pos, window, sinks)
     return res

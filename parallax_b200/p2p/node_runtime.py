@@ -210,6 +210,7 @@ class NodeRuntime:
         weights = loader.load_weights("cpu", None) if loader is not None else None
         self.peer = PeerExecutor(cfg, start_layer, end_layer, device=device, node_id=agent.node_id,
                                  page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
+                                 kv_cache_dtype=getattr(args, "kv_cache_dtype", None),
                                  max_batch_size=args.max_batch_size,
                                  max_num_tokens_per_batch=args.max_num_tokens_per_batch,
                                  micro_batch_ratio=args.micro_batch_ratio,

@@ -177,7 +177,8 @@ class DistEngine:
                  seed: int = 0, weights: Optional[dict] = None, fused: Optional[bool] = None,
                  max_in_flight: Optional[int] = None, weights_prefiltered: bool = False,
                  liveness_timeout_s: float = 10.0, step_timeout_s: float = 600.0, align_rows: int = 0,
-                 executor_thread: Optional[bool] = None, ep: int = 1, ep_local_init: Optional[bool] = None):
+                 executor_thread: Optional[bool] = None, ep: int = 1, ep_local_init: Optional[bool] = None,
+                 kv_cache_dtype: Optional[str] = None):
         assert dist.is_initialized(), "init the default process group first (nccl on GPUs, gloo on CPU)"
         self.cfg = cfg
         self.device = torch.device(device)
@@ -282,7 +283,8 @@ class DistEngine:
                                   tp_rank=topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm,
                                   num_linear_slots=max(max_batch_size * 2, 16) if cfg.has_linear_layers else 0,
                                   ep_rank=stage_ep[0], ep_size=stage_ep[1], ep_comm=stage_ep[2],
-                                  ep_local_init=bool(ep_local_init) and weights is None)
+                                  ep_local_init=bool(ep_local_init) and weights is None,
+                                  kv_cache_dtype=kv_cache_dtype)
         if cfg.has_linear_layers:
             enable_prefix_cache = False
         # every rank must agree on the number of KV blocks

@@ -22,7 +22,7 @@ logger = logging.getLogger(__name__)
 
 _ENGINE_KEYS = ("page_size", "kv_fraction", "max_batch_size", "max_num_tokens_per_batch", "micro_batch_ratio",
                 "chunked_prefill_size", "max_prefill_tokens_per_batch", "enable_prefix_cache", "max_total_length", "request_timeout_s", "num_blocks",
-                "seed", "fused", "executor_thread", "align_rows", "max_in_flight", "ep")
+                "seed", "fused", "executor_thread", "align_rows", "max_in_flight", "ep", "kv_cache_dtype")
 
 
 def free_port() -> int:
@@ -144,6 +144,7 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
     spec = dict(model_path=path, model_name=name.split("/")[-1], pp=args.pp_size, tp=tp_size, device_type=device_type,
                 dtype=args.dtype if args.dtype in ("bfloat16", "float16") else "bfloat16",
                 page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
+                kv_cache_dtype=getattr(args, "kv_cache_dtype", None),
                 max_batch_size=args.max_batch_size, max_num_tokens_per_batch=args.max_num_tokens_per_batch,
                 micro_batch_ratio=args.micro_batch_ratio, chunked_prefill_size=args.chunked_prefill_size,
                 max_prefill_tokens_per_batch=getattr(args, "max_prefill_tokens_per_batch", 0) or None,
