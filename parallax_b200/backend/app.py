@@ -29,14 +29,11 @@ from parallax_b200.backend.scheduler_manage import SchedulerManage
 from parallax_b200.backend.static_config import get_model_list, get_node_join_command, init_model_info_dict_cache
 from parallax_b200.frontend.openai_compat import openai_error_response, openai_models_payload
 
-_PAGE = """<!doctype html><meta charset="utf-8"><title>parallax cluster</title>
-<style>body{font-family:system-ui;margin:2rem}td,th{padding:.3rem .8rem;border-bottom:1px solid #ddd;text-align:left}</style>
-<h1>Cluster</h1><pre id="s"></pre><table><thead><tr><th>node</th><th>status</th><th>GPU</th><th>layers</th></tr></thead>
-<tbody id="n"></tbody></table><script>
-async function tick(){const d=(await (await fetch('/cluster/status_json')).json()).data;
-document.getElementById('s').textContent=`model: ${d.model_name}\\nstatus: ${d.status}\\ncapacity: ${d.max_running_request}\\njoin: ${(d.node_join_command||{}).command||'-'}`;
-document.getElementById('n').innerHTML=d.node_list.map(n=>`<tr><td>${n.node_id}</td><td>${n.status}</td><td>${n.gpu_num} x ${n.gpu_name}</td><td>[${n.start_layer}, ${n.end_layer})</td></tr>`).join('');}
-tick();setInterval(tick,2000);</script>"""
+def _ui_page(name: str) -> str:
+    from pathlib import Path
+
+    return (Path(__file__).resolve().parent.parent / "frontend" / "ui" / name).read_text()
+
 
 
 def create_app(scheduler_manage: SchedulerManage, request_handler: Optional[RequestHandler] = None) -> FastAPI:
@@ -50,10 +47,7 @@ def create_app(scheduler_manage: SchedulerManage, request_handler: Optional[Requ
 
     @app.get("/chat")
     async def chat_ui():
-        from pathlib import Path
-
-        page = Path(__file__).resolve().parent.parent / "frontend" / "ui" / "index.html"
-        return HTMLResponse(page.read_text())
+        return HTMLResponse(_ui_page("index.html"))
 
     @app.post("/weight/refit")
     async def weight_refit(req: HttpRequest):
@@ -154,7 +148,8 @@ def create_app(scheduler_manage: SchedulerManage, request_handler: Optional[Requ
 
     @app.get("/")
     async def index():
-        return HTMLResponse(_PAGE, headers={"Cache-Control": "no-store"})
+        # the cluster web app: set up -> join -> chat (one static file, hash routes)
+        return HTMLResponse(_ui_page("app.html"), headers={"Cache-Control": "no-store"})
 
     return app
 

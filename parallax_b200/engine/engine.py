@@ -534,7 +534,10 @@ class Engine:
             for s, k in zip(owners, st.slot_index):
                 del s.req.output_ids[k:]
             self._in_flight = None
-            raise ops.KernelError(f"device status after step {st.serial}: {_describe_status(code)}")
+            fb = st.fb
+            raise ops.KernelError(f"device status after step {st.serial}: {_describe_status(code)} "
+                                  f"[{fb.num_tokens} rows: {fb.num_prefill_tokens} prompt rows in "
+                                  f"{fb.num_prefill_seqs} slices, {fb.num_decode} decode rows, {fb.num_logits} logit rows]")
         t_synced = time.perf_counter()
         now = time.time()
         for i, s in enumerate(owners):

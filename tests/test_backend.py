@@ -102,3 +102,34 @@ def test_all_pipelines_busy_is_429(backend):
     r = c.post("/v1/chat/completions", json={"messages": []})
     assert r.status_code in (429, 503)
     assert r.json()["error"]["code"] in ("rate_limit_exceeded", "routing_not_ready")
+
+
+def test_web_app_pages_and_the_calls_they_make(backend):
+    """The cluster web app is one static file with three views; every endpoint it calls answers in the shape
+    the page reads (set up -> /model/list + /scheduler/init, join -> /node/join/command + /cluster/status,
+    chat -> /v1/models + /v1/chat/completions)."""
+    import json as _json
+    import re
+
+    c, sm, _ = backend
+    page = c.get("/").text
+    for view in ("#/setup", "#/join", "#/chat"):
+        assert view in page
+    called = set(re.findall(r"['\"`](/(?:model|scheduler|node|cluster|v1)/[a-z_/]+)['\"`]", page))
+    assert {"/model/list", "/scheduler/init", "/node/join/command", "/cluster/status", "/cluster/status_json",
+            "/v1/models", "/v1/chat/completions"} <= called
+    models = c.get("/model/list").json()["data"]
+    assert models and {"name", "vram_gb"} <= set(models[0])
+    # before set-up: no model, the page starts on the set-up view
+    d = c.get("/cluster/status_json").json()["data"]
+    assert d["model_name"] is None and d["node_list"] == []
+    assert c.post("/scheduler/init", json={"init_nodes_num": 2}).status_code == 400
+    sm.run("test/model", 2, True, model_info=MODEL)
+    cmd = c.get("/node/join/command").json()["data"]
+    assert "command" in cmd and "parallax" in cmd["command"]
+    c.post("/node/join", json=_node_msg("a", 3000))
+    d = c.get("/cluster/status_json").json()["data"]       # the stream sends this same object once a second
+    assert {"status", "model_name", "init_nodes_num", "node_list", "need_more_nodes", "max_running_request"} <= set(d)
+    assert d["init_nodes_num"] == 2 and [n["node_id"] for n in d["node_list"]] == ["a"]
+    assert {"node_id", "status", "gpu_num", "gpu_name", "gpu_memory", "start_layer", "end_layer"} <= set(d["node_list"][0])
+    assert "chat" in c.get("/chat").text

@@ -214,6 +214,6 @@ def test_engine_on_an_e4m3_cache_tracks_the_bf16_cache_engine_gpu(cu):
         compared += 1
         if not torch.equal(x.argmax(-1), y.argmax(-1)):
             break              # a near-tie went the other way: from here on the two engines see different tokens
-    assert compared >= 3       # the three prompt slices of the long prompt at least
+    assert compared >= 2       # at least the first two batches of finished prompts
     assert not quant.stages[0].model._native      # e4m3 pages run through the per-layer path with the fp8 kernels
     assert quant.cache.num_free_blocks() + quant.cache.prefix_cache.num_nodes == quant.cache.num_blocks
