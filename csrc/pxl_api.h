@@ -142,13 +142,15 @@ int pxl_attn_prefill_tc(const void* q, int64_t q_stride, const void* k_cache, co
 
 // ---- sampler.cu ----------------------------------------------------------------
 // Greedy arg-max over logits [B, V] (bf16 if logits_bf16 else fp32, row stride ld).
+// A row without a finite maximum (all NaN) yields token 0 and sets PXL_DEV_NONFINITE_LOGITS in *status
+// (status may be null).
 int pxl_argmax(const void* logits, int logits_bf16, int64_t ld, int B, int V, int* out_ids,
-               float* out_logprob, pxl_stream_t stream);
+               float* out_logprob, int* status, pxl_stream_t stream);
 // Temperature / top-k / top-p / min-p sampling, one uniform random number per row.
 // temperature <= 0 or top_k == 1 selects arg-max for that row.
 int pxl_sample(const void* logits, int logits_bf16, int64_t ld, int B, int V,
                const float* temperature, const int* top_k, const float* top_p, const float* min_p,
-               const float* uniform, int* out_ids, float* out_prob, pxl_stream_t stream);
+               const float* uniform, int* out_ids, float* out_prob, int* status, pxl_stream_t stream);
 
 // ---- moe.cu ------------------------------------------------------------------
 // Router: scores [T, E] fp32/bf16 logits -> top-k expert ids and weights.

@@ -81,12 +81,22 @@ __device__ float block_sumexp(const void* row, int V, float mx, float inv_t, flo
 
 template <bool BF16>
 __global__ void __launch_bounds__(1024)
-argmax_kernel(const void* logits, int64_t ld, int V, int* out_ids, float* out_logprob) {
+argmax_kernel(const void* logits, int64_t ld, int V, int* out_ids, float* out_logprob, int* status) {
   __shared__ MaxIdx sm[32];
   __shared__ float red[32];
   const char* base = static_cast<const char*>(logits);
   const void* row = base + static_cast<size_t>(blockIdx.x) * ld * (BF16 ? 2 : 4);
   const MaxIdx r = block_argmax<BF16>(row, V, sm);
+  if (r.i < 0 || r.i >= V) {
+    // no logit of the row compared greater than -inf: the row is all NaN (or -inf). Report it and
+    // hand out a valid id, so that nothing downstream indexes a table with the sentinel.
+    if (threadIdx.x == 0) {
+      if (status) atomicCAS(status, 0, PXL_DEV_NONFINITE_LOGITS);
+      out_ids[blockIdx.x] = 0;
+      if (out_logprob) out_logprob[blockIdx.x] = 0.f;
+    }
+    return;
+  }
   if (threadIdx.x == 0) out_ids[blockIdx.x] = r.i;
   if (out_logprob) {
     const float z = block_sumexp<BF16>(row, V, r.v, 1.f, red);
@@ -99,7 +109,7 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const void* logits, int64_t ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ min_p, const float* __restrict__ uniform, int* out_ids,
-              float* out_prob) {
+              float* out_prob, int* status) {
   __shared__ MaxIdx sm[32];
   __shared__ float red[32];
   __shared__ float scan[1024];
@@ -113,6 +123,14 @@ sample_kernel(const void* logits, int64_t ld, int V, const float* __restrict__ t
   const float mp = min_p ? min_p[b] : 0.f;
 
   const MaxIdx best = block_argmax<BF16>(row, V, sm);
+  if (best.i < 0 || best.i >= V) {  // all-NaN row: see argmax_kernel
+    if (threadIdx.x == 0) {
+      if (status) atomicCAS(status, 0, PXL_DEV_NONFINITE_LOGITS);
+      out_ids[b] = 0;
+      if (out_prob) out_prob[b] = 0.f;
+    }
+    return;
+  }
   if (temp <= 0.f || k == 1) {
     if (threadIdx.x == 0) out_ids[b] = best.i;
     if (out_prob) {
@@ -241,26 +259,26 @@ PXL_EXPORT int pxl_apply_penalties(void* logits, int logits_bf16, int64_t ld, in
 }
 
 PXL_EXPORT int pxl_argmax(const void* logits, int logits_bf16, int64_t ld, int B, int V,
-                          int* out_ids, float* out_logprob, pxl_stream_t stream) {
+                          int* out_ids, float* out_logprob, int* status, pxl_stream_t stream) {
   if (B <= 0) return PXL_OK;
   if (logits_bf16)
-    argmax_kernel<true><<<B, 1024, 0, stream>>>(logits, ld, V, out_ids, out_logprob);
+    argmax_kernel<true><<<B, 1024, 0, stream>>>(logits, ld, V, out_ids, out_logprob, status);
   else
-    argmax_kernel<false><<<B, 1024, 0, stream>>>(logits, ld, V, out_ids, out_logprob);
+    argmax_kernel<false><<<B, 1024, 0, stream>>>(logits, ld, V, out_ids, out_logprob, status);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
 }
 
 PXL_EXPORT int pxl_sample(const void* logits, int logits_bf16, int64_t ld, int B, int V,
                           const float* temperature, const int* top_k, const float* top_p,
                           const float* min_p, const float* uniform, int* out_ids, float* out_prob,
-                          pxl_stream_t stream) {
+                          int* status, pxl_stream_t stream) {
   if (B <= 0) return PXL_OK;
   if (!uniform) return PXL_ERR_INVALID_ARG;
   if (logits_bf16)
     sample_kernel<true><<<B, 1024, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p,
-                                                uniform, out_ids, out_prob);
+                                                uniform, out_ids, out_prob, status);
   else
     sample_kernel<false><<<B, 1024, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p,
-                                                 uniform, out_ids, out_prob);
+                                                 uniform, out_ids, out_prob, status);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
 }

@@ -28,6 +28,7 @@ _ERRORS = {
     108: "row id of a gather (token id / logit row) outside the table",
     109: "block-table entry read by decode attention outside the cache",
     110: "block-table entry read by prefill attention (or the cp.async decode path) outside the cache",
+    111: "a row of logits had no finite value (NaN activations): token 0 was returned for it",
 }
 
 EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_F32 = 0, 1, 2, 3
@@ -103,9 +104,9 @@ _SIGS = {
                              c_float, _P],
     "pxl_msa_select": [_P, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P],
     "pxl_rmsnorm_strided": [_P, c_int64, _P, _P, c_int64, c_int, c_int, c_float, c_float, _P],
-    "pxl_argmax": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P],
+    "pxl_argmax": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P],
     "pxl_apply_penalties": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
-    "pxl_sample": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P],
+    "pxl_sample": [_P, c_int, c_int64, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P],
 }
 
 

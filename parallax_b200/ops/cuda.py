@@ -491,7 +491,7 @@ def argmax(logits: torch.Tensor, want_logprob: bool = False):
     lp = torch.empty(B, dtype=torch.float32, device=logits.device) if want_logprob else None
     check(_lib.lib().pxl_argmax(logits.data_ptr(), int(logits.dtype == torch.bfloat16),
                                 logits.stride(0), B, V, ids.data_ptr(), _ptr(lp),
-                                _stream(logits.device)), "pxl_argmax")
+                                status_tensor(logits.device).data_ptr(), _stream(logits.device)), "pxl_argmax")
     _count()
     return (ids, lp) if want_logprob else ids
 
@@ -526,7 +526,8 @@ def sample(
         _lib.lib().pxl_sample(logits.data_ptr(), int(logits.dtype == torch.bfloat16),
                               logits.stride(0), B, V, temperature.data_ptr(), top_k.data_ptr(),
                               top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(),
-                              ids.data_ptr(), _ptr(pr), _stream(logits.device)),
+                              ids.data_ptr(), _ptr(pr), status_tensor(logits.device).data_ptr(),
+                              _stream(logits.device)),
         "pxl_sample",
     )
     _count()

@@ -421,3 +421,31 @@ def test_patch_ids(cu):
     cu.patch_ids(dst, di, src, si)
     assert dst[3] == 109 and dst[19] == 100 and dst[0] == 104 and int((dst == -1).sum()) == 17
     cu.check_status(dev)
+
+
+def test_sampler_reports_rows_without_a_finite_logit(cu):
+    """An all-NaN row (what diverged activations leave behind) must not come back as an index outside the
+    vocabulary: token 0 and a status code that fails the step."""
+    from parallax_b200.ops._lib import KernelError
+
+    dev = _dev()
+    V = 5000
+    logits = torch.randn(3, V, device=dev, dtype=torch.bfloat16)
+    logits[1] = float("nan")
+    ids = cu.argmax(logits)
+    torch.cuda.synchronize()
+    assert ids.tolist()[1] == 0 and 0 <= ids.tolist()[0] < V and ids.tolist()[0] == int(logits[0].float().argmax())
+    with pytest.raises(KernelError, match="finite"):
+        cu.check_status(dev)
+    cu.check_status(dev)        # the word was cleared
+    B = 3
+    t = torch.full((B,), 0.8, device=dev)
+    k = torch.full((B,), 40, dtype=torch.int32, device=dev)
+    p = torch.full((B,), 0.9, device=dev)
+    mp = torch.zeros(B, device=dev)
+    u = torch.rand(B, device=dev)
+    ids, pr = cu.sample(logits.float(), t, k, p, mp, u, want_prob=True)
+    torch.cuda.synchronize()
+    assert ids.tolist()[1] == 0 and all(0 <= i < V for i in ids.tolist())
+    with pytest.raises(KernelError, match="finite"):
+        cu.check_status(dev)
