@@ -32,6 +32,7 @@ enum PxlStatus : int {
   PXL_DEV_BAD_ROW_ID = 108,        // row id of a gather (token id, logit row) outside the table
   PXL_DEV_BAD_BLOCK_DECODE = 109,  // block-table entry read by decode attention outside the cache
   PXL_DEV_BAD_BLOCK_PREFILL = 110, // block-table entry read by prefill attention outside the cache
+  PXL_DEV_BAD_POSITION = 112,      // a token position outside the rotary table (row left unrotated)
   PXL_DEV_NONFINITE_LOGITS = 111,  // a row of logits had no finite maximum (all NaN): token 0 was returned
 };
 

@@ -184,7 +184,7 @@ qk_norm_rope_cache_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ q_nor
                           const int64_t* __restrict__ slot_mapping, void* __restrict__ k_cache,
                           void* __restrict__ v_cache, int T, int Hq, int Hkv, int rot_dim,
                           int page_size, int64_t num_slots, float eps, float w_offset,
-                          float k_inv_scale, float v_inv_scale, int* status) {
+                          float k_inv_scale, float v_inv_scale, int max_pos, int* status) {
   constexpr int EPL = D / 32;  // elements per lane
   __shared__ float sh[8][D];
   pdl_wait();
@@ -220,12 +220,15 @@ qk_norm_rope_cache_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ q_nor
             __float2bfloat16(v[j] * inv * (__bfloat162float(nw[lane * EPL + j]) + w_offset)));
       }
     }
-    if (rot_dim > 0) {
+    const int p = rot_dim > 0 ? positions[t] : 0;
+    const bool p_ok = p >= 0 && (max_pos <= 0 || p < max_pos);
+    if (rot_dim > 0 && !p_ok && status && lane == 0) atomicCAS(status, 0, PXL_DEV_BAD_POSITION);
+    if (rot_dim > 0 && p_ok) {   // a position outside the table is reported, its row is left unrotated
 #pragma unroll
       for (int j = 0; j < EPL; ++j) sh[warp][lane * EPL + j] = v[j];
       __syncwarp();
       const int half = rot_dim >> 1;
-      const float* cs = cos_sin + static_cast<size_t>(positions[t]) * rot_dim;
+      const float* cs = cos_sin + static_cast<size_t>(p) * rot_dim;
 #pragma unroll
       for (int j = 0; j < EPL; ++j) {
         const int e = lane * EPL + j;
@@ -419,7 +422,7 @@ int qk_norm_rope_cache_impl(void* qkv, const void* q_norm_w, const void* k_norm_
                             const int64_t* slot_mapping, void* k_cache, void* v_cache, int T, int Hq,
                             int Hkv, int D, int rot_dim, int page_size, int64_t num_slots, float eps,
                             float norm_w_offset, bool cache_fp8, float k_inv_scale,
-                            float v_inv_scale, int* status, pxl_stream_t stream) {
+                            float v_inv_scale, int max_pos, int* status, pxl_stream_t stream) {
   if (T <= 0) return PXL_OK;
   if (rot_dim > D || (rot_dim & 1)) return PXL_ERR_INVALID_ARG;
   const int64_t warps = static_cast<int64_t>(T) * (Hq + 2 * Hkv);
@@ -430,13 +433,13 @@ int qk_norm_rope_cache_impl(void* qkv, const void* q_norm_w, const void* k_norm_
         static_cast<bf16*>(qkv), static_cast<const bf16*>(q_norm_w),                          \
         static_cast<const bf16*>(k_norm_w), cos_sin, positions, slot_mapping, k_cache,        \
         v_cache, T, Hq, Hkv, rot_dim, page_size, num_slots, eps, norm_w_offset, k_inv_scale,  \
-        v_inv_scale, status);                                                                 \
+        v_inv_scale, max_pos, status);                                                        \
   else                                                                                        \
     pxl_host::launch(qk_norm_rope_cache_kernel<DD, false>, grid, 256, 0, stream,               \
         static_cast<bf16*>(qkv), static_cast<const bf16*>(q_norm_w),                          \
         static_cast<const bf16*>(k_norm_w), cos_sin, positions, slot_mapping, k_cache,        \
         v_cache, T, Hq, Hkv, rot_dim, page_size, num_slots, eps, norm_w_offset, 1.f, 1.f,     \
-        status)
+        max_pos, status)
   switch (D) {
     case 64: PXL_QKROPE(64); break;
     case 96: PXL_QKROPE(96); break;
@@ -454,10 +457,10 @@ PXL_EXPORT int pxl_qk_norm_rope_cache(void* qkv, const void* q_norm_w, const voi
                                       const int64_t* slot_mapping, void* k_cache, void* v_cache,
                                       int T, int Hq, int Hkv, int D, int rot_dim, int page_size,
                                       int64_t num_slots, float eps, float norm_w_offset,
-                                      int* status, pxl_stream_t stream) {
+                                      int max_pos, int* status, pxl_stream_t stream) {
   return qk_norm_rope_cache_impl(qkv, q_norm_w, k_norm_w, cos_sin, positions, slot_mapping, k_cache,
                                  v_cache, T, Hq, Hkv, D, rot_dim, page_size, num_slots, eps,
-                                 norm_w_offset, false, 1.f, 1.f, status, stream);
+                                 norm_w_offset, false, 1.f, 1.f, max_pos, status, stream);
 }
 
 // Same with e4m3 caches: K is stored as k / k_scale, V as v / v_scale (scales > 0).
@@ -466,12 +469,12 @@ PXL_EXPORT int pxl_qk_norm_rope_cache_fp8(void* qkv, const void* q_norm_w, const
                                           const int64_t* slot_mapping, void* k_cache, void* v_cache,
                                           int T, int Hq, int Hkv, int D, int rot_dim, int page_size,
                                           int64_t num_slots, float eps, float norm_w_offset,
-                                          float k_scale, float v_scale, int* status,
+                                          float k_scale, float v_scale, int max_pos, int* status,
                                           pxl_stream_t stream) {
   if (!(k_scale > 0.f) || !(v_scale > 0.f)) return PXL_ERR_INVALID_ARG;
   return qk_norm_rope_cache_impl(qkv, q_norm_w, k_norm_w, cos_sin, positions, slot_mapping, k_cache,
                                  v_cache, T, Hq, Hkv, D, rot_dim, page_size, num_slots, eps,
-                                 norm_w_offset, true, 1.f / k_scale, 1.f / v_scale, status, stream);
+                                 norm_w_offset, true, 1.f / k_scale, 1.f / v_scale, max_pos, status, stream);
 }
 
 // dst[dst_idx[i]] = src[src_idx[i]]: the decode rows of a step take their input ids from the token

@@ -61,12 +61,13 @@ int pxl_rmsnorm_strided(const void* x, int64_t ldx, const void* weight, void* ou
 // Per-head q/k RMSNorm (optional) + rotary embedding (neox pairing, first `rot_dim`
 // dims) on a packed qkv activation [T, (Hq + 2*Hkv) * D], writing q in place and
 // scattering k, v into the paged cache [blocks, Hkv, page, D] at slot_mapping[t]
-// (slot < 0: skip). cos_sin: fp32 [max_pos, rot_dim] = cos | sin halves.
+// (slot < 0: skip). cos_sin: fp32 [max_pos, rot_dim] = cos | sin halves. A position outside [0, max_pos)
+// sets PXL_DEV_BAD_POSITION and leaves its row unrotated (max_pos <= 0: not checked).
 int pxl_qk_norm_rope_cache(void* qkv, const void* q_norm_w, const void* k_norm_w,
                            const float* cos_sin, const int* positions, const int64_t* slot_mapping,
                            void* k_cache, void* v_cache, int T, int Hq, int Hkv, int D, int rot_dim,
                            int page_size, int64_t num_slots, float eps, float norm_w_offset,
-                           int* status, pxl_stream_t stream);
+                           int max_pos, int* status, pxl_stream_t stream);
 // Plain scatter of k, v [T, Hkv, D] (row strides in elements) into the paged cache.
 int pxl_reshape_and_cache(const void* k, const void* v, int64_t k_stride, int64_t v_stride,
                           const int64_t* slot_mapping, void* k_cache, void* v_cache, int T,
@@ -80,7 +81,7 @@ int pxl_qk_norm_rope_cache_fp8(void* qkv, const void* q_norm_w, const void* k_no
                                const int64_t* slot_mapping, void* k_cache, void* v_cache, int T,
                                int Hq, int Hkv, int D, int rot_dim, int page_size, int64_t num_slots,
                                float eps, float norm_w_offset, float k_scale, float v_scale,
-                               int* status, pxl_stream_t stream);
+                               int max_pos, int* status, pxl_stream_t stream);
 int pxl_reshape_and_cache_fp8(const void* k, const void* v, int64_t k_stride, int64_t v_stride,
                               const int64_t* slot_mapping, void* k_cache, void* v_cache, int T,
                               int Hkv, int Dk, int Dv, int page_size, int64_t num_slots,

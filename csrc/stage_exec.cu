@@ -35,7 +35,8 @@ struct PxlDenseLayer {
 struct PxlStageDesc {
   int H, Hq, Hkv, D, I, rot_dim, page, n_layers;
   int64_t num_blocks;
-  float eps, norm_offset, scale, pad_;
+  float eps, norm_offset, scale;
+  int max_pos;             // rows of cos_sin
   const float* cos_sin;
   const PxlDenseLayer* layers;  // host array of n_layers entries
 };
@@ -127,7 +128,7 @@ PXL_EXPORT int pxl_stage_forward_dense(const PxlStageDesc* st, const PxlStepDesc
                           stream));
     PXL_TRY(pxl_qk_norm_rope_cache(qkv, L.q_norm, L.k_norm, st->cos_sin, sp->positions, sp->slots, L.k_cache,
                                    L.v_cache, T, Hq, Hkv, D, st->rot_dim, st->page, num_slots, st->eps,
-                                   st->norm_offset, status, stream));
+                                   st->norm_offset, st->max_pos, status, stream));
     n += 3;
     if (sp->Tp > 0) {
       if (prefill_tc) {

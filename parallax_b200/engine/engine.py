@@ -198,7 +198,10 @@ class Engine:
         self.device = torch.device(device)
         self.page_size = page_size
         stage_layers = stage_layers or [(0, cfg.num_hidden_layers)]
-        max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
+        # the rotary table covers every position a request may reach, whatever length the checkpoint's
+        # config advertises (positions beyond that length are the caller's choice, as with the reference's
+        # on-the-fly rotary embedding); a table cut at the advertised length was read out of bounds
+        max_positions = max_total_length + 8
         self.stages: list[StageWorker] = []
         max_requests = max(max_batch_size * 2, 16)
         # hybrid models resume a shared prefix from a snapshot of the recurrent state taken at a block

@@ -22,7 +22,7 @@ class _Layer(Structure):
 class _StageDesc(Structure):
     _fields_ = [(n, c_int) for n in ("H", "Hq", "Hkv", "D", "I", "rot_dim", "page", "n_layers")] + \
                [("num_blocks", c_int64), ("eps", c_float), ("norm_offset", c_float), ("scale", c_float),
-                ("pad_", c_float), ("cos_sin", c_void_p), ("layers", POINTER(_Layer))]
+                ("max_pos", c_int), ("cos_sin", c_void_p), ("layers", POINTER(_Layer))]
 
 
 class _StepDesc(Structure):
@@ -56,7 +56,7 @@ class NativeDenseStage:
         d.H, d.Hq, d.Hkv, d.D = cfg.hidden_size, cfg.num_attention_heads, kc0.shape[1], cfg.head_dim
         d.I, d.rot_dim, d.page, d.n_layers = stage.layers[0].w_down.shape[1], cfg.rot_dim, kc0.shape[2], n
         d.num_blocks, d.eps, d.norm_offset, d.scale = kc0.shape[0], cfg.rms_norm_eps, stage.norm_offset, stage.scale
-        d.cos_sin = stage.cos_sin.data_ptr()
+        d.cos_sin, d.max_pos = stage.cos_sin.data_ptr(), int(stage.cos_sin.shape[0])
         d.layers = ctypes.cast(self._layers, POINTER(_Layer))
         self.desc = d
         self.qkv_n = (d.Hq + 2 * d.Hkv) * d.D

@@ -46,7 +46,10 @@ class PeerExecutor:
                  weights: Optional[dict] = None, shared_state=None, kv_cache_dtype: Optional[str] = None):
         self.cfg, self.node_id = cfg, node_id
         self.device = torch.device(device)
-        max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
+        # the rotary table covers every position a request may reach, whatever length the checkpoint's
+        # config advertises (positions beyond that length are the caller's choice, as with the reference's
+        # on-the-fly rotary embedding); a table cut at the advertised length was read out of bounds
+        max_positions = max_total_length + 8
         self.worker = StageWorker(cfg, start_layer, end_layer, self.device, dtype, page_size, num_blocks=num_blocks,
                                   kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
                                   kv_cache_dtype=kv_cache_dtype)

@@ -139,6 +139,8 @@ class BatchScheduler:
             rid = req.request_id
             if rid in self._running:
                 continue
+            # a request may not outgrow what the engine was sized for (block tables, rotary table)
+            req.max_total_length = min(req.max_total_length, self.max_total_length)
             if req.total_length > self.max_total_length:
                 req.update_status(RequestStatus.FINISHED_ABORT)
                 req.abort = True

@@ -28,6 +28,7 @@ _ERRORS = {
     108: "row id of a gather (token id / logit row) outside the table",
     109: "block-table entry read by decode attention outside the cache",
     110: "block-table entry read by prefill attention (or the cp.async decode path) outside the cache",
+    112: "a token position outside the rotary table (longer than the engine's max_total_length)",
     111: "a row of logits had no finite value (NaN activations): token 0 was returned for it",
 }
 
@@ -57,11 +58,11 @@ _SIGS = {
     "pxl_gemm_bf16_mid_m": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "pxl_rmsnorm": [_P, _P, _P, _P, c_int, c_int, c_float, c_float, _P],
     "pxl_qk_norm_rope_cache": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int64, c_float, c_float, _P, _P],
+                               c_int, c_int64, c_float, c_float, c_int, _P, _P],
     "pxl_reshape_and_cache": [_P, _P, c_int64, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int,
                               c_int, c_int64, _P, _P],
     "pxl_qk_norm_rope_cache_fp8": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                                   c_int, c_int64, c_float, c_float, c_float, c_float, _P, _P],
+                                   c_int, c_int64, c_float, c_float, c_float, c_float, c_int, _P, _P],
     "pxl_reshape_and_cache_fp8": [_P, _P, c_int64, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int,
                                   c_int, c_int64, c_float, c_float, _P, _P],
     "pxl_attn_decode_fp8": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -265,13 +265,14 @@ def qk_norm_rope_cache(
     slots = k_cache.shape[0] * page if k_cache is not None else 0
     if cos_sin is None:
         rot_dim = 0
+    max_pos = cos_sin.shape[0] if cos_sin is not None else 0
     if _is_fp8_cache(k_cache):
         check(
             _lib.lib().pxl_qk_norm_rope_cache_fp8(
                 qkv.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin), positions.data_ptr(),
                 _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), T, num_q_heads, num_kv_heads,
                 head_dim, rot_dim, page, slots, eps, norm_w_offset, float(kv_scale[0]), float(kv_scale[1]),
-                status_tensor(qkv.device).data_ptr(), _stream(qkv.device)),
+                max_pos, status_tensor(qkv.device).data_ptr(), _stream(qkv.device)),
             "pxl_qk_norm_rope_cache_fp8",
         )
         _count()
@@ -280,7 +281,7 @@ def qk_norm_rope_cache(
         _lib.lib().pxl_qk_norm_rope_cache(
             qkv.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin), positions.data_ptr(),
             _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), T, num_q_heads, num_kv_heads,
-            head_dim, rot_dim, page, slots, eps, norm_w_offset,
+            head_dim, rot_dim, page, slots, eps, norm_w_offset, max_pos,
             status_tensor(qkv.device).data_ptr(), _stream(qkv.device)),
         "pxl_qk_norm_rope_cache",
     )

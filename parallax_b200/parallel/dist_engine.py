@@ -277,7 +277,10 @@ class DistEngine:
             from parallax_b200.loader.filter import filter_weights_for_range
 
             weights = filter_weights_for_range(weights, start, end, cfg.num_hidden_layers, cfg.tie_word_embeddings)
-        max_positions = min(cfg.max_position_embeddings, max_total_length + 8)
+        # the rotary table covers every position a request may reach, whatever length the checkpoint's
+        # config advertises (positions beyond that length are the caller's choice, as with the reference's
+        # on-the-fly rotary embedding); a table cut at the advertised length was read out of bounds
+        max_positions = max_total_length + 8
         self.worker = StageWorker(cfg, start, end, self.device, dtype, page_size, num_blocks=num_blocks,
                                   kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
                                   tp_rank=topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm,

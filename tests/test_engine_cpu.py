@@ -320,3 +320,28 @@ def test_sampling_penalties_change_greedy_output_as_specified():
     want[0, 5] = 8.0 / 2 - (0.25 * 1 + 0.5)    # prompt + generated once
     want[0, 9] = -2.0 * 2 - (0.25 * 2 + 0.5)   # generated twice
     assert torch.allclose(got, want)
+
+
+def test_positions_beyond_the_advertised_context_length():
+    """A checkpoint whose config advertises a shorter context than the engine is asked to serve: the rotary table
+    follows the engine's ``max_total_length`` (not the advertised length), and a request cannot outgrow the engine's
+    own limit even if it asks for more."""
+    import copy
+
+    cfg = copy.copy(named_config("tiny"))
+    cfg.max_position_embeddings = 64
+    eng = Engine(cfg, device="cpu", num_blocks=64, page_size=16, max_batch_size=2, chunked_prefill_size=32,
+                 max_total_length=160, seed=0)
+    assert eng.stages[0].model.cos_sin.shape[0] >= 160
+    ref = Engine(named_config("tiny"), device="cpu", num_blocks=64, page_size=16, max_batch_size=2,
+                 chunked_prefill_size=32, max_total_length=160, seed=0)
+    prompt = [(7 * i + 1) % 1000 for i in range(100)]          # positions 0..120 cross the advertised 64
+    sp = SamplingParams(max_new_tokens=20, temperature=0.0, ignore_eos=True)
+    assert eng.generate([prompt], sp) == ref.generate([prompt], sp)
+    # asks for 10000 tokens in total: stops at the engine's 160
+    r = Request(input_ids=prompt, sampling_params=SamplingParams(max_new_tokens=500, temperature=0.0, ignore_eos=True),
+                max_total_length=10000)
+    eng.add_request(r)
+    while eng.has_work():
+        eng.step()
+    assert len(r.input_ids) + len(r.output_ids) <= 160 and len(r.output_ids) >= 50

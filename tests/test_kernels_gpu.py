@@ -449,3 +449,32 @@ def test_sampler_reports_rows_without_a_finite_logit(cu):
     assert ids.tolist()[1] == 0 and all(0 <= i < V for i in ids.tolist())
     with pytest.raises(KernelError, match="finite"):
         cu.check_status(dev)
+
+
+def test_rope_position_outside_the_table_is_reported_not_read(cu):
+    from parallax_b200.ops._lib import KernelError
+
+    dev = _dev()
+    torch.manual_seed(0)
+    T, Hq, Hkv, D, page, blocks = 6, 4, 2, 128, 16, 4
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev, dtype=torch.bfloat16)
+    cs = ref.build_cos_sin(32, D, 1e6, device=dev)                 # 32 positions only
+    pos = torch.tensor([0, 5, 31, 32, 7, 1000], device=dev, dtype=torch.int32)
+    slots = torch.arange(T, device=dev, dtype=torch.int64)
+    kc = torch.zeros(blocks, Hkv, page, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q1, q2 = qkv.clone(), qkv.clone()
+    cu.qk_norm_rope_cache(q1, None, None, cs, pos, slots, kc, vc, Hq, Hkv, D, D)
+    torch.cuda.synchronize()
+    with pytest.raises(KernelError, match="position"):
+        cu.check_status(dev)
+    good = torch.tensor([0, 1, 2, 4], device=dev)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(kc)
+    ref.qk_norm_rope_cache(q2[good], None, None, cs, pos[good], slots[good], kc2, vc2, Hq, Hkv, D, D)
+    assert torch.isfinite(q1.float()).all()
+    # rows inside the table are rotated as usual; the two rows outside it are left as they came
+    want = qkv.clone()
+    tmp = qkv[good].clone()
+    ref.qk_norm_rope_cache(tmp, None, None, cs, pos[good], slots[good], torch.zeros_like(kc), torch.zeros_like(kc), Hq, Hkv, D, D)
+    want[good] = tmp
+    assert _rel_err(q1[:, :Hq * D], want[:, :Hq * D]) < 1e-2
