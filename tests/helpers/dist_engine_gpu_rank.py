@@ -1,6 +1,7 @@
 """One rank of a multi-GPU DistEngine check (started with torchrun by tests/test_tp_gpu.py).
 
-The layout comes as a string: ``pp<P>``, ``tp<T>`` (fused tensor-parallel kernels), ``dpep<E>`` (expert
+The layout comes as a string: ``pp<P>``, ``tp<T>`` (fused tensor-parallel kernels for the GQA decoder; heads split over library collectives
+for ``@small-mla`` / ``@small-dsa`` / ``@small-hybrid`` / ``@small-msa``), ``dpep<E>`` (expert
 parallelism with data-parallel attention) and combinations such as ``pp2tp2`` or ``pp2dpep2``; ``ep2``
 is attention tensor-parallel with the experts sharded over the same two ranks. Rank 0 runs the same
 prompts through a single-GPU engine on its own GPU afterwards and compares:
@@ -44,6 +45,9 @@ def main() -> None:
 
     faulthandler.dump_traceback_later(150, exit=True)   # a stuck rank shows where and ends itself
     mode, out_path = sys.argv[1], sys.argv[2]
+    # "<layout>@<named config>" picks another model family, "<layout>#fp8kv" an e4m3 KV cache (on both engines)
+    mode, _, kv_flag = mode.partition("#")
+    mode, _, model = mode.partition("@")
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     launcher.init_process_group(rank, world, int(os.environ["MASTER_PORT"]), "cuda")
     dev = torch.device("cuda", rank)
@@ -53,8 +57,12 @@ def main() -> None:
     if moe:        # Qwen3-30B-A3B layer shapes (128 experts, top-8), a few layers
         cfg = named_config("qwen3-30b-a3b")
         cfg.num_hidden_layers = max(2, pp)
+    if model:
+        cfg = named_config(model)
     kw = dict(page_size=16, num_blocks=512, max_batch_size=8, max_num_tokens_per_batch=2048, chunked_prefill_size=512,
               max_total_length=2048, seed=0)
+    if kv_flag == "fp8kv":
+        kw["kv_cache_dtype"] = "fp8_e4m3"
     eng = DistEngine(cfg, pp, tp, dev, torch.bfloat16, ep=dpep, **kw)
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (37, 300, 5, 129, 64, 700)]

@@ -44,7 +44,11 @@ def _run_dist(mode, tmp_path, port, nproc=2):
 # layout, GPUs it needs. The 4- and 8-GPU rows run when the box has that many devices.
 LAYOUTS = [("tp2", 2), ("pp2", 2), ("ep2", 2), ("dpep2", 2),
            ("tp4", 4), ("pp4", 4), ("pp2tp2", 4), ("dpep4", 4), ("pp2dpep2", 4),
-           ("tp8", 8), ("pp8", 8), ("pp2tp4", 8), ("dpep8", 8), ("pp2dpep4", 8)]
+           ("tp8", 8), ("pp8", 8), ("pp2tp4", 8), ("dpep8", 8), ("pp2dpep4", 8),
+           # tensor-parallel stages of the other families (heads split, sequence-sharded residual stream)
+           ("tp2@small-mla", 2), ("tp2@small-dsa", 2), ("tp2@small-hybrid", 2), ("tp2@small-msa", 2),
+           # e4m3 KV pages under pipeline and tensor parallelism
+           ("pp2#fp8kv", 2), ("tp2#fp8kv", 2)]
 
 
 @pytest.mark.parametrize("mode,n", LAYOUTS)
@@ -59,7 +63,7 @@ def test_dist_engine_layout_matches_one_gpu(mode, n, tmp_path):
     assert r["equal"] == r["compared"], r
     if "logit_rel_err" in r:
         assert r["logit_rel_err"] < 3e-2, r
-    if mode.startswith("pp") and "tp" not in mode and "ep" not in mode:
+    if mode.startswith("pp") and "tp" not in mode and "ep" not in mode and "#" not in mode:
         # same kernels in the same order on every stage: only the hand-off differs
         assert r["token_agreement"] > 0.95, r
 
