@@ -216,9 +216,12 @@ class TPHybridStage(FamilyTPMixin, HybridStage):
         if lw.kind == LINEAR:
             Hk, Hv = self._heads_full
             qk, vv = Hk * self.Dk, Hv * self.Dv
-            if lw.w_in.shape[0] != 2 * qk + 2 * vv + 2 * Hv:
+            if lw.w_in.shape[0] != 2 * qk + 2 * vv + 2 * Hv or lw.w_out.shape[1] != vv:
                 return                              # already cut
-            lw.w_in = _segments(lw.w_in, [qk, qk, vv, vv, Hv, Hv], r, tp)
+            w_in = _segments(lw.w_in, [qk, qk, vv, vv, Hv, Hv], r, tp)
+            if w_in.shape[0] % 8:        # the GEMM wants a multiple of 8 output columns: zero rows at the end
+                w_in = torch.cat([w_in, w_in.new_zeros(8 - w_in.shape[0] % 8, w_in.shape[1])]).contiguous()
+            lw.w_in = w_in
             lw.conv_w = _segments(lw.conv_w, [qk, qk, vv], r, tp)
             lw.conv_b = _segments(lw.conv_b, [qk, qk, vv], r, tp)
             lw.A_log, lw.dt_bias = _part(lw.A_log, r, tp), _part(lw.dt_bias, r, tp)

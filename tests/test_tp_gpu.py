@@ -59,7 +59,7 @@ def test_dist_engine_layout_matches_one_gpu(mode, n, tmp_path):
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
     r = _run_dist(mode, tmp_path, 29600 + LAYOUTS.index((mode, n)) * 2, nproc=n)
-    assert r["compared"] >= 8, r
+    assert r["compared"] >= (4 if "#fp8kv" in mode else 8), r
     assert r["equal"] == r["compared"], r
     if "logit_rel_err" in r:
         assert r["logit_rel_err"] < 3e-2, r
