@@ -185,7 +185,78 @@ __global__ void store_rows_kernel(const bf16* __restrict__ src, int64_t ld, cons
     st_bf16x8(cache + slot * D + i * 8, ld_bf16x8(src + t * ld + i * 8));
 }
 
+// Indexer pre-processing of one step, one block (128 threads) per token:
+//   q_idx[t, h, :R]  <- interleaved RoPE at position(t), in place (every index head)
+//   cache[slot(t)]   <- RoPE(LayerNorm(kv[t, k_off : k_off + Di]) * w + b) on the first R dims
+//   w_out[t, h]      <- kv[t, w_off + h] * w_scale                              (fp32)
+// The model code did this with five framework calls per layer (layer norm, two rotations, two concatenations)
+// and a separate store; semantics follow the reference's indexer (deepseek_v32.py:84-238).
+__global__ void __launch_bounds__(128)
+dsa_index_prep_kernel(bf16* __restrict__ q_idx, int64_t ldq, const bf16* __restrict__ kv, int64_t ldkv, int k_off,
+                      int w_off, const bf16* __restrict__ ln_w, const bf16* __restrict__ ln_b, float ln_eps,
+                      const float* __restrict__ cos_sin, const int* __restrict__ positions, int max_pos,
+                      const int64_t* __restrict__ slots, bf16* __restrict__ cache, int64_t num_slots,
+                      float* __restrict__ w_out, float w_scale, int Hi, int R, int* status) {
+  __shared__ float red[32];
+  __shared__ float y_s[kDi];
+  const int t = blockIdx.x, d = threadIdx.x;
+  const int pos = positions[t];
+  const bool pos_ok = pos >= 0 && (max_pos <= 0 || pos < max_pos);
+  if (!pos_ok && d == 0 && status) atomicCAS(status, 0, PXL_DEV_BAD_POSITION);
+  const float* cs = cos_sin + static_cast<size_t>(pos_ok ? pos : 0) * R;
+  const int half = R >> 1;
+  // ---- head weights
+  if (d < Hi) w_out[static_cast<size_t>(t) * Hi + d] = __bfloat162float(kv[t * ldkv + w_off + d]) * w_scale;
+  // ---- queries: one thread per (head, pair)
+  if (pos_ok) {
+    for (int idx = d; idx < Hi * half; idx += blockDim.x) {
+      const int h = idx / half, i = idx % half;
+      bf16* p = q_idx + t * ldq + static_cast<int64_t>(h) * kDi + 2 * i;
+      const float x0 = __bfloat162float(p[0]), x1 = __bfloat162float(p[1]);
+      const float c = cs[i], sn = cs[half + i];
+      p[0] = __float2bfloat16(x0 * c - x1 * sn);
+      p[1] = __float2bfloat16(x0 * sn + x1 * c);
+    }
+  }
+  // ---- key: layer norm over the Di dims (two passes in fp32), rotation, store
+  const float x = __bfloat162float(kv[t * ldkv + k_off + d]);
+  const float mean = block_reduce_sum(x, red) * (1.f / kDi);
+  const float dx = x - mean;
+  const float var = block_reduce_sum(dx * dx, red) * (1.f / kDi);
+  const float y = dx * rsqrtf(var + ln_eps) * __bfloat162float(ln_w[d]) + (ln_b ? __bfloat162float(ln_b[d]) : 0.f);
+  y_s[d] = y;
+  __syncthreads();
+  float out = y;
+  if (pos_ok && d < R) {
+    const int i = d >> 1;
+    const float c = cs[i], sn = cs[half + i];
+    out = (d & 1) ? y_s[d - 1] * sn + y * c : y * c - y_s[d + 1] * sn;
+  }
+  const int64_t slot = slots[t];
+  if (slot < 0) return;
+  if (slot >= num_slots) {
+    if (d == 0 && status) atomicCAS(status, 0, PXL_DEV_BAD_INDEX);
+    return;
+  }
+  cache[slot * kDi + d] = __float2bfloat16(out);
+}
+
 }  // namespace
+
+PXL_EXPORT int pxl_dsa_index_prep(void* q_idx, int64_t ldq, const void* kv, int64_t ldkv, int k_off, int w_off,
+                                  const void* ln_w, const void* ln_b, float ln_eps, const float* cos_sin,
+                                  const int* positions, int max_pos, const int64_t* slots, void* cache,
+                                  int64_t num_slots, float* w_out, float w_scale, int T, int Hi, int Di, int R,
+                                  int* status, cudaStream_t stream) {
+  if (T <= 0) return PXL_OK;
+  if (Di != kDi || Hi <= 0 || Hi > 128 || R <= 0 || R > Di || (R & 1)) return PXL_ERR_INVALID_ARG;
+  dsa_index_prep_kernel<<<T, 128, 0, stream>>>(static_cast<pxl::bf16*>(q_idx), ldq, static_cast<const pxl::bf16*>(kv),
+                                               ldkv, k_off, w_off, static_cast<const pxl::bf16*>(ln_w),
+                                               static_cast<const pxl::bf16*>(ln_b), ln_eps, cos_sin, positions,
+                                               max_pos, slots, static_cast<pxl::bf16*>(cache), num_slots, w_out,
+                                               w_scale, Hi, R, status);
+  return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
+}
 
 PXL_EXPORT int pxl_dsa_index_scores(const void* q, const float* w, const void* index_cache,
                                     const int* block_tables, const int* cu_q, const int* positions,

@@ -215,6 +215,14 @@ int pxl_dsa_index_scores(const void* q, const float* w, const void* index_cache,
 // most k candidates are filled with -1 ("attend densely").
 int pxl_topk_select(const float* scores, int64_t ld, const int* positions, int T, int k, int* out,
                     int64_t ld_out, pxl_stream_t stream);
+// Indexer pre-processing of a step (Di == 128): q_idx [T, Hi*Di] gets the interleaved rotation on the first R
+// dims of every head in place; the index key kv[t, k_off : k_off+Di] is layer-normed (w, optional b), rotated
+// on its first R dims and stored at cache[slots[t]]; w_out[t, h] = kv[t, w_off+h] * w_scale (fp32).
+int pxl_dsa_index_prep(void* q_idx, int64_t ldq, const void* kv, int64_t ldkv, int k_off, int w_off,
+                       const void* ln_w, const void* ln_b, float ln_eps, const float* cos_sin,
+                       const int* positions, int max_pos, const int64_t* slots, void* cache, int64_t num_slots,
+                       float* w_out, float w_scale, int T, int Hi, int Di, int R, int* status,
+                       pxl_stream_t stream);
 // cache[slots[t], :] = src[t, :] (slot < 0: skip)
 int pxl_store_rows(const void* src, int64_t ld, const int64_t* slots, void* cache, int T, int D,
                    int64_t num_slots, int* status, pxl_stream_t stream);

@@ -17,13 +17,11 @@ import math
 from typing import Optional
 
 import torch
-import torch.nn.functional as F
 
 from parallax_b200 import ops
 from parallax_b200.engine.batch import ForwardBatch
 from parallax_b200.models.config import ModelConfig
 from parallax_b200.models.decoder import DecoderStage
-from parallax_b200.ops.reference import _rope_interleaved
 
 
 def derive_indexer_types(cfg: ModelConfig) -> list[str]:
@@ -253,14 +251,10 @@ class DeepseekStage(DecoderStage):
         k_top = cfg.index_topk
         cache = self.kv_caches[li].index_k
         iq = ops.linear(qr, lw.idx_wq_b).view(T, Hi, Di)
-        iq = torch.cat([_rope_interleaved(iq[..., :R], self.cos_sin, fb.positions).to(iq.dtype), iq[..., R:]], dim=-1)
         n0 = lw.n_kv_a
-        ik = F.layer_norm(kv[:, n0:n0 + Di].float(), (Di,), lw.idx_k_norm_w.float(), lw.idx_k_norm_b.float(),
-                          self.idx_eps)
-        ik = torch.cat([_rope_interleaved(ik[:, :R], self.cos_sin, fb.positions), ik[:, R:]], dim=-1).to(iq.dtype)
-        iw = (kv[:, n0 + Di:n0 + Di + Hi].float() * (Hi ** -0.5 * Di ** -0.5)).contiguous()
-        ops.store_rows(ik.contiguous(), fb.slot_mapping, cache)
-        iq = iq.contiguous()
+        # one launch: rotate the index queries, norm + rotate + store the index key, scale the head weights
+        iw = ops.dsa_index_prep(iq, kv, n0, n0 + Di, lw.idx_k_norm_w, lw.idx_k_norm_b, self.idx_eps, self.cos_sin,
+                                fb.positions, fb.slot_mapping, cache, Hi ** -0.5 * Di ** -0.5, R)
         Tp = fb.num_prefill_tokens
         need_p = Tp > 0 and fb.p_max_ctx > k_top
         need_d = fb.num_decode > 0 and fb.d_max_ctx > k_top

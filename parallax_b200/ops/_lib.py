@@ -69,6 +69,8 @@ _SIGS = {
                             c_int64, c_float, c_int, c_int, c_int, c_float, c_float, _P, _P],
     "pxl_attn_prefill_fp8": [_P, c_int64, _P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int64, c_float, c_int, c_float, c_float, _P, _P],
+    "pxl_dsa_index_prep": [_P, c_int64, _P, c_int64, c_int, c_int, _P, _P, c_float, _P, _P, c_int, _P, _P, c_int64, _P,
+                           c_float, c_int, c_int, c_int, c_int, _P, _P],
     "pxl_act_mul": [_P, _P, c_int, c_int, c_int, c_float, _P],
     "pxl_gather_rows": [_P, _P, _P, c_int, c_int, c_int64, c_int, _P, _P],
     "pxl_add_inplace": [_P, _P, c_int64, _P],

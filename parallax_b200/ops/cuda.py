@@ -741,6 +741,23 @@ def store_rows(src, slot_mapping, cache):
     _count()
 
 
+def dsa_index_prep(q_idx, kv, k_off: int, w_off: int, ln_w, ln_b, ln_eps: float, cos_sin, positions, slot_mapping,
+                   cache, w_scale: float, rope_dim: int):
+    """Indexer pre-processing in one launch (``csrc/dsa.cu``): rotates ``q_idx [T, Hi, Di]`` in place, stores the
+    normed + rotated index key of every token in ``cache`` and returns the scaled head weights ``[T, Hi]`` fp32."""
+    T, Hi, Di = q_idx.shape
+    assert q_idx.is_contiguous() and kv.stride(1) == 1 and kv.dtype == q_idx.dtype == torch.bfloat16
+    w_out = torch.empty((T, Hi), dtype=torch.float32, device=q_idx.device)
+    check(_lib.lib().pxl_dsa_index_prep(q_idx.data_ptr(), Hi * Di, kv.data_ptr(), kv.stride(0), k_off, w_off,
+                                        ln_w.data_ptr(), _ptr(ln_b), ln_eps, cos_sin.data_ptr(), positions.data_ptr(),
+                                        cos_sin.shape[0], slot_mapping.data_ptr(), cache.data_ptr(),
+                                        cache.numel() // Di, w_out.data_ptr(), w_scale, T, Hi, Di, rope_dim,
+                                        status_tensor(q_idx.device).data_ptr(), _stream(q_idx.device)),
+          "pxl_dsa_index_prep")
+    _count()
+    return w_out
+
+
 def dsa_index_scores(q_idx, w, index_cache, block_tables, cu_q, positions, max_ctx: int):
     T, Hi, Di = q_idx.shape
     ld = (max_ctx + 63) // 64 * 64

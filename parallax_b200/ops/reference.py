@@ -432,6 +432,22 @@ def store_rows(src, slot_mapping, cache):
     flat[slot_mapping[ok].long()] = src[ok].to(cache.dtype)
 
 
+def dsa_index_prep(q_idx, kv, k_off: int, w_off: int, ln_w, ln_b, ln_eps: float, cos_sin, positions, slot_mapping,
+                   cache, w_scale: float, rope_dim: int):
+    """Lightning-indexer pre-processing (``src/parallax/models/deepseek_v32.py:84-238``): interleaved rotation
+    of the first ``rope_dim`` dims of every index-query head (in place on ``q_idx [T, Hi, Di]``), layer norm +
+    rotation of the index key ``kv[:, k_off:k_off+Di]`` stored at ``cache[slot]``, head weights
+    ``kv[:, w_off:w_off+Hi] * w_scale`` returned as fp32."""
+    T, Hi, Di = q_idx.shape
+    R = rope_dim
+    q_idx[..., :R] = _rope_interleaved(q_idx[..., :R], cos_sin, positions).to(q_idx.dtype)
+    ik = torch.nn.functional.layer_norm(kv[:, k_off:k_off + Di].float(), (Di,), ln_w.float(),
+                                        None if ln_b is None else ln_b.float(), ln_eps)
+    ik = torch.cat([_rope_interleaved(ik[:, :R], cos_sin, positions), ik[:, R:]], dim=-1).to(q_idx.dtype)
+    store_rows(ik, slot_mapping, cache)
+    return (kv[:, w_off:w_off + Hi].float() * w_scale).contiguous()
+
+
 def dsa_index_scores(q_idx, w, index_cache, block_tables, cu_q, positions, max_ctx: int):
     """scores[t, j] = sum_h relu(q[t,h] . k_j) * w[t,h] for j <= positions[t], -inf beyond."""
     T = q_idx.shape[0]

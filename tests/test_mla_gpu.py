@@ -194,3 +194,35 @@ def test_deepseek_engine_gpu_matches_cpu(name):
     # which bf16 and fp32 may pick differently among near-ties of a random-weight model
     assert len(want) == len(got) and all(a.shape == b.shape for a, b in zip(got, want))
     assert _rel(got[0], want[0]) < 6e-2, _rel(got[0], want[0])
+
+
+def test_dsa_index_prep_kernel_matches_the_restatement():
+    """Rotation of the index queries, layer norm + rotation + store of the index key and the head weights, in one
+    launch, against the framework-op restatement (fp32 math, one rounding to bf16)."""
+    from parallax_b200.ops import cuda as cu
+    from parallax_b200.ops import reference as ref
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    T, Hi, Di, R, page, blocks = 77, 8, 128, 64, 16, 8
+    k_off, ld = 576, 576 + Di + Hi + 8
+    q = torch.randn(T, Hi, Di, device=dev, dtype=torch.bfloat16)
+    kv = torch.randn(T, ld, device=dev, dtype=torch.bfloat16) * 2
+    w = (1 + 0.2 * torch.randn(Di, device=dev)).to(torch.bfloat16)
+    b = (0.1 * torch.randn(Di, device=dev)).to(torch.bfloat16)
+    cs = ref.build_cos_sin(256, R, 1e4, device=dev)
+    pos = torch.randint(0, 256, (T,), device=dev, dtype=torch.int32)
+    slots = torch.randperm(blocks * page, device=dev)[:T].to(torch.int64)
+    slots[9] = -1
+    c1 = torch.zeros(blocks, 1, page, Di, device=dev, dtype=torch.bfloat16)
+    c2 = torch.zeros_like(c1)
+    q1, q2 = q.clone(), q.clone()
+    w1 = cu.dsa_index_prep(q1, kv, k_off, k_off + Di, w, b, 1e-5, cs, pos, slots, c1, 0.03, R)
+    w2 = ref.dsa_index_prep(q2, kv, k_off, k_off + Di, w, b, 1e-5, cs, pos, slots, c2, 0.03, R)
+    cu.check_status(dev)
+    assert torch.equal(q1[..., R:], q[..., R:])                       # dims past the rotary part are untouched
+    assert float((q1.float() - q2.float()).abs().max()) <= 2 ** -6 * float(q2.float().abs().max())
+    assert float((c1.float() - c2.float()).abs().max()) <= 2 ** -6 * float(c2.float().abs().max())
+    assert torch.allclose(w1, w2, rtol=1e-6, atol=1e-7)
+    assert float(c1.view(-1, Di)[torch.tensor([s for s in range(blocks * page) if s not in set(slots.tolist())],
+                                               device=dev)].abs().max()) == 0.0
