@@ -493,6 +493,20 @@ __global__ void patch_i32_kernel(int* __restrict__ dst, const int* __restrict__ 
   dst[d] = src[s];
 }
 
+// Self-test of the bounded peer wait: one thread waits for `flag` to reach `epoch` the way the fused
+// kernels wait for a peer. With a flag that nothing sets the wait runs out after its limit (about 1.5 s),
+// the kernel records PXL_DEV_TIMEOUT_PEER in *status and returns; *result is 1 if the flag arrived, 0 if
+// the wait gave up. The context stays usable either way.
+__global__ void bounded_wait_selftest_kernel(const uint32_t* flag, uint32_t epoch, int* result, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *result = flag_wait_bounded<false>(flag, epoch, nullptr, status) ? 1 : 0;
+}
+
+PXL_EXPORT int pxl_selftest_bounded_wait(const uint32_t* flag, uint32_t epoch, int* result, int* status,
+                                         pxl_stream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(flag, epoch, result, status);
+  return check_launch();
+}
+
 PXL_EXPORT int pxl_patch_i32(int* dst, const int* dst_idx, const int* src, const int* src_idx, int n, int dst_len,
                              int src_len, int* status, pxl_stream_t stream) {
   if (n <= 0) return PXL_OK;

@@ -103,6 +103,9 @@ int pxl_act_mul(const void* x, void* out, int T, int I, int mode, float limit, p
 // out[t, :] = table[ids[t], :]  (ids int32 or int64 per `ids_are_i64`)
 int pxl_gather_rows(const void* table, const void* ids, void* out, int T, int H, int64_t num_rows,
                     int ids_are_i64, int* status, pxl_stream_t stream);
+// Bounded-wait self-test (see elementwise.cu): waits for *flag >= epoch like a fused kernel waits for a peer;
+// *result = 1 when it arrived, 0 when the wait ran out (then *status = PXL_DEV_TIMEOUT_PEER).
+int pxl_selftest_bounded_wait(const uint32_t* flag, uint32_t epoch, int* result, int* status, pxl_stream_t stream);
 // dst[dst_idx[i]] = src[src_idx[i]] for i < n (int32 words; indices checked against dst_len / src_len)
 int pxl_patch_i32(int* dst, const int* dst_idx, const int* src, const int* src_idx, int n, int dst_len, int src_len,
                   int* status, pxl_stream_t stream);

@@ -7,7 +7,7 @@ error: the GPU path never falls back silently to PyTorch eager.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_int64, c_void_p
+from ctypes import c_uint32, c_float, c_int, c_int64, c_void_p
 from functools import lru_cache
 
 from parallax_b200 import _build
@@ -74,6 +74,7 @@ _SIGS = {
     "pxl_act_mul": [_P, _P, c_int, c_int, c_int, c_float, _P],
     "pxl_gather_rows": [_P, _P, _P, c_int, c_int, c_int64, c_int, _P, _P],
     "pxl_add_inplace": [_P, _P, c_int64, _P],
+    "pxl_selftest_bounded_wait": [_P, c_uint32, _P, _P, _P],
     "pxl_patch_i32": [_P, _P, _P, _P, c_int, c_int, c_int, _P, _P],
     "pxl_attn_decode": [_P, c_int64, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_int64, c_float, c_int, c_int, c_int, _P, _P],

@@ -478,3 +478,38 @@ def test_rope_position_outside_the_table_is_reported_not_read(cu):
     ref.qk_norm_rope_cache(tmp, None, None, cs, pos[good], slots[good], torch.zeros_like(kc), torch.zeros_like(kc), Hq, Hkv, D, D)
     want[good] = tmp
     assert _rel_err(q1[:, :Hq * D], want[:, :Hq * D]) < 1e-2
+
+
+def test_bounded_wait_runs_out_and_the_host_sees_it(cu):
+    """A wait on a flag that nothing sets gives up after its limit (about 1.5 s), records a status code that the
+    host reads, and leaves the context usable; a flag that is already there is seen at once."""
+    import time
+
+    from parallax_b200.ops import _lib
+    from parallax_b200.ops._lib import KernelError
+
+    dev = _dev()
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    result = torch.full((1,), -1, dtype=torch.int32, device=dev)
+    status = cu.status_tensor(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    flag.fill_(7)
+    assert _lib.lib().pxl_selftest_bounded_wait(flag.data_ptr(), 7, result.data_ptr(), status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(result) == 1
+    cu.check_status(dev)
+    flag.zero_()
+    t0 = time.time()
+    assert _lib.lib().pxl_selftest_bounded_wait(flag.data_ptr(), 1, result.data_ptr(), status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    dt = time.time() - t0
+    assert int(result) == 0 and 0.5 < dt < 10.0, dt
+    with pytest.raises(KernelError, match="timed out"):
+        cu.check_status(dev)
+    # the context is intact: an ordinary kernel runs and the status word is clean again
+    x = torch.randn(64, 1024, device=dev, dtype=torch.bfloat16)
+    w = torch.ones(1024, device=dev, dtype=torch.bfloat16)
+    y = cu.rmsnorm(x, w, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y.float()).all()
+    cu.check_status(dev)
