@@ -107,18 +107,27 @@ def main() -> None:
                 for rq, gap in zip(produced, (top2[:, 0] - top2[:, 1]).tolist()):
                     gaps[rq.request_id].append(gap)
         routs = [r.output_ids for r in rreqs]
+        res = {"mode": mode}
+        if first_logits is not None and ref_logits is not None and first_logits.shape == ref_logits.shape and dpep == 1:
+            res["logit_rel_err"] = float((first_logits - ref_logits).norm() / ref_logits.norm())
+            res["logit_abs_err"] = float((first_logits - ref_logits).abs().max())
+            res["logit_shape"] = list(ref_logits.shape)
+            # the two engines run different tile shapes (other row counts per step): a margin counts as clear
+            # when it is several times the logit difference that this alone produced in the first step
+            noise = max(noise, 4.0 * res["logit_abs_err"])
         compared = equal = 0
-        for r, x, y in zip(rreqs, outs, routs):
+        mismatches = []
+        for ri, (r, x, y) in enumerate(zip(rreqs, outs, routs)):
             for i, (a, b) in enumerate(zip(x, y)):
                 gp = gaps[r.request_id]
                 if i >= len(gp) or gp[i] < noise:
                     break
                 compared += 1
                 equal += int(a == b)
-        res = {"mode": mode, "outs": outs, "ref_outs": routs, "compared": compared, "equal": equal, "noise": noise}
-        if first_logits is not None and ref_logits is not None and first_logits.shape == ref_logits.shape and dpep == 1:
-            res["logit_rel_err"] = float((first_logits - ref_logits).norm() / ref_logits.norm())
-            res["logit_shape"] = list(ref_logits.shape)
+                if a != b:
+                    mismatches.append([ri, i, round(gp[i], 4), a, b])
+        res.update({"compared": compared, "equal": equal, "noise": round(noise, 4), "mismatches": mismatches,
+                    "outs": outs, "ref_outs": routs})
         agree = sum(int(a == b) for x, y in zip(outs, routs) for a, b in zip(x, y))
         res["token_agreement"] = agree / sum(len(x) for x in routs)
         with open(out_path, "w") as f:
