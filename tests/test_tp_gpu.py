@@ -59,8 +59,10 @@ def test_dist_engine_layout_matches_one_gpu(mode, n, tmp_path):
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
     r = _run_dist(mode, tmp_path, 29600 + LAYOUTS.index((mode, n)) * 2, nproc=n)
-    brief = {k: r.get(k) for k in ("mode", "compared", "equal", "noise", "logit_rel_err", "logit_abs_err", "mismatches",
-                                   "token_agreement")}
+    import json
+
+    brief = json.dumps({k: r.get(k) for k in ("mode", "compared", "equal", "noise", "logit_rel_err", "logit_abs_err",
+                                              "mismatches", "token_agreement")})
     assert r["compared"] >= (4 if "#fp8kv" in mode else 8), brief
     assert r["equal"] == r["compared"], brief
     if "logit_rel_err" in r:
