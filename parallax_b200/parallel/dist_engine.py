@@ -376,6 +376,14 @@ class DistEngine:
         if slot.buf is None or slot.buf.shape[0] < rows:
             slot.buf = torch.empty((max(rows, 256), H), dtype=self.worker.dtype, device=self.device)
             slot.free = None
+            if self.device.type == "cuda" and self.topo.tp == 1:
+                # The memory comes from the compute stream's pool: it may be a block that a tensor of an
+                # earlier micro-batch gave back while kernels that use it are still queued there. Stream
+                # order protects such reuse on the compute stream only, and the first writer of this buffer
+                # is the receive on the side stream - so that receive waits for everything queued so far.
+                slot.free = torch.cuda.Event()
+                slot.free.record(torch.cuda.current_stream(self.device))
+                slot.buf.record_stream(self._recv_stream)
         hidden = slot.buf[:rows]
         if self.device.type != "cuda" or self.topo.tp > 1:
             # tensor-parallel stages keep the receive in stream order: their fused GEMM + collective kernels
