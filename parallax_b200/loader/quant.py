@@ -112,3 +112,74 @@ def quantize_mxfp4(w: torch.Tensor):
     blocks = (idx[..., 0::2] | (idx[..., 1::2] << 4)).reshape(*prefix, K // 32, 16)
     scales = (exp + 127).to(torch.uint8).reshape(*prefix, K // 32)
     return blocks.contiguous(), scales.contiguous()
+
+
+# ------------------------------------------------------------------------- affine group quantisation
+# Checkpoints converted for MLX store a quantised linear layer as three tensors: ``<name>.weight`` (uint32,
+# ``32 / bits`` values per word, the first value in the lowest bits), ``<name>.scales`` and ``<name>.biases``
+# (one pair per group of ``group_size`` inputs): ``w = q * scale + bias``. ``config.json`` carries
+# ``"quantization": {"group_size": g, "bits": b, "<module path>": {"group_size": ..., "bits": ...} | false}``
+# with per-module overrides. The reference rebuilds quantised MLX modules from these
+# (``src/parallax/server/shard_loader.py:495-537,610-643``); this engine serves bf16 / fp8 on B200, so the
+# layers are expanded to floating point when the shard is loaded.
+def quantize_affine(w: torch.Tensor, bits: int = 4, group_size: int = 64):
+    """``w [out, in]`` -> ``(packed uint32 as int32 [out, in * bits / 32], scales, biases [out, in / group])``."""
+    if 32 % bits:
+        raise ValueError("bits must divide 32 (2, 4 or 8)")
+    out_f, in_f = w.shape
+    g = w.float().view(out_f, in_f // group_size, group_size)
+    lo, hi = g.amin(-1, keepdim=True), g.amax(-1, keepdim=True)
+    levels = (1 << bits) - 1
+    scale = ((hi - lo) / levels).clamp_min(1e-8)
+    q = ((g - lo) / scale).round().clamp_(0, levels).to(torch.int64).view(out_f, in_f)
+    per = 32 // bits
+    shifts = (torch.arange(per, dtype=torch.int64) * bits)
+    words = (q.view(out_f, in_f // per, per) << shifts).sum(-1)
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)     # torch has no uint32 math
+    return words, scale.squeeze(-1).to(torch.float16), lo.squeeze(-1).to(torch.float16)
+
+
+def dequant_affine(words: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, bits: int, group_size: int,
+                   dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Expand an affine group-quantised weight (see above) to ``[out, in]`` in ``dtype``."""
+    if 32 % bits:
+        raise ValueError(f"{bits}-bit affine quantisation is packed across word boundaries; supported: 2, 4, 8")
+    per = 32 // bits
+    w64 = words.to(torch.int64) & 0xFFFFFFFF
+    shifts = (torch.arange(per, dtype=torch.int64, device=words.device) * bits)
+    q = ((w64.unsqueeze(-1) >> shifts) & ((1 << bits) - 1)).reshape(words.shape[0], -1).float()
+    out_f, in_f = q.shape
+    if scales.shape != (out_f, in_f // group_size):
+        raise ValueError(f"scales {tuple(scales.shape)} do not fit a [{out_f}, {in_f}] weight in groups of {group_size}")
+    g = q.view(out_f, in_f // group_size, group_size)
+    return (g * scales.float().unsqueeze(-1) + biases.float().unsqueeze(-1)).view(out_f, in_f).to(dtype)
+
+
+def expand_affine_quantized(tensors: dict, quantization: Optional[dict], dtype: torch.dtype = torch.bfloat16) -> int:
+    """In place: every ``<module>.weight`` that comes with ``.scales`` / ``.biases`` is replaced by its floating
+    expansion and the two side tensors are dropped. Per-module entries of ``quantization`` override the global
+    ``bits`` / ``group_size`` (a module path may be given with or without the ``model.`` / ``language_model.``
+    prefixes a converter added); ``false`` marks a module that was left unquantised. Returns the number of
+    layers expanded."""
+    if not quantization or "bits" not in quantization:
+        return 0
+    n = 0
+    for key in [k for k in tensors if k.endswith(".scales")]:
+        mod = key[: -len(".scales")]
+        wkey, bkey = mod + ".weight", mod + ".biases"
+        if wkey not in tensors or bkey not in tensors:
+            continue
+        spec = None
+        for cand in (mod, "model." + mod, "language_model." + mod, mod.removeprefix("model."),
+                     mod.removeprefix("language_model.")):
+            if cand in quantization:
+                spec = quantization[cand]
+                break
+        if spec is False:
+            continue
+        spec = spec if isinstance(spec, dict) else {}
+        bits = int(spec.get("bits", quantization["bits"]))
+        group = int(spec.get("group_size", quantization["group_size"]))
+        tensors[wkey] = dequant_affine(tensors[wkey], tensors.pop(key), tensors.pop(bkey), bits, group, dtype)
+        n += 1
+    return n

@@ -79,6 +79,12 @@ class ShardLoader:
                             and not key.endswith("_scale_inv"):
                         t = t.to(dtype)
                     out[normalize_weight_key(key)] = t
+        q = (self.hf_config or {}).get("quantization")
+        if isinstance(q, dict) and "bits" in q:
+            from parallax_b200.loader.quant import expand_affine_quantized
+
+            n = expand_affine_quantized(out, q, dtype or torch.bfloat16)
+            logger.info("expanded %d affine group-quantised layers (per-module overrides honoured)", n)
         logger.info("stage [%d, %d): loaded %d tensors from %s", self.start_layer, self.end_layer,
                     len(out), self.model_path)
         return out
