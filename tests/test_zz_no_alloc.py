@@ -80,6 +80,30 @@ def test_static_scratch_matches_regular_entry_point_twice():
         assert torch.allclose(got.float(), want.float(), atol=1e-2, rtol=1e-2)
 
 
+def test_static_scratch_head_dim_64_takes_the_cp_async_kernel():
+    """Head dim 64 (and page size 8) is outside the TMA-fed kernel: the same entry point then runs the
+    cp.async kernel over the same built-in scratch, against the fp32 restatement."""
+    from parallax_b200.ops import cuda as cu
+    from parallax_b200.ops import reference as ref
+
+    fn = _bind()
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    status = cu.status_tensor(dev)
+    q, kc, vc, bt, cl = _case(21, 7, 500, Hq=16, Hkv=4, D=64, page=8)
+    scale = 1.0 / math.sqrt(64)
+    want = ref.attn_decode(q, kc, vc, bt, cl, scale)
+    for splits in (1, 3):
+        got = torch.full_like(q, float("nan"))
+        rc = fn(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), cl.data_ptr(),
+                got.data_ptr(), None, q.shape[0], 16, 4, 64, 8, bt.shape[1], kc.shape[0], scale, 0, splits,
+                status.data_ptr(), stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        cu.check_status(dev)
+        assert _rel_err(got, want) < 2e-2, splits
+
+
 def test_static_scratch_rejects_oversize_and_bad_splits():
     fn = _bind()
     q, kc, vc, bt, cl = _case(13, 4, 64)
