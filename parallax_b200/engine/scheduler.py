@@ -205,8 +205,14 @@ class BatchScheduler:
         prefill_cap = self.max_prefill_tokens_per_batch
         cm = self.cache_manager
         starting: set = set()      # first blocks that prompts of this batch are about to compute
+        # Decode rows ride along first: prompt slices are cut to fill whatever room is left, so a backlog of
+        # prompt tokens (long prompts, many arrivals) would otherwise take the whole budget step after step
+        # and no running request would get its next token until the backlog is gone. (The reference fills
+        # prefills first as well, src/parallax/server/scheduler.py:357-379, but never cuts a slice to fit.)
+        n_dec_cap = min(len(decodes), max(self.micro_batch_size - (1 if prefills else 0), 0), budget)
+        budget_p = budget - n_dec_cap
         for req in prefills:
-            if len(batch) >= self.micro_batch_size:
+            if len(batch) >= self.micro_batch_size - n_dec_cap:
                 break
             if prefill_cap is not None and used >= prefill_cap:
                 break
@@ -230,7 +236,7 @@ class BatchScheduler:
                 req.num_computed_tokens = req.prompt_len - 1
                 remaining = 1
             cost = remaining if not chunk else min(remaining, chunk)
-            room = budget - used
+            room = budget_p - used
             if prefill_cap is not None:
                 room = min(room, prefill_cap - used)
             if room <= 0:

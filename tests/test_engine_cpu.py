@@ -345,3 +345,31 @@ def test_positions_beyond_the_advertised_context_length():
     while eng.has_work():
         eng.step()
     assert len(r.input_ids) + len(r.output_ids) <= 160 and len(r.output_ids) >= 50
+
+
+def test_a_backlog_of_prompt_tokens_does_not_starve_decoding_requests():
+    """Token budget = one prompt slice + one row per request. While a long prompt is being prefilled slice by
+    slice, a request that is already decoding gets a token in every step (its row is reserved before prompt
+    slices are cut to fill the budget)."""
+    cfg = named_config("tiny")
+    eng = Engine(cfg, device="cpu", num_blocks=128, page_size=16, max_batch_size=4, chunked_prefill_size=32,
+                 max_num_tokens_per_batch=32 + 4, enable_prefix_cache=False, max_total_length=512, seed=0,
+                 async_scheduling=False)
+    short = Request(input_ids=[3, 4, 5, 6, 7], sampling_params=SamplingParams(max_new_tokens=30, temperature=0.0,
+                                                                               ignore_eos=True))
+    eng.add_request(short)
+    eng.step()
+    assert len(short.output_ids) == 1
+    longs = [Request(input_ids=[(11 * i + j) % 1000 for i in range(200)],
+                     sampling_params=SamplingParams(max_new_tokens=2, temperature=0.0, ignore_eos=True)) for j in range(2)]
+    for r in longs:
+        eng.add_request(r)
+    produced = []
+    for _ in range(10):                       # 400 prompt tokens at <= 35 per step: the backlog outlasts these steps
+        before = len(short.output_ids)
+        eng.step()
+        st = eng.last_step_stats
+        assert st["tokens"] <= 36
+        produced.append(len(short.output_ids) - before)
+        assert st["prefill_tokens"] >= 30      # the prompt slices still take (almost) the whole budget
+    assert produced == [1] * 10, produced
