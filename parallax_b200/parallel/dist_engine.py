@@ -178,7 +178,7 @@ class DistEngine:
                  max_in_flight: Optional[int] = None, weights_prefiltered: bool = False,
                  liveness_timeout_s: float = 10.0, step_timeout_s: float = 600.0, align_rows: int = 0,
                  executor_thread: Optional[bool] = None, ep: int = 1, ep_local_init: Optional[bool] = None,
-                 kv_cache_dtype: Optional[str] = None):
+                 kv_cache_dtype: Optional[str] = None, linear_prefix_slots: Optional[int] = None):
         assert dist.is_initialized(), "init the default process group first (nccl on GPUs, gloo on CPU)"
         self.cfg = cfg
         self.device = torch.device(device)
@@ -281,15 +281,21 @@ class DistEngine:
         # config advertises (positions beyond that length are the caller's choice, as with the reference's
         # on-the-fly rotary embedding); a table cut at the advertised length was read out of bounds
         max_positions = max_total_length + 8
+        # hybrid models: the prefix cache keeps snapshots of the recurrent state at block boundaries in extra
+        # state slots behind the requests' own (the same layout on every rank; rank 0 decides the copies and
+        # every rank carries them out in plan order, see `slot_pre` / `slot_post` in the step plan)
+        hybrid_prefix = 0
+        if cfg.has_linear_layers and enable_prefix_cache and ep == 1:
+            hybrid_prefix = 32 if linear_prefix_slots is None else max(int(linear_prefix_slots), 0)
+        if cfg.has_linear_layers and not hybrid_prefix:
+            enable_prefix_cache = False
         self.worker = StageWorker(cfg, start, end, self.device, dtype, page_size, num_blocks=num_blocks,
                                   kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
                                   tp_rank=topo.tp_rank, tp_size=tp, tp_group=self.tp_group, comm=comm,
-                                  num_linear_slots=max(max_batch_size * 2, 16) if cfg.has_linear_layers else 0,
+                                  num_linear_slots=(max(max_batch_size * 2, 16) + hybrid_prefix) if cfg.has_linear_layers else 0,
                                   ep_rank=stage_ep[0], ep_size=stage_ep[1], ep_comm=stage_ep[2],
                                   ep_local_init=bool(ep_local_init) and weights is None,
                                   kv_cache_dtype=kv_cache_dtype)
-        if cfg.has_linear_layers:
-            enable_prefix_cache = False
         # every rank must agree on the number of KV blocks
         nb = torch.tensor([self.worker.num_blocks], dtype=torch.int64)
         dist.all_reduce(nb, op=dist.ReduceOp.MIN, group=self.ctrl)
@@ -306,7 +312,10 @@ class DistEngine:
             for _ in range(self.n_plans):
                 pl = Planner(cfg, self.num_blocks, page_size, lane_batch if ep > 1 else max_batch_size, lane_tokens,
                              ratio, chunked_prefill_size, enable_prefix_cache, max_total_length, request_timeout_s,
-                             eos_token_id)
+                             eos_token_id, linear_prefix_slots=hybrid_prefix)
+                if pl.cache.needs_slots:
+                    # a request that matched a snapshot starts from a copy of it: queued for the next plan
+                    pl.cache.on_copy_slot = lambda dst, src: self._slot_pre.append((int(dst), int(src)))
                 pl.scheduler.max_prefill_tokens_per_batch = max_prefill_tokens_per_batch
                 pl.scheduler.align_rows = align_rows
                 self.planners.append(pl)
@@ -314,6 +323,7 @@ class DistEngine:
         self.builders = [BatchBuilder(self.device, lane_tokens + max_batch_size, max_batch_size,
                                       max_blocks) for _ in range(self.max_in_flight + 1)]
         self._bi = 0
+        self._slot_pre: list = []        # rank 0: state-slot copies (dst, src) that the next plan carries
         self.in_flight: deque = deque()
         self._pending_sends: deque = deque()
         self._side_events: list = []
@@ -487,8 +497,12 @@ class DistEngine:
             if on_gpu and self.marks and len(self._busy_events) < 100000:
                 ev0 = torch.cuda.Event(enable_timing=True)      # only between benchmark marks
                 ev0.record()
+            for dst, src in lp.get("slot_pre") or ():
+                w.pool.copy_slot(dst, src)                 # resume from a snapshot of the recurrent state
             with torch.inference_mode():
                 out = w.run(fb, hidden)
+            for dst, src in lp.get("slot_post") or ():
+                w.pool.copy_slot(dst, src)                 # snapshot at the block boundary this step reached
             if slot_free is not None:
                 slot_free.record()
             if ev0 is not None:
@@ -767,6 +781,25 @@ class DistEngine:
         if all(x is None for x in planned):
             return False
         lane_plans = [None if x is None else x[1] for x in planned]
+        # prefill bookkeeping that does not depend on the sampled token: the next chunk of a long
+        # prompt may enter the pipeline right behind this one. The chunk's full blocks are published now:
+        # whoever matches them is planned later and every rank runs the plans in order. For hybrid models
+        # this also decides the state snapshots of the step (taken on every rank right after its forward).
+        for pl, x in zip(self.planners, planned):
+            if x is None:
+                continue
+            post: list = []
+            snap = (lambda src, dst: post.append((int(dst), int(src)))) if pl.cache.needs_slots else None
+            for s in x[0]["ordered"]:
+                if s.is_prefill:
+                    s.req.num_computed_tokens = s.start + s.num_tokens
+                    pl.cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens,
+                                                         snapshot_linear=snap)
+                    if not s.produces_token:
+                        pl.scheduler.enque_request(s.req)
+            if pl.cache.needs_slots:
+                x[1]["slot_pre"], self._slot_pre = self._slot_pre, []
+                x[1]["slot_post"] = post
         plan = {"cmd": "step", "lanes": lane_plans,
                 "max_rows": max(int(lp["pos"].shape[0]) for lp in lane_plans if lp is not None)}
         t1 = time.perf_counter()
@@ -778,17 +811,6 @@ class DistEngine:
         hs["plan"] += t1 - t0
         hs["publish"] += t2 - t1
         hs["launch"] += t3 - t2
-        # prefill bookkeeping that does not depend on the sampled token: the next chunk of a long
-        # prompt may enter the pipeline right behind this one
-        for pl, x in zip(self.planners, planned):
-            if x is None:
-                continue
-            for s in x[0]["ordered"]:
-                if s.is_prefill:
-                    s.req.num_computed_tokens = s.start + s.num_tokens
-                    pl.cache.insert_full_blocks_to_cache(s.req.request_id, s.req.num_computed_tokens)
-                    if not s.produces_token:
-                        pl.scheduler.enque_request(s.req)
         self.in_flight.append(([None if x is None else x[0] for x in planned], res))
         return True
 

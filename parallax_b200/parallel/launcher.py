@@ -22,7 +22,7 @@ logger = logging.getLogger(__name__)
 
 _ENGINE_KEYS = ("page_size", "kv_fraction", "max_batch_size", "max_num_tokens_per_batch", "micro_batch_ratio",
                 "chunked_prefill_size", "max_prefill_tokens_per_batch", "enable_prefix_cache", "max_total_length", "request_timeout_s", "num_blocks",
-                "seed", "fused", "executor_thread", "align_rows", "max_in_flight", "ep", "kv_cache_dtype")
+                "seed", "fused", "executor_thread", "align_rows", "max_in_flight", "ep", "kv_cache_dtype", "linear_prefix_slots")
 
 
 def free_port() -> int:

@@ -10,6 +10,14 @@ from parallax_b200.engine.request import SamplingParams
 from parallax_b200.parallel import launcher
 
 
+def _nodes(root):
+    stack = list(root.children.values())
+    while stack:
+        n = stack.pop()
+        stack.extend(n.children.values())
+        yield n
+
+
 def main() -> None:
     spec = json.loads(sys.argv[1])
     out_path = sys.argv[2]
@@ -24,9 +32,13 @@ def main() -> None:
         outs = eng.generate(prompts, SamplingParams(max_new_tokens=spec["max_new"], temperature=0.0, ignore_eos=True))
         eng.mark()
         probe = eng.elapsed()
+        pc = eng.cache.prefix_cache if eng.n_plans == 1 else None
+        hits = None if pc is None else pc.hits
+        snapshots = None if pc is None else sum(1 for n in _nodes(pc.root) if n.linear_slot is not None)
         eng.shutdown()
         with open(out_path, "w") as f:
-            json.dump({"outputs": outs, "steps": eng.steps, "probe": probe}, f)
+            json.dump({"outputs": outs, "steps": eng.steps, "probe": probe, "prefix_hits": hits,
+                       "state_snapshots": snapshots}, f)
     else:
         eng.serve_forever()
     import torch.distributed as dist

@@ -116,6 +116,20 @@ def test_tensor_parallel_stages_of_the_other_families(model, pp, tmp_path):
     assert got["outputs"] == want
 
 
+@pytest.mark.parametrize("pp,tp", [(2, 1), (1, 2)])
+def test_hybrid_prefix_cache_across_ranks(pp, tp, tmp_path):
+    """Gated delta-net layers under pipeline / tensor parallelism with the prefix cache on: rank 0 decides
+    which recurrent-state snapshots are taken and restored, every rank carries the copies out around its
+    forward in plan order. Six prompts share a 64-token prefix, four run at a time: the later ones resume
+    from the snapshots the earlier ones left. Same tokens as the single-process engine."""
+    base = [(13 * i + 5) % 1000 for i in range(64)]
+    prompts = [base + [100 + j, 200 + j, 300 + j][: 1 + j % 3] for j in range(6)]
+    want = _single(model="tiny-hybrid", max_new=5, prompts=prompts)
+    got = _run_group(pp, tp, tmp_path, model="tiny-hybrid", max_new=5, prompts=prompts)
+    assert got["outputs"] == want
+    assert got["prefix_hits"] >= 2 and got["state_snapshots"] >= 1, got
+
+
 def test_rank_loss_is_detected_on_the_host(tmp_path):
     """Failure detection without touching a device: the second pipeline rank exits between steps;
     the scheduling rank sees its heartbeat stop and raises within seconds."""
