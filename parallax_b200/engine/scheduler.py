@@ -209,10 +209,11 @@ class BatchScheduler:
         # prompt tokens (long prompts, many arrivals) would otherwise take the whole budget step after step
         # and no running request would get its next token until the backlog is gone. (The reference fills
         # prefills first as well, src/parallax/server/scheduler.py:357-379, but never cuts a slice to fit.)
-        n_dec_cap = min(len(decodes), max(self.micro_batch_size - (1 if prefills else 0), 0), budget)
-        budget_p = budget - n_dec_cap
+        # Only tokens are reserved: sequence slots go to prompts first, as before (a step takes few prompts
+        # and the running set never exceeds the slots of an unsplit batch).
+        budget_p = budget - min(len(decodes), self.micro_batch_size, budget)
         for req in prefills:
-            if len(batch) >= self.micro_batch_size - n_dec_cap:
+            if len(batch) >= self.micro_batch_size:
                 break
             if prefill_cap is not None and used >= prefill_cap:
                 break
