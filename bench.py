@@ -325,8 +325,14 @@ def run_group(args, wl, cfg, par, world, rank, local_rank, device, invalid) -> N
                     admit(out_len)
         return toks
 
+    # The staggered start above is the steady state only if every initial request waits for the last prompt
+    # before it decodes on: prompts first while the loop is being built, the serving policy afterwards.
+    for pl in eng.planners:
+        pl.scheduler.decode_first = False
     while any(r.is_prefill for r in initial):
         rotation()
+    for pl in eng.planners:
+        pl.scheduler.decode_first = True
     for _ in range(max(args.warmup, 0)):
         rotation()
     torch.cuda.synchronize()
@@ -553,10 +559,14 @@ def main() -> None:
 
     # ---- untimed: bring the closed loop to its steady state
     initial = [admit(out_len - (i * out_len) // conc, in_len + (i * out_len) // conc) for i in range(conc)]
+    # (prompts first while the loop is being built: the staggered start is the steady state only if every
+    # initial request waits for the last prompt before it decodes on; the serving policy afterwards)
+    eng.scheduler.decode_first = False
     while any(r.is_prefill for r in initial):
         for req, _tok in eng.step():
             if req.is_finished:
                 admit(out_len)
+    eng.scheduler.decode_first = True
     torch.cuda.synchronize()
     cu.check_status(device)
 

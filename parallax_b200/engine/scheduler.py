@@ -78,6 +78,9 @@ class BatchScheduler:
         self.request_timeout_s = request_timeout_s
         self.eos_token_ids = _normalize_token_ids(eos_token_id)
         self.max_total_length = max_total_length
+        # ready decode rows keep their place in a step when prompt tokens would fill the budget (see form_batch);
+        # False restores prompts-first, which benchmarks use while they build a closed loop's steady state
+        self.decode_first = True
         self.is_first_peer = is_first_peer
         self.prefill_priority = prefill_priority
         self.shared_state = shared_state
@@ -211,7 +214,7 @@ class BatchScheduler:
         # prefills first as well, src/parallax/server/scheduler.py:357-379, but never cuts a slice to fit.)
         # Only tokens are reserved: sequence slots go to prompts first, as before (a step takes few prompts
         # and the running set never exceeds the slots of an unsplit batch).
-        budget_p = budget - min(len(decodes), self.micro_batch_size, budget)
+        budget_p = budget - (min(len(decodes), self.micro_batch_size, budget) if self.decode_first else 0)
         for req in prefills:
             if len(batch) >= self.micro_batch_size:
                 break
