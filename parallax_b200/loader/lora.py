@@ -153,8 +153,11 @@ class LoRAManager:
     """Adapters by name: which are resident in which slot, least recently used ones make room. A slot that a
     running request uses is pinned."""
 
-    def __init__(self, stacks: list[LoRAStack], max_loaded: int, paths: Optional[dict] = None):
+    def __init__(self, stacks: list[LoRAStack], max_loaded: int, paths: Optional[dict] = None, on_load=None):
+        """``on_load(slot, name, path)``: called instead of loading into ``stacks`` - the multi-GPU engine
+        sends the load to every rank with its next step plan."""
         self.stacks = stacks
+        self.on_load = on_load
         self.max_loaded = max_loaded
         self.paths: dict[str, str] = dict(paths or {})
         self.slot_of: "OrderedDict[str, int]" = OrderedDict()       # resident adapters, least recently used first
@@ -178,9 +181,12 @@ class LoRAManager:
                     raise RuntimeError("every LoRA slot is in use by a running request")
                 self.free.append(self.slot_of.pop(victim))
             slot = self.free.pop()
-            adapter = LoRAAdapter.load(self.paths[name], name)
-            for st in self.stacks:
-                st.load(slot, adapter)
+            if self.on_load is not None:
+                self.on_load(slot, name, self.paths[name])
+            else:
+                adapter = LoRAAdapter.load(self.paths[name], name)
+                for st in self.stacks:
+                    st.load(slot, adapter)
             self.slot_of[name] = slot
         self.pins[name] = self.pins.get(name, 0) + 1
         return self.slot_of[name]

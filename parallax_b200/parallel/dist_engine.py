@@ -178,7 +178,8 @@ class DistEngine:
                  max_in_flight: Optional[int] = None, weights_prefiltered: bool = False,
                  liveness_timeout_s: float = 10.0, step_timeout_s: float = 600.0, align_rows: int = 0,
                  executor_thread: Optional[bool] = None, ep: int = 1, ep_local_init: Optional[bool] = None,
-                 kv_cache_dtype: Optional[str] = None, linear_prefix_slots: Optional[int] = None):
+                 kv_cache_dtype: Optional[str] = None, linear_prefix_slots: Optional[int] = None,
+                 lora: Optional[dict] = None):
         assert dist.is_initialized(), "init the default process group first (nccl on GPUs, gloo on CPU)"
         self.cfg = cfg
         self.device = torch.device(device)
@@ -323,6 +324,21 @@ class DistEngine:
         self.builders = [BatchBuilder(self.device, lane_tokens + max_batch_size, max_batch_size,
                                       max_blocks) for _ in range(self.max_in_flight + 1)]
         self._bi = 0
+        # per-request LoRA adapters: every rank keeps the adapter slots of its own layers; rank 0 decides which
+        # adapter lives in which slot and sends the loads (slot, name, path) with the next step plan
+        self.lora = None
+        self._lora_loads: list = []
+        if lora:
+            from parallax_b200.loader.lora import LoRAManager, LoRAStack
+
+            if tp > 1 or ep > 1 or not hasattr(self.worker.model, "lora") or family != "decoder":
+                raise ValueError("per-request LoRA in the multi-GPU engine is available for pipeline stages of the "
+                                 "GQA decoder families (tp = ep = 1)")
+            n_slots, max_rank = int(lora.get("max_loaded") or 4), int(lora.get("max_rank") or 64)
+            self.worker.model.lora = LoRAStack(self.worker.model, n_slots, max_rank)
+            if rank == 0:
+                self.lora = LoRAManager([], n_slots, lora.get("paths"),
+                                        on_load=lambda slot, name, path: self._lora_loads.append((int(slot), name, path)))
         self._slot_pre: list = []        # rank 0: state-slot copies (dst, src) that the next plan carries
         self.in_flight: deque = deque()
         self._pending_sends: deque = deque()
@@ -425,6 +441,11 @@ class DistEngine:
     def add_request(self, req: Request) -> None:
         req.sampling_params.verify()
         req.max_total_length = min(req.max_total_length, self.planner.max_total_length)
+        req.lora_slot = -1
+        if getattr(req, "lora_path", None):
+            if self.lora is None:
+                raise ValueError("this engine was started without LoRA support (--enable-lora)")
+            req.lora_slot = self.lora.acquire(req.lora_path)       # the load travels with the next plan
         # expert-parallel lanes: the request stays with the least loaded lane for its whole life
         pl = min(self.planners, key=lambda p: p.scheduler.num_queued_requests + p.scheduler.num_running_requests)
         pl.scheduler.enque_request(req)
@@ -470,6 +491,10 @@ class DistEngine:
         topo, w = self.topo, self.worker
         on_gpu = self.device.type == "cuda"
         lane_plans = plan["lanes"]
+        for slot, name, path in plan.get("lora_load") or ():
+            from parallax_b200.loader.lora import LoRAAdapter
+
+            w.model.lora.load(slot, LoRAAdapter.load(path, name))     # this rank's layers of the adapter
         lp = lane_plans[topo.lane if self.n_plans > 1 else 0]
         if self.ep_comm is not None:
             self.ep_comm.step_max_rows = plan.get("max_rows")
@@ -484,7 +509,8 @@ class DistEngine:
             self._bi = (self._bi + 1) % len(self.builders)
             fb = b.build(lp["ids"] if topo.is_first_stage else None, lp["pos"], lp["slots"], lp["p_q"],
                          lp["p_ctx"], lp["p_tables"], lp["d_ctx"], lp["d_tables"], lp["logit_rows"],
-                         lp.get("seq_rows"))
+                         lp.get("seq_rows"),
+                         extra={"lora_ids": lp["lora_ids"]} if lp.get("lora_ids") is not None else None)
             self.h2d_bytes += fb.h2d_bytes
             T = fb.num_tokens
             hidden = None
@@ -732,9 +758,15 @@ class DistEngine:
                     f"rank {i}: {_lib.describe(c)}" for i, c in enumerate(codes) if c))
 
     # ------------------------------------------------------------------ rank-0 step
+    def _release_lora(self, req: Request) -> None:
+        if self.lora is not None and getattr(req, "lora_slot", -1) >= 0:
+            self.lora.release(req.lora_path)
+            req.lora_slot = -1
+
     def _drop(self, pl, req: Request) -> None:
         pl.scheduler.evict_request(req.request_id)
         pl.cache.free_request(req.request_id)
+        self._release_lora(req)
         self._side_events.append((req, None))
 
     def _plan_one(self, pl):
@@ -764,6 +796,13 @@ class DistEngine:
         lp = {k: arrays[k] for k in ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables",
                                      "logit_rows", "seq_rows")}
         lp.update(n_logits=len(owners), greedy=greedy)
+        if self.lora is not None and any(getattr(s.req, "lora_slot", -1) >= 0 for s in arrays["ordered"]):
+            rows = np.full(arrays["pos"].shape[0], -1, dtype=np.int32)      # adapter slot of every token row
+            o = 0
+            for s in arrays["ordered"]:
+                rows[o:o + s.num_tokens] = getattr(s.req, "lora_slot", -1)
+                o += s.num_tokens
+            lp["lora_ids"] = rows
         from parallax_b200.engine.sampling import build_penalties
 
         pen = build_penalties([s.req for s in owners])
@@ -802,6 +841,8 @@ class DistEngine:
                 x[1]["slot_post"] = post
         plan = {"cmd": "step", "lanes": lane_plans,
                 "max_rows": max(int(lp["pos"].shape[0]) for lp in lane_plans if lp is not None)}
+        if self._lora_loads:
+            plan["lora_load"], self._lora_loads = self._lora_loads, []
         t1 = time.perf_counter()
         self.chan.publish(plan)
         t2 = time.perf_counter()
@@ -918,6 +959,7 @@ class DistEngine:
                 cache.append_request_token(req.request_id, tok)
                 if sched.check_and_update_request_status(req):
                     cache.free_request(req.request_id)
+                    self._release_lora(req)
                 else:
                     sched.enque_request(req, now=now)
                 out.append((req, tok))

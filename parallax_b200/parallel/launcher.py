@@ -22,7 +22,7 @@ logger = logging.getLogger(__name__)
 
 _ENGINE_KEYS = ("page_size", "kv_fraction", "max_batch_size", "max_num_tokens_per_batch", "micro_batch_ratio",
                 "chunked_prefill_size", "max_prefill_tokens_per_batch", "enable_prefix_cache", "max_total_length", "request_timeout_s", "num_blocks",
-                "seed", "fused", "executor_thread", "align_rows", "max_in_flight", "ep", "kv_cache_dtype", "linear_prefix_slots")
+                "seed", "fused", "executor_thread", "align_rows", "max_in_flight", "ep", "kv_cache_dtype", "linear_prefix_slots", "lora")
 
 
 def free_port() -> int:
@@ -151,6 +151,12 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
                 enable_prefix_cache=args.enable_prefix_cache, max_total_length=args.max_sequence_length,
                 request_timeout_s=args.request_timeout_s, num_blocks=None if device_type == "cuda" else 1024,
                 lora_paths=(args.lora_paths or []) if args.enable_lora else [], log_level=args.log_level)
+    from parallax_b200.launch import _lora_spec
+
+    per_request = _lora_spec(args)
+    if per_request is not None:
+        # named adapters are served per request (pipeline stages only); a single unnamed one is merged at load
+        spec["lora"], spec["lora_paths"] = per_request, []
     engine, procs = launch_dist_engine(spec)
     state = SharedState.create(in_process=True)
     state.set_layer_allocation(name, 0, cfg.num_hidden_layers, tp_size, changed=False)

@@ -29,7 +29,19 @@ def main() -> None:
     if rank == 0:
         prompts = spec["prompts"]
         eng.mark()
-        outs = eng.generate(prompts, SamplingParams(max_new_tokens=spec["max_new"], temperature=0.0, ignore_eos=True))
+        sp = SamplingParams(max_new_tokens=spec["max_new"], temperature=0.0, ignore_eos=True)
+        if spec.get("lora_of"):
+            from parallax_b200.engine.request import Request
+
+            reqs = [Request(input_ids=list(p), sampling_params=SamplingParams.from_dict(sp.to_dict()), lora_path=a)
+                    for p, a in zip(prompts, spec["lora_of"])]
+            for r in reqs:
+                eng.add_request(r)
+            while eng.has_work():
+                eng.step()
+            outs = [r.output_ids for r in reqs]
+        else:
+            outs = eng.generate(prompts, sp)
         eng.mark()
         probe = eng.elapsed()
         pc = eng.cache.prefix_cache if eng.n_plans == 1 else None
