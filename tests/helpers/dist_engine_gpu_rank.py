@@ -113,8 +113,8 @@ def main() -> None:
             res["logit_abs_err"] = float((first_logits - ref_logits).abs().max())
             res["logit_shape"] = list(ref_logits.shape)
             # the two engines run different tile shapes (other row counts per step): a margin counts as clear
-            # when it is several times the logit difference that this alone produced in the first step
-            noise = max(noise, 4.0 * res["logit_abs_err"])
+            # when it is twice the largest difference that this alone produced on any logit of the first step
+            noise = max(noise, 2.0 * res["logit_abs_err"])
         compared = equal = 0
         mismatches = []
         for ri, (r, x, y) in enumerate(zip(rreqs, outs, routs)):
