@@ -193,7 +193,11 @@ class Engine:
         linear_prefix_slots: Optional[int] = None,
         lora: Optional[dict] = None,
         kv_cache_dtype: Optional[str] = None,
+        tokenizer=None,
     ):
+        """``tokenizer`` (anything with ``token_text(id)`` and ``eos_token_ids``) is only needed for requests
+        with a ``json_schema``: constrained decoding checks candidate tokens by their text."""
+        self.tokenizer = tokenizer
         self.cfg = cfg
         self.device = torch.device(device)
         self.page_size = page_size
@@ -264,6 +268,9 @@ class Engine:
         self.wire_hook = wire_hook  # optional transform applied to hidden states between stages
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(seed + 12345)
+        import random as _random
+
+        self._py_rng = _random.Random(seed + 777)          # draws among valid candidates of constrained requests
         self.last_step_stats: dict = {}
         self.total_steps = 0
         self.keep_logits = False
@@ -281,6 +288,13 @@ class Engine:
             if self.lora is None:
                 raise ValueError("this engine was started without LoRA support (--enable-lora)")
             req.lora_slot = self.lora.acquire(req.lora_path)     # loads the adapter if it is not resident
+        req.grammar = None
+        if req.sampling_params.json_schema:
+            if self.tokenizer is None:
+                raise ValueError("json_schema needs an engine that knows its tokenizer (Engine(tokenizer=...))")
+            from parallax_b200.engine.structured import JsonSchemaMatcher
+
+            req.grammar = JsonSchemaMatcher(req.sampling_params.json_schema)
         self.scheduler.enque_request(req)
 
     def abort_request(self, rid: str) -> None:
@@ -300,6 +314,38 @@ class Engine:
         sps = [s.req.sampling_params for s in owners]
         want_prob = any(s.req.return_probs for s in owners)
         logits = apply_penalties(logits, build_penalties([s.req for s in owners]))
+        if any(getattr(s.req, "grammar", None) is not None for s in owners):
+            ids, probs = self._sample_rows(logits, owners, sps, want_prob)
+            return self._constrain(logits, owners, ids), probs
+        return self._sample_rows(logits, owners, sps, want_prob)
+
+    def _constrain(self, logits: torch.Tensor, owners: list[ScheduledSeq], ids: torch.Tensor) -> torch.Tensor:
+        """Rows of requests with a JSON schema: the best candidate token (or a draw among the valid ones)
+        whose text keeps the request's document valid replaces what the sampler picked. Such steps are
+        committed before the next one is planned, so the matcher is always up to date here."""
+        from parallax_b200.engine.structured import TokenChooser
+
+        tok = self.tokenizer
+        chooser = TokenChooser(tok.token_text, sorted(getattr(tok, "eos_token_ids", ()) or ()))
+        picks = []
+        for row, s in enumerate(owners):
+            g = getattr(s.req, "grammar", None)
+            if g is None:
+                continue
+            sp = s.req.sampling_params
+            choice = chooser.choose(g, logits[row], 0.0 if sp.is_greedy else sp.temperature, self._py_rng)
+            if choice is None:
+                s.req.grammar_stuck = True          # nothing valid: the request ends with what it has
+                choice = 0
+            picks.append((row, int(choice)))
+        if picks:
+            rows = torch.tensor([r for r, _t in picks], dtype=torch.long, device=ids.device)
+            vals = torch.tensor([t for _r, t in picks], dtype=ids.dtype, device=ids.device)
+            ids = ids.clone()
+            ids[rows] = vals
+        return ids
+
+    def _sample_rows(self, logits: torch.Tensor, owners: list[ScheduledSeq], sps, want_prob: bool):
         if all(sp.is_greedy for sp in sps):
             if want_prob:
                 ids, lp = ops.argmax(logits, want_logprob=True)
@@ -392,7 +438,8 @@ class Engine:
         prev = self._in_flight
         # penalties count the tokens a request has produced: their rows need the previous step's values on
         # the host, so such a step is not launched ahead of them
-        needs_values = any(s.req.sampling_params.has_penalties for s in live)
+        needs_values = any(s.req.sampling_params.has_penalties or getattr(s.req, "grammar", None) is not None
+                           for s in live)
         if needs_values and prev is not None:
             self._in_flight = None
             out += self._commit(prev)
@@ -552,6 +599,15 @@ class Engine:
             req.fill_token(k, tok, prob_list[i] if prob_list else None, now=now)
             cache.append_request_token(req.request_id, tok)
             why = sched.finish_reason(req, k + 1, tok)
+            g = getattr(req, "grammar", None)
+            if g is not None and why is None:
+                # the document grows by the token's text; it ends the request once it is complete
+                text = self.tokenizer.token_text(tok)
+                stuck = getattr(req, "grammar_stuck", False) or not text or not g.advance(text)
+                if stuck or g.done:
+                    why = RequestStatus.FINISHED_EOS
+                if stuck:
+                    del req.output_ids[k:]      # no candidate fitted: the stand-in token is not part of the reply
             if why is not None:
                 del req.output_ids[k + 1:]      # a placeholder of the step that is already running
                 req.update_status(why)

@@ -24,7 +24,8 @@ from typing import Optional
 _WS = " \n\t\r"
 _DIGITS = "0123456789"
 _HEX = "0123456789abcdefABCDEF"
-_MAX_WS_RUN = 8          # a model that only emits whitespace must run out of allowed continuations
+_MAX_WS_RUN = 2          # a model that only emits whitespace must run out of allowed continuations
+_MAX_NUM_CHARS = 24      # likewise for digits
 
 
 class SchemaError(ValueError):
@@ -46,7 +47,7 @@ class JsonSchemaMatcher:
                 for name, sub in (schema.get(key) or {}).items():
                     self._defs[f"#/{key}/{name}"] = sub
         # a state is a frozenset of stacks; a stack is a tuple of frames, the innermost frame last
-        self._states = frozenset([(("val", self._id(schema)),)])
+        self._states = frozenset([(("val", self._id(schema), False),)])       # no whitespace before the document
         self.text = ""
 
     # ------------------------------------------------------------------ schema table
@@ -126,6 +127,8 @@ class JsonSchemaMatcher:
                 return
             self._step(rest, ch, out)
         elif kind == "val":
+            if ch in _WS and len(frame) > 2 and not frame[2]:
+                return
             self._value(rest, frame[1], ch, out)
         elif kind == "lit":
             if ch == frame[1][0]:
@@ -144,7 +147,7 @@ class JsonSchemaMatcher:
     # ---- a value of schema `sid` starts at `ch`
     def _value(self, rest: tuple, sid: int, ch: str, out: set) -> None:
         if ch in _WS:
-            out.add(rest + (("ws", 1), ("val", sid)))
+            out.add(rest + (("val", sid), ("ws", 1)))
             return
         s = self._resolve(sid)
         if s is True or s == {} or s is None:
@@ -190,11 +193,11 @@ class JsonSchemaMatcher:
             elif t in ("number", "integer"):
                 io = t == "integer"
                 if ch == "-":
-                    out.add(rest + (("num", 0, io),))
+                    out.add(rest + (("num", 0, io, 1),))
                 elif ch == "0":
-                    out.add(rest + (("num", 1, io),))
+                    out.add(rest + (("num", 1, io, 1),))
                 elif ch in "123456789":
-                    out.add(rest + (("num", 2, io),))
+                    out.add(rest + (("num", 2, io, 1),))
             elif t == "boolean":
                 if ch == "t":
                     out.add(rest + (("lit", "rue"),))
@@ -227,35 +230,43 @@ class JsonSchemaMatcher:
     #      0 after '-', 1 a lone 0, 2 integer digits, 3 after '.', 4 fraction digits, 5 after e/E, 6 after the
     #      exponent's sign, 7 exponent digits. Phases 1, 2, 4, 7 may end: the character goes to the frame below.
     def _number(self, rest, frame, ch, out):
-        _k, ph, io = frame
+        _k, ph, io, n = frame
+        room = n < _MAX_NUM_CHARS
+
+        def go(phase):
+            out.add(rest + (("num", phase, io, n + 1),))
+
         if ph == 0:
             if ch == "0":
-                out.add(rest + (("num", 1, io),))
+                go(1)
             elif ch in "123456789":
-                out.add(rest + (("num", 2, io),))
+                go(2)
             return
         if ph in (2, 4, 7) and ch in _DIGITS:
-            out.add(rest + (("num", ph, io),))
+            if room:
+                go(ph)
             return
         if ph in (1, 2) and ch == "." and not io:
-            out.add(rest + (("num", 3, io),))
+            if room:
+                go(3)
             return
         if ph in (1, 2, 4) and ch in "eE" and not io:
-            out.add(rest + (("num", 5, io),))
+            if room:
+                go(5)
             return
         if ph == 3:
             if ch in _DIGITS:
-                out.add(rest + (("num", 4, io),))
+                go(4)
             return
         if ph == 5:
             if ch in "+-":
-                out.add(rest + (("num", 6, io),))
+                go(6)
             elif ch in _DIGITS:
-                out.add(rest + (("num", 7, io),))
+                go(7)
             return
         if ph == 6:
             if ch in _DIGITS:
-                out.add(rest + (("num", 7, io),))
+                go(7)
             return
         # the number is over: whoever is below sees this character (a top-level number ends at whitespace)
         if rest:
@@ -275,7 +286,7 @@ class JsonSchemaMatcher:
         return props, required, extra
 
     def _object(self, rest, frame, ch, out):
-        _k, sid, idx, phase, count = frame
+        _k, sid, idx, phase, count = frame[:5]
         props, required, extra = self._props(sid)
         if phase == 0 or phase == 4:                 # 4: after ',' (a key must follow)
             if ch in _WS:
@@ -343,11 +354,6 @@ class JsonSchemaMatcher:
                 out.add(rest + (("arr", sid, n, 2),))
         elif ch == "]" and n >= lo:
             out.add(rest)
-
-
-def _fix_ws_frames(stack):  # pragma: no cover - documentation of the invariant only
-    """A ("ws", n) frame always sits directly above the frame that continues after the whitespace."""
-    return stack
 
 
 class TokenChooser:

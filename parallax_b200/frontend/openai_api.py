@@ -47,7 +47,26 @@ def sampling_params_from_body(body: dict, default_max_tokens: int = 512) -> Samp
         stop_token_ids=body.get("stop_token_ids"), ignore_eos=bool(body.get("ignore_eos", False)),
         stop_strs=stop, repetition_penalty=float(_num(body, "repetition_penalty", 1.0)),
         presence_penalty=float(_num(body, "presence_penalty", 0.0)),
-        frequency_penalty=float(_num(body, "frequency_penalty", 0.0)), seed=body.get("seed"))
+        frequency_penalty=float(_num(body, "frequency_penalty", 0.0)), seed=body.get("seed"),
+        json_schema=_json_schema_of(body))
+
+
+def _json_schema_of(body: dict):
+    """``response_format`` of the OpenAI API (``{"type": "json_schema", "json_schema": {"schema": ...}}`` or
+    ``{"type": "json_object"}``) or a bare ``json_schema`` field, as JSON text; None when the reply is free text."""
+    import json
+
+    rf = body.get("response_format")
+    schema = body.get("json_schema")
+    if isinstance(rf, dict):
+        if rf.get("type") == "json_object":
+            schema = {"type": "object"}
+        elif rf.get("type") == "json_schema":
+            js = rf.get("json_schema") or {}
+            schema = js.get("schema", js) if isinstance(js, dict) else js
+    if schema is None:
+        return None
+    return schema if isinstance(schema, str) else json.dumps(schema)
 
 
 async def _events(q, poll_s: float = 0.002) -> AsyncIterator[TokenEvent]:

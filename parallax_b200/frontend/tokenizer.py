@@ -73,6 +73,25 @@ class TokenizerWrapper:
     def decode(self, ids, skip_special_tokens: bool = True) -> str:
         return self.tok.decode(list(ids), skip_special_tokens=skip_special_tokens)
 
+    def token_text(self, token_id: int) -> Optional[str]:
+        """Text that this token adds on its own, or None for special tokens and for tokens that are only a
+        fragment of a character (constrained decoding checks candidate tokens with this)."""
+        cache = self.__dict__.setdefault("_token_text", {})
+        if token_id in cache:
+            return cache[token_id]
+        t: Optional[str]
+        if isinstance(self.tok, ByteTokenizer):
+            t = chr(token_id) if token_id < 128 else None
+        else:
+            try:
+                t = self.tok.decode([int(token_id)], skip_special_tokens=True)
+            except Exception:
+                t = None
+            if t is not None and (t == "" or "\ufffd" in t):
+                t = None
+        cache[token_id] = t
+        return t
+
     def _clamp(self, ids: list[int]) -> list[int]:
         # random-init models may have a smaller vocabulary than the tokenizer in use
         if self.vocab_size:

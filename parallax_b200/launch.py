@@ -115,9 +115,10 @@ def run_standalone(args) -> None:
         run_multi_gpu(args, cfg, name, path)
         return
     engine = build_engine(args, cfg, loader, start, end, state)
+    tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size)
+    engine.tokenizer = tok           # requests with a JSON schema check candidate tokens by their text
     loop = EngineLoop(engine, shared_state=state)
     loop.start()
-    tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size)
     app = create_app(loop, tok, name, max_model_len=args.max_sequence_length)
     if args.engine_core_input_addr and args.engine_core_output_addr:
         from parallax_b200.frontend.engine_core_server import EngineCoreServer
