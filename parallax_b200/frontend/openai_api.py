@@ -87,6 +87,9 @@ async def _events(q, poll_s: float = 0.002) -> AsyncIterator[TokenEvent]:
 def create_app(loop: EngineLoop, tokenizer: TokenizerWrapper, model_name: str, max_model_len: int = 32768):
     app = FastAPI(title="parallax_b200 node")
     app.state.loop, app.state.tokenizer, app.state.model_name = loop, tokenizer, model_name
+    eng = getattr(loop, "engine", None)
+    if eng is not None and getattr(eng, "tokenizer", 0) is None:
+        eng.tokenizer = tokenizer      # constrained decoding (response_format) checks tokens by their text
 
     @app.get("/")
     @app.get("/ui")

@@ -81,3 +81,16 @@ def test_incremental_detokenizer_utf8_and_stop():
     d2 = IncrementalDetokenizer(t)
     out2 = "".join(d2.add(b) for b in "日本語".encode("utf-8")) + d2.flush()
     assert out2 == "日本語"
+
+
+def test_response_format_json_schema_over_http(client):
+    schema = {"type": "object", "properties": {"answer": {"type": "boolean"}, "n": {"type": "integer"}},
+              "required": ["answer", "n"]}
+    r = client.post("/v1/chat/completions", json={
+        "messages": [{"role": "user", "content": "reply in json"}], "max_tokens": 120, "temperature": 0,
+        "response_format": {"type": "json_schema", "json_schema": {"name": "reply", "schema": schema}}})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    doc = json.loads(body["choices"][0]["message"]["content"])
+    assert isinstance(doc["answer"], bool) and isinstance(doc["n"], int) and set(doc) == {"answer", "n"}
+    assert body["choices"][0]["finish_reason"] == "stop"
