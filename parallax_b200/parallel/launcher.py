@@ -138,10 +138,14 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
     from parallax_b200.utils.shared_state import SharedState
 
     # experts of MoE layers are sharded over the stage's tensor-parallel group, so an expert-parallel
-    # size simply asks for a group of that many ranks
-    tp_size = max(args.tp_size, getattr(args, "ep_size", 1))
+    # size simply asks for a group of that many ranks; with --enable-dp-attention the expert-parallel
+    # ranks instead each run attention on their own requests and meet only in the MoE layers
+    ep_size = getattr(args, "ep_size", 1)
+    dp_lanes = ep_size if (getattr(args, "enable_dp_attention", False) and ep_size > 1 and cfg.is_moe) else 1
+    tp_size = args.tp_size if dp_lanes > 1 else max(args.tp_size, ep_size)
     device_type = "cuda" if torch.cuda.is_available() else "cpu"
-    spec = dict(model_path=path, model_name=name.split("/")[-1], pp=args.pp_size, tp=tp_size, device_type=device_type,
+    spec = dict(model_path=path, model_name=name.split("/")[-1], pp=args.pp_size, tp=tp_size, ep=dp_lanes,
+                device_type=device_type,
                 dtype=args.dtype if args.dtype in ("bfloat16", "float16") else "bfloat16",
                 page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
                 kv_cache_dtype=getattr(args, "kv_cache_dtype", None),
@@ -165,7 +169,8 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
     tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size)
     app = create_app(loop, tok, name, max_model_len=args.max_sequence_length)
     state.set_status("available")
-    logger.info("serving %s on http://%s:%d with pp=%d tp=%d", name, args.host, args.port, args.pp_size, tp_size)
+    logger.info("serving %s on http://%s:%d with pp=%d tp=%d dp-attention lanes=%d", name, args.host, args.port,
+                args.pp_size, tp_size, dp_lanes)
     _server, thread = serve_http(app, args.host, args.port, args.log_level)
     try:
         while thread.is_alive():
