@@ -608,6 +608,7 @@ class Engine:
                     why = RequestStatus.FINISHED_EOS
                 if stuck:
                     del req.output_ids[k:]      # no candidate fitted: the stand-in token is not part of the reply
+                    tok = None
             if why is not None:
                 del req.output_ids[k + 1:]      # a placeholder of the step that is already running
                 req.update_status(why)

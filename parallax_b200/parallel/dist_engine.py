@@ -179,7 +179,7 @@ class DistEngine:
                  liveness_timeout_s: float = 10.0, step_timeout_s: float = 600.0, align_rows: int = 0,
                  executor_thread: Optional[bool] = None, ep: int = 1, ep_local_init: Optional[bool] = None,
                  kv_cache_dtype: Optional[str] = None, linear_prefix_slots: Optional[int] = None,
-                 lora: Optional[dict] = None):
+                 lora: Optional[dict] = None, tokenizer=None):
         assert dist.is_initialized(), "init the default process group first (nccl on GPUs, gloo on CPU)"
         self.cfg = cfg
         self.device = torch.device(device)
@@ -340,6 +340,14 @@ class DistEngine:
                 self.lora = LoRAManager([], n_slots, lora.get("paths"),
                                         on_load=lambda slot, name, path: self._lora_loads.append((int(slot), name, path)))
         self._slot_pre: list = []        # rank 0: state-slot copies (dst, src) that the next plan carries
+        # JSON-schema constrained requests: rank 0 keeps a matcher per request to know when the document is
+        # complete; the rank that samples keeps its own copy (built from the schema that rides with the
+        # request's first constrained plan) and advances it with the tokens it picks
+        self.tokenizer = tokenizer
+        self._grammar_known: set = set()        # rank 0: request ids whose schema has travelled
+        self._grammar_drops: list = []          # rank 0: finished constrained requests, for the next plan
+        self._grammars: dict = {}               # sampling rank: request id -> matcher
+        self._py_rng = __import__("random").Random(seed + 777)
         self.in_flight: deque = deque()
         self._pending_sends: deque = deque()
         self._side_events: list = []
@@ -446,6 +454,13 @@ class DistEngine:
             if self.lora is None:
                 raise ValueError("this engine was started without LoRA support (--enable-lora)")
             req.lora_slot = self.lora.acquire(req.lora_path)       # the load travels with the next plan
+        req.grammar = None
+        if req.sampling_params.json_schema:
+            if self.tokenizer is None:
+                raise ValueError("json_schema needs an engine that knows its tokenizer (DistEngine(tokenizer=...))")
+            from parallax_b200.engine.structured import JsonSchemaMatcher
+
+            req.grammar = JsonSchemaMatcher(req.sampling_params.json_schema)
         # expert-parallel lanes: the request stays with the least loaded lane for its whole life
         pl = min(self.planners, key=lambda p: p.scheduler.num_queued_requests + p.scheduler.num_running_requests)
         pl.scheduler.enque_request(req)
@@ -470,20 +485,52 @@ class DistEngine:
                                            for p in self.planners)
 
     # ------------------------------------------------------------------ one micro-batch on this rank
-    def _sample(self, lp: dict, out: torch.Tensor) -> torch.Tensor:
+    def _sample(self, lp: dict, out: torch.Tensor, constrain: bool = False) -> torch.Tensor:
         if lp.get("pen") is not None:
             from parallax_b200.engine.sampling import apply_penalties
 
             out = apply_penalties(out, lp["pen"])
         if lp["greedy"]:
-            return ops.argmax(out)
-        dev = out.device
-        sp = lp["sampling"]
-        return ops.sample(out, torch.tensor(sp["t"], dtype=torch.float32, device=dev),
-                          torch.tensor(sp["k"], dtype=torch.int32, device=dev),
-                          torch.tensor(sp["p"], dtype=torch.float32, device=dev),
-                          torch.tensor(sp["mp"], dtype=torch.float32, device=dev),
-                          torch.tensor(sp["u"], dtype=torch.float32, device=dev))
+            tokens = ops.argmax(out)
+        else:
+            dev = out.device
+            sp = lp["sampling"]
+            tokens = ops.sample(out, torch.tensor(sp["t"], dtype=torch.float32, device=dev),
+                                torch.tensor(sp["k"], dtype=torch.int32, device=dev),
+                                torch.tensor(sp["p"], dtype=torch.float32, device=dev),
+                                torch.tensor(sp["mp"], dtype=torch.float32, device=dev),
+                                torch.tensor(sp["u"], dtype=torch.float32, device=dev))
+        if constrain and lp.get("grammar"):
+            tokens = self._constrain(lp, out, tokens)
+        return tokens
+
+    def _constrain(self, lp: dict, logits: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+        """Sampling rank: rows of requests with a JSON schema get the best candidate (or a draw among the
+        valid candidates) whose text keeps the request's document valid; -1 where no token fits, which
+        ends the request on rank 0. A request is never in two micro-batches at once, so this rank's
+        matcher, advanced with every token picked here, is the document's state."""
+        from parallax_b200.engine.structured import JsonSchemaMatcher, TokenChooser
+
+        tok = self.tokenizer
+        if tok is None:
+            raise RuntimeError("a constrained request reached a sampling rank that has no tokenizer")
+        chooser = TokenChooser(tok.token_text, sorted(getattr(tok, "eos_token_ids", ()) or ()))
+        rows, vals = [], []
+        for row, rid, schema, temp in lp["grammar"]:
+            g = self._grammars.get(rid)
+            if g is None:
+                g = self._grammars[rid] = JsonSchemaMatcher(schema)
+            choice = chooser.choose(g, logits[row], temp, self._py_rng)
+            if choice is not None:
+                text = tok.token_text(int(choice))
+                if text and not g.done:
+                    g.advance(text)
+            rows.append(int(row))
+            vals.append(-1 if choice is None else int(choice))
+        tokens = tokens.clone()
+        tokens[torch.tensor(rows, dtype=torch.long, device=tokens.device)] = torch.tensor(
+            vals, dtype=tokens.dtype, device=tokens.device)
+        return tokens
 
     def _execute(self, plan: dict):
         """Run this rank's part of one planned micro-batch. Returns, on rank 0, one handle per plan of
@@ -495,6 +542,8 @@ class DistEngine:
             from parallax_b200.loader.lora import LoRAAdapter
 
             w.model.lora.load(slot, LoRAAdapter.load(path, name))     # this rank's layers of the adapter
+        for rid in plan.get("grammar_drop") or ():
+            self._grammars.pop(rid, None)
         lp = lane_plans[topo.lane if self.n_plans > 1 else 0]
         if self.ep_comm is not None:
             self.ep_comm.step_max_rows = plan.get("max_rows")
@@ -542,7 +591,7 @@ class DistEngine:
                 out = out if out.is_contiguous() else out.contiguous()
                 self._pending_sends.append((dist.isend(out, dst=self._next(), group=self.hop_out), out))
             elif n_logits > 0:
-                tokens = self._sample(lp, out)
+                tokens = self._sample(lp, out, constrain=is_sender)
                 if is_sender:
                     # the status word of the sampling rank rides with the tokens
                     packed = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)
@@ -803,6 +852,16 @@ class DistEngine:
                 rows[o:o + s.num_tokens] = getattr(s.req, "lora_slot", -1)
                 o += s.num_tokens
             lp["lora_ids"] = rows
+        if any(getattr(s.req, "grammar", None) is not None for s in owners):
+            rows = []
+            for row, s in enumerate(owners):
+                if getattr(s.req, "grammar", None) is None:
+                    continue
+                rid, sp = s.req.request_id, s.req.sampling_params
+                first = rid not in self._grammar_known
+                self._grammar_known.add(rid)
+                rows.append((row, rid, sp.json_schema if first else None, 0.0 if sp.is_greedy else sp.temperature))
+            lp["grammar"] = rows
         from parallax_b200.engine.sampling import build_penalties
 
         pen = build_penalties([s.req for s in owners])
@@ -843,6 +902,8 @@ class DistEngine:
                 "max_rows": max(int(lp["pos"].shape[0]) for lp in lane_plans if lp is not None)}
         if self._lora_loads:
             plan["lora_load"], self._lora_loads = self._lora_loads, []
+        if self._grammar_drops:
+            plan["grammar_drop"], self._grammar_drops = self._grammar_drops, []
         t1 = time.perf_counter()
         self.chan.publish(plan)
         t2 = time.perf_counter()
@@ -955,14 +1016,25 @@ class DistEngine:
             for s, tok in zip(arrays["owners"], toks):
                 req = s.req
                 tok = int(tok)
-                req.commit_new_token(tok, now=now)
-                cache.append_request_token(req.request_id, tok)
+                g = getattr(req, "grammar", None)
+                if tok >= 0:
+                    req.commit_new_token(tok, now=now)
+                    cache.append_request_token(req.request_id, tok)
+                if g is not None and not req.is_finished:
+                    # the document grows by the token's text; it ends the request once it is complete,
+                    # and so does a step in which no token fitted (-1 from the sampling rank)
+                    text = self.tokenizer.token_text(tok) if tok >= 0 else None
+                    if not text or not g.advance(text) or g.done:
+                        req.update_status(RequestStatus.FINISHED_EOS)
                 if sched.check_and_update_request_status(req):
                     cache.free_request(req.request_id)
                     self._release_lora(req)
+                    if g is not None:
+                        self._grammar_known.discard(req.request_id)
+                        self._grammar_drops.append(req.request_id)
                 else:
                     sched.enque_request(req, now=now)
-                out.append((req, tok))
+                out.append((req, tok if tok >= 0 else None))
         self.host_s["commit"] += time.perf_counter() - tc
         return out
 
