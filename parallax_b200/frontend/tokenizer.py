@@ -112,6 +112,22 @@ class TokenizerWrapper:
         return self.encode(text, add_special_tokens=False)
 
 
+class LazyTokenizer:
+    """A :class:`TokenizerWrapper` that is loaded at first use: ranks of a multi-process engine that never
+    sample a constrained request never pay for reading the vocabulary."""
+
+    def __init__(self, model_path: Optional[str], vocab_size: Optional[int] = None):
+        self._args = (model_path, vocab_size)
+        self._tok: Optional[TokenizerWrapper] = None
+
+    def __getattr__(self, name):
+        if name.startswith("_"):
+            raise AttributeError(name)
+        if self._tok is None:
+            self._tok = TokenizerWrapper.from_pretrained(*self._args)
+        return getattr(self._tok, name)
+
+
 def _content_text(content) -> str:
     if isinstance(content, str):
         return content

@@ -79,6 +79,10 @@ def build_dist_engine(spec: dict):
         for lp in spec.get("lora_paths") or []:
             apply_lora_adapter(weights, lp)
     kw = {k: spec[k] for k in _ENGINE_KEYS if k in spec and spec[k] is not None}
+    from parallax_b200.frontend.tokenizer import LazyTokenizer
+
+    # constrained decoding turns token ids into text on the rank that samples; loaded there on first use
+    kw["tokenizer"] = LazyTokenizer(spec.get("model_path"), cfg.vocab_size)
     return DistEngine(cfg, pp, tp, device, dtype, weights=weights, weights_prefiltered=weights is not None, **kw)
 
 

@@ -30,7 +30,22 @@ def main() -> None:
         prompts = spec["prompts"]
         eng.mark()
         sp = SamplingParams(max_new_tokens=spec["max_new"], temperature=0.0, ignore_eos=True)
-        if spec.get("lora_of"):
+        if spec.get("schema_of"):
+            # per prompt a JSON schema (or None): constrained decoding on the rank that samples
+            from parallax_b200.engine.request import Request
+
+            reqs = []
+            for p, sch in zip(prompts, spec["schema_of"]):
+                d = dict(sp.to_dict(), max_new_tokens=spec["max_new"] if sch is None else 120)
+                if sch is not None:
+                    d.update(json_schema=json.dumps(sch), ignore_eos=False)
+                reqs.append(Request(input_ids=list(p), sampling_params=SamplingParams.from_dict(d)))
+            for r in reqs:
+                eng.add_request(r)
+            while eng.has_work():
+                eng.step()
+            outs = [r.output_ids for r in reqs]
+        elif spec.get("lora_of"):
             from parallax_b200.engine.request import Request
 
             reqs = [Request(input_ids=list(p), sampling_params=SamplingParams.from_dict(sp.to_dict()), lora_path=a)

@@ -130,6 +130,45 @@ def test_hybrid_prefix_cache_across_ranks(pp, tp, tmp_path):
     assert got["prefix_hits"] >= 2 and got["state_snapshots"] >= 1, got
 
 
+@pytest.mark.parametrize("pp,tp", [(2, 1), (1, 2)])
+def test_constrained_decoding_on_the_sampling_rank(pp, tp, tmp_path):
+    """JSON-schema requests in a multi-rank engine: the rank that samples keeps the matcher, rank 0 ends the
+    request when the document is complete; the result equals the single-process engine's, and the
+    unconstrained request of the same batch is untouched."""
+    from parallax_b200.engine.request import Request
+    from parallax_b200.engine.structured import JsonSchemaMatcher
+    from parallax_b200.frontend.tokenizer import TokenizerWrapper
+
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}, "n": {"type": "integer"}},
+              "required": ["ok", "n"]}
+    schema_of = [schema, None, schema]
+    prompts = PROMPTS[:3]
+    got = _run_group(pp, tp, tmp_path, prompts=prompts, schema_of=schema_of)["outputs"]
+    cfg = named_config("tiny")
+    tok = TokenizerWrapper.from_pretrained(None, vocab_size=cfg.vocab_size)
+    torch.manual_seed(0)
+    eng = Engine(cfg, device="cpu", num_blocks=256, page_size=16, max_batch_size=4, max_num_tokens_per_batch=64,
+                 chunked_prefill_size=16, max_total_length=256, seed=0, tokenizer=tok)
+    reqs = []
+    for p, sch in zip(prompts, schema_of):
+        d = dict(max_new_tokens=6 if sch is None else 120, temperature=0.0, ignore_eos=sch is None)
+        if sch is not None:
+            d["json_schema"] = json.dumps(sch)
+        reqs.append(Request(input_ids=list(p), sampling_params=SamplingParams.from_dict(d)))
+        eng.add_request(reqs[-1])
+    while eng.has_work():
+        eng.step()
+    for r, ids, sch in zip(reqs, got, schema_of):
+        if sch is not None:
+            text = tok.decode(ids)
+            m = JsonSchemaMatcher(sch)
+            assert m.advance(text) and m.done, text
+            assert set(json.loads(text)) >= {"ok", "n"}
+        if tp == 1:
+            assert ids == r.output_ids      # same summation order as the single process
+    assert len(got[1]) == 6
+
+
 def test_rank_loss_is_detected_on_the_host(tmp_path):
     """Failure detection without touching a device: the second pipeline rank exits between steps;
     the scheduling rank sees its heartbeat stop and raises within seconds."""

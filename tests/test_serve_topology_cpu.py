@@ -49,6 +49,11 @@ def test_serve_with_in_box_topology(model, topo, tmp_path):
         b = _post(port, body)
         assert a["usage"]["completion_tokens"] >= 1
         assert a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+        # constrained decoding runs on the rank that samples (the last stage, or every expert-parallel lane)
+        schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}
+        c = _post(port, dict(body, max_tokens=80,
+                             response_format={"type": "json_schema", "json_schema": {"name": "x", "schema": schema}}))
+        assert isinstance(json.loads(c["choices"][0]["message"]["content"])["ok"], bool)
     finally:
         if proc.poll() is None:
             os.killpg(proc.pid, signal.SIGTERM)      # the server and the ranks it spawned share this process group
