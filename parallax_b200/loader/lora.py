@@ -149,6 +149,96 @@ class LoRAStack:
         return out
 
 
+class TPLoRAStack(LoRAStack):
+    """Slots of a tensor-parallel stage whose residual stream is sharded by rows. The adapters are cut the way
+    the base weights are: ``B`` of q/k/v keeps the rows of this rank's heads (``A`` whole), ``A`` of ``o_proj``
+    and ``down_proj`` keeps the columns of this rank's heads / intermediate slice (``B`` whole). The rank-r
+    intermediate is the only thing that crosses ranks: for q/k/v every rank projects its own rows and the
+    ``[rows, r]`` pieces are all-gathered; for ``o_proj`` / ``down_proj`` the partial ``[T, r]`` products are
+    reduce-scattered to the rows' owners, which add ``B`` times them to the projection's (already reduced)
+    output. Plain matrix products per resident adapter: adapters are a small share of a step."""
+
+    def __init__(self, stage, max_slots: int, max_rank: int):
+        super().__init__(stage, max_slots, max_rank)
+        cfg, tp = stage.cfg, stage.tp_size
+        D, H, I = cfg.head_dim, cfg.hidden_size, cfg.intermediate_size
+        self.tp, self.tp_rank = tp, stage.tp_rank
+        self.hq_l, self.hkv_l, self.i_l = stage.hq_l, stage.hkv_l, I // tp
+        self.q_full, self.kv_full = self.q_out, self.kv_out
+        self.q_out, self.kv_out = self.hq_l * D, self.hkv_l * D
+        self.dims = {"qkv": (H, (self.hq_l + 2 * self.hkv_l) * D, _pad64(3 * max_rank)),
+                     "o": (self.hq_l * D, H, _pad64(max_rank)), "down": (self.i_l, H, _pad64(max_rank))}
+        for per in self.layers:
+            for tgt in list(per):
+                n_in, n_out, R = self.dims[tgt]
+                per[tgt] = (torch.zeros((max_slots * R, n_in), dtype=self.dtype, device=self.device),
+                            torch.zeros((max_slots * n_out, R), dtype=self.dtype, device=self.device))
+        self.scale_host = [0.0] * max_slots
+
+    def load(self, slot: int, adapter: LoRAAdapter) -> None:
+        r, k = self.tp_rank, adapter.rank
+        ql, kvl, il = self.q_out, self.kv_out, self.i_l
+        cut = {}
+        for (layer, mod), (A, B) in adapter.tensors.items():
+            if mod == "q_proj":
+                cut[(layer, mod)] = (A, B[r * ql:(r + 1) * ql])
+            elif mod in ("k_proj", "v_proj"):
+                cut[(layer, mod)] = (A, B[r * kvl:(r + 1) * kvl])
+            elif mod == "o_proj":
+                cut[(layer, mod)] = (A[:, r * ql:(r + 1) * ql], B)
+            elif mod == "down_proj":
+                cut[(layer, mod)] = (A[:, r * il:(r + 1) * il], B)
+        super().load(slot, LoRAAdapter(adapter.name, k, adapter.scaling, cut))
+        self.scale_host[slot] = float(adapter.scaling)
+
+    def _index(self, fb, rp: int):
+        """Per step: for every adapter slot in use the rows of the whole (padded) batch and this rank's own rows."""
+        idx = fb.extras.get("_lora_tp_index")
+        if idx is None or idx[0] != rp:
+            host = fb.extras.get("lora_ids_host")
+            if host is None:
+                host = fb.extras["lora_ids"].cpu().numpy()
+            import numpy as np
+
+            full = np.full(rp * self.tp, -1, dtype=np.int64)
+            full[:len(host)] = host
+            mine = full[self.tp_rank * rp:(self.tp_rank + 1) * rp]
+            per = {}
+            for s in sorted(set(int(v) for v in full if v >= 0)):
+                per[s] = (torch.from_numpy(np.nonzero(full == s)[0]).to(self.device),
+                          torch.from_numpy(np.nonzero(mine == s)[0]).to(self.device))
+            idx = fb.extras["_lora_tp_index"] = (rp, per)
+        return idx[1]
+
+    def apply_tp(self, tgt: str, li: int, x: torch.Tensor, y: torch.Tensor, fb, comm) -> torch.Tensor:
+        """``tgt == "qkv"``: ``x`` are this rank's normalised rows ``[Rp, H]``, ``y`` the gathered batch's
+        projection on this rank's heads ``[tp*Rp, cols]``. ``"o"`` / ``"down"``: ``x`` is the gathered batch on
+        this rank's input slice ``[tp*Rp, in_local]``, ``y`` this rank's rows of the reduced output ``[Rp, H]``.
+        Every rank of the group calls this for the same steps (the row -> adapter map is the whole batch's)."""
+        per = self.layers[li].get(tgt)
+        if per is None:
+            return y
+        a_stack, b_stack = per
+        _n_in, n_out, R = self.dims[tgt]
+        rp = x.shape[0] if tgt == "qkv" else y.shape[0]
+        index = self._index(fb, rp)
+        if not index:
+            return y
+        t = torch.zeros((x.shape[0], R), dtype=torch.float32, device=x.device)
+        for s, (rows_all, rows_mine) in index.items():
+            rows = rows_mine if tgt == "qkv" else rows_all
+            if rows.numel():
+                t[rows] = x[rows].float() @ a_stack[s * R:(s + 1) * R].float().t()
+        t = comm.all_gather_rows(t) if tgt == "qkv" else comm.reduce_scatter_rows(t)
+        y = y.clone() if not y.is_contiguous() else y
+        for s, (rows_all, rows_mine) in index.items():
+            rows = rows_all if tgt == "qkv" else rows_mine
+            if rows.numel():
+                d = t[rows] @ b_stack[s * n_out:(s + 1) * n_out].float().t()
+                y[rows] = (y[rows].float() + self.scale_host[s] * d).to(y.dtype)
+        return y
+
+
 class LoRAManager:
     """Adapters by name: which are resident in which slot, least recently used ones make room. A slot that a
     running request uses is pinned."""

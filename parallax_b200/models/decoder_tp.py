@@ -142,8 +142,12 @@ class TPDecoderStage(TPStageMixin, DecoderStage):
         eps, D, T = cfg.rms_norm_eps, cfg.head_dim, fb.num_tokens
         hq, hkv = self.hq_l, self.hkv_l
         Tp = fb.num_prefill_tokens
+        # per-request adapters: only steps in which some row uses one pay for them
+        lora = self.lora if (self.lora is not None and fb.extras.get("lora_ids") is not None) else None
         for li, lw in enumerate(self.layers):
             qkv = comm.norm_ag_linear(h_shard, lw.ln1, eps, lw.w_qkv, bias=lw.b_qkv, w_offset=self.norm_offset)
+            if lora is not None:
+                qkv = lora.apply_tp("qkv", li, ops.rmsnorm(h_shard, lw.ln1, eps, w_offset=self.norm_offset), qkv, fb, comm)
             T_pad = qkv.shape[0]
             kc, vc = self.kv_caches[li]
             kvs = getattr(self.kv_caches[li], "kv_scale", (1.0, 1.0))
@@ -159,6 +163,8 @@ class TPDecoderStage(TPStageMixin, DecoderStage):
                 ops.attn_decode(q[Tp:], kc, vc, fb.d_block_tables, fb.d_ctx_lens, self.scale, window=lw.window,
                                 sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:T], kv_scale=kvs)
             h_shard = comm.linear_rs(attn.view(T_pad, hq * D), lw.w_o, residual=h_shard)
+            if lora is not None:
+                h_shard = lora.apply_tp("o", li, attn.view(T_pad, hq * D), h_shard, fb, comm)
             if lw.moe is not None:
                 # attention is tensor parallel, the experts are expert parallel: every rank routes its
                 # own token rows and the dispatch / combine kernels move them to the experts' owners
@@ -175,4 +181,6 @@ class TPDecoderStage(TPStageMixin, DecoderStage):
             else:
                 act = comm.norm_ag_linear(h_shard, lw.ln2, eps, lw.w_gu, epi=ops.EPI_SILU_MUL, w_offset=self.norm_offset)
             h_shard = comm.linear_rs(act, lw.w_down, residual=h_shard)
+            if lora is not None:
+                h_shard = lora.apply_tp("down", li, act, h_shard, fb, comm)
         return h_shard

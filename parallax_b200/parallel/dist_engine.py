@@ -329,13 +329,14 @@ class DistEngine:
         self.lora = None
         self._lora_loads: list = []
         if lora:
-            from parallax_b200.loader.lora import LoRAManager, LoRAStack
+            from parallax_b200.loader.lora import LoRAManager, LoRAStack, TPLoRAStack
 
-            if tp > 1 or ep > 1 or not hasattr(self.worker.model, "lora") or family != "decoder":
-                raise ValueError("per-request LoRA in the multi-GPU engine is available for pipeline stages of the "
-                                 "GQA decoder families (tp = ep = 1)")
+            if not hasattr(self.worker.model, "lora") or family != "decoder":
+                raise ValueError("per-request LoRA in the multi-GPU engine is available for the GQA decoder families")
             n_slots, max_rank = int(lora.get("max_loaded") or 4), int(lora.get("max_rank") or 64)
-            self.worker.model.lora = LoRAStack(self.worker.model, n_slots, max_rank)
+            # tensor-parallel ranks keep their slice of every adapter; expert-parallel lanes run whole attention
+            # layers (the adapters' targets) on their own requests, so each keeps whole adapters
+            self.worker.model.lora = (TPLoRAStack if tp > 1 else LoRAStack)(self.worker.model, n_slots, max_rank)
             if rank == 0:
                 self.lora = LoRAManager([], n_slots, lora.get("paths"),
                                         on_load=lambda slot, name, path: self._lora_loads.append((int(slot), name, path)))
@@ -560,6 +561,8 @@ class DistEngine:
                          lp["p_ctx"], lp["p_tables"], lp["d_ctx"], lp["d_tables"], lp["logit_rows"],
                          lp.get("seq_rows"),
                          extra={"lora_ids": lp["lora_ids"]} if lp.get("lora_ids") is not None else None)
+            if lp.get("lora_ids") is not None:
+                fb.extras["lora_ids_host"] = lp["lora_ids"]
             self.h2d_bytes += fb.h2d_bytes
             T = fb.num_tokens
             hidden = None

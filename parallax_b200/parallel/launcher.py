@@ -163,7 +163,7 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
 
     per_request = _lora_spec(args)
     if per_request is not None:
-        # named adapters are served per request (pipeline stages only); a single unnamed one is merged at load
+        # named adapters are served per request; a single unnamed one is merged into the weights at load
         spec["lora"], spec["lora_paths"] = per_request, []
     engine, procs = launch_dist_engine(spec)
     state = SharedState.create(in_process=True)

@@ -76,6 +76,17 @@ class CollectiveTPComm:
         dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
         return full
 
+    def reduce_scatter_rows(self, x):
+        """Sum ``[tp*Rp, n]`` over the group, keep this rank's ``Rp`` rows (fp32, small side products)."""
+        x = x.float().contiguous()
+        rp = x.shape[0] // self.tp
+        if x.is_cuda:
+            out = torch.empty((rp, x.shape[1]), dtype=torch.float32, device=x.device)
+            dist.reduce_scatter_tensor(out, x, group=self.group)
+            return out
+        dist.all_reduce(x, group=self.group)
+        return x[self.rank * rp:(self.rank + 1) * rp]
+
     def all_gather_cols(self, x):
         """Concatenate per-rank column blocks: ``[T, n] -> [T, tp*n]`` (vocab-parallel logits)."""
         parts = [torch.empty_like(x) for _ in range(self.tp)]

@@ -130,25 +130,32 @@ def test_lora_update_on_grouped_tcgen05_gemms(tmp_path):
     cu.check_status(dev)
 
 
-def test_per_request_adapters_across_pipeline_stages(tmp_path):
-    """Two pipeline stages as two processes: rank 0 decides which adapter lives in which slot, the load travels
-    with the step plan and every rank loads its own layers of the adapter. Same tokens as the single-process
-    engine with the same adapters."""
+import pytest
+
+
+@pytest.mark.parametrize("model,pp,tp,ep", [("tiny", 2, 1, 1), ("tiny", 1, 2, 1), ("tiny", 2, 2, 1), ("tiny-moe", 1, 1, 2)])
+def test_per_request_adapters_across_ranks(model, pp, tp, ep, tmp_path):
+    """Several ranks as processes: rank 0 decides which adapter lives in which slot, the load travels with the
+    step plan and every rank loads its own part of the adapter - its layers (pipeline stages), its heads and
+    intermediate slice (tensor-parallel ranks), or the whole adapter (expert-parallel lanes, which run whole
+    attention layers on their own requests). Same tokens as the single-process engine with the same adapters."""
     import os
     import subprocess
     import sys
 
     from parallax_b200.parallel.launcher import free_port
 
-    cfg = named_config("tiny")
+    cfg = named_config(model)
     a1 = _make_adapter(cfg, tmp_path / "a1", 1)
     a2 = _make_adapter(cfg, tmp_path / "a2", 2, rank=8, alpha=4)
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (21, 9, 33, 17)]
     lora_of = ["x", "y", None, "x"]
+    world = pp * tp * ep
     lora = {"max_loaded": 2, "max_rank": 8, "paths": {"x": a1, "y": a2}}
     kw = dict(num_blocks=128, page_size=16, max_batch_size=4, max_num_tokens_per_batch=64, chunked_prefill_size=16,
               max_total_length=256, seed=0)
+    torch.manual_seed(0)
     eng = Engine(cfg, device="cpu", lora=lora, **kw)
     reqs = [Request(input_ids=p, sampling_params=SamplingParams(max_new_tokens=6, temperature=0.0, ignore_eos=True),
                     lora_path=a) for p, a in zip(prompts, lora_of)]
@@ -159,14 +166,15 @@ def test_per_request_adapters_across_pipeline_stages(tmp_path):
     want = [r.output_ids for r in reqs]
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     helper = os.path.join(root, "tests", "helpers", "dist_engine_rank.py")
-    spec = dict(model_name="tiny", pp=2, tp=1, device_type="cpu", prompts=prompts, max_new=6, lora=lora, lora_of=lora_of, **kw)
+    spec = dict(model_name=model, pp=pp, tp=tp, ep=ep, device_type="cpu", prompts=prompts, max_new=6, lora=lora,
+                lora_of=lora_of, **kw)
     out, port = tmp_path / "out.json", free_port()
     procs = []
-    for r in range(2):
-        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                    OMP_NUM_THREADS="2", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
         procs.append(subprocess.Popen([sys.executable, helper, json.dumps(spec), str(out)], env=env))
-    assert [p.wait(timeout=240) for p in procs] == [0, 0]
+    assert [p.wait(timeout=240) for p in procs] == [0] * world
     got = json.loads(out.read_text())["outputs"]
     assert got == want
     # the adapters really change the output of their requests
