@@ -20,7 +20,9 @@ import numpy as np
 # header bytes: [0:8] reserved, 7 reader cursors (int64), 7 reader heartbeats (int64 ns) from byte 64,
 # 7 reader device-status words (int64, 0 = healthy) from byte 128
 _HDR = 256
-_SLOT_HDR = 16       # seq (int64), nbytes (int64)
+_SLOT_HDR = 16       # seq (int64), nbytes (int64; bit 40 set: the message continues in the next slot)
+_MORE = 1 << 40
+_CREATED_HERE: set = set()      # segments created by this process
 
 
 class CtrlChannel:
@@ -30,18 +32,20 @@ class CtrlChannel:
         size = _HDR + slots * (slot_bytes + _SLOT_HDR)
         if create:
             self.shm = shared_memory.SharedMemory(name=name, create=True, size=size)
+            _CREATED_HERE.add(name)
             self.shm.buf[:_HDR] = bytes(_HDR)
             for i in range(slots):
                 o = _HDR + i * (slot_bytes + _SLOT_HDR)
                 self.shm.buf[o:o + _SLOT_HDR] = bytes(_SLOT_HDR)
         else:
             self.shm = shared_memory.SharedMemory(name=name, create=False)
-            try:        # the creating process owns the segment; readers must not unlink it at exit
-                from multiprocessing import resource_tracker
+            if name not in _CREATED_HERE:      # (writer and reader in one process share one tracker entry)
+                try:        # the creating process owns the segment; readers must not unlink it at exit
+                    from multiprocessing import resource_tracker
 
-                resource_tracker.unregister(self.shm._name, "shared_memory")
-            except Exception:
-                pass
+                    resource_tracker.unregister(self.shm._name, "shared_memory")
+                except Exception:
+                    pass
         self.owner = create
         self.cursors = np.ndarray((7,), dtype=np.int64, buffer=self.shm.buf, offset=8)
         self.beats = np.ndarray((7,), dtype=np.int64, buffer=self.shm.buf, offset=64)
@@ -57,9 +61,14 @@ class CtrlChannel:
 
     # ------------------------------------------------------------------ writer (rank 0)
     def publish(self, obj, timeout_s: float = 600.0) -> None:
+        """A message larger than a slot (a step plan that carries a large JSON schema, say) travels as several
+        slots in a row; every part but the last has the ``_MORE`` bit set in its length word."""
         data = pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL)
-        if len(data) > self.slot_bytes:
-            raise ValueError(f"control message of {len(data)} bytes exceeds the slot size {self.slot_bytes}")
+        for o in range(0, max(len(data), 1), self.slot_bytes):
+            part = data[o:o + self.slot_bytes]
+            self._publish_part(part, o + len(part) < len(data), timeout_s)
+
+    def _publish_part(self, data: bytes, more: bool, timeout_s: float) -> None:
         nxt = self.seq + 1
         t0 = time.monotonic()
         while self.n_readers and nxt - int(self.cursors[: self.n_readers].min()) > self.slots:
@@ -68,12 +77,20 @@ class CtrlChannel:
             time.sleep(0.0002)
         hdr, off = self._slot(nxt)
         self.shm.buf[off:off + len(data)] = data
-        hdr[1] = len(data)
+        hdr[1] = len(data) | (_MORE if more else 0)
         hdr[0] = nxt          # published last: readers poll this word
         self.seq = nxt
 
     # ------------------------------------------------------------------ readers
     def receive(self, timeout_s: float = 600.0):
+        parts = []
+        while True:
+            data, more = self._receive_part(timeout_s)
+            parts.append(data)
+            if not more:
+                return pickle.loads(parts[0] if len(parts) == 1 else b"".join(parts))
+
+    def _receive_part(self, timeout_s: float):
         nxt = self.seq + 1
         hdr, off = self._slot(nxt)
         t0 = time.monotonic()
@@ -86,12 +103,13 @@ class CtrlChannel:
                     self.beat()          # an idle reader is still alive
                     if time.monotonic() - t0 > timeout_s:
                         raise TimeoutError("no control message from rank 0")
-        n = int(hdr[1])
-        obj = pickle.loads(bytes(self.shm.buf[off:off + n]))
+        word = int(hdr[1])
+        n = word & (_MORE - 1)
+        data = bytes(self.shm.buf[off:off + n])
         self.seq = nxt
         self.cursors[self.reader_index] = nxt
         self.beat()
-        return obj
+        return data, bool(word & _MORE)
 
     # ------------------------------------------------------------------ liveness
     def beat(self) -> None:
