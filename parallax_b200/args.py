@@ -76,7 +76,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--lora-backend", choices=["triton", "csgmv"], default="triton")
     p.add_argument("--max-lora-chunk-size", choices=[16, 32, 64, 128], type=int, default=16)
     p.add_argument("--fully-sharded-loras", action="store_true")
-    p.add_argument("--enable-return-routed-experts", action="store_true")
+    p.add_argument("--enable-return-routed-experts", action="store_true",
+                   help="Return the experts every token was routed to with non-streaming replies (rollout replay; "
+                        "single-process engine, MoE models)")
     # parallelism
     p.add_argument("--tp-size", type=int, default=1, help="Tensor parallel size")
     p.add_argument("--dp-size", type=int, default=1, help="Data parallel size")

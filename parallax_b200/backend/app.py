@@ -188,6 +188,11 @@ def main(argv=None) -> None:
                          weight_refit_mode=a.weight_refit_mode, advertise_addr=adv)
     if a.model_name is not None and a.init_nodes_num is not None:
         sm.run(a.model_name, a.init_nodes_num, a.is_local_network)
+    from parallax_b200.utils.banner import display_parallax_run
+    from parallax_b200.utils.version_check import check_latest_release
+
+    display_parallax_run()
+    check_latest_release()
     uvicorn.run(create_app(sm), host=a.host, port=a.port, log_level="info")
 
 

@@ -194,6 +194,7 @@ class Engine:
         lora: Optional[dict] = None,
         kv_cache_dtype: Optional[str] = None,
         tokenizer=None,
+        return_routed_experts: bool = False,
     ):
         """``tokenizer`` (anything with ``token_text(id)`` and ``eos_token_ids``) is only needed for requests
         with a ``json_schema``: constrained decoding checks candidate tokens by their text."""
@@ -265,6 +266,13 @@ class Engine:
                 st.model.lora = LoRAStack(st.model, int(lora.get("max_loaded") or 4), int(lora.get("max_rank") or 64))
                 stacks.append(st.model.lora)
             self.lora = LoRAManager(stacks, int(lora.get("max_loaded") or 4), lora.get("paths"))
+        # routed-experts record for rollout replay: finished requests carry `routed_experts`
+        # ([tokens with K/V][MoE layers][top-k]); a model without MoE layers leaves it off
+        self.return_routed_experts = False
+        if return_routed_experts:
+            on = [st.model.enable_routed_capture(nb * page_size) for st in self.stages
+                  if hasattr(st.model, "enable_routed_capture")]
+            self.return_routed_experts = any(on)
         self.wire_hook = wire_hook  # optional transform applied to hidden states between stages
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(seed + 12345)
@@ -394,7 +402,25 @@ class Engine:
         return code
 
     # ------------------------------------------------------------------ one step
+    def _routed_experts(self, req: Request):
+        """The request's routing record, read by the KV slots of its tokens (one device-to-host copy at the
+        end of the request): ``[tokens][MoE layers of all stages][top-k]``."""
+        rid = req.request_id
+        if not self.cache.has_request(rid):
+            return None
+        n = min(self.cache.get_context_length(rid), req.prompt_len + max(len(req.output_ids) - 1, 0))
+        table = self.cache.get_block_table(rid)
+        if n <= 0 or not table:
+            return None
+        ps = self.page_size
+        slots = (torch.tensor(table, dtype=torch.int64).view(-1, 1) * ps + torch.arange(ps).view(1, -1)).flatten()[:n]
+        slots = slots.to(self.device)
+        parts = [st.model.routed_experts_of(slots) for st in self.stages if getattr(st.model, "routed_buf", None) is not None]
+        return torch.cat(parts, dim=1).cpu().tolist()
+
     def _release(self, req: Request) -> None:
+        if self.return_routed_experts and req.is_finished and getattr(req, "routed_experts", None) is None:
+            req.routed_experts = self._routed_experts(req)
         self.cache.free_request(req.request_id)
         if self.lora is not None and getattr(req, "lora_slot", -1) >= 0:
             self.lora.release(req.lora_path)

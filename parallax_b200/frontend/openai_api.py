@@ -240,6 +240,10 @@ def create_app(loop: EngineLoop, tokenizer: TokenizerWrapper, model_name: str, m
                "choices": [choice], "usage": usage()}
         if req.return_probs:
             out["choices"][0]["token_probs"] = req.output_probs
+        if getattr(req, "routed_experts", None) is not None:
+            # engines started with --enable-return-routed-experts: [token][MoE layer][top-k] expert ids of
+            # every token that was fed to the model (prompt and all generated tokens but the last)
+            out["choices"][0]["routed_experts"] = req.routed_experts
         return JSONResponse(out)
 
     @app.post("/v1/chat/completions")

@@ -73,7 +73,8 @@ def build_engine(args, cfg, loader, start: int, end: int, shared_state=None):
                   max_total_length=args.max_sequence_length, request_timeout_s=args.request_timeout_s,
                   weights=weights, shared_state=shared_state,
                   num_blocks=None if device != "cpu" else 1024, lora=_lora_spec(args),
-                  kv_cache_dtype=getattr(args, "kv_cache_dtype", None))
+                  kv_cache_dtype=getattr(args, "kv_cache_dtype", None),
+                  return_routed_experts=bool(getattr(args, "enable_return_routed_experts", False)))
 
 
 def _lora_spec(args):
@@ -177,6 +178,9 @@ def run_scheduler_mode(args) -> None:
             agent.on_refit = runtime.apply_refit
             state.update(_layer_allocation_changed=False)
             state.set_status("available")
+            from parallax_b200.utils.banner import display_parallax_join
+
+            display_parallax_join(info["model_name"], info["block_start_index"], info["block_end_index"])
             runtime.serve_until_allocation_changes()
             runtime.shutdown()
             logger.info("layer allocation changed; reloading the executor")
@@ -191,6 +195,9 @@ def main(argv=None) -> None:
     set_log_level("DEBUG" if args.verbose else args.log_level)
     os.environ.setdefault("TOKENIZERS_PARALLELISM", "false")
     if args.scheduler_addr:
+        from parallax_b200.utils.version_check import check_latest_release
+
+        check_latest_release()
         run_scheduler_mode(args)
     else:
         run_standalone(args)

@@ -31,6 +31,7 @@ logger = logging.getLogger(__name__)
 
 _KEY = re.compile(r"^(?:base_model\.model\.)?(?:model\.)?layers\.(\d+)\.(?:self_attn|mlp)\.(\w+)\.lora_([AB])"
                   r"(?:\.default)?\.weight$")
+_KEY_MLX = re.compile(r"^(?:model\.)?(?:language_model\.)?(?:model\.)?layers\.(\d+)\.(?:self_attn|mlp)\.(\w+)\.lora_([ab])$")
 TARGETS = ("q_proj", "k_proj", "v_proj", "o_proj", "down_proj")
 
 
@@ -46,14 +47,29 @@ class LoRAAdapter:
 
         p = Path(path)
         cfg = json.loads((p / "adapter_config.json").read_text()) if (p / "adapter_config.json").exists() else {}
-        rank = int(cfg.get("r") or cfg.get("lora_rank") or 8)
-        scaling = float(cfg.get("lora_alpha", rank)) / rank
-        raw = load_file(str(p / "adapter_model.safetensors" if p.is_dir() else p))
-        halves: dict = {}
-        for k, v in raw.items():
-            m = _KEY.match(k)
-            if m and m.group(2) in TARGETS + ("gate_proj", "up_proj"):
-                halves.setdefault((int(m.group(1)), m.group(2)), {})[m.group(3)] = v
+        mlx_file = p / "adapters.safetensors" if p.is_dir() else None
+        if mlx_file is not None and mlx_file.exists() and not (p / "adapter_model.safetensors").exists():
+            # the layout adapters are converted to for the reference's own backend
+            # (src/parallax_utils/prepare_adapter.py): one file, ``...q_proj.lora_a [in, r]`` / ``lora_b [r, out]``,
+            # ``lora_parameters: {rank, scale}`` with the scale applied as it stands
+            lp = cfg.get("lora_parameters") or {}
+            rank = int(lp.get("rank") or cfg.get("r") or 8)
+            scaling = float(lp["scale"]) if "scale" in lp else float(cfg.get("lora_alpha", rank)) / rank
+            raw = load_file(str(mlx_file))
+            halves = {}
+            for k, v in raw.items():
+                m = _KEY_MLX.match(k)
+                if m and m.group(2) in TARGETS + ("gate_proj", "up_proj"):
+                    halves.setdefault((int(m.group(1)), m.group(2)), {})[m.group(3).upper()] = v.t().contiguous()
+        else:
+            rank = int(cfg.get("r") or cfg.get("lora_rank") or 8)
+            scaling = float(cfg.get("lora_alpha", rank)) / rank
+            raw = load_file(str(p / "adapter_model.safetensors" if p.is_dir() else p))
+            halves = {}
+            for k, v in raw.items():
+                m = _KEY.match(k)
+                if m and m.group(2) in TARGETS + ("gate_proj", "up_proj"):
+                    halves.setdefault((int(m.group(1)), m.group(2)), {})[m.group(3)] = v
         unsupported = sorted({mod for (_l, mod) in halves if mod not in TARGETS})
         if unsupported:
             raise ValueError(f"adapter {path}: per-request serving covers {TARGETS}; it also has {unsupported} "

@@ -105,6 +105,8 @@ class DecoderStage(ExpertParallelMixin):
         self.dense_act_mode = 1 if (cfg.swiglu_limit or cfg.hidden_act == "swigluoai") else 0
         self.dense_limit = float(cfg.swiglu_limit or 7.0)
         self.lora = None        # parallax_b200.loader.lora.LoRAStack when per-request adapters are enabled
+        self.routed_buf = None  # [kv slots, MoE layers, top-k] int16 when routed experts are recorded
+        self._route_slots = None
 
     # ------------------------------------------------------------------ weights
     def num_local_layers(self) -> int:
@@ -288,7 +290,41 @@ class DecoderStage(ExpertParallelMixin):
                 self.lm_head = self.embed
         if replaced and self._native:
             self._native = None            # rebuilt on the next step with the new pointers
+        if self.routed_buf is not None:
+            self._install_route_capture()
         return sum(by_layer.values()) + (n_global if glob is not None else 0)
+
+    # ------------------------------------------------------------------ routed-experts record
+    def enable_routed_capture(self, num_kv_slots: int) -> bool:
+        """Record which experts every token was routed to, per KV slot (the slot a token's K/V is written to
+        names the token for as long as its request lives, prefix-cache hits included): ``routed_buf[slot, j]``
+        holds the top-k expert ids of this stage's j-th MoE layer. The reference exposes the same record for
+        rollout replay in RL training behind ``--enable-return-routed-experts``
+        (``src/parallax/server/executor/vllm_executor.py:480-584``). Returns False for a stage without MoE layers."""
+        n_moe = sum(1 for lw in self.layers if getattr(lw, "moe", None) is not None)
+        if n_moe == 0:
+            return False
+        self.routed_buf = torch.full((num_kv_slots + 1, n_moe, self.cfg.num_experts_per_tok), -1, dtype=torch.int16,
+                                     device=self.device)
+        self._install_route_capture()
+        return True
+
+    def _install_route_capture(self) -> None:
+        j = 0
+        for lw in self.layers:
+            if getattr(lw, "moe", None) is not None:
+                lw.moe.capture = (lambda ids, j=j: self._record_route(j, ids))
+                j += 1
+
+    def _record_route(self, j: int, ids: torch.Tensor) -> None:
+        slots = self._route_slots
+        if slots is not None and slots.shape[0] == ids.shape[0]:
+            # rows without a KV slot (negative) are parked in the last row of the buffer, which no request reads
+            self.routed_buf[torch.where(slots < 0, self.routed_buf.shape[0] - 1, slots), j] = ids.to(torch.int16)
+
+    def routed_experts_of(self, slots: torch.Tensor) -> torch.Tensor:
+        """``[len(slots), MoE layers, top-k]`` for the given KV slots (int64, on this device)."""
+        return self.routed_buf[slots]
 
     def _prepare_shadow(self, shadow) -> None:
         """Hook for subclasses: reset per-stage loader state on the temporary stage that reloads one layer."""
@@ -471,6 +507,8 @@ class DecoderStage(ExpertParallelMixin):
             n_out = self.cfg.vocab_size if self.is_last else self.cfg.hidden_size
             return torch.empty((0, n_out), dtype=self.dtype, device=self.device)
         h = self.embed_tokens(fb) if self.is_first else hidden
+        if self.routed_buf is not None:
+            self._route_slots = fb.slot_mapping
         h = self.forward_layers(h, fb)
         if self.is_last:
             return self.logits(h, fb)

@@ -71,6 +71,7 @@ class MoEWeights:
         # expert parallelism with data-parallel attention: set to the group's exchange object
         # (parallax_b200.parallel.ep.EPComm); the local expert weights then hold `experts_per_rank` experts
         self.ep = None
+        self.capture = None        # callable(ids [T, k]) when the engine records the routed experts
 
     def tensors(self):
         ts = [t for t in (self.router, self.e_bias, self.w1, self.w2, self.shared_gu, self.shared_down,
@@ -239,8 +240,11 @@ class MoEWeights:
     def route(self, xn: torch.Tensor):
         cfg = self.cfg
         logits = ops.linear(xn, self.router, bias=self.router_bias, epi=ops.EPI_F32)
-        return ops.moe_route(logits, self.e_bias, self.top_k, self.mode, cfg.norm_topk_prob, cfg.n_group,
-                             cfg.topk_group, cfg.routed_scaling_factor)
+        ids, w = ops.moe_route(logits, self.e_bias, self.top_k, self.mode, cfg.norm_topk_prob, cfg.n_group,
+                               cfg.topk_group, cfg.routed_scaling_factor)
+        if self.capture is not None:
+            self.capture(ids)          # routed-experts record for rollout replay (see DecoderStage.enable_routed_capture)
+        return ids, w
 
     def forward(self, xn: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
         """Returns ``h + MoE(xn)`` (the residual add is fused into the combine / shared-expert GEMM)."""

@@ -180,3 +180,27 @@ def test_per_request_adapters_across_ranks(model, pp, tp, ep, tmp_path):
     # the adapters really change the output of their requests
     base = Engine(cfg, device="cpu", **kw).generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0, ignore_eos=True))
     assert got[2] == base[2] and (got[0] != base[0] or got[1] != base[1])
+
+
+def test_adapter_preparation_and_both_layouts(tmp_path):
+    """An adapter prepared for either layout loads to the same matrices and scale, and the completed config
+    carries the fields of both."""
+    from parallax_b200.utils.prepare_adapter import main as prepare_main, prepare_adapter
+
+    cfg = named_config("tiny")
+    src = _make_adapter(cfg, tmp_path / "peft", 5, rank=4, alpha=8)
+    (tmp_path / "base").mkdir()
+    (tmp_path / "base" / "config.json").write_text(json.dumps({"num_hidden_layers": cfg.num_hidden_layers}))
+    mlx = prepare_adapter(src, str(tmp_path / "mlx"), base=str(tmp_path / "base"), layout="mlx", dtype="float32")
+    c = json.loads((mlx / "adapter_config.json").read_text())
+    assert c["fine_tune_type"] == "lora" and c["num_layers"] == cfg.num_hidden_layers
+    assert c["lora_parameters"] == {"rank": 4, "scale": 2.0, "dropout": 0.0} and c["r"] == 4 and c["lora_alpha"] == 8
+    assert (mlx / "adapters.safetensors").exists() and not (mlx / "adapter_model.safetensors").exists()
+    a, b = LoRAAdapter.load(src), LoRAAdapter.load(str(mlx))
+    assert a.rank == b.rank == 4 and a.scaling == b.scaling == 2.0 and set(a.tensors) == set(b.tensors)
+    for k in a.tensors:
+        assert torch.equal(a.tensors[k][0], b.tensors[k][0]) and torch.equal(a.tensors[k][1], b.tensors[k][1])
+    # and back, through the command
+    prepare_main([str(mlx), "--out", str(tmp_path / "back"), "--layout", "peft", "--dtype", "float32"])
+    c2 = LoRAAdapter.load(str(tmp_path / "back"))
+    assert c2.scaling == 2.0 and all(torch.equal(a.tensors[k][1], c2.tensors[k][1]) for k in a.tensors)
