@@ -11,6 +11,7 @@ from parallax_b200.cache.kv_pool import KVPool, bytes_per_block
 from parallax_b200.engine.batch import ForwardBatch
 from parallax_b200.models.config import ModelConfig
 from parallax_b200.models.registry import build_stage
+from parallax_b200.utils.trace import nvtx_enabled, nvtx_range
 
 logger = logging.getLogger(__name__)
 
@@ -80,4 +81,8 @@ class StageWorker:
 
     @torch.inference_mode()
     def run(self, fb: ForwardBatch, hidden: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if nvtx_enabled():
+            m = self.model
+            with nvtx_range(f"stage [{m.start_layer},{m.end_layer}) T={fb.num_tokens}"):
+                return m.forward(fb, hidden)
         return self.model.forward(fb, hidden)

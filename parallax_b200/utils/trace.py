@@ -4,6 +4,9 @@
 The reference has no tracing or profiling hooks (only an EWMA of per-layer latency,
 ``src/parallax/server/executor/base_executor.py:711-732``). Enabled with ``Engine(..., trace=...)``
 or the ``PXL_TRACE=<file>`` environment variable; costs two CUDA events per step.
+
+``PXL_NVTX=1`` additionally wraps every stage forward and engine step in an NVTX range (:func:`nvtx_range`),
+so that a timeline tool shows the steps by name; off, the helper is a no-op without any call into CUDA.
 """
 
 from __future__ import annotations
@@ -12,6 +15,54 @@ import json
 import os
 import time
 from typing import Optional
+
+
+_NVTX: Optional[bool] = None
+
+
+class _NoRange:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+_NO_RANGE = _NoRange()
+
+
+class _NvtxRange:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        import torch
+
+        torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *a):
+        import torch
+
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
+def nvtx_enabled() -> bool:
+    global _NVTX
+    if _NVTX is None:
+        on = os.environ.get("PXL_NVTX", "") not in ("", "0")
+        if on:
+            import torch
+
+            on = torch.cuda.is_available()
+        _NVTX = on
+    return _NVTX
+
+
+def nvtx_range(name: str):
+    """``with nvtx_range("stage 0 [0,18) T=512"): ...``"""
+    return _NvtxRange(name) if nvtx_enabled() else _NO_RANGE
 
 
 class StepTracer:

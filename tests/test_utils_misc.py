@@ -43,3 +43,19 @@ def test_banners_are_plain_text_off_a_terminal(capsys):
     banner.display_parallax_run()                # stdout is captured, not a terminal: nothing is printed
     banner.display_parallax_join("m")
     assert capsys.readouterr().out == ""
+
+
+def test_nvtx_ranges_are_a_no_op_when_off(monkeypatch):
+    from parallax_b200.utils import trace
+
+    monkeypatch.setattr(trace, "_NVTX", None)
+    monkeypatch.delenv("PXL_NVTX", raising=False)
+    assert not trace.nvtx_enabled()
+    with trace.nvtx_range("x") as r:
+        assert r is trace._NO_RANGE
+    monkeypatch.setattr(trace, "_NVTX", None)
+    monkeypatch.setenv("PXL_NVTX", "1")
+    import torch
+
+    assert trace.nvtx_enabled() == torch.cuda.is_available()
+    monkeypatch.setattr(trace, "_NVTX", None)
