@@ -3,7 +3,8 @@
 The layout comes as a string: ``pp<P>``, ``tp<T>`` (fused tensor-parallel kernels for the GQA decoder; heads split over library collectives
 for ``@small-mla`` / ``@small-dsa`` / ``@small-hybrid`` / ``@small-msa``), ``dpep<E>`` (expert
 parallelism with data-parallel attention) and combinations such as ``pp2tp2`` or ``pp2dpep2``; ``ep2``
-is attention tensor-parallel with the experts sharded over the same two ranks. Rank 0 runs the same
+is attention tensor-parallel with the experts sharded over the same two ranks. ``#fp8kv`` stores K/V pages as
+e4m3, ``%lora`` gives four of the six requests one of two LoRA adapters. Rank 0 runs the same
 prompts through a single-GPU engine on its own GPU afterwards and compares:
 
 * the generated tokens, margin-aware: a request is compared up to (not including) its first step at
@@ -40,12 +41,37 @@ def parse_layout(mode: str):
     return pp, tp, dpep, moe
 
 
+def _write_adapters(cfg, adir: str) -> None:
+    """Two PEFT-format adapters (rank 4 and 8) on q/k/v/o/down of every layer, small enough not to swamp the model."""
+    from safetensors.torch import save_file
+
+    D, Hq, Hkv, H, I = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.hidden_size, cfg.intermediate_size
+    dims = {"self_attn.q_proj": (H, Hq * D), "self_attn.k_proj": (H, Hkv * D), "self_attn.v_proj": (H, Hkv * D),
+            "self_attn.o_proj": (Hq * D, H)}
+    if not cfg.is_moe:
+        dims["mlp.down_proj"] = (I, H)
+    for seed, (name, r) in enumerate((("x", 4), ("y", 8))):
+        g = torch.Generator().manual_seed(100 + seed)
+        t = {}
+        for li in range(cfg.num_hidden_layers):
+            for mod, (n_in, n_out) in dims.items():
+                base = f"base_model.model.model.layers.{li}.{mod}"
+                t[base + ".lora_A.weight"] = torch.randn(r, n_in, generator=g) * 0.03
+                t[base + ".lora_B.weight"] = torch.randn(n_out, r, generator=g) * 0.03
+        os.makedirs(os.path.join(adir, name), exist_ok=True)
+        save_file(t, os.path.join(adir, name, "adapter_model.safetensors"))
+        with open(os.path.join(adir, name, "adapter_config.json"), "w") as f:
+            json.dump({"r": r, "lora_alpha": 2 * r}, f)
+
+
 def main() -> None:
     import faulthandler
 
     faulthandler.dump_traceback_later(150, exit=True)   # a stuck rank shows where and ends itself
     mode, out_path = sys.argv[1], sys.argv[2]
     # "<layout>@<named config>" picks another model family, "<layout>#fp8kv" an e4m3 KV cache (on both engines)
+    # "<layout>%lora": two of the requests use a LoRA adapter each (on both engines)
+    mode, _, lora_flag = mode.partition("%")
     mode, _, kv_flag = mode.partition("#")
     mode, _, model = mode.partition("@")
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -63,6 +89,13 @@ def main() -> None:
               max_total_length=2048, seed=0)
     if kv_flag == "fp8kv":
         kw["kv_cache_dtype"] = "fp8_e4m3"
+    lora_of = [None] * 6
+    if lora_flag == "lora":
+        adir = os.path.join(os.path.dirname(out_path), "adapters")
+        kw["lora"] = {"max_loaded": 2, "max_rank": 8, "paths": {"x": os.path.join(adir, "x"), "y": os.path.join(adir, "y")}}
+        lora_of = ["x", None, "y", "x", None, "y"]
+        if rank == 0:
+            _write_adapters(cfg, adir)       # the other ranks read them when the load arrives with a step plan
     eng = DistEngine(cfg, pp, tp, dev, torch.bfloat16, ep=dpep, **kw)
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (37, 300, 5, 129, 64, 700)]
@@ -71,8 +104,8 @@ def main() -> None:
         eng.serve_forever()
     else:
         eng.keep_logits = True
-        reqs = [Request(input_ids=p, sampling_params=SamplingParams.from_dict(sp.to_dict()), max_total_length=2048)
-                for p in prompts]
+        reqs = [Request(input_ids=p, sampling_params=SamplingParams.from_dict(sp.to_dict()), max_total_length=2048,
+                        lora_path=a) for p, a in zip(prompts, lora_of)]
         for r in reqs:
             eng.add_request(r)
         eng.step()
@@ -85,8 +118,8 @@ def main() -> None:
         # step by step, so that the logits of a step and the tokens it returns belong together
         ref = Engine(cfg, device=dev, dtype=torch.bfloat16, async_scheduling=False, **kw)
         ref.keep_logits = True
-        rreqs = [Request(input_ids=p, sampling_params=SamplingParams.from_dict(sp.to_dict()), max_total_length=2048)
-                 for p in prompts]
+        rreqs = [Request(input_ids=p, sampling_params=SamplingParams.from_dict(sp.to_dict()), max_total_length=2048,
+                         lora_path=a) for p, a in zip(prompts, lora_of)]
         for r in rreqs:
             ref.add_request(r)
         gaps = {r.request_id: [] for r in rreqs}       # per request: top-2 logit gap of every generated token

@@ -206,3 +206,38 @@ def test_long_context_chunked_prefill_32k():
     if float(top2[0, 0] - top2[0, 1]) > 4 * float((lg_four - lg_one).abs().max()):
         assert four[0] == one[0]
     assert len(four) == len(one) == 6
+
+
+def test_constrained_decoding_on_gpu():
+    """JSON-schema requests on the GPU engine (lookahead on): valid documents that end by themselves, next to an
+    unconstrained request whose tokens are what they are without the neighbours."""
+    import json
+
+    from parallax_b200.engine.structured import JsonSchemaMatcher
+    from parallax_b200.frontend.tokenizer import TokenizerWrapper
+
+    cfg = _cfg()
+    tok = TokenizerWrapper(None, vocab_size=cfg.vocab_size)
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}, "n": {"type": "integer"}}, "required": ["ok", "n"]}
+    kw = dict(device="cuda:0", dtype=torch.bfloat16, num_blocks=128, page_size=16, max_batch_size=8, seed=0)
+    eng = Engine(cfg, tokenizer=tok, **kw)
+    free_sp = SamplingParams(max_new_tokens=10, temperature=0.0, ignore_eos=True)
+    p = _prompts(3, 24, 250, seed=2)
+    reqs = [Request(input_ids=p[0], sampling_params=SamplingParams(max_new_tokens=150, temperature=0.0,
+                                                                   json_schema=json.dumps(schema))),
+            Request(input_ids=p[1], sampling_params=SamplingParams(max_new_tokens=150, temperature=0.8,
+                                                                   json_schema=json.dumps(schema))),
+            Request(input_ids=p[2], sampling_params=free_sp)]
+    for r in reqs:
+        eng.add_request(r)
+    while eng.has_work():
+        eng.step()
+    for r in reqs[:2]:
+        text = tok.decode(r.output_ids)
+        m = JsonSchemaMatcher(schema)
+        assert m.advance(text) and m.done, text
+        assert set(json.loads(text)) >= {"ok", "n"} and r.status.name == "FINISHED_EOS" and len(r.output_ids) < 150
+    assert len(reqs[2].output_ids) == 10
+    from parallax_b200.ops import cuda as cu
+
+    cu.check_status(torch.device("cuda:0"))

@@ -120,3 +120,46 @@ def test_moe_ffn_swigluoai_with_expert_biases(cu):
                        limit=7.0, b1=b1.cpu().float(), b2=b2.cpu().float())
     cu.check_status(torch.device(DEV))
     assert _rel(got.cpu(), want) < 1e-2
+
+
+def test_routed_experts_record_on_gpu():
+    """The per-slot routing record with the lookahead engine on the GPU: complete for every token that has K/V,
+    equal to the step-by-step engine's, and unchanged by prompt slicing."""
+    from parallax_b200.engine.engine import Engine
+    from parallax_b200.engine.request import Request, SamplingParams
+    from parallax_b200.models.config import config_from_hf
+
+    cfg = config_from_hf(dict(architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", hidden_size=512,
+                              num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+                              intermediate_size=1024, moe_intermediate_size=256, num_experts=16,
+                              num_experts_per_tok=4, norm_topk_prob=True, vocab_size=2048, rope_theta=1e4))
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (70, 9, 33)]
+
+    def run(**kw):
+        eng = Engine(cfg, device=DEV, dtype=torch.bfloat16, num_blocks=64, max_batch_size=8, seed=0,
+                     enable_prefix_cache=False, return_routed_experts=True, **kw)
+        reqs = [Request(input_ids=p, sampling_params=SamplingParams(max_new_tokens=5, temperature=0.0, ignore_eos=True))
+                for p in prompts]
+        for r in reqs:
+            eng.add_request(r)
+        while eng.has_work():
+            eng.step()
+        return reqs
+
+    a = run()
+    for r in a:
+        rec = torch.tensor(r.routed_experts)
+        assert rec.shape == (r.prompt_len + len(r.output_ids) - 1, 2, 4)
+        assert int(rec.min()) >= 0 and int(rec.max()) < 16
+    b = run(async_scheduling=False)
+    c = run(chunked_prefill_size=32)
+    same_b = sum(x.routed_experts == y.routed_experts for x, y in zip(a, b))
+    assert same_b == len(a)                      # same kernels on the same rows
+    for x, y in zip(a, c):
+        # other row counts per step change the GEMM tiles: a router logit near a tie may flip, most do not
+        rx, ry = torch.tensor(x.routed_experts)[:x.prompt_len], torch.tensor(y.routed_experts)[:y.prompt_len]
+        assert (rx.sort(-1).values == ry.sort(-1).values).float().mean() > 0.97
+    from parallax_b200.ops import cuda as cu
+
+    cu.check_status(torch.device(DEV))

@@ -48,7 +48,9 @@ LAYOUTS = [("tp2", 2), ("pp2", 2), ("ep2", 2), ("dpep2", 2),
            # tensor-parallel stages of the other families (heads split, sequence-sharded residual stream)
            ("tp2@small-mla", 2), ("tp2@small-dsa", 2), ("tp2@small-hybrid", 2), ("tp2@small-msa", 2),
            # e4m3 KV pages under pipeline and tensor parallelism
-           ("pp2#fp8kv", 2), ("tp2#fp8kv", 2)]
+           ("pp2#fp8kv", 2), ("tp2#fp8kv", 2),
+           # per-request LoRA adapters on tensor-parallel ranks (sliced adapters) and on pipeline stages
+           ("tp2%lora", 2), ("pp2%lora", 2)]
 
 
 @pytest.mark.parametrize("mode,n", LAYOUTS)
