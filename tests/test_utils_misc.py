@@ -59,3 +59,13 @@ def test_nvtx_ranges_are_a_no_op_when_off(monkeypatch):
 
     assert trace.nvtx_enabled() == torch.cuda.is_available()
     monkeypatch.setattr(trace, "_NVTX", None)
+
+
+def test_offline_generation_reports_prefill_and_decode_steps():
+    from parallax_b200.generate import percentile, run
+
+    lines = []
+    res = run("tiny", "Hello there", max_tokens=5, random_init=True, device="cpu", out=lines.append)
+    assert res["generated_tokens"] == 5 and len(res["decode_ms"]) == 4 and res["prompt_tps"] > 0
+    assert any(l.startswith("Prefill:") for l in lines) and any(l.startswith("Decode step time (ms): min=") for l in lines)
+    assert percentile([1, 2, 3, 4], 50) == 2.5 and percentile([5], 99) == 5
