@@ -115,6 +115,9 @@ def run_standalone(args) -> None:
 
         run_multi_gpu(args, cfg, name, path)
         return
+    if (start, end) != (0, cfg.num_hidden_layers):
+        run_static_peer(args, state, name, start, end)
+        return
     engine = build_engine(args, cfg, loader, start, end, state)
     tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size)
     engine.tokenizer = tok           # requests with a JSON schema check candidate tokens by their text
@@ -141,6 +144,29 @@ def run_standalone(args) -> None:
     finally:
         server.should_exit = True
         loop.stop()
+
+
+def run_static_peer(args, state: SharedState, name: str, start: int, end: int) -> None:
+    """``parallax serve --start-layer a --end-layer b --initial-peers <other nodes>``: one stage of a pipeline
+    whose nodes find each other without a scheduler (the first node serves the API and routes by layer range)."""
+    from parallax_b200.p2p.node_runtime import NodeRuntime
+    from parallax_b200.p2p.static_peers import StaticAgent, StaticPeers
+
+    host = "127.0.0.1" if args.host in ("localhost", "0.0.0.0") else args.host
+    url = args.announce_maddrs[0] if args.announce_maddrs else f"http://{host}:{args.port}"
+    if "://" not in url:
+        url = "http://" + url
+    peers = StaticPeers(f"{host}:{args.port}", url, start, end, list(args.initial_peers or []))
+    runtime = NodeRuntime(args, StaticAgent(peers), state, name, start, end)
+    state.set_status("available")
+    logger.info("serving layers [%d, %d) of %s on %s; peers: %s", start, end, name, url, peers.seeds or "none yet")
+    try:
+        while runtime.thread.is_alive():
+            time.sleep(0.5)
+    except KeyboardInterrupt:
+        pass
+    finally:
+        runtime.shutdown()
 
 
 def wait_for_allocation(state: SharedState, timeout_s: float = 300.0, poll_s: float = 0.2) -> Optional[dict]:

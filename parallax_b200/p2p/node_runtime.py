@@ -42,12 +42,18 @@ class PeerLoop:
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self.steps = 0
+        self.default_route = None       # callable -> routing table for requests that arrive without one
 
     # ---- frontend side
     def submit(self, req: Request):
         q: "queue.Queue[TokenEvent]" = queue.Queue()
         with self._lock:
             self._streams[req.request_id] = q
+        if not req.routing_table and self.default_route is not None:
+            table = self.default_route()       # no scheduler: peers chained by their layer ranges
+            if table is None:
+                raise RuntimeError("no chain of peers covers every layer yet; start the missing nodes")
+            req.routing_table = list(table)
         if not req.routing_table:
             req.routing_table = [self.peer.node_id]
         self._inbox.put(("add", req))
@@ -237,6 +243,16 @@ class NodeRuntime:
         async def set_peers(req: HttpRequest):
             self.peer_urls.update(await req.json())
             return {"ok": True}
+
+        static = getattr(agent, "peers", None)
+        if static is not None:
+            # no scheduler: this node tells others who it is, and the first node routes by layer range
+            @self.app.get("/peer/info")
+            async def peer_info():
+                return static.describe()
+
+            if self.peer.is_first:
+                self.loop.default_route = lambda: static.route(cfg.num_hidden_layers)
 
         self.loop.start()
         self.server, self.thread = serve_http(self.app, args.host, args.port, args.log_level)

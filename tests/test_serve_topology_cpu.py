@@ -62,3 +62,61 @@ def test_serve_with_in_box_topology(model, topo, tmp_path):
             except subprocess.TimeoutExpired:
                 os.killpg(proc.pid, signal.SIGKILL)
         log.close()
+
+
+def test_two_nodes_with_manual_layer_ranges_and_no_scheduler(tmp_path):
+    """`parallax serve --start-layer/--end-layer --initial-peers`: two processes, each with half of the layers,
+    find each other over HTTP; the first one serves the API. Same reply as one process with all layers."""
+    from parallax_b200.p2p.static_peers import StaticPeers
+
+    p0, p1, p2 = free_port(), free_port(), free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    common = [sys.executable, "-m", "parallax_b200.launch", "--model-path", "tiny", "--random-init", "--host", "127.0.0.1",
+              "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING"]
+    logs = [open(tmp_path / f"n{i}.log", "w") for i in range(3)]
+    procs = [
+        subprocess.Popen(common + ["--port", str(p0), "--start-layer", "0", "--end-layer", "2", "--initial-peers",
+                                   f"127.0.0.1:{p1}"], cwd=ROOT, env=env, stdout=logs[0], stderr=subprocess.STDOUT),
+        subprocess.Popen(common + ["--port", str(p1), "--start-layer", "2", "--end-layer", "4", "--initial-peers",
+                                   f"http://127.0.0.1:{p0}"], cwd=ROOT, env=env, stdout=logs[1], stderr=subprocess.STDOUT),
+        subprocess.Popen(common + ["--port", str(p2)], cwd=ROOT, env=env, stdout=logs[2], stderr=subprocess.STDOUT),
+    ]
+    try:
+        for port, path in ((p0, "/v1/models"), (p1, "/peer/info"), (p2, "/v1/models")):
+            deadline = time.time() + 120
+            up = False
+            while time.time() < deadline and all(p.poll() is None for p in procs):
+                try:
+                    with urllib.request.urlopen(f"http://127.0.0.1:{port}{path}", timeout=2) as r:
+                        up = r.status == 200
+                        break
+                except OSError:
+                    time.sleep(0.5)
+            assert up, "".join(open(tmp_path / f"n{i}.log").read()[-1500:] for i in range(3))
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 8, "temperature": 0}
+        split = _post(p0, body)
+        whole = _post(p2, body)
+        assert split["usage"]["completion_tokens"] == whole["usage"]["completion_tokens"] >= 1
+        assert split["choices"][0]["message"]["content"] == whole["choices"][0]["message"]["content"]
+        with urllib.request.urlopen(f"http://127.0.0.1:{p1}/peer/info", timeout=5) as r:
+            info = json.loads(r.read())
+        assert (info["start_layer"], info["end_layer"]) == (2, 4) and f"http://127.0.0.1:{p0}" in info["peers"]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.terminate()
+        for p in procs:
+            try:
+                p.wait(15)
+            except subprocess.TimeoutExpired:
+                p.kill()
+        for f in logs:
+            f.close()
+
+    # the chain is found through peers of peers, and a gap is reported as "no route yet"
+    net = {"http://a/peer/info": {"node_id": "a", "url": "http://a", "start_layer": 0, "end_layer": 3, "peers": ["http://b"]},
+           "http://b/peer/info": {"node_id": "b", "url": "http://b", "start_layer": 3, "end_layer": 5, "peers": ["http://c"]},
+           "http://c/peer/info": {"node_id": "c", "url": "http://c", "start_layer": 5, "end_layer": 8, "peers": []}}
+    me = StaticPeers("a", "http://a", 0, 3, ["http://b"], http_get=lambda u: net[u])
+    assert me.route(8) == ["a", "b", "c"] and me.node_addresses()["c"] == "http://c"
+    assert me.route(9) is None
