@@ -148,6 +148,54 @@ __global__ void sigmoid_gate_mul_kernel(const bf16* __restrict__ x, int64_t ldx,
   }
 }
 
+// out = (res +) x * sigmoid(gate[:, col / group]): one gate value per `group` consecutive columns (a head of the
+// attention output, or a whole row for the shared expert's scalar gate); group is a multiple of 8
+__global__ void gate_mul_grouped_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restrict__ gate,
+                                        int64_t ldg, const bf16* __restrict__ res, int64_t ldr,
+                                        bf16* __restrict__ out, int64_t ldo, int n8, int group8) {
+  const int t = blockIdx.x;
+  for (int v = threadIdx.x; v < n8; v += blockDim.x) {
+    const float g = __bfloat162float(gate[t * ldg + v / group8]);
+    const float s = 1.f / (1.f + __expf(-g));
+    const bf16x8 a = ld_bf16x8(x + t * ldx + v * 8);
+    bf16x8 r;
+    if (res != nullptr) r = ld_bf16x8(res + t * ldr + v * 8);
+    bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 av = unpack_bf16x2(a.u[j]);
+      float2 ov = make_float2(av.x * s, av.y * s);
+      if (res != nullptr) {
+        const float2 rv = unpack_bf16x2(r.u[j]);
+        ov.x += rv.x;
+        ov.y += rv.y;
+      }
+      o.u[j] = pack_bf16x2(ov.x, ov.y);
+    }
+    st_bf16x8(out + t * ldo + v * 8, o);
+  }
+}
+
+// out[t] = x[t, :] . w  (one warp per row; the one-column projection of a scalar gate is too thin for a GEMM tile)
+__global__ void row_dot_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restrict__ w,
+                               bf16* __restrict__ out, int T, int k8) {
+  const int t = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  if (t >= T) return;
+  const int lane = threadIdx.x % 32;
+  float acc = 0.f;
+  for (int v = lane; v < k8; v += 32) {
+    const bf16x8 a = ld_bf16x8(x + t * ldx + v * 8), b = ld_bf16x8(w + v * 8);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 av = unpack_bf16x2(a.u[j]), bv = unpack_bf16x2(b.u[j]);
+      acc += av.x * bv.x + av.y * bv.y;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) out[t] = __float2bfloat16(acc);
+}
+
 }  // namespace
 
 PXL_EXPORT int pxl_causal_conv1d_silu(const void* x, int64_t ldx, const void* w, const void* bias, void* conv_state,
@@ -184,5 +232,26 @@ PXL_EXPORT int pxl_sigmoid_gate_mul(const void* x, int64_t ldx, const void* gate
   sigmoid_gate_mul_kernel<<<T, 128, 0, stream>>>(static_cast<const pxl::bf16*>(x), ldx,
                                                  static_cast<const pxl::bf16*>(gate), ldg,
                                                  static_cast<pxl::bf16*>(out), ldo, N / 8);
+  return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
+}
+
+PXL_EXPORT int pxl_gate_mul_grouped(const void* x, int64_t ldx, const void* gate, int64_t ldg, const void* res,
+                                    int64_t ldr, void* out, int64_t ldo, int T, int N, int group,
+                                    cudaStream_t stream) {
+  if (T <= 0) return PXL_OK;
+  if (N % 8 || group <= 0 || group % 8 || N % group) return PXL_ERR_INVALID_ARG;
+  gate_mul_grouped_kernel<<<T, 128, 0, stream>>>(static_cast<const pxl::bf16*>(x), ldx,
+                                                 static_cast<const pxl::bf16*>(gate), ldg,
+                                                 static_cast<const pxl::bf16*>(res), ldr,
+                                                 static_cast<pxl::bf16*>(out), ldo, N / 8, group / 8);
+  return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
+}
+
+PXL_EXPORT int pxl_row_dot(const void* x, int64_t ldx, const void* w, void* out, int T, int K, cudaStream_t stream) {
+  if (T <= 0) return PXL_OK;
+  if (K % 8) return PXL_ERR_INVALID_ARG;
+  row_dot_kernel<<<pxl::ceil_div(T, 4), 128, 0, stream>>>(static_cast<const pxl::bf16*>(x), ldx,
+                                                          static_cast<const pxl::bf16*>(w),
+                                                          static_cast<pxl::bf16*>(out), T, K / 8);
   return cudaGetLastError() == cudaSuccess ? PXL_OK : PXL_ERR_CUDA;
 }

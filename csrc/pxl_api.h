@@ -279,6 +279,12 @@ int pxl_gated_delta_rule(const void* qkv, int64_t ld_qkv, const void* a, const v
 int pxl_sigmoid_gate_mul(const void* x, int64_t ldx, const void* gate, int64_t ldg, void* out, int64_t ldo,
                          int T, int N, pxl_stream_t stream);
 
+// out = (res +) x * sigmoid(gate[:, col / group]); gate [T, N / group]; res may be null; group % 8 == 0
+int pxl_gate_mul_grouped(const void* x, int64_t ldx, const void* gate, int64_t ldg, const void* res, int64_t ldr,
+                         void* out, int64_t ldo, int T, int N, int group, pxl_stream_t stream);
+// out[t] = x[t, :K] . w[:K] (bf16 out)
+int pxl_row_dot(const void* x, int64_t ldx, const void* w, void* out, int T, int K, pxl_stream_t stream);
+
 // ---- msa.cu: block-sparse attention indexer --------------------------------------------------
 // scores[t, j] = max over index heads and visible tokens of 128-token block j of scale * iq . ik
 int pxl_msa_block_scores(const void* iq, const void* index_cache, const int* block_tables, const int* cu_q,

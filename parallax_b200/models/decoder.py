@@ -444,9 +444,8 @@ class DecoderStage(ExpertParallelMixin):
         if fb.num_decode:
             ops.attn_decode(q[Tp:], kc, vc, fb.d_block_tables, fb.d_ctx_lens, self.scale,
                             window=lw.window, sinks=lw.sinks, max_ctx=fb.d_max_ctx, out=attn[Tp:], kv_scale=kvs)
-        if lw.w_g is not None:
-            gate = torch.sigmoid(ops.linear(xn, lw.w_g).float()).to(attn.dtype)      # [T, Hq]
-            attn = attn * gate.unsqueeze(-1)
+        if lw.w_g is not None:      # head-wise gate: every head's output times sigmoid of that head's gate logit
+            return ops.gate_mul_grouped(attn.view(T, Hq * D), ops.linear(xn, lw.w_g), D)
         return attn.view(T, Hq * D)
 
     def _mlp(self, lw: LayerWeights, xn: torch.Tensor, h: torch.Tensor, li: int = 0, fb=None) -> torch.Tensor:

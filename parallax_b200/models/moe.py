@@ -112,8 +112,8 @@ class MoEWeights:
         act = ops.linear(xn, self.shared_gu, epi=ops.EPI_SILU_MUL)
         if self.shared_gate is None:
             return ops.linear(act, self.shared_down, residual=h)
-        gate = torch.sigmoid(xn.float() @ self.shared_gate.float().t()).to(h.dtype)
-        return h + gate * ops.linear(act, self.shared_down)
+        y = ops.linear(act, self.shared_down)
+        return ops.gate_mul_grouped(y, ops.row_dot(xn, self.shared_gate), y.shape[1], residual=h)
 
     def quantize_fp8(self) -> None:
         """Replace the expert (and shared-expert) matrices by e4m3 + scales per 64 x 128 block."""
@@ -263,8 +263,9 @@ class MoEWeights:
             if self.shared_gate is None:
                 base = ops.linear(act, self.shared_down, residual=h)
             else:
-                gate = torch.sigmoid(xn.float() @ self.shared_gate.float().t()).to(h.dtype)  # [T, 1]: too thin for a tile
-                base = h + gate * ops.linear(act, self.shared_down)
+                # scalar gate per token: a [T, H] x [H] row dot (too thin for a GEMM tile), applied with the residual
+                y = ops.linear(act, self.shared_down)
+                base = ops.gate_mul_grouped(y, ops.row_dot(xn, self.shared_gate), y.shape[1], residual=h)
         if self.ep is not None:
             return self.ep.moe_ffn(self, xn, ids, w, base=base)
         if self.act_mode:

@@ -16,7 +16,7 @@ _NAMES = [
     "linear", "rmsnorm", "qk_norm_rope_cache", "reshape_and_cache", "act_mul", "gather_rows",
     "add_inplace", "patch_ids", "attn_decode", "attn_prefill", "argmax", "apply_penalties", "sample", "moe_route", "moe_ffn",
     "mla_kv_prep", "mla_q_absorb", "mla_attn", "mla_unabsorb", "store_rows", "dsa_index_prep", "dsa_index_scores", "topk_select",
-    "quant_fp8_rows", "linear_fp8", "moe_ffn_fp8", "causal_conv1d_silu", "gated_delta_rule", "sigmoid_gate_mul", "msa_block_scores", "msa_select",
+    "quant_fp8_rows", "linear_fp8", "moe_ffn_fp8", "causal_conv1d_silu", "gated_delta_rule", "sigmoid_gate_mul", "gate_mul_grouped", "row_dot", "msa_block_scores", "msa_select",
 ]
 
 

@@ -104,6 +104,8 @@ _SIGS = {
     "pxl_gated_delta_rule": [_P, c_int64, _P, _P, c_int64, _P, _P, _P, c_int64, _P, _P, _P, _P, _P, _P, c_int64,
                              c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "pxl_sigmoid_gate_mul": [_P, c_int64, _P, c_int64, _P, c_int64, c_int, c_int, _P],
+    "pxl_gate_mul_grouped": [_P, c_int64, _P, c_int64, _P, c_int64, _P, c_int64, c_int, c_int, c_int, _P],
+    "pxl_row_dot": [_P, c_int64, _P, _P, c_int, c_int, _P],
     "pxl_msa_block_scores": [_P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_float, _P],
     "pxl_msa_select": [_P, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, _P],

@@ -873,6 +873,33 @@ def sigmoid_gate_mul(x, gate):
     return out
 
 
+def gate_mul_grouped(x, gate, group: int, residual=None):
+    """``(residual +) x * sigmoid(gate)`` with one gate value per ``group`` columns of ``x``."""
+    T, N = x.shape
+    x = x if x.stride(1) == 1 else x.contiguous()
+    gate = gate if gate.stride(-1) == 1 else gate.contiguous()
+    out = torch.empty((T, N), dtype=x.dtype, device=x.device)
+    if residual is not None and residual.stride(1) != 1:
+        residual = residual.contiguous()
+    check(_lib.lib().pxl_gate_mul_grouped(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0),
+                                          _ptr(residual), residual.stride(0) if residual is not None else 0,
+                                          out.data_ptr(), out.stride(0), T, N, int(group), _stream(x.device)),
+          "pxl_gate_mul_grouped")
+    _count()
+    return out
+
+
+def row_dot(x, w):
+    """``x @ w`` for one weight row ``w [K]``: ``[T, 1]``."""
+    T, K = x.shape
+    x = x if x.stride(1) == 1 else x.contiguous()
+    out = torch.empty((T, 1), dtype=x.dtype, device=x.device)
+    check(_lib.lib().pxl_row_dot(x.data_ptr(), x.stride(0), w.contiguous().data_ptr(), out.data_ptr(), T, K,
+                                 _stream(x.device)), "pxl_row_dot")
+    _count()
+    return out
+
+
 # ---------------------------------------------------------------------------- block-sparse indexer (MSA)
 def msa_block_scores(iq, index_cache, block_tables, cu_q, positions, max_ctx: int, sparse_block: int, scale: float):
     T, Hi, Di = iq.shape

@@ -582,6 +582,18 @@ def sigmoid_gate_mul(x, gate):
     return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)
 
 
+def gate_mul_grouped(x, gate, group: int, residual=None):
+    T, N = x.shape
+    y = (x.float().view(T, N // group, group) * torch.sigmoid(gate.float()).view(T, N // group, 1)).view(T, N)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def row_dot(x, w):
+    return (x.float() @ w.float().view(-1, 1)).to(x.dtype)
+
+
 # ---------------------------------------------------------------------------- block-sparse indexer (MSA)
 def msa_block_scores(iq, index_cache, block_tables, cu_q, positions, max_ctx: int, sparse_block: int, scale: float):
     """scores[t, j] = max over index heads and visible tokens of block j of scale * iq . ik."""

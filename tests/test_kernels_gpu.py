@@ -513,3 +513,21 @@ def test_bounded_wait_runs_out_and_the_host_sees_it(cu):
     torch.cuda.synchronize()
     assert torch.isfinite(y.float()).all()
     cu.check_status(dev)
+
+
+@pytest.mark.parametrize("T,N,group", [(300, 1024, 128), (7, 2048, 2048), (65, 512, 64)])
+def test_gate_mul_grouped_and_row_dot(cu, T, N, group):
+    """Head-wise / scalar sigmoid gates (Step-3.5 attention gate, the shared expert's gate) against fp32 math."""
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, N, generator=g).to(torch.bfloat16).to(_dev())
+    gate = (torch.randn(T, N // group, generator=g) * 2).to(torch.bfloat16).to(_dev())
+    res = torch.randn(T, N, generator=g).to(torch.bfloat16).to(_dev())
+    for r in (None, res):
+        got = cu.gate_mul_grouped(x, gate, group, residual=r).float()
+        want = ref.gate_mul_grouped(x.float(), gate.float(), group, residual=None if r is None else r.float())
+        assert _rel_err(got, want) < 6e-3
+    w = (torch.randn(N, generator=g) * 0.05).to(torch.bfloat16).to(_dev())
+    got = cu.row_dot(x, w).float()
+    want = x.float() @ w.float().view(-1, 1)
+    assert got.shape == (T, 1) and float((got - want).abs().max()) < 0.02 * float(want.abs().max()) + 1e-2
+    cu.check_status(_dev())
