@@ -43,16 +43,23 @@ class PeerExecutor:
                  micro_batch_ratio: int = 1, chunked_prefill_size: Optional[int] = 1024,
                  enable_prefix_cache: bool = True, max_total_length: int = 32768,
                  request_timeout_s: Optional[float] = 600, eos_token_id=None, seed: int = 0,
-                 weights: Optional[dict] = None, shared_state=None, kv_cache_dtype: Optional[str] = None):
+                 weights: Optional[dict] = None, shared_state=None, kv_cache_dtype: Optional[str] = None,
+                 stage_group=None):
+        """``stage_group`` (:class:`parallax_b200.parallel.peer_group.TPStageGroup`): the node's GPUs run this
+        peer's layers tensor-parallel; this process is rank 0 of that group and the group owns the stage worker."""
         self.cfg, self.node_id = cfg, node_id
         self.device = torch.device(device)
+        self.group = stage_group
         # the rotary table covers every position a request may reach, whatever length the checkpoint's
         # config advertises (positions beyond that length are the caller's choice, as with the reference's
         # on-the-fly rotary embedding); a table cut at the advertised length was read out of bounds
         max_positions = max_total_length + 8
-        self.worker = StageWorker(cfg, start_layer, end_layer, self.device, dtype, page_size, num_blocks=num_blocks,
-                                  kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
-                                  kv_cache_dtype=kv_cache_dtype)
+        if stage_group is not None:
+            self.worker = stage_group.worker
+        else:
+            self.worker = StageWorker(cfg, start_layer, end_layer, self.device, dtype, page_size, num_blocks=num_blocks,
+                                      kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
+                                      kv_cache_dtype=kv_cache_dtype)
         self.is_first, self.is_last = self.worker.is_first, self.worker.is_last
         self.planner = Planner(cfg, self.worker.num_blocks, page_size, max_batch_size, max_num_tokens_per_batch,
                                micro_batch_ratio, chunked_prefill_size, enable_prefix_cache, max_total_length,
@@ -81,6 +88,12 @@ class PeerExecutor:
         hidden = None
         if hidden_of is not None:
             hidden = torch.cat([hidden_of[id(s)] for s in arrays["ordered"]], dim=0)
+        if self.group is not None:
+            # every rank of the node runs the stage on this plan; rank 0 (here) keeps the result
+            out = self.group.forward(arrays, hidden, want_logits=bool(arrays["owners"]))
+            if on_gpu:
+                _cuda.status_copy_async(self.device)
+            return arrays, out
         fb = self.builder.build(arrays["ids"] if self.is_first else None, arrays["pos"], arrays["slots"],
                                 arrays["p_q"], arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"],
                                 arrays["d_tables"], arrays["logit_rows"])

@@ -110,13 +110,13 @@ def run_standalone(args) -> None:
     start = 0 if args.start_layer is None else args.start_layer
     end = cfg.num_hidden_layers if args.end_layer is None else args.end_layer
     state.set_layer_allocation(name, start, end, args.tp_size, changed=False)
+    if (start, end) != (0, cfg.num_hidden_layers):
+        run_static_peer(args, state, name, start, end)     # one peer of a pipeline (tensor-parallel with --tp-size)
+        return
     if args.pp_size * args.tp_size * args.ep_size > 1:
         from parallax_b200.parallel.launcher import run_multi_gpu
 
         run_multi_gpu(args, cfg, name, path)
-        return
-    if (start, end) != (0, cfg.num_hidden_layers):
-        run_static_peer(args, state, name, start, end)
         return
     engine = build_engine(args, cfg, loader, start, end, state)
     tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size)

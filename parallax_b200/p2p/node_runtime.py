@@ -213,8 +213,23 @@ class NodeRuntime:
         args.start_layer, args.end_layer = start_layer, end_layer
         cfg, loader, name, path = resolve_model(args)
         device = "cuda:0" if torch.cuda.is_available() else "cpu"
-        weights = loader.load_weights("cpu", None) if loader is not None else None
+        self.group, self._followers = None, []
+        tp = int(getattr(args, "tp_size", 1) or 1)
+        if tp > 1:
+            # the node's GPUs run this peer's layers tensor-parallel: this process is rank 0, the others follow
+            from parallax_b200.parallel.peer_group import launch_followers
+
+            spec = dict(model_path=path, model_name=name.split("/")[-1], start_layer=start_layer, end_layer=end_layer,
+                        device_type="cuda" if device != "cpu" else "cpu",
+                        dtype=args.dtype if args.dtype in ("bfloat16", "float16") else "bfloat16",
+                        page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
+                        kv_cache_dtype=getattr(args, "kv_cache_dtype", None), max_batch_size=args.max_batch_size,
+                        max_num_tokens_per_batch=args.max_num_tokens_per_batch, max_total_length=args.max_sequence_length,
+                        num_blocks=None if device != "cpu" else 1024, log_level=args.log_level)
+            self.group, self._followers = launch_followers(spec, tp)
+        weights = loader.load_weights("cpu", None) if (loader is not None and self.group is None) else None
         self.peer = PeerExecutor(cfg, start_layer, end_layer, device=device, node_id=agent.node_id,
+                                 stage_group=self.group,
                                  page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
                                  kv_cache_dtype=getattr(args, "kv_cache_dtype", None),
                                  max_batch_size=args.max_batch_size,
@@ -224,7 +239,8 @@ class NodeRuntime:
                                  enable_prefix_cache=args.enable_prefix_cache,
                                  max_total_length=args.max_sequence_length,
                                  request_timeout_s=args.request_timeout_s, weights=weights, shared_state=state,
-                                 num_blocks=None if device != "cpu" else 1024)
+                                 num_blocks=(self.group.num_blocks if self.group is not None
+                                             else (None if device != "cpu" else 1024)))
         self.peer_urls: dict[str, str] = {}
 
         def resolve(node_id: str):
@@ -258,25 +274,13 @@ class NodeRuntime:
         self.server, self.thread = serve_http(self.app, args.host, args.port, args.log_level)
 
     def apply_refit(self, refit: dict) -> int:
-        """Apply a weight-refit request whose blocks are readable files (``paths``: cid -> file)."""
-        from parallax_b200.utils.weight_refit import (concat_weight_partition, filter_weight_cid_list,
-                                                      parse_safetensors_from_memory, verify_block)
+        """Apply a weight-refit request whose blocks are readable files (``paths``: cid -> file); on a
+        tensor-parallel node every rank applies it to its own slices."""
+        from parallax_b200.utils.weight_refit import apply_refit_to_stage
 
-        cfg = self.peer.cfg
-        need = filter_weight_cid_list(self.peer.worker.start_layer, self.peer.worker.end_layer,
-                                      cfg.num_hidden_layers, refit.get("index_map") or {})
-        paths = refit.get("paths") or {}
-        tensors = {}
-        for cid in need:
-            p = paths.get(cid)
-            if p is None:
-                logger.warning("refit block %s has no source; skipped", cid)
-                continue
-            blob = open(p, "rb").read()
-            if not verify_block(blob, cid):
-                raise ValueError(f"refit block {cid} failed its content-id check")
-            tensors.update(parse_safetensors_from_memory(blob))
-        return self.peer.worker.model.update_weights(concat_weight_partition(tensors))
+        if self.group is not None:
+            return self.group.command("refit", refit, local=lambda: apply_refit_to_stage(self.peer.worker, self.peer.cfg, refit))
+        return apply_refit_to_stage(self.peer.worker, self.peer.cfg, refit)
 
     def serve_until_allocation_changes(self, poll_s: float = 0.5) -> None:
         while not self.state.get_layer_allocation_changed() and self.thread.is_alive():
@@ -286,3 +290,8 @@ class NodeRuntime:
         self.server.should_exit = True
         self.loop.stop()
         self.thread.join(5.0)
+        if self.group is not None:
+            from parallax_b200.parallel.peer_group import stop_followers
+
+            stop_followers(self.group, self._followers)
+            self.group = None

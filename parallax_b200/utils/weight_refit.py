@@ -12,6 +12,7 @@ from __future__ import annotations
 import base64
 import hashlib
 import json
+import logging
 import os
 import re
 import struct
@@ -21,6 +22,8 @@ from typing import Optional
 import torch
 
 from parallax_b200.loader.filter import should_include_weight_key
+
+logger = logging.getLogger(__name__)
 
 _PART_RE = re.compile(r"^(.*)\.weight_part(\d+)$")
 _ST_DTYPES = {"F16": torch.float16, "BF16": torch.bfloat16, "F32": torch.float32, "F64": torch.float64,
@@ -117,3 +120,24 @@ class RefitVersionStore:
             shutil.rmtree(old, ignore_errors=True)
             dropped.append(old)
         return dropped
+
+
+def apply_refit_to_stage(worker, cfg, refit: dict) -> int:
+    """Apply a weight-refit request whose blocks are readable files (``paths``: cid -> file) to one stage worker:
+    pick the blocks that hold this stage's layers, check every block against its content id, join partitioned
+    tensors and hand them to the stage's own loader. Returns the number of tensors used. Every rank of a
+    tensor-parallel node runs this on the same request."""
+    need = filter_weight_cid_list(worker.start_layer, worker.end_layer, cfg.num_hidden_layers, refit.get("index_map") or {})
+    paths = refit.get("paths") or {}
+    tensors = {}
+    for cid in need:
+        p = paths.get(cid)
+        if p is None:
+            logger.warning("refit block %s has no source; skipped", cid)
+            continue
+        with open(p, "rb") as f:
+            blob = f.read()
+        if not verify_block(blob, cid):
+            raise ValueError(f"refit block {cid} failed its content-id check")
+        tensors.update(parse_safetensors_from_memory(blob))
+    return worker.model.update_weights(concat_weight_partition(tensors))

@@ -120,3 +120,50 @@ def test_two_nodes_with_manual_layer_ranges_and_no_scheduler(tmp_path):
     me = StaticPeers("a", "http://a", 0, 3, ["http://b"], http_get=lambda u: net[u])
     assert me.route(8) == ["a", "b", "c"] and me.node_addresses()["c"] == "http://c"
     assert me.route(9) is None
+
+
+def test_two_nodes_each_tensor_parallel_over_two_ranks(tmp_path):
+    """Two pipeline peers without a scheduler, each running its half of the layers tensor-parallel over two
+    processes (`--tp-size 2`): rank 0 of a node owns the peer executor and hands every batch to its follower
+    through the node's control channel. Same reply as one process with all layers."""
+    p0, p1, p2 = free_port(), free_port(), free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    common = [sys.executable, "-m", "parallax_b200.launch", "--model-path", "tiny", "--random-init", "--host", "127.0.0.1",
+              "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING"]
+    logs = [open(tmp_path / f"n{i}.log", "w") for i in range(3)]
+    kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
+    procs = [
+        subprocess.Popen(common + ["--port", str(p0), "--start-layer", "0", "--end-layer", "2", "--tp-size", "2",
+                                   "--initial-peers", f"127.0.0.1:{p1}"], stdout=logs[0], **kw),
+        subprocess.Popen(common + ["--port", str(p1), "--start-layer", "2", "--end-layer", "4", "--tp-size", "2",
+                                   "--initial-peers", f"127.0.0.1:{p0}"], stdout=logs[1], **kw),
+        subprocess.Popen(common + ["--port", str(p2)], stdout=logs[2], **kw),
+    ]
+    try:
+        for port, path in ((p0, "/v1/models"), (p1, "/peer/info"), (p2, "/v1/models")):
+            deadline = time.time() + 150
+            up = False
+            while time.time() < deadline and all(p.poll() is None for p in procs):
+                try:
+                    with urllib.request.urlopen(f"http://127.0.0.1:{port}{path}", timeout=2) as r:
+                        up = r.status == 200
+                        break
+                except OSError:
+                    time.sleep(0.5)
+            assert up, "".join(open(tmp_path / f"n{i}.log").read()[-2000:] for i in range(3))
+        for content, n in (("hello there", 8), ("a much longer prompt " * 6, 5)):
+            body = {"model": "tiny", "messages": [{"role": "user", "content": content}], "max_tokens": n, "temperature": 0}
+            split, whole = _post(p0, body), _post(p2, body)
+            assert split["usage"]["completion_tokens"] == whole["usage"]["completion_tokens"] >= 1
+            assert split["choices"][0]["message"]["content"] == whole["choices"][0]["message"]["content"]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                os.killpg(p.pid, signal.SIGTERM)
+        for p in procs:
+            try:
+                p.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(p.pid, signal.SIGKILL)
+        for f in logs:
+            f.close()
