@@ -6,7 +6,7 @@ Builds the same closed-loop state as ``bench.py`` (Qwen3-8B, 512 concurrent, 102
 GPU, switches the stage to the per-layer Python loop and brackets every op with CUDA events (with a
 synchronisation after each, so the total is the serialised sum, a little above the real step time).
 """
-import sys, os, json, collections
+import sys, os, collections
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 steps = int(sys.argv[sys.argv.index('--steps') + 1]) if '--steps' in sys.argv else 4
 import torch
@@ -14,7 +14,6 @@ import bench
 from parallax_b200.engine.engine import Engine
 from parallax_b200.engine.request import Request, SamplingParams
 from parallax_b200.models.config import named_config
-from parallax_b200 import ops
 from parallax_b200.ops import cuda as cu
 
 cfg = named_config("qwen3-8b")

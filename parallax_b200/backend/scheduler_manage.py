@@ -12,7 +12,6 @@ rack needs.
 from __future__ import annotations
 
 import logging
-import threading
 import time
 from typing import Optional
 

@@ -31,7 +31,7 @@ import torch
 
 from parallax_b200 import ops
 from parallax_b200.cache.manager import CacheManager
-from parallax_b200.engine.batch import BatchBuilder, ForwardBatch
+from parallax_b200.engine.batch import BatchBuilder
 from parallax_b200.engine.request import PENDING_TOKEN, Request, RequestStatus, SamplingParams
 from parallax_b200.engine.scheduler import BatchScheduler, ScheduledSeq
 from parallax_b200.engine.worker import StageWorker

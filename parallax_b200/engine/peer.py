@@ -28,7 +28,7 @@ import torch
 from parallax_b200 import ops
 from parallax_b200.engine.batch import BatchBuilder
 from parallax_b200.engine.engine import Planner
-from parallax_b200.engine.request import IntermediateRequest, Request, RequestStatus, SamplingParams
+from parallax_b200.engine.request import IntermediateRequest, Request, RequestStatus
 from parallax_b200.engine.scheduler import ScheduledSeq
 from parallax_b200.engine.worker import StageWorker
 from parallax_b200.models.config import ModelConfig

@@ -11,7 +11,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass, field
-from typing import Any, Optional
+from typing import Optional
 
 # layer kinds (same vocabulary as the reference's ``utils/layer_types.py:5-20``)
 ATTENTION = "attention"

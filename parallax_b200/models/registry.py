@@ -8,7 +8,6 @@ stage classes cover MLA/DSA (DeepSeek) and hybrid linear-attention models.
 
 from __future__ import annotations
 
-from typing import Callable
 
 from parallax_b200.models.config import ModelConfig
 

@@ -12,7 +12,6 @@ cache scatter (``.../reshape_and_cache/reshape_and_cache.metal:32-96``), and the
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 

@@ -15,7 +15,6 @@ The reference runs with expert parallelism switched off
 
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_int, c_int64, c_uint32, c_void_p as P
 from typing import Optional
 

@@ -56,7 +56,7 @@ def build_dist_engine(spec: dict):
     """Build this rank's :class:`DistEngine` from a JSON-able spec (same on every rank)."""
     import torch
 
-    from parallax_b200.models.config import ModelConfig, config_from_hf, named_config
+    from parallax_b200.models.config import config_from_hf, named_config
     from parallax_b200.parallel.dist_engine import DistEngine, split_layers
     import torch.distributed as dist
 

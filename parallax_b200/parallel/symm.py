@@ -15,10 +15,8 @@ the previous use) and hands out monotonically increasing epochs for their flags.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
 
 import torch
-import torch.distributed as dist
 
 
 class SymmBuffer:

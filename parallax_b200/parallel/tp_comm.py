@@ -16,7 +16,6 @@ all-reduce after o_proj / down_proj (``src/parallax/sglang/model_runner.py:134-1
 
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -108,7 +108,6 @@ def test_web_app_pages_and_the_calls_they_make(backend):
     """The cluster web app is one static file with three views; every endpoint it calls answers in the shape
     the page reads (set up -> /model/list + /scheduler/init, join -> /node/join/command + /cluster/status,
     chat -> /v1/models + /v1/chat/completions)."""
-    import json as _json
     import re
 
     c, sm, _ = backend

@@ -3,13 +3,11 @@
 import time
 
 import pytest
-import torch
 from fastapi.testclient import TestClient
 
 from parallax_b200 import cli
 from parallax_b200.args import parse_args
 from parallax_b200.engine.peer import PeerExecutor
-from parallax_b200.engine.request import Request, SamplingParams
 from parallax_b200.frontend.tokenizer import ByteTokenizer, TokenizerWrapper
 from parallax_b200.launch_chat import create_chat_app
 from parallax_b200.models.config import named_config

@@ -9,7 +9,7 @@ import torch
 
 from parallax_b200.engine.engine import Engine
 from parallax_b200.engine.request import Request, SamplingParams
-from parallax_b200.models.config import config_from_hf, named_config
+from parallax_b200.models.config import config_from_hf
 from parallax_b200.ops import reference as ref
 
 F8 = torch.float8_e4m3fn

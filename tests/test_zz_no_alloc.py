@@ -10,7 +10,6 @@ The file name keeps it last in collection order, so a run that stops at the firs
 already run every other test.
 """
 
-import ctypes
 import math
 from ctypes import c_float, c_int, c_int64, c_void_p
 
