@@ -246,8 +246,10 @@ class BatchScheduler:
             if room <= 0:
                 break
             if cost > room:
-                if not chunk and prefill_cap is None:
-                    continue
+                if not chunk and prefill_cap is None and used > 0 and cost <= budget_p:
+                    continue        # unsliced prompts wait for a step with enough room of their own
+                # a slice of the prompt; also without chunked prefill when the prompt is longer than any
+                # step's budget, which would otherwise wait for ever
                 cost = room
             last = cost == remaining
             if not last:
