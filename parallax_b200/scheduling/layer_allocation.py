@@ -216,7 +216,8 @@ class BaseLayerAllocator:
         caps, power = [], []
         for i, node in enumerate(nodes):
             if i == 0:
-                cap = node.get_decoder_layer_capacity(include_input_embed=True)
+                # (a pipeline of one node stores the embedding and the head)
+                cap = node.get_decoder_layer_capacity(include_input_embed=True, include_lm_head=n == 1)
             elif i == n - 1:
                 cap = node.get_decoder_layer_capacity(include_lm_head=True)
             else:
@@ -377,6 +378,7 @@ class DynamicProgrammingLayerAllocator(BaseLayerAllocator):
         cap = [x.get_decoder_layer_capacity() for x in nodes]
         cap_head = [x.get_decoder_layer_capacity(include_input_embed=True) for x in nodes]
         cap_tail = [x.get_decoder_layer_capacity(include_lm_head=True) for x in nodes]
+        cap_solo = [x.get_decoder_layer_capacity(include_input_embed=True, include_lm_head=True) for x in nodes]
         suffix = [0] * (n + 1)
         for i in range(n - 1, -1, -1):
             suffix[i] = suffix[i + 1] + cap[i]
@@ -417,7 +419,9 @@ class DynamicProgrammingLayerAllocator(BaseLayerAllocator):
                 if c < best:
                     best, act = c, ("assign", j, closes)
             if to_start > 0:  # open a new pipeline at node i
-                left = L - cap_head[i]
+                # a node is a pipeline of its own only if the head fits beside the embedding as well; one that
+                # falls short of that by the head alone opens a pipeline and leaves its last layer to the next node
+                left = 0 if cap_solo[i] >= L else max(L - cap_head[i], 1)
                 if left <= 0:
                     c = 1 + solve(i + 1, open_res, done + 1)
                     if c < best:
