@@ -618,10 +618,14 @@ class Engine:
         now = time.time()
         for i, s in enumerate(owners):
             req = s.req
-            if req.is_finished:           # ended earlier (EOS seen after this row was launched, abort)
-                continue
             k = st.slot_index[i]
             tok = int(token_list[i])
+            if req.is_finished:           # ended earlier (EOS seen after this row was launched, abort)
+                if k < len(req.output_ids) and req.output_ids[k] == PENDING_TOKEN:
+                    # aborted (client, time-out, KV memory) while this token was on its way: it was computed,
+                    # so it takes its place in the record (the request's stream has ended already)
+                    req.fill_token(k, tok, prob_list[i] if prob_list else None, now=now)
+                continue
             req.fill_token(k, tok, prob_list[i] if prob_list else None, now=now)
             cache.append_request_token(req.request_id, tok)
             why = sched.finish_reason(req, k + 1, tok)

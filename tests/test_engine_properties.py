@@ -16,6 +16,7 @@ CFG = config_from_hf(dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3"
 workload = st.fixed_dictionaries({
     "batch": st.integers(1, 6), "ratio": st.integers(1, 2), "budget": st.integers(24, 96),
     "chunk": st.sampled_from([None, 16, 32]), "lookahead": st.booleans(), "prefix_cache": st.booleans(),
+    "blocks": st.sampled_from([6, 10, 24, 96]),
     "reqs": st.lists(st.tuples(st.integers(1, 70), st.integers(1, 6), st.booleans()), min_size=1, max_size=9),
 })
 
@@ -23,7 +24,7 @@ workload = st.fixed_dictionaries({
 @settings(max_examples=150, deadline=None, suppress_health_check=[HealthCheck.too_slow])
 @given(workload)
 def test_limits_hold_and_everything_finishes(w):
-    eng = Engine(CFG, device="cpu", num_blocks=96, page_size=16, max_batch_size=w["batch"], micro_batch_ratio=w["ratio"],
+    eng = Engine(CFG, device="cpu", num_blocks=w["blocks"], page_size=16, max_batch_size=w["batch"], micro_batch_ratio=w["ratio"],
                  max_num_tokens_per_batch=w["budget"], chunked_prefill_size=w["chunk"], enable_prefix_cache=w["prefix_cache"],
                  max_total_length=128, seed=0, async_scheduling=w["lookahead"])
     g = torch.Generator().manual_seed(1)
@@ -48,7 +49,10 @@ def test_limits_hold_and_everything_finishes(w):
                 assert s["prefill_tokens"] <= max(w["budget"], w["chunk"]), s
         assert steps < 2000, "the loop does not terminate"
     for r in reqs:
-        assert r.is_finished and len(r.output_ids) == r.sampling_params.max_new_tokens, (r.status, r.output_ids)
+        # a request ends with all its tokens, or aborted when the KV memory ran out (small pools)
+        assert r.is_finished, (r.status, len(r.input_ids))
+        assert len(r.output_ids) == r.sampling_params.max_new_tokens or \
+            (r.status.name == "FINISHED_ABORT" and w["blocks"] < 96), (r.status, r.output_ids)
         assert all(0 <= t < 128 for t in r.output_ids)
     assert not eng.cache.reqs
     held = 0
@@ -58,4 +62,4 @@ def test_limits_hold_and_everything_finishes(w):
             n = stack.pop()
             held += 1
             stack.extend(n.children.values())
-    assert eng.cache.num_free_blocks() == 96 - held
+    assert eng.cache.num_free_blocks() == w["blocks"] - held
