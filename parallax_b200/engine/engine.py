@@ -305,11 +305,12 @@ class Engine:
             req.grammar = JsonSchemaMatcher(req.sampling_params.json_schema)
         self.scheduler.enque_request(req)
 
-    def abort_request(self, rid: str) -> None:
+    def abort_request(self, rid: str) -> Optional[Request]:
+        """Returns the request if it was still waiting for admission (it ends here, without a step)."""
         try:
-            self.scheduler.cancel_request(rid)
+            return self.scheduler.cancel_request(rid)
         except ValueError:
-            pass
+            return None
 
     def has_work(self) -> bool:
         return (self._in_flight is not None or self.scheduler.num_queued_requests > 0

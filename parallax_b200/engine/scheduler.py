@@ -123,16 +123,18 @@ class BatchScheduler:
     def evict_request(self, rid: str) -> Optional[Request]:
         return self._running.pop(rid, None)
 
-    def cancel_request(self, rid: str) -> None:
+    def cancel_request(self, rid: str) -> Optional[Request]:
+        """A running request is flagged and ends at its next step; one that still waits for admission is taken
+        out of the queue and returned (status CANCELLED): it produces no further event by itself."""
         req = self._running.get(rid)
         if req is not None:
             req.abort = True
-            return
+            return None
         for r in list(self._wait_queue):
             if r.request_id == rid:
                 self._wait_queue.remove(r)
                 r.update_status(RequestStatus.CANCELLED)
-                return
+                return r
         raise ValueError(f"Attempted to cancel non-existent request {rid}.")
 
     # ------------------------------------------------------------------ phase 1

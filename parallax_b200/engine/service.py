@@ -99,7 +99,9 @@ class EngineLoop:
                     req.update_status(RequestStatus.ERROR)
                     self._emit(TokenEvent(req.request_id, None, True, req.status, error=str(exc)))
             else:
-                self.engine.abort_request(str(payload))
+                gone = self.engine.abort_request(str(payload))
+                if gone is not None:     # cancelled before it ever ran: close its stream here
+                    self._emit(TokenEvent(gone.request_id, None, True, gone.status))
 
     def _fail_batch(self, exc: Exception) -> None:
         """A failed forward pass releases every running request with an ERROR event."""

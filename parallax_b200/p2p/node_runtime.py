@@ -124,7 +124,9 @@ class PeerLoop:
                             logger.warning("rejected request %s: %s", req.request_id, exc)
                     elif kind == "abort":
                         try:
-                            peer.scheduler.cancel_request(str(payload))
+                            gone = peer.scheduler.cancel_request(str(payload))
+                            if gone is not None:       # cancelled before it ever ran: close its stream here
+                                self._emit(gone, None)
                         except ValueError:
                             pass
                     elif kind == "release":

@@ -466,13 +466,14 @@ class DistEngine:
         pl = min(self.planners, key=lambda p: p.scheduler.num_queued_requests + p.scheduler.num_running_requests)
         pl.scheduler.enque_request(req)
 
-    def abort_request(self, rid: str) -> None:
+    def abort_request(self, rid: str) -> Optional[Request]:
+        """Returns the request if it was still waiting for admission (it ends here, without a step)."""
         for pl in self.planners:
             try:
-                pl.scheduler.cancel_request(rid)
-                return
+                return pl.scheduler.cancel_request(rid)
             except ValueError:
                 pass
+        return None
 
     @property
     def stages(self):
@@ -594,7 +595,8 @@ class DistEngine:
                 out = out if out.is_contiguous() else out.contiguous()
                 self._pending_sends.append((dist.isend(out, dst=self._next(), group=self.hop_out), out))
             elif n_logits > 0:
-                tokens = self._sample(lp, out, constrain=is_sender)
+                with torch.inference_mode():        # (penalties update the stage's logits in place)
+                    tokens = self._sample(lp, out, constrain=is_sender)
                 if is_sender:
                     # the status word of the sampling rank rides with the tokens
                     packed = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)

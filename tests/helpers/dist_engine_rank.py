@@ -30,7 +30,51 @@ def main() -> None:
         prompts = spec["prompts"]
         eng.mark()
         sp = SamplingParams(max_new_tokens=spec["max_new"], temperature=0.0, ignore_eos=True)
-        if spec.get("schema_of"):
+        if spec.get("stress_seed") is not None:
+            # a random mix: staggered arrivals, shared prefixes, sampling, penalties, client aborts, a small KV pool
+            import random
+
+            from parallax_b200.engine.request import Request
+
+            rnd = random.Random(spec["stress_seed"])
+            vocab = eng.cfg.vocab_size
+            shared = [rnd.randrange(vocab) for _ in range(48)]
+            plan = []
+            for i in range(spec.get("stress_requests", 14)):
+                n = rnd.randint(1, 90)
+                ids = (shared[:min(n, 48)] + [rnd.randrange(vocab) for _ in range(max(n - 48, 0))]) if rnd.random() < 0.4 \
+                    else [rnd.randrange(vocab) for _ in range(n)]
+                d = dict(max_new_tokens=rnd.randint(1, 7), temperature=rnd.choice([0.0, 0.0, 0.8]), ignore_eos=True)
+                if rnd.random() < 0.25:
+                    d.update(repetition_penalty=1.3, presence_penalty=0.5)
+                if d["temperature"] > 0:
+                    d.update(top_k=rnd.choice([-1, 5]), top_p=rnd.choice([1.0, 0.9]))
+                plan.append((rnd.randint(0, 25), Request(input_ids=ids, sampling_params=SamplingParams.from_dict(d)),
+                             rnd.random() < 0.15))
+            reqs = [r for _a, r, _k in plan]
+            step, aborted = 0, set()
+            while plan or eng.has_work():
+                for a, r, _k in [x for x in plan if x[0] <= step]:
+                    eng.add_request(r)
+                plan = [x for x in plan if x[0] > step]
+                eng.step()
+                step += 1
+                if step % 7 == 3:       # a client goes away now and then
+                    live = [r for r in reqs if not r.is_finished and r.output_ids and r.request_id not in aborted]
+                    if live and rnd.random() < 0.5:
+                        victim = rnd.choice(live)
+                        aborted.add(victim.request_id)
+                        eng.abort_request(victim.request_id)
+                assert step < 3000, "the engine does not drain"
+            outs = [r.output_ids for r in reqs]
+            spec["_stress"] = {"status": [r.status.name for r in reqs], "want": [r.sampling_params.max_new_tokens for r in reqs],
+                               "aborted": [r.request_id in aborted for r in reqs],
+                               "live_requests": sum(len(pl.cache.reqs) for pl in eng.planners),
+                               "free_blocks": [pl.cache.num_free_blocks() for pl in eng.planners],
+                               "tree_blocks": [0 if pl.cache.prefix_cache is None else pl.cache.prefix_cache.num_nodes
+                                               for pl in eng.planners],
+                               "num_blocks": eng.num_blocks, "steps": step}
+        elif spec.get("schema_of"):
             # per prompt a JSON schema (or None): constrained decoding on the rank that samples
             from parallax_b200.engine.request import Request
 
@@ -65,7 +109,7 @@ def main() -> None:
         eng.shutdown()
         with open(out_path, "w") as f:
             json.dump({"outputs": outs, "steps": eng.steps, "probe": probe, "prefix_hits": hits,
-                       "state_snapshots": snapshots}, f)
+                       "state_snapshots": snapshots, "stress": spec.get("_stress")}, f)
     else:
         eng.serve_forever()
     import torch.distributed as dist

@@ -25,7 +25,8 @@ def _run_group(pp, tp, tmp_path, max_new=6, chunk=16, model="tiny", prompts=None
     spec = dict(model_name=model, pp=pp, tp=tp, device_type="cpu", num_blocks=256, page_size=16, max_batch_size=4,
                 max_num_tokens_per_batch=64, chunked_prefill_size=chunk, max_total_length=256,
                 prompts=prompts or PROMPTS,
-                max_new=max_new, seed=0, **extra)
+                max_new=max_new, seed=0)
+    spec.update(extra)
     world, port = pp * tp * extra.get("ep", 1), free_port()
     out = tmp_path / f"out_{pp}_{tp}.json"
     procs = []
@@ -167,6 +168,26 @@ def test_constrained_decoding_on_the_sampling_rank(pp, tp, tmp_path):
         if tp == 1:
             assert ids == r.output_ids      # same summation order as the single process
     assert len(got[1]) == 6
+
+
+@pytest.mark.parametrize("model,pp,tp,ep,seed", [("tiny", 2, 1, 1, 1), ("tiny", 1, 2, 1, 2), ("tiny-moe", 1, 1, 2, 3),
+                                                 ("tiny", 3, 1, 1, 4)])
+def test_random_mix_drains_and_returns_all_memory(model, pp, tp, ep, seed, tmp_path):
+    """A random mix of requests (staggered arrivals, shared prefixes, sampling, penalties, client aborts) on a
+    small KV pool: every request ends - with all its tokens, or aborted - and rank 0's bookkeeping is empty
+    afterwards, with every block either free or held by the prefix tree."""
+    extra = dict(ep=ep) if ep > 1 else {}
+    r = _run_group(pp, tp, tmp_path, model=model, stress_seed=seed, num_blocks=40, **extra)["stress"]
+    for status, want, got, aborted in zip(r["status"], r["want"], _lens(r, tmp_path, pp, tp), r["aborted"]):
+        assert status.startswith("FINISHED"), r
+        assert got == want or status == "FINISHED_ABORT", (status, want, got, aborted)
+    assert r["live_requests"] == 0
+    for free, tree in zip(r["free_blocks"], r["tree_blocks"]):
+        assert free + tree == r["num_blocks"], r
+
+
+def _lens(r, tmp_path, pp, tp):
+    return [len(o) for o in json.loads((tmp_path / f"out_{pp}_{tp}.json").read_text())["outputs"]]
 
 
 def test_rank_loss_is_detected_on_the_host(tmp_path):

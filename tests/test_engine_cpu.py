@@ -373,3 +373,31 @@ def test_a_backlog_of_prompt_tokens_does_not_starve_decoding_requests():
         produced.append(len(short.output_ids) - before)
         assert st["prefill_tokens"] >= 30      # the prompt slices still take (almost) the whole budget
     assert produced == [1] * 10, produced
+
+
+def test_abort_of_a_waiting_request_closes_its_stream():
+    """A request aborted before it was ever admitted (the running set is full) ends with one finished event, so that
+    whoever waits on its stream is released and the loop's stream table does not grow."""
+    from parallax_b200.engine.service import EngineLoop
+
+    cfg = named_config("tiny")
+    eng = Engine(cfg, device="cpu", num_blocks=64, page_size=16, max_batch_size=1, max_total_length=256)
+    loop = EngineLoop(eng)
+    long_sp = SamplingParams(max_new_tokens=60, temperature=0.0, ignore_eos=True)
+    first = Request(input_ids=list(range(3, 20)), sampling_params=long_sp)
+    waiting = Request(input_ids=list(range(5, 12)), sampling_params=SamplingParams.from_dict(long_sp.to_dict()))
+    q1 = loop.submit(first)
+    q2 = loop.submit(waiting)
+    loop.abort(waiting.request_id)          # queued behind the add: the request is still waiting when it is cancelled
+    loop.start()
+    try:
+        ev = q2.get(timeout=30)
+        assert ev.finished and ev.token_id is None and waiting.status.name == "CANCELLED"
+        loop.abort(first.request_id)
+        while True:
+            ev = q1.get(timeout=30)
+            if ev.finished:
+                break
+        assert loop.num_inflight == 0
+    finally:
+        loop.stop()

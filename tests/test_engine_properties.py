@@ -18,6 +18,8 @@ workload = st.fixed_dictionaries({
     "chunk": st.sampled_from([None, 16, 32]), "lookahead": st.booleans(), "prefix_cache": st.booleans(),
     "blocks": st.sampled_from([6, 10, 24, 96]),
     "reqs": st.lists(st.tuples(st.integers(1, 70), st.integers(1, 6), st.booleans()), min_size=1, max_size=9),
+    "sampled": st.lists(st.sampled_from(["greedy", "sample", "penalty"]), min_size=9, max_size=9),
+    "abort_at": st.one_of(st.none(), st.integers(1, 12)),
 })
 
 
@@ -32,15 +34,24 @@ def test_limits_hold_and_everything_finishes(w):
     reqs = []
     for n, max_new, share in w["reqs"]:
         ids = (shared[:min(n, 48)] if share else []) + torch.randint(0, 128, (max(n - 48, 1) if share else n,), generator=g).tolist()
-        reqs.append(Request(input_ids=ids, sampling_params=SamplingParams(max_new_tokens=max_new, temperature=0.0, ignore_eos=True)))
+        kind = w["sampled"][len(reqs)]
+        sp = SamplingParams(max_new_tokens=max_new, temperature=0.8 if kind == "sample" else 0.0, ignore_eos=True,
+                            top_k=5 if kind == "sample" else -1, repetition_penalty=1.3 if kind == "penalty" else 1.0)
+        reqs.append(Request(input_ids=ids, sampling_params=sp))
     pending = list(reqs)
     micro = max(w["batch"] // w["ratio"], 1)
     steps = 0
+    aborted = set()
     while pending or eng.has_work():
         if pending:
             eng.add_request(pending.pop(0))         # arrivals interleave with steps
         eng.step()
         steps += 1
+        if w["abort_at"] == steps:               # a client goes away
+            live = [r for r in reqs if not r.is_finished and r not in pending]
+            if live:
+                eng.abort_request(live[0].request_id)
+                aborted.add(live[0].request_id)
         s = eng.last_step_stats
         if s:
             assert s["tokens"] <= w["budget"] + micro, s           # prompt tokens within the budget, plus the decode rows
@@ -52,7 +63,8 @@ def test_limits_hold_and_everything_finishes(w):
         # a request ends with all its tokens, or aborted when the KV memory ran out (small pools)
         assert r.is_finished, (r.status, len(r.input_ids))
         assert len(r.output_ids) == r.sampling_params.max_new_tokens or \
-            (r.status.name == "FINISHED_ABORT" and w["blocks"] < 96), (r.status, r.output_ids)
+            (r.status.name == "FINISHED_ABORT" and (w["blocks"] < 96 or r.request_id in aborted)) or \
+            (r.status.name == "CANCELLED" and r.request_id in aborted and not r.output_ids), (r.status, r.output_ids)
         assert all(0 <= t < 128 for t in r.output_ids)
     assert not eng.cache.reqs
     held = 0
