@@ -7,13 +7,17 @@ from hypothesis import strategies as st
 
 from parallax_b200.engine.engine import Engine
 from parallax_b200.engine.request import Request, SamplingParams
-from parallax_b200.models.config import config_from_hf
+from parallax_b200.models.config import config_from_hf, named_config
 
 CFG = config_from_hf(dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=64, num_hidden_layers=1,
                           num_attention_heads=2, num_key_value_heads=1, head_dim=32, intermediate_size=128, vocab_size=128,
                           tie_word_embeddings=True, rope_theta=1e4))
 
+MODELS = {"dense": CFG, "hybrid": named_config("tiny-hybrid"), "mla": named_config("tiny-mla"),
+          "dsa": named_config("tiny-dsa"), "msa": named_config("tiny-msa"), "moe": named_config("tiny-moe")}
+
 workload = st.fixed_dictionaries({
+    "model": st.sampled_from(sorted(MODELS)),
     "batch": st.integers(1, 6), "ratio": st.integers(1, 2), "budget": st.integers(24, 96),
     "chunk": st.sampled_from([None, 16, 32]), "lookahead": st.booleans(), "prefix_cache": st.booleans(),
     "blocks": st.sampled_from([6, 10, 24, 96]),
@@ -26,14 +30,16 @@ workload = st.fixed_dictionaries({
 @settings(max_examples=150, deadline=None, suppress_health_check=[HealthCheck.too_slow])
 @given(workload)
 def test_limits_hold_and_everything_finishes(w):
-    eng = Engine(CFG, device="cpu", num_blocks=w["blocks"], page_size=16, max_batch_size=w["batch"], micro_batch_ratio=w["ratio"],
+    cfg = MODELS[w["model"]]
+    V = cfg.vocab_size
+    eng = Engine(cfg, device="cpu", num_blocks=w["blocks"], page_size=16, max_batch_size=w["batch"], micro_batch_ratio=w["ratio"],
                  max_num_tokens_per_batch=w["budget"], chunked_prefill_size=w["chunk"], enable_prefix_cache=w["prefix_cache"],
                  max_total_length=128, seed=0, async_scheduling=w["lookahead"])
     g = torch.Generator().manual_seed(1)
-    shared = torch.randint(0, 128, (48,), generator=g).tolist()
+    shared = torch.randint(0, V, (48,), generator=g).tolist()
     reqs = []
     for n, max_new, share in w["reqs"]:
-        ids = (shared[:min(n, 48)] if share else []) + torch.randint(0, 128, (max(n - 48, 1) if share else n,), generator=g).tolist()
+        ids = (shared[:min(n, 48)] if share else []) + torch.randint(0, V, (max(n - 48, 1) if share else n,), generator=g).tolist()
         kind = w["sampled"][len(reqs)]
         sp = SamplingParams(max_new_tokens=max_new, temperature=0.8 if kind == "sample" else 0.0, ignore_eos=True,
                             top_k=5 if kind == "sample" else -1, repetition_penalty=1.3 if kind == "penalty" else 1.0)
@@ -65,7 +71,7 @@ def test_limits_hold_and_everything_finishes(w):
         assert len(r.output_ids) == r.sampling_params.max_new_tokens or \
             (r.status.name == "FINISHED_ABORT" and (w["blocks"] < 96 or r.request_id in aborted)) or \
             (r.status.name == "CANCELLED" and r.request_id in aborted and not r.output_ids), (r.status, r.output_ids)
-        assert all(0 <= t < 128 for t in r.output_ids)
+        assert all(0 <= t < V for t in r.output_ids)
     assert not eng.cache.reqs
     held = 0
     if eng.cache.prefix_cache is not None:
@@ -75,3 +81,14 @@ def test_limits_hold_and_everything_finishes(w):
             held += 1
             stack.extend(n.children.values())
     assert eng.cache.num_free_blocks() == w["blocks"] - held
+    if eng.cache.needs_slots:
+        # recurrent-state slots: the requests' own are all back, snapshots are held by tree nodes only
+        assert eng.cache.slot_allocator.get_num_free_slots() == eng.cache.slot_allocator.num_slots
+        snaps = 0
+        stack = list(eng.cache.prefix_cache.root.children.values()) if eng.cache.prefix_cache is not None else []
+        while stack:
+            n = stack.pop()
+            snaps += int(n.linear_slot is not None)
+            stack.extend(n.children.values())
+        if eng.cache.prefix_slot_allocator is not None:
+            assert eng.cache.prefix_slot_allocator.get_num_free_slots() == eng.cache.prefix_slot_allocator.num_slots - snaps
