@@ -817,10 +817,17 @@ class DistEngine:
             self.lora.release(req.lora_path)
             req.lora_slot = -1
 
+    def _release_grammar(self, req: Request) -> None:
+        """A constrained request ended (however): the sampling rank forgets its matcher with the next plan."""
+        if getattr(req, "grammar", None) is not None and req.request_id in self._grammar_known:
+            self._grammar_known.discard(req.request_id)
+            self._grammar_drops.append(req.request_id)
+
     def _drop(self, pl, req: Request) -> None:
         pl.scheduler.evict_request(req.request_id)
         pl.cache.free_request(req.request_id)
         self._release_lora(req)
+        self._release_grammar(req)
         self._side_events.append((req, None))
 
     def _plan_one(self, pl):
@@ -1034,9 +1041,7 @@ class DistEngine:
                 if sched.check_and_update_request_status(req):
                     cache.free_request(req.request_id)
                     self._release_lora(req)
-                    if g is not None:
-                        self._grammar_known.discard(req.request_id)
-                        self._grammar_drops.append(req.request_id)
+                    self._release_grammar(req)
                 else:
                     sched.enque_request(req, now=now)
                 out.append((req, tok if tok >= 0 else None))
@@ -1052,6 +1057,8 @@ class DistEngine:
                 req.update_status(RequestStatus.FINISHED_ABORT)
                 pl.scheduler.evict_request(req.request_id)
                 pl.cache.free_request(req.request_id)
+                self._release_lora(req)
+                self._release_grammar(req)
                 out.append((req, None))
         issued = False
         while len(self.in_flight) < self.max_in_flight:

@@ -49,8 +49,15 @@ def main() -> None:
                     d.update(repetition_penalty=1.3, presence_penalty=0.5)
                 if d["temperature"] > 0:
                     d.update(top_k=rnd.choice([-1, 5]), top_p=rnd.choice([1.0, 0.9]))
-                plan.append((rnd.randint(0, 25), Request(input_ids=ids, sampling_params=SamplingParams.from_dict(d)),
-                             rnd.random() < 0.15))
+                adapter = None
+                feats = spec.get("stress_features") or []
+                if "schema" in feats and rnd.random() < 0.3:
+                    d.update(json_schema=json.dumps(spec["stress_schema"]), max_new_tokens=60, ignore_eos=False)
+                    ids = [t % 250 for t in ids]
+                elif "lora" in feats and rnd.random() < 0.5:
+                    adapter = rnd.choice(sorted(spec["lora"]["paths"]))
+                plan.append((rnd.randint(0, 25), Request(input_ids=ids, sampling_params=SamplingParams.from_dict(d),
+                                                         lora_path=adapter), rnd.random() < 0.15))
             reqs = [r for _a, r, _k in plan]
             step, aborted = 0, set()
             while plan or eng.has_work():
@@ -73,7 +80,10 @@ def main() -> None:
                                "free_blocks": [pl.cache.num_free_blocks() for pl in eng.planners],
                                "tree_blocks": [0 if pl.cache.prefix_cache is None else pl.cache.prefix_cache.num_nodes
                                                for pl in eng.planners],
-                               "num_blocks": eng.num_blocks, "steps": step}
+                               "num_blocks": eng.num_blocks, "steps": step,
+                               "schema": [bool(r.sampling_params.json_schema) for r in reqs],
+                               "lora_pins": None if eng.lora is None else sum(eng.lora.pins.values()),
+                               "grammars_known": len(eng._grammar_known)}
         elif spec.get("schema_of"):
             # per prompt a JSON schema (or None): constrained decoding on the rank that samples
             from parallax_b200.engine.request import Request

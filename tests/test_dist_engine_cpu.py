@@ -186,6 +186,42 @@ def test_random_mix_drains_and_returns_all_memory(model, pp, tp, ep, seed, tmp_p
         assert free + tree == r["num_blocks"], r
 
 
+@pytest.mark.parametrize("pp,tp", [(2, 1), (1, 2)])
+def test_random_mix_with_adapters_and_schemas(pp, tp, tmp_path):
+    """The same random mix with per-request LoRA adapters and JSON-schema requests among the others: adapter pins and
+    the matchers' bookkeeping are back to zero at the end, and finished schema requests hold valid documents."""
+    from parallax_b200.engine.structured import JsonSchemaMatcher
+    from parallax_b200.frontend.tokenizer import TokenizerWrapper
+    from tests.test_lora_cpu import _make_adapter
+
+    cfg = named_config("tiny")
+    lora = {"max_loaded": 2, "max_rank": 8,
+            "paths": {"x": _make_adapter(cfg, tmp_path / "x", 1), "y": _make_adapter(cfg, tmp_path / "y", 2, rank=8, alpha=4)}}
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}
+    out = _run_group(pp, tp, tmp_path, stress_seed=11, num_blocks=64, lora=lora, stress_features=["lora", "schema"],
+                     stress_schema=schema, stress_requests=16)
+    r = out["stress"]
+    tok = TokenizerWrapper.from_pretrained(None, vocab_size=cfg.vocab_size)
+    assert any(r["schema"])
+    for status, want, ids, is_schema in zip(r["status"], r["want"], out["outputs"], r["schema"]):
+        assert status.startswith("FINISHED"), r
+        if is_schema and status == "FINISHED_EOS":
+            text = tok.decode(ids)
+            m = JsonSchemaMatcher(schema)
+            assert m.advance(text) and m.done, text
+        elif not is_schema:
+            assert len(ids) == want or status == "FINISHED_ABORT", (status, want, ids)
+    assert r["live_requests"] == 0 and r["lora_pins"] == 0 and r["grammars_known"] == 0, r
+
+
+def test_random_mix_on_a_hybrid_model_with_state_snapshots(tmp_path):
+    out = _run_group(2, 1, tmp_path, model="tiny-hybrid", stress_seed=5, num_blocks=48)
+    r = out["stress"]
+    for status, want, ids in zip(r["status"], r["want"], out["outputs"]):
+        assert status.startswith("FINISHED") and (len(ids) == want or status == "FINISHED_ABORT"), (status, want, ids)
+    assert r["live_requests"] == 0
+
+
 def _lens(r, tmp_path, pp, tp):
     return [len(o) for o in json.loads((tmp_path / f"out_{pp}_{tp}.json").read_text())["outputs"]]
 
