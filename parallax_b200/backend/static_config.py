@@ -73,10 +73,14 @@ def get_model_info(model_name: str, use_hfcache: bool = False) -> ModelInfo:
     try:
         return model_info_from_config(load_config_only(model_name, local_files_only=use_hfcache), model_name)
     except Exception:
-        if model_name in _BUILTIN:
-            from parallax_b200.models.config import named_config
+        from parallax_b200.models.config import named_config
 
+        if model_name in _BUILTIN:
             return model_info_from_config(named_config(_BUILTIN[model_name]).raw, model_name)
+        try:      # a named architecture (what `--random-init` serves), e.g. "qwen3-8b" or "tiny"
+            return model_info_from_config(named_config(model_name.split("/")[-1]).raw, model_name)
+        except KeyError:
+            pass
         raise
 
 

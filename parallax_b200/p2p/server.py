@@ -60,14 +60,30 @@ class SchedulerClient:
         return self._post("/node/addresses", {})
 
 
+def _http_rtt_ms(url: str, timeout_s: float = 1.0) -> Optional[float]:
+    import httpx
+
+    t0 = time.perf_counter()
+    r = httpx.get(url.rstrip("/") + "/health", timeout=timeout_s, trust_env=False)
+    if r.status_code >= 500:
+        return None
+    return (time.perf_counter() - t0) * 1e3
+
+
 class NodeAgent:
     def __init__(self, scheduler: SchedulerClient, shared_state: SharedState, http_addr: str,
                  node_id: Optional[str] = None, hardware: Optional[HardwareInfo] = None,
                  max_batch_size: int = 8, max_sequence_length: int = 32768, param_mem_ratio: float = 0.65,
                  kvcache_mem_ratio: float = 0.25, start_layer: Optional[int] = None,
                  end_layer: Optional[int] = None, on_refit: Optional[Callable[[dict], None]] = None,
-                 heartbeat_interval_s: float = HEARTBEAT_INTERVAL_S):
+                 heartbeat_interval_s: float = HEARTBEAT_INTERVAL_S,
+                 probe: Optional[Callable[[str], Optional[float]]] = None):
+        """``probe(url) -> round-trip ms or None``: how the agent measures the way to another node (default: a timed
+        ``GET <url>/health``)."""
         self.scheduler = scheduler
+        self.probe = probe or _http_rtt_ms
+        self._rtt_at: dict[str, float] = {}
+        self._rtt_missing = False
         self.state = shared_state
         self.http_addr = http_addr
         self.node_id = node_id or f"node-{uuid.uuid4().hex[:12]}"
@@ -120,7 +136,39 @@ class NodeAgent:
         self._apply_allocation(alloc)
         return alloc
 
+    def measure_rtts(self, refresh_s: float = 60.0) -> None:
+        """Round-trip times to the other nodes of the cluster, which the scheduler needs to price a pipeline's
+        hops (the reference reads them from its peer-to-peer layer, ``src/parallax/p2p/server.py:867-905``):
+        peers are learnt from the scheduler and probed at most once per ``refresh_s``; one that does not answer
+        yet stays unknown and is tried again with the next heartbeat."""
+        try:
+            peers = self.scheduler.node_addresses() or {}
+        except Exception as e:
+            logger.debug("no peer addresses yet: %s", e)
+            return
+        now = time.time()
+        missing = False
+        for nid, url in peers.items():
+            if nid == self.node_id or not url:
+                continue
+            if nid in self.rtt_to_nodes and now - self._rtt_at.get(nid, 0.0) < refresh_s:
+                continue
+            ms = None
+            try:
+                ms = self.probe(url)
+            except Exception:
+                ms = None
+            if ms is None:
+                missing = True
+                continue
+            self.rtt_to_nodes[nid] = float(ms)
+            self._rtt_at[nid] = now
+        for nid in [n for n in self.rtt_to_nodes if n not in peers]:
+            self.rtt_to_nodes.pop(nid, None)
+        self._rtt_missing = missing
+
     def heartbeat_once(self) -> tuple[dict, dict]:
+        self.measure_rtts()
         active = self.state.get_status() == "available"
         alloc, refit = self.scheduler.node_update(self.node_info(is_active=active))
         self._apply_allocation(alloc)
@@ -134,11 +182,14 @@ class NodeAgent:
 
     def start(self) -> None:
         def loop():
-            while not self._stop.wait(self.interval):
+            wait = 0.5          # the first beat follows the join at once: it carries the first measured hops
+            while not self._stop.wait(wait):
                 try:
                     self.heartbeat_once()
                 except Exception as e:
                     logger.warning("heartbeat failed: %s", e)
+                # until every peer has answered a probe (nodes come up at different times) beat faster
+                wait = min(self.interval, 2.0) if self._rtt_missing else self.interval
 
         self._thread = threading.Thread(target=loop, name="NodeHeartbeat", daemon=True)
         self._thread.start()

@@ -123,7 +123,7 @@ class _MemoryPlan:
         self.hardware, self.param_ratio, self.kv_ratio = hardware, param_ratio, kv_ratio
 
     def _device_bytes(self, all_gpus: bool = True) -> float:
-        gpus = self.hardware.num_gpus if all_gpus else 1
+        gpus = max(self.hardware.num_gpus, 1) if all_gpus else 1      # a CPU-only node counts as one device
         return gpus * self.hardware.memory_gb * _BYTES_PER_GIB
 
     @property

@@ -202,8 +202,14 @@ class Scheduler:
             if node.start_layer is None or node.end_layer is None:
                 raise ValueError(f"node {node.node_id} wants a manual placement but names no layer range")
             self.layer_allocator.allocate(node, node.start_layer, node.end_layer)
-            if not self.bootstrapped and self.has_full_pipeline():
-                self._ready.set()
+            if self.has_full_pipeline():
+                # the hand-placed nodes cover every layer: a router that works from registered pipelines learns
+                # them now (it is only asked for a path once it reports a ready pipeline)
+                register = getattr(self.request_router, "bootstrap", None)
+                if register is not None:
+                    register()
+                if not self.bootstrapped:
+                    self._ready.set()
         elif serving and not is_new:
             self.node_manager.upsert(node)      # a re-join replaces the node object
         self.emit_alloc_log_snapshot(reason=f"after {node.node_id} joined")
@@ -370,7 +376,24 @@ class Scheduler:
             if self.request_router.routing_ready():
                 self.dispatch_next_request(timeout=poll_interval)
             else:
+                self._retry_pipeline_registration()
                 time.sleep(max(0.0, poll_interval))
+
+    def _retry_pipeline_registration(self, every_s: float = 1.0) -> None:
+        """A router that works from registered pipelines found none it could price when the cluster came up
+        (the nodes had not measured the hops between them yet): look again until one is ready."""
+        router = self.request_router
+        if not self.bootstrapped or not hasattr(router, "get_registered_pipelines") or not hasattr(router, "bootstrap"):
+            return
+        now = time.time()
+        if now - getattr(self, "_last_registration_try", 0.0) < every_s or router.get_registered_pipelines():
+            return
+        self._last_registration_try = now
+        try:
+            if router.bootstrap():
+                logger.info("pipelines registered: %s", router.get_registered_pipelines())
+        except Exception as e:
+            logger.debug("pipeline registration not possible yet: %s", e)
 
     def start(self, *, poll_interval: float = 0.05) -> None:
         """Start the event thread and the dispatcher without blocking; dispatching begins by itself

@@ -174,3 +174,31 @@ def test_chat_app_forwards_to_backend():
         assert c.post("/v1/chat/completions", json={"messages": []}).json()["choices"][0]["message"]["content"] == "pong"
         assert c.get("/cluster/status_json").json()["data"]["status"] == "available"
         assert "parallax chat" in c.get("/").text
+
+
+def test_node_agent_measures_the_hops_to_its_peers():
+    """The scheduler prices a pipeline by the round trips between its nodes, so every node probes the others it
+    learns of from the scheduler and sends what it measured with its heartbeats; a peer that does not answer yet
+    stays unknown, is tried again, and makes the agent beat faster until then."""
+
+    class Sched:
+        def __init__(self):
+            self.updates = []
+
+        def node_addresses(self):
+            return {"me": "http://me", "b": "http://b", "c": "http://c"}
+
+        def node_update(self, info):
+            self.updates.append(info)
+            return {}, {}
+
+    up = {"http://b": 1.5}
+    sched = Sched()
+    agent = NodeAgent(sched, SharedState.create(in_process=True), "http://me", node_id="me",
+                      hardware=HardwareInfo(1, "NVIDIA B200", 2250.0, 180.0, 7700.0, "cuda"),
+                      probe=lambda url: up.get(url))
+    agent.heartbeat_once()
+    assert sched.updates[-1]["rtt_to_nodes"] == {"b": 1.5} and agent._rtt_missing
+    up["http://c"] = 0.7
+    agent.heartbeat_once()
+    assert sched.updates[-1]["rtt_to_nodes"] == {"b": 1.5, "c": 0.7} and not agent._rtt_missing

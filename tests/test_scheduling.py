@@ -234,9 +234,10 @@ def test_heartbeat_eviction():
     assert sched.get_node("solo") is None and not sched.has_full_pipeline()
 
 
-def test_manual_assignment_bootstraps():
+@pytest.mark.parametrize("routing", ["dp", "rr"])
+def test_manual_assignment_bootstraps(routing):
     m = model(6)
-    sched = Scheduler(m, [], strategy="greedy", routing_strategy="dp")
+    sched = Scheduler(m, [], strategy="greedy", routing_strategy=routing)
     a = node("a100-80g", m, "a", manual_layer_assignment=True, start_layer=0, end_layer=3)
     b = node("a100-80g", m, "b", manual_layer_assignment=True, start_layer=3, end_layer=6)
     sched.enqueue_join(a)

@@ -167,3 +167,64 @@ def test_two_nodes_each_tensor_parallel_over_two_ranks(tmp_path):
                 os.killpg(p.pid, signal.SIGKILL)
         for f in logs:
             f.close()
+
+
+@pytest.mark.parametrize("manual", [True, False])
+def test_scheduler_and_two_joined_nodes_end_to_end(manual, tmp_path):
+    """`parallax run` + two `parallax join` processes + a chat completion through the scheduler: the whole control
+    and data path as separate processes. With layer halves assigned by hand the pipeline has two stages (the nodes
+    measure the hop between them, the scheduler registers the pipeline once it can price it); left to itself the
+    scheduler gives each node the whole (small) model."""
+    ps, p0, p1 = free_port(), free_port(), free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    logs = [open(tmp_path / f"p{i}.log", "w") for i in range(3)]
+    kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
+    node = [sys.executable, "-m", "parallax_b200.launch", "--scheduler-addr", f"127.0.0.1:{ps}", "--random-init",
+            "--host", "127.0.0.1", "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING"]
+    procs = [subprocess.Popen([sys.executable, "-m", "parallax_b200.backend.app", "--host", "127.0.0.1", "--port", str(ps),
+                               "--model-name", "tiny", "--init-nodes-num", "2", "--log-level", "WARNING"], stdout=logs[0], **kw)]
+    try:
+        deadline = time.time() + 60
+        while time.time() < deadline:
+            try:
+                urllib.request.urlopen(f"http://127.0.0.1:{ps}/cluster/status_json", timeout=2).read()
+                break
+            except OSError:
+                time.sleep(0.3)
+        r0, r1 = (["--start-layer", "0", "--end-layer", "2"], ["--start-layer", "2", "--end-layer", "4"]) if manual else ([], [])
+        procs.append(subprocess.Popen(node + ["--port", str(p0)] + r0, stdout=logs[1], **kw))
+        procs.append(subprocess.Popen(node + ["--port", str(p1)] + r1, stdout=logs[2], **kw))
+        status = None
+        deadline = time.time() + 150
+        while time.time() < deadline and all(p.poll() is None for p in procs):
+            with urllib.request.urlopen(f"http://127.0.0.1:{ps}/cluster/status_json", timeout=5) as r:
+                status = json.loads(r.read())["data"]
+            if status["status"] == "available" and len(status["node_list"]) == 2:
+                break
+            time.sleep(0.5)
+        tails = "".join(open(tmp_path / f"p{i}.log").read()[-1500:] for i in range(3))
+        assert status and status["status"] == "available", (status, tails)
+        spans = sorted((n["start_layer"], n["end_layer"]) for n in status["node_list"])
+        assert spans == ([(0, 2), (2, 4)] if manual else [(0, 4), (0, 4)]), status
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 8, "temperature": 0}
+        reply = None
+        for _ in range(20):          # the first node may still be loading when the cluster turns available
+            try:
+                reply = _post(ps, body, timeout=60)
+                break
+            except OSError:
+                time.sleep(1.0)
+        assert reply is not None and reply["usage"]["completion_tokens"] >= 1, tails
+        again = _post(ps, body, timeout=60)
+        assert again["choices"][0]["message"]["content"] == reply["choices"][0]["message"]["content"]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                os.killpg(p.pid, signal.SIGTERM)
+        for p in procs:
+            try:
+                p.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(p.pid, signal.SIGKILL)
+        for f in logs:
+            f.close()
