@@ -65,6 +65,7 @@ class CacheManager:
         )
         self.prefix_slot_base = num_linear_slots
         # hooks for the physical pools of hybrid models: zero / copy a state slot
+        self.weights_epoch = 0          # bumped by invalidate_prefix_cache()
         self.on_zero_slot = None
         self.on_copy_slot = None
         self.prefix_cache: Optional[BlockRadixCache] = None
@@ -75,6 +76,21 @@ class CacheManager:
                 on_evict_linear_slot=self._on_evict_linear_slot,
                 require_linear_slot=self.needs_slots,
             )
+
+    # ------------------------------------------------------------------ weights changed
+    def invalidate_prefix_cache(self) -> int:
+        """The model's weights changed (online refit): K/V pages and state snapshots computed before are stale.
+        Every cached block that no running request holds is freed now, and requests admitted from here on live in
+        a new namespace, so they cannot match what running requests still publish or hold under the old weights
+        (those blocks become evictable when their requests end). Returns the number of blocks freed."""
+        if self.prefix_cache is None:
+            return 0
+        self.weights_epoch += 1
+        freed = self.prefix_cache.evict_lru_blocks(self.num_blocks)
+        root = self.prefix_cache.root
+        for key in [k for k, n in root.children.items() if n.block_id < 0 and not n.children]:
+            del root.children[key]              # empty per-namespace roots of earlier epochs
+        return freed
 
     # ------------------------------------------------------------------ callbacks
     def _on_evict_block(self, block_id: int) -> None:
@@ -139,6 +155,9 @@ class CacheManager:
         if row < 0:
             return False, 0
         st = _ReqState(row)
+        if self.weights_epoch:
+            # blocks written under older weights must not be matched: the epoch is part of the namespace
+            namespace = (namespace, self.weights_epoch)
         st.namespace = namespace
         matched_blocks: list[int] = []
         if self.prefix_cache is not None and token_ids is not None:

@@ -305,6 +305,14 @@ class Engine:
             req.grammar = JsonSchemaMatcher(req.sampling_params.json_schema)
         self.scheduler.enque_request(req)
 
+    def update_weights(self, tensors: dict) -> int:
+        """Online refit of this engine's stages from HF-named tensors (whole layers; see
+        ``DecoderStage.reload_layers``). Cached prefixes were computed with the old weights and are dropped.
+        Call between steps. Returns the number of tensors used."""
+        used = sum(st.model.update_weights(tensors) for st in self.stages)
+        self.cache.invalidate_prefix_cache()
+        return used
+
     def abort_request(self, rid: str) -> Optional[Request]:
         """Returns the request if it was still waiting for admission (it ends here, without a step)."""
         try:

@@ -280,9 +280,14 @@ class NodeRuntime:
         tensor-parallel node every rank applies it to its own slices."""
         from parallax_b200.utils.weight_refit import apply_refit_to_stage
 
-        if self.group is not None:
-            return self.group.command("refit", refit, local=lambda: apply_refit_to_stage(self.peer.worker, self.peer.cfg, refit))
-        return apply_refit_to_stage(self.peer.worker, self.peer.cfg, refit)
+        try:
+            if self.group is not None:
+                return self.group.command("refit", refit,
+                                          local=lambda: apply_refit_to_stage(self.peer.worker, self.peer.cfg, refit))
+            return apply_refit_to_stage(self.peer.worker, self.peer.cfg, refit)
+        finally:
+            # K/V pages cached for prefix reuse were computed with the old weights
+            self.peer.cache.invalidate_prefix_cache()
 
     def serve_until_allocation_changes(self, poll_s: float = 0.5) -> None:
         while not self.state.get_layer_allocation_changed() and self.thread.is_alive():

@@ -15,6 +15,7 @@ with plain HTTP, which is sufficient inside a rack:
 from __future__ import annotations
 
 import logging
+import os
 import threading
 import time
 import uuid
@@ -25,7 +26,8 @@ from parallax_b200.utils.shared_state import SharedState
 
 logger = logging.getLogger(__name__)
 
-HEARTBEAT_INTERVAL_S = 10.0
+# seconds between heartbeats (the reference's node_update period); PARALLAX_HEARTBEAT_INTERVAL_S overrides it
+HEARTBEAT_INTERVAL_S = float(os.environ.get("PARALLAX_HEARTBEAT_INTERVAL_S", "10"))
 
 
 class SchedulerClient:

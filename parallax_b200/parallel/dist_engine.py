@@ -49,6 +49,12 @@ from parallax_b200.parallel.tp_comm import CollectiveTPComm, FusedTPComm
 logger = logging.getLogger(__name__)
 
 
+def _ret_len(lane_plan: dict) -> int:
+    """Length of the int32 message a sampling rank returns for one lane plan."""
+    n = lane_plan["n_logits"]
+    return n + 1 + (n if lane_plan.get("want_prob") else 0)
+
+
 def cu_launch_count() -> int:
     from parallax_b200.ops import cuda as cu
 
@@ -361,7 +367,7 @@ class DistEngine:
         self.h2d_bytes = 0
         self.host_s = {"plan": 0.0, "publish": 0.0, "launch": 0.0, "wait": 0.0, "commit": 0.0}
         # token return: pinned host buffers (tokens + the last stage's status word), reused round-robin
-        self._ret_host = [torch.empty(max_batch_size + 1, dtype=torch.int32, pin_memory=on_gpu)
+        self._ret_host = [torch.empty(2 * max_batch_size + 1, dtype=torch.int32, pin_memory=on_gpu)
                           for _ in range((self.max_in_flight + 2) * self.n_plans)] if rank == 0 else []
         self._ret_n = 0
         # rank 0: the stage's launches run in their own thread (on GPUs; CPU ranks keep one thread)
@@ -492,19 +498,34 @@ class DistEngine:
             from parallax_b200.engine.sampling import apply_penalties
 
             out = apply_penalties(out, lp["pen"])
+        want_prob = bool(lp.get("want_prob"))
+        probs = None
         if lp["greedy"]:
-            tokens = ops.argmax(out)
+            if want_prob:
+                tokens, logp = ops.argmax(out, want_logprob=True)
+                probs = logp.exp()
+            else:
+                tokens = ops.argmax(out)
         else:
             dev = out.device
             sp = lp["sampling"]
-            tokens = ops.sample(out, torch.tensor(sp["t"], dtype=torch.float32, device=dev),
-                                torch.tensor(sp["k"], dtype=torch.int32, device=dev),
-                                torch.tensor(sp["p"], dtype=torch.float32, device=dev),
-                                torch.tensor(sp["mp"], dtype=torch.float32, device=dev),
-                                torch.tensor(sp["u"], dtype=torch.float32, device=dev))
+            args = (out, torch.tensor(sp["t"], dtype=torch.float32, device=dev),
+                    torch.tensor(sp["k"], dtype=torch.int32, device=dev),
+                    torch.tensor(sp["p"], dtype=torch.float32, device=dev),
+                    torch.tensor(sp["mp"], dtype=torch.float32, device=dev),
+                    torch.tensor(sp["u"], dtype=torch.float32, device=dev))
+            if want_prob:
+                tokens, probs = ops.sample(*args, want_prob=True)
+            else:
+                tokens = ops.sample(*args)
         if constrain and lp.get("grammar"):
             tokens = self._constrain(lp, out, tokens)
-        return tokens
+            if want_prob:      # the constrained rows' tokens changed: their probability under the step's logits
+                rows = torch.tensor([int(g[0]) for g in lp["grammar"]], dtype=torch.long, device=out.device)
+                picked = tokens[rows].long().clamp_min(0)
+                probs = probs.clone()
+                probs[rows] = torch.softmax(out[rows].float(), dim=-1).gather(1, picked.view(-1, 1)).view(-1)
+        return (tokens, probs) if want_prob else tokens
 
     def _constrain(self, lp: dict, logits: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
         """Sampling rank: rows of requests with a JSON schema get the best candidate (or a draw among the
@@ -597,16 +618,22 @@ class DistEngine:
             elif n_logits > 0:
                 with torch.inference_mode():        # (penalties update the stage's logits in place)
                     tokens = self._sample(lp, out, constrain=is_sender)
+                probs = None
+                if lp.get("want_prob"):
+                    tokens, probs = tokens
                 if is_sender:
-                    # the status word of the sampling rank rides with the tokens
-                    packed = torch.empty(n_logits + 1, dtype=torch.int32, device=self.device)
+                    # the status word of the sampling rank rides with the tokens; the tokens' probabilities
+                    # (fp32 bit patterns) follow it when some request of the step asked for them
+                    packed = torch.empty(_ret_len(lp), dtype=torch.int32, device=self.device)
                     packed[:n_logits].copy_(tokens)
+                    if probs is not None:
+                        packed[n_logits + 1:].copy_(probs.float().contiguous().view(torch.int32))
                     if on_gpu:
                         from parallax_b200.ops import cuda as cu
 
-                        packed[n_logits:].copy_(cu.status_tensor(self.device))
+                        packed[n_logits:n_logits + 1].copy_(cu.status_tensor(self.device))
                     else:
-                        packed[n_logits:].zero_()
+                        packed[n_logits:n_logits + 1].zero_()
                     tokens = packed
                     if topo.rank != 0:
                         self._pending_sends.append((dist.isend(packed, dst=0, group=self.ret[topo.rank]), packed))
@@ -628,31 +655,31 @@ class DistEngine:
             if p_i is None or p_i["n_logits"] == 0:
                 handles.append(None)
                 continue
-            n = p_i["n_logits"]
+            m = _ret_len(p_i)        # tokens, status word, and the probabilities if they were asked for
             snd = topo.token_senders[i]
             host = self._ret_host[self._ret_n % len(self._ret_host)]
             self._ret_n += 1
             if snd != 0:
                 # post the receive now, in the same order in which the sender posts its sends
                 if not on_gpu:
-                    t = torch.empty(n + 1, dtype=torch.int32, device=self.device)
+                    t = torch.empty(m, dtype=torch.int32, device=self.device)
                     handles.append(("recv", (t, dist.irecv(t, src=snd, group=self.ret[snd]), None, None)))
                     continue
                 # on a side stream: reading the tokens later must not wait for the compute of the
                 # micro-batches that were queued behind this one
                 ev = torch.cuda.Event()
                 with torch.cuda.stream(self._ret_stream):
-                    t = torch.empty(n + 1, dtype=torch.int32, device=self.device)   # from the side stream's pool
+                    t = torch.empty(m, dtype=torch.int32, device=self.device)   # from the side stream's pool
                     work = dist.irecv(t, src=snd, group=self.ret[snd])
                     work.wait()
-                    host[:n + 1].copy_(t, non_blocking=True)
+                    host[:m].copy_(t, non_blocking=True)
                     ev.record()
-                handles.append(("recv", (t, None, host[:n + 1], ev)))
+                handles.append(("recv", (t, None, host[:m], ev)))
             elif on_gpu:
                 ev = torch.cuda.Event()
-                host[:n + 1].copy_(tokens, non_blocking=True)
+                host[:m].copy_(tokens, non_blocking=True)
                 ev.record()
-                handles.append(("recv", (tokens, None, host[:n + 1], ev)))
+                handles.append(("recv", (tokens, None, host[:m], ev)))
             else:
                 handles.append(("have", tokens))
         return handles
@@ -857,6 +884,8 @@ class DistEngine:
         lp = {k: arrays[k] for k in ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables",
                                      "logit_rows", "seq_rows")}
         lp.update(n_logits=len(owners), greedy=greedy)
+        if any(s.req.return_probs for s in owners):
+            lp["want_prob"] = True
         if self.lora is not None and any(getattr(s.req, "lora_slot", -1) >= 0 for s in arrays["ordered"]):
             rows = np.full(arrays["pos"].shape[0], -1, dtype=np.int32)      # adapter slot of every token row
             o = 0
@@ -1004,6 +1033,7 @@ class DistEngine:
             raise self._exec_err.pop(0)
         handles = box[0]
         tokens_of: list = []
+        probs_of: dict = {}
         codes = {}
         for i, arrays in enumerate(arrays_list):
             toks = []
@@ -1014,23 +1044,28 @@ class DistEngine:
                     self._wait_return(ev, work)
                     if ev is not None:
                         t = host
-                toks = t.tolist()
-                codes[self.topo.token_senders[i]] = int(toks.pop())
+                vals = t.tolist()
+                n = len(arrays["owners"])
+                toks = vals[:n]
+                codes[self.topo.token_senders[i]] = int(vals[n])
+                if len(vals) > n + 1:      # the tokens' probabilities follow the status word as fp32 bit patterns
+                    probs_of[i] = np.array(vals[n + 1:], dtype=np.int32).view(np.float32).tolist()
             tokens_of.append(toks)
         self.host_s["wait"] += time.perf_counter() - tw
         self._check_device_status(codes)
         tc = time.perf_counter()
         now = time.time()
-        for pl, arrays, toks in zip(self.planners, arrays_list, tokens_of):
+        for lane, (pl, arrays, toks) in enumerate(zip(self.planners, arrays_list, tokens_of)):
             if arrays is None:
                 continue
             sched, cache = pl.scheduler, pl.cache
-            for s, tok in zip(arrays["owners"], toks):
+            probs = probs_of.get(lane)
+            for j, (s, tok) in enumerate(zip(arrays["owners"], toks)):
                 req = s.req
                 tok = int(tok)
                 g = getattr(req, "grammar", None)
                 if tok >= 0:
-                    req.commit_new_token(tok, now=now)
+                    req.commit_new_token(tok, probs[j] if (probs is not None and req.return_probs) else None, now=now)
                     cache.append_request_token(req.request_id, tok)
                 if g is not None and not req.is_finished:
                     # the document grows by the token's text; it ends the request once it is complete,

@@ -23,6 +23,18 @@ def _post(port: int, body: dict, timeout: float = 120.0) -> dict:
         return json.loads(r.read())
 
 
+def _probs(reply: dict) -> list:
+    """The reply's fingerprint: the probability of every generated token (the text of a random-init model is mostly
+    unprintable, so comparing contents would compare empty strings)."""
+    probs = reply["choices"][0]["token_probs"]
+    assert len(probs) == reply["usage"]["completion_tokens"] >= 1
+    return [float(p) for p in probs]
+
+
+def _close(a: list, b: list, rel: float = 2e-3) -> bool:
+    return len(a) == len(b) and all(abs(x - y) <= rel * max(abs(x), abs(y)) for x, y in zip(a, b))
+
+
 @pytest.mark.parametrize("model,topo", [("tiny", ["--pp-size", "2"]),
                                         ("tiny-moe", ["--ep-size", "2", "--enable-dp-attention"])])
 def test_serve_with_in_box_topology(model, topo, tmp_path):
@@ -44,11 +56,11 @@ def test_serve_with_in_box_topology(model, topo, tmp_path):
             except OSError:
                 time.sleep(0.5)
         assert up, open(tmp_path / "serve.log").read()[-3000:]
-        body = {"model": model, "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0}
+        body = {"model": model, "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0, "return_probs": True}
         a = _post(port, body)
         b = _post(port, body)
         assert a["usage"]["completion_tokens"] >= 1
-        assert a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+        assert _close(_probs(a), _probs(b))      # (the second time the prompt comes from the prefix cache)
         # constrained decoding runs on the rank that samples (the last stage, or every expert-parallel lane)
         schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}
         c = _post(port, dict(body, max_tokens=80,
@@ -93,11 +105,11 @@ def test_two_nodes_with_manual_layer_ranges_and_no_scheduler(tmp_path):
                 except OSError:
                     time.sleep(0.5)
             assert up, "".join(open(tmp_path / f"n{i}.log").read()[-1500:] for i in range(3))
-        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 8, "temperature": 0}
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 8, "temperature": 0, "return_probs": True}
         split = _post(p0, body)
         whole = _post(p2, body)
         assert split["usage"]["completion_tokens"] == whole["usage"]["completion_tokens"] >= 1
-        assert split["choices"][0]["message"]["content"] == whole["choices"][0]["message"]["content"]
+        assert _close(_probs(split), _probs(whole)), (_probs(split), _probs(whole))
         with urllib.request.urlopen(f"http://127.0.0.1:{p1}/peer/info", timeout=5) as r:
             info = json.loads(r.read())
         assert (info["start_layer"], info["end_layer"]) == (2, 4) and f"http://127.0.0.1:{p0}" in info["peers"]
@@ -152,10 +164,10 @@ def test_two_nodes_each_tensor_parallel_over_two_ranks(tmp_path):
                     time.sleep(0.5)
             assert up, "".join(open(tmp_path / f"n{i}.log").read()[-2000:] for i in range(3))
         for content, n in (("hello there", 8), ("a much longer prompt " * 6, 5)):
-            body = {"model": "tiny", "messages": [{"role": "user", "content": content}], "max_tokens": n, "temperature": 0}
+            body = {"model": "tiny", "messages": [{"role": "user", "content": content}], "max_tokens": n, "temperature": 0, "return_probs": True}
             split, whole = _post(p0, body), _post(p2, body)
             assert split["usage"]["completion_tokens"] == whole["usage"]["completion_tokens"] >= 1
-            assert split["choices"][0]["message"]["content"] == whole["choices"][0]["message"]["content"]
+            assert _close(_probs(split), _probs(whole)), (_probs(split), _probs(whole))
     finally:
         for p in procs:
             if p.poll() is None:
@@ -206,7 +218,7 @@ def test_scheduler_and_two_joined_nodes_end_to_end(manual, tmp_path):
         assert status and status["status"] == "available", (status, tails)
         spans = sorted((n["start_layer"], n["end_layer"]) for n in status["node_list"])
         assert spans == ([(0, 2), (2, 4)] if manual else [(0, 4), (0, 4)]), status
-        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 8, "temperature": 0}
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 8, "temperature": 0, "return_probs": True}
         reply = None
         for _ in range(20):          # the first node may still be loading when the cluster turns available
             try:
@@ -216,7 +228,106 @@ def test_scheduler_and_two_joined_nodes_end_to_end(manual, tmp_path):
                 time.sleep(1.0)
         assert reply is not None and reply["usage"]["completion_tokens"] >= 1, tails
         again = _post(ps, body, timeout=60)
-        assert again["choices"][0]["message"]["content"] == reply["choices"][0]["message"]["content"]
+        assert _close(_probs(again), _probs(reply))
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                os.killpg(p.pid, signal.SIGTERM)
+        for p in procs:
+            try:
+                p.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(p.pid, signal.SIGKILL)
+        for f in logs:
+            f.close()
+
+
+def test_refit_reaches_every_node_of_a_running_cluster(tmp_path):
+    """Online weight refit end to end: the scheduler hands a refit request (content-addressed blocks on disk) to
+    both nodes of a two-stage pipeline with their heartbeats; afterwards the cluster answers as a model with the
+    new weights does."""
+    import torch
+    from fastapi.testclient import TestClient
+    from safetensors.torch import save_file
+
+    from parallax_b200.engine.engine import Engine
+    from parallax_b200.engine.service import EngineLoop
+    from parallax_b200.frontend.openai_api import create_app
+    from parallax_b200.frontend.tokenizer import TokenizerWrapper
+    from parallax_b200.models.config import named_config
+    from parallax_b200.utils.weight_refit import calculate_cid
+    from tests.test_engine_gpu import _export_weights
+
+    cfg = named_config("tiny")
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 8, "temperature": 0, "return_probs": True}
+
+    def local_reply(seed):
+        torch.manual_seed(0)
+        eng = Engine(cfg, device="cpu", num_blocks=64, page_size=16, max_batch_size=4, max_total_length=256, seed=seed)
+        loop = EngineLoop(eng)
+        loop.start()
+        try:
+            with TestClient(create_app(loop, TokenizerWrapper.from_pretrained(None, vocab_size=cfg.vocab_size), "tiny", 256)) as c:
+                return _probs(c.post("/v1/chat/completions", json=body).json()), eng
+        finally:
+            loop.stop()
+
+    before, _ = local_reply(0)
+    after, other = local_reply(7)
+    assert not _close(before, after)
+    w = _export_weights(other)
+    w.pop("lm_head.weight", None)
+    names = sorted(w)
+    index_map, paths = {}, {}
+    for i, group in enumerate((names[0::2], names[1::2])):
+        f = tmp_path / f"block{i}.safetensors"
+        save_file({k: w[k].contiguous() for k in group}, str(f))
+        cid = calculate_cid(f.read_bytes())
+        paths[cid] = str(f)
+        index_map.update({k: cid for k in group})
+
+    ps, p0, p1 = free_port(), free_port(), free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT, PARALLAX_HEARTBEAT_INTERVAL_S="1")
+    logs = [open(tmp_path / f"p{i}.log", "w") for i in range(3)]
+    kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
+    node = [sys.executable, "-m", "parallax_b200.launch", "--scheduler-addr", f"127.0.0.1:{ps}", "--random-init",
+            "--host", "127.0.0.1", "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING",
+            "--enable-weight-refit"]
+    procs = [subprocess.Popen([sys.executable, "-m", "parallax_b200.backend.app", "--host", "127.0.0.1", "--port", str(ps),
+                               "--model-name", "tiny", "--init-nodes-num", "2", "--log-level", "WARNING",
+                               "--enable-weight-refit", "true"], stdout=logs[0], **kw)]
+    try:
+        deadline = time.time() + 60
+        while time.time() < deadline:
+            try:
+                urllib.request.urlopen(f"http://127.0.0.1:{ps}/cluster/status_json", timeout=2).read()
+                break
+            except OSError:
+                time.sleep(0.3)
+        procs.append(subprocess.Popen(node + ["--port", str(p0), "--start-layer", "0", "--end-layer", "2"], stdout=logs[1], **kw))
+        procs.append(subprocess.Popen(node + ["--port", str(p1), "--start-layer", "2", "--end-layer", "4"], stdout=logs[2], **kw))
+
+        def chat():
+            for _ in range(40):
+                try:
+                    return _probs(_post(ps, body, timeout=60))
+                except OSError:
+                    time.sleep(1.0)
+            raise AssertionError("".join(open(tmp_path / f"p{i}.log").read()[-1500:] for i in range(3)))
+
+        assert _close(chat(), before)
+        req = urllib.request.Request(f"http://127.0.0.1:{ps}/weight/refit", headers={"Content-Type": "application/json"},
+                                     data=json.dumps({"time_stamp": time.time(), "cid": sorted(paths), "index_map": index_map,
+                                                      "paths": paths}).encode())
+        assert urllib.request.urlopen(req, timeout=10).status == 200
+        got = None
+        deadline = time.time() + 60
+        while time.time() < deadline:
+            got = chat()
+            if _close(got, after):
+                break
+            time.sleep(1.0)
+        assert _close(got, after), (got, after, before)
     finally:
         for p in procs:
             if p.poll() is None:

@@ -95,3 +95,31 @@ def test_refit_request_applied_to_a_live_stage(tmp_path):
     bad.write_bytes(raw[:-1] + bytes([raw[-1] ^ 0xFF]))
     with pytest.raises(ValueError):
         apply_refit_to_stage(live.stages[0], cfg, refit)
+
+
+def test_refit_drops_cached_prefixes():
+    """K/V pages cached for prefix reuse belong to the weights that computed them: after a refit the same prompt
+    must be computed anew, also while a request that started before the refit still runs and publishes blocks."""
+    from tests.test_engine_gpu import _export_weights
+
+    cfg = named_config("tiny")
+    kw = dict(device="cpu", num_blocks=64, page_size=16, max_batch_size=4, max_total_length=128)
+    live, other = Engine(cfg, seed=0, **kw), Engine(cfg, seed=7, **kw)
+    prompt = list(range(5, 60))
+    want = _first_logits(other, prompt)
+    _first_logits(live, prompt)                       # fills the prefix cache of the live engine
+    assert live.cache.prefix_cache.num_nodes >= 3
+    running = Request(input_ids=prompt[:40] + [7, 7, 7], sampling_params=SamplingParams(max_new_tokens=30, temperature=0.0,
+                                                                                      ignore_eos=True))
+    live.add_request(running)
+    live.step()                                       # a request of the old weights is in flight during the refit
+    w = _export_weights(other)
+    w.pop("lm_head.weight", None)
+    live.update_weights(w)
+    while live.has_work():                            # it ends under the new weights and leaves its blocks behind
+        live.step()
+    hits = live.cache.prefix_cache.hits
+    got = _first_logits(live, prompt)
+    assert live.cache.prefix_cache.hits == hits       # nothing of the old epoch was matched
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
+    assert running.is_finished and not live.cache.reqs
