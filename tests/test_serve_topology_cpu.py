@@ -339,3 +339,98 @@ def test_refit_reaches_every_node_of_a_running_cluster(tmp_path):
                 os.killpg(p.pid, signal.SIGKILL)
         for f in logs:
             f.close()
+
+
+def _wait_status(ps: int, want: str, nodes: int, timeout_s: float = 120.0) -> dict:
+    status = None
+    deadline = time.time() + timeout_s
+    while time.time() < deadline:
+        try:
+            with urllib.request.urlopen(f"http://127.0.0.1:{ps}/cluster/status_json", timeout=5) as r:
+                status = json.loads(r.read())["data"]
+            if status["status"] == want and len(status["node_list"]) == nodes:
+                return status
+        except OSError:
+            pass
+        time.sleep(0.4)
+    raise AssertionError(f"cluster did not become {want} with {nodes} node(s): {status}")
+
+
+def _post_to(url: str, body: dict, timeout: float = 60.0):
+    req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=timeout) as r:
+            return r.status, json.loads(r.read())
+    except urllib.error.HTTPError as e:
+        return e.code, json.loads(e.read() or b"{}")
+
+
+def test_router_in_front_of_a_cluster_whose_node_leaves_and_is_replaced(tmp_path):
+    """Router -> scheduler -> node as processes. The node is stopped (it says goodbye), the cluster goes back to
+    waiting and requests are answered with an error instead of hanging; a new node joins and service resumes,
+    through the same router registration."""
+    import urllib.error  # noqa: F401  (used by _post_to)
+
+    pr, ps, p0, p1 = free_port(), free_port(), free_port(), free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT, PARALLAX_HEARTBEAT_INTERVAL_S="1")
+    logs = [open(tmp_path / f"p{i}.log", "w") for i in range(4)]
+    kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
+    node = [sys.executable, "-m", "parallax_b200.launch", "--scheduler-addr", f"127.0.0.1:{ps}", "--random-init",
+            "--host", "127.0.0.1", "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING"]
+    procs = {
+        "sched": subprocess.Popen([sys.executable, "-m", "parallax_b200.backend.app", "--host", "127.0.0.1", "--port", str(ps),
+                                   "--model-name", "tiny", "--init-nodes-num", "1", "--log-level", "WARNING"], stdout=logs[0], **kw),
+        "router": subprocess.Popen([sys.executable, "-m", "parallax_b200.router.app", "--host", "127.0.0.1", "--port", str(pr)],
+                                   stdout=logs[1], **kw),
+    }
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 6, "temperature": 0,
+            "return_probs": True}
+    try:
+        _wait_status(ps, "waiting", 0, 60)
+        procs["a"] = subprocess.Popen(node + ["--port", str(p0)], stdout=logs[2], **kw)
+        _wait_status(ps, "available", 1)
+        for _ in range(100):
+            try:
+                urllib.request.urlopen(f"http://127.0.0.1:{pr}/health", timeout=2).read()
+                break
+            except OSError:
+                time.sleep(0.2)
+        code, reg = _post_to(f"http://127.0.0.1:{pr}/register", {"endpoint": f"http://127.0.0.1:{ps}"})
+        assert code == 200 and reg["base_url"].endswith(str(ps)), reg
+        first = None
+        for _ in range(30):
+            code, first = _post_to(f"http://127.0.0.1:{pr}/v1/chat/completions", body)
+            if code == 200:
+                break
+            time.sleep(1.0)
+        assert code == 200, first
+        fp = _probs(first)
+        # the node goes away
+        os.killpg(procs["a"].pid, signal.SIGTERM)
+        procs["a"].wait(30)
+        _wait_status(ps, "waiting", 0, 60)
+        t0 = time.time()
+        code, err = _post_to(f"http://127.0.0.1:{pr}/v1/chat/completions", body, timeout=90)
+        assert code >= 400 and time.time() - t0 < 80, (code, err)          # an error, not a hang
+        # a replacement joins
+        procs["b"] = subprocess.Popen(node + ["--port", str(p1)], stdout=logs[3], **kw)
+        _wait_status(ps, "available", 1)
+        again = None
+        for _ in range(40):
+            code, again = _post_to(f"http://127.0.0.1:{pr}/v1/chat/completions", body)
+            if code == 200:
+                break
+            time.sleep(1.0)
+        assert code == 200, again
+        assert _close(_probs(again), fp)
+    finally:
+        for p in procs.values():
+            if p.poll() is None:
+                os.killpg(p.pid, signal.SIGTERM)
+        for p in procs.values():
+            try:
+                p.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(p.pid, signal.SIGKILL)
+        for f in logs:
+            f.close()
