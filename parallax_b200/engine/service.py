@@ -50,6 +50,9 @@ class EngineLoop:
     # ---- client side (any thread)
     def submit(self, req: Request) -> "queue.Queue[TokenEvent]":
         q: "queue.Queue[TokenEvent]" = queue.Queue()
+        if self._stop.is_set():
+            q.put(TokenEvent(req.request_id, None, True, RequestStatus.ERROR, error="the engine stopped serving"))
+            return q
         with self._lock:
             self._streams[req.request_id] = q
         self._inbox.put(("add", req))
@@ -60,14 +63,21 @@ class EngineLoop:
 
     def start(self) -> None:
         if self._thread is None:
+            self._stop.clear()
             self._thread = threading.Thread(target=self._run, name="EngineLoop", daemon=True)
             self._thread.start()
 
     def stop(self, timeout: float = 5.0) -> None:
+        """Stop stepping and end every open stream with an error event, so that nobody waits for tokens that will
+        never come; requests submitted afterwards are refused the same way."""
         self._stop.set()
         if self._thread is not None:
             self._thread.join(timeout)
             self._thread = None
+        with self._lock:
+            open_streams, self._streams = self._streams, {}
+        for rid, q in open_streams.items():
+            q.put(TokenEvent(rid, None, True, RequestStatus.ERROR, error="the engine stopped serving"))
 
     @property
     def num_inflight(self) -> int:

@@ -196,9 +196,11 @@ def run_scheduler_mode(args) -> None:
     if info is None:
         raise SystemExit("no layer allocation received from the scheduler within 300 s")
     agent.start()
+    own_model_path = args.model_path      # None: serve whatever model the scheduler names, also after it changes
     try:
         while True:
             info = state.get_model_info()
+            args.model_path = own_model_path or info["model_name"]
             runtime = NodeRuntime(args, agent, state, info["model_name"], info["block_start_index"],
                                   info["block_end_index"])
             agent.on_refit = runtime.apply_refit

@@ -47,6 +47,10 @@ class PeerLoop:
     # ---- frontend side
     def submit(self, req: Request):
         q: "queue.Queue[TokenEvent]" = queue.Queue()
+        if self._stop.is_set():
+            q.put(TokenEvent(req.request_id, None, True, RequestStatus.ERROR,
+                             error="the node stopped serving (shutdown or reload)"))
+            return q
         with self._lock:
             self._streams[req.request_id] = q
         if not req.routing_table and self.default_route is not None:
@@ -79,9 +83,16 @@ class PeerLoop:
         self._thread.start()
 
     def stop(self) -> None:
+        """Stop stepping and end every open stream with an error event: a client whose request was in flight (or
+        arrived while the node was going down, e.g. for a new layer allocation) gets an answer instead of waiting
+        for one that will never come. Requests submitted after this are refused the same way."""
         self._stop.set()
         if self._thread is not None:
             self._thread.join(5.0)
+        with self._lock:
+            open_streams, self._streams = self._streams, {}
+        for rid, q in open_streams.items():
+            q.put(TokenEvent(rid, None, True, RequestStatus.ERROR, error="the node stopped serving (shutdown or reload)"))
 
     # ---- loop
     def _emit(self, req: Request, tok) -> None:

@@ -434,3 +434,57 @@ def test_router_in_front_of_a_cluster_whose_node_leaves_and_is_replaced(tmp_path
                 os.killpg(p.pid, signal.SIGKILL)
         for f in logs:
             f.close()
+
+
+def test_switching_the_model_reloads_the_joined_node(tmp_path):
+    """`POST /scheduler/init` with another model while a node is serving: the node learns the new allocation from
+    its next heartbeat, reloads its executor and serves the new model - the elastic path of a running cluster."""
+    ps, p0 = free_port(), free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT, PARALLAX_HEARTBEAT_INTERVAL_S="1")
+    logs = [open(tmp_path / f"p{i}.log", "w") for i in range(2)]
+    kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
+    procs = [subprocess.Popen([sys.executable, "-m", "parallax_b200.backend.app", "--host", "127.0.0.1", "--port", str(ps),
+                               "--model-name", "tiny", "--init-nodes-num", "1", "--log-level", "WARNING"], stdout=logs[0], **kw)]
+    body = {"messages": [{"role": "user", "content": "hello there"}], "max_tokens": 6, "temperature": 0, "return_probs": True}
+
+    def chat():
+        last = None
+        for _ in range(40):
+            code, last = _post_to(f"http://127.0.0.1:{ps}/v1/chat/completions", body)
+            if code == 200:
+                return last
+            time.sleep(1.0)
+        raise AssertionError((last, "".join(open(tmp_path / f"p{i}.log").read()[-1500:] for i in range(2))))
+
+    try:
+        _wait_status(ps, "waiting", 0, 60)
+        procs.append(subprocess.Popen([sys.executable, "-m", "parallax_b200.launch", "--scheduler-addr", f"127.0.0.1:{ps}",
+                                       "--random-init", "--host", "127.0.0.1", "--port", str(p0), "--max-batch-size", "4",
+                                       "--max-sequence-length", "256", "--log-level", "INFO"], stdout=logs[1], **kw))
+        assert _wait_status(ps, "available", 1)["model_name"] == "tiny"
+        dense = _probs(chat())
+        code, _r = _post_to(f"http://127.0.0.1:{ps}/scheduler/init", {"model_name": "tiny-moe", "init_nodes_num": 1})
+        assert code == 200
+        deadline = time.time() + 90
+        moe = None
+        while time.time() < deadline:
+            st = _wait_status(ps, "available", 1, 90)
+            if st["model_name"] == "tiny-moe":
+                reply = chat()
+                moe = _probs(reply)
+                if not _close(moe, dense):
+                    break
+            time.sleep(1.0)
+        assert moe is not None and not _close(moe, dense)
+        assert "reloading the executor" in open(tmp_path / "p1.log").read()
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                os.killpg(p.pid, signal.SIGTERM)
+        for p in procs:
+            try:
+                p.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(p.pid, signal.SIGKILL)
+        for f in logs:
+            f.close()
