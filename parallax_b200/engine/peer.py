@@ -237,6 +237,13 @@ class PeerExecutor:
             if req is None:
                 continue
             if pk.abort or pk.status in (RequestStatus.FINISHED_ABORT, RequestStatus.ERROR):
+                if req.num_cached_tokens > 0 and not req.output_ids:
+                    # a later peer refused a prompt whose first part this peer skipped as cached: it does not
+                    # hold that prefix (any more - it may have restarted). Forget the cached prefixes here, so
+                    # that the next request sends whole prompts down the pipeline again.
+                    logger.warning("request %s was refused downstream with %d cached prompt tokens: dropping this "
+                                   "peer's cached prefixes", req.request_id, req.num_cached_tokens)
+                    self.cache.invalidate_prefix_cache()
                 req.abort = True
                 self._commit(req, None, None, events, releases)
                 continue

@@ -200,7 +200,8 @@ def create_app(loop: EngineLoop, tokenizer: TokenizerWrapper, model_name: str, m
                         finish = "stop"
                     if ev.finished:
                         text += detok.flush()
-                        finish = finish or ("error" if ev.error else _FINISH.get(ev.status, "stop"))
+                        finish = finish or ("error" if (ev.error or ev.status == RequestStatus.ERROR)
+                                            else _FINISH.get(ev.status, "stop"))
                     if text or first:
                         yield _chunk(req.request_id, chat, created, text, None, first)
                         first = False
@@ -226,6 +227,8 @@ def create_app(loop: EngineLoop, tokenizer: TokenizerWrapper, model_name: str, m
             if ev.finished:
                 pieces.append(detok.flush())
                 err = ev.error
+                if err is None and ev.status == RequestStatus.ERROR:
+                    err = "the request failed on the serving node (a pipeline peer did not answer, or a step failed)"
                 finish = finish or _FINISH.get(ev.status, "stop")
         if err:
             return openai_error_response(err, status_code=500)

@@ -111,6 +111,37 @@ class PeerLoop:
             if table and len(table) > 1:
                 self.transport.send_abort([rid], table, self.peer.node_id)
 
+    def _forward(self, packets, tables: dict) -> None:
+        """Hand packets to their next hops. What cannot be delivered (the peer died or is unknown) ends its request
+        here: the first peer fails it towards the client and releases it everywhere; a later peer frees its share
+        and tells the first peer, which does the rest."""
+        lost = self.transport.send_forward(packets, self.peer.node_id)
+        if not lost:
+            return
+        peer = self.peer
+        if peer.is_first:
+            releases = []
+            for pk in lost:
+                req = peer.scheduler.get_running_request(pk.request_id)
+                if req is None or req.is_finished:
+                    continue
+                req.update_status(RequestStatus.ERROR)
+                peer.scheduler.evict_request(req.request_id)
+                peer.cache.free_request(req.request_id)
+                self._emit(req, None)
+                releases.append(req.request_id)
+            self._broadcast_release(releases, tables)
+            return
+        from parallax_b200.engine.request import IntermediateRequest
+
+        for pk in lost:
+            peer.release([pk.request_id])
+            table = pk.routing_table or []
+            if table and table[0] != peer.node_id:
+                bad = IntermediateRequest(pk.request_id, pk.current_position, RequestStatus.FINISHED_ABORT, routing_table=table)
+                bad.abort = True
+                self.transport.send_to(table[0], [bad])
+
     def _run(self) -> None:
         peer = self.peer
         tables: dict[str, list[str]] = {}
@@ -153,7 +184,7 @@ class PeerLoop:
                             out = peer.process_packets(payload)
                             self.steps += 1
                             if out:
-                                self.transport.send_forward(out, peer.node_id)
+                                self._forward(out, tables)
                             if self.state is not None:
                                 self.state.update_metrics(current_requests=len(peer.mirror),
                                                           layer_latency_ms_sample=(time.perf_counter() - t0) * 1e3 / n_layers)
@@ -177,7 +208,7 @@ class PeerLoop:
                     self._emit(req, tok)
                 self._broadcast_release(releases, tables)
                 if packets:
-                    self.transport.send_forward(packets, peer.node_id)
+                    self._forward(packets, tables)
                 if self.state is not None and (packets or events):
                     self.state.update_metrics(current_requests=peer.scheduler.num_running_requests,
                                               layer_latency_ms_sample=(time.perf_counter() - t0) * 1e3 / n_layers)

@@ -219,10 +219,13 @@ class PeerTransport:
             return
         import httpx
 
-        httpx.post(url, content=body, headers={"content-type": "application/msgpack"}, timeout=600, trust_env=False)
+        # a peer that is gone fails the connect at once; one that is busy may take long to answer
+        httpx.post(url, content=body, headers={"content-type": "application/msgpack"},
+                   timeout=httpx.Timeout(600.0, connect=5.0), trust_env=False)
 
-    def send_forward(self, packets, self_id: str) -> None:
-        """Group packets by their next hop in the routing table and ship one message per hop."""
+    def send_forward(self, packets, self_id: str) -> list:
+        """Group packets by their next hop in the routing table and ship one message per hop. Returns the packets
+        that could not be delivered (the next peer is gone or unknown)."""
         from parallax_b200.p2p.message_util import request_to_proto
 
         groups: dict[str, list] = {}
@@ -235,20 +238,34 @@ class PeerTransport:
             else:
                 continue
             groups.setdefault(nxt, []).append(pk)
+        undelivered = []
         for nid, group in groups.items():
-            url = self.resolve(nid)
-            if url is None:
-                logger.warning("no address for peer %s; dropping %d packet(s)", nid, len(group))
-                continue
-            t0 = time.time()
-            blob = request_to_proto(group)
+            if not self.send_to(nid, group):
+                undelivered.extend(group)
+        return undelivered
+
+    def send_to(self, nid: str, group: list) -> bool:
+        """Ship packets to one peer. False when the peer has no address or does not answer."""
+        from parallax_b200.p2p.message_util import request_to_proto
+
+        url = self.resolve(nid)
+        if url is None:
+            logger.warning("no address for peer %s; %d packet(s) not delivered", nid, len(group))
+            return False
+        t0 = time.time()
+        blob = request_to_proto(group)
+        try:
             self._post(url.rstrip("/") + "/pp_forward", blob)
-            logger.debug("sent %.2f MB to %s in %.1f ms", len(blob) / 1e6, nid, (time.time() - t0) * 1e3)
-            if self.notify_url:
-                try:
-                    self._post(self.notify_url, blob[:0])
-                except Exception:
-                    pass
+        except Exception as e:
+            logger.warning("peer %s did not take %d packet(s): %s", nid, len(group), e)
+            return False
+        logger.debug("sent %.2f MB to %s in %.1f ms", len(blob) / 1e6, nid, (time.time() - t0) * 1e3)
+        if self.notify_url:
+            try:
+                self._post(self.notify_url, blob[:0])
+            except Exception:
+                pass
+        return True
 
     def send_abort(self, request_ids: list[str], routing_table: list[str], self_id: str) -> None:
         from parallax_b200.p2p.message_util import abort_request_to_proto

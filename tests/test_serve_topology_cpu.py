@@ -488,3 +488,68 @@ def test_switching_the_model_reloads_the_joined_node(tmp_path):
                 os.killpg(p.pid, signal.SIGKILL)
         for f in logs:
             f.close()
+
+
+def test_a_peer_that_dies_fails_requests_instead_of_hanging_them(tmp_path):
+    """Two peers without a scheduler; the second is killed outright. A request then ends with an error within
+    seconds (the first peer cannot deliver the activations), the first peer keeps serving, and once a second peer
+    is back on the same address requests complete again."""
+    import urllib.error  # noqa: F401
+
+    p0, p1 = free_port(), free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    common = [sys.executable, "-m", "parallax_b200.launch", "--model-path", "tiny", "--random-init", "--host", "127.0.0.1",
+              "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING"]
+    second = common + ["--port", str(p1), "--start-layer", "2", "--end-layer", "4", "--initial-peers", f"127.0.0.1:{p0}"]
+    logs = [open(tmp_path / f"n{i}.log", "w") for i in range(3)]
+    kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
+    procs = [subprocess.Popen(common + ["--port", str(p0), "--start-layer", "0", "--end-layer", "2", "--initial-peers",
+                                        f"127.0.0.1:{p1}"], stdout=logs[0], **kw),
+             subprocess.Popen(second, stdout=logs[1], **kw)]
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 6, "temperature": 0,
+            "return_probs": True}
+
+    def wait_up(port, path):
+        deadline = time.time() + 120
+        while time.time() < deadline:
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}{path}", timeout=2) as r:
+                    if r.status == 200:
+                        return
+            except OSError:
+                time.sleep(0.4)
+        raise AssertionError(f"{port}{path} did not come up")
+
+    try:
+        wait_up(p0, "/v1/models")
+        wait_up(p1, "/peer/info")
+        code, ok = _post_to(f"http://127.0.0.1:{p0}/v1/chat/completions", body)
+        assert code == 200
+        fp = _probs(ok)
+        os.killpg(procs[1].pid, signal.SIGKILL)
+        procs[1].wait(10)
+        t0 = time.time()
+        code, err = _post_to(f"http://127.0.0.1:{p0}/v1/chat/completions", body, timeout=60)
+        assert code >= 500 and time.time() - t0 < 30, (code, err, time.time() - t0)
+        procs.append(subprocess.Popen(second, stdout=logs[2], **kw))
+        wait_up(p1, "/peer/info")
+        # the new peer does not hold the prefix that the first peer has cached for this prompt: the first attempt may
+        # come back aborted (no tokens), which makes the first peer drop its cached prefixes; the retry completes
+        again = None
+        for _ in range(20):
+            code, again = _post_to(f"http://127.0.0.1:{p0}/v1/chat/completions", body)
+            if code == 200 and again["usage"]["completion_tokens"] >= 1:
+                break
+            time.sleep(1.0)
+        assert code == 200 and _close(_probs(again), fp), again
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                os.killpg(p.pid, signal.SIGTERM)
+        for p in procs:
+            try:
+                p.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(p.pid, signal.SIGKILL)
+        for f in logs:
+            f.close()
