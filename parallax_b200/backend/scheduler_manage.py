@@ -12,6 +12,7 @@ rack needs.
 from __future__ import annotations
 
 import logging
+import os
 import time
 from typing import Optional
 
@@ -140,9 +141,13 @@ class SchedulerManage:
         self.is_local_network = is_local_network
         self.model_name, self.init_nodes_num = model_name, init_nodes_num
         info = model_info or get_model_info(model_name, self.use_hfcache)
+        kw = dict(self.scheduler_kwargs)
+        if "heartbeat_timeout" not in kw and os.environ.get("PARALLAX_HEARTBEAT_TIMEOUT_S"):
+            # seconds of silence after which a node is dropped from the cluster (default 30)
+            kw["heartbeat_timeout"] = float(os.environ["PARALLAX_HEARTBEAT_TIMEOUT_S"])
         self.scheduler = Scheduler(info, [], min_nodes_bootstrapping=init_nodes_num,
                                    enable_weight_refit=self.enable_weight_refit,
-                                   weight_refit_mode=self.weight_refit_mode, **self.scheduler_kwargs)
+                                   weight_refit_mode=self.weight_refit_mode, **kw)
         self.connection_handler = NodeRPCHandler(self.scheduler, self.call_urls)
         self.scheduler.start(poll_interval=0.05)
 

@@ -553,3 +553,58 @@ def test_a_peer_that_dies_fails_requests_instead_of_hanging_them(tmp_path):
                 os.killpg(p.pid, signal.SIGKILL)
         for f in logs:
             f.close()
+
+
+def test_a_joined_node_that_dies_is_dropped_and_its_requests_fail_fast(tmp_path):
+    """Scheduler + two hand-placed nodes; the second is killed outright (no goodbye). Requests routed through the
+    broken pipeline end with an error within seconds, the scheduler drops the silent node after its heartbeat
+    time-out and reports the cluster as waiting; when a node takes the vacant layers the cluster serves again."""
+    import urllib.error  # noqa: F401
+
+    ps, p0, p1, p2 = free_port(), free_port(), free_port(), free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT, PARALLAX_HEARTBEAT_INTERVAL_S="1", PARALLAX_HEARTBEAT_TIMEOUT_S="5")
+    logs = [open(tmp_path / f"p{i}.log", "w") for i in range(4)]
+    kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
+    node = [sys.executable, "-m", "parallax_b200.launch", "--scheduler-addr", f"127.0.0.1:{ps}", "--random-init",
+            "--host", "127.0.0.1", "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING"]
+    procs = [subprocess.Popen([sys.executable, "-m", "parallax_b200.backend.app", "--host", "127.0.0.1", "--port", str(ps),
+                               "--model-name", "tiny", "--init-nodes-num", "2", "--log-level", "WARNING"], stdout=logs[0], **kw)]
+    body = {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 6, "temperature": 0,
+            "return_probs": True}
+
+    def chat_ok(tries=40):
+        last = None
+        for _ in range(tries):
+            code, last = _post_to(f"http://127.0.0.1:{ps}/v1/chat/completions", body)
+            if code == 200 and last["usage"]["completion_tokens"] >= 1:
+                return last
+            time.sleep(1.0)
+        raise AssertionError((last, "".join(open(tmp_path / f"p{i}.log").read()[-1200:] for i in range(4))))
+
+    try:
+        _wait_status(ps, "waiting", 0, 60)
+        procs.append(subprocess.Popen(node + ["--port", str(p0), "--start-layer", "0", "--end-layer", "2"], stdout=logs[1], **kw))
+        procs.append(subprocess.Popen(node + ["--port", str(p1), "--start-layer", "2", "--end-layer", "4"], stdout=logs[2], **kw))
+        _wait_status(ps, "available", 2)
+        fp = _probs(chat_ok())
+        os.killpg(procs[2].pid, signal.SIGKILL)
+        procs[2].wait(10)
+        t0 = time.time()
+        code, err = _post_to(f"http://127.0.0.1:{ps}/v1/chat/completions", body, timeout=90)
+        assert code >= 400 and time.time() - t0 < 45, (code, err, time.time() - t0)
+        st = _wait_status(ps, "waiting", 1, 60)                  # the silent node is gone from the list
+        assert [(n["start_layer"], n["end_layer"]) for n in st["node_list"]] in ([(0, 2)], [(None, None)])
+        procs.append(subprocess.Popen(node + ["--port", str(p2), "--start-layer", "2", "--end-layer", "4"], stdout=logs[3], **kw))
+        _wait_status(ps, "available", 2)
+        assert _close(_probs(chat_ok()), fp)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                os.killpg(p.pid, signal.SIGTERM)
+        for p in procs:
+            try:
+                p.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(p.pid, signal.SIGKILL)
+        for f in logs:
+            f.close()
