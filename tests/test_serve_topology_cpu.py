@@ -260,6 +260,17 @@ def test_scheduler_and_two_joined_nodes_end_to_end(manual, tmp_path):
         assert reply is not None and reply["usage"]["completion_tokens"] >= 1, tails
         again = _post(ps, body, timeout=60)
         assert _close(_probs(again), _probs(reply))
+        # the same through the scheduler as a stream: SSE chunks, a usage chunk, the end marker
+        req = urllib.request.Request(f"http://127.0.0.1:{ps}/v1/chat/completions", headers={"Content-Type": "application/json"},
+                                     data=json.dumps(dict(body, stream=True)).encode())
+        with urllib.request.urlopen(req, timeout=60) as r:
+            assert r.headers.get("content-type", "").startswith("text/event-stream")
+            lines = [ln.decode() for ln in r.read().split(b"\n") if ln.startswith(b"data: ")]
+        assert lines[-1].strip() == "data: [DONE]"
+        chunks = [json.loads(ln[6:]) for ln in lines[:-1]]
+        usage = [c["usage"] for c in chunks if c.get("usage")]
+        assert usage and usage[-1]["completion_tokens"] == reply["usage"]["completion_tokens"]
+        assert any(c["choices"] and c["choices"][0].get("finish_reason") for c in chunks)
     finally:
         for p in procs:
             if p.poll() is None:
@@ -644,3 +655,45 @@ def test_a_joined_node_that_dies_is_dropped_and_its_requests_fail_fast(tmp_path)
                 os.killpg(p.pid, signal.SIGKILL)
         for f in logs:
             f.close()
+
+
+@_retry_startup
+def test_in_box_server_ends_when_one_of_its_ranks_dies(tmp_path):
+    """`parallax serve --pp-size 2`: when a worker rank is killed the serving process notices (child exit, or the
+    rank's heartbeat in the control channel going stale), fails what is in flight and exits with an error status
+    instead of hanging - a supervisor can restart it."""
+    psutil = pytest.importorskip("psutil")
+    port = free_port()
+    log = open(tmp_path / "serve.log", "w")
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    proc = subprocess.Popen([sys.executable, "-m", "parallax_b200.launch", "--model-path", "tiny", "--random-init", "--port",
+                             str(port), "--host", "127.0.0.1", "--max-batch-size", "4", "--max-sequence-length", "256",
+                             "--log-level", "WARNING", "--pp-size", "2"], cwd=ROOT, env=env, stdout=log,
+                            stderr=subprocess.STDOUT, start_new_session=True)
+    try:
+        deadline = time.time() + 120
+        up = False
+        while time.time() < deadline and proc.poll() is None:
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=2) as r:
+                    up = r.status == 200
+                    break
+            except OSError:
+                time.sleep(0.5)
+        if not up:
+            raise _StartupError(open(tmp_path / "serve.log").read()[-3000:])
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0}
+        assert _post(port, body)["usage"]["completion_tokens"] >= 1
+        workers = [c for c in psutil.Process(proc.pid).children(recursive=True) if "parallax_b200.parallel.launcher" in " ".join(c.cmdline())]
+        assert len(workers) == 1, [c.cmdline() for c in psutil.Process(proc.pid).children(recursive=True)]
+        workers[0].kill()
+        code = proc.wait(60)                     # the server goes down by itself ...
+        assert code != 0                         # ... and says so
+    finally:
+        if proc.poll() is None:
+            os.killpg(proc.pid, signal.SIGTERM)
+            try:
+                proc.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(proc.pid, signal.SIGKILL)
+        log.close()
