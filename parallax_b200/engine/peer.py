@@ -44,9 +44,12 @@ class PeerExecutor:
                  enable_prefix_cache: bool = True, max_total_length: int = 32768,
                  request_timeout_s: Optional[float] = 600, eos_token_id=None, seed: int = 0,
                  weights: Optional[dict] = None, shared_state=None, kv_cache_dtype: Optional[str] = None,
-                 stage_group=None):
+                 stage_group=None, lora: Optional[dict] = None):
         """``stage_group`` (:class:`parallax_b200.parallel.peer_group.TPStageGroup`): the node's GPUs run this
-        peer's layers tensor-parallel; this process is rank 0 of that group and the group owns the stage worker."""
+        peer's layers tensor-parallel; this process is rank 0 of that group and the group owns the stage worker.
+        ``lora``: per-request adapters ``{"max_loaded", "max_rank", "paths": {name: dir}}``; every peer keeps the
+        slots of its own layers and loads an adapter when the first packet that names it arrives (the adapter's
+        name travels with the packets, as in ``src/parallax/server/request.py:268-393``)."""
         self.cfg, self.node_id = cfg, node_id
         self.device = torch.device(device)
         self.group = stage_group
@@ -68,6 +71,15 @@ class PeerExecutor:
         self.builder = BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size, max_batch_size,
                                     self.cache.max_blocks_per_seq)
         self.mirror: dict[str, Request] = {}   # later peers: per-request shadow state
+        self.lora = None
+        if lora:
+            from parallax_b200.loader.lora import LoRAManager, LoRAStack
+
+            if stage_group is not None or not hasattr(self.worker.model, "lora"):
+                raise ValueError("per-request LoRA on a pipeline peer needs a single-GPU stage of a GQA decoder family")
+            n_slots = int(lora.get("max_loaded") or 4)
+            self.worker.model.lora = LoRAStack(self.worker.model, n_slots, int(lora.get("max_rank") or 64))
+            self.lora = LoRAManager([self.worker.model.lora], n_slots, lora.get("paths"))
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(seed + 777)
 
@@ -94,9 +106,19 @@ class PeerExecutor:
             if on_gpu:
                 _cuda.status_copy_async(self.device)
             return arrays, out
+        extra = None
+        if self.lora is not None and any(getattr(s.req, "lora_slot", -1) >= 0 for s in arrays["ordered"]):
+            import numpy as np
+
+            rows = np.full(arrays["pos"].shape[0], -1, dtype=np.int32)      # adapter slot of every token row
+            o = 0
+            for s in arrays["ordered"]:
+                rows[o:o + s.num_tokens] = getattr(s.req, "lora_slot", -1)
+                o += s.num_tokens
+            extra = {"lora_ids": rows}
         fb = self.builder.build(arrays["ids"] if self.is_first else None, arrays["pos"], arrays["slots"],
                                 arrays["p_q"], arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"],
-                                arrays["d_tables"], arrays["logit_rows"])
+                                arrays["d_tables"], arrays["logit_rows"], extra=extra)
         with torch.inference_mode():
             if self.is_last:
                 h = self.worker.model.embed_tokens(fb) if self.is_first else hidden
@@ -152,11 +174,25 @@ class PeerExecutor:
             o += n
         return out
 
+    # ------------------------------------------------------------------ adapters
+    def _acquire_lora(self, req: Request) -> None:
+        req.lora_slot = getattr(req, "lora_slot", -1)
+        if req.lora_path and req.lora_slot < 0:
+            if self.lora is None:
+                raise ValueError("this node was started without LoRA support (--enable-lora)")
+            req.lora_slot = self.lora.acquire(req.lora_path)       # loads the adapter if it is not resident
+
+    def _release_lora(self, req: Optional[Request]) -> None:
+        if req is not None and self.lora is not None and getattr(req, "lora_slot", -1) >= 0:
+            self.lora.release(req.lora_path)
+            req.lora_slot = -1
+
     # ------------------------------------------------------------------ first peer
     def add_request(self, req: Request) -> None:
         assert self.is_first, "requests enter the pipeline at the first peer"
         req.sampling_params.verify()
         req.max_total_length = min(req.max_total_length, self.planner.max_total_length)
+        self._acquire_lora(req)
         self.scheduler.enque_request(req)
 
     def has_work(self) -> bool:
@@ -212,6 +248,7 @@ class PeerExecutor:
     def _finish_first(self, req: Request, events, releases) -> None:
         self.scheduler.evict_request(req.request_id)
         self.cache.free_request(req.request_id)
+        self._release_lora(req)
         events.append((req, None))
         releases.append(req.request_id)
 
@@ -221,6 +258,7 @@ class PeerExecutor:
             self.cache.update_request_tokens(req.request_id, [int(tok)])
         if self.scheduler.check_and_update_request_status(req):
             self.cache.free_request(req.request_id)
+            self._release_lora(req)
             releases.append(req.request_id)
             events.append((req, tok))
         else:
@@ -253,7 +291,7 @@ class PeerExecutor:
     # ------------------------------------------------------------------ later peers
     def release(self, request_ids) -> None:
         for rid in request_ids:
-            self.mirror.pop(rid, None)
+            self._release_lora(self.mirror.pop(rid, None))
             self.cache.free_request(rid)
 
     def _admit_packet(self, pk: IntermediateRequest) -> Optional[ScheduledSeq]:
@@ -265,11 +303,17 @@ class PeerExecutor:
             if m is None:
                 m = Request(request_id=rid, input_ids=ids, sampling_params=pk.sampling_params,
                             routing_table=pk.routing_table, return_probs=pk.return_probs,
-                            max_total_length=self.planner.max_total_length)
-                ok, matched = self.cache.allocate_request(rid, end, token_ids=ids)
+                            max_total_length=self.planner.max_total_length, lora_path=pk.lora_path)
+                ok, matched = self.cache.allocate_request(rid, end, token_ids=ids, namespace=pk.lora_path)
                 if not ok or matched < pk.chunk_start:
                     if ok:
                         self.cache.free_request(rid)
+                    return None
+                try:
+                    self._acquire_lora(m)
+                except Exception as e:
+                    logger.warning("request %s: adapter %r cannot be served here: %s", rid, pk.lora_path, e)
+                    self.cache.free_request(rid)
                     return None
                 self.mirror[rid] = m
             else:

@@ -249,7 +249,7 @@ class NodeRuntime:
 
         from parallax_b200.engine.peer import PeerExecutor
         from parallax_b200.frontend.tokenizer import TokenizerWrapper
-        from parallax_b200.launch import resolve_model, serve_http
+        from parallax_b200.launch import _lora_spec, resolve_model, serve_http
         from parallax_b200.p2p.server import PeerTransport
 
         self.args, self.agent, self.state = args, agent, state
@@ -284,7 +284,8 @@ class NodeRuntime:
                                  max_total_length=args.max_sequence_length,
                                  request_timeout_s=args.request_timeout_s, weights=weights, shared_state=state,
                                  num_blocks=(self.group.num_blocks if self.group is not None
-                                             else (None if device != "cpu" else 1024)))
+                                             else (None if device != "cpu" else 1024)),
+                                 lora=_lora_spec(args) if self.group is None else None)
         self.peer_urls: dict[str, str] = {}
 
         def resolve(node_id: str):

@@ -132,3 +132,48 @@ def test_later_peer_out_of_kv_drops_only_that_request():
     # the aborted request produced correct tokens up to the point where it was dropped
     a = aborted[0]
     assert a.output_ids == want[reqs.index(a)][:len(a.output_ids)]
+
+
+def test_per_request_adapters_travel_with_the_packets(tmp_path):
+    """Every peer keeps the adapter slots of its own layers and loads an adapter when the first packet that names it
+    arrives; the chained peers produce what the single engine with the same adapters produces, and every pin is
+    released at the end."""
+    from tests.test_lora_cpu import _make_adapter
+
+    cfg = named_config("tiny")
+    lora = {"max_loaded": 2, "max_rank": 8,
+            "paths": {"x": _make_adapter(cfg, tmp_path / "x", 1), "y": _make_adapter(cfg, tmp_path / "y", 2, rank=8, alpha=4)}}
+    prompts = _prompts(4, 27, cfg.vocab_size, seed=8)
+    lora_of = ["x", None, "y", "x"]
+    sp = dict(max_new_tokens=5, temperature=0.0, ignore_eos=True)
+    eng = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=8, lora=lora)
+    ref = [Request(input_ids=p, sampling_params=SamplingParams(**sp), lora_path=a) for p, a in zip(prompts, lora_of)]
+    for r in ref:
+        eng.add_request(r)
+    while eng.has_work():
+        eng.step()
+    peers = [PeerExecutor(cfg, s, e, device="cpu", node_id=f"n{i}", num_blocks=128, max_batch_size=8, lora=lora)
+             for i, (s, e) in enumerate([(0, 1), (1, 3), (3, 4)])]
+    table = [p.node_id for p in peers]
+    reqs = [Request(input_ids=p, routing_table=table, sampling_params=SamplingParams(**sp), lora_path=a)
+            for p, a in zip(prompts, lora_of)]
+    for r in reqs:
+        peers[0].add_request(r)
+    steps = 0
+    while peers[0].has_work() and steps < 300:
+        steps += 1
+        packets, _events, releases = peers[0].step_first()
+        for peer in peers[1:]:
+            peer.release(releases)
+        back = []
+        for peer in peers[1:]:
+            packets = peer.process_packets(_wire(packets))
+            back = packets
+        _events, releases = peers[0].receive_tokens(_wire([p for p in back if p.hidden_states is None]))
+        for peer in peers[1:]:
+            peer.release(releases)
+    assert [r.output_ids for r in reqs] == [r.output_ids for r in ref]
+    base = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=8).generate(prompts, SamplingParams(**sp))
+    assert reqs[1].output_ids == base[1] and (reqs[0].output_ids != base[0] or reqs[2].output_ids != base[2])
+    for p in peers:
+        assert not any(p.lora.pins.values()) and not p.mirror and not p.cache.reqs
