@@ -71,6 +71,13 @@ class PeerExecutor:
         self.builder = BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size, max_batch_size,
                                     self.cache.max_blocks_per_seq)
         self.mirror: dict[str, Request] = {}   # later peers: per-request shadow state
+        # JSON-schema constrained requests: the peer that samples (the last one) keeps a matcher per request and
+        # picks among the step's candidates; the first peer keeps a twin to know when the document is complete
+        self.tokenizer = None                  # anything with token_text(id) and eos_token_ids; set by the node runtime
+        self._grammars: dict = {}
+        import random as _random
+
+        self._py_rng = _random.Random(seed + 777)
         self.lora = None
         if lora:
             from parallax_b200.loader.lora import LoRAManager, LoRAStack
@@ -140,7 +147,7 @@ class PeerExecutor:
             ids, lp = ops.argmax(logits, want_logprob=True)
             out = ids.tolist(), lp.exp().tolist()
             self._raise_if_device_error()
-            return out
+            return self._constrain(logits, owners, *out)
         dev = logits.device
         t = torch.tensor([0.0 if sp.is_greedy else sp.temperature for sp in sps], dtype=torch.float32, device=dev)
         k = torch.tensor([sp.top_k if sp.top_k > 0 else 0 for sp in sps], dtype=torch.int32, device=dev)
@@ -150,7 +157,37 @@ class PeerExecutor:
         ids, pr = ops.sample(logits, t, k, p, mp, u, want_prob=True)
         out = ids.tolist(), pr.tolist()
         self._raise_if_device_error()
-        return out
+        return self._constrain(logits, owners, *out)
+
+    def _constrain(self, logits: torch.Tensor, owners: list[ScheduledSeq], ids: list, probs: list):
+        """Rows of requests with a JSON schema: the best candidate (or a draw among the valid ones) whose text
+        keeps the request's document valid replaces the sampled token; ``None`` where nothing fits (the request
+        ends). The matcher advances with every token picked here: this peer is the only one that samples."""
+        if not any(s.req.sampling_params.json_schema for s in owners):
+            return ids, probs
+        from parallax_b200.engine.structured import JsonSchemaMatcher, TokenChooser
+
+        tok = self.tokenizer
+        if tok is None:
+            raise RuntimeError("a constrained request reached a peer that has no tokenizer")
+        chooser = TokenChooser(tok.token_text, sorted(getattr(tok, "eos_token_ids", ()) or ()))
+        for row, s in enumerate(owners):
+            sp = s.req.sampling_params
+            if not sp.json_schema:
+                continue
+            g = self._grammars.get(s.req.request_id)
+            if g is None:
+                g = self._grammars[s.req.request_id] = JsonSchemaMatcher(sp.json_schema)
+            choice = chooser.choose(g, logits[row], 0.0 if sp.is_greedy else sp.temperature, self._py_rng)
+            if choice is None:
+                ids[row] = None
+                continue
+            text = tok.token_text(int(choice))
+            if text and not g.done:
+                g.advance(text)
+            ids[row] = int(choice)
+            probs[row] = float(torch.softmax(logits[row].float(), dim=-1)[int(choice)])
+        return ids, probs
 
     def _raise_if_device_error(self) -> None:
         """After a synchronising read of a batch's outputs: fail the batch if one of its kernels gave up."""
@@ -193,6 +230,13 @@ class PeerExecutor:
         req.sampling_params.verify()
         req.max_total_length = min(req.max_total_length, self.planner.max_total_length)
         self._acquire_lora(req)
+        req.grammar = None
+        if req.sampling_params.json_schema:
+            if self.tokenizer is None:
+                raise ValueError("json_schema needs a node that knows its tokenizer")
+            from parallax_b200.engine.structured import JsonSchemaMatcher
+
+            req.grammar = JsonSchemaMatcher(req.sampling_params.json_schema)
         self.scheduler.enque_request(req)
 
     def has_work(self) -> bool:
@@ -237,6 +281,8 @@ class PeerExecutor:
             idx = {id(s): i for i, s in enumerate(arrays["owners"])}
             for s in arrays["ordered"]:
                 i = idx.get(id(s))
+                if i is not None and toks[i] is None:          # no token keeps the constrained document valid
+                    s.req.update_status(RequestStatus.FINISHED_EOS)
                 self._commit(s.req, None if i is None else toks[i], None if i is None else probs[i], events, releases)
             return [], events, releases
         packets = self._hidden_packets(arrays, h)
@@ -249,6 +295,7 @@ class PeerExecutor:
         self.scheduler.evict_request(req.request_id)
         self.cache.free_request(req.request_id)
         self._release_lora(req)
+        self._grammars.pop(req.request_id, None)
         events.append((req, None))
         releases.append(req.request_id)
 
@@ -256,9 +303,16 @@ class PeerExecutor:
         if tok is not None:
             req.commit_new_token(int(tok), prob if req.return_probs else None)
             self.cache.update_request_tokens(req.request_id, [int(tok)])
+            g = getattr(req, "grammar", None)
+            if g is not None and not req.is_finished:
+                # the document grows by the token's text; it ends the request once it is complete
+                text = self.tokenizer.token_text(int(tok))
+                if not text or not g.advance(text) or g.done:
+                    req.update_status(RequestStatus.FINISHED_EOS)
         if self.scheduler.check_and_update_request_status(req):
             self.cache.free_request(req.request_id)
             self._release_lora(req)
+            self._grammars.pop(req.request_id, None)
             releases.append(req.request_id)
             events.append((req, tok))
         else:
@@ -273,6 +327,10 @@ class PeerExecutor:
         for pk in packets:
             req = self.scheduler.get_running_request(pk.request_id)
             if req is None:
+                continue
+            if pk.status == RequestStatus.FINISHED_EOS and pk.next_token_id is None:
+                req.update_status(RequestStatus.FINISHED_EOS)       # the sampling peer ended a constrained request
+                self._commit(req, None, None, events, releases)
                 continue
             if pk.abort or pk.status in (RequestStatus.FINISHED_ABORT, RequestStatus.ERROR):
                 if req.num_cached_tokens > 0 and not req.output_ids:
@@ -292,6 +350,7 @@ class PeerExecutor:
     def release(self, request_ids) -> None:
         for rid in request_ids:
             self._release_lora(self.mirror.pop(rid, None))
+            self._grammars.pop(rid, None)
             self.cache.free_request(rid)
 
     def _admit_packet(self, pk: IntermediateRequest) -> Optional[ScheduledSeq]:
@@ -378,6 +437,10 @@ class PeerExecutor:
             toks, probs = self._sample(logits, arrays["owners"])
             for s, t, p in zip(arrays["owners"], toks, probs):
                 r = s.req
+                if t is None:      # no token keeps the constrained document valid: the request ends with what it has
+                    out.append(IntermediateRequest(r.request_id, r.total_length, RequestStatus.FINISHED_EOS,
+                                                   routing_table=r.routing_table, sampling_params=r.sampling_params))
+                    continue
                 out.append(IntermediateRequest(r.request_id, r.total_length + 1, RequestStatus.DECODING,
                                                next_token_id=int(t), routing_table=r.routing_table,
                                                sampling_params=r.sampling_params, token_prob=float(p),

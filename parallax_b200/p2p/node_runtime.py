@@ -298,6 +298,11 @@ class NodeRuntime:
 
         self.loop = PeerLoop(self.peer, PeerTransport(resolve, notify_url=args.notify_url), state)
         tok = TokenizerWrapper.from_pretrained(path, vocab_size=cfg.vocab_size) if self.peer.is_first else None
+        from parallax_b200.frontend.tokenizer import LazyTokenizer
+
+        # constrained decoding turns token ids into text where tokens are sampled (the last peer) and where the
+        # document's end is noticed (the first peer)
+        self.peer.tokenizer = tok if tok is not None else LazyTokenizer(path, cfg.vocab_size)
         self.app = create_peer_app(self.loop, tok, name, args.max_sequence_length)
 
         @self.app.post("/peers")

@@ -177,3 +177,54 @@ def test_per_request_adapters_travel_with_the_packets(tmp_path):
     assert reqs[1].output_ids == base[1] and (reqs[0].output_ids != base[0] or reqs[2].output_ids != base[2])
     for p in peers:
         assert not any(p.lora.pins.values()) and not p.mirror and not p.cache.reqs
+
+
+def test_constrained_requests_through_chained_peers():
+    """The last peer samples under the request's JSON schema, the first peer notices the end of the document: the reply
+    is a valid document and equals the single engine's; the unconstrained request next to it is untouched."""
+    import json
+
+    from parallax_b200.engine.structured import JsonSchemaMatcher
+    from parallax_b200.frontend.tokenizer import TokenizerWrapper
+
+    cfg = named_config("tiny")
+    tok = TokenizerWrapper.from_pretrained(None, vocab_size=cfg.vocab_size)
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}, "n": {"type": "integer"}}, "required": ["ok", "n"]}
+    prompts = [[t % 250 for t in p] for p in _prompts(2, 19, cfg.vocab_size, seed=9)]
+    sps = [dict(max_new_tokens=120, temperature=0.0, json_schema=json.dumps(schema)),
+           dict(max_new_tokens=5, temperature=0.0, ignore_eos=True)]
+    eng = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=8, tokenizer=tok)
+    ref = [Request(input_ids=p, sampling_params=SamplingParams(**sp)) for p, sp in zip(prompts, sps)]
+    for r in ref:
+        eng.add_request(r)
+    while eng.has_work():
+        eng.step()
+    for spans in ([(0, 4)], [(0, 2), (2, 4)]):
+        peers = [PeerExecutor(cfg, s, e, device="cpu", node_id=f"n{i}", num_blocks=128, max_batch_size=8)
+                 for i, (s, e) in enumerate(spans)]
+        for p in peers:
+            p.tokenizer = tok
+        table = [p.node_id for p in peers]
+        reqs = [Request(input_ids=p, routing_table=table, sampling_params=SamplingParams(**sp)) for p, sp in zip(prompts, sps)]
+        for r in reqs:
+            peers[0].add_request(r)
+        steps = 0
+        while peers[0].has_work() and steps < 400:
+            steps += 1
+            packets, _events, releases = peers[0].step_first()
+            for peer in peers[1:]:
+                peer.release(releases)
+            back = []
+            for peer in peers[1:]:
+                packets = peer.process_packets(_wire(packets))
+                back = packets
+            if len(peers) > 1:
+                _events, releases = peers[0].receive_tokens(_wire([p for p in back if p.hidden_states is None]))
+                for peer in peers[1:]:
+                    peer.release(releases)
+        text = tok.decode(reqs[0].output_ids)
+        m = JsonSchemaMatcher(schema)
+        assert m.advance(text) and m.done and set(json.loads(text)) >= {"ok", "n"}, text
+        assert reqs[0].status.name == "FINISHED_EOS" and len(reqs[0].output_ids) < 120
+        assert [r.output_ids for r in reqs] == [r.output_ids for r in ref]
+        assert not peers[-1]._grammars and not any(p.cache.reqs for p in peers)

@@ -260,6 +260,11 @@ def test_scheduler_and_two_joined_nodes_end_to_end(manual, tmp_path):
         assert reply is not None and reply["usage"]["completion_tokens"] >= 1, tails
         again = _post(ps, body, timeout=60)
         assert _close(_probs(again), _probs(reply))
+        # a JSON-schema request through the scheduler: the last node samples under the schema
+        schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}
+        constrained = _post(ps, dict(body, max_tokens=80, response_format={"type": "json_schema",
+                                                                           "json_schema": {"name": "x", "schema": schema}}))
+        assert isinstance(json.loads(constrained["choices"][0]["message"]["content"])["ok"], bool)
         # the same through the scheduler as a stream: SSE chunks, a usage chunk, the end marker
         req = urllib.request.Request(f"http://127.0.0.1:{ps}/v1/chat/completions", headers={"Content-Type": "application/json"},
                                      data=json.dumps(dict(body, stream=True)).encode())
