@@ -57,12 +57,19 @@ class PeerExecutor:
         # config advertises (positions beyond that length are the caller's choice, as with the reference's
         # on-the-fly rotary embedding); a table cut at the advertised length was read out of bounds
         max_positions = max_total_length + 8
+        max_requests = max(max_batch_size * 2, 16)
+        if cfg.has_linear_layers:
+            # recurrent layers keep one state slot per request (the cache manager's row of the request). Prefix
+            # reuse would need state snapshots that every peer of a pipeline holds for the same prefixes; peers
+            # cache independently, so hybrid models run without the prefix cache here
+            enable_prefix_cache = False
         if stage_group is not None:
             self.worker = stage_group.worker
         else:
             self.worker = StageWorker(cfg, start_layer, end_layer, self.device, dtype, page_size, num_blocks=num_blocks,
                                       kv_fraction=kv_fraction, seed=seed, weights=weights, max_positions=max_positions,
-                                      kv_cache_dtype=kv_cache_dtype)
+                                      kv_cache_dtype=kv_cache_dtype,
+                                      num_linear_slots=max_requests if cfg.has_linear_layers else 0)
         self.is_first, self.is_last = self.worker.is_first, self.worker.is_last
         self.planner = Planner(cfg, self.worker.num_blocks, page_size, max_batch_size, max_num_tokens_per_batch,
                                micro_batch_ratio, chunked_prefill_size, enable_prefix_cache, max_total_length,
@@ -125,7 +132,7 @@ class PeerExecutor:
             extra = {"lora_ids": rows}
         fb = self.builder.build(arrays["ids"] if self.is_first else None, arrays["pos"], arrays["slots"],
                                 arrays["p_q"], arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"],
-                                arrays["d_tables"], arrays["logit_rows"], extra=extra)
+                                arrays["d_tables"], arrays["logit_rows"], arrays["seq_rows"], extra=extra)
         with torch.inference_mode():
             if self.is_last:
                 h = self.worker.model.embed_tokens(fb) if self.is_first else hidden

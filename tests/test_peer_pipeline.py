@@ -228,3 +228,21 @@ def test_constrained_requests_through_chained_peers():
         assert reqs[0].status.name == "FINISHED_EOS" and len(reqs[0].output_ids) < 120
         assert [r.output_ids for r in reqs] == [r.output_ids for r in ref]
         assert not peers[-1]._grammars and not any(p.cache.reqs for p in peers)
+
+
+def test_every_model_family_through_chained_peers():
+    """MLA, sparse-indexer, block-sparse, hybrid (recurrent state slots) and MoE models split over two peers, with
+    prompts that share a prefix and prompt slices, against the single engine."""
+    for name in ("tiny-hybrid", "tiny-mla", "tiny-dsa", "tiny-msa", "tiny-moe"):
+        cfg = named_config(name)
+        L = cfg.num_hidden_layers
+        g = torch.Generator().manual_seed(1)
+        shared = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
+        prompts = [shared + torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 9)] \
+            + _prompts(1, 23, cfg.vocab_size, seed=3)
+        want = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=8).generate(
+            prompts, SamplingParams(max_new_tokens=5, temperature=0.0, ignore_eos=True))
+        got, peers = _run_pipeline(cfg, [(0, L // 2), (L // 2, L)], prompts, 5, chunked_prefill_size=16)
+        assert got == want, name
+        for p in peers:
+            assert not p.cache.reqs and not p.mirror, name
