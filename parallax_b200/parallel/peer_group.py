@@ -32,7 +32,7 @@ from parallax_b200.parallel.ctrl_channel import CtrlChannel
 
 logger = logging.getLogger(__name__)
 
-_ARRAYS = ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables", "logit_rows")
+_ARRAYS = ("ids", "pos", "slots", "p_q", "p_ctx", "p_tables", "d_ctx", "d_tables", "logit_rows", "seq_rows")
 
 
 class TPStageGroup:
@@ -75,7 +75,8 @@ class TPStageGroup:
         self.worker = StageWorker(cfg, start_layer, end_layer, self.device, dtype, page_size, num_blocks=num_blocks,
                                   kv_fraction=kv_fraction, seed=seed, weights=weights,
                                   max_positions=max_total_length + 8, tp_rank=self.rank, tp_size=self.tp,
-                                  tp_group=self.tp_group, comm=comm, kv_cache_dtype=kv_cache_dtype)
+                                  tp_group=self.tp_group, comm=comm, kv_cache_dtype=kv_cache_dtype,
+                                  num_linear_slots=max(max_batch_size * 2, 16) if cfg.has_linear_layers else 0)
         nb = torch.tensor([self.worker.num_blocks], dtype=torch.int64)
         dist.all_reduce(nb, op=dist.ReduceOp.MIN, group=self.ctrl)      # every rank must agree on the KV blocks
         self.worker.num_blocks = self.num_blocks = int(nb)
@@ -99,7 +100,7 @@ class TPStageGroup:
         a, T = plan["arrays"], plan["rows"]
         model = self.worker.model
         fb = self.builder.build(a["ids"] if model.is_first else None, a["pos"], a["slots"], a["p_q"], a["p_ctx"],
-                                a["p_tables"], a["d_ctx"], a["d_tables"], a["logit_rows"])
+                                a["p_tables"], a["d_ctx"], a["d_tables"], a["logit_rows"], a.get("seq_rows"))
         rp = self.comm.rows_per_rank(T)
         with torch.inference_mode():
             if plan["has_hidden"]:

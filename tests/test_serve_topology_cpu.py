@@ -162,14 +162,15 @@ def test_two_nodes_with_manual_layer_ranges_and_no_scheduler(tmp_path):
     assert me.route(9) is None
 
 
+@pytest.mark.parametrize("model", ["tiny", "tiny-hybrid"])
 @_retry_startup
-def test_two_nodes_each_tensor_parallel_over_two_ranks(tmp_path):
+def test_two_nodes_each_tensor_parallel_over_two_ranks(model, tmp_path):
     """Two pipeline peers without a scheduler, each running its half of the layers tensor-parallel over two
     processes (`--tp-size 2`): rank 0 of a node owns the peer executor and hands every batch to its follower
     through the node's control channel. Same reply as one process with all layers."""
     p0, p1, p2 = free_port(), free_port(), free_port()
     env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
-    common = [sys.executable, "-m", "parallax_b200.launch", "--model-path", "tiny", "--random-init", "--host", "127.0.0.1",
+    common = [sys.executable, "-m", "parallax_b200.launch", "--model-path", model, "--random-init", "--host", "127.0.0.1",
               "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING"]
     logs = [open(tmp_path / f"n{i}.log", "w") for i in range(3)]
     kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
@@ -194,7 +195,7 @@ def test_two_nodes_each_tensor_parallel_over_two_ranks(tmp_path):
             if not up:
                 raise _StartupError("".join(open(tmp_path / f"n{i}.log").read()[-2000:] for i in range(3)))
         for content, n in (("hello there", 8), ("a much longer prompt " * 6, 5)):
-            body = {"model": "tiny", "messages": [{"role": "user", "content": content}], "max_tokens": n, "temperature": 0, "return_probs": True}
+            body = {"model": model, "messages": [{"role": "user", "content": content}], "max_tokens": n, "temperature": 0, "return_probs": True}
             split, whole = _post(p0, body), _post(p2, body)
             assert split["usage"]["completion_tokens"] == whole["usage"]["completion_tokens"] >= 1
             assert _close(_probs(split), _probs(whole)), (_probs(split), _probs(whole))
