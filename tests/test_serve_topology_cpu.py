@@ -703,3 +703,50 @@ def test_in_box_server_ends_when_one_of_its_ranks_dies(tmp_path):
             except subprocess.TimeoutExpired:
                 os.killpg(proc.pid, signal.SIGKILL)
         log.close()
+
+
+@_retry_startup
+def test_cli_serve_and_graceful_shutdown(tmp_path):
+    """The `parallax` command itself: `serve` (with an in-box pipeline, so that there are worker processes) answers
+    requests, and an interrupt takes the whole process tree down without leaving ranks behind."""
+    psutil = pytest.importorskip("psutil")
+    port = free_port()
+    log = open(tmp_path / "cli.log", "w")
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    proc = subprocess.Popen([sys.executable, "-m", "parallax_b200.cli", "serve", "-m", "tiny", "--random-init", "--port", str(port),
+                             "--host", "127.0.0.1", "--max-batch-size", "4", "--max-sequence-length", "256", "--pp-size", "2",
+                             "--log-level", "WARNING"], cwd=ROOT, env=env, stdout=log, stderr=subprocess.STDOUT,
+                            start_new_session=True)
+    try:
+        deadline = time.time() + 120
+        up = False
+        while time.time() < deadline and proc.poll() is None:
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=2) as r:
+                    up = r.status == 200
+                    break
+            except OSError:
+                time.sleep(0.5)
+        if not up:
+            raise _StartupError(open(tmp_path / "cli.log").read()[-3000:])
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 5, "temperature": 0}
+        assert _post(port, body)["usage"]["completion_tokens"] >= 1
+        tree = psutil.Process(proc.pid).children(recursive=True)
+        assert len(tree) >= 2, [c.cmdline() for c in tree]          # the launcher and at least one worker rank
+        proc.send_signal(signal.SIGINT)
+        proc.wait(40)
+        gone, alive = psutil.wait_procs(tree, timeout=20)
+        assert not alive, [c.cmdline() for c in alive]
+    finally:
+        if proc.poll() is None:
+            os.killpg(proc.pid, signal.SIGTERM)
+            try:
+                proc.wait(20)
+            except subprocess.TimeoutExpired:
+                os.killpg(proc.pid, signal.SIGKILL)
+        else:
+            try:
+                os.killpg(proc.pid, signal.SIGKILL)      # whatever is left of the group
+            except ProcessLookupError:
+                pass
+        log.close()
