@@ -313,6 +313,16 @@ class Engine:
         self.cache.invalidate_prefix_cache()
         return used
 
+    def apply_refit(self, refit: dict) -> int:
+        """A refit request in the scheduler's format (``index_map``: weight -> content id, ``paths``: content id ->
+        readable file): every stage takes the blocks of its layers, checks them against their ids and reloads.
+        Call between steps (``EngineLoop.call`` does). Returns the number of tensors used."""
+        from parallax_b200.utils.weight_refit import apply_refit_to_stage
+
+        used = sum(apply_refit_to_stage(st, self.cfg, refit) for st in self.stages)
+        self.cache.invalidate_prefix_cache()
+        return used
+
     def abort_request(self, rid: str) -> Optional[Request]:
         """Returns the request if it was still waiting for admission (it ends here, without a step)."""
         try:

@@ -61,6 +61,15 @@ class EngineLoop:
     def abort(self, request_id: str) -> None:
         self._inbox.put(("abort", request_id))
 
+    def call(self, fn):
+        """Run ``fn()`` on the engine thread between two steps (weight refit, cache maintenance). Returns a
+        ``concurrent.futures.Future`` with its result."""
+        import concurrent.futures
+
+        fut: "concurrent.futures.Future" = concurrent.futures.Future()
+        self._inbox.put(("call", (fn, fut)))
+        return fut
+
     def start(self) -> None:
         if self._thread is None:
             self._stop.clear()
@@ -108,6 +117,12 @@ class EngineLoop:
                 except Exception as exc:  # invalid sampling params etc.
                     req.update_status(RequestStatus.ERROR)
                     self._emit(TokenEvent(req.request_id, None, True, req.status, error=str(exc)))
+            elif kind == "call":
+                fn, fut = payload
+                try:
+                    fut.set_result(fn())
+                except BaseException as exc:
+                    fut.set_exception(exc)
             else:
                 gone = self.engine.abort_request(str(payload))
                 if gone is not None:     # cancelled before it ever ran: close its stream here

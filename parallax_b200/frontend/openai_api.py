@@ -249,6 +249,21 @@ def create_app(loop: EngineLoop, tokenizer: TokenizerWrapper, model_name: str, m
             out["choices"][0]["routed_experts"] = req.routed_experts
         return JSONResponse(out)
 
+    @app.post("/weight/refit")
+    async def weight_refit(req: HttpRequest):
+        """Online refit of a stand-alone server (cluster nodes get theirs from the scheduler): the scheduler's
+        request format, ``{"index_map": {weight: content id}, "paths": {content id: file}}``. Applied on the engine
+        thread between two steps."""
+        eng = getattr(loop, "engine", None)
+        if eng is None or not hasattr(eng, "apply_refit") or not hasattr(loop, "call"):
+            return openai_error_response("this server takes weight refits from its scheduler", status_code=404)
+        try:
+            body = await req.json()
+            used = await asyncio.wrap_future(loop.call(lambda: eng.apply_refit(body)))
+        except Exception as e:
+            return openai_error_response(f"weight refit failed: {e}", status_code=400, err_type="invalid_request_error")
+        return JSONResponse({"type": "weight_refit", "data": {"tensors": int(used)}})
+
     @app.post("/v1/chat/completions")
     async def chat_completions(req: HttpRequest):
         return await _serve(req, chat=True)

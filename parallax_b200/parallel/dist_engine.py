@@ -789,10 +789,29 @@ class DistEngine:
             self._on_mark()
         elif cmd == "elapsed":
             self._on_elapsed()
+        elif cmd == "refit":
+            from parallax_b200.utils.weight_refit import apply_refit_to_stage
+
+            apply_refit_to_stage(self.worker, self.cfg, plan["refit"])
         else:
             self._execute(plan)
             self.steps += 1
         return True
+
+    def apply_refit(self, refit: dict) -> int:
+        """Rank 0, between steps: every rank applies a refit request (``index_map`` + ``paths`` of content-addressed
+        blocks on disk) to its own layers and slices, at the same place in the order of plans; the work already
+        queued on the devices still runs with the old weights. Cached prefixes are dropped. Returns the number
+        of tensors rank 0 used."""
+        from parallax_b200.utils.weight_refit import apply_refit_to_stage
+
+        assert self.topo.rank == 0
+        self._drain_executor()
+        self.chan.publish({"cmd": "refit", "refit": refit})
+        used = apply_refit_to_stage(self.worker, self.cfg, refit)
+        for pl in self.planners:
+            pl.cache.invalidate_prefix_cache()
+        return used
 
     def finish_sends(self) -> None:
         for work, _ in self._pending_sends:

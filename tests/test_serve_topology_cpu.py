@@ -87,6 +87,42 @@ def test_serve_with_in_box_topology(model, topo, tmp_path):
         b = _post(port, body)
         assert a["usage"]["completion_tokens"] >= 1
         assert _close(_probs(a), _probs(b))      # (the second time the prompt comes from the prefix cache)
+        if model == "tiny":
+            # online refit of the in-box server: every rank reloads its own layers from the blocks on disk
+            import torch
+            from safetensors.torch import save_file
+
+            from parallax_b200.engine.engine import Engine
+            from parallax_b200.models.config import named_config
+            from parallax_b200.utils.weight_refit import calculate_cid
+            from tests.test_engine_gpu import _export_weights
+
+            other = Engine(named_config("tiny"), device="cpu", num_blocks=16, page_size=16, max_batch_size=2, seed=7)
+            w = _export_weights(other)
+            w.pop("lm_head.weight", None)
+            f = tmp_path / "all.safetensors"
+            save_file({k: v.contiguous() for k, v in w.items()}, str(f))
+            cid = calculate_cid(f.read_bytes())
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/weight/refit", headers={"Content-Type": "application/json"},
+                                         data=json.dumps({"index_map": {k: cid for k in w}, "paths": {cid: str(f)}}).encode())
+            assert urllib.request.urlopen(req, timeout=60).status == 200
+            c2 = _post(port, body)
+            assert not _close(_probs(c2), _probs(a))
+            # ... and the reply is the new model's
+            from fastapi.testclient import TestClient
+
+            from parallax_b200.engine.service import EngineLoop
+            from parallax_b200.frontend.openai_api import create_app
+            from parallax_b200.frontend.tokenizer import TokenizerWrapper
+
+            ref_loop = EngineLoop(other)
+            ref_loop.start()
+            try:
+                with TestClient(create_app(ref_loop, TokenizerWrapper.from_pretrained(None, vocab_size=1024), "tiny", 256)) as tc:
+                    want = _probs(tc.post("/v1/chat/completions", json=body).json())
+            finally:
+                ref_loop.stop()
+            assert _close(_probs(c2), want), (_probs(c2), want)
         # constrained decoding runs on the rank that samples (the last stage, or every expert-parallel lane)
         schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}
         c = _post(port, dict(body, max_tokens=80,

@@ -123,3 +123,51 @@ def test_refit_drops_cached_prefixes():
     assert live.cache.prefix_cache.hits == hits       # nothing of the old epoch was matched
     assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
     assert running.is_finished and not live.cache.reqs
+
+
+def test_refit_endpoint_of_a_stand_alone_server(tmp_path):
+    """`POST /weight/refit` on a server without a scheduler: applied on the engine thread between steps, the next
+    reply comes from the new weights; a damaged block is refused with an error and changes nothing."""
+    from fastapi.testclient import TestClient
+    from safetensors.torch import save_file
+
+    from parallax_b200.engine.service import EngineLoop
+    from parallax_b200.frontend.openai_api import create_app
+    from parallax_b200.frontend.tokenizer import TokenizerWrapper
+    from tests.test_engine_gpu import _export_weights
+
+    cfg = named_config("tiny")
+    kw = dict(device="cpu", num_blocks=64, page_size=16, max_batch_size=2, max_total_length=128)
+    live, other = Engine(cfg, seed=0, **kw), Engine(cfg, seed=7, **kw)
+    w = _export_weights(other)
+    w.pop("lm_head.weight", None)
+    f = tmp_path / "all.safetensors"
+    save_file({k: v.contiguous() for k, v in w.items()}, str(f))
+    cid = calculate_cid(f.read_bytes())
+    refit = {"time_stamp": 1, "index_map": {k: cid for k in w}, "paths": {cid: str(f)}}
+    body = {"prompt": list(range(5, 40)), "max_tokens": 4, "temperature": 0, "ignore_eos": True, "return_probs": True}
+
+    def reply(engine):
+        loop = EngineLoop(engine)
+        loop.start()
+        try:
+            with TestClient(create_app(loop, TokenizerWrapper.from_pretrained(None, vocab_size=cfg.vocab_size), "tiny", 128)) as c:
+                return c.post("/v1/completions", json=body).json()["choices"][0]["token_probs"]
+        finally:
+            loop.stop()
+
+    want = reply(other)
+    loop = EngineLoop(live)
+    loop.start()
+    try:
+        with TestClient(create_app(loop, TokenizerWrapper.from_pretrained(None, vocab_size=cfg.vocab_size), "tiny", 128)) as c:
+            before = c.post("/v1/completions", json=body).json()["choices"][0]["token_probs"]
+            assert any(abs(a - b) > 1e-4 for a, b in zip(before, want))
+            bad = dict(refit, paths={cid: str(tmp_path / "missing.safetensors")})
+            assert c.post("/weight/refit", json=bad).status_code == 400
+            r = c.post("/weight/refit", json=refit)
+            assert r.status_code == 200 and r.json()["data"]["tensors"] >= len(w) - 1
+            after = c.post("/v1/completions", json=body).json()["choices"][0]["token_probs"]
+    finally:
+        loop.stop()
+    assert all(abs(a - b) <= 1e-5 for a, b in zip(after, want)), (after, want)
