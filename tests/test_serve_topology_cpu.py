@@ -248,7 +248,7 @@ def test_two_nodes_each_tensor_parallel_over_two_ranks(model, tmp_path):
             f.close()
 
 
-@pytest.mark.parametrize("manual", [True, False])
+@pytest.mark.parametrize("manual", [True, False, "tensor-parallel nodes"])
 @_retry_startup
 def test_scheduler_and_two_joined_nodes_end_to_end(manual, tmp_path):
     """`parallax run` + two `parallax join` processes + a chat completion through the scheduler: the whole control
@@ -272,6 +272,8 @@ def test_scheduler_and_two_joined_nodes_end_to_end(manual, tmp_path):
             except OSError:
                 time.sleep(0.3)
         r0, r1 = (["--start-layer", "0", "--end-layer", "2"], ["--start-layer", "2", "--end-layer", "4"]) if manual else ([], [])
+        if manual == "tensor-parallel nodes":        # each joined node runs its layers over two ranks
+            r0, r1 = r0 + ["--tp-size", "2"], r1 + ["--tp-size", "2"]
         procs.append(subprocess.Popen(node + ["--port", str(p0)] + r0, stdout=logs[1], **kw))
         procs.append(subprocess.Popen(node + ["--port", str(p1)] + r1, stdout=logs[2], **kw))
         status = None
