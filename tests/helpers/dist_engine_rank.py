@@ -57,7 +57,8 @@ def main() -> None:
                 elif "lora" in feats and rnd.random() < 0.5:
                     adapter = rnd.choice(sorted(spec["lora"]["paths"]))
                 plan.append((rnd.randint(0, 25), Request(input_ids=ids, sampling_params=SamplingParams.from_dict(d),
-                                                         lora_path=adapter), rnd.random() < 0.15))
+                                                         lora_path=adapter, return_probs=rnd.random() < 0.4),
+                             rnd.random() < 0.15))
             reqs = [r for _a, r, _k in plan]
             step, aborted = 0, set()
             while plan or eng.has_work():
@@ -82,6 +83,9 @@ def main() -> None:
                                                for pl in eng.planners],
                                "num_blocks": eng.num_blocks, "steps": step,
                                "schema": [bool(r.sampling_params.json_schema) for r in reqs],
+                               "probs_ok": [(not r.return_probs) or (len(r.output_probs) == len(r.output_ids)
+                                                                     and all(0.0 <= p <= 1.0 + 1e-6 for p in r.output_probs))
+                                            for r in reqs],
                                "lora_pins": None if eng.lora is None else sum(eng.lora.pins.values()),
                                "grammars_known": len(eng._grammar_known)}
         elif spec.get("schema_of"):

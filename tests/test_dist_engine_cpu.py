@@ -181,7 +181,7 @@ def test_random_mix_drains_and_returns_all_memory(model, pp, tp, ep, seed, tmp_p
     for status, want, got, aborted in zip(r["status"], r["want"], _lens(r, tmp_path, pp, tp), r["aborted"]):
         assert status.startswith("FINISHED"), r
         assert got == want or status == "FINISHED_ABORT", (status, want, got, aborted)
-    assert r["live_requests"] == 0
+    assert r["live_requests"] == 0 and all(r["probs_ok"]), r
     for free, tree in zip(r["free_blocks"], r["tree_blocks"]):
         assert free + tree == r["num_blocks"], r
 
@@ -211,7 +211,7 @@ def test_random_mix_with_adapters_and_schemas(pp, tp, tmp_path):
             assert m.advance(text) and m.done, text
         elif not is_schema:
             assert len(ids) == want or status == "FINISHED_ABORT", (status, want, ids)
-    assert r["live_requests"] == 0 and r["lora_pins"] == 0 and r["grammars_known"] == 0, r
+    assert r["live_requests"] == 0 and r["lora_pins"] == 0 and r["grammars_known"] == 0 and all(r["probs_ok"]), r
 
 
 def test_random_mix_on_a_hybrid_model_with_state_snapshots(tmp_path):
