@@ -498,8 +498,8 @@ def test_router_in_front_of_a_cluster_whose_node_leaves_and_is_replaced(tmp_path
         procs["a"].wait(30)
         _wait_status(ps, "waiting", 0, 60)
         t0 = time.time()
-        code, err = _post_to(f"http://127.0.0.1:{pr}/v1/chat/completions", body, timeout=90)
-        assert code >= 400 and time.time() - t0 < 80, (code, err)          # an error, not a hang
+        code, err = _post_to(f"http://127.0.0.1:{pr}/v1/chat/completions", body, timeout=200)
+        assert code >= 400 and time.time() - t0 < 150, (code, err)         # an error, not a hang
         # a replacement joins
         procs["b"] = subprocess.Popen(node + ["--port", str(p1)], stdout=logs[3], **kw)
         _wait_status(ps, "available", 1)
@@ -619,8 +619,8 @@ def test_a_peer_that_dies_fails_requests_instead_of_hanging_them(tmp_path):
         os.killpg(procs[1].pid, signal.SIGKILL)
         procs[1].wait(10)
         t0 = time.time()
-        code, err = _post_to(f"http://127.0.0.1:{p0}/v1/chat/completions", body, timeout=60)
-        assert code >= 500 and time.time() - t0 < 30, (code, err, time.time() - t0)
+        code, err = _post_to(f"http://127.0.0.1:{p0}/v1/chat/completions", body, timeout=120)
+        assert code >= 500 and time.time() - t0 < 90, (code, err, time.time() - t0)
         procs.append(subprocess.Popen(second, stdout=logs[2], **kw))
         wait_up(p1, "/peer/info")
         # the new peer does not hold the prefix that the first peer has cached for this prompt: the first attempt may
@@ -681,8 +681,8 @@ def test_a_joined_node_that_dies_is_dropped_and_its_requests_fail_fast(tmp_path)
         os.killpg(procs[2].pid, signal.SIGKILL)
         procs[2].wait(10)
         t0 = time.time()
-        code, err = _post_to(f"http://127.0.0.1:{ps}/v1/chat/completions", body, timeout=90)
-        assert code >= 400 and time.time() - t0 < 45, (code, err, time.time() - t0)
+        code, err = _post_to(f"http://127.0.0.1:{ps}/v1/chat/completions", body, timeout=150)
+        assert code >= 400 and time.time() - t0 < 120, (code, err, time.time() - t0)
         st = _wait_status(ps, "waiting", 1, 60)                  # the silent node is gone from the list
         assert [(n["start_layer"], n["end_layer"]) for n in st["node_list"]] in ([(0, 2)], [(None, None)])
         procs.append(subprocess.Popen(node + ["--port", str(p2), "--start-layer", "2", "--end-layer", "4"], stdout=logs[3], **kw))
