@@ -272,6 +272,9 @@ class NodeRuntime:
                         num_blocks=None if device != "cpu" else 1024, log_level=args.log_level)
             self.group, self._followers = launch_followers(spec, tp)
         weights = loader.load_weights("cpu", None) if (loader is not None and self.group is None) else None
+        if self.group is not None and _lora_spec(args) is not None:
+            logger.warning("per-request LoRA adapters are not served by a tensor-parallel node; requests that name one "
+                           "are refused here (merge the adapter at load, or run the node on one GPU)")
         self.peer = PeerExecutor(cfg, start_layer, end_layer, device=device, node_id=agent.node_id,
                                  stage_group=self.group,
                                  page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
