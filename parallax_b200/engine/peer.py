@@ -89,11 +89,21 @@ class PeerExecutor:
         if lora:
             from parallax_b200.loader.lora import LoRAManager, LoRAStack
 
-            if stage_group is not None or not hasattr(self.worker.model, "lora"):
-                raise ValueError("per-request LoRA on a pipeline peer needs a single-GPU stage of a GQA decoder family")
+            if not hasattr(self.worker.model, "lora"):
+                raise ValueError("per-request LoRA on a pipeline peer needs a GQA decoder family")
             n_slots = int(lora.get("max_loaded") or 4)
-            self.worker.model.lora = LoRAStack(self.worker.model, n_slots, int(lora.get("max_rank") or 64))
-            self.lora = LoRAManager([self.worker.model.lora], n_slots, lora.get("paths"))
+            if stage_group is not None:
+                # a tensor-parallel node: the group built a sliced stack on every rank; loads go out as commands
+                from parallax_b200.loader.lora import LoRAAdapter
+
+                def load_everywhere(slot, name, path):
+                    stage_group.command("lora_load", (int(slot), name, path),
+                                        local=lambda: self.worker.model.lora.load(int(slot), LoRAAdapter.load(path, name)))
+
+                self.lora = LoRAManager([], n_slots, lora.get("paths"), on_load=load_everywhere)
+            else:
+                self.worker.model.lora = LoRAStack(self.worker.model, n_slots, int(lora.get("max_rank") or 64))
+                self.lora = LoRAManager([self.worker.model.lora], n_slots, lora.get("paths"))
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(seed + 777)
 
@@ -114,12 +124,6 @@ class PeerExecutor:
         hidden = None
         if hidden_of is not None:
             hidden = torch.cat([hidden_of[id(s)] for s in arrays["ordered"]], dim=0)
-        if self.group is not None:
-            # every rank of the node runs the stage on this plan; rank 0 (here) keeps the result
-            out = self.group.forward(arrays, hidden, want_logits=bool(arrays["owners"]))
-            if on_gpu:
-                _cuda.status_copy_async(self.device)
-            return arrays, out
         extra = None
         if self.lora is not None and any(getattr(s.req, "lora_slot", -1) >= 0 for s in arrays["ordered"]):
             import numpy as np
@@ -130,6 +134,13 @@ class PeerExecutor:
                 rows[o:o + s.num_tokens] = getattr(s.req, "lora_slot", -1)
                 o += s.num_tokens
             extra = {"lora_ids": rows}
+        if self.group is not None:
+            # every rank of the node runs the stage on this plan; rank 0 (here) keeps the result
+            out = self.group.forward(arrays, hidden, want_logits=bool(arrays["owners"]),
+                                     lora_ids=None if extra is None else extra["lora_ids"])
+            if on_gpu:
+                _cuda.status_copy_async(self.device)
+            return arrays, out
         fb = self.builder.build(arrays["ids"] if self.is_first else None, arrays["pos"], arrays["slots"],
                                 arrays["p_q"], arrays["p_ctx"], arrays["p_tables"], arrays["d_ctx"],
                                 arrays["d_tables"], arrays["logit_rows"], arrays["seq_rows"], extra=extra)

@@ -269,12 +269,9 @@ class NodeRuntime:
                         page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
                         kv_cache_dtype=getattr(args, "kv_cache_dtype", None), max_batch_size=args.max_batch_size,
                         max_num_tokens_per_batch=args.max_num_tokens_per_batch, max_total_length=args.max_sequence_length,
-                        num_blocks=None if device != "cpu" else 1024, log_level=args.log_level)
+                        num_blocks=None if device != "cpu" else 1024, log_level=args.log_level, lora=_lora_spec(args))
             self.group, self._followers = launch_followers(spec, tp)
         weights = loader.load_weights("cpu", None) if (loader is not None and self.group is None) else None
-        if self.group is not None and _lora_spec(args) is not None:
-            logger.warning("per-request LoRA adapters are not served by a tensor-parallel node; requests that name one "
-                           "are refused here (merge the adapter at load, or run the node on one GPU)")
         self.peer = PeerExecutor(cfg, start_layer, end_layer, device=device, node_id=agent.node_id,
                                  stage_group=self.group,
                                  page_size=args.kv_block_size, kv_fraction=args.kv_cache_memory_fraction,
@@ -288,7 +285,7 @@ class NodeRuntime:
                                  request_timeout_s=args.request_timeout_s, weights=weights, shared_state=state,
                                  num_blocks=(self.group.num_blocks if self.group is not None
                                              else (None if device != "cpu" else 1024)),
-                                 lora=_lora_spec(args) if self.group is None else None)
+                                 lora=_lora_spec(args))
         self.peer_urls: dict[str, str] = {}
 
         def resolve(node_id: str):

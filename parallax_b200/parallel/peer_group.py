@@ -39,7 +39,8 @@ class TPStageGroup:
     def __init__(self, cfg: ModelConfig, start_layer: int, end_layer: int, device, dtype=None, page_size: int = 16,
                  num_blocks: Optional[int] = None, kv_fraction: float = 0.8, max_batch_size: int = 8,
                  max_num_tokens_per_batch: int = 16384, max_total_length: int = 32768, seed: int = 0,
-                 weights: Optional[dict] = None, kv_cache_dtype: Optional[str] = None, fused: Optional[bool] = None):
+                 weights: Optional[dict] = None, kv_cache_dtype: Optional[str] = None, fused: Optional[bool] = None,
+                 lora: Optional[dict] = None):
         assert dist.is_initialized(), "init the node's process group first (one rank per GPU of the node)"
         from parallax_b200.models.registry import family_of
         from parallax_b200.parallel.tp_comm import CollectiveTPComm, FusedTPComm
@@ -82,16 +83,26 @@ class TPStageGroup:
         self.worker.num_blocks = self.num_blocks = int(nb)
         self.builder = BatchBuilder(self.device, max_num_tokens_per_batch + max_batch_size, max_batch_size, max_blocks)
         self.on_command = None          # followers: callable(name, payload) for commands other than a forward
+        if lora:
+            # per-request adapters: every rank keeps its slice of each resident adapter (see TPLoRAStack); rank 0
+            # decides which adapter lives in which slot and sends the loads as commands
+            from parallax_b200.loader.lora import TPLoRAStack
+
+            if not hasattr(self.worker.model, "lora") or family != "decoder":
+                raise ValueError("per-request LoRA on a tensor-parallel node needs a GQA decoder family")
+            self.worker.model.lora = TPLoRAStack(self.worker.model, int(lora.get("max_loaded") or 4),
+                                                 int(lora.get("max_rank") or 64))
         import threading
 
         self._lock = threading.Lock()   # rank 0: forwards and commands are published (and run here) one at a time
 
     # ------------------------------------------------------------------ one forward on every rank
-    def forward(self, arrays: dict, hidden: Optional[torch.Tensor], want_logits: bool):
-        """Rank 0: run the stage on a planned batch. ``hidden`` ``[T, H]`` (later peers) or None (first peer).
+    def forward(self, arrays: dict, hidden: Optional[torch.Tensor], want_logits: bool, lora_ids=None):
+        """Rank 0: run the stage on a planned batch. ``hidden`` ``[T, H]`` (later peers) or None (first peer);
+        ``lora_ids``: adapter slot of every token row (int32, -1 = none) when some request uses an adapter.
         Returns ``(stage output [T, H] or None on the last peer, logits or None)``."""
         plan = {"cmd": "fwd", "arrays": {k: arrays[k] for k in _ARRAYS}, "rows": int(arrays["pos"].shape[0]),
-                "has_hidden": hidden is not None, "want_logits": bool(want_logits)}
+                "has_hidden": hidden is not None, "want_logits": bool(want_logits), "lora_ids": lora_ids}
         with self._lock:
             self.chan.publish(plan)
             return self._execute(plan, hidden)
@@ -99,8 +110,12 @@ class TPStageGroup:
     def _execute(self, plan: dict, hidden: Optional[torch.Tensor]):
         a, T = plan["arrays"], plan["rows"]
         model = self.worker.model
+        rows_lora = plan.get("lora_ids")
         fb = self.builder.build(a["ids"] if model.is_first else None, a["pos"], a["slots"], a["p_q"], a["p_ctx"],
-                                a["p_tables"], a["d_ctx"], a["d_tables"], a["logit_rows"], a.get("seq_rows"))
+                                a["p_tables"], a["d_ctx"], a["d_tables"], a["logit_rows"], a.get("seq_rows"),
+                                extra={"lora_ids": rows_lora} if rows_lora is not None else None)
+        if rows_lora is not None:
+            fb.extras["lora_ids_host"] = rows_lora
         rp = self.comm.rows_per_rank(T)
         with torch.inference_mode():
             if plan["has_hidden"]:
@@ -169,7 +184,7 @@ def build_group(spec: dict) -> TPStageGroup:
 
         weights = ShardLoader(spec["model_path"], spec["start_layer"], spec["end_layer"]).load_weights("cpu", None)
     keys = ("page_size", "num_blocks", "kv_fraction", "max_batch_size", "max_num_tokens_per_batch", "max_total_length",
-            "seed", "kv_cache_dtype")
+            "seed", "kv_cache_dtype", "lora")
     return TPStageGroup(cfg, spec["start_layer"], spec["end_layer"], device, dtype, weights=weights,
                         **{k: spec[k] for k in keys if spec.get(k) is not None})
 
@@ -214,6 +229,11 @@ def follower_main() -> None:
             from parallax_b200.utils.weight_refit import apply_refit_to_stage
 
             apply_refit_to_stage(group.worker, cfg=group.cfg, refit=payload)
+        elif name == "lora_load":
+            from parallax_b200.loader.lora import LoRAAdapter
+
+            slot, adapter, path = payload
+            group.worker.model.lora.load(int(slot), LoRAAdapter.load(path, adapter))
 
     group.on_command = on_command
     try:

@@ -198,7 +198,7 @@ def test_two_nodes_with_manual_layer_ranges_and_no_scheduler(tmp_path):
     assert me.route(9) is None
 
 
-@pytest.mark.parametrize("model", ["tiny", "tiny-hybrid"])
+@pytest.mark.parametrize("model", ["tiny", "tiny-hybrid", "tiny+lora"])
 @_retry_startup
 def test_two_nodes_each_tensor_parallel_over_two_ranks(model, tmp_path):
     """Two pipeline peers without a scheduler, each running its half of the layers tensor-parallel over two
@@ -206,8 +206,21 @@ def test_two_nodes_each_tensor_parallel_over_two_ranks(model, tmp_path):
     through the node's control channel. Same reply as one process with all layers."""
     p0, p1, p2 = free_port(), free_port(), free_port()
     env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    lora_flags, adapter = [], None
+    if model.endswith("+lora"):
+        # per-request adapters on tensor-parallel nodes: every rank keeps its slice, loads travel as commands
+        from parallax_b200.models.config import named_config
+        from tests.test_lora_cpu import _make_adapter
+
+        model = model.split("+")[0]
+        root = tmp_path if tmp_path.name != "second_try" else tmp_path.parent
+        paths = {n: (str(root / n) if (root / n).exists() else _make_adapter(named_config(model), root / n, seed))
+                 for seed, n in enumerate(("x", "y"), 1)}
+        lora_flags = ["--enable-lora", "--lora-paths"] + [f"{n}={d}" for n, d in paths.items()]
+        adapter = "x"
     common = [sys.executable, "-m", "parallax_b200.launch", "--model-path", model, "--random-init", "--host", "127.0.0.1",
               "--max-batch-size", "4", "--max-sequence-length", "256", "--log-level", "WARNING"]
+    common = common + lora_flags
     logs = [open(tmp_path / f"n{i}.log", "w") for i in range(3)]
     kw = dict(cwd=ROOT, env=env, stderr=subprocess.STDOUT, start_new_session=True)
     procs = [
@@ -232,9 +245,14 @@ def test_two_nodes_each_tensor_parallel_over_two_ranks(model, tmp_path):
                 raise _StartupError("".join(open(tmp_path / f"n{i}.log").read()[-2000:] for i in range(3)))
         for content, n in (("hello there", 8), ("a much longer prompt " * 6, 5)):
             body = {"model": model, "messages": [{"role": "user", "content": content}], "max_tokens": n, "temperature": 0, "return_probs": True}
+            if adapter is not None:
+                plain = _probs(_post(p0, body))
+                body["lora_path"] = adapter
             split, whole = _post(p0, body), _post(p2, body)
             assert split["usage"]["completion_tokens"] == whole["usage"]["completion_tokens"] >= 1
             assert _close(_probs(split), _probs(whole)), (_probs(split), _probs(whole))
+            if adapter is not None:
+                assert not _close(_probs(split), plain)        # the adapter changes the reply
     finally:
         for p in procs:
             if p.poll() is None:
