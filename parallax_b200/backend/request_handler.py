@@ -12,6 +12,7 @@ from __future__ import annotations
 import asyncio
 import json
 import logging
+import os
 import time
 from typing import Optional
 
@@ -29,8 +30,9 @@ logger = logging.getLogger(__name__)
 class RequestHandler:
     MAX_FORWARD_RETRY = 10
     MAX_ROUTING_RETRY = 20
-    FORWARD_DELAY_SEC = 10
-    RETRY_DELAY_SEC = 5
+    # seconds between attempts (the reference's 10 and 5); the environment can shorten them for small clusters
+    FORWARD_DELAY_SEC = float(os.environ.get("PARALLAX_FORWARD_RETRY_DELAY_S", "10"))
+    RETRY_DELAY_SEC = float(os.environ.get("PARALLAX_ROUTING_RETRY_DELAY_S", "5"))
 
     def __init__(self, http_client_factory=None):
         self.scheduler_manage = None
