@@ -14,6 +14,9 @@ import pytest
 from parallax_b200.parallel.launcher import free_port
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# the tests below run up to five model processes at once on tiny models: two threads each is plenty, and it keeps
+# them from fighting over the cores (inherited by every child process; torch is already loaded here)
+os.environ.setdefault("OMP_NUM_THREADS", "2")
 
 
 class _StartupError(AssertionError):
