@@ -669,8 +669,9 @@ def test_a_peer_that_dies_fails_requests_instead_of_hanging_them(tmp_path):
             f.close()
 
 
+@pytest.mark.parametrize("victim", ["last", "first"])
 @_retry_startup
-def test_a_joined_node_that_dies_is_dropped_and_its_requests_fail_fast(tmp_path):
+def test_a_joined_node_that_dies_is_dropped_and_its_requests_fail_fast(victim, tmp_path):
     """Scheduler + two hand-placed nodes; the second is killed outright (no goodbye). Requests routed through the
     broken pipeline end with an error within seconds, the scheduler drops the silent node after its heartbeat
     time-out and reports the cluster as waiting; when a node takes the vacant layers the cluster serves again."""
@@ -703,14 +704,17 @@ def test_a_joined_node_that_dies_is_dropped_and_its_requests_fail_fast(tmp_path)
         procs.append(subprocess.Popen(node + ["--port", str(p1), "--start-layer", "2", "--end-layer", "4"], stdout=logs[2], **kw))
         _wait_status(ps, "available", 2)
         fp = _probs(chat_ok())
-        os.killpg(procs[2].pid, signal.SIGKILL)
-        procs[2].wait(10)
+        k = 2 if victim == "last" else 1            # the node that samples, or the one the scheduler forwards to
+        os.killpg(procs[k].pid, signal.SIGKILL)
+        procs[k].wait(10)
         t0 = time.time()
         code, err = _post_to(f"http://127.0.0.1:{ps}/v1/chat/completions", body, timeout=150)
         assert code >= 400 and time.time() - t0 < 120, (code, err, time.time() - t0)
         st = _wait_status(ps, "waiting", 1, 60)                  # the silent node is gone from the list
-        assert [(n["start_layer"], n["end_layer"]) for n in st["node_list"]] in ([(0, 2)], [(None, None)])
-        procs.append(subprocess.Popen(node + ["--port", str(p2), "--start-layer", "2", "--end-layer", "4"], stdout=logs[3], **kw))
+        left = (0, 2) if victim == "last" else (2, 4)
+        assert [(n["start_layer"], n["end_layer"]) for n in st["node_list"]] in ([left], [(None, None)])
+        vacant = ["--start-layer", "2", "--end-layer", "4"] if victim == "last" else ["--start-layer", "0", "--end-layer", "2"]
+        procs.append(subprocess.Popen(node + ["--port", str(p2)] + vacant, stdout=logs[3], **kw))
         _wait_status(ps, "available", 2)
         assert _close(_probs(chat_ok()), fp)
     finally:
