@@ -159,6 +159,8 @@ def run_multi_gpu(args, cfg, name: str, path: Optional[str]) -> None:
                 enable_prefix_cache=args.enable_prefix_cache, max_total_length=args.max_sequence_length,
                 request_timeout_s=args.request_timeout_s, num_blocks=None if device_type == "cuda" else 1024,
                 lora_paths=(args.lora_paths or []) if args.enable_lora else [], log_level=args.log_level)
+    if getattr(args, "enable_return_routed_experts", False):
+        logger.warning("--enable-return-routed-experts is served by the single-process engine only; ignored here")
     from parallax_b200.launch import _lora_spec
 
     per_request = _lora_spec(args)
