@@ -46,6 +46,7 @@ class EngineLoop:
         self._thread: Optional[threading.Thread] = None
         self.steps = 0
         self.errors = 0
+        self._reported = -1          # 0 once the idle load has been written to the shared metrics
 
     # ---- client side (any thread)
     def submit(self, req: Request) -> "queue.Queue[TokenEvent]":
@@ -145,8 +146,15 @@ class EngineLoop:
         while not self._stop.is_set():
             self._drain_inbox()
             if not eng.has_work():
+                if self.shared_state is not None and self._reported != 0:
+                    try:        # the reported load follows the engine to idle (see the peer loop)
+                        self.shared_state.update_metrics(current_requests=0)
+                        self._reported = 0
+                    except Exception:
+                        pass
                 time.sleep(self.idle_sleep_s)
                 continue
+            self._reported = -1
             t0 = time.perf_counter()
             try:
                 results = eng.step()

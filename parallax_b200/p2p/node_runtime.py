@@ -43,6 +43,7 @@ class PeerLoop:
         self._thread: Optional[threading.Thread] = None
         self.steps = 0
         self.default_route = None       # callable -> routing table for requests that arrive without one
+        self._reported = -1             # request count last written to the shared metrics
 
     # ---- frontend side
     def submit(self, req: Request):
@@ -212,6 +213,16 @@ class PeerLoop:
                 if self.state is not None and (packets or events):
                     self.state.update_metrics(current_requests=peer.scheduler.num_running_requests,
                                               layer_latency_ms_sample=(time.perf_counter() - t0) * 1e3 / n_layers)
+            # the load this node reports with its heartbeats must follow the requests it holds, also when the last
+            # ones end without another step (a count left over from a busy moment made the scheduler answer 429)
+            holding = peer.scheduler.num_running_requests + peer.scheduler.num_queued_requests if peer.is_first \
+                else len(peer.mirror)
+            if self.state is not None and holding != self._reported:
+                try:
+                    self.state.update_metrics(current_requests=holding)
+                    self._reported = holding
+                except Exception:
+                    pass
             if not busy:
                 time.sleep(self.idle_sleep_s)
 
@@ -229,6 +240,15 @@ def create_peer_app(loop: PeerLoop, tokenizer=None, model_name: str = "", max_mo
         @app.get("/health")
         async def health():
             return {"status": "ok", "steps": loop.steps}
+
+    @app.get("/peer/stats")
+    async def peer_stats():
+        """What this peer currently holds: requests in its scheduler, shadow requests of later peers, requests with
+        KV memory, open client streams, steps run."""
+        p = loop.peer
+        return {"node_id": p.node_id, "layers": [p.worker.start_layer, p.worker.end_layer], "steps": loop.steps,
+                "running": p.scheduler.num_running_requests + p.scheduler.num_queued_requests, "mirror": len(p.mirror),
+                "kv_requests": len(p.cache.reqs), "free_blocks": p.cache.num_free_blocks(), "streams": loop.num_inflight}
 
     @app.post("/pp_forward")
     async def pp_forward(req: HttpRequest):

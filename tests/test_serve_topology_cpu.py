@@ -320,6 +320,38 @@ def test_scheduler_and_two_joined_nodes_end_to_end(manual, tmp_path):
         assert reply is not None and reply["usage"]["completion_tokens"] >= 1, tails
         again = _post(ps, body, timeout=60)
         assert _close(_probs(again), _probs(reply))
+        if manual is True:
+            # a burst of clients through the scheduler, half of which hang up mid-stream: afterwards neither node holds
+            # a request, a shadow request, KV memory or an open stream
+            import threading
+
+            def client(i: int) -> None:
+                b = dict(body, max_tokens=24, ignore_eos=True, stream=True,
+                         messages=[{"role": "user", "content": f"client number {i} " * (1 + i % 3)}])
+                rq = urllib.request.Request(f"http://127.0.0.1:{ps}/v1/chat/completions", data=json.dumps(b).encode(),
+                                            headers={"Content-Type": "application/json"})
+                with urllib.request.urlopen(rq, timeout=120) as resp:
+                    seen = 0
+                    for line in resp:
+                        if line.startswith(b"data: "):
+                            seen += 1
+                            if i % 2 == 0 and seen >= 3:
+                                return                      # leaving closes the connection mid-stream
+
+            threads = [threading.Thread(target=client, args=(i,)) for i in range(8)]
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join(150)
+            assert not any(t.is_alive() for t in threads)
+            deadline = time.time() + 60
+            stats = None
+            while time.time() < deadline:
+                stats = [json.loads(urllib.request.urlopen(f"http://127.0.0.1:{p}/peer/stats", timeout=5).read()) for p in (p0, p1)]
+                if all(st["running"] == st["mirror"] == st["kv_requests"] == st["streams"] == 0 for st in stats):
+                    break
+                time.sleep(0.5)
+            assert all(st["running"] == st["mirror"] == st["kv_requests"] == st["streams"] == 0 for st in stats), stats
         # a JSON-schema request through the scheduler: the last node samples under the schema
         schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}
         constrained = _post(ps, dict(body, max_tokens=80, response_format={"type": "json_schema",
