@@ -126,6 +126,35 @@ def test_serve_with_in_box_topology(model, topo, tmp_path):
             finally:
                 ref_loop.stop()
             assert _close(_probs(c2), want), (_probs(c2), want)
+        # a burst of clients, half of which hang up mid-stream; the server then still answers as before
+        import threading
+
+        errors = []
+
+        def client(i: int) -> None:
+            try:
+                b = dict(body, max_tokens=20, ignore_eos=True, stream=True,
+                         messages=[{"role": "user", "content": f"client number {i} " * (1 + i % 3)}])
+                rq = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=json.dumps(b).encode(),
+                                            headers={"Content-Type": "application/json"})
+                with urllib.request.urlopen(rq, timeout=120) as resp:
+                    seen = 0
+                    for line in resp:
+                        if line.startswith(b"data: "):
+                            seen += 1
+                            if i % 2 == 0 and seen >= 3:
+                                return
+            except Exception as e:      # noqa: BLE001
+                errors.append(repr(e))
+
+        threads = [threading.Thread(target=client, args=(i,)) for i in range(8)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(150)
+        assert not errors and not any(t.is_alive() for t in threads), errors
+        after_burst = _post(port, body)
+        assert after_burst["usage"]["completion_tokens"] == b["usage"]["completion_tokens"]
         # constrained decoding runs on the rank that samples (the last stage, or every expert-parallel lane)
         schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"]}
         c = _post(port, dict(body, max_tokens=80,
