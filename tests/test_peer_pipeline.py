@@ -246,3 +246,39 @@ def test_every_model_family_through_chained_peers():
         assert got == want, name
         for p in peers:
             assert not p.cache.reqs and not p.mirror, name
+
+
+def test_request_time_out_releases_every_peer():
+    """The time-out counts the time without progress (as in the reference, ``src/parallax/server/scheduler.py:314-333``):
+    when the next peer stops answering, the first peer aborts the request after `request_timeout_s`, every peer releases
+    it, and the pipeline serves the next request as if nothing had happened."""
+    import time
+
+    cfg = named_config("tiny")
+    peers = [PeerExecutor(cfg, s, e, device="cpu", node_id=f"n{i}", num_blocks=64, max_batch_size=4, request_timeout_s=0.3)
+             for i, (s, e) in enumerate([(0, 2), (2, 4)])]
+    table = [p.node_id for p in peers]
+    slow = Request(input_ids=list(range(3, 30)), routing_table=table,
+                   sampling_params=SamplingParams(max_new_tokens=500, temperature=0.0, ignore_eos=True))
+    peers[0].add_request(slow)
+    events, pending_releases = [], []
+    deadline = time.time() + 20
+    steps = 0
+    while peers[0].has_work() and time.time() < deadline:
+        steps += 1
+        packets, ev, releases = peers[0].step_first()
+        events += ev
+        pending_releases += releases
+        if steps <= 5:                                   # the second peer answers for five steps, then goes silent
+            back = peers[1].process_packets(_wire(packets))
+            ev, releases = peers[0].receive_tokens(_wire([p for p in back if p.hidden_states is None]))
+            events += ev
+            pending_releases += releases
+        time.sleep(0.02)
+    assert slow.status.name == "FINISHED_ABORT" and 0 < len(slow.output_ids) <= 5
+    assert any(r is slow and r.is_finished for r, _t in events) and slow.request_id in pending_releases
+    peers[1].release(pending_releases)                   # the abort notice reaches the silent peer when it is back
+    for p in peers:
+        assert not p.cache.reqs and not p.mirror
+    got, _ = _run_pipeline(cfg, [(0, 2), (2, 4)], _prompts(1, 12, cfg.vocab_size, seed=1), 3)
+    assert len(got[0]) == 3
