@@ -282,3 +282,13 @@ def test_request_time_out_releases_every_peer():
         assert not p.cache.reqs and not p.mirror
     got, _ = _run_pipeline(cfg, [(0, 2), (2, 4)], _prompts(1, 12, cfg.vocab_size, seed=1), 3)
     assert len(got[0]) == 3
+
+
+def test_e4m3_kv_pages_through_chained_peers():
+    cfg = named_config("tiny")
+    prompts = _prompts(3, 37, cfg.vocab_size, seed=2)
+    want = Engine(cfg, device="cpu", num_blocks=128, max_batch_size=8, kv_cache_dtype="fp8_e4m3").generate(
+        prompts, SamplingParams(max_new_tokens=6, temperature=0.0, ignore_eos=True))
+    got, peers = _run_pipeline(cfg, [(0, 2), (2, 4)], prompts, 6, kv_cache_dtype="fp8_e4m3")
+    assert got == want
+    assert all(p.worker.pool.layers[0].kv_scale is not None for p in peers)
